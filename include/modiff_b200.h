@@ -1,0 +1,210 @@
+/*
+ * modiff_b200.h -- C ABI of libmodiff_b200.so
+ *
+ * Hand-written sm_100a CUDA for the modulated-quantization UNet sampling path of
+ * MoDiff (qdiff.QuantModel / QuantModule / UniformAffineQuantizer).  The reference
+ * has no native boundary: its arithmetic lives in Python/PyTorch, so every entry
+ * point below cites the reference Python it stands in for (path:line inside the
+ * reference project).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
+ *     nothing synchronises the device;
+ *   - no entry point allocates device memory: callers own every buffer;
+ *   - every function returns MODIFF_OK (0) or a negative/positive error code and
+ *     leaves a human-readable message for modiff_last_error() (thread local);
+ *   - fp32 activation tensors are NCHW (linear layers: rows x features, i.e.
+ *     N = rows, H = W = 1); integer code tensors use the private layout below.
+ *
+ * Activation-code layout ("code planes")
+ *   int8 [batch * nplanes][hp][wp][cp], nplanes = stride*stride,
+ *   cp = round_up(cin, 16), hp = ceil((h + pad_t + pad_b) / stride),
+ *   wp = ceil((w + pad_l + pad_r) / stride).
+ *   Input pixel (y, x) of image n lives at padded coordinate (y + pad_t, x + pad_l),
+ *   plane ((y + pad_t) % stride) * stride + (x + pad_l) % stride, row
+ *   (y + pad_t) / stride, column (x + pad_l) / stride.  Halo positions and padded
+ *   channels are never written: the caller zero-fills the buffer once.
+ *
+ * Weight-code layout
+ *   int8 [cout_rows][kh*kw][kp], kp = round_up(cin, 128); value = q - zoff with
+ *   zoff chosen per output channel so the value fits int8; w_corr = zoff - zp is
+ *   the integer to multiply with the receptive-field sum of activation codes.
+ */
+#ifndef MODIFF_B200_H_
+#define MODIFF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MODIFF_OK 0
+#define MODIFF_ERR_INVALID 1     /* bad argument / unsupported geometry */
+#define MODIFF_ERR_CUDA 2        /* a CUDA runtime / driver call failed */
+#define MODIFF_ERR_UNSUPPORTED 3 /* this build or device cannot run the request */
+#define MODIFF_ERR_DEVICE 4      /* a kernel reported a bounded wait that ran out */
+
+#define MODIFF_IMPL_AUTO 0
+#define MODIFF_IMPL_SIMT 1     /* dp4a CUDA-core implicit GEMM (any geometry) */
+#define MODIFF_IMPL_TCGEN05 2  /* tcgen05 kind::i8 tensor-core implicit GEMM */
+
+/* Geometry of one conv2d / conv1d(k=1) / linear layer.
+ * Mirrors the kwargs captured by QuantModule.__init__ (qdiff/quant_layer.py:268-278). */
+typedef struct modiff_conv_geom {
+  int32_t batch;  /* images, or rows for a linear layer */
+  int32_t cin;
+  int32_t cout;
+  int32_t h, w;   /* input spatial size; 1,1 for linear */
+  int32_t kh, kw;
+  int32_t stride; /* 1 or 2 */
+  int32_t pad_t, pad_l, pad_b, pad_r;
+  int32_t split;  /* 0, or the channel count of the first activation/weight segment
+                     (qdiff/quant_layer.py:313-319, 330-333, 346-349) */
+} modiff_conv_geom;
+
+/* Library / device information. */
+int modiff_version(void);
+const char* modiff_last_error(void);
+/* Fills sm_count, cc_major, cc_minor of the current device (host pointers). */
+int modiff_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/* Reads (and optionally clears) the sticky device status word: non-zero after a kernel
+ * gave up on a bounded wait.  Synchronises the device.  `status` is a host pointer. */
+int modiff_device_status(int* status, int reset);
+
+/* Sizes (host side helpers, no device work). */
+int64_t modiff_codes_bytes(const modiff_conv_geom* g);      /* activation-code buffer */
+int64_t modiff_wcodes_bytes(const modiff_conv_geom* g, int with_sum_rows);
+int32_t modiff_out_h(const modiff_conv_geom* g);
+int32_t modiff_out_w(const modiff_conv_geom* g);
+/* cout rows stored per 128-channel tile when the tcgen05 kernel needs the
+ * receptive-field sum (one all-ones row + 15 zero rows are appended per tile). */
+int32_t modiff_wcodes_rows(const modiff_conv_geom* g, int with_sum_rows);
+
+/* Per-output-channel asymmetric weight quantisation, done once per weight tensor.
+ * Replaces UniformAffineQuantizer.init_quantization_scale(channel_wise=True)
+ * + forward on weights (qdiff/quant_layer.py:160-190, 94-102, 345-351).
+ *   w        fp32 [cout][cin][kh*kw] (PyTorch conv/linear layout)
+ *   wcodes   int8 weight-code layout (see top); with_sum_rows != 0 selects the
+ *            tiled layout [cout/128 tiles][144 rows] used by the tcgen05 kernel
+ *            when any w_corr is non-zero
+ *   w_scale  fp32 [2][cout]  delta per segment (row 1 unused without split)
+ *   w_zp     fp32 [2][cout]  zero point per segment (as the reference stores it)
+ *   w_corr   int32 [2][cout] zoff - zp
+ *   w_dq     fp32 [cin*kh*kw][cout]  dequantised weights (q - zp) * delta, K order
+ *            (cin, ky, kx), for the first (unquantised-activation) step; may be NULL
+ */
+int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
+                       int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
+                       int32_t* w_corr, float* w_dq, void* stream);
+
+/* Modulated activation quantiser: r = x - a_hat, dynamic symmetric per-tensor (or
+ * per-segment with split) scale, round-half-even codes, a_hat += code * delta.
+ * Replaces QuantModule.forward lines qdiff/quant_layer.py:325-336 together with
+ * UniformAffineQuantizer.forward (:81-102) and init_quantization_scale (:191-214).
+ *   x        fp32 NCHW [batch][cin][h][w]
+ *   a_hat    fp32 NCHW, updated in place; NULL = plain (non-modulated) quantisation
+ *   codes    int8 code planes (see top)
+ *   x_scale  fp32 [2] out: delta of segment 0 / 1
+ *   scratch  at least MODIFF_MODQ_SCRATCH_BYTES, zero-filled once by the caller;
+ *            the kernels leave it zeroed again
+ *   per_sample != 0: one scale per image (channel_wise activations, dim 0 = batch,
+ *            qdiff/quant_layer.py:160-190); x_scale then has [batch] entries and
+ *            split must be 0
+ */
+#define MODIFF_MODQ_SCRATCH_BYTES 64
+int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                void* stream);
+
+/* Int8 implicit-GEMM conv / linear with the modulation epilogue
+ *   out = acc0 * (x_scale[0] * w_scale[0][c]) (+ acc1 * (x_scale[1] * w_scale[1][c]))
+ *         (+ o_hat) (+ bias[c]);   acc = sum codes * (wcodes + w_corr)
+ * Replaces F.conv2d / F.linear on fake-quantised operands plus "out = o_hat + out;
+ * o_hat = out" (qdiff/quant_layer.py:357-365).
+ *   o_hat    fp32 NCHW [batch][cout][ho][wo]; read when accumulate != 0, always written
+ *   bias     fp32 [cout] or NULL
+ *   w_corr   may be NULL when all corrections are zero
+ *   impl     MODIFF_IMPL_*; AUTO picks tcgen05 when the geometry allows it
+ *   acc_out  optional int32 [batch*ho*wo][cout] raw corrected accumulators of
+ *            segment 0 (+ segment 1 at offset batch*ho*wo*cout) for parity tests
+ */
+int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                      const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                      float* o_hat, int accumulate, const float* bias,
+                      const modiff_conv_geom* g, int per_sample, int impl,
+                      int32_t* acc_out, void* stream);
+
+/* First-step conv / linear: fp32 activations x dequantised weights + bias
+ * (qdiff/quant_layer.py:326-327, 358-359; also the weight-only-quant and
+ * unquantised paths :309-311, :364-365).
+ *   x fp32 NCHW, w_kn fp32 [cin*kh*kw][cout] (K order cin,ky,kx), out fp32 NCHW. */
+int modiff_conv_fp32(const float* x, const float* w_kn, const float* bias, float* out,
+                     const modiff_conv_geom* g, void* stream);
+
+/* Stand-alone fake quantiser returning the dequantised tensor
+ * (UniformAffineQuantizer.forward, qdiff/quant_layer.py:70-111; scale rules
+ * :160-214).  Supports symmetric / asymmetric, per-tensor ('max') and per-dim-0
+ * slice scales, always_zero.
+ *   x, y     fp32, `slices` x `slice_len` elements (slices = 1 for per-tensor)
+ *   delta,zp fp32 [slices] out (in when dynamic == 0 and inited != 0)
+ *   scratch  at least 16 * slices + 64 bytes, zero-filled once by the caller
+ */
+int modiff_fake_quant(const float* x, float* y, int64_t slices, int64_t slice_len,
+                      int n_bits, int symmetric, int always_zero, int channel_wise,
+                      int recompute, float* delta, float* zp, void* scratch, void* stream);
+
+/* GroupNorm (+ optional SiLU) over NCHW fp32: y = act(gn(x) * gamma + beta).
+ * Replaces Normalize + nonlinearity (ddim/models/diffusion.py:27-33, 121-128,
+ * 356-357).  x may be given as two channel-concatenated tensors (x0: c0 channels,
+ * x1: c - c0 channels; x1 NULL when c0 == c), which fuses the torch.cat of the
+ * up path (ddim/models/diffusion.py:345-349). */
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, float* y,
+                          const float* gamma, const float* beta, int batch, int c, int hw,
+                          int groups, float eps, int silu, void* stream);
+
+/* y = x * sigmoid(x)  (ddim/models/diffusion.py:27-29). */
+int modiff_silu(const float* x, float* y, int64_t n, void* stream);
+
+/* out = a + b, where b is either a full tensor (b_per_channel == 0) or a
+ * [batch][c] tensor broadcast over hw (the "+ temb_proj(...)[:, :, None, None]" of
+ * ddim/models/diffusion.py:124). */
+int modiff_add(const float* a, const float* b, float* out, int batch, int c, int hw,
+               int b_per_channel, void* stream);
+
+/* Nearest-neighbour 2x upsample NCHW (ddim/models/diffusion.py:47-48). */
+int modiff_upsample2x(const float* x, float* y, int batch, int c, int h, int w, void* stream);
+
+/* Channel concat of two NCHW tensors (ddim/models/diffusion.py:345-349). */
+int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, int batch,
+                    int hw, void* stream);
+
+/* Sinusoidal timestep embedding [batch][dim] (ddim/models/diffusion.py:6-24). */
+int modiff_timestep_embedding(const float* t, float* emb, int batch, int dim, void* stream);
+
+/* One DDIM (generalised) update (ddim/functions/denoising.py:30-48):
+ *   x0 = (x - e*s1) / s2;  x' = s3*x0 + c1*noise + c2*e
+ * with the host scalars s1 = sqrt(1-at), s2 = sqrt(at), s3 = sqrt(at_next) and c1, c2
+ * as the reference computes them in fp32.  noise may be NULL (eta = 0); x0 may be NULL. */
+int modiff_ddim_step(const float* x, const float* e, const float* noise, float* x_next,
+                     float* x0, int64_t n, float s1, float s2, float s3, float c1, float c2,
+                     void* stream);
+
+/* int4 nibble pack / unpack of int8 codes: element 2i -> low nibble, 2i+1 -> high
+ * nibble, two's complement (qdiff/quant_layer_int4.py:341-346, 354-366). */
+int modiff_pack_int4(const int8_t* codes, uint8_t* packed, int64_t n, void* stream);
+int modiff_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n, int is_signed,
+                       void* stream);
+
+/* NCHW fp32 -> code planes without modulation state: codes = clamp(rne(x / delta))
+ * with a given scale (layout transform used by tests and by static-scale callers). */
+int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
+                           const modiff_conv_geom* g, int n_bits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MODIFF_B200_H_ */

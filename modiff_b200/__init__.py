@@ -1,0 +1,16 @@
+"""B200-native (sm_100a) implementation of MoDiff's modulated-quantisation UNet sampling path
+behind qdiff's Python API.  See include/modiff_b200.h for the C ABI the modules call into."""
+from ._lib import ModiffError, lib, device_status
+from .quant_layer import QuantModule, UniformAffineQuantizer, StraightThrough, round_ste
+from .quant_block import BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, get_specials
+from .quant_model import QuantModel
+from .unet import Model, make_config
+from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
+                      make_timestep_sequence)
+
+__all__ = [
+    "ModiffError", "lib", "device_status", "QuantModule", "UniformAffineQuantizer",
+    "StraightThrough", "round_ste", "BaseQuantBlock", "QuantResnetBlock", "QuantAttnBlock",
+    "get_specials", "QuantModel", "Model", "make_config", "generalized_steps", "compute_alpha",
+    "get_beta_schedule", "make_timestep_sequence",
+]

@@ -1,0 +1,123 @@
+"""ctypes binding of libmodiff_b200.so (the C ABI declared in include/modiff_b200.h).
+
+There is no CPU fallback: `lib()` raises if the shared library is missing, and every
+wrapper raises `ModiffError` when an entry point returns a non-zero status.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmodiff_b200.so")
+
+IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2
+MODQ_SCRATCH_BYTES = 64
+
+
+class ModiffError(RuntimeError):
+    pass
+
+
+class ConvGeom(C.Structure):
+    """Mirror of `modiff_conv_geom`."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "batch", "cin", "cout", "h", "w", "kh", "kw", "stride",
+        "pad_t", "pad_l", "pad_b", "pad_r", "split")]
+
+    def key(self):
+        return tuple(getattr(self, n) for n, _ in self._fields_)
+
+    def copy(self, **kw):
+        g = ConvGeom(*[getattr(self, n) for n, _ in self._fields_])
+        for k, v in kw.items():
+            setattr(g, k, v)
+        return g
+
+
+_P = C.c_void_p
+_G = C.POINTER(ConvGeom)
+
+# name -> (restype, argtypes); one entry per declaration of include/modiff_b200.h
+SIGNATURES = {
+    "modiff_version": (C.c_int, []),
+    "modiff_last_error": (C.c_char_p, []),
+    "modiff_device_info": (C.c_int, [C.POINTER(C.c_int)] * 3),
+    "modiff_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "modiff_codes_bytes": (C.c_int64, [_G]),
+    "modiff_wcodes_bytes": (C.c_int64, [_G, C.c_int]),
+    "modiff_out_h": (C.c_int32, [_G]),
+    "modiff_out_w": (C.c_int32, [_G]),
+    "modiff_wcodes_rows": (C.c_int32, [_G, C.c_int]),
+    "modiff_weight_pack": (C.c_int, [_P, _G, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P]),
+    "modiff_modq": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P, _P]),
+    "modiff_igemm_conv": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P, _G, C.c_int,
+                                    C.c_int, _P, _P]),
+    "modiff_conv_fp32": (C.c_int, [_P, _P, _P, _P, _G, _P]),
+    "modiff_fake_quant": (C.c_int, [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                    C.c_int, C.c_int, _P, _P, _P, _P]),
+    "modiff_groupnorm_silu": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int,
+                                        C.c_int, C.c_float, C.c_int, _P]),
+    "modiff_silu": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "modiff_add": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "modiff_upsample2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "modiff_concat_c": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_int, _P]),
+    "modiff_timestep_embedding": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),
+    "modiff_ddim_step": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64] + [C.c_float] * 5 + [_P]),
+    "modiff_pack_int4": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "modiff_unpack_int4": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
+    "modiff_quantize_static": (C.c_int, [_P, _P, _P, _G, C.c_int, _P]),
+}
+
+_lib = None
+
+
+def lib():
+    """Load the shared library once; fail loudly when it was not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ModiffError(
+                f"{LIB_PATH} is missing: build it with `python -m modiff_b200.build` "
+                "(there is no CPU or PyTorch fallback for the quantised path)")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        msg = lib().modiff_last_error().decode(errors="replace")
+        raise ModiffError(f"libmodiff_b200 error {rc}: {msg}")
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(t, what="tensor"):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ModiffError(
+            f"{what} must be a CUDA tensor: the quantised path runs only on the GPU "
+            "(no CPU fallback)")
+    if t.dtype != torch.float32:
+        raise ModiffError(f"{what} must be float32, got {t.dtype}")
+
+
+def device_status(reset=True):
+    s = C.c_int(0)
+    check(lib().modiff_device_status(C.byref(s), 1 if reset else 0))
+    return s.value
+
+
+def out_hw(g):
+    return lib().modiff_out_h(C.byref(g)), lib().modiff_out_w(C.byref(g))

@@ -1,0 +1,73 @@
+// Shared host/device helpers for libmodiff_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "modiff_b200.h"
+
+namespace modiff {
+
+// Thread-local message buffer behind modiff_last_error().
+char* error_buffer();
+int set_error(int code, const char* fmt, ...);
+
+#define MODIFF_CHECK_ARG(cond, ...)                                   \
+  do {                                                                \
+    if (!(cond)) return ::modiff::set_error(MODIFF_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define MODIFF_CUDA(call)                                                         \
+  do {                                                                            \
+    cudaError_t e__ = (call);                                                     \
+    if (e__ != cudaSuccess)                                                       \
+      return ::modiff::set_error(MODIFF_ERR_CUDA, "%s failed: %s (%s:%d)", #call, \
+                                 cudaGetErrorString(e__), __FILE__, __LINE__);    \
+  } while (0)
+
+#define MODIFF_LAUNCH_CHECK(name)                                                 \
+  do {                                                                            \
+    cudaError_t e__ = cudaGetLastError();                                         \
+    if (e__ != cudaSuccess)                                                       \
+      return ::modiff::set_error(MODIFF_ERR_CUDA, "launch of %s failed: %s", name, \
+                                 cudaGetErrorString(e__));                        \
+  } while (0)
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
+
+// Derived quantities of a layer geometry (host and device).
+struct Derived {
+  int ho, wo;        // output spatial size
+  int hp, wp;        // code-plane rows / columns
+  int cp;            // channels stored per code pixel (multiple of 16)
+  int kp;            // weight K stride per tap (multiple of 128)
+  int nplanes;       // stride * stride
+  int taps;          // kh * kw
+  int nseg;          // 1, or 2 with split
+};
+
+__host__ __device__ inline Derived derive(const modiff_conv_geom& g) {
+  Derived d;
+  d.ho = (g.h + g.pad_t + g.pad_b - g.kh) / g.stride + 1;
+  d.wo = (g.w + g.pad_l + g.pad_r - g.kw) / g.stride + 1;
+  d.hp = ceil_div(g.h + g.pad_t + g.pad_b, g.stride);
+  d.wp = ceil_div(g.w + g.pad_l + g.pad_r, g.stride);
+  d.cp = round_up(g.cin, 16);
+  d.kp = round_up(g.cin, 128);
+  d.nplanes = g.stride * g.stride;
+  d.taps = g.kh * g.kw;
+  d.nseg = g.split > 0 ? 2 : 1;
+  return d;
+}
+
+int validate_geom(const modiff_conv_geom* g);
+
+// Symmetric activation code range of an n-bit quantiser
+// (n_levels = 2^(b-1) - 1; clamp(-n_levels - 1, n_levels)).
+__host__ __device__ inline int sym_levels(int n_bits) { return (1 << (n_bits - 1)) - 1; }
+
+}  // namespace modiff

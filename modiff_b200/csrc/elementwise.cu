@@ -1,0 +1,320 @@
+// HBM-bound fp32 NCHW kernels of the UNet graph between the quantised layers:
+// GroupNorm(+SiLU) with fused channel concat, SiLU, broadcast add, nearest 2x upsample,
+// channel concat, sinusoidal timestep embedding, the DDIM update and int4 nibble packing.
+// Reference: ddim/models/diffusion.py:6-52, 121-128, 345-357; ddim/functions/denoising.py:30-48;
+// qdiff/quant_layer_int4.py:341-366 (nibble order).
+#include "common.cuh"
+
+namespace modiff {
+
+namespace {
+
+__device__ inline float silu_f(float y) { return y * (1.0f / (1.0f + expf(-y))); }
+
+__device__ inline float block_sum(float v, float* sh) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? sh[lane] : 0.0f;
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;  // every thread holds the total
+}
+
+// One block per (image, group).  Three sweeps over the group's elements (mean, centred
+// variance, normalise); sweeps 2 and 3 hit L1/L2.
+__global__ void __launch_bounds__(512)
+groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1, int c0,
+                      float* __restrict__ y, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, int c, int hw, int groups, float eps,
+                      int silu) {
+  __shared__ float sh[32];
+  const int n = blockIdx.x / groups;
+  const int grp = blockIdx.x % groups;
+  const int cpg = c / groups;
+  const int cbeg = grp * cpg;
+  const int count = cpg * hw;
+  const int c1 = c - c0;
+  const bool vec = (hw % 4 == 0);
+
+  auto src = [&](int ch) -> const float* {
+    return (ch < c0) ? x0 + ((size_t)n * c0 + ch) * hw : x1 + ((size_t)n * c1 + (ch - c0)) * hw;
+  };
+
+  float s = 0.0f;
+  if (vec) {
+    const int hw4 = hw >> 2;
+    for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
+      const int ch = cbeg + i / hw4;
+      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < count; i += blockDim.x) s += __ldg(src(cbeg + i / hw) + i % hw);
+  }
+  const float mean = block_sum(s, sh) / (float)count;
+
+  float q = 0.0f;
+  if (vec) {
+    const int hw4 = hw >> 2;
+    for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
+      const int ch = cbeg + i / hw4;
+      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
+      const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, dd = v.w - mean;
+      q += (a * a + b * b) + (cc * cc + dd * dd);
+    }
+  } else {
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+      const float a = __ldg(src(cbeg + i / hw) + i % hw) - mean;
+      q += a * a;
+    }
+  }
+  const float var = block_sum(q, sh) / (float)count;
+  const float rstd = 1.0f / sqrtf(var + eps);
+
+  float* yn = y + (size_t)n * c * hw;
+  if (vec) {
+    const int hw4 = hw >> 2;
+    for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
+      const int ch = cbeg + i / hw4;
+      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
+      const float ga = gamma[ch] * rstd, be = beta[ch];
+      float4 o;
+      o.x = (v.x - mean) * ga + be;
+      o.y = (v.y - mean) * ga + be;
+      o.z = (v.z - mean) * ga + be;
+      o.w = (v.w - mean) * ga + be;
+      if (silu) { o.x = silu_f(o.x); o.y = silu_f(o.y); o.z = silu_f(o.z); o.w = silu_f(o.w); }
+      reinterpret_cast<float4*>(yn + (size_t)ch * hw)[i % hw4] = o;
+    }
+  } else {
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+      const int ch = cbeg + i / hw;
+      float o = (__ldg(src(ch) + i % hw) - mean) * (gamma[ch] * rstd) + beta[ch];
+      if (silu) o = silu_f(o);
+      yn[(size_t)ch * hw + i % hw] = o;
+    }
+  }
+}
+
+__global__ void silu_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) y[i] = silu_f(x[i]);
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                           float* __restrict__ out, int64_t n, int hw, int per_channel) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = __fadd_rn(a[i], per_channel ? b[i / hw] : b[i]);
+}
+
+__global__ void add4_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
+                            float4* __restrict__ out, int64_t n4) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    float4 u = a[i], v = b[i];
+    out[i] = make_float4(__fadd_rn(u.x, v.x), __fadd_rn(u.y, v.y), __fadd_rn(u.z, v.z),
+                         __fadd_rn(u.w, v.w));
+  }
+}
+
+__global__ void upsample2x_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                  int64_t planes, int h, int w) {
+  // one thread per input element, writes a 2x2 block
+  const int64_t total = planes * h * w;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int xx = (int)(i % w);
+    const int yy = (int)((i / w) % h);
+    const int64_t pl = i / ((int64_t)w * h);
+    const float v = x[i];
+    float* o = y + (pl * 2 * h + 2 * yy) * 2 * w + 2 * xx;
+    *reinterpret_cast<float2*>(o) = make_float2(v, v);
+    *reinterpret_cast<float2*>(o + 2 * w) = make_float2(v, v);
+  }
+}
+
+__global__ void concat_c_kernel(const float* __restrict__ a, int64_t ea, const float* __restrict__ b,
+                                int64_t eb, float* __restrict__ y, int64_t total) {
+  // per image: ea elements of a followed by eb elements of b
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t per = ea + eb;
+  for (; i < total; i += stride) {
+    const int64_t n = i / per, r = i % per;
+    y[i] = (r < ea) ? a[n * ea + r] : b[n * eb + (r - ea)];
+  }
+}
+
+__global__ void timestep_embedding_kernel(const float* __restrict__ t, float* __restrict__ emb,
+                                          int batch, int dim) {
+  const int half = dim / 2;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * dim) return;
+  const int b = i / dim, j = i % dim;
+  if (j >= 2 * half) { emb[i] = 0.0f; return; }  // odd dim: zero pad
+  const int f = (j < half) ? j : j - half;
+  const float coef = (float)(-(log(10000.0) / (double)(half - 1)));
+  const float freq = expf(__fmul_rn((float)f, coef));
+  const float arg = __fmul_rn(t[b], freq);
+  emb[i] = (j < half) ? sinf(arg) : cosf(arg);
+}
+
+__global__ void ddim_step_kernel(const float* __restrict__ x, const float* __restrict__ e,
+                                 const float* __restrict__ noise, float* __restrict__ x_next,
+                                 float* __restrict__ x0_out, int64_t n, float s1, float s2,
+                                 float s3, float c1, float c2) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const float ev = e[i];
+    const float x0 = __fdiv_rn(__fsub_rn(x[i], __fmul_rn(ev, s1)), s2);
+    float acc = __fmul_rn(s3, x0);
+    acc = __fadd_rn(acc, noise ? __fmul_rn(c1, noise[i]) : 0.0f);
+    acc = __fadd_rn(acc, __fmul_rn(c2, ev));
+    x_next[i] = acc;
+    if (x0_out) x0_out[i] = x0;
+  }
+}
+
+__global__ void pack_int4_kernel(const int8_t* __restrict__ codes, uint8_t* __restrict__ packed,
+                                 int64_t n) {
+  const int64_t nb = (n + 1) / 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < nb; i += stride) {
+    const int lo = codes[2 * i] & 0xf;
+    const int hi = (2 * i + 1 < n) ? (codes[2 * i + 1] & 0xf) : 0;
+    packed[i] = (uint8_t)(lo | (hi << 4));
+  }
+}
+
+__global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ codes,
+                                   int64_t n, int is_signed) {
+  const int64_t nb = (n + 1) / 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < nb; i += stride) {
+    const int v = packed[i];
+    int lo = v & 0xf, hi = (v >> 4) & 0xf;
+    if (is_signed) {
+      if (lo > 7) lo -= 16;
+      if (hi > 7) hi -= 16;
+    }
+    codes[2 * i] = (int8_t)lo;
+    if (2 * i + 1 < n) codes[2 * i + 1] = (int8_t)hi;
+  }
+}
+
+inline int grid_for(int64_t n, int block) {
+  int64_t b = ceil_div64(n, block);
+  const int64_t cap = 148 * 32;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+}  // namespace modiff
+
+using namespace modiff;
+
+extern "C" {
+
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, float* y, const float* gamma,
+                          const float* beta, int batch, int c, int hw, int groups, float eps,
+                          int silu, void* stream) {
+  MODIFF_CHECK_ARG(x0 && y && gamma && beta, "NULL pointer argument");
+  MODIFF_CHECK_ARG(batch > 0 && c > 0 && hw > 0 && groups > 0 && c % groups == 0,
+                   "bad GroupNorm shape: c=%d groups=%d", c, groups);
+  MODIFF_CHECK_ARG(c0 > 0 && c0 <= c && (c0 == c || x1 != nullptr), "bad concat split c0=%d", c0);
+  MODIFF_CHECK_ARG((((uintptr_t)x0 | (uintptr_t)y | (uintptr_t)x1) & 15) == 0,
+                   "GroupNorm tensors must be 16-byte aligned");
+  const int count = (c / groups) * hw;
+  const int threads = count >= 4096 ? 512 : (count >= 1024 ? 256 : 128);
+  groupnorm_silu_kernel<<<batch * groups, threads, 0, (cudaStream_t)stream>>>(
+      x0, x1, c0, y, gamma, beta, c, hw, groups, eps, silu);
+  MODIFF_LAUNCH_CHECK("groupnorm_silu_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_silu(const float* x, float* y, int64_t n, void* stream) {
+  MODIFF_CHECK_ARG(x && y && n >= 0, "bad argument");
+  if (n == 0) return MODIFF_OK;
+  silu_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(x, y, n);
+  MODIFF_LAUNCH_CHECK("silu_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_add(const float* a, const float* b, float* out, int batch, int c, int hw,
+               int b_per_channel, void* stream) {
+  MODIFF_CHECK_ARG(a && b && out && batch > 0 && c > 0 && hw > 0, "bad argument");
+  const int64_t n = (int64_t)batch * c * hw;
+  const bool al = ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0) && (n % 4 == 0);
+  if (!b_per_channel && al) {
+    add4_kernel<<<grid_for(n / 4, 256), 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)a, (const float4*)b, (float4*)out, n / 4);
+  } else {
+    add_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(a, b, out, n, hw, b_per_channel);
+  }
+  MODIFF_LAUNCH_CHECK("add_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_upsample2x(const float* x, float* y, int batch, int c, int h, int w, void* stream) {
+  MODIFF_CHECK_ARG(x && y && batch > 0 && c > 0 && h > 0 && w > 0, "bad argument");
+  MODIFF_CHECK_ARG(((uintptr_t)y & 7) == 0, "output must be 8-byte aligned");
+  const int64_t planes = (int64_t)batch * c;
+  upsample2x_kernel<<<grid_for(planes * h * w, 256), 256, 0, (cudaStream_t)stream>>>(x, y, planes, h, w);
+  MODIFF_LAUNCH_CHECK("upsample2x_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, int batch, int hw,
+                    void* stream) {
+  MODIFF_CHECK_ARG(a && b && y && ca > 0 && cb > 0 && batch > 0 && hw > 0, "bad argument");
+  const int64_t ea = (int64_t)ca * hw, eb = (int64_t)cb * hw;
+  const int64_t total = (ea + eb) * batch;
+  concat_c_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(a, ea, b, eb, y, total);
+  MODIFF_LAUNCH_CHECK("concat_c_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_timestep_embedding(const float* t, float* emb, int batch, int dim, void* stream) {
+  MODIFF_CHECK_ARG(t && emb && batch > 0 && dim >= 4, "bad argument");
+  timestep_embedding_kernel<<<ceil_div(batch * dim, 256), 256, 0, (cudaStream_t)stream>>>(t, emb, batch, dim);
+  MODIFF_LAUNCH_CHECK("timestep_embedding_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_ddim_step(const float* x, const float* e, const float* noise, float* x_next, float* x0,
+                     int64_t n, float s1, float s2, float s3, float c1, float c2, void* stream) {
+  MODIFF_CHECK_ARG(x && e && x_next && n > 0, "bad argument");
+  ddim_step_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(x, e, noise, x_next, x0, n, s1,
+                                                                      s2, s3, c1, c2);
+  MODIFF_LAUNCH_CHECK("ddim_step_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_pack_int4(const int8_t* codes, uint8_t* packed, int64_t n, void* stream) {
+  MODIFF_CHECK_ARG(codes && packed && n >= 0, "bad argument");
+  if (n == 0) return MODIFF_OK;
+  pack_int4_kernel<<<grid_for((n + 1) / 2, 256), 256, 0, (cudaStream_t)stream>>>(codes, packed, n);
+  MODIFF_LAUNCH_CHECK("pack_int4_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n, int is_signed, void* stream) {
+  MODIFF_CHECK_ARG(codes && packed && n >= 0, "bad argument");
+  if (n == 0) return MODIFF_OK;
+  unpack_int4_kernel<<<grid_for((n + 1) / 2, 256), 256, 0, (cudaStream_t)stream>>>(packed, codes, n,
+                                                                                 is_signed);
+  MODIFF_LAUNCH_CHECK("unpack_int4_kernel");
+  return MODIFF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,594 @@
+// Int8 implicit-GEMM conv / linear on the 5th-generation tensor cores (sm_100a):
+//   - activation-code tiles (128 output pixels x 128 input channels of one filter tap) and
+//     weight-code tiles arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a
+//     shared-memory ring;
+//   - one elected thread issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=128|144, K=32)
+//     with int32 accumulators in tensor memory, double buffered across output tiles;
+//   - four epilogue warps read the accumulators with tcgen05.ld and apply the modulation
+//     epilogue  out = o_hat + acc * delta_x * delta_w[c] (+ bias), writing the new o_hat.
+// Persistent kernel, one CTA per SM, warp specialised (TMA / MMA / epilogue).
+// Every mbarrier wait is bounded: when a limit runs out the kernel records an error word,
+// every role leaves its loop, tensor memory is released and the kernel returns.
+//
+// Reference arithmetic: qdiff/quant_layer.py:345-365 (see igemm_simt.cu).
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace modiff {
+
+int launch_igemm_simt(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                      const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                      float* o_hat, int accumulate, const float* bias, const modiff_conv_geom* g,
+                      int per_sample, int32_t* acc_out, cudaStream_t s);
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kChunkK = 128;          // bytes of K per pipeline stage (one swizzle atom row)
+constexpr int kATileBytes = kTileM * kChunkK;
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 6;
+constexpr uint32_t kSpinLimit = 1u << 28;
+
+__device__ int g_device_status = 0;   // sticky: non-zero after a bounded wait ran out
+
+struct TcParams {
+  modiff_conv_geom g;
+  Derived d;
+  int bw, bh, bn;                // box of output pixels forming one M tile
+  int tiles_w, tiles_h, tiles_n; // tiles along each direction
+  int n_tiles;                   // output-channel tiles
+  int total_tiles;
+  int umma_n;                    // 128, or 144 with the receptive-field-sum rows
+  int stages;
+  int nbuf;                      // accumulator buffers in tensor memory (1 or 2)
+  int buf_cols;                  // columns per buffer
+  int tmem_cols;                 // allocation (power of two)
+  int a_bytes;                   // bytes one activation-tile copy delivers
+  int chunks[2];                 // 128-byte K chunks per tap of segment 0 / 1
+  int cbeg[2];                   // first channel of segment 0 / 1
+  int nseg;
+  int with_sum;
+  int accumulate;
+  int per_sample;
+  const float* x_scale;
+  const float* w_scale;
+  const int32_t* w_corr;
+  const float* bias;
+  float* o_hat;
+  int32_t* acc_out;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ inline uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ inline void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ inline void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ inline uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait (about two seconds).  Returns false when the limit ran out or another role
+// of this CTA already gave up.
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > 2000000000ull) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&g_device_status, 1);
+  return false;
+}
+
+__device__ inline void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                   int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                   int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ inline void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ inline void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ inline void tc_ld32(uint32_t taddr, int (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ inline void tc_ld1(uint32_t taddr, int& v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr) : "memory");
+}
+__device__ inline void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.
+__device__ inline uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);       // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                         // layout type: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::i8: s8 x s8 -> s32, both operands K-major.
+__host__ __device__ inline uint32_t make_idesc_i8(int m, int n) {
+  uint32_t d = 0;
+  d |= 2u << 4;                 // D format: s32
+  d |= 1u << 7;                 // A format: signed 8 bit
+  d |= 1u << 10;                // B format: signed 8 bit
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= (uint32_t)(m >> 4) << 24;
+  return d;
+}
+
+struct TileCoord {
+  int tn, th, tw, nt;
+};
+__device__ inline TileCoord decode_tile(int tile, const TcParams& p) {
+  TileCoord t;
+  t.nt = tile % p.n_tiles;
+  int m = tile / p.n_tiles;
+  t.tw = m % p.tiles_w;
+  m /= p.tiles_w;
+  t.th = m % p.tiles_h;
+  t.tn = m / p.tiles_h;
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[2];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ uint32_t tmem_base_sh;
+  __shared__ int abort_sh;
+  __shared__ float ep_scale[2][128];
+  __shared__ int ep_corr[2][128];
+  __shared__ float ep_bias[128];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &abort_sh;
+
+  // 1024-byte aligned tile ring
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;
+  const int b_rows = p.umma_n;
+  const uint32_t b_tile_bytes = (uint32_t)b_rows * kChunkK;
+  const uint32_t stage_bytes = kATileBytes + ((b_tile_bytes + 1023u) & ~1023u);
+
+  if (threadIdx.x == 0) {
+    abort_sh = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[b]), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_base_sh)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_sh;
+
+  const int k_iters_seg0 = p.d.taps * p.chunks[0];
+  const int k_iters_seg1 = (p.nseg == 2) ? p.d.taps * p.chunks[1] : 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const TileCoord t = decode_tile(tile, p);
+        for (int seg = 0; seg < p.nseg && ok; ++seg) {
+          for (int tap = 0; tap < p.d.taps && ok; ++tap) {
+            const int r = tap / p.g.kw, sx = tap % p.g.kw;
+            const int plane = (r % p.g.stride) * p.g.stride + (sx % p.g.stride);
+            const int dh = r / p.g.stride, dw = sx / p.g.stride;
+            for (int ch = 0; ch < p.chunks[seg]; ++ch) {
+              ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
+              if (!ok) break;
+              const uint32_t full = smem_u32(&bar_full[stage]);
+              const uint32_t a_dst = ring + stage * stage_bytes;
+              const uint32_t b_dst = a_dst + kATileBytes;
+              const int c0 = p.cbeg[seg] + ch * kChunkK;
+              mbar_arrive_expect_tx(full, (uint32_t)p.a_bytes + b_tile_bytes);
+              tma_load_5d(a_dst, &map_a, full, c0, t.tw * p.bw + dw, t.th * p.bh + dh, plane,
+                          t.tn * p.bn);
+              tma_load_2d(b_dst, &map_b, full, tap * p.d.kp + c0, t.nt * b_rows);
+              if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_i8(kTileM, p.umma_n);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t bphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), bphase ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int seg = 0; seg < p.nseg && ok; ++seg) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.buf_cols + seg * p.umma_n);
+          const int iters = seg == 0 ? k_iters_seg0 : k_iters_seg1;
+          for (int it = 0; it < iters; ++it) {
+            ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_src = ring + stage * stage_bytes;
+            const uint64_t adesc = make_smem_desc(a_src);
+            const uint64_t bdesc = make_smem_desc(a_src + kATileBytes);
+#pragma unroll
+            for (int k = 0; k < kChunkK / 32; ++k) {
+              // advancing K by 32 bytes inside the swizzle atom = +2 in the address field
+              tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                        (it > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&bar_empty[stage]));
+            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;           // tensor-memory lane quarter this warp may read
+    const int ep_tid = threadIdx.x - 64;    // 0..127
+    const int row = quarter * 32 + lane;    // accumulator row = output pixel of the tile
+    const int howo = p.d.ho * p.d.wo;
+    const size_t M = (size_t)p.g.batch * howo;
+    int buf = 0;
+    uint32_t bphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(tile, p);
+      // per-tile channel parameters
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      {
+        const int co = t.nt * 128 + ep_tid;
+        const bool cv = co < p.g.cout;
+        for (int seg = 0; seg < p.nseg; ++seg) {
+          ep_scale[seg][ep_tid] = cv ? p.w_scale[seg * p.g.cout + co] : 0.0f;
+          ep_corr[seg][ep_tid] = (cv && p.w_corr) ? p.w_corr[seg * p.g.cout + co] : 0;
+        }
+        ep_bias[ep_tid] = (cv && p.bias) ? p.bias[co] : 0.0f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+
+      if (ok) ok = mbar_wait(smem_u32(&bar_tmem_full[buf]), bphase, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+
+      const int ni = row / (p.bh * p.bw);
+      const int hi = (row / p.bw) % p.bh;
+      const int wi = row % p.bw;
+      const int n = t.tn * p.bn + ni;
+      const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
+      const bool valid = n < p.g.batch;
+      const size_t m = (size_t)n * howo + hw;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.buf_cols);
+
+      float xs[2];
+      xs[0] = p.per_sample ? (valid ? p.x_scale[n] : 0.0f) : p.x_scale[0];
+      xs[1] = (p.nseg == 2) ? p.x_scale[1] : 0.0f;
+      int rsum[2] = {0, 0};
+      if (p.with_sum) {
+        for (int seg = 0; seg < p.nseg; ++seg) tc_ld1(t_row + seg * p.umma_n + 128, rsum[seg]);
+        tc_wait_ld();
+      }
+      float* obase = p.o_hat + ((size_t)n * p.g.cout) * howo + hw;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        int a0[32], a1[32];
+        tc_ld32(t_row + cc * 32, a0);
+        if (p.nseg == 2) tc_ld32(t_row + p.umma_n + cc * 32, a1);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int cl = cc * 32 + j;
+            const int co = t.nt * 128 + cl;
+            if (co < p.g.cout) {
+              const int i0 = a0[j] + ep_corr[0][cl] * rsum[0];
+              float v = (float)i0 * __fmul_rn(xs[0], ep_scale[0][cl]);
+              if (p.nseg == 2) {
+                const int i1 = a1[j] + ep_corr[1][cl] * rsum[1];
+                v += (float)i1 * __fmul_rn(xs[1], ep_scale[1][cl]);
+                if (p.acc_out) p.acc_out[(M + m) * p.g.cout + co] = i1;
+              }
+              if (p.acc_out) p.acc_out[m * p.g.cout + co] = i0;
+              float* o = obase + (size_t)co * howo;
+              if (p.accumulate) v += *o;
+              *o = v + ep_bias[cl];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+      if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (abort_sh) {
+    // give copies that may still be in flight time to land before the CTA retires
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+}  // namespace
+
+// Whether the tensor-core kernel covers this geometry; the message says why not.
+bool tc_supported(const modiff_conv_geom* g, int per_sample, const char** why) {
+  Derived d = derive(*g);
+  static const char* msgs[] = {"cin < 128", "output width/height not a power of two <= 128",
+                               "split not a multiple of 128", "cin not a multiple of 16",
+                               "kernel larger than 7x7"};
+  if (g->cin < 128) { *why = msgs[0]; return false; }
+  if (g->cin % 16) { *why = msgs[3]; return false; }
+  if (!is_pow2(d.wo) || !is_pow2(d.ho) || d.wo > 128) { *why = msgs[1]; return false; }
+  if (g->split % 128) { *why = msgs[2]; return false; }
+  if (g->kh > 7 || g->kw > 7) { *why = msgs[4]; return false; }
+  (void)per_sample;
+  return true;
+}
+
+int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                    const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                    float* o_hat, int accumulate, const float* bias, const modiff_conv_geom* g,
+                    int per_sample, int32_t* acc_out, cudaStream_t s) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+  MODIFF_CHECK_ARG(w_corr == nullptr || with_sum_rows,
+                   "w_corr given but the weight codes were packed without sum rows");
+  Derived d = derive(*g);
+  TcParams p;
+  p.g = *g;
+  p.d = d;
+  p.bw = d.wo < 128 ? d.wo : 128;
+  p.bh = (d.ho < 128 / p.bw) ? d.ho : 128 / p.bw;
+  p.bn = 128 / (p.bw * p.bh);
+  p.tiles_w = d.wo / p.bw;
+  p.tiles_h = d.ho / p.bh;
+  p.tiles_n = ceil_div(g->batch, p.bn);
+  p.n_tiles = ceil_div(g->cout, 128);
+  p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+  p.with_sum = with_sum_rows ? 1 : 0;
+  p.umma_n = with_sum_rows ? 144 : 128;
+  p.nseg = d.nseg;
+  p.buf_cols = p.nseg * p.umma_n;
+  p.nbuf = (2 * p.buf_cols <= 512) ? 2 : 1;
+  int cols = p.nbuf * p.buf_cols;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < cols) p.tmem_cols *= 2;
+  p.cbeg[0] = 0;
+  p.cbeg[1] = g->split;
+  const int c_seg0 = p.nseg == 2 ? g->split : g->cin;
+  p.chunks[0] = ceil_div(c_seg0, kChunkK);
+  p.chunks[1] = p.nseg == 2 ? ceil_div(g->cin - g->split, kChunkK) : 0;
+  p.accumulate = accumulate;
+  p.per_sample = per_sample;
+  p.x_scale = x_scale;
+  p.w_scale = w_scale;
+  p.w_corr = w_corr;
+  p.bias = bias;
+  p.o_hat = o_hat;
+  p.acc_out = acc_out;
+
+  const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
+  const uint32_t stage_bytes = kATileBytes + b_tile;
+  p.stages = (int)((200u * 1024u) / stage_bytes);
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+
+  // Activation codes: [batch][planes][hp][wp][cp] int8, innermost first.
+  CUtensorMap map_a, map_b;
+  {
+    cuuint64_t dims[5] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp, (cuuint64_t)d.hp,
+                          (cuuint64_t)d.nplanes, (cuuint64_t)g->batch};
+    cuuint64_t strides[4] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp * d.cp,
+                             (cuuint64_t)d.hp * d.wp * d.cp,
+                             (cuuint64_t)d.nplanes * d.hp * d.wp * d.cp};
+    // The image extent of the box never exceeds the batch; rows of the tile that no copy
+    // fills belong to images >= batch and are masked in the epilogue.
+    const int bn_box = p.bn < g->batch ? p.bn : g->batch;
+    p.a_bytes = kChunkK * p.bw * p.bh * bn_box;
+    cuuint32_t box[5] = {(cuuint32_t)kChunkK, (cuuint32_t)p.bw, (cuuint32_t)p.bh, 1u,
+                         (cuuint32_t)bn_box};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void*)codes, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(activation codes) failed: %d", (int)r);
+  }
+  {
+    const int rows = modiff_wcodes_rows(g, with_sum_rows);
+    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)d.taps * d.kp};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)p.umma_n};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)wcodes, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(weight codes) failed: %d", (int)r);
+  }
+
+  static int sm_count = 0;
+  static bool attr_set = false;
+  if (!sm_count) {
+    int dev = 0;
+    MODIFF_CUDA(cudaGetDevice(&dev));
+    MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (!attr_set) {
+    MODIFF_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     220 * 1024));
+    attr_set = true;
+  }
+  const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
+  igemm_tc_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, p);
+  MODIFF_LAUNCH_CHECK("igemm_tc_kernel");
+  return MODIFF_OK;
+}
+
+int read_device_status(int* status, int reset) {
+  MODIFF_CUDA(cudaMemcpyFromSymbol(status, g_device_status, sizeof(int)));
+  if (reset) {
+    int zero = 0;
+    MODIFF_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  }
+  return MODIFF_OK;
+}
+
+}  // namespace modiff
+
+using namespace modiff;
+
+extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                                 const float* x_scale, const float* w_scale,
+                                 const int32_t* w_corr, float* o_hat, int accumulate,
+                                 const float* bias, const modiff_conv_geom* g, int per_sample,
+                                 int impl, int32_t* acc_out, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(codes && wcodes && x_scale && w_scale && o_hat, "NULL pointer argument");
+  MODIFF_CHECK_ARG((((uintptr_t)codes | (uintptr_t)wcodes) & 15) == 0,
+                   "code buffers must be 16-byte aligned");
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  cudaStream_t s = (cudaStream_t)stream;
+  const char* why = "";
+  const bool tc_ok = tc_supported(g, per_sample, &why);
+  if (impl == MODIFF_IMPL_TCGEN05 && !tc_ok)
+    return set_error(MODIFF_ERR_UNSUPPORTED, "tcgen05 path does not cover this layer: %s", why);
+  if (impl == MODIFF_IMPL_SIMT || !tc_ok)
+    return launch_igemm_simt(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat,
+                             accumulate, bias, g, per_sample, acc_out, s);
+  MODIFF_CHECK_ARG(impl == MODIFF_IMPL_AUTO || impl == MODIFF_IMPL_TCGEN05, "unknown impl %d", impl);
+  return launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                         bias, g, per_sample, acc_out, s);
+}
+
+extern "C" int modiff_device_status(int* status, int reset) {
+  MODIFF_CHECK_ARG(status != nullptr, "status is NULL");
+  return read_device_status(status, reset);
+}

@@ -1,0 +1,254 @@
+// Modulated activation quantiser (two kernels on one stream):
+//   1. modq_absmax_kernel : max |x - a_hat| per scale slot; the last block to finish
+//                           turns it into delta (double division, as the reference's
+//                           Python float arithmetic does) and re-zeroes the scratch;
+//   2. modq_encode_kernel : codes = clamp(rne((x - a_hat) / delta)), a_hat += codes*delta,
+//                           NCHW fp32 -> NHWC int8 code planes through a shared-memory
+//                           transpose.
+//
+// Reference arithmetic: qdiff/quant_layer.py:329-336 (residual, cache update),
+// :191-214 (per-tensor 'max' scale), :160-190 (per-sample scale), :94-102 (codes).
+// Every floating-point step is an explicitly rounded single operation (no FMA
+// contraction, true division) so codes and the cache are bit-identical to PyTorch.
+#include "common.cuh"
+
+namespace modiff {
+
+namespace {
+
+constexpr int kTileC = 64;   // channels per block
+constexpr int kTileP = 64;   // pixels per block
+constexpr int kThreads = 256;
+
+struct ModqScratch {
+  unsigned int counter;
+  unsigned int pad[3];
+  unsigned int absmax_bits[1];  // [slots]
+};
+
+__device__ inline float load1(const float* p) { return __ldg(p); }
+
+template <bool VEC4>
+__device__ inline void load4(const float* __restrict__ base, int p, int hw, float (&v)[4]) {
+  if (VEC4) {
+    float4 t = __ldg(reinterpret_cast<const float4*>(base + p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = (p + j < hw) ? __ldg(base + p + j) : 0.0f;
+  }
+}
+
+template <bool VEC4>
+__device__ inline void store4(float* __restrict__ base, int p, int hw, const float (&v)[4]) {
+  if (VEC4) {
+    *reinterpret_cast<float4*>(base + p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (p + j < hw) base[p + j] = v[j];
+  }
+}
+
+// slot of channel c of image n: per-sample -> n; split -> segment; else 0
+__device__ inline int slot_of(int n, int c, int split, int per_sample) {
+  if (per_sample) return n;
+  return (split > 0 && c >= split) ? 1 : 0;
+}
+
+template <bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
+                   modiff_conv_geom g, int n_levels, int per_sample, int slots,
+                   ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
+  const int hw = g.h * g.w;
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * kTileC;
+  const int p0 = blockIdx.x * kTileP;
+  const int cg = threadIdx.x >> 4;
+  const int pq = threadIdx.x & 15;
+  const int p = p0 + 4 * pq;
+
+  float m0 = 0.0f, m1 = 0.0f;
+  if (p < hw) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + 4 * cg + i;
+      if (c < g.cin) {
+        const size_t off = ((size_t)n * g.cin + c) * hw;
+        float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f};
+        load4<VEC4>(x + off, p, hw, xv);
+        if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+        float m = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m = fmaxf(m, fabsf(__fsub_rn(xv[j], av[j])));
+        if (g.split > 0 && c >= g.split) m1 = fmaxf(m1, m); else m0 = fmaxf(m0, m);
+      }
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+  }
+  __shared__ float s0[kThreads / 32], s1[kThreads / 32];
+  __shared__ bool is_last;
+  if ((threadIdx.x & 31) == 0) {
+    s0[threadIdx.x >> 5] = m0;
+    s1[threadIdx.x >> 5] = m1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kThreads / 32; ++i) {
+      m0 = fmaxf(m0, s0[i]);
+      m1 = fmaxf(m1, s1[i]);
+    }
+    // Non-negative floats order like their bit patterns.
+    const int slot0 = per_sample ? n : 0;
+    if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
+    if (g.split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    __threadfence();
+    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == total - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    for (int s = threadIdx.x; s < slots; s += blockDim.x) {
+      const unsigned int bits = atomicExch(&scratch->absmax_bits[s], 0u);
+      // delta = x_absmax / n_levels in Python floats (doubles), floor 1e-8, then cast
+      // to fp32 by torch.tensor(delta).type_as(x).
+      double delta = (double)__uint_as_float(bits) / (double)n_levels;
+      if (delta < 1e-8) delta = 1e-8;
+      x_scale[s] = (float)delta;
+    }
+    if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
+
+template <bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+modq_encode_kernel(const float* __restrict__ x, float* __restrict__ a_hat,
+                   int8_t* __restrict__ codes, const float* __restrict__ x_scale,
+                   modiff_conv_geom g, Derived d, int n_levels, int per_sample) {
+  __shared__ uint32_t tile[kTileP][kTileC / 4 + 1];
+  const int hw = g.h * g.w;
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * kTileC;
+  const int p0 = blockIdx.x * kTileP;
+  const int cg = threadIdx.x >> 4;
+  const int pq = threadIdx.x & 15;
+  const int p = p0 + 4 * pq;
+  const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+
+  int q[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[i][j] = 0;
+
+  if (p < hw) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + 4 * cg + i;
+      if (c < g.cin) {
+        const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
+        const size_t off = ((size_t)n * g.cin + c) * hw;
+        float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
+        load4<VEC4>(x + off, p, hw, xv);
+        if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float r = __fsub_rn(xv[j], av[j]);
+          float qf = rintf(__fdiv_rn(r, delta));
+          qf = fminf(fmaxf(qf, lo), hi);
+          q[i][j] = (int)qf;
+          nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
+        }
+        if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t word = (uint32_t)(q[0][j] & 0xff) | ((uint32_t)(q[1][j] & 0xff) << 8) |
+                          ((uint32_t)(q[2][j] & 0xff) << 16) | ((uint32_t)(q[3][j] & 0xff) << 24);
+    tile[4 * pq + j][cg] = word;
+  }
+  __syncthreads();
+  // 4 threads per pixel, 16 bytes each.
+  const int px = threadIdx.x >> 2;
+  const int piece = threadIdx.x & 3;
+  const int pp = p0 + px;
+  const int cbase = c0 + 16 * piece;
+  if (pp < hw && cbase < d.cp) {
+    const int y = pp / g.w + g.pad_t;
+    const int xq = pp % g.w + g.pad_l;
+    const int plane = (y % g.stride) * g.stride + (xq % g.stride);
+    const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + y / g.stride) * d.wp + xq / g.stride;
+    int4 v = make_int4(tile[px][4 * piece], tile[px][4 * piece + 1], tile[px][4 * piece + 2],
+                       tile[px][4 * piece + 3]);
+    *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+  }
+}
+
+}  // namespace
+
+int launch_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                bool compute_scale, cudaStream_t s) {
+  Derived d = derive(*g);
+  const int hw = g->h * g->w;
+  const int n_levels = sym_levels(n_bits);
+  const int slots = per_sample ? g->batch : d.nseg;
+  dim3 grid(ceil_div(hw, kTileP), ceil_div(g->cin, kTileC), g->batch);
+  const bool vec = (hw % 4 == 0) && (((uintptr_t)x & 15) == 0) &&
+                   (a_hat == nullptr || ((uintptr_t)a_hat & 15) == 0);
+  if (compute_scale) {
+    if (vec)
+      modq_absmax_kernel<true><<<grid, kThreads, 0, s>>>(x, a_hat, *g, n_levels, per_sample, slots,
+                                                         (ModqScratch*)scratch, x_scale);
+    else
+      modq_absmax_kernel<false><<<grid, kThreads, 0, s>>>(x, a_hat, *g, n_levels, per_sample, slots,
+                                                          (ModqScratch*)scratch, x_scale);
+    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+  }
+  if (vec)
+    modq_encode_kernel<true><<<grid, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, n_levels,
+                                                       per_sample);
+  else
+    modq_encode_kernel<false><<<grid, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, n_levels,
+                                                        per_sample);
+  MODIFF_LAUNCH_CHECK("modq_encode_kernel");
+  return MODIFF_OK;
+}
+
+}  // namespace modiff
+
+using namespace modiff;
+
+extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                           const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                           void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(x && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(g->batch <= 65535, "batch %d exceeds the grid limit 65535", g->batch);
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
+                     (cudaStream_t)stream);
+}
+
+extern "C" int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
+                                      const modiff_conv_geom* g, int n_bits, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(x && codes && delta, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(g->batch <= 65535, "batch %d exceeds the grid limit 65535", g->batch);
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  return launch_modq(x, nullptr, codes, const_cast<float*>(delta), g, n_bits, 0, nullptr, false,
+                     (cudaStream_t)stream);
+}

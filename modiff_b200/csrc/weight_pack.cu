@@ -1,0 +1,126 @@
+// Per-output-channel asymmetric weight quantisation into the int8 weight-code layout.
+//
+// Arithmetic follows UniformAffineQuantizer with channel_wise=True, symmetric=False
+// (qdiff/quant_layer.py:160-190 for delta / zero point, :94-102 for the codes): every
+// operation is a single correctly-rounded fp32 operation in the same order, so the
+// integer codes are identical to round(w / delta) + zp computed by PyTorch.
+#include "common.cuh"
+
+namespace modiff {
+
+namespace {
+
+__device__ inline float warp_min(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ inline float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// One block per (output channel, segment).
+__global__ void __launch_bounds__(256)
+weight_pack_kernel(const float* __restrict__ w, modiff_conv_geom g, Derived d, int n_bits,
+                   int with_sum_rows, int8_t* __restrict__ wcodes, float* __restrict__ w_scale,
+                   float* __restrict__ w_zp, int32_t* __restrict__ w_corr,
+                   float* __restrict__ w_dq) {
+  const int co = blockIdx.x;
+  const int seg = blockIdx.y;
+  const int cb = (seg == 0) ? 0 : g.split;
+  const int ce = (d.nseg == 1 || seg == 1) ? g.cin : g.split;
+  const int taps = d.taps;
+  const int n = (ce - cb) * taps;
+  const float* wrow = w + ((size_t)co * g.cin + cb) * taps;  // contiguous [ce-cb][taps]
+
+  __shared__ float s_min[8], s_max[8];
+  __shared__ float s_delta, s_zp;
+
+  float mn = INFINITY, mx = -INFINITY;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = wrow[i];
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  mn = warp_min(mn);
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) {
+    s_min[threadIdx.x >> 5] = mn;
+    s_max[threadIdx.x >> 5] = mx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) {
+      mn = fminf(mn, s_min[i]);
+      mx = fmaxf(mx, s_max[i]);
+    }
+    const float n_levels = (float)(1 << n_bits);
+    float delta = __fdiv_rn(__fsub_rn(mx, mn), __fsub_rn(n_levels, 1.0f));
+    if (delta < 1e-8f) delta = 1e-8f;
+    float zp = rintf(__fdiv_rn(-mn, delta));
+    s_delta = delta;
+    s_zp = zp;
+    int zpi = (int)zp;
+    int zoff = (n_bits >= 8) ? 128 : min(max(zpi, 0), 127);
+    w_scale[seg * g.cout + co] = delta;
+    w_zp[seg * g.cout + co] = zp;
+    w_corr[seg * g.cout + co] = zoff - zpi;
+  }
+  __syncthreads();
+  const float delta = s_delta, zp = s_zp;
+  const int zpi = (int)zp;
+  const int zoff = (n_bits >= 8) ? 128 : min(max(zpi, 0), 127);
+  const float qmax = (float)((1 << n_bits) - 1);
+  const int row = with_sum_rows ? (co / 128) * 144 + (co % 128) : co;
+  int8_t* crow = wcodes + (size_t)row * taps * d.kp;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int c = cb + i / taps;
+    const int tap = i % taps;
+    float v = wrow[i];
+    float xi = __fadd_rn(rintf(__fdiv_rn(v, delta)), zp);
+    float q = fminf(fmaxf(xi, 0.0f), qmax);
+    crow[(size_t)tap * d.kp + c] = (int8_t)((int)q - zoff);
+    if (w_dq) {
+      w_dq[((size_t)c * taps + tap) * g.cout + co] = __fmul_rn(__fsub_rn(q, zp), delta);
+    }
+  }
+}
+
+// Row 128 of every 144-row tile is all ones over the real input channels, so that the
+// tensor-core kernel obtains the receptive-field sum of the activation codes as one
+// more accumulator column.
+__global__ void weight_sum_rows_kernel(int8_t* __restrict__ wcodes, modiff_conv_geom g, Derived d) {
+  const int tile = blockIdx.x;
+  int8_t* row = wcodes + ((size_t)tile * 144 + 128) * d.taps * d.kp;
+  const int n = d.taps * d.kp;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int c = i % d.kp;
+    row[i] = (c < g.cin) ? 1 : 0;
+  }
+}
+
+}  // namespace
+}  // namespace modiff
+
+using namespace modiff;
+
+extern "C" int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
+                                  int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
+                                  int32_t* w_corr, float* w_dq, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(w && wcodes && w_scale && w_zp && w_corr, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "weight n_bits %d outside [2, 8]", n_bits);
+  cudaStream_t s = (cudaStream_t)stream;
+  Derived d = derive(*g);
+  MODIFF_CUDA(cudaMemsetAsync(wcodes, 0, (size_t)modiff_wcodes_bytes(g, with_sum_rows), s));
+  dim3 grid(g->cout, d.nseg);
+  weight_pack_kernel<<<grid, 256, 0, s>>>(w, *g, d, n_bits, with_sum_rows, wcodes, w_scale, w_zp,
+                                          w_corr, w_dq);
+  MODIFF_LAUNCH_CHECK("weight_pack_kernel");
+  if (with_sum_rows) {
+    weight_sum_rows_kernel<<<ceil_div(g->cout, 128), 256, 0, s>>>(wcodes, *g, d);
+    MODIFF_LAUNCH_CHECK("weight_sum_rows_kernel");
+  }
+  return MODIFF_OK;
+}

@@ -1,0 +1,139 @@
+"""Thin Python wrappers over the fp32 graph kernels of libmodiff_b200.so.
+
+Each function allocates its output with torch (device memory plumbing) and launches one
+hand-written kernel on the current CUDA stream.  CUDA float32 tensors only.
+"""
+import torch
+
+from . import _lib
+from ._lib import ModiffError
+
+
+def _req(*ts):
+    for t in ts:
+        if t is not None:
+            _lib.require_cuda(t)
+
+
+def groupnorm(x, norm, silu=False, x1=None):
+    """GroupNorm (+SiLU) of `x`, or of the channel concat [x, x1] without materialising it.
+
+    `norm` is a torch.nn.GroupNorm holding gamma / beta / groups / eps.
+    """
+    _req(x, x1)
+    x = x.contiguous()
+    b, c0 = x.shape[0], x.shape[1]
+    hw = x.numel() // (b * c0)
+    c = c0
+    if x1 is not None:
+        x1 = x1.contiguous()
+        c = c0 + x1.shape[1]
+    if c != norm.num_channels:
+        raise ModiffError(f"GroupNorm expects {norm.num_channels} channels, got {c}")
+    y = torch.empty((b, c) + tuple(x.shape[2:]), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().modiff_groupnorm_silu(
+        x.data_ptr(), _lib.ptr(x1), c0, y.data_ptr(), norm.weight.data_ptr(), norm.bias.data_ptr(),
+        b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr()))
+    return y
+
+
+def silu(x):
+    _req(x)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _lib.check(_lib.lib().modiff_silu(x.data_ptr(), y.data_ptr(), x.numel(), _lib.stream_ptr()))
+    return y
+
+
+def add(a, b):
+    """a + b for equal shapes."""
+    _req(a, b)
+    if a.shape != b.shape:
+        raise ModiffError(f"add: shapes differ {tuple(a.shape)} vs {tuple(b.shape)}")
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty_like(a)
+    _lib.check(_lib.lib().modiff_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), 1, 1, a.numel(), 0,
+                                     _lib.stream_ptr()))
+    return out
+
+
+def add_channel_bias(a, b):
+    """a[B,C,H,W] + b[B,C][:, :, None, None]."""
+    _req(a, b)
+    a, b = a.contiguous(), b.contiguous()
+    bsz, c = a.shape[0], a.shape[1]
+    if tuple(b.shape) != (bsz, c):
+        raise ModiffError(f"add_channel_bias: bias shape {tuple(b.shape)} != {(bsz, c)}")
+    hw = a.numel() // (bsz * c)
+    out = torch.empty_like(a)
+    _lib.check(_lib.lib().modiff_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), bsz, c, hw, 1,
+                                     _lib.stream_ptr()))
+    return out
+
+
+def upsample2x(x):
+    _req(x)
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    y = torch.empty((b, c, 2 * h, 2 * w), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().modiff_upsample2x(x.data_ptr(), y.data_ptr(), b, c, h, w, _lib.stream_ptr()))
+    return y
+
+
+def concat_channels(a, b):
+    _req(a, b)
+    a, b = a.contiguous(), b.contiguous()
+    bsz, ca, cb = a.shape[0], a.shape[1], b.shape[1]
+    hw = a.numel() // (bsz * ca)
+    y = torch.empty((bsz, ca + cb) + tuple(a.shape[2:]), dtype=torch.float32, device=a.device)
+    _lib.check(_lib.lib().modiff_concat_c(a.data_ptr(), ca, b.data_ptr(), cb, y.data_ptr(), bsz, hw,
+                                          _lib.stream_ptr()))
+    return y
+
+
+def timestep_embedding(t, dim):
+    _req(t)
+    t = t.contiguous()
+    emb = torch.empty((t.shape[0], dim), dtype=torch.float32, device=t.device)
+    _lib.check(_lib.lib().modiff_timestep_embedding(t.data_ptr(), emb.data_ptr(), t.shape[0], dim,
+                                                    _lib.stream_ptr()))
+    return emb
+
+
+def ddim_step(x, e, s1, s2, s3, c1, c2, noise=None, want_x0=False):
+    _req(x, e, noise)
+    x, e = x.contiguous(), e.contiguous()
+    x_next = torch.empty_like(x)
+    x0 = torch.empty_like(x) if want_x0 else None
+    _lib.check(_lib.lib().modiff_ddim_step(x.data_ptr(), e.data_ptr(), _lib.ptr(noise),
+                                           x_next.data_ptr(), _lib.ptr(x0), x.numel(),
+                                           s1, s2, s3, c1, c2, _lib.stream_ptr()))
+    return (x_next, x0) if want_x0 else x_next
+
+
+def pack_int4(codes):
+    if not codes.is_cuda or codes.dtype != torch.int8:
+        raise ModiffError("pack_int4 expects a CUDA int8 tensor")
+    codes = codes.contiguous()
+    n = codes.numel()
+    out = torch.empty((n + 1) // 2, dtype=torch.uint8, device=codes.device)
+    _lib.check(_lib.lib().modiff_pack_int4(codes.data_ptr(), out.data_ptr(), n, _lib.stream_ptr()))
+    return out
+
+
+def unpack_int4(packed, n, signed=True):
+    if not packed.is_cuda or packed.dtype != torch.uint8:
+        raise ModiffError("unpack_int4 expects a CUDA uint8 tensor")
+    out = torch.empty(n, dtype=torch.int8, device=packed.device)
+    _lib.check(_lib.lib().modiff_unpack_int4(packed.data_ptr(), out.data_ptr(), n, int(signed),
+                                             _lib.stream_ptr()))
+    return out
+
+
+def attention(q, k, v, scale):
+    """Single-head attention over [B, C, T] tensors, fp32 (qdiff/quant_block.py:344-360):
+    out[b,:,i] = sum_j softmax_j(q[b,:,i] . k[b,:,j] * scale) v[b,:,j]."""
+    _req(q, k, v)
+    w_ = torch.bmm(q.permute(0, 2, 1), k)
+    w_ = torch.softmax(w_ * scale, dim=2)
+    return torch.bmm(v, w_.permute(0, 2, 1))

@@ -1,0 +1,89 @@
+"""Quantised block wrappers with the reference's class names and setters
+(qdiff/quant_block.py:20-41 BaseQuantBlock, :267-313 QuantResnetBlock, :316-369
+QuantAttnBlock, :372-384 get_specials).
+
+Blocks are matched by class NAME, so both this package's `unet.ResnetBlock` / `AttnBlock`
+and the reference's own classes of the same names are re-hosted.
+"""
+import torch.nn as nn
+
+from .quant_layer import QuantModule, UniformAffineQuantizer, StraightThrough
+from . import unet
+
+
+class BaseQuantBlock(nn.Module):
+    """Base of all block structures (qdiff/quant_block.py:20-41)."""
+
+    def __init__(self, act_quant_params: dict = {}):
+        super().__init__()
+        self.use_weight_quant = False
+        self.use_act_quant = False
+        self.act_quantizer = UniformAffineQuantizer(**act_quant_params)
+        self.activation_function = StraightThrough()
+        self.ignore_reconstruction = False
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self.use_weight_quant = weight_quant
+        self.use_act_quant = act_quant
+        for m in self.modules():
+            if isinstance(m, QuantModule):
+                m.set_quant_state(weight_quant, act_quant)
+
+
+class QuantResnetBlock(BaseQuantBlock):
+    """Re-hosted pixel-UNet residual block (qdiff/quant_block.py:267-313)."""
+
+    def __init__(self, res, act_quant_params: dict = {}):
+        super().__init__(act_quant_params)
+        self.in_channels = res.in_channels
+        self.out_channels = res.out_channels
+        self.use_conv_shortcut = res.use_conv_shortcut
+        self.norm1 = res.norm1
+        self.conv1 = res.conv1
+        self.temb_proj = res.temb_proj
+        self.norm2 = res.norm2
+        self.dropout = res.dropout
+        self.conv2 = res.conv2
+        if self.in_channels != self.out_channels:
+            if self.use_conv_shortcut:
+                self.conv_shortcut = res.conv_shortcut
+            else:
+                self.nin_shortcut = res.nin_shortcut
+
+    def forward(self, x, temb=None, split=0):
+        return unet.resnet_forward(self, x, temb, split)
+
+
+class QuantAttnBlock(BaseQuantBlock):
+    """Re-hosted pixel-UNet attention block (qdiff/quant_block.py:316-369).  As in the
+    reference, the q/k/v/w quantisers are constructed (with sm_abit bits) but the attention
+    matmuls themselves run unquantised."""
+
+    def __init__(self, attn, act_quant_params: dict = {}, sm_abit=8):
+        super().__init__(act_quant_params)
+        self.in_channels = attn.in_channels
+        self.norm = attn.norm
+        self.q = attn.q
+        self.k = attn.k
+        self.v = attn.v
+        self.proj_out = attn.proj_out
+        params_w = act_quant_params.copy()
+        params_w['n_bits'] = sm_abit
+        self.act_quantizer_w = UniformAffineQuantizer(**params_w)
+        self.act_quantizer_q = UniformAffineQuantizer(**params_w)
+        self.act_quantizer_k = UniformAffineQuantizer(**params_w)
+        self.act_quantizer_v = UniformAffineQuantizer(**params_w)
+
+    def forward(self, x):
+        return unet.attn_forward(self, x)
+
+    def set_dynamic_state(self, dynamic):
+        self.act_quantizer_w.dynamic = dynamic
+
+
+def get_specials(quant_act=False):
+    """Class-name -> quantised block map (qdiff/quant_block.py:372-384, pixel-UNet entries)."""
+    return {
+        'ResnetBlock': QuantResnetBlock,
+        'AttnBlock': QuantAttnBlock,
+    }

@@ -1,0 +1,421 @@
+"""QuantModule / UniformAffineQuantizer with the reference's Python surface, backed by the
+sm_100a kernels of libmodiff_b200.so.
+
+Mirrors qdiff/quant_layer.py of the reference: same constructor arguments, attributes, flag
+setters (including the misspelt `set_modualtion`) and forward semantics
+(qdiff/quant_layer.py:307-367).  What differs is where the arithmetic happens: activations
+are quantised to real int8 codes by `modiff_modq`, multiplied on the tensor cores by
+`modiff_igemm_conv`, and the cached output `o_hat` is updated in the GEMM epilogue.
+
+There is no CPU path: CUDA float32 tensors only, anything else raises `ModiffError`.
+"""
+import ctypes as C
+import logging
+from typing import Union
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import ConvGeom, ModiffError
+
+logger = logging.getLogger(__name__)
+
+
+class StraightThrough(nn.Module):
+    """Identity placeholder (qdiff/quant_layer.py:11-16)."""
+
+    def __init__(self, channel_num: int = 1):
+        super().__init__()
+
+    def forward(self, input):
+        return input
+
+
+def round_ste(x: torch.Tensor):
+    """Round half to even with a straight-through gradient (qdiff/quant_layer.py:19-23)."""
+    return (x.round() - x).detach() + x
+
+
+def _zeros(n, dtype, device):
+    return torch.zeros(n, dtype=dtype, device=device)
+
+
+class UniformAffineQuantizer(nn.Module):
+    """Uniform affine fake quantiser (qdiff/quant_layer.py:36-111, scale rules :134-235).
+
+    `forward(x)` returns the dequantised tensor like the reference.  `delta` and `zero_point`
+    are device tensors (no host synchronisation); inside a `QuantModule` the activation
+    quantiser's `delta` is a view of the scale buffer the kernels update every step.
+    """
+
+    def __init__(self, n_bits: int = 8, symmetric: bool = False, channel_wise: bool = False,
+                 scale_method: str = 'max', leaf_param: bool = False, always_zero: bool = False,
+                 dynamic: bool = False):
+        super().__init__()
+        self.sym = symmetric
+        self.n_bits = n_bits
+        self.n_levels = 2 ** self.n_bits if not self.sym else 2 ** (self.n_bits - 1) - 1
+        self.delta = None
+        self.zero_point = None
+        self.inited = False
+        self.leaf_param = leaf_param
+        self.channel_wise = channel_wise
+        self.scale_method = scale_method
+        self.running_stat = False
+        self.always_zero = always_zero
+        if self.leaf_param:
+            self.x_min, self.x_max = None, None
+        self.dynamic = dynamic
+        self._scratch = None
+
+    def forward(self, x: torch.Tensor):
+        _lib.require_cuda(x, "quantiser input")
+        if 'max' not in self.scale_method:
+            raise ModiffError(f"scale_method {self.scale_method!r} is a calibration-time search "
+                              "and is not part of the accelerated sampling path")
+        if self.running_stat:
+            raise ModiffError("running_stat (EMA ranges) is not part of the accelerated path")
+        x = x.contiguous()
+        slices = x.shape[0] if self.channel_wise else 1
+        slice_len = x.numel() // slices
+        recompute = (not self.inited) or self.dynamic
+        dev = x.device
+        if self.delta is None or not isinstance(self.delta, torch.Tensor) or \
+                self.delta.numel() != slices or self.delta.device != dev:
+            if not recompute:
+                raise ModiffError("quantiser scale does not match the input")
+            shape = [slices] + [1] * (x.dim() - 1) if self.channel_wise else []
+            self.delta = torch.empty(shape, dtype=torch.float32, device=dev)
+            self.zero_point = torch.empty(shape, dtype=torch.float32, device=dev)
+        if self._scratch is None or self._scratch.device != dev or \
+                self._scratch.numel() < 16 * slices + 64:
+            self._scratch = _zeros(16 * slices + 64, torch.uint8, dev)
+        y = torch.empty_like(x)
+        _lib.check(_lib.lib().modiff_fake_quant(
+            x.data_ptr(), y.data_ptr(), slices, slice_len, self.n_bits, int(self.sym),
+            int(self.always_zero), int(self.channel_wise), int(recompute),
+            self.delta.data_ptr(), self.zero_point.data_ptr(), self._scratch.data_ptr(),
+            _lib.stream_ptr()))
+        self.inited = True
+        return y
+
+    def bitwidth_refactor(self, refactored_bit: int):
+        """qdiff/quant_layer.py:246-249 (note: resets n_levels to the asymmetric count)."""
+        self.n_bits = refactored_bit
+        self.n_levels = 2 ** self.n_bits
+
+    def extra_repr(self):
+        return (f'bit={self.n_bits}, scale_method={self.scale_method}, symmetric={self.sym}, '
+                f'channel_wise={self.channel_wise}, leaf_param={self.leaf_param}')
+
+
+class _Buffers:
+    """Device buffers of one layer geometry."""
+
+    def __init__(self, g: ConvGeom, device, per_sample):
+        l = _lib.lib()
+        self.g = g
+        self.codes = _zeros(l.modiff_codes_bytes(C.byref(g)), torch.int8, device)
+        self.x_scale = _zeros(max(2, g.batch if per_sample else 2), torch.float32, device)
+        self.scratch = _zeros(_lib.MODQ_SCRATCH_BYTES + 4 * g.batch, torch.uint8, device)
+        self.ho, self.wo = _lib.out_hw(g)
+
+
+class QuantModule(nn.Module):
+    """Quantised conv2d / conv1d(k=1) / linear with MoDiff modulation caches.
+
+    Same contract as qdiff/quant_layer.py:257-392.  `forward(input, split=0)`:
+      * first modulated call: `a_hat = input`, fp32 activations x fake-quantised weights + bias;
+      * later calls: int8 codes of `input - a_hat` with a dynamic scale, int8 GEMM, `+ o_hat`.
+    The returned tensor IS the cached `o_hat` buffer unless `alias_output` is False, so callers
+    must not modify it in place.
+    """
+
+    alias_output = True
+    igemm_impl = _lib.IMPL_AUTO
+
+    def __init__(self, org_module: Union[nn.Conv2d, nn.Linear, nn.Conv1d],
+                 weight_quant_params: dict = {}, act_quant_params: dict = {},
+                 disable_act_quant: bool = False, act_quant_mode: str = 'qdiff',
+                 modulate: bool = False):
+        super().__init__()
+        self.weight_quant_params = weight_quant_params
+        self.act_quant_params = act_quant_params
+        if isinstance(org_module, (nn.Conv2d, nn.Conv1d)):
+            self.fwd_kwargs = dict(stride=org_module.stride, padding=org_module.padding,
+                                   dilation=org_module.dilation, groups=org_module.groups)
+            self.fwd_func = F.conv2d if isinstance(org_module, nn.Conv2d) else F.conv1d
+        else:
+            self.fwd_kwargs = dict()
+            self.fwd_func = F.linear
+        self.weight = org_module.weight
+        self.org_weight = org_module.weight.data.clone()
+        if org_module.bias is not None:
+            self.bias = org_module.bias
+            self.org_bias = org_module.bias.data.clone()
+        else:
+            self.bias = None
+            self.org_bias = None
+        self.use_weight_quant = False
+        self.use_act_quant = False
+        self.act_quant_mode = act_quant_mode
+        self.disable_act_quant = disable_act_quant
+        self.weight_quantizer = UniformAffineQuantizer(**self.weight_quant_params)
+        self.act_quantizer = UniformAffineQuantizer(**self.act_quant_params)
+        self.split = 0
+
+        self.activation_function = StraightThrough()
+        self.ignore_reconstruction = False
+        self.extra_repr = org_module.extra_repr
+
+        self.modulate = modulate
+        self.a_hat = None
+        self.o_hat = None
+
+        # private device state
+        self._buffers = {}
+        self._wpack = None
+        self._org_kn = None
+        self.implicit_pad = (0, 0, 0, 0)   # extra (left, right, top, bottom) zero padding
+
+    # ------------------------------------------------------------------ geometry
+    def _geom(self, input, split):
+        k = self.fwd_kwargs
+        w = self.weight
+        if self.fwd_func is F.linear:
+            if input.shape[-1] != w.shape[1]:
+                raise ModiffError(f"linear expects {w.shape[1]} features, got {input.shape[-1]}")
+            rows = input.numel() // w.shape[1]
+            return ConvGeom(rows, w.shape[1], w.shape[0], 1, 1, 1, 1, 1, 0, 0, 0, 0, split)
+        if any(d != 1 for d in k['dilation']) or k['groups'] != 1:
+            raise ModiffError("dilated / grouped convolutions are not supported")
+        if isinstance(k['padding'], str):
+            raise ModiffError("string padding modes are not supported")
+        if self.fwd_func is F.conv2d:
+            if input.dim() != 4 or input.shape[1] != w.shape[1]:
+                raise ModiffError(f"conv2d expects [B,{w.shape[1]},H,W], got {tuple(input.shape)}")
+            sh, sw = k['stride']
+            ph, pw = k['padding']
+            b, _, h, ww = input.shape
+            kh, kw = w.shape[2], w.shape[3]
+        else:
+            if input.dim() != 3 or input.shape[1] != w.shape[1]:
+                raise ModiffError(f"conv1d expects [B,{w.shape[1]},T], got {tuple(input.shape)}")
+            sh, sw = 1, k['stride'][0]
+            ph, pw = 0, k['padding'][0]
+            b, _, ww = input.shape
+            h, kh, kw = 1, 1, w.shape[2]
+        if sh != sw and not (self.fwd_func is F.conv1d and sw == 1):
+            raise ModiffError("anisotropic strides are not supported")
+        el, er, et, eb = self.implicit_pad
+        return ConvGeom(b, w.shape[1], w.shape[0], h, ww, kh, kw, sw,
+                        ph + et, pw + el, ph + eb, pw + er, split)
+
+    def _get_buffers(self, g, device):
+        key = g.key()
+        buf = self._buffers.get(key)
+        if buf is None or buf.codes.device != device:
+            per_sample = bool(self.act_quantizer.channel_wise)
+            buf = _Buffers(g, device, per_sample)
+            self._buffers = {key: buf}   # one live geometry per layer
+            n = g.batch if per_sample else 1
+            self.act_quantizer.delta = buf.x_scale[0:n].view([n] + [1] * 3) if per_sample \
+                else buf.x_scale[0:1].view([])
+            self.act_quantizer.zero_point = 0
+            self.act_quantizer.inited = True
+            if g.split:
+                self.act_quantizer_0.delta = buf.x_scale[1:2].view([])
+                self.act_quantizer_0.zero_point = 0
+                self.act_quantizer_0.inited = True
+        return buf
+
+    # ------------------------------------------------------------------ weights
+    def _pack_weights(self, g):
+        """Quantise + pack the weights once per (weight version, bits, split)."""
+        w = self.weight
+        n_bits = self.weight_quantizer.n_bits
+        key = (w.data_ptr(), w._version, n_bits, g.split, str(w.device))
+        if self._wpack is not None and self._wpack['key'] == key:
+            return self._wpack
+        wq = self.weight_quantizer
+        if wq.sym or not wq.channel_wise or 'max' not in wq.scale_method:
+            raise ModiffError("the accelerated path expects per-output-channel asymmetric 'max' "
+                              "weight quantisation (the reference's wq_params)")
+        _lib.require_cuda(w, "weight")
+        l = _lib.lib()
+        dev = w.device
+        wc = w.detach().contiguous()
+        gp = g.copy(batch=1)
+        taps = g.kh * g.kw
+        pack = None
+        for with_sum in ((1,) if n_bits >= 8 else (0, 1)):
+            wcodes = torch.empty(l.modiff_wcodes_bytes(C.byref(gp), with_sum), dtype=torch.int8,
+                                 device=dev)
+            w_scale = _zeros(2 * g.cout, torch.float32, dev)
+            w_zp = _zeros(2 * g.cout, torch.float32, dev)
+            w_corr = _zeros(2 * g.cout, torch.int32, dev)
+            w_dq = torch.empty(g.cin * taps * g.cout, dtype=torch.float32, device=dev)
+            _lib.check(l.modiff_weight_pack(wc.data_ptr(), C.byref(gp), n_bits, with_sum,
+                                            wcodes.data_ptr(), w_scale.data_ptr(), w_zp.data_ptr(),
+                                            w_corr.data_ptr(), w_dq.data_ptr(), _lib.stream_ptr()))
+            need_corr = bool(w_corr.any().item())      # one-time host read at pack time
+            pack = dict(key=key, wcodes=wcodes, w_scale=w_scale, w_zp=w_zp,
+                        w_corr=w_corr if need_corr else None, w_dq=w_dq, with_sum=with_sum)
+            if not need_corr or with_sum:
+                break
+        shape = [g.cout] + [1] * (w.dim() - 1)
+        self.weight_quantizer.delta = pack['w_scale'][:g.cout].view(shape)
+        self.weight_quantizer.zero_point = pack['w_zp'][:g.cout].view(shape)
+        self.weight_quantizer.inited = True
+        if g.split:
+            self.weight_quantizer_0.delta = pack['w_scale'][g.cout:].view(shape)
+            self.weight_quantizer_0.zero_point = pack['w_zp'][g.cout:].view(shape)
+            self.weight_quantizer_0.inited = True
+        self._wpack = pack
+        return pack
+
+    def _org_weights_kn(self):
+        """Unquantised weights as [cin*kh*kw][cout] for the fp32 kernel."""
+        if self.org_weight.device != self.weight.device:   # plain attribute: .to() skips it
+            self.org_weight = self.org_weight.to(self.weight.device)
+            if self.org_bias is not None:
+                self.org_bias = self.org_bias.to(self.weight.device)
+        w = self.org_weight
+        key = (w.data_ptr(), w._version)
+        if self._org_kn is None or self._org_kn[0] != key:
+            self._org_kn = (key, w.reshape(w.shape[0], -1).t().contiguous())
+        return self._org_kn[1]
+
+    def packed_weights(self, split=0):
+        """Weight codes / scales as the kernels consume them (test and tooling hook)."""
+        g = ConvGeom(1, self.weight.shape[1], self.weight.shape[0], 1, 1,
+                     *(self.weight.shape[2:] if self.weight.dim() == 4 else
+                       (1, self.weight.shape[2]) if self.weight.dim() == 3 else (1, 1)),
+                     1, 0, 0, 0, 0, split)
+        return self._pack_weights(g)
+
+    # ------------------------------------------------------------------ kernels
+    def _conv_fp32(self, x, w_kn, bias, g, out):
+        _lib.check(_lib.lib().modiff_conv_fp32(x.data_ptr(), w_kn.data_ptr(), _lib.ptr(bias),
+                                               out.data_ptr(), C.byref(g), _lib.stream_ptr()))
+
+    def _modq(self, x, a_hat, buf, g):
+        aq = self.act_quantizer
+        if not aq.sym:
+            raise ModiffError("the int8 path implements symmetric activation codes (--a_sym)")
+        if not aq.dynamic:
+            raise ModiffError("the int8 path implements dynamic activation scales "
+                              "(quant_mode='dynamic'); static calibrated scales are not covered")
+        _lib.check(_lib.lib().modiff_modq(x.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                                          buf.x_scale.data_ptr(), C.byref(g), aq.n_bits,
+                                          int(aq.channel_wise), buf.scratch.data_ptr(),
+                                          _lib.stream_ptr()))
+
+    def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
+        aq = self.act_quantizer
+        _lib.check(_lib.lib().modiff_igemm_conv(
+            buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
+            buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
+            o_hat.data_ptr(), int(accumulate), _lib.ptr(bias), C.byref(g),
+            int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr()))
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input: torch.Tensor, split: int = 0):
+        _lib.require_cuda(input, "QuantModule input")
+        input = input.contiguous()
+
+        if not self.use_weight_quant and not self.use_act_quant and not self.modulate:
+            g = self._geom(input, 0)
+            buf_ho_wo = _lib.out_hw(g)
+            out = torch.empty(self._shape_from(input, g, buf_ho_wo), dtype=torch.float32,
+                              device=input.device)
+            self._conv_fp32(input, self._org_weights_kn(), self.org_bias, g, out)
+            return self.activation_function(out)
+
+        if split != 0:
+            if self.split != 0:
+                assert split == self.split
+            else:
+                logger.info(f"split at {split}!")
+                self.split = split
+                self.set_split()
+
+        act_q = (not self.disable_act_quant) and self.use_act_quant
+        g = self._geom(input, self.split if (act_q or self.use_weight_quant) else 0)
+        ho_wo = _lib.out_hw(g)
+        out_shape = self._shape_from(input, g, ho_wo)
+
+        if self.use_weight_quant:
+            pack = self._pack_weights(g)
+            w_kn, bias = pack['w_dq'], self.bias
+        else:
+            pack = None
+            w_kn, bias = self._org_weights_kn(), self.org_bias
+
+        if not act_q:
+            # weight-only quantisation or fully unquantised weights with modulate flag set
+            out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
+            self._conv_fp32(input, w_kn, bias, g, out)
+            if self.modulate and self.use_act_quant:
+                self.o_hat = out
+            return self.activation_function(out)
+
+        if pack is None:
+            raise ModiffError("activation quantisation without weight quantisation is not "
+                              "part of the accelerated path (call set_quant_state(True, True))")
+
+        buf = self._get_buffers(g, input.device)
+        if self.modulate:
+            if self.a_hat is None:
+                # first step: activations pass through unquantised (quant_layer.py:326-327, 358-359)
+                self.a_hat = input.clone()
+                out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
+                self._conv_fp32(input, w_kn, bias, g, out)
+                self.o_hat = out
+            else:
+                if self.a_hat.shape != input.shape:
+                    raise ModiffError(f"input shape {tuple(input.shape)} differs from the cached "
+                                      f"{tuple(self.a_hat.shape)}; call reset_cache() first")
+                self._modq(input, self.a_hat, buf, g)
+                self._igemm(buf, pack, self.o_hat, True, None, g)
+            out = self.o_hat if self.alias_output else self.o_hat.clone()
+        else:
+            out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
+            self._modq(input, None, buf, g)
+            self._igemm(buf, pack, out, False, bias, g)
+        return self.activation_function(out)
+
+    def _shape_from(self, input, g, ho_wo):
+        if self.fwd_func is F.linear:
+            return tuple(input.shape[:-1]) + (g.cout,)
+        if self.fwd_func is F.conv1d:
+            return (g.batch, g.cout, ho_wo[1])
+        return (g.batch, g.cout, ho_wo[0], ho_wo[1])
+
+    # ------------------------------------------------------------------ flag setters
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self.use_weight_quant = weight_quant
+        self.use_act_quant = act_quant
+
+    def set_dynamic_state(self, dynamic):
+        self.act_quantizer.dynamic = dynamic
+        if self.split != 0:
+            self.act_quantizer_0.dynamic = dynamic
+
+    def set_modualtion(self, modulation):
+        self.modulate = modulation
+
+    def reset_cache(self):
+        self.a_hat = None
+        self.o_hat = None
+
+    def set_split(self):
+        self.weight_quantizer_0 = UniformAffineQuantizer(**self.weight_quant_params)
+        self.act_quantizer_0 = UniformAffineQuantizer(**self.act_quant_params)
+
+    def set_running_stat(self, running_stat: bool):
+        self.act_quantizer.running_stat = running_stat
+        if self.split != 0:
+            self.act_quantizer_0.running_stat = running_stat

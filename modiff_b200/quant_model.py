@@ -1,0 +1,85 @@
+"""QuantModel: in-place rewrite of a UNet into quantised modules / blocks plus the flag
+fan-out, with the reference's surface (qdiff/quant_model.py:12-118)."""
+import logging
+
+import torch.nn as nn
+
+from .quant_block import get_specials, BaseQuantBlock, QuantAttnBlock
+from .quant_layer import QuantModule, StraightThrough
+
+logger = logging.getLogger(__name__)
+
+
+class QuantModel(nn.Module):
+
+    def __init__(self, model: nn.Module, weight_quant_params: dict = {},
+                 act_quant_params: dict = {}, **kwargs):
+        super().__init__()
+        self.model = model
+        self.sm_abit = kwargs.get('sm_abit', 8)
+        self.modulate = kwargs.get("modulate", False)
+        self.in_channels = model.in_channels
+        if hasattr(model, 'image_size'):
+            self.image_size = model.image_size
+        self.specials = get_specials(act_quant_params['leaf_param'])
+        self.quant_module_refactor(self.model, weight_quant_params, act_quant_params)
+        self.quant_block_refactor(self.model, weight_quant_params, act_quant_params)
+
+    def quant_module_refactor(self, module: nn.Module, weight_quant_params: dict = {},
+                              act_quant_params: dict = {}):
+        """Replace every Conv2d / Conv1d / Linear child by a QuantModule, recursively
+        (qdiff/quant_model.py:26-44)."""
+        for name, child in module.named_children():
+            if isinstance(child, (nn.Conv2d, nn.Conv1d, nn.Linear)):
+                setattr(module, name, QuantModule(child, weight_quant_params, act_quant_params,
+                                                  modulate=self.modulate))
+            elif isinstance(child, StraightThrough):
+                continue
+            else:
+                self.quant_module_refactor(child, weight_quant_params, act_quant_params)
+
+    def quant_block_refactor(self, module: nn.Module, weight_quant_params: dict = {},
+                             act_quant_params: dict = {}):
+        """Re-host residual / attention blocks (qdiff/quant_model.py:46-62)."""
+        for name, child in module.named_children():
+            special = self.specials.get(type(child).__name__)
+            if special is not None and not isinstance(child, BaseQuantBlock):
+                if special is QuantAttnBlock:
+                    setattr(module, name, special(child, act_quant_params, sm_abit=self.sm_abit))
+                else:
+                    setattr(module, name, special(child, act_quant_params))
+            else:
+                self.quant_block_refactor(child, weight_quant_params, act_quant_params)
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        for m in self.model.modules():
+            if isinstance(m, (QuantModule, BaseQuantBlock)):
+                m.set_quant_state(weight_quant, act_quant)
+
+    def reset_cache(self):
+        for m in self.model.modules():
+            if isinstance(m, QuantModule):
+                m.reset_cache()
+
+    def set_dynamic_state(self, dynamic):
+        for m in self.model.modules():
+            if isinstance(m, (QuantModule, QuantAttnBlock)):
+                m.set_dynamic_state(dynamic)
+
+    def set_modulation(self, modulation):
+        for m in self.model.modules():
+            if isinstance(m, QuantModule):
+                m.set_modualtion(modulation)
+
+    def forward(self, x, timesteps=None, context=None):
+        return self.model(x, timesteps, context)
+
+    def set_running_stat(self, running_stat: bool, sm_only=False):
+        for m in self.model.modules():
+            if isinstance(m, QuantModule) and not sm_only:
+                m.set_running_stat(running_stat)
+
+    def set_grad_ckpt(self, grad_ckpt: bool):
+        for _, m in self.model.named_modules():
+            if hasattr(m, 'checkpoint') and isinstance(m, BaseQuantBlock):
+                m.checkpoint = grad_ckpt

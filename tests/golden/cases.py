@@ -1,0 +1,118 @@
+"""Case definitions shared by make_golden.py (which runs the reference on them) and by the
+tests (which re-create the same inputs / weights from the recorded seeds)."""
+import numpy as np
+import torch
+import torch.nn as nn
+
+# ---------------------------------------------------------------- stand-alone quantiser
+QUANTIZER_CASES = [
+    dict(name="pt_sym8", shape=(2, 16, 8, 8), n_bits=8, sym=True, channel_wise=False, seed=11),
+    dict(name="pt_sym4", shape=(2, 16, 8, 8), n_bits=4, sym=True, channel_wise=False, seed=12),
+    dict(name="pt_sym3", shape=(3, 8, 5, 7), n_bits=3, sym=True, channel_wise=False, seed=13),
+    dict(name="pt_asym8", shape=(2, 16, 8, 8), n_bits=8, sym=False, channel_wise=False, seed=14),
+    dict(name="pt_asym4_pos", shape=(2, 16, 8, 8), n_bits=4, sym=False, channel_wise=False,
+         seed=15, offset=3.0),
+    dict(name="pt_asym8_az", shape=(4, 33), n_bits=8, sym=False, channel_wise=False, seed=16,
+         always_zero=True, relu=True),
+    dict(name="cw_asym8", shape=(32, 16, 3, 3), n_bits=8, sym=False, channel_wise=True, seed=17),
+    dict(name="cw_asym4", shape=(32, 16, 3, 3), n_bits=4, sym=False, channel_wise=True, seed=18),
+    dict(name="cw_sym8", shape=(6, 4, 9, 9), n_bits=8, sym=True, channel_wise=True, seed=19),
+    dict(name="cw_asym8_2d", shape=(24, 40), n_bits=8, sym=False, channel_wise=True, seed=20),
+    dict(name="pt_sym8_zero", shape=(2, 4, 4, 4), n_bits=8, sym=True, channel_wise=False, seed=21,
+         scale=0.0),
+    dict(name="pt_sym8_ties", shape=(1, 1, 1, 255), n_bits=8, sym=True, channel_wise=False,
+         seed=22, ties=True),
+]
+
+
+def quantizer_input(c):
+    g = torch.Generator().manual_seed(c["seed"])
+    if c.get("ties"):
+        # multiples of half a quantisation step: exercises round-half-to-even
+        n = int(np.prod(c["shape"]))
+        x = (torch.arange(n, dtype=torch.float32) - n // 2) * 0.5
+        return x.reshape(c["shape"])
+    x = torch.randn(c["shape"], generator=g) * c.get("scale", 1.0) + c.get("offset", 0.0)
+    if c.get("relu"):
+        x = torch.relu(x)
+    return x
+
+
+# ---------------------------------------------------------------- single modulated layers
+LAYER_CASES = [
+    dict(name="c3_w8a8", kind="conv", cin=128, cout=128, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=8, a_bits=8, seed=101),
+    dict(name="c3_w4a4", kind="conv", cin=256, cout=128, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=4, a_bits=4, seed=102),
+    dict(name="c3_w4a3", kind="conv", cin=128, cout=256, k=3, stride=1, pad=1, hw=4, batch=3,
+         w_bits=4, a_bits=3, seed=103),
+    dict(name="c1_split_w4a4", kind="conv", cin=384, cout=128, k=1, stride=1, pad=0, hw=8,
+         batch=2, w_bits=4, a_bits=4, split=256, seed=104),
+    dict(name="c1_split_w8a8", kind="conv", cin=256, cout=128, k=1, stride=1, pad=0, hw=4,
+         batch=2, w_bits=8, a_bits=8, split=128, seed=105),
+    dict(name="down_w8a8", kind="conv", cin=128, cout=128, k=3, stride=2, pad=0, hw=8, batch=2,
+         w_bits=8, a_bits=8, pad_br=True, seed=106),
+    dict(name="lin_w8a8", kind="linear", cin=512, cout=256, batch=4, w_bits=8, a_bits=8, seed=107),
+    dict(name="lin_w4a4", kind="linear", cin=128, cout=512, batch=4, w_bits=4, a_bits=4, seed=108),
+    dict(name="cin3_w8a8", kind="conv", cin=3, cout=128, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=8, a_bits=8, seed=109),
+    dict(name="cout3_w4a4", kind="conv", cin=128, cout=3, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=4, a_bits=4, seed=110),
+    dict(name="c3_32_w8a8", kind="conv", cin=128, cout=16, k=3, stride=1, pad=1, hw=32, batch=1,
+         w_bits=8, a_bits=8, seed=111, skip_a_hat=True),
+]
+
+
+def layer_module(c):
+    """The fp32 torch layer whose default init (seeded) supplies the weights."""
+    torch.manual_seed(c["seed"])
+    if c["kind"] == "linear":
+        return nn.Linear(c["cin"], c["cout"])
+    return nn.Conv2d(c["cin"], c["cout"], kernel_size=c["k"], stride=c["stride"], padding=c["pad"])
+
+
+def layer_inputs(c):
+    """Four drifting inputs: step 0 (unquantised), two residual steps, one zero-residual step."""
+    g = torch.Generator().manual_seed(c["seed"] + 1000)
+    shape = (c["batch"], c["cin"]) if c["kind"] == "linear" else \
+        (c["batch"], c["cin"], c["hw"], c["hw"])
+    x0 = torch.randn(shape, generator=g)
+    x1 = x0 + 0.1 * torch.randn(shape, generator=g)
+    x2 = x1 + 0.03 * torch.randn(shape, generator=g)
+    return [x0, x1, x2, x2.clone()]
+
+
+def quant_params(c):
+    """The dicts scripts/sample_diffusion_ddim.py:143-146 builds for
+    --ptq --quant_act --quant_mode dynamic --a_sym."""
+    wq = {'n_bits': c["w_bits"], 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': c["a_bits"], 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    return wq, aq
+
+
+# ---------------------------------------------------------------- whole-UNet sampling runs
+UNET_CASES = [
+    dict(name="fp32_b8_s100", quant=False, split=False, batch=8, steps=100, noise_seed=0),
+    dict(name="w8a8_b8_s100", quant=True, split=False, w_bits=8, a_bits=8, batch=8, steps=100,
+         noise_seed=0, keep_eps=3),
+    dict(name="w4a4_split_b8_s100", quant=True, split=True, w_bits=4, a_bits=4, batch=8, steps=100,
+         noise_seed=1, keep_eps=3),
+    dict(name="w4a3_split_b4_s100", quant=True, split=True, w_bits=4, a_bits=3, batch=4, steps=100,
+         noise_seed=2),
+    dict(name="w8a8_b2_s10", quant=True, split=False, w_bits=8, a_bits=8, batch=2, steps=10,
+         noise_seed=3, keep_eps=10),
+    dict(name="w4a4_split_b2_s10", quant=True, split=True, w_bits=4, a_bits=4, batch=2, steps=10,
+         noise_seed=4, keep_eps=10),
+]
+
+
+def unet_noise(c):
+    g = torch.Generator().manual_seed(c["noise_seed"])
+    return torch.randn(c["batch"], 3, 32, 32, generator=g)
+
+
+def unet_sequence(c):
+    """Quad skip over 1000 timesteps (scripts/sample_diffusion_ddim.py:377-384)."""
+    seq = np.linspace(0, np.sqrt(1000 * 0.8), c["steps"]) ** 2
+    return [int(s) for s in list(seq)]

@@ -1,0 +1,171 @@
+"""Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
+ddim packages, imported read-only from a checkout) on CPU.
+
+    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer]
+
+Needs the reference checkout, so it runs where that exists; the fixtures it writes are
+committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
+from the seeds recorded in `cases.py` (torch CPU generators), only the reference's outputs are.
+"""
+import json
+import os
+import sys
+import time
+import warnings
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.dont_write_bytecode = True
+import cases  # noqa: E402
+
+REF = next((a for a in sys.argv[1:] if not a.startswith("--")), "/root/reference")
+ONLY = sys.argv[sys.argv.index("--only") + 1] if "--only" in sys.argv else None
+sys.path.insert(0, REF)
+warnings.filterwarnings("ignore", category=SyntaxWarning)
+
+from qdiff.quant_layer import QuantModule as RefQuantModule  # noqa: E402
+from qdiff.quant_layer import UniformAffineQuantizer as RefQuantizer  # noqa: E402
+from qdiff.quant_model import QuantModel as RefQuantModel  # noqa: E402
+from ddim.models.diffusion import Model as RefModel  # noqa: E402
+from ddim.functions.denoising import compute_alpha as ref_compute_alpha  # noqa: E402
+
+
+def ref_config(split_shortcut):
+    import yaml
+    import argparse
+
+    def ns(d):
+        n = argparse.Namespace()
+        for k, v in d.items():
+            setattr(n, k, ns(v) if isinstance(v, dict) else v)
+        return n
+
+    with open(os.path.join(REF, "configs", "cifar10.yml")) as fh:
+        cfg = ns(yaml.safe_load(fh))
+    cfg.split_shortcut = split_shortcut
+    return cfg
+
+
+def gen_quantizer():
+    out = {}
+    for c in cases.QUANTIZER_CASES:
+        x = cases.quantizer_input(c)
+        q = RefQuantizer(n_bits=c["n_bits"], symmetric=c["sym"], channel_wise=c["channel_wise"],
+                         scale_method="max", leaf_param=False, always_zero=c.get("always_zero", False),
+                         dynamic=True)
+        y = q(x)
+        out[c["name"] + "/y"] = y.detach().numpy()
+        out[c["name"] + "/delta"] = np.asarray(q.delta.detach().numpy(), dtype=np.float32).reshape(-1)
+        zp = q.zero_point
+        zp = zp.detach().numpy() if isinstance(zp, torch.Tensor) else np.asarray([zp])
+        out[c["name"] + "/zp"] = np.asarray(zp, dtype=np.float32).reshape(-1)
+    np.savez_compressed(os.path.join(HERE, "quantizer.npz"), **out)
+    print("quantizer.npz", len(out))
+
+
+def gen_layers():
+    out = {}
+    for c in cases.LAYER_CASES:
+        org = cases.layer_module(c)
+        wq, aq = cases.quant_params(c)
+        m = RefQuantModule(org, wq, aq, modulate=True)
+        m.set_quant_state(True, True)
+        xs = cases.layer_inputs(c)
+        with torch.no_grad():
+            for s, x in enumerate(xs):
+                if c.get("pad_br"):
+                    x = F.pad(x, (0, 1, 0, 1))
+                y = m(x, split=c.get("split", 0)) if c.get("split", 0) else m(x)
+                out[f"{c['name']}/out{s}"] = y.numpy().copy()
+                if s > 0:
+                    d = [float(m.act_quantizer.delta)]
+                    if c.get("split", 0):
+                        d.append(float(m.act_quantizer_0.delta))
+                    out[f"{c['name']}/delta{s}"] = np.asarray(d, dtype=np.float32)
+            if not c.get("skip_a_hat"):
+                out[f"{c['name']}/a_hat"] = m.a_hat.numpy().copy()
+        wd = m.weight_quantizer.delta.detach().reshape(-1).numpy()
+        out[f"{c['name']}/w_delta"] = wd.copy()
+        out[f"{c['name']}/w_zp"] = m.weight_quantizer.zero_point.detach().reshape(-1).numpy().copy()
+    np.savez_compressed(os.path.join(HERE, "layers.npz"), **out)
+    print("layers.npz", len(out))
+
+
+def gen_weights():
+    torch.manual_seed(0)
+    model = RefModel(ref_config(False))
+    summary = {}
+    for k, v in model.state_dict().items():
+        v = v.double()
+        summary[k] = [list(v.shape), float(v.sum()), float(v.abs().sum()),
+                      float((v * torch.arange(1, v.numel() + 1, dtype=torch.float64).reshape(v.shape)
+                             ).sum() / v.numel())]
+    with open(os.path.join(HERE, "weights_seed0.json"), "w") as fh:
+        json.dump(summary, fh)
+    print("weights_seed0.json", len(summary))
+
+
+def ref_sample(qnn, x, seq, betas, on_step=None):
+    """ddim/functions/denoising.py:10-55 without its .to('cuda')."""
+    n = x.size(0)
+    seq_next = [-1] + list(seq[:-1])
+    xt = x
+    with torch.no_grad():
+        for step, (i, j) in enumerate(zip(reversed(seq), reversed(seq_next))):
+            t = torch.ones(n) * i
+            next_t = torch.ones(n) * j
+            at = ref_compute_alpha(betas, t.long())
+            at_next = ref_compute_alpha(betas, next_t.long())
+            et = qnn(xt, t)
+            x0_t = (xt - et * (1 - at).sqrt()) / at.sqrt()
+            c2 = (1 - at_next).sqrt()
+            xt = at_next.sqrt() * x0_t + c2 * et
+            if on_step:
+                on_step(step, et, xt)
+    return xt
+
+
+def gen_unet():
+    out = {}
+    betas = torch.from_numpy(np.linspace(1e-4, 2e-2, 1000, dtype=np.float64)).float()
+    for c in cases.UNET_CASES:
+        t0 = time.time()
+        torch.manual_seed(0)
+        model = RefModel(ref_config(c["split"])).eval()
+        x = cases.unet_noise(c)
+        seq = cases.unet_sequence(c)
+        if c["quant"]:
+            wq, aq = cases.quant_params(c)
+            qnn = RefQuantModel(model=model, weight_quant_params=wq, act_quant_params=aq,
+                                sm_abit=8, modulate=True).eval()
+            qnn.set_quant_state(True, True)
+            qnn.reset_cache()
+            fn = qnn
+        else:
+            fn = lambda a, b: model(a, b)  # noqa: E731
+        eps = []
+
+        def grab(step, et, xt):
+            if step < c.get("keep_eps", 0):
+                eps.append(et.numpy().copy())
+
+        final = ref_sample(fn, x, seq, betas, grab)
+        out[c["name"] + "/final"] = final.numpy().copy()
+        for s, e in enumerate(eps):
+            out[f"{c['name']}/eps{s}"] = e
+        print(c["name"], f"{time.time() - t0:.1f}s", float(final.std()))
+    np.savez_compressed(os.path.join(HERE, "unet.npz"), **out)
+    print("unet.npz", len(out))
+
+
+if __name__ == "__main__":
+    torch.set_num_threads(os.cpu_count())
+    todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet)
+    for name, fn in todo.items():
+        if ONLY in (None, name):
+            fn()
