@@ -182,8 +182,11 @@ int modiff_upsample2x(const float* x, float* y, int batch, int c, int h, int w, 
 int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, int batch,
                     int hw, void* stream);
 
-/* Sinusoidal timestep embedding [batch][dim] (ddim/models/diffusion.py:6-24). */
-int modiff_timestep_embedding(const float* t, float* emb, int batch, int dim, void* stream);
+/* Sinusoidal timestep embedding [batch][dim]: sin(t*freq) | cos(t*freq)
+ * (ddim/models/diffusion.py:6-24).  freq[dim/2] = exp(-i*log(10000)/(dim/2-1)) is supplied by
+ * the caller so that it carries the same bits as the host library's exp. */
+int modiff_timestep_embedding(const float* t, const float* freq, float* emb, int batch, int dim,
+                              void* stream);
 
 /* One DDIM (generalised) update (ddim/functions/denoising.py:30-48):
  *   x0 = (x - e*s1) / s2;  x' = s3*x0 + c1*noise + c2*e

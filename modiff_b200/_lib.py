@@ -62,7 +62,7 @@ SIGNATURES = {
     "modiff_add": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_upsample2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_concat_c": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_int, _P]),
-    "modiff_timestep_embedding": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),
+    "modiff_timestep_embedding": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P]),
     "modiff_ddim_step": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64] + [C.c_float] * 5 + [_P]),
     "modiff_pack_int4": (C.c_int, [_P, _P, C.c_int64, _P]),
     "modiff_unpack_int4": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
@@ -87,6 +87,54 @@ def lib():
             fn.argtypes = args
         _lib = l
     return _lib
+
+
+# kernels one successful call of an entry point launches (for launch accounting)
+KERNELS_PER_CALL = {
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
+    "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
+    "modiff_upsample2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
+    "modiff_ddim_step": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
+    "modiff_quantize_static": 1,
+}
+LAUNCHES = [0]        # kernels launched through `call` since import
+TIMER = None          # a KernelTimer while per-kernel timing is on
+
+
+class KernelTimer:
+    """Brackets every `call` with CUDA events on the current stream and sums, per entry point,
+    device time and the algorithmic bytes the caller declares."""
+
+    def __init__(self):
+        self.records = {}
+
+    def add(self, name, start, end, nbytes):
+        self.records.setdefault(name, []).append((start, end, nbytes))
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, recs in self.records.items():
+            ms = sum(s.elapsed_time(e) for s, e, _ in recs)
+            out[name] = dict(launches=len(recs), ms=ms, bytes=sum(b for _, _, b in recs))
+        return out
+
+
+def call(name, *args, nbytes=0):
+    """Invoke an entry point, raise on a non-zero status, account its launches."""
+    fn = getattr(lib(), name)
+    if TIMER is None:
+        rc = fn(*args)
+    else:
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        rc = fn(*args)
+        end.record()
+        TIMER.add(name, start, end, nbytes)
+    if rc != 0:
+        check(rc)
+    LAUNCHES[0] += KERNELS_PER_CALL.get(name, 0)
 
 
 def check(rc):

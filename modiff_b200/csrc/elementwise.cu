@@ -152,17 +152,16 @@ __global__ void concat_c_kernel(const float* __restrict__ a, int64_t ea, const f
   }
 }
 
-__global__ void timestep_embedding_kernel(const float* __restrict__ t, float* __restrict__ emb,
-                                          int batch, int dim) {
+__global__ void timestep_embedding_kernel(const float* __restrict__ t,
+                                          const float* __restrict__ freq,
+                                          float* __restrict__ emb, int batch, int dim) {
   const int half = dim / 2;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch * dim) return;
   const int b = i / dim, j = i % dim;
   if (j >= 2 * half) { emb[i] = 0.0f; return; }  // odd dim: zero pad
   const int f = (j < half) ? j : j - half;
-  const float coef = (float)(-(log(10000.0) / (double)(half - 1)));
-  const float freq = expf(__fmul_rn((float)f, coef));
-  const float arg = __fmul_rn(t[b], freq);
+  const float arg = __fmul_rn(t[b], freq[f]);
   emb[i] = (j < half) ? sinf(arg) : cosf(arg);
 }
 
@@ -284,9 +283,10 @@ int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, in
   return MODIFF_OK;
 }
 
-int modiff_timestep_embedding(const float* t, float* emb, int batch, int dim, void* stream) {
-  MODIFF_CHECK_ARG(t && emb && batch > 0 && dim >= 4, "bad argument");
-  timestep_embedding_kernel<<<ceil_div(batch * dim, 256), 256, 0, (cudaStream_t)stream>>>(t, emb, batch, dim);
+int modiff_timestep_embedding(const float* t, const float* freq, float* emb, int batch, int dim,
+                              void* stream) {
+  MODIFF_CHECK_ARG(t && freq && emb && batch > 0 && dim >= 4, "bad argument");
+  timestep_embedding_kernel<<<ceil_div(batch * dim, 256), 256, 0, (cudaStream_t)stream>>>(t, freq, emb, batch, dim);
   MODIFF_LAUNCH_CHECK("timestep_embedding_kernel");
   return MODIFF_OK;
 }

@@ -4,7 +4,7 @@
 //     shared-memory ring;
 //   - one elected thread issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=128|144, K=32)
 //     with int32 accumulators in tensor memory, double buffered across output tiles;
-//   - four epilogue warps read the accumulators with tcgen05.ld and apply the modulation
+//   - eight epilogue warps read the accumulators with tcgen05.ld and apply the modulation
 //     epilogue  out = o_hat + acc * delta_x * delta_w[c] (+ bias), writing the new o_hat.
 // Persistent kernel, one CTA per SM, warp specialised (TMA / MMA / epilogue).
 // Every mbarrier wait is bounded: when a limit runs out the kernel records an error word,
@@ -27,7 +27,7 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kChunkK = 128;          // bytes of K per pipeline stage (one swizzle atom row)
 constexpr int kATileBytes = kTileM * kChunkK;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;            // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kMaxStages = 6;
 constexpr uint32_t kSpinLimit = 1u << 28;
 
@@ -228,7 +228,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[b]), 4);
+      mbar_init(smem_u32(&bar_tmem_empty[b]), 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -315,9 +315,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;           // tensor-memory lane quarter this warp may read
-    const int ep_tid = threadIdx.x - 64;    // 0..127
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each tensor-memory lane quarter; each takes 64 of the 128 columns.
+    const int quarter = warp & 3;           // lane quarter this warp may read
+    const int half = (warp - 2) >> 2;       // column half this warp handles
+    const int ep_tid = threadIdx.x - 64;    // 0..255
     const int row = quarter * 32 + lane;    // accumulator row = output pixel of the tile
     const int howo = p.d.ho * p.d.wo;
     const size_t M = (size_t)p.g.batch * howo;
@@ -327,8 +329,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(tile, p);
       // per-tile channel parameters
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      {
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (ep_tid < 128) {
         const int co = t.nt * 128 + ep_tid;
         const bool cv = co < p.g.cout;
         for (int seg = 0; seg < p.nseg; ++seg) {
@@ -337,11 +339,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         ep_bias[ep_tid] = (cv && p.bias) ? p.bias[co] : 0.0f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-
-      if (ok) ok = mbar_wait(smem_u32(&bar_tmem_full[buf]), bphase, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
 
       const int ni = row / (p.bh * p.bw);
       const int hi = (row / p.bw) % p.bh;
@@ -350,8 +348,23 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
       const bool valid = n < p.g.batch;
       const size_t m = (size_t)n * howo + hw;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.buf_cols);
+      const int col0 = half * 64;                       // first column of this warp
+      const int co0 = t.nt * 128 + col0;                // first output channel of this warp
+      const int ncols = min(64, p.g.cout - co0);        // may be <= 0 on a ragged last tile
+      float* obase = p.o_hat + ((size_t)n * p.g.cout + co0) * howo + hw;
 
+      // The cached output of this thread's 64 elements: all loads are issued before the
+      // accumulators are awaited so that they overlap the tail of the MMA work.
+      float ov[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j)
+        ov[j] = (valid && p.accumulate && j < ncols) ? obase[(size_t)j * howo] : 0.0f;
+
+      if (ok) ok = mbar_wait(smem_u32(&bar_tmem_full[buf]), bphase, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.buf_cols);
       float xs[2];
       xs[0] = p.per_sample ? (valid ? p.x_scale[n] : 0.0f) : p.x_scale[0];
       xs[1] = (p.nseg == 2) ? p.x_scale[1] : 0.0f;
@@ -360,31 +373,30 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int seg = 0; seg < p.nseg; ++seg) tc_ld1(t_row + seg * p.umma_n + 128, rsum[seg]);
         tc_wait_ld();
       }
-      float* obase = p.o_hat + ((size_t)n * p.g.cout) * howo + hw;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        int a0[32], a1[32];
-        tc_ld32(t_row + cc * 32, a0);
-        if (p.nseg == 2) tc_ld32(t_row + p.umma_n + cc * 32, a1);
-        tc_wait_ld();
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        // one segment at a time through the same registers: ov accumulates the result
+        for (int seg = 0; seg < p.nseg; ++seg) {
+          int a[32];
+          tc_ld32(t_row + seg * p.umma_n + col0 + c2 * 32, a);
+          tc_wait_ld();
+          const float xsv = xs[seg];
+          const int rs = rsum[seg];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int jj = c2 * 32 + j;
+            const int cl = col0 + jj;
+            const int iv = a[j] + ep_corr[seg][cl] * rs;
+            ov[jj] += (float)iv * __fmul_rn(xsv, ep_scale[seg][cl]);
+            if (p.acc_out && valid && jj < ncols)
+              p.acc_out[((size_t)seg * M + m) * p.g.cout + co0 + jj] = iv;
+          }
+        }
         if (valid) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int cl = cc * 32 + j;
-            const int co = t.nt * 128 + cl;
-            if (co < p.g.cout) {
-              const int i0 = a0[j] + ep_corr[0][cl] * rsum[0];
-              float v = (float)i0 * __fmul_rn(xs[0], ep_scale[0][cl]);
-              if (p.nseg == 2) {
-                const int i1 = a1[j] + ep_corr[1][cl] * rsum[1];
-                v += (float)i1 * __fmul_rn(xs[1], ep_scale[1][cl]);
-                if (p.acc_out) p.acc_out[(M + m) * p.g.cout + co] = i1;
-              }
-              if (p.acc_out) p.acc_out[m * p.g.cout + co] = i0;
-              float* o = obase + (size_t)co * howo;
-              if (p.accumulate) v += *o;
-              *o = v + ep_bias[cl];
-            }
+            const int jj = c2 * 32 + j;
+            if (jj < ncols) obase[(size_t)jj * howo] = ov[jj] + ep_bias[col0 + jj];
           }
         }
       }

@@ -1,0 +1,81 @@
+"""Data-parallel sampling over the image batch: one process per GPU, every rank samples its
+own shard with its own noise seed, and a single all-gather at the end assembles the samples.
+The reference is single-process (its only multi-GPU switch raises NotImplementedError,
+qdiff/layer_recon.py:102-105); images are independent given their x_T, so nothing is
+exchanged inside the sampling loop.
+
+Per-tensor dynamic activation scales couple the images of one shard (the scale is the maximum
+over the whole batch tensor, qdiff/quant_layer.py:197-206), so a rank's samples equal a
+single-process run on exactly that shard, not a slice of one big batch.
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def env_world():
+    """(rank, local_rank, world_size) from the torchrun environment (1 process -> 0, 0, 1)."""
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+def init(backend=None):
+    """Initialise the default process group when launched by torchrun; no-op otherwise."""
+    rank, local_rank, world = env_world()
+    if world > 1 and not dist.is_initialized():
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        kw = {}
+        if backend == "nccl":
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, **kw)
+    return rank, local_rank, world
+
+
+def shard_bounds(total, rank, world):
+    """Contiguous shard [lo, hi) of `total` images for `rank`; the first `total % world` ranks
+    hold one image more."""
+    base, rem = divmod(total, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def rank_seed(base_seed, rank):
+    """Noise seed of a rank's shard (rank r uses base + r)."""
+    return int(base_seed) + int(rank)
+
+
+def shard_noise(shape, base_seed, rank, device):
+    """x_T ~ N(0, 1) of one shard, drawn on the host from the rank's seed so that a
+    single-process run can re-create any shard exactly."""
+    g = torch.Generator().manual_seed(rank_seed(base_seed, rank))
+    return torch.randn(shape, generator=g).to(device)
+
+
+def gather_samples(local, group=None):
+    """All-gather equal-sized shards along dim 0 in rank order (one collective)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    local = local.contiguous()
+    out = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype,
+                      device=local.device)
+    dist.all_gather_into_tensor(out, local, group=group)
+    return out
+
+
+def gather_ragged(local, total, group=None):
+    """All-gather shards produced by `shard_bounds` (sizes may differ by one): pads to the
+    largest shard, gathers once, and drops the padding."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    sizes = [shard_bounds(total, r, world) for r in range(world)]
+    biggest = max(hi - lo for lo, hi in sizes)
+    pad = biggest - local.shape[0]
+    if pad:
+        local = torch.cat([local, local.new_zeros((pad,) + tuple(local.shape[1:]))], dim=0)
+    full = gather_samples(local, group).view((world, biggest) + tuple(local.shape[1:]))
+    return torch.cat([full[r, :hi - lo] for r, (lo, hi) in enumerate(sizes)], dim=0)

@@ -3,6 +3,8 @@
 Each function allocates its output with torch (device memory plumbing) and launches one
 hand-written kernel on the current CUDA stream.  CUDA float32 tensors only.
 """
+import math
+
 import torch
 
 from . import _lib
@@ -31,9 +33,9 @@ def groupnorm(x, norm, silu=False, x1=None):
     if c != norm.num_channels:
         raise ModiffError(f"GroupNorm expects {norm.num_channels} channels, got {c}")
     y = torch.empty((b, c) + tuple(x.shape[2:]), dtype=torch.float32, device=x.device)
-    _lib.check(_lib.lib().modiff_groupnorm_silu(
+    _lib.call('modiff_groupnorm_silu', 
         x.data_ptr(), _lib.ptr(x1), c0, y.data_ptr(), norm.weight.data_ptr(), norm.bias.data_ptr(),
-        b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr()))
+        b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr())
     return y
 
 
@@ -41,7 +43,7 @@ def silu(x):
     _req(x)
     x = x.contiguous()
     y = torch.empty_like(x)
-    _lib.check(_lib.lib().modiff_silu(x.data_ptr(), y.data_ptr(), x.numel(), _lib.stream_ptr()))
+    _lib.call('modiff_silu', x.data_ptr(), y.data_ptr(), x.numel(), _lib.stream_ptr())
     return y
 
 
@@ -52,8 +54,8 @@ def add(a, b):
         raise ModiffError(f"add: shapes differ {tuple(a.shape)} vs {tuple(b.shape)}")
     a, b = a.contiguous(), b.contiguous()
     out = torch.empty_like(a)
-    _lib.check(_lib.lib().modiff_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), 1, 1, a.numel(), 0,
-                                     _lib.stream_ptr()))
+    _lib.call('modiff_add', a.data_ptr(), b.data_ptr(), out.data_ptr(), 1, 1, a.numel(), 0,
+                                     _lib.stream_ptr())
     return out
 
 
@@ -66,8 +68,8 @@ def add_channel_bias(a, b):
         raise ModiffError(f"add_channel_bias: bias shape {tuple(b.shape)} != {(bsz, c)}")
     hw = a.numel() // (bsz * c)
     out = torch.empty_like(a)
-    _lib.check(_lib.lib().modiff_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), bsz, c, hw, 1,
-                                     _lib.stream_ptr()))
+    _lib.call('modiff_add', a.data_ptr(), b.data_ptr(), out.data_ptr(), bsz, c, hw, 1,
+                                     _lib.stream_ptr())
     return out
 
 
@@ -76,7 +78,7 @@ def upsample2x(x):
     x = x.contiguous()
     b, c, h, w = x.shape
     y = torch.empty((b, c, 2 * h, 2 * w), dtype=torch.float32, device=x.device)
-    _lib.check(_lib.lib().modiff_upsample2x(x.data_ptr(), y.data_ptr(), b, c, h, w, _lib.stream_ptr()))
+    _lib.call('modiff_upsample2x', x.data_ptr(), y.data_ptr(), b, c, h, w, _lib.stream_ptr())
     return y
 
 
@@ -86,17 +88,32 @@ def concat_channels(a, b):
     bsz, ca, cb = a.shape[0], a.shape[1], b.shape[1]
     hw = a.numel() // (bsz * ca)
     y = torch.empty((bsz, ca + cb) + tuple(a.shape[2:]), dtype=torch.float32, device=a.device)
-    _lib.check(_lib.lib().modiff_concat_c(a.data_ptr(), ca, b.data_ptr(), cb, y.data_ptr(), bsz, hw,
-                                          _lib.stream_ptr()))
+    _lib.call('modiff_concat_c', a.data_ptr(), ca, b.data_ptr(), cb, y.data_ptr(), bsz, hw,
+                                          _lib.stream_ptr())
     return y
+
+
+_FREQ_CACHE = {}
+
+
+def _embedding_freqs(dim, device):
+    """exp(arange(half) * -(log(10000) / (half - 1))) evaluated by torch on the host, as the
+    reference does on its device (ddim/models/diffusion.py:17-19), cached per device."""
+    key = (dim, str(device))
+    if key not in _FREQ_CACHE:
+        half = dim // 2
+        emb = math.log(10000) / (half - 1)
+        _FREQ_CACHE[key] = torch.exp(torch.arange(half, dtype=torch.float32) * -emb).to(device)
+    return _FREQ_CACHE[key]
 
 
 def timestep_embedding(t, dim):
     _req(t)
     t = t.contiguous()
+    freq = _embedding_freqs(dim, t.device)
     emb = torch.empty((t.shape[0], dim), dtype=torch.float32, device=t.device)
-    _lib.check(_lib.lib().modiff_timestep_embedding(t.data_ptr(), emb.data_ptr(), t.shape[0], dim,
-                                                    _lib.stream_ptr()))
+    _lib.call('modiff_timestep_embedding', t.data_ptr(), freq.data_ptr(), emb.data_ptr(),
+                                                    t.shape[0], dim, _lib.stream_ptr())
     return emb
 
 
@@ -105,9 +122,9 @@ def ddim_step(x, e, s1, s2, s3, c1, c2, noise=None, want_x0=False):
     x, e = x.contiguous(), e.contiguous()
     x_next = torch.empty_like(x)
     x0 = torch.empty_like(x) if want_x0 else None
-    _lib.check(_lib.lib().modiff_ddim_step(x.data_ptr(), e.data_ptr(), _lib.ptr(noise),
+    _lib.call('modiff_ddim_step', x.data_ptr(), e.data_ptr(), _lib.ptr(noise),
                                            x_next.data_ptr(), _lib.ptr(x0), x.numel(),
-                                           s1, s2, s3, c1, c2, _lib.stream_ptr()))
+                                           s1, s2, s3, c1, c2, _lib.stream_ptr())
     return (x_next, x0) if want_x0 else x_next
 
 
@@ -117,7 +134,7 @@ def pack_int4(codes):
     codes = codes.contiguous()
     n = codes.numel()
     out = torch.empty((n + 1) // 2, dtype=torch.uint8, device=codes.device)
-    _lib.check(_lib.lib().modiff_pack_int4(codes.data_ptr(), out.data_ptr(), n, _lib.stream_ptr()))
+    _lib.call('modiff_pack_int4', codes.data_ptr(), out.data_ptr(), n, _lib.stream_ptr())
     return out
 
 
@@ -125,8 +142,8 @@ def unpack_int4(packed, n, signed=True):
     if not packed.is_cuda or packed.dtype != torch.uint8:
         raise ModiffError("unpack_int4 expects a CUDA uint8 tensor")
     out = torch.empty(n, dtype=torch.int8, device=packed.device)
-    _lib.check(_lib.lib().modiff_unpack_int4(packed.data_ptr(), out.data_ptr(), n, int(signed),
-                                             _lib.stream_ptr()))
+    _lib.call('modiff_unpack_int4', packed.data_ptr(), out.data_ptr(), n, int(signed),
+                                             _lib.stream_ptr())
     return out
 
 

@@ -11,6 +11,7 @@ There is no CPU path: CUDA float32 tensors only, anything else raises `ModiffErr
 """
 import ctypes as C
 import logging
+import os
 from typing import Union
 
 import torch
@@ -93,11 +94,11 @@ class UniformAffineQuantizer(nn.Module):
                 self._scratch.numel() < 16 * slices + 64:
             self._scratch = _zeros(16 * slices + 64, torch.uint8, dev)
         y = torch.empty_like(x)
-        _lib.check(_lib.lib().modiff_fake_quant(
-            x.data_ptr(), y.data_ptr(), slices, slice_len, self.n_bits, int(self.sym),
-            int(self.always_zero), int(self.channel_wise), int(recompute),
-            self.delta.data_ptr(), self.zero_point.data_ptr(), self._scratch.data_ptr(),
-            _lib.stream_ptr()))
+        _lib.call('modiff_fake_quant',
+                  x.data_ptr(), y.data_ptr(), slices, slice_len, self.n_bits, int(self.sym),
+                  int(self.always_zero), int(self.channel_wise), int(recompute),
+                  self.delta.data_ptr(), self.zero_point.data_ptr(), self._scratch.data_ptr(),
+                  _lib.stream_ptr())
         self.inited = True
         return y
 
@@ -134,7 +135,8 @@ class QuantModule(nn.Module):
     """
 
     alias_output = True
-    igemm_impl = _lib.IMPL_AUTO
+    # MODIFF_IGEMM_IMPL=1 forces the CUDA-core kernel, =2 the tensor-core kernel (debug aid)
+    igemm_impl = int(os.environ.get("MODIFF_IGEMM_IMPL", _lib.IMPL_AUTO))
 
     def __init__(self, org_module: Union[nn.Conv2d, nn.Linear, nn.Conv1d],
                  weight_quant_params: dict = {}, act_quant_params: dict = {},
@@ -257,9 +259,9 @@ class QuantModule(nn.Module):
             w_zp = _zeros(2 * g.cout, torch.float32, dev)
             w_corr = _zeros(2 * g.cout, torch.int32, dev)
             w_dq = torch.empty(g.cin * taps * g.cout, dtype=torch.float32, device=dev)
-            _lib.check(l.modiff_weight_pack(wc.data_ptr(), C.byref(gp), n_bits, with_sum,
-                                            wcodes.data_ptr(), w_scale.data_ptr(), w_zp.data_ptr(),
-                                            w_corr.data_ptr(), w_dq.data_ptr(), _lib.stream_ptr()))
+            _lib.call('modiff_weight_pack', wc.data_ptr(), C.byref(gp), n_bits, with_sum,
+                      wcodes.data_ptr(), w_scale.data_ptr(), w_zp.data_ptr(),
+                      w_corr.data_ptr(), w_dq.data_ptr(), _lib.stream_ptr())
             need_corr = bool(w_corr.any().item())      # one-time host read at pack time
             pack = dict(key=key, wcodes=wcodes, w_scale=w_scale, w_zp=w_zp,
                         w_corr=w_corr if need_corr else None, w_dq=w_dq, with_sum=with_sum)
@@ -298,8 +300,9 @@ class QuantModule(nn.Module):
 
     # ------------------------------------------------------------------ kernels
     def _conv_fp32(self, x, w_kn, bias, g, out):
-        _lib.check(_lib.lib().modiff_conv_fp32(x.data_ptr(), w_kn.data_ptr(), _lib.ptr(bias),
-                                               out.data_ptr(), C.byref(g), _lib.stream_ptr()))
+        _lib.call('modiff_conv_fp32', x.data_ptr(), w_kn.data_ptr(), _lib.ptr(bias),
+                  out.data_ptr(), C.byref(g), _lib.stream_ptr(),
+                  nbytes=4 * (x.numel() + out.numel() + w_kn.numel()))
 
     def _modq(self, x, a_hat, buf, g):
         aq = self.act_quantizer
@@ -308,18 +311,22 @@ class QuantModule(nn.Module):
         if not aq.dynamic:
             raise ModiffError("the int8 path implements dynamic activation scales "
                               "(quant_mode='dynamic'); static calibrated scales are not covered")
-        _lib.check(_lib.lib().modiff_modq(x.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
-                                          buf.x_scale.data_ptr(), C.byref(g), aq.n_bits,
-                                          int(aq.channel_wise), buf.scratch.data_ptr(),
-                                          _lib.stream_ptr()))
+        # algorithmic bytes: x 4 + a_hat read/write 8 + code 1 per element
+        _lib.call('modiff_modq', x.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                  buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, int(aq.channel_wise),
+                  buf.scratch.data_ptr(), _lib.stream_ptr(),
+                  nbytes=(13 if a_hat is not None else 5) * x.numel())
 
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
-        _lib.check(_lib.lib().modiff_igemm_conv(
-            buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
-            buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
-            o_hat.data_ptr(), int(accumulate), _lib.ptr(bias), C.byref(g),
-            int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr()))
+        # algorithmic bytes: o_hat read + write 8 per output element, 1 per input code, weights
+        _lib.call('modiff_igemm_conv',
+                  buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
+                  buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
+                  o_hat.data_ptr(), int(accumulate), _lib.ptr(bias), C.byref(g),
+                  int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr(),
+                  nbytes=(8 if accumulate else 4) * o_hat.numel() + g.batch * g.cin * g.h * g.w
+                  + g.cout * g.cin * g.kh * g.kw)
 
     # ------------------------------------------------------------------ forward
     def forward(self, input: torch.Tensor, split: int = 0):

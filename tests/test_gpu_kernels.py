@@ -128,7 +128,8 @@ def _pack(w, g, bits, with_sum, dev):
     wc = torch.zeros(2 * g.cout, dtype=torch.int32, device=dev)
     taps = g.kh * g.kw
     wdq = torch.empty(g.cin * taps * g.cout, device=dev)
-    L.check(l.modiff_weight_pack(w.to(dev).contiguous().data_ptr(), C.byref(gp), bits, with_sum,
+    w_d = w.to(dev).contiguous()
+    L.check(l.modiff_weight_pack(w_d.data_ptr(), C.byref(gp), bits, with_sum,
                                  wcodes.data_ptr(), ws.data_ptr(), wz.data_ptr(), wc.data_ptr(),
                                  wdq.data_ptr(), L.stream_ptr()))
     torch.cuda.synchronize()
@@ -262,9 +263,10 @@ def test_conv_fp32_matches_torch(cuda):
         bias = torch.randn(cout)
         g = _geom(b, cin, cout, hw, hw, k=k, stride=stride, pad=pad)
         w_kn = w.reshape(cout, -1).t().contiguous().to(cuda)
+        x_d, bias_d = x.to(cuda), bias.to(cuda)     # keep the device copies alive
         ho, wo = L.out_hw(g)
         out = torch.empty(b, cout, ho, wo, device=cuda)
-        L.check(l.modiff_conv_fp32(x.to(cuda).data_ptr(), w_kn.data_ptr(), bias.to(cuda).data_ptr(),
+        L.check(l.modiff_conv_fp32(x_d.data_ptr(), w_kn.data_ptr(), bias_d.data_ptr(),
                                    out.data_ptr(), C.byref(g), L.stream_ptr()))
         exp = F.conv2d(x.double(), w.double(), bias.double(), stride=stride,
                        padding=(pad[0], pad[1]))

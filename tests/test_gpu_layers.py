@@ -80,19 +80,21 @@ def test_module_modes_and_errors(cuda):
     org = cases.layer_module(c)
     wq, aq = cases.quant_params(c)
     x = cases.layer_inputs(c)[0]
-    mod = m.QuantModule(org, wq, aq, modulate=False).to(cuda)
+    with torch.no_grad():
+        ref = org(x)
+    w_cpu, b_cpu = org.weight.detach().clone(), org.bias.detach().clone()
+    mod = m.QuantModule(org, wq, aq, modulate=False).to(cuda)   # moves org's parameters too
     # unquantised path == original layer
     y = mod(x.to(cuda)).cpu()
-    ref = org(x)
     assert (y - ref).abs().max() < 1e-4 * ref.abs().max()
     # weight-only quantisation
     mod.set_quant_state(True, False)
-    dq, *_ = oracle.weight_codes(org.weight.detach(), 8)
-    ref = torch.nn.functional.conv2d(x, dq, org.bias, padding=1)
+    dq, *_ = oracle.weight_codes(w_cpu, 8)
+    ref = torch.nn.functional.conv2d(x, dq, b_cpu, padding=1)
     assert (mod(x.to(cuda)).cpu() - ref).abs().max() < 1e-4 * ref.abs().max()
     # plain (non-modulated) W+A quantisation
     mod.set_quant_state(True, True)
-    orc = oracle.OracleQuantModule(org.weight.detach(), org.bias.detach(), 1, 1, 8, 8, modulate=False)
+    orc = oracle.OracleQuantModule(w_cpu, b_cpu, 1, 1, 8, 8, modulate=False)
     ref = orc.forward(x)
     assert (mod(x.to(cuda)).cpu() - ref).abs().max() < 2e-5 * ref.abs().max()
     # CPU tensors are refused, shape changes with a live cache are refused

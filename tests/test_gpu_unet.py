@@ -41,17 +41,25 @@ def sample(c, cuda, keep_eps=0):
     return xs[-1].cpu(), [e.cpu() for e in eps]
 
 
-@pytest.mark.parametrize("name", ["w8a8_b2_s10", "w4a4_split_b2_s10"])
-def test_eps_per_step(cuda, name, golden_unet):
-    """Free-running 10 steps.  Step 0 is fp32 end to end (tight); later steps are not
-    bit-reproducible in principle (an upstream fp32 rounding difference can move a residual
-    across a rounding boundary), so the bound is relative to the eps range."""
+@pytest.mark.parametrize("name,floor_db", [("w8a8_b2_s10", 40.0), ("w4a4_split_b2_s10", 20.0)])
+def test_eps_per_step(cuda, name, floor_db, golden_unet):
+    """Free-running 10 steps against the reference's per-step eps.  Step 0 is fp32 end to end
+    and must agree to 1e-4 of the eps range.  Later steps quantise step-to-step RESIDUALS, which
+    are differences of nearly equal fp32 numbers: a last-bit difference upstream (GPU vs CPU
+    summation order) moves some residuals across a rounding boundary, so those steps are not
+    bit-reproducible between any two machines; they are held to a PSNR floor per bit width and
+    the run to the 40 dB bound on the final sample."""
     c = next(u for u in cases.UNET_CASES if u["name"] == name)
     final, eps = sample(c, cuda, keep_eps=c["keep_eps"])
     for s, e in enumerate(eps):
         ref = golden_unet[f"{name}/eps{s}"]
         err = np.abs(e.numpy() - ref).max() / np.abs(ref).max()
-        assert err < (1e-4 if s == 0 else 2e-2), (s, err)
+        p = oracle.psnr(ref, e.numpy())
+        print(f"{name} step {s}: max|eps-ref|/max|ref| = {err:.2e}, PSNR {p:.1f} dB")
+        if s == 0:
+            assert err < 1e-4, err
+        else:
+            assert p >= floor_db, (s, p)
     ref = golden_unet[name + "/final"]
     assert oracle.psnr(ref, final.numpy()) >= 40.0
 
