@@ -108,19 +108,29 @@ class KernelTimer:
     def __init__(self):
         self.records = {}
 
-    def add(self, name, start, end, nbytes):
+    def add(self, name, start, end, nbytes, tag=None):
         self.records.setdefault(name, []).append((start, end, nbytes))
+        if tag is not None:
+            self.records.setdefault((name, tag), []).append((start, end, nbytes))
 
     def summary(self):
         torch.cuda.synchronize()
         out = {}
         for name, recs in self.records.items():
+            if not isinstance(name, str):
+                continue
             ms = sum(s.elapsed_time(e) for s, e, _ in recs)
             out[name] = dict(launches=len(recs), ms=ms, bytes=sum(b for _, _, b in recs))
         return out
 
+    def by_tag(self):
+        """{(entry point, tag): (launches, ms, bytes)} for calls that carried a tag."""
+        torch.cuda.synchronize()
+        return {k: (len(r), sum(s.elapsed_time(e) for s, e, _ in r), sum(b for _, _, b in r))
+                for k, r in self.records.items() if not isinstance(k, str)}
 
-def call(name, *args, nbytes=0):
+
+def call(name, *args, nbytes=0, tag=None):
     """Invoke an entry point, raise on a non-zero status, account its launches."""
     fn = getattr(lib(), name)
     if TIMER is None:
@@ -131,7 +141,7 @@ def call(name, *args, nbytes=0):
         start.record()
         rc = fn(*args)
         end.record()
-        TIMER.add(name, start, end, nbytes)
+        TIMER.add(name, start, end, nbytes, tag)
     if rc != 0:
         check(rc)
     LAUNCHES[0] += KERNELS_PER_CALL.get(name, 0)

@@ -27,7 +27,8 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kChunkK = 128;          // bytes of K per pipeline stage (one swizzle atom row)
 constexpr int kATileBytes = kTileM * kChunkK;
-constexpr int kThreads = 320;            // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;   // TMA warp, MMA warp, epilogue warps
 constexpr int kMaxStages = 6;
 constexpr uint32_t kSpinLimit = 1u << 28;
 
@@ -46,6 +47,7 @@ struct TcParams {
   int buf_cols;                  // columns per buffer
   int tmem_cols;                 // allocation (power of two)
   int a_bytes;                   // bytes one activation-tile copy delivers
+  int o_bytes;                   // bytes one cached-output-tile copy delivers
   int chunks[2];                 // 128-byte K chunks per tap of segment 0 / 1
   int cbeg[2];                   // first channel of segment 0 / 1
   int nseg;
@@ -124,6 +126,21 @@ __device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_
       : "memory");
 }
 
+__device__ inline void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                   int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ inline void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 __device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -195,14 +212,21 @@ __device__ inline TileCoord decode_tile(int tile, const TcParams& p) {
   return t;
 }
 
+// TMA_EPI: the cached-output tile travels by bulk tensor copies (global -> shared before the
+// epilogue, shared -> global after it), so the epilogue threads touch only tensor memory and
+// shared memory.  Used for full-size layers with per-tensor scales and no bias; the generic
+// variant reads and writes o_hat directly and covers everything else.
+template <int NSEG, bool WITH_SUM, bool TMA_EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const TcParams p) {
+                const __grid_constant__ CUtensorMap map_o, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ __align__(8) uint64_t bar_o_full;
+  __shared__ __align__(8) uint64_t bar_o_empty;
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ float ep_scale[2][128];
@@ -213,12 +237,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &abort_sh;
 
-  // 1024-byte aligned tile ring
+  // 1024-byte aligned tile ring, followed by the cached-output tile
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t ring = (raw + 1023u) & ~1023u;
   const int b_rows = p.umma_n;
   const uint32_t b_tile_bytes = (uint32_t)b_rows * kChunkK;
   const uint32_t stage_bytes = kATileBytes + ((b_tile_bytes + 1023u) & ~1023u);
+  const uint32_t obuf = ring + (uint32_t)p.stages * stage_bytes;
+  float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
 
   if (threadIdx.x == 0) {
     abort_sh = 0;
@@ -228,8 +254,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[b]), 8);
+      mbar_init(smem_u32(&bar_tmem_empty[b]), kEpiWarps);
     }
+    mbar_init(smem_u32(&bar_o_full), 1);
+    mbar_init(smem_u32(&bar_o_empty), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -246,12 +274,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int k_iters_seg0 = p.d.taps * p.chunks[0];
   const int k_iters_seg1 = (p.nseg == 2) ? p.d.taps * p.chunks[1] : 0;
+  const int howo = p.d.ho * p.d.wo;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t ophase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const TileCoord t = decode_tile(tile, p);
@@ -274,6 +304,16 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               if (++stage == p.stages) { stage = 0; phase ^= 1u; }
             }
           }
+        }
+        if (TMA_EPI && ok && p.accumulate) {
+          // After this tile's operand copies are queued: fetch its cached-output tile as soon
+          // as the epilogue of the previous tile has drained the buffer.
+          ok = mbar_wait(smem_u32(&bar_o_empty), ophase ^ 1u, abort_flag);
+          if (!ok) break;
+          const uint32_t ofull = smem_u32(&bar_o_full);
+          mbar_arrive_expect_tx(ofull, (uint32_t)p.o_bytes);
+          tma_load_3d(obuf, &map_o, ofull, t.th * p.bh * p.d.wo, t.nt * 128, t.tn * p.bn);
+          ophase ^= 1u;
         }
       }
     }
@@ -318,93 +358,140 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------------------------------------ epilogue (warps 2..9)
     // Two warps share each tensor-memory lane quarter; each takes 64 of the 128 columns.
     const int quarter = warp & 3;           // lane quarter this warp may read
-    const int half = (warp - 2) >> 2;       // column half this warp handles
+    const int half = (warp - 2) >> 2;       // which 64 columns this warp handles
     const int ep_tid = threadIdx.x - 64;    // 0..255
     const int row = quarter * 32 + lane;    // accumulator row = output pixel of the tile
-    const int howo = p.d.ho * p.d.wo;
     const size_t M = (size_t)p.g.batch * howo;
+    const int tile_px = p.bh * p.bw;        // pixels per image in one tile
+    const int ni = row / tile_px;
+    const int pl = row % tile_px;           // pixel index inside the image's part of the tile
+    const int hi = pl / p.bw;
+    const int wi = pl % p.bw;
+    const int col0 = half * 64;
     int buf = 0;
     uint32_t bphase = 0;
+    uint32_t ophase = 0;
+    int last_nt = -1;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(tile, p);
-      // per-tile channel parameters
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (ep_tid < 128) {
-        const int co = t.nt * 128 + ep_tid;
-        const bool cv = co < p.g.cout;
-        for (int seg = 0; seg < p.nseg; ++seg) {
-          ep_scale[seg][ep_tid] = cv ? p.w_scale[seg * p.g.cout + co] : 0.0f;
-          ep_corr[seg][ep_tid] = (cv && p.w_corr) ? p.w_corr[seg * p.g.cout + co] : 0;
+      // per-tile channel parameters (only when the channel tile changes)
+      if (t.nt != last_nt) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ep_tid < 128) {
+          const int co = t.nt * 128 + ep_tid;
+          const bool cv = co < p.g.cout;
+          for (int seg = 0; seg < NSEG; ++seg) {
+            float sc = cv ? p.w_scale[seg * p.g.cout + co] : 0.0f;
+            if (TMA_EPI) sc = __fmul_rn(p.x_scale[seg], sc);
+            ep_scale[seg][ep_tid] = sc;
+            ep_corr[seg][ep_tid] = (cv && p.w_corr) ? p.w_corr[seg * p.g.cout + co] : 0;
+          }
+          ep_bias[ep_tid] = (cv && p.bias) ? p.bias[co] : 0.0f;
         }
-        ep_bias[ep_tid] = (cv && p.bias) ? p.bias[co] : 0.0f;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        last_nt = t.nt;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-
-      const int ni = row / (p.bh * p.bw);
-      const int hi = (row / p.bw) % p.bh;
-      const int wi = row % p.bw;
-      const int n = t.tn * p.bn + ni;
-      const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
-      const bool valid = n < p.g.batch;
-      const size_t m = (size_t)n * howo + hw;
-      const int col0 = half * 64;                       // first column of this warp
-      const int co0 = t.nt * 128 + col0;                // first output channel of this warp
-      const int ncols = min(64, p.g.cout - co0);        // may be <= 0 on a ragged last tile
-      float* obase = p.o_hat + ((size_t)n * p.g.cout + co0) * howo + hw;
-
-      // The cached output of this thread's 64 elements: all loads are issued before the
-      // accumulators are awaited so that they overlap the tail of the MMA work.
-      float ov[64];
-#pragma unroll
-      for (int j = 0; j < 64; ++j)
-        ov[j] = (valid && p.accumulate && j < ncols) ? obase[(size_t)j * howo] : 0.0f;
 
       if (ok) ok = mbar_wait(smem_u32(&bar_tmem_full[buf]), bphase, abort_flag);
       if (!ok) break;
       tc_fence_after();
-
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.buf_cols);
-      float xs[2];
-      xs[0] = p.per_sample ? (valid ? p.x_scale[n] : 0.0f) : p.x_scale[0];
-      xs[1] = (p.nseg == 2) ? p.x_scale[1] : 0.0f;
       int rsum[2] = {0, 0};
-      if (p.with_sum) {
-        for (int seg = 0; seg < p.nseg; ++seg) tc_ld1(t_row + seg * p.umma_n + 128, rsum[seg]);
+      if (WITH_SUM) {
+#pragma unroll
+        for (int seg = 0; seg < NSEG; ++seg) tc_ld1(t_row + seg * p.umma_n + 128, rsum[seg]);
         tc_wait_ld();
       }
+
+      if (TMA_EPI) {
+        if (p.accumulate) {
+          ok = mbar_wait(smem_u32(&bar_o_full), ophase, abort_flag);
+          if (!ok) break;
+        }
+        // shared-memory tile: [image][channel][pixel]; lanes walk consecutive pixels
+        float* orow = obuf_ptr + (size_t)ni * 128 * tile_px + pl;
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        // one segment at a time through the same registers: ov accumulates the result
-        for (int seg = 0; seg < p.nseg; ++seg) {
-          int a[32];
-          tc_ld32(t_row + seg * p.umma_n + col0 + c2 * 32, a);
-          tc_wait_ld();
-          const float xsv = xs[seg];
-          const int rs = rsum[seg];
+        for (int c2 = 0; c2 < 2; ++c2) {
+          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int jj = c2 * 32 + j;
-            const int cl = col0 + jj;
-            const int iv = a[j] + ep_corr[seg][cl] * rs;
-            ov[jj] += (float)iv * __fmul_rn(xsv, ep_scale[seg][cl]);
-            if (p.acc_out && valid && jj < ncols)
-              p.acc_out[((size_t)seg * M + m) * p.g.cout + co0 + jj] = iv;
+          for (int j = 0; j < 32; ++j)
+            v[j] = p.accumulate ? orow[(col0 + c2 * 32 + j) * tile_px] : 0.0f;
+#pragma unroll
+          for (int seg = 0; seg < NSEG; ++seg) {
+            int a[32];
+            tc_ld32(t_row + seg * p.umma_n + col0 + c2 * 32, a);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int cl = col0 + c2 * 32 + j;
+              int iv = a[j];
+              if (WITH_SUM) iv += ep_corr[seg][cl] * rsum[seg];
+              v[j] = fmaf((float)iv, ep_scale[seg][cl], v[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) orow[(col0 + c2 * 32 + j) * tile_px] = v[j];
+        }
+        // accumulators consumed: release the tensor-memory buffer, then publish the tile
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (ep_tid == 0) {
+          tma_store_3d(&map_o, obuf, t.th * p.bh * p.d.wo, t.nt * 128, t.tn * p.bn);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(smem_u32(&bar_o_empty));
+        }
+        if (!p.accumulate) asm volatile("bar.sync 2, 256;" ::: "memory");  // buffer reuse
+        ophase ^= 1u;
+      } else {
+        const int n = t.tn * p.bn + ni;
+        const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
+        const bool valid = n < p.g.batch;
+        const size_t m = (size_t)n * howo + hw;
+        float xs[2];
+        xs[0] = p.per_sample ? (valid ? p.x_scale[n] : 0.0f) : p.x_scale[0];
+        xs[1] = (NSEG == 2) ? p.x_scale[1] : 0.0f;
+#pragma unroll 1
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int co0 = t.nt * 128 + col0 + c2 * 32;
+          const int ncols = min(32, p.g.cout - co0);   // <= 0 on a ragged last tile
+          float* obase = p.o_hat + ((size_t)n * p.g.cout + co0) * howo + hw;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = (p.accumulate && valid && j < ncols) ? obase[(size_t)j * howo] : 0.0f;
+#pragma unroll
+          for (int seg = 0; seg < NSEG; ++seg) {
+            int a[32];
+            tc_ld32(t_row + seg * p.umma_n + col0 + c2 * 32, a);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int cl = col0 + c2 * 32 + j;
+              int iv = a[j];
+              if (WITH_SUM) iv += ep_corr[seg][cl] * rsum[seg];
+              v[j] += (float)iv * __fmul_rn(xs[seg], ep_scale[seg][cl]);
+              if (p.acc_out && valid && j < ncols)
+                p.acc_out[((size_t)seg * M + m) * p.g.cout + co0 + j] = iv;
+            }
+          }
+          if (valid) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) obase[(size_t)j * howo] = v[j] + ep_bias[col0 + c2 * 32 + j];
           }
         }
-        if (valid) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int jj = c2 * 32 + j;
-            if (jj < ncols) obase[(size_t)jj * howo] = ov[jj] + ep_bias[col0 + jj];
-          }
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
       if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
     }
+    if (TMA_EPI && ep_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ---------------------------------------------------------------- teardown
@@ -505,11 +592,17 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   p.o_hat = o_hat;
   p.acc_out = acc_out;
 
+  // The bulk-copy epilogue needs full-width row tiles of at least 4 pixels per image, per-tensor
+  // scales, no bias and no accumulator dump.
+  const int tile_px = p.bh * p.bw;
+  const bool tma_epi = !per_sample && !bias && !acc_out && tile_px >= 4 && p.bw == d.wo &&
+                       (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0);
   const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
   const uint32_t stage_bytes = kATileBytes + b_tile;
-  p.stages = (int)((200u * 1024u) / stage_bytes);
+  const uint32_t o_tile = tma_epi ? 128u * 128u * 4u : 0u;
+  p.stages = (int)((204u * 1024u - o_tile) / stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
-  const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+  const size_t smem = (size_t)p.stages * stage_bytes + o_tile + 1024;
 
   // Activation codes: [batch][planes][hp][wp][cp] int8, innermost first.
   CUtensorMap map_a, map_b;
@@ -545,20 +638,58 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(weight codes) failed: %d", (int)r);
   }
 
+  CUtensorMap map_o = map_b;   // placeholder when the bulk-copy epilogue is off
+  p.o_bytes = 0;
+  if (tma_epi) {
+    // Cached output: [batch][cout][ho*wo] fp32, innermost first.
+    const int bn_box = p.bn < g->batch ? p.bn : g->batch;
+    const int c_box = g->cout < 128 ? g->cout : 128;
+    cuuint64_t dims[3] = {(cuuint64_t)(d.ho * d.wo), (cuuint64_t)g->cout, (cuuint64_t)g->batch};
+    cuuint64_t strides[2] = {(cuuint64_t)d.ho * d.wo * 4, (cuuint64_t)g->cout * d.ho * d.wo * 4};
+    cuuint32_t box[3] = {(cuuint32_t)tile_px, (cuuint32_t)c_box, (cuuint32_t)bn_box};
+    cuuint32_t estr[3] = {1, 1, 1};
+    // the shared-memory tile is addressed as [image][128][tile_px]: boxes narrower than 128
+    // channels would change that pitch, so they use the generic epilogue instead
+    if (c_box == 128) {
+      CUresult r = encode(&map_o, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)o_hat, dims, strides,
+                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS)
+        return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output) failed: %d", (int)r);
+      p.o_bytes = tile_px * 128 * bn_box * 4;
+    }
+  }
+  const bool use_tma_epi = tma_epi && p.o_bytes > 0;
+
   static int sm_count = 0;
-  static bool attr_set = false;
   if (!sm_count) {
     int dev = 0;
     MODIFF_CUDA(cudaGetDevice(&dev));
     MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  if (!attr_set) {
-    MODIFF_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     220 * 1024));
-    attr_set = true;
-  }
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
-  igemm_tc_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, p);
+  const int variant = (p.nseg == 2 ? 4 : 0) | (p.with_sum ? 2 : 0) | (use_tma_epi ? 1 : 0);
+#define MODIFF_TC_LAUNCH(NSEG, SUM, EPI)                                                       \
+  {                                                                                            \
+    static bool attr_set = false;                                                              \
+    if (!attr_set) {                                                                           \
+      MODIFF_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<NSEG, SUM, EPI>,                        \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+      attr_set = true;                                                                         \
+    }                                                                                          \
+    igemm_tc_kernel<NSEG, SUM, EPI><<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);      \
+  }
+  switch (variant) {
+    case 0: MODIFF_TC_LAUNCH(1, false, false) break;
+    case 1: MODIFF_TC_LAUNCH(1, false, true) break;
+    case 2: MODIFF_TC_LAUNCH(1, true, false) break;
+    case 3: MODIFF_TC_LAUNCH(1, true, true) break;
+    case 4: MODIFF_TC_LAUNCH(2, false, false) break;
+    case 5: MODIFF_TC_LAUNCH(2, false, true) break;
+    case 6: MODIFF_TC_LAUNCH(2, true, false) break;
+    default: MODIFF_TC_LAUNCH(2, true, true) break;
+  }
+#undef MODIFF_TC_LAUNCH
   MODIFF_LAUNCH_CHECK("igemm_tc_kernel");
   return MODIFF_OK;
 }

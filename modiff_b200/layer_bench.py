@@ -1,0 +1,77 @@
+"""Micro-benchmark of one modulated QuantModule geometry (quantiser + int8 GEMM kernels).
+
+    python -m modiff_b200.layer_bench --cin 128 --cout 128 --hw 32 --k 3 --batch 256 --iters 20
+
+Prints one JSON line: device time per call and achieved algorithmic GB/s of `modiff_modq`
+and `modiff_igemm_conv` (CUDA events on the launching stream; the tensors of one layer at
+batch 256 exceed L2).  Small enough to sit under `ncu -k regex:... -c 1`.
+"""
+import argparse
+import json
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .quant_layer import QuantModule
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cin", type=int, default=128)
+    ap.add_argument("--cout", type=int, default=128)
+    ap.add_argument("--hw", type=int, default=32)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--split", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--w-bits", type=int, default=4)
+    ap.add_argument("--a-bits", type=int, default=4)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=int, default=_lib.IMPL_AUTO)
+    ap.add_argument("--linear", action="store_true")
+    args = ap.parse_args()
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    if args.linear:
+        org = nn.Linear(args.cin, args.cout)
+        shape = (args.batch, args.cin)
+    else:
+        pad = args.k // 2 if args.stride == 1 else 0
+        org = nn.Conv2d(args.cin, args.cout, args.k, stride=args.stride, padding=pad)
+        shape = (args.batch, args.cin, args.hw, args.hw)
+    wq = {'n_bits': args.w_bits, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': args.a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    mod = QuantModule(org, wq, aq, modulate=True).to(dev)
+    mod.set_quant_state(True, True)
+    mod.igemm_impl = args.impl
+    if args.stride == 2:
+        mod.implicit_pad = (0, 1, 0, 1)
+
+    x = torch.randn(shape, device=dev)
+    drift = [0.05 * torch.randn(shape, device=dev) for _ in range(2)]
+    kw = dict(split=args.split) if args.split else {}
+    with torch.no_grad():
+        mod(x, **kw)                                   # first step: fp32 path, creates caches
+        for i in range(args.warmup):
+            mod(x + drift[i % 2], **kw)
+        _lib.TIMER = _lib.KernelTimer()
+        for i in range(args.iters):
+            mod(x + drift[i % 2], **kw)
+        summ = _lib.TIMER.summary()
+        _lib.TIMER = None
+    status = _lib.device_status()
+    out = {"geometry": vars(args), "device_status": status}
+    for name in ("modiff_modq", "modiff_igemm_conv"):
+        v = summ[name]
+        out[name] = {"us_per_call": 1000.0 * v["ms"] / v["launches"],
+                     "algorithmic_GBps": v["bytes"] / (v["ms"] / 1000.0) / 1e9,
+                     "algorithmic_bytes_per_call": v["bytes"] // v["launches"]}
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

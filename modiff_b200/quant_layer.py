@@ -315,7 +315,7 @@ class QuantModule(nn.Module):
         _lib.call('modiff_modq', x.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
                   buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, int(aq.channel_wise),
                   buf.scratch.data_ptr(), _lib.stream_ptr(),
-                  nbytes=(13 if a_hat is not None else 5) * x.numel())
+                  nbytes=(13 if a_hat is not None else 5) * x.numel(), tag=g.key())
 
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
@@ -326,7 +326,7 @@ class QuantModule(nn.Module):
                   o_hat.data_ptr(), int(accumulate), _lib.ptr(bias), C.byref(g),
                   int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr(),
                   nbytes=(8 if accumulate else 4) * o_hat.numel() + g.batch * g.cin * g.h * g.w
-                  + g.cout * g.cin * g.kh * g.kw)
+                  + g.cout * g.cin * g.kh * g.kw, tag=g.key())
 
     # ------------------------------------------------------------------ forward
     def forward(self, input: torch.Tensor, split: int = 0):
