@@ -26,8 +26,6 @@ struct ModqScratch {
   unsigned int absmax_bits[1];  // [slots]
 };
 
-__device__ inline float load1(const float* p) { return __ldg(p); }
-
 template <bool VEC4>
 __device__ inline void load4(const float* __restrict__ base, int p, int hw, float (&v)[4]) {
   if (VEC4) {
@@ -56,33 +54,55 @@ __device__ inline int slot_of(int n, int c, int split, int per_sample) {
   return (split > 0 && c >= split) ? 1 : 0;
 }
 
+struct TileGrid {
+  int pb, cb, total;   // pixel blocks, channel blocks, pb * cb * batch
+};
+
 template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
-                   modiff_conv_geom g, int n_levels, int per_sample, int slots,
+                   modiff_conv_geom g, TileGrid tg, int n_levels, int per_sample, int slots,
                    ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
   const int hw = g.h * g.w;
-  const int n = blockIdx.z;
-  const int c0 = blockIdx.y * kTileC;
-  const int p0 = blockIdx.x * kTileP;
   const int cg = threadIdx.x >> 4;
   const int pq = threadIdx.x & 15;
-  const int p = p0 + 4 * pq;
+  __shared__ float s0[kThreads / 32], s1[kThreads / 32];
+  __shared__ bool is_last;
 
   float m0 = 0.0f, m1 = 0.0f;
-  if (p < hw) {
+  int cur_n = -1;
+  // Each block walks a strided list of tiles and publishes one maximum per scale slot, so the
+  // number of same-address atomics is bounded by the grid size, not by the tensor size.
+  for (int tile = blockIdx.x; tile < tg.total; tile += gridDim.x) {
+    const int n = tile / (tg.pb * tg.cb);
+    const int rem = tile % (tg.pb * tg.cb);
+    const int c0 = (rem / tg.pb) * kTileC;
+    const int p = (rem % tg.pb) * kTileP + 4 * pq;
+    if (per_sample && n != cur_n) {
+      // flush the running maximum of the previous image
+      if (cur_n >= 0) {
+        float v = m0;
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if ((threadIdx.x & 31) == 0 && v > 0.0f)
+          atomicMax(&scratch->absmax_bits[cur_n], __float_as_uint(v));
+      }
+      m0 = 0.0f;
+      cur_n = n;
+    }
+    if (p < hw) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = c0 + 4 * cg + i;
-      if (c < g.cin) {
-        const size_t off = ((size_t)n * g.cin + c) * hw;
-        float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f};
-        load4<VEC4>(x + off, p, hw, xv);
-        if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
-        float m = 0.0f;
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + 4 * cg + i;
+        if (c < g.cin) {
+          const size_t off = ((size_t)n * g.cin + c) * hw;
+          float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f};
+          load4<VEC4>(x + off, p, hw, xv);
+          if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+          float m = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) m = fmaxf(m, fabsf(__fsub_rn(xv[j], av[j])));
-        if (g.split > 0 && c >= g.split) m1 = fmaxf(m1, m); else m0 = fmaxf(m0, m);
+          for (int j = 0; j < 4; ++j) m = fmaxf(m, fabsf(__fsub_rn(xv[j], av[j])));
+          if (g.split > 0 && c >= g.split) m1 = fmaxf(m1, m); else m0 = fmaxf(m0, m);
+        }
       }
     }
   }
@@ -90,8 +110,6 @@ modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
     m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
   }
-  __shared__ float s0[kThreads / 32], s1[kThreads / 32];
-  __shared__ bool is_last;
   if ((threadIdx.x & 31) == 0) {
     s0[threadIdx.x >> 5] = m0;
     s1[threadIdx.x >> 5] = m1;
@@ -103,13 +121,12 @@ modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
       m1 = fmaxf(m1, s1[i]);
     }
     // Non-negative floats order like their bit patterns.
-    const int slot0 = per_sample ? n : 0;
+    const int slot0 = per_sample ? (cur_n < 0 ? 0 : cur_n) : 0;
     if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
     if (g.split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
     __threadfence();
-    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
     const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
-    is_last = (ticket == total - 1);
+    is_last = (ticket == gridDim.x - 1);
   }
   __syncthreads();
   if (is_last) {
@@ -130,65 +147,157 @@ template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 modq_encode_kernel(const float* __restrict__ x, float* __restrict__ a_hat,
                    int8_t* __restrict__ codes, const float* __restrict__ x_scale,
-                   modiff_conv_geom g, Derived d, int n_levels, int per_sample) {
-  __shared__ uint32_t tile[kTileP][kTileC / 4 + 1];
+                   modiff_conv_geom g, Derived d, TileGrid tg, int n_levels, int per_sample) {
+  __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
   const int hw = g.h * g.w;
-  const int n = blockIdx.z;
-  const int c0 = blockIdx.y * kTileC;
-  const int p0 = blockIdx.x * kTileP;
   const int cg = threadIdx.x >> 4;
   const int pq = threadIdx.x & 15;
-  const int p = p0 + 4 * pq;
   const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
 
-  int q[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) q[i][j] = 0;
+  // Tiles are visited in the REVERSE of the absmax kernel's order: what that pass touched
+  // last is still in L2 and is consumed first.
+  for (int it = blockIdx.x; it < tg.total; it += gridDim.x) {
+    const int tile = tg.total - 1 - it;
+    const int n = tile / (tg.pb * tg.cb);
+    const int rem = tile % (tg.pb * tg.cb);
+    const int c0 = (rem / tg.pb) * kTileC;
+    const int p0 = (rem % tg.pb) * kTileP;
+    const int p = p0 + 4 * pq;
 
-  if (p < hw) {
+    int q[4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = c0 + 4 * cg + i;
-      if (c < g.cin) {
-        const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
-        const size_t off = ((size_t)n * g.cin + c) * hw;
-        float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
-        load4<VEC4>(x + off, p, hw, xv);
-        if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float r = __fsub_rn(xv[j], av[j]);
-          float qf = rintf(__fdiv_rn(r, delta));
-          qf = fminf(fmaxf(qf, lo), hi);
-          q[i][j] = (int)qf;
-          nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
+      for (int j = 0; j < 4; ++j) q[i][j] = 0;
+
+    if (p < hw) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + 4 * cg + i;
+        if (c < g.cin) {
+          const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
+          const size_t off = ((size_t)n * g.cin + c) * hw;
+          float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
+          load4<VEC4>(x + off, p, hw, xv);
+          if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float r = __fsub_rn(xv[j], av[j]);
+            float qf = rintf(__fdiv_rn(r, delta));
+            qf = fminf(fmaxf(qf, lo), hi);
+            q[i][j] = (int)qf;
+            nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
+          }
+          if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
         }
-        if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
       }
     }
-  }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t word = (uint32_t)(q[0][j] & 0xff) | ((uint32_t)(q[1][j] & 0xff) << 8) |
-                          ((uint32_t)(q[2][j] & 0xff) << 16) | ((uint32_t)(q[3][j] & 0xff) << 24);
-    tile[4 * pq + j][cg] = word;
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t word = (uint32_t)(q[0][j] & 0xff) | ((uint32_t)(q[1][j] & 0xff) << 8) |
+                            ((uint32_t)(q[2][j] & 0xff) << 16) | ((uint32_t)(q[3][j] & 0xff) << 24);
+      tile_sh[4 * pq + j][cg] = word;
+    }
+    __syncthreads();
+    // 4 threads per pixel, 16 bytes each.
+    const int px = threadIdx.x >> 2;
+    const int piece = threadIdx.x & 3;
+    const int pp = p0 + px;
+    const int cbase = c0 + 16 * piece;
+    if (pp < hw && cbase < d.cp) {
+      const int y = pp / g.w + g.pad_t;
+      const int xq = pp % g.w + g.pad_l;
+      const int plane = (y % g.stride) * g.stride + (xq % g.stride);
+      const size_t pix =
+          (((size_t)n * d.nplanes + plane) * d.hp + y / g.stride) * d.wp + xq / g.stride;
+      int4 v = make_int4(tile_sh[px][4 * piece], tile_sh[px][4 * piece + 1],
+                         tile_sh[px][4 * piece + 2], tile_sh[px][4 * piece + 3]);
+      *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+    }
+    __syncthreads();
+  }
+}
+
+// Linear layers (h = w = 1, cin a multiple of 16): activations [rows][cin] and codes
+// [rows][cin] share one flat index, so both passes are plain elementwise sweeps.
+__global__ void __launch_bounds__(kThreads)
+modq_flat_absmax_kernel(const float4* __restrict__ x, const float4* __restrict__ a_hat, int64_t n4,
+                        int cin, int split, int n_levels, int per_sample, int slots,
+                        ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
+  __shared__ float s0[kThreads / 32], s1[kThreads / 32];
+  __shared__ bool is_last;
+  float m0 = 0.0f, m1 = 0.0f;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 xv = __ldg(x + i);
+    float4 av = a_hat ? __ldg(a_hat + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = fmaxf(fmaxf(fabsf(__fsub_rn(xv.x, av.x)), fabsf(__fsub_rn(xv.y, av.y))),
+                    fmaxf(fabsf(__fsub_rn(xv.z, av.z)), fabsf(__fsub_rn(xv.w, av.w))));
+    const int c = (int)((i * 4) % cin);
+    if (per_sample) {
+      if (m > 0.0f) atomicMax(&scratch->absmax_bits[(i * 4) / cin], __float_as_uint(m));
+    } else if (split > 0 && c >= split) {
+      m1 = fmaxf(m1, m);
+    } else {
+      m0 = fmaxf(m0, m);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s0[threadIdx.x >> 5] = m0;
+    s1[threadIdx.x >> 5] = m1;
   }
   __syncthreads();
-  // 4 threads per pixel, 16 bytes each.
-  const int px = threadIdx.x >> 2;
-  const int piece = threadIdx.x & 3;
-  const int pp = p0 + px;
-  const int cbase = c0 + 16 * piece;
-  if (pp < hw && cbase < d.cp) {
-    const int y = pp / g.w + g.pad_t;
-    const int xq = pp % g.w + g.pad_l;
-    const int plane = (y % g.stride) * g.stride + (xq % g.stride);
-    const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + y / g.stride) * d.wp + xq / g.stride;
-    int4 v = make_int4(tile[px][4 * piece], tile[px][4 * piece + 1], tile[px][4 * piece + 2],
-                       tile[px][4 * piece + 3]);
-    *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kThreads / 32; ++i) {
+      m0 = fmaxf(m0, s0[i]);
+      m1 = fmaxf(m1, s1[i]);
+    }
+    if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[0], __float_as_uint(m0));
+    if (m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    for (int s = threadIdx.x; s < slots; s += blockDim.x) {
+      const unsigned int bits = atomicExch(&scratch->absmax_bits[s], 0u);
+      double delta = (double)__uint_as_float(bits) / (double)n_levels;
+      if (delta < 1e-8) delta = 1e-8;
+      x_scale[s] = (float)delta;
+    }
+    if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat,
+                        uint32_t* __restrict__ codes, const float* __restrict__ x_scale, int64_t n4,
+                        int cin, int split, int n_levels, int per_sample) {
+  const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const int c = (int)((i * 4) % cin);
+    const int slot = per_sample ? (int)((i * 4) / cin) : ((split > 0 && c >= split) ? 1 : 0);
+    const float delta = x_scale[slot];
+    float4 xv = __ldg(x + i);
+    float4 av = a_hat ? a_hat[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float xs[4] = {xv.x, xv.y, xv.z, xv.w}, as[4] = {av.x, av.y, av.z, av.w}, nv[4];
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float qf = rintf(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta));
+      qf = fminf(fmaxf(qf, lo), hi);
+      word |= (uint32_t)((int)qf & 0xff) << (8 * j);
+      nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
+    }
+    if (a_hat) a_hat[i] = make_float4(nv[0], nv[1], nv[2], nv[3]);
+    codes[i] = word;
   }
 }
 
@@ -201,24 +310,50 @@ int launch_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
   const int hw = g->h * g->w;
   const int n_levels = sym_levels(n_bits);
   const int slots = per_sample ? g->batch : d.nseg;
-  dim3 grid(ceil_div(hw, kTileP), ceil_div(g->cin, kTileC), g->batch);
-  const bool vec = (hw % 4 == 0) && (((uintptr_t)x & 15) == 0) &&
-                   (a_hat == nullptr || ((uintptr_t)a_hat & 15) == 0);
+  const bool aligned = (((uintptr_t)x & 15) == 0) && (a_hat == nullptr || ((uintptr_t)a_hat & 15) == 0);
+  constexpr int kMaxBlocks = 148 * 8;
+
+  if (hw == 1 && g->cin % 16 == 0 && aligned && g->split % 4 == 0 && g->stride == 1 &&
+      g->pad_t + g->pad_b + g->pad_l + g->pad_r == 0) {
+    const int64_t n4 = (int64_t)g->batch * g->cin / 4;
+    int blocks = (int)ceil_div64(n4, kThreads);
+    if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+    if (compute_scale) {
+      modq_flat_absmax_kernel<<<blocks, kThreads, 0, s>>>(
+          (const float4*)x, (const float4*)a_hat, n4, g->cin, g->split, n_levels, per_sample, slots,
+          (ModqScratch*)scratch, x_scale);
+      MODIFF_LAUNCH_CHECK("modq_flat_absmax_kernel");
+    }
+    modq_flat_encode_kernel<<<blocks, kThreads, 0, s>>>((const float4*)x, (float4*)a_hat,
+                                                        (uint32_t*)codes, x_scale, n4, g->cin,
+                                                        g->split, n_levels, per_sample);
+    MODIFF_LAUNCH_CHECK("modq_flat_encode_kernel");
+    return MODIFF_OK;
+  }
+
+  TileGrid tg;
+  tg.pb = ceil_div(hw, kTileP);
+  tg.cb = ceil_div(g->cin, kTileC);
+  const int64_t total = (int64_t)tg.pb * tg.cb * g->batch;
+  if (total >= (1ll << 31)) return set_error(MODIFF_ERR_INVALID, "activation tensor too large");
+  tg.total = (int)total;
+  const int blocks = tg.total < kMaxBlocks ? tg.total : kMaxBlocks;
+  const bool vec = (hw % 4 == 0) && aligned;
   if (compute_scale) {
     if (vec)
-      modq_absmax_kernel<true><<<grid, kThreads, 0, s>>>(x, a_hat, *g, n_levels, per_sample, slots,
-                                                         (ModqScratch*)scratch, x_scale);
+      modq_absmax_kernel<true><<<blocks, kThreads, 0, s>>>(x, a_hat, *g, tg, n_levels, per_sample,
+                                                           slots, (ModqScratch*)scratch, x_scale);
     else
-      modq_absmax_kernel<false><<<grid, kThreads, 0, s>>>(x, a_hat, *g, n_levels, per_sample, slots,
-                                                          (ModqScratch*)scratch, x_scale);
+      modq_absmax_kernel<false><<<blocks, kThreads, 0, s>>>(x, a_hat, *g, tg, n_levels, per_sample,
+                                                            slots, (ModqScratch*)scratch, x_scale);
     MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
   }
   if (vec)
-    modq_encode_kernel<true><<<grid, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, n_levels,
-                                                       per_sample);
+    modq_encode_kernel<true><<<blocks, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, tg,
+                                                         n_levels, per_sample);
   else
-    modq_encode_kernel<false><<<grid, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, n_levels,
-                                                        per_sample);
+    modq_encode_kernel<false><<<blocks, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, tg,
+                                                          n_levels, per_sample);
   MODIFF_LAUNCH_CHECK("modq_encode_kernel");
   return MODIFF_OK;
 }
@@ -235,7 +370,6 @@ extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x
   MODIFF_CHECK_ARG(x && codes && x_scale && scratch, "NULL pointer argument");
   MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
   MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
-  MODIFF_CHECK_ARG(g->batch <= 65535, "batch %d exceeds the grid limit 65535", g->batch);
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                      (cudaStream_t)stream);
@@ -247,7 +381,6 @@ extern "C" int modiff_quantize_static(const float* x, const float* delta, int8_t
   if (rc) return rc;
   MODIFF_CHECK_ARG(x && codes && delta, "NULL pointer argument");
   MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
-  MODIFF_CHECK_ARG(g->batch <= 65535, "batch %d exceeds the grid limit 65535", g->batch);
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, nullptr, codes, const_cast<float*>(delta), g, n_bits, 0, nullptr, false,
                      (cudaStream_t)stream);
