@@ -120,6 +120,29 @@ int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
                 const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                 void* stream);
 
+/* Same quantiser as modiff_modq for callers that cannot hand over scratch memory.
+ * This entry point has no counterpart in the reference; it exists for hosts that must not
+ * allocate once they are running - for example a serving process whose device memory is
+ * carved up at start-up and frozen, where a later cudaMalloc may fail against the fixed budget
+ * and stalls every stream of the device while it runs - and that own no spare buffer to pass
+ * as `scratch`.  The two reduction words and the per-image maxima live instead in an array
+ * compiled into the library (file-scope __device__, 64 + 4 * MODIFF_MODQ_STATIC_MAX_BATCH
+ * bytes, resident on every GPU that loads the library until the process exits).
+ *   - x, a_hat, codes, x_scale, g, n_bits, per_sample: exactly as for modiff_modq; inputs and
+ *     outputs are still the caller's.
+ *   - nothing is allocated or freed, here or in any routine it calls.
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress
+ *     with that device current) and caches it; make that first call before any stream capture.
+ *   - per_sample != 0 needs one slot per image: batch > MODIFF_MODQ_STATIC_MAX_BATCH is
+ *     rejected with MODIFF_ERR_INVALID (use modiff_modq with your own scratch instead).
+ *   - all calls on a device share the one array and it keeps the previous call's contents; the
+ *     part a call uses is cleared in stream order before its kernels run.  Calls that may
+ *     overlap on the GPU (different streams) race on it: serialise them.
+ */
+#define MODIFF_MODQ_STATIC_MAX_BATCH 4096
+int modiff_modq_static(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                       const modiff_conv_geom* g, int n_bits, int per_sample, void* stream);
+
 /* Int8 implicit-GEMM conv / linear with the modulation epilogue
  *   out = acc0 * (x_scale[0] * w_scale[0][c]) (+ acc1 * (x_scale[1] * w_scale[1][c]))
  *         (+ o_hat) (+ bias[c]);   acc = sum codes * (wcodes + w_corr)

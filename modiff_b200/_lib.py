@@ -51,6 +51,7 @@ SIGNATURES = {
     "modiff_wcodes_rows": (C.c_int32, [_G, C.c_int]),
     "modiff_weight_pack": (C.c_int, [_P, _G, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P]),
     "modiff_modq": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P, _P]),
+    "modiff_modq_static": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P]),
     "modiff_igemm_conv": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P, _G, C.c_int,
                                     C.c_int, _P, _P]),
     "modiff_conv_fp32": (C.c_int, [_P, _P, _P, _P, _G, _P]),
@@ -91,7 +92,7 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
     "modiff_ddim_step": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,

@@ -12,6 +12,8 @@
 // contraction, true division) so codes and the cache are bit-identical to PyTorch.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace modiff {
 
 namespace {
@@ -373,6 +375,61 @@ extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                      (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot allocate.
+//
+// The array below lives in every GPU that loads the library until the process exits.  Its
+// name is only a host-side handle: the device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and that address is what the kernels get.
+constexpr int kStaticSlots = MODIFF_MODQ_STATIC_MAX_BATCH;
+constexpr size_t kStaticScratchBytes = 64 + 4 * (size_t)kStaticSlots;
+static __device__ __align__(256) unsigned char g_modq_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the built-in scratch on the CURRENT device (looked up on first use).
+int static_scratch_address(void** out) {
+  int dev = 0;
+  MODIFF_CUDA(cudaGetDevice(&dev));
+  MODIFF_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "device index %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    MODIFF_CUDA(cudaGetSymbolAddress(&ptr, g_modq_static_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return MODIFF_OK;
+}
+}  // namespace
+
+extern "C" int modiff_modq_static(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                                  const modiff_conv_geom* g, int n_bits, int per_sample,
+                                  void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(x && codes && x_scale, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  const int slots = per_sample ? g->batch : 2;
+  MODIFF_CHECK_ARG(slots <= kStaticSlots,
+                   "per-sample batch %d needs more scratch than the built-in %d slots; use "
+                   "modiff_modq with caller-owned scratch",
+                   g->batch, kStaticSlots);
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  // The array keeps whatever the previous call left (an interrupted call may leave partial
+  // maxima), so the part this call uses is cleared first, in stream order.
+  MODIFF_CUDA(cudaMemsetAsync(scratch, 0, 64 + 4 * (size_t)slots, s));
+  return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
 }
 
 extern "C" int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
