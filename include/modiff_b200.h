@@ -120,6 +120,29 @@ int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
                 const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                 void* stream);
 
+/* Where a quantised layer's input comes from when it is not a materialised tensor: the channel
+ * concat [x0 | x1], plus an optional per-(image, channel) bias, optionally GroupNorm'ed with
+ * given statistics and passed through SiLU.  Lets the quantiser read the producer's output
+ * directly instead of a normalised copy (ddim/models/diffusion.py:121-128, 345-349). */
+typedef struct modiff_act_source {
+  const float* x0;        /* NCHW [batch][c0][h*w] */
+  const float* x1;        /* NCHW [batch][cin - c0][h*w], or NULL */
+  int32_t c0;             /* channels of x0 (== cin when x1 is NULL) */
+  int32_t groups;         /* GroupNorm groups (ignored without gn_stats) */
+  const float* chan_bias; /* [batch][cin] or NULL */
+  const float* gn_stats;  /* [batch][groups][2] mean, rstd (modiff_groupnorm_silu), or NULL */
+  const float* gamma;     /* [cin] */
+  const float* beta;      /* [cin] */
+  int32_t silu;           /* apply x * sigmoid(x) last */
+  int32_t reserved;
+} modiff_act_source;
+
+/* modiff_modq with the input described by a modiff_act_source (same arithmetic on the
+ * transformed value; qdiff/quant_layer.py:325-336). */
+int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, float* x_scale,
+                    const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                    void* stream);
+
 /* Same quantiser as modiff_modq for callers that cannot hand over scratch memory.
  * This entry point has no counterpart in the reference; it exists for hosts that must not
  * allocate once they are running - for example a serving process whose device memory is
@@ -181,13 +204,16 @@ int modiff_fake_quant(const float* x, float* y, int64_t slices, int64_t slice_le
                       int recompute, float* delta, float* zp, void* scratch, void* stream);
 
 /* GroupNorm (+ optional SiLU) over NCHW fp32: y = act(gn(x) * gamma + beta).
- * Replaces Normalize + nonlinearity (ddim/models/diffusion.py:27-33, 121-128,
- * 356-357).  x may be given as two channel-concatenated tensors (x0: c0 channels,
- * x1: c - c0 channels; x1 NULL when c0 == c), which fuses the torch.cat of the
- * up path (ddim/models/diffusion.py:345-349). */
-int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, float* y,
-                          const float* gamma, const float* beta, int batch, int c, int hw,
-                          int groups, float eps, int silu, void* stream);
+ * Replaces Normalize + nonlinearity (ddim/models/diffusion.py:27-33, 121-128, 356-357).
+ *   x = [x0 | x1] channel concat (x0: c0 channels, x1: c - c0 channels; x1 NULL when c0 == c),
+ *       which fuses the torch.cat of the up path (ddim/models/diffusion.py:345-349);
+ *   chan_bias fp32 [batch][c] or NULL: added to x first (the "+ temb_proj(...)[:, :, None, None]"
+ *       of ddim/models/diffusion.py:124);
+ *   y may be NULL and stats non-NULL to obtain only the statistics:
+ *   stats fp32 [batch][groups][2] = (mean, 1/sqrt(var + eps)) out, or NULL. */
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
+                          float* stats, const float* gamma, const float* beta, int batch, int c,
+                          int hw, int groups, float eps, int silu, void* stream);
 
 /* y = x * sigmoid(x)  (ddim/models/diffusion.py:27-29). */
 int modiff_silu(const float* x, float* y, int64_t n, void* stream);

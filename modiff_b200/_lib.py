@@ -35,6 +35,13 @@ class ConvGeom(C.Structure):
         return g
 
 
+class ActSourceStruct(C.Structure):
+    """Mirror of `modiff_act_source`."""
+    _fields_ = [("x0", C.c_void_p), ("x1", C.c_void_p), ("c0", C.c_int32), ("groups", C.c_int32),
+                ("chan_bias", C.c_void_p), ("gn_stats", C.c_void_p), ("gamma", C.c_void_p),
+                ("beta", C.c_void_p), ("silu", C.c_int32), ("reserved", C.c_int32)]
+
+
 _P = C.c_void_p
 _G = C.POINTER(ConvGeom)
 
@@ -51,14 +58,16 @@ SIGNATURES = {
     "modiff_wcodes_rows": (C.c_int32, [_G, C.c_int]),
     "modiff_weight_pack": (C.c_int, [_P, _G, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P]),
     "modiff_modq": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P, _P]),
+    "modiff_modq_src": (C.c_int, [C.POINTER(ActSourceStruct), _P, _P, _P, _G, C.c_int, C.c_int, _P,
+                                  _P]),
     "modiff_modq_static": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P]),
     "modiff_igemm_conv": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P, _G, C.c_int,
                                     C.c_int, _P, _P]),
     "modiff_conv_fp32": (C.c_int, [_P, _P, _P, _P, _G, _P]),
     "modiff_fake_quant": (C.c_int, [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int,
                                     C.c_int, C.c_int, _P, _P, _P, _P]),
-    "modiff_groupnorm_silu": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int,
-                                        C.c_int, C.c_float, C.c_int, _P]),
+    "modiff_groupnorm_silu": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, _P, C.c_int, C.c_int,
+                                        C.c_int, C.c_int, C.c_float, C.c_int, _P]),
     "modiff_silu": (C.c_int, [_P, _P, C.c_int64, _P]),
     "modiff_add": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_upsample2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
@@ -92,7 +101,7 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
     "modiff_ddim_step": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,

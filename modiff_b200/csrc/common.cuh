@@ -66,6 +66,18 @@ __host__ __device__ inline Derived derive(const modiff_conv_geom& g) {
 
 int validate_geom(const modiff_conv_geom* g);
 
+#ifdef __CUDACC__
+// x * sigmoid(x), shared by every kernel that applies the UNet's nonlinearity, so that a value
+// is the same wherever it is (re)computed.  Hardware exp2 / reciprocal: about 2 ulp, a few
+// instructions (the quantiser kernels evaluate it twice per element and are otherwise
+// memory-bound).
+__device__ inline float silu_f(float y) { return __fdividef(y, 1.0f + __expf(-y)); }
+// GroupNorm affine step, one fused multiply-add everywhere it is evaluated.
+__device__ inline float gn_apply(float v, float mean, float ga, float be) {
+  return fmaf(v - mean, ga, be);
+}
+#endif
+
 // Symmetric activation code range of an n-bit quantiser
 // (n_levels = 2^(b-1) - 1; clamp(-n_levels - 1, n_levels)).
 __host__ __device__ inline int sym_levels(int n_bits) { return (1 << (n_bits - 1)) - 1; }

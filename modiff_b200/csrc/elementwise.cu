@@ -9,8 +9,6 @@ namespace modiff {
 
 namespace {
 
-__device__ inline float silu_f(float y) { return y * (1.0f / (1.0f + expf(-y))); }
-
 __device__ inline float block_sum(float v, float* sh) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -23,11 +21,13 @@ __device__ inline float block_sum(float v, float* sh) {
   return t;  // every thread holds the total
 }
 
-// One block per (image, group).  Three sweeps over the group's elements (mean, centred
-// variance, normalise); sweeps 2 and 3 hit L1/L2.
+// One block per (image, group).  Sweeps over the group's elements: mean, centred variance and
+// (unless only the statistics are wanted) normalise; sweeps 2 and 3 hit L1/L2.
+// Input = channel concat [x0 | x1] plus an optional per-(image, channel) bias.
 __global__ void __launch_bounds__(512)
 groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1, int c0,
-                      float* __restrict__ y, const float* __restrict__ gamma,
+                      const float* __restrict__ chan_bias, float* __restrict__ y,
+                      float* __restrict__ stats, const float* __restrict__ gamma,
                       const float* __restrict__ beta, int c, int hw, int groups, float eps,
                       int silu) {
   __shared__ float sh[32];
@@ -42,37 +42,40 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
   auto src = [&](int ch) -> const float* {
     return (ch < c0) ? x0 + ((size_t)n * c0 + ch) * hw : x1 + ((size_t)n * c1 + (ch - c0)) * hw;
   };
+  auto bias_of = [&](int ch) -> float { return chan_bias ? chan_bias[(size_t)n * c + ch] : 0.0f; };
 
-  float s = 0.0f;
+  // One sweep: sums of (v - shift) and (v - shift)^2 with shift = the group's first element,
+  // which keeps the variance free of cancellation when the mean is far from zero.
+  const float shift = __fadd_rn(__ldg(src(cbeg)), bias_of(cbeg));
+  float s = 0.0f, q = 0.0f;
   if (vec) {
     const int hw4 = hw >> 2;
     for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
       const int ch = cbeg + i / hw4;
       float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
-      s += (v.x + v.y) + (v.z + v.w);
-    }
-  } else {
-    for (int i = threadIdx.x; i < count; i += blockDim.x) s += __ldg(src(cbeg + i / hw) + i % hw);
-  }
-  const float mean = block_sum(s, sh) / (float)count;
-
-  float q = 0.0f;
-  if (vec) {
-    const int hw4 = hw >> 2;
-    for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
-      const int ch = cbeg + i / hw4;
-      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
-      const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, dd = v.w - mean;
-      q += (a * a + b * b) + (cc * cc + dd * dd);
+      const float b = bias_of(ch);
+      const float a = __fadd_rn(v.x, b) - shift, bb = __fadd_rn(v.y, b) - shift,
+                  cc = __fadd_rn(v.z, b) - shift, dd = __fadd_rn(v.w, b) - shift;
+      s += (a + bb) + (cc + dd);
+      q += (a * a + bb * bb) + (cc * cc + dd * dd);
     }
   } else {
     for (int i = threadIdx.x; i < count; i += blockDim.x) {
-      const float a = __ldg(src(cbeg + i / hw) + i % hw) - mean;
+      const int ch = cbeg + i / hw;
+      const float a = __fadd_rn(__ldg(src(ch) + i % hw), bias_of(ch)) - shift;
+      s += a;
       q += a * a;
     }
   }
-  const float var = block_sum(q, sh) / (float)count;
+  const float ms = block_sum(s, sh) / (float)count;          // mean - shift
+  const float mean = shift + ms;
+  const float var = fmaxf(block_sum(q, sh) / (float)count - ms * ms, 0.0f);
   const float rstd = 1.0f / sqrtf(var + eps);
+  if (stats && threadIdx.x == 0) {
+    stats[2 * blockIdx.x] = mean;
+    stats[2 * blockIdx.x + 1] = rstd;
+  }
+  if (!y) return;
 
   float* yn = y + (size_t)n * c * hw;
   if (vec) {
@@ -80,19 +83,21 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
     for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
       const int ch = cbeg + i / hw4;
       float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
+      const float b = bias_of(ch);
       const float ga = gamma[ch] * rstd, be = beta[ch];
       float4 o;
-      o.x = (v.x - mean) * ga + be;
-      o.y = (v.y - mean) * ga + be;
-      o.z = (v.z - mean) * ga + be;
-      o.w = (v.w - mean) * ga + be;
+      o.x = gn_apply(__fadd_rn(v.x, b), mean, ga, be);
+      o.y = gn_apply(__fadd_rn(v.y, b), mean, ga, be);
+      o.z = gn_apply(__fadd_rn(v.z, b), mean, ga, be);
+      o.w = gn_apply(__fadd_rn(v.w, b), mean, ga, be);
       if (silu) { o.x = silu_f(o.x); o.y = silu_f(o.y); o.z = silu_f(o.z); o.w = silu_f(o.w); }
       reinterpret_cast<float4*>(yn + (size_t)ch * hw)[i % hw4] = o;
     }
   } else {
     for (int i = threadIdx.x; i < count; i += blockDim.x) {
       const int ch = cbeg + i / hw;
-      float o = (__ldg(src(ch) + i % hw) - mean) * (gamma[ch] * rstd) + beta[ch];
+      float o = gn_apply(__fadd_rn(__ldg(src(ch) + i % hw), bias_of(ch)), mean, gamma[ch] * rstd,
+                         beta[ch]);
       if (silu) o = silu_f(o);
       yn[(size_t)ch * hw + i % hw] = o;
     }
@@ -224,10 +229,11 @@ using namespace modiff;
 
 extern "C" {
 
-int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, float* y, const float* gamma,
-                          const float* beta, int batch, int c, int hw, int groups, float eps,
-                          int silu, void* stream) {
-  MODIFF_CHECK_ARG(x0 && y && gamma && beta, "NULL pointer argument");
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
+                          float* stats, const float* gamma, const float* beta, int batch, int c,
+                          int hw, int groups, float eps, int silu, void* stream) {
+  MODIFF_CHECK_ARG(x0 && (y || stats), "NULL pointer argument");
+  MODIFF_CHECK_ARG(!y || (gamma && beta), "gamma / beta are NULL");
   MODIFF_CHECK_ARG(batch > 0 && c > 0 && hw > 0 && groups > 0 && c % groups == 0,
                    "bad GroupNorm shape: c=%d groups=%d", c, groups);
   MODIFF_CHECK_ARG(c0 > 0 && c0 <= c && (c0 == c || x1 != nullptr), "bad concat split c0=%d", c0);
@@ -236,7 +242,7 @@ int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, float* y, co
   const int count = (c / groups) * hw;
   const int threads = count >= 4096 ? 512 : (count >= 1024 ? 256 : 128);
   groupnorm_silu_kernel<<<batch * groups, threads, 0, (cudaStream_t)stream>>>(
-      x0, x1, c0, y, gamma, beta, c, hw, groups, eps, silu);
+      x0, x1, c0, chan_bias, y, stats, gamma, beta, c, hw, groups, eps, silu);
   MODIFF_LAUNCH_CHECK("groupnorm_silu_kernel");
   return MODIFF_OK;
 }

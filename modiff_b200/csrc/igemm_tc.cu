@@ -28,7 +28,10 @@ constexpr int kTileM = 128;
 constexpr int kChunkK = 128;          // bytes of K per pipeline stage (one swizzle atom row)
 constexpr int kATileBytes = kTileM * kChunkK;
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpiWarps;   // TMA warp, MMA warp, epilogue warps
+constexpr int kOSlots = 3;                // ring of cached-output half tiles (64 channels each)
+constexpr int kOHalfBytes = 64 * 128 * 4;
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // TMA warp, MMA warp, epilogue warps, store warp
+constexpr int kStoreWarp = 2 + kEpiWarps;
 constexpr int kMaxStages = 6;
 constexpr uint32_t kSpinLimit = 1u << 28;
 
@@ -220,13 +223,14 @@ template <int NSEG, bool WITH_SUM, bool TMA_EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_o, const TcParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
-  __shared__ __align__(8) uint64_t bar_o_full;
-  __shared__ __align__(8) uint64_t bar_o_empty;
+  __shared__ __align__(8) uint64_t bar_o_full[kOSlots];
+  __shared__ __align__(8) uint64_t bar_o_empty[kOSlots];
+  __shared__ __align__(8) uint64_t bar_o_ready[kOSlots];
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ float ep_scale[2][128];
@@ -237,13 +241,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &abort_sh;
 
-  // 1024-byte aligned tile ring, followed by the cached-output tile
+  // 1024-byte aligned tile ring (the dynamic segment is declared with that alignment),
+  // followed by the cached-output ring
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t ring = (raw + 1023u) & ~1023u;
+  const uint32_t ring = raw;
   const int b_rows = p.umma_n;
   const uint32_t b_tile_bytes = (uint32_t)b_rows * kChunkK;
   const uint32_t stage_bytes = kATileBytes + ((b_tile_bytes + 1023u) & ~1023u);
-  const uint32_t obuf = ring + (uint32_t)p.stages * stage_bytes;
+  const uint32_t obuf = ring + (uint32_t)p.stages * stage_bytes;   // kOSlots x 32 KB
   float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
 
   if (threadIdx.x == 0) {
@@ -256,8 +261,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[b]), kEpiWarps);
     }
-    mbar_init(smem_u32(&bar_o_full), 1);
-    mbar_init(smem_u32(&bar_o_empty), 1);
+    for (int b = 0; b < kOSlots; ++b) {
+      mbar_init(smem_u32(&bar_o_full[b]), 1);
+      mbar_init(smem_u32(&bar_o_empty[b]), 1);
+      mbar_init(smem_u32(&bar_o_ready[b]), kEpiWarps);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -282,6 +290,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       uint32_t ophase = 0;
+      int oslot = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const TileCoord t = decode_tile(tile, p);
@@ -305,15 +314,22 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
           }
         }
-        if (TMA_EPI && ok && p.accumulate) {
-          // After this tile's operand copies are queued: fetch its cached-output tile as soon
-          // as the epilogue of the previous tile has drained the buffer.
-          ok = mbar_wait(smem_u32(&bar_o_empty), ophase ^ 1u, abort_flag);
-          if (!ok) break;
-          const uint32_t ofull = smem_u32(&bar_o_full);
-          mbar_arrive_expect_tx(ofull, (uint32_t)p.o_bytes);
-          tma_load_3d(obuf, &map_o, ofull, t.th * p.bh * p.d.wo, t.nt * 128, t.tn * p.bn);
-          ophase ^= 1u;
+        if (TMA_EPI && ok) {
+          // After this tile's operand copies are queued: claim two slots of the cached-output
+          // ring (as soon as earlier stores have drained them) and fetch both 64-channel halves.
+          for (int half = 0; half < 2 && ok; ++half) {
+            ok = mbar_wait(smem_u32(&bar_o_empty[oslot]), ophase ^ 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t ofull = smem_u32(&bar_o_full[oslot]);
+            if (p.accumulate) {
+              mbar_arrive_expect_tx(ofull, (uint32_t)p.o_bytes);
+              tma_load_3d(obuf + oslot * kOHalfBytes, &map_o, ofull, t.th * p.bh * p.d.wo,
+                          t.nt * 128 + half * 64, t.tn * p.bn);
+            } else {
+              mbar_arrive(ofull);
+            }
+            if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+          }
         }
       }
     }
@@ -354,6 +370,29 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
       }
     }
+  } else if (warp == kStoreWarp) {
+    // ------------------------------------------------------------ cached-output store warp
+    // Writes each finished half tile back with one bulk tensor store and hands the ring slot
+    // to the producer as soon as the store has read shared memory.
+    if (TMA_EPI && lane == 0) {
+      int oslot = 0;
+      uint32_t ophase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const TileCoord t = decode_tile(tile, p);
+        for (int hh = 0; hh < 2; ++hh) {
+          ok = mbar_wait(smem_u32(&bar_o_ready[oslot]), ophase, abort_flag);
+          if (!ok) break;
+          tma_store_3d(&map_o, obuf + oslot * kOHalfBytes, t.th * p.bh * p.d.wo,
+                       t.nt * 128 + hh * 64, t.tn * p.bn);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          mbar_arrive(smem_u32(&bar_o_empty[oslot]));
+          if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     // Two warps share each tensor-memory lane quarter; each takes 64 of the 128 columns.
@@ -371,6 +410,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int buf = 0;
     uint32_t bphase = 0;
     uint32_t ophase = 0;
+    int oslot = 0;
     int last_nt = -1;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
@@ -405,48 +445,43 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
 
       if (TMA_EPI) {
-        if (p.accumulate) {
-          ok = mbar_wait(smem_u32(&bar_o_full), ophase, abort_flag);
+        // Each half tile (64 channels) sits in one ring slot as [image][channel][pixel]; lanes
+        // walk consecutive pixels.  The two warps of a lane quarter take 32 channels each.
+        const int sub = (warp - 2) >> 2;          // 0 / 1: which 32 channels of the half
+        for (int hh = 0; hh < 2; ++hh) {
+          ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
-        }
-        // shared-memory tile: [image][channel][pixel]; lanes walk consecutive pixels
-        float* orow = obuf_ptr + (size_t)ni * 128 * tile_px + pl;
-#pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
+          float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)ni * 64 * tile_px +
+                        (size_t)(sub * 32) * tile_px + pl;
+          const int colbase = hh * 64 + sub * 32;
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = p.accumulate ? orow[(col0 + c2 * 32 + j) * tile_px] : 0.0f;
+          for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * tile_px] : 0.0f;
 #pragma unroll
           for (int seg = 0; seg < NSEG; ++seg) {
             int a[32];
-            tc_ld32(t_row + seg * p.umma_n + col0 + c2 * 32, a);
+            tc_ld32(t_row + seg * p.umma_n + colbase, a);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int cl = col0 + c2 * 32 + j;
               int iv = a[j];
-              if (WITH_SUM) iv += ep_corr[seg][cl] * rsum[seg];
-              v[j] = fmaf((float)iv, ep_scale[seg][cl], v[j]);
+              if (WITH_SUM) iv += ep_corr[seg][colbase + j] * rsum[seg];
+              v[j] = fmaf((float)iv, ep_scale[seg][colbase + j], v[j]);
             }
           }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) orow[(col0 + c2 * 32 + j) * tile_px] = v[j];
+          for (int j = 0; j < 32; ++j) orow[j * tile_px] = v[j];
+          if (hh == 1) tc_fence_before();
+          // make the tile visible to the bulk-copy engine, then tell the store warp
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&bar_o_ready[oslot]));
+            if (hh == 1) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));   // accumulators consumed
+          }
+          if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
         }
-        // accumulators consumed: release the tensor-memory buffer, then publish the tile
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-        if (ep_tid == 0) {
-          tma_store_3d(&map_o, obuf, t.th * p.bh * p.d.wo, t.nt * 128, t.tn * p.bn);
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          mbar_arrive(smem_u32(&bar_o_empty));
-        }
-        if (!p.accumulate) asm volatile("bar.sync 2, 256;" ::: "memory");  // buffer reuse
-        ophase ^= 1u;
+        if (!ok) break;
       } else {
         const int n = t.tn * p.bn + ni;
         const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
@@ -491,7 +526,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
     }
-    if (TMA_EPI && ep_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // ---------------------------------------------------------------- teardown
@@ -599,10 +633,10 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
                        (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0);
   const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
   const uint32_t stage_bytes = kATileBytes + b_tile;
-  const uint32_t o_tile = tma_epi ? 128u * 128u * 4u : 0u;
-  p.stages = (int)((204u * 1024u - o_tile) / stage_bytes);
+  const uint32_t o_ring = tma_epi ? (uint32_t)kOSlots * kOHalfBytes : 0u;
+  p.stages = (int)((224u * 1024u - o_ring) / stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
-  const size_t smem = (size_t)p.stages * stage_bytes + o_tile + 1024;
+  const size_t smem = (size_t)p.stages * stage_bytes + o_ring;
 
   // Activation codes: [batch][planes][hp][wp][cp] int8, innermost first.
   CUtensorMap map_a, map_b;
@@ -646,7 +680,7 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
     const int c_box = g->cout < 128 ? g->cout : 128;
     cuuint64_t dims[3] = {(cuuint64_t)(d.ho * d.wo), (cuuint64_t)g->cout, (cuuint64_t)g->batch};
     cuuint64_t strides[2] = {(cuuint64_t)d.ho * d.wo * 4, (cuuint64_t)g->cout * d.ho * d.wo * 4};
-    cuuint32_t box[3] = {(cuuint32_t)tile_px, (cuuint32_t)c_box, (cuuint32_t)bn_box};
+    cuuint32_t box[3] = {(cuuint32_t)tile_px, 64u, (cuuint32_t)bn_box};
     cuuint32_t estr[3] = {1, 1, 1};
     // the shared-memory tile is addressed as [image][128][tile_px]: boxes narrower than 128
     // channels would change that pitch, so they use the generic epilogue instead
@@ -656,7 +690,7 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS)
         return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output) failed: %d", (int)r);
-      p.o_bytes = tile_px * 128 * bn_box * 4;
+      p.o_bytes = tile_px * 64 * bn_box * 4;
     }
   }
   const bool use_tma_epi = tma_epi && p.o_bytes > 0;
@@ -671,11 +705,11 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   const int variant = (p.nseg == 2 ? 4 : 0) | (p.with_sum ? 2 : 0) | (use_tma_epi ? 1 : 0);
 #define MODIFF_TC_LAUNCH(NSEG, SUM, EPI)                                                       \
   {                                                                                            \
-    static bool attr_set = false;                                                              \
-    if (!attr_set) {                                                                           \
+    static size_t attr_bytes = 0;                                                              \
+    if (smem > attr_bytes) {                                                                   \
       MODIFF_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<NSEG, SUM, EPI>,                        \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
-      attr_set = true;                                                                         \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      attr_bytes = smem;                                                                       \
     }                                                                                          \
     igemm_tc_kernel<NSEG, SUM, EPI><<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);      \
   }

@@ -50,6 +50,46 @@ __device__ inline void store4(float* __restrict__ base, int p, int hw, const flo
   }
 }
 
+// Device-side view of a modiff_act_source.
+struct SrcView {
+  const float* x0;
+  const float* x1;
+  const float* bias;
+  const float* stats;
+  const float* gamma;
+  const float* beta;
+  int c0, c1, groups, cpg, silu;
+};
+
+// Four consecutive pixels of channel c of image n, after the source transform.
+template <bool VEC4, bool XFORM>
+__device__ inline void load_src(const SrcView& s, int n, int c, int cin, int p, int hw,
+                                float (&v)[4]) {
+  if (!XFORM) {
+    load4<VEC4>(s.x0 + ((size_t)n * cin + c) * hw, p, hw, v);
+    return;
+  }
+  const float* base = (c < s.c0) ? s.x0 + ((size_t)n * s.c0 + c) * hw
+                                 : s.x1 + ((size_t)n * s.c1 + (c - s.c0)) * hw;
+  load4<VEC4>(base, p, hw, v);
+  if (s.bias) {
+    const float b = __ldg(s.bias + (size_t)n * cin + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], b);
+  }
+  if (s.stats) {
+    const float* st = s.stats + 2 * ((size_t)n * s.groups + c / s.cpg);
+    const float mean = __ldg(st), rstd = __ldg(st + 1);
+    const float ga = __ldg(s.gamma + c) * rstd, be = __ldg(s.beta + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = gn_apply(v[j], mean, ga, be);
+  }
+  if (s.silu) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = silu_f(v[j]);
+  }
+}
+
 // slot of channel c of image n: per-sample -> n; split -> segment; else 0
 __device__ inline int slot_of(int n, int c, int split, int per_sample) {
   if (per_sample) return n;
@@ -60,9 +100,9 @@ struct TileGrid {
   int pb, cb, total;   // pixel blocks, channel blocks, pb * cb * batch
 };
 
-template <bool VEC4>
+template <bool VEC4, bool XFORM>
 __global__ void __launch_bounds__(kThreads)
-modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
+modq_absmax_kernel(const SrcView src, const float* __restrict__ a_hat,
                    modiff_conv_geom g, TileGrid tg, int n_levels, int per_sample, int slots,
                    ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
   const int hw = g.h * g.w;
@@ -98,7 +138,7 @@ modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
         if (c < g.cin) {
           const size_t off = ((size_t)n * g.cin + c) * hw;
           float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f};
-          load4<VEC4>(x + off, p, hw, xv);
+          load_src<VEC4, XFORM>(src, n, c, g.cin, p, hw, xv);
           if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
           float m = 0.0f;
 #pragma unroll
@@ -145,9 +185,9 @@ modq_absmax_kernel(const float* __restrict__ x, const float* __restrict__ a_hat,
   }
 }
 
-template <bool VEC4>
+template <bool VEC4, bool XFORM>
 __global__ void __launch_bounds__(kThreads)
-modq_encode_kernel(const float* __restrict__ x, float* __restrict__ a_hat,
+modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
                    int8_t* __restrict__ codes, const float* __restrict__ x_scale,
                    modiff_conv_geom g, Derived d, TileGrid tg, int n_levels, int per_sample) {
   __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
@@ -180,7 +220,7 @@ modq_encode_kernel(const float* __restrict__ x, float* __restrict__ a_hat,
           const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
           const size_t off = ((size_t)n * g.cin + c) * hw;
           float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
-          load4<VEC4>(x + off, p, hw, xv);
+          load_src<VEC4, XFORM>(src, n, c, g.cin, p, hw, xv);
           if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -305,17 +345,19 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
 
 }  // namespace
 
-int launch_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
-                const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
-                bool compute_scale, cudaStream_t s) {
+int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes, float* x_scale,
+                    const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                    bool compute_scale, cudaStream_t s) {
   Derived d = derive(*g);
   const int hw = g->h * g->w;
   const int n_levels = sym_levels(n_bits);
   const int slots = per_sample ? g->batch : d.nseg;
-  const bool aligned = (((uintptr_t)x & 15) == 0) && (a_hat == nullptr || ((uintptr_t)a_hat & 15) == 0);
+  const float* x = src.x0;
+  const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)src.x1 & 15) == 0) &&
+                       (a_hat == nullptr || ((uintptr_t)a_hat & 15) == 0);
   constexpr int kMaxBlocks = 148 * 8;
 
-  if (hw == 1 && g->cin % 16 == 0 && aligned && g->split % 4 == 0 && g->stride == 1 &&
+  if (!xform && hw == 1 && g->cin % 16 == 0 && aligned && g->split % 4 == 0 && g->stride == 1 &&
       g->pad_t + g->pad_b + g->pad_l + g->pad_r == 0) {
     const int64_t n4 = (int64_t)g->batch * g->cin / 4;
     int blocks = (int)ceil_div64(n4, kThreads);
@@ -341,23 +383,33 @@ int launch_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
   tg.total = (int)total;
   const int blocks = tg.total < kMaxBlocks ? tg.total : kMaxBlocks;
   const bool vec = (hw % 4 == 0) && aligned;
-  if (compute_scale) {
-    if (vec)
-      modq_absmax_kernel<true><<<blocks, kThreads, 0, s>>>(x, a_hat, *g, tg, n_levels, per_sample,
-                                                           slots, (ModqScratch*)scratch, x_scale);
-    else
-      modq_absmax_kernel<false><<<blocks, kThreads, 0, s>>>(x, a_hat, *g, tg, n_levels, per_sample,
-                                                            slots, (ModqScratch*)scratch, x_scale);
-    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+#define MODIFF_MODQ_LAUNCH(V, X)                                                                   \
+  {                                                                                              \
+    if (compute_scale) {                                                                         \
+      modq_absmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_levels, per_sample, \
+                                                          slots, (ModqScratch*)scratch, x_scale); \
+      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");                                                 \
+    }                                                                                            \
+    modq_encode_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, codes, x_scale, *g, d, tg,    \
+                                                        n_levels, per_sample);                   \
+    MODIFF_LAUNCH_CHECK("modq_encode_kernel");                                                   \
   }
-  if (vec)
-    modq_encode_kernel<true><<<blocks, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, tg,
-                                                         n_levels, per_sample);
-  else
-    modq_encode_kernel<false><<<blocks, kThreads, 0, s>>>(x, a_hat, codes, x_scale, *g, d, tg,
-                                                          n_levels, per_sample);
-  MODIFF_LAUNCH_CHECK("modq_encode_kernel");
+  if (vec && xform) MODIFF_MODQ_LAUNCH(true, true)
+  else if (vec) MODIFF_MODQ_LAUNCH(true, false)
+  else if (xform) MODIFF_MODQ_LAUNCH(false, true)
+  else MODIFF_MODQ_LAUNCH(false, false)
+#undef MODIFF_MODQ_LAUNCH
   return MODIFF_OK;
+}
+
+int launch_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                bool compute_scale, cudaStream_t s) {
+  SrcView v = {};
+  v.x0 = x;
+  v.c0 = g->cin;
+  return launch_modq_src(v, false, a_hat, codes, x_scale, g, n_bits, per_sample, scratch,
+                         compute_scale, s);
 }
 
 }  // namespace modiff
@@ -375,6 +427,38 @@ extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                      (cudaStream_t)stream);
+}
+
+extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes,
+                               float* x_scale, const modiff_conv_geom* g, int n_bits, int per_sample,
+                               void* scratch, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  if (src->gn_stats) {
+    MODIFF_CHECK_ARG(src->groups > 0 && g->cin % src->groups == 0 && src->gamma && src->beta,
+                     "bad GroupNorm description (groups=%d)", src->groups);
+  }
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.bias = src->chan_bias;
+  v.stats = src->gn_stats;
+  v.gamma = src->gamma;
+  v.beta = src->beta;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.groups = src->gn_stats ? src->groups : 1;
+  v.cpg = g->cin / v.groups;
+  v.silu = src->silu;
+  const bool xform = src->x1 || src->chan_bias || src->gn_stats || src->silu;
+  return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
+                         (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------

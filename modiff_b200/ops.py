@@ -17,12 +17,10 @@ def _req(*ts):
             _lib.require_cuda(t)
 
 
-def groupnorm(x, norm, silu=False, x1=None):
-    """GroupNorm (+SiLU) of `x`, or of the channel concat [x, x1] without materialising it.
-
-    `norm` is a torch.nn.GroupNorm holding gamma / beta / groups / eps.
-    """
-    _req(x, x1)
+def groupnorm(x, norm, silu=False, x1=None, chan_bias=None):
+    """GroupNorm (+SiLU) of `x` (+ a per-(image, channel) bias), or of the channel concat
+    [x, x1] without materialising it.  `norm` is a torch.nn.GroupNorm."""
+    _req(x, x1, chan_bias)
     x = x.contiguous()
     b, c0 = x.shape[0], x.shape[1]
     hw = x.numel() // (b * c0)
@@ -32,11 +30,95 @@ def groupnorm(x, norm, silu=False, x1=None):
         c = c0 + x1.shape[1]
     if c != norm.num_channels:
         raise ModiffError(f"GroupNorm expects {norm.num_channels} channels, got {c}")
+    if chan_bias is not None:
+        chan_bias = chan_bias.contiguous()
     y = torch.empty((b, c) + tuple(x.shape[2:]), dtype=torch.float32, device=x.device)
-    _lib.call('modiff_groupnorm_silu', 
-        x.data_ptr(), _lib.ptr(x1), c0, y.data_ptr(), norm.weight.data_ptr(), norm.bias.data_ptr(),
-        b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr())
+    _lib.call('modiff_groupnorm_silu', x.data_ptr(), _lib.ptr(x1), c0, _lib.ptr(chan_bias),
+              y.data_ptr(), None, norm.weight.data_ptr(), norm.bias.data_ptr(),
+              b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr())
     return y
+
+
+class ActSource:
+    """A quantised layer's input that has not been materialised: the channel concat
+    [x0 | x1], plus an optional [B, C] bias, optionally GroupNorm'ed (`norm`) and SiLU'ed.
+
+    A modulated `QuantModule` reads such a source directly in its quantiser kernels (the
+    normalised tensor is never written); everything else calls `materialize()`.
+    """
+
+    def __init__(self, x0, x1=None, chan_bias=None, norm=None, silu=False):
+        _req(x0, x1, chan_bias)
+        self.x0 = x0.contiguous()
+        self.x1 = None if x1 is None else x1.contiguous()
+        self.chan_bias = None if chan_bias is None else chan_bias.contiguous()
+        self.norm = norm
+        self.silu = bool(silu)
+        c = self.x0.shape[1] + (0 if self.x1 is None else self.x1.shape[1])
+        self.shape = torch.Size((self.x0.shape[0], c) + tuple(self.x0.shape[2:]))
+        self.device = self.x0.device
+        self.dtype = self.x0.dtype
+        self.is_cuda = True
+        self._stats = None
+        self._tensor = None
+        self._struct = None
+
+    def dim(self):
+        return len(self.shape)
+
+    def size(self, d):
+        return self.shape[d]
+
+    def numel(self):
+        return self.shape.numel()
+
+    def contiguous(self):
+        return self
+
+    @property
+    def trivial(self):
+        return self.x1 is None and self.chan_bias is None and self.norm is None and not self.silu
+
+    def stats(self):
+        """[B, groups, 2] (mean, rstd) of the GroupNorm over this source, computed once."""
+        if self._stats is None and self.norm is not None:
+            b, c = self.shape[0], self.shape[1]
+            hw = self.numel() // (b * c)
+            self._stats = torch.empty((b, self.norm.num_groups, 2), dtype=torch.float32,
+                                      device=self.device)
+            _lib.call('modiff_groupnorm_silu', self.x0.data_ptr(), _lib.ptr(self.x1),
+                      self.x0.shape[1], _lib.ptr(self.chan_bias), None, self._stats.data_ptr(),
+                      None, None, b, c, hw, self.norm.num_groups, float(self.norm.eps), 0,
+                      _lib.stream_ptr())
+        return self._stats
+
+    def materialize(self):
+        """The transformed tensor, computed once with the stand-alone kernels."""
+        if self._tensor is None:
+            if self.norm is not None:
+                self._tensor = groupnorm(self.x0, self.norm, self.silu, self.x1, self.chan_bias)
+            else:
+                t = self.x0 if self.x1 is None else concat_channels(self.x0, self.x1)
+                if self.chan_bias is not None:
+                    t = add_channel_bias(t, self.chan_bias)
+                if self.silu:
+                    t = silu(t)
+                self._tensor = t
+        return self._tensor
+
+    def struct(self):
+        """ctypes mirror of modiff_act_source (keeps this object's tensors alive)."""
+        if self._struct is None:
+            st = self.stats()
+            n = self.norm
+            if n is not None and self.shape[1] != n.num_channels:
+                raise ModiffError(f"GroupNorm expects {n.num_channels} channels, got {self.shape[1]}")
+            self._struct = _lib.ActSourceStruct(
+                self.x0.data_ptr(), _lib.ptr(self.x1), self.x0.shape[1],
+                n.num_groups if n is not None else 1, _lib.ptr(self.chan_bias), _lib.ptr(st),
+                n.weight.data_ptr() if n is not None else None,
+                n.bias.data_ptr() if n is not None else None, int(self.silu), 0)
+        return self._struct
 
 
 def silu(x):

@@ -81,6 +81,9 @@ class QuantAttnBlock(BaseQuantBlock):
         self.act_quantizer_w.dynamic = dynamic
 
 
+unet._LAZY_BLOCKS = unet._LAZY_BLOCKS + (QuantResnetBlock,)
+
+
 def get_specials(quant_act=False):
     """Class-name -> quantised block map (qdiff/quant_block.py:372-384, pixel-UNet entries)."""
     return {

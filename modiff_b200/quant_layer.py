@@ -304,13 +304,19 @@ class QuantModule(nn.Module):
                   out.data_ptr(), C.byref(g), _lib.stream_ptr(),
                   nbytes=4 * (x.numel() + out.numel() + w_kn.numel()))
 
-    def _modq(self, x, a_hat, buf, g):
+    def _modq(self, x, a_hat, buf, g, src=None):
         aq = self.act_quantizer
         if not aq.sym:
             raise ModiffError("the int8 path implements symmetric activation codes (--a_sym)")
         if not aq.dynamic:
             raise ModiffError("the int8 path implements dynamic activation scales "
                               "(quant_mode='dynamic'); static calibrated scales are not covered")
+        if src is not None:
+            _lib.call('modiff_modq_src', C.byref(src.struct()), _lib.ptr(a_hat),
+                      buf.codes.data_ptr(), buf.x_scale.data_ptr(), C.byref(g), aq.n_bits,
+                      int(aq.channel_wise), buf.scratch.data_ptr(), _lib.stream_ptr(),
+                      nbytes=13 * src.numel(), tag=g.key())
+            return
         # algorithmic bytes: x 4 + a_hat read/write 8 + code 1 per element
         _lib.call('modiff_modq', x.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
                   buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, int(aq.channel_wise),
@@ -329,9 +335,27 @@ class QuantModule(nn.Module):
                   + g.cout * g.cin * g.kh * g.kw, tag=g.key())
 
     # ------------------------------------------------------------------ forward
-    def forward(self, input: torch.Tensor, split: int = 0):
-        _lib.require_cuda(input, "QuantModule input")
-        input = input.contiguous()
+    def forward_shared(self, owner, input):
+        """Forward of a layer whose input equals `owner`'s input at every step (the k and v
+        projections next to q in an attention block): the residual codes, their scale and the
+        cached input are the owner's, so the quantiser runs once for all of them."""
+        return self.forward(input, 0, _owner=owner)
+
+    def forward(self, input, split: int = 0, _owner=None):
+        """`input` is a CUDA fp32 tensor, or an `ops.ActSource` describing one lazily."""
+        from .ops import ActSource
+        src = None
+        if isinstance(input, ActSource):
+            # only the modulated int8 steps read a source directly; every other path gets the tensor
+            fused = (self.modulate and self.use_act_quant and not self.disable_act_quant and
+                     self.use_weight_quant and self.a_hat is not None and not input.trivial)
+            if fused:
+                src = input
+            else:
+                input = input.x0 if input.trivial else input.materialize()
+        if src is None:
+            _lib.require_cuda(input, "QuantModule input")
+            input = input.contiguous()
 
         if not self.use_weight_quant and not self.use_act_quant and not self.modulate:
             g = self._geom(input, 0)
@@ -373,11 +397,16 @@ class QuantModule(nn.Module):
             raise ModiffError("activation quantisation without weight quantisation is not "
                               "part of the accelerated path (call set_quant_state(True, True))")
 
+        shared = (_owner is not None and self.modulate and _owner.modulate and
+                  _owner.a_hat is not None and _owner is not self)
         buf = self._get_buffers(g, input.device)
+        if shared:
+            obuf = _owner._buffers.get(g.copy(cout=_owner.weight.shape[0]).key())
+            shared = obuf is not None and _owner.act_quantizer.n_bits == self.act_quantizer.n_bits
         if self.modulate:
             if self.a_hat is None:
                 # first step: activations pass through unquantised (quant_layer.py:326-327, 358-359)
-                self.a_hat = input.clone()
+                self.a_hat = _owner.a_hat if shared else input.clone()
                 out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
                 self._conv_fp32(input, w_kn, bias, g, out)
                 self.o_hat = out
@@ -385,7 +414,10 @@ class QuantModule(nn.Module):
                 if self.a_hat.shape != input.shape:
                     raise ModiffError(f"input shape {tuple(input.shape)} differs from the cached "
                                       f"{tuple(self.a_hat.shape)}; call reset_cache() first")
-                self._modq(input, self.a_hat, buf, g)
+                if shared and self.a_hat is _owner.a_hat:
+                    buf = obuf             # the owner's quantiser already ran on this input
+                else:
+                    self._modq(input, self.a_hat, buf, g, src)
                 self._igemm(buf, pack, self.o_hat, True, None, g)
             out = self.o_hat if self.alias_output else self.o_hat.clone()
         else:

@@ -128,26 +128,53 @@ class ResnetBlock(nn.Module):
         return resnet_forward(self, x, temb, split)
 
 
+def _is_quant(m):
+    """QuantModule children take lazily described inputs (ops.ActSource)."""
+    return hasattr(m, "implicit_pad")
+
+
 def resnet_forward(blk, x, temb, split=0):
-    """Shared by ResnetBlock and QuantResnetBlock (qdiff/quant_block.py:293-313)."""
+    """Shared by ResnetBlock and QuantResnetBlock (qdiff/quant_block.py:293-313).
+
+    `x` is a tensor, or an `ops.ActSource` holding the two halves of the up path's channel
+    concat.  With QuantModule children the GroupNorm + swish (+ temb bias) are described to the
+    layer instead of being materialised; plain torch children get materialised tensors.
+    """
     if temb is None:
         assert len(x) == 2
         x, temb = x
-    h = ops.groupnorm(x, blk.norm1, silu=True)
-    h = blk.conv1(h)
-    h = ops.add_channel_bias(h, blk.temb_proj(ops.silu(temb)))
-    h = ops.groupnorm(h, blk.norm2, silu=True)
+    if isinstance(x, ops.ActSource):
+        xa, xb = x.x0, x.x1
+    else:
+        xa, xb = x, None
+    quant = _is_quant(blk.conv1)
     if blk.dropout.training and blk.dropout.p > 0:
-        h = blk.dropout(h)
-    h = blk.conv2(h)
+        quant = False   # dropout needs the materialised tensor
+
+    src1 = ops.ActSource(xa, xb, norm=blk.norm1, silu=True)
+    h = blk.conv1(src1 if quant else src1.materialize())
+    tb = blk.temb_proj(ops.silu(temb))
+    src2 = ops.ActSource(h, chan_bias=tb, norm=blk.norm2, silu=True)
+    if quant:
+        h = blk.conv2(src2)
+    else:
+        h2 = src2.materialize()
+        if blk.dropout.training and blk.dropout.p > 0:
+            h2 = blk.dropout(h2)
+        h = blk.conv2(h2)
+
     if blk.in_channels != blk.out_channels:
-        if blk.use_conv_shortcut:
-            x = blk.conv_shortcut(x)
-        elif split != 0:
-            x = blk.nin_shortcut(x, split)
+        xin = ops.ActSource(xa, xb)
+        short = blk.conv_shortcut if blk.use_conv_shortcut else blk.nin_shortcut
+        if not _is_quant(short):
+            xin = xin.x0 if xin.trivial else xin.materialize()
+        if blk.use_conv_shortcut or split == 0:
+            xs = short(xin)
         else:
-            x = blk.nin_shortcut(x)
-    return ops.add(x, h)
+            xs = short(xin, split)
+    else:
+        xs = xa if xb is None else ops.concat_channels(xa, xb)
+    return ops.add(xs, h)
 
 
 class AttnBlock(nn.Module):
@@ -169,15 +196,23 @@ class AttnBlock(nn.Module):
 def attn_forward(blk, x):
     """Shared by AttnBlock and QuantAttnBlock (qdiff/quant_block.py:338-366): the attention
     matmuls and softmax stay in fp32, as in the reference."""
-    h_ = ops.groupnorm(x, blk.norm, silu=False)
+    src = ops.ActSource(x, norm=blk.norm, silu=False)
+    h_ = src if _is_quant(blk.q) else src.materialize()
     q = blk.q(h_)
-    k = blk.k(h_)
-    v = blk.v(h_)
+    if _is_quant(blk.q) and _is_quant(blk.k) and _is_quant(blk.v):
+        k = blk.k.forward_shared(blk.q, h_)     # same input: one quantisation for q, k, v
+        v = blk.v.forward_shared(blk.q, h_)
+    else:
+        k = blk.k(h_)
+        v = blk.v(h_)
     b, c, h, w = q.shape
     h_ = ops.attention(q.reshape(b, c, h * w), k.reshape(b, c, h * w), v.reshape(b, c, h * w),
                        float(int(c) ** (-0.5)))
     h_ = blk.proj_out(h_.reshape(b, c, h, w))
     return ops.add(x, h_)
+
+
+_LAZY_BLOCKS = (ResnetBlock,)   # quant_block extends this with QuantResnetBlock
 
 
 class Model(nn.Module):
@@ -286,16 +321,19 @@ class Model(nn.Module):
             stage = self.up[lvl]
             for i in range(self.num_res_blocks + 1):
                 split_ = h.size(1) if split_shortcut else 0
-                cat = ops.concat_channels(h, hs.pop())
-                h = stage.block[i](cat, temb, split=split_) if split_shortcut \
-                    else stage.block[i](cat, temb)
+                blk = stage.block[i]
+                skip = hs.pop()
+                # our own blocks read the two halves of the concat in place
+                cat = ops.ActSource(h, skip) if isinstance(blk, _LAZY_BLOCKS) \
+                    else ops.concat_channels(h, skip)
+                h = blk(cat, temb, split=split_) if split_shortcut else blk(cat, temb)
                 if len(stage.attn) > 0:
                     h = stage.attn[i](h)
             if lvl != 0:
                 h = stage.upsample(h)
 
-        h = ops.groupnorm(h, self.norm_out, silu=True)
-        return self.conv_out(h)
+        src = ops.ActSource(h, norm=self.norm_out, silu=True)
+        return self.conv_out(src if _is_quant(self.conv_out) else src.materialize())
 
     def reset_cache(self):
         pass
