@@ -121,20 +121,16 @@ int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x_scale,
                 void* stream);
 
 /* Where a quantised layer's input comes from when it is not a materialised tensor: the channel
- * concat [x0 | x1], plus an optional per-(image, channel) bias, optionally GroupNorm'ed with
- * given statistics and passed through SiLU.  Lets the quantiser read the producer's output
+ * concat [x0 | x1], then either a per-(image, channel) scale / shift (GroupNorm with its
+ * statistics and any bias folded in) or a plain per-(image, channel) bias, then optionally SiLU.  Lets the quantiser read the producer's output
  * directly instead of a normalised copy (ddim/models/diffusion.py:121-128, 345-349). */
 typedef struct modiff_act_source {
   const float* x0;        /* NCHW [batch][c0][h*w] */
   const float* x1;        /* NCHW [batch][cin - c0][h*w], or NULL */
   int32_t c0;             /* channels of x0 (== cin when x1 is NULL) */
-  int32_t groups;         /* GroupNorm groups (ignored without gn_stats) */
-  const float* chan_bias; /* [batch][cin] or NULL */
-  const float* gn_stats;  /* [batch][groups][2] mean, rstd (modiff_groupnorm_silu), or NULL */
-  const float* gamma;     /* [cin] */
-  const float* beta;      /* [cin] */
   int32_t silu;           /* apply x * sigmoid(x) last */
-  int32_t reserved;
+  const float* affine;    /* [batch][cin][2] scale, shift (modiff_groupnorm_silu), or NULL */
+  const float* chan_bias; /* [batch][cin] added when affine is NULL, or NULL */
 } modiff_act_source;
 
 /* modiff_modq with the input described by a modiff_act_source (same arithmetic on the
@@ -209,10 +205,11 @@ int modiff_fake_quant(const float* x, float* y, int64_t slices, int64_t slice_le
  *       which fuses the torch.cat of the up path (ddim/models/diffusion.py:345-349);
  *   chan_bias fp32 [batch][c] or NULL: added to x first (the "+ temb_proj(...)[:, :, None, None]"
  *       of ddim/models/diffusion.py:124);
- *   y may be NULL and stats non-NULL to obtain only the statistics:
- *   stats fp32 [batch][groups][2] = (mean, 1/sqrt(var + eps)) out, or NULL. */
+ *   y may be NULL and affine non-NULL to obtain only the normalisation as a per-(image,
+ *   channel) scale / shift with the bias folded in:
+ *   affine fp32 [batch][c][2] out (or NULL): gn(x + bias) = x * affine[..][0] + affine[..][1]. */
 int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
-                          float* stats, const float* gamma, const float* beta, int batch, int c,
+                          float* affine, const float* gamma, const float* beta, int batch, int c,
                           int hw, int groups, float eps, int silu, void* stream);
 
 /* y = x * sigmoid(x)  (ddim/models/diffusion.py:27-29). */

@@ -37,9 +37,8 @@ class ConvGeom(C.Structure):
 
 class ActSourceStruct(C.Structure):
     """Mirror of `modiff_act_source`."""
-    _fields_ = [("x0", C.c_void_p), ("x1", C.c_void_p), ("c0", C.c_int32), ("groups", C.c_int32),
-                ("chan_bias", C.c_void_p), ("gn_stats", C.c_void_p), ("gamma", C.c_void_p),
-                ("beta", C.c_void_p), ("silu", C.c_int32), ("reserved", C.c_int32)]
+    _fields_ = [("x0", C.c_void_p), ("x1", C.c_void_p), ("c0", C.c_int32), ("silu", C.c_int32),
+                ("affine", C.c_void_p), ("chan_bias", C.c_void_p)]
 
 
 _P = C.c_void_p

@@ -27,9 +27,9 @@ __device__ inline float block_sum(float v, float* sh) {
 __global__ void __launch_bounds__(512)
 groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1, int c0,
                       const float* __restrict__ chan_bias, float* __restrict__ y,
-                      float* __restrict__ stats, const float* __restrict__ gamma,
+                      float* __restrict__ affine, const float* __restrict__ gamma,
                       const float* __restrict__ beta, int c, int hw, int groups, float eps,
-                      int silu) {
+                      int silu, int lg_hw4) {
   __shared__ float sh[32];
   const int n = blockIdx.x / groups;
   const int grp = blockIdx.x % groups;
@@ -48,11 +48,14 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
   // which keeps the variance free of cancellation when the mean is far from zero.
   const float shift = __fadd_rn(__ldg(src(cbeg)), bias_of(cbeg));
   float s = 0.0f, q = 0.0f;
-  if (vec) {
-    const int hw4 = hw >> 2;
-    for (int i = threadIdx.x; i < cpg * hw4; i += blockDim.x) {
-      const int ch = cbeg + i / hw4;
-      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + i % hw4);
+  if (vec && lg_hw4 >= 0) {
+    // flat sweep over the group, channel = i >> lg_hw4: no divisions, four loads in flight
+    const int total4 = cpg << lg_hw4;
+    const int mask = (1 << lg_hw4) - 1;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < total4; i += blockDim.x) {
+      const int ch = cbeg + (i >> lg_hw4);
+      float4 v = __ldg(reinterpret_cast<const float4*>(src(ch)) + (i & mask));
       const float b = bias_of(ch);
       const float a = __fadd_rn(v.x, b) - shift, bb = __fadd_rn(v.y, b) - shift,
                   cc = __fadd_rn(v.z, b) - shift, dd = __fadd_rn(v.w, b) - shift;
@@ -60,20 +63,30 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
       q += (a * a + bb * bb) + (cc * cc + dd * dd);
     }
   } else {
-    for (int i = threadIdx.x; i < count; i += blockDim.x) {
-      const int ch = cbeg + i / hw;
-      const float a = __fadd_rn(__ldg(src(ch) + i % hw), bias_of(ch)) - shift;
-      s += a;
-      q += a * a;
+    for (int k = 0; k < cpg; ++k) {
+      const int ch = cbeg + k;
+      const float* sp = src(ch);
+      const float b = bias_of(ch);
+      for (int i = threadIdx.x; i < hw; i += blockDim.x) {
+        const float a = __fadd_rn(__ldg(sp + i), b) - shift;
+        s += a;
+        q += a * a;
+      }
     }
   }
   const float ms = block_sum(s, sh) / (float)count;          // mean - shift
   const float mean = shift + ms;
   const float var = fmaxf(block_sum(q, sh) / (float)count - ms * ms, 0.0f);
   const float rstd = 1.0f / sqrtf(var + eps);
-  if (stats && threadIdx.x == 0) {
-    stats[2 * blockIdx.x] = mean;
-    stats[2 * blockIdx.x + 1] = rstd;
+  if (affine) {
+    // per-(image, channel) scale / shift with the bias folded in:
+    // gn(x + b) = x * (gamma*rstd) + (beta + (b - mean) * gamma*rstd)
+    for (int k = threadIdx.x; k < cpg; k += blockDim.x) {
+      const int ch = cbeg + k;
+      const float ga = gamma[ch] * rstd;
+      affine[2 * ((size_t)n * c + ch)] = ga;
+      affine[2 * ((size_t)n * c + ch) + 1] = fmaf(bias_of(ch) - mean, ga, beta[ch]);
+    }
   }
   if (!y) return;
 
@@ -230,19 +243,26 @@ using namespace modiff;
 extern "C" {
 
 int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
-                          float* stats, const float* gamma, const float* beta, int batch, int c,
+                          float* affine, const float* gamma, const float* beta, int batch, int c,
                           int hw, int groups, float eps, int silu, void* stream) {
-  MODIFF_CHECK_ARG(x0 && (y || stats), "NULL pointer argument");
-  MODIFF_CHECK_ARG(!y || (gamma && beta), "gamma / beta are NULL");
+  MODIFF_CHECK_ARG(x0 && (y || affine) && gamma && beta, "NULL pointer argument");
   MODIFF_CHECK_ARG(batch > 0 && c > 0 && hw > 0 && groups > 0 && c % groups == 0,
                    "bad GroupNorm shape: c=%d groups=%d", c, groups);
   MODIFF_CHECK_ARG(c0 > 0 && c0 <= c && (c0 == c || x1 != nullptr), "bad concat split c0=%d", c0);
   MODIFF_CHECK_ARG((((uintptr_t)x0 | (uintptr_t)y | (uintptr_t)x1) & 15) == 0,
                    "GroupNorm tensors must be 16-byte aligned");
   const int count = (c / groups) * hw;
-  const int threads = count >= 4096 ? 512 : (count >= 1024 ? 256 : 128);
+  const int threads = count >= 8192 ? 512 : (count >= 1024 ? 256 : 128);
+  int lg_hw4 = -1;   // log2(hw / 4) when hw / 4 is a power of two
+  if (hw % 4 == 0) {
+    const int hw4 = hw / 4;
+    if ((hw4 & (hw4 - 1)) == 0) {
+      lg_hw4 = 0;
+      while ((1 << lg_hw4) < hw4) ++lg_hw4;
+    }
+  }
   groupnorm_silu_kernel<<<batch * groups, threads, 0, (cudaStream_t)stream>>>(
-      x0, x1, c0, chan_bias, y, stats, gamma, beta, c, hw, groups, eps, silu);
+      x0, x1, c0, chan_bias, y, affine, gamma, beta, c, hw, groups, eps, silu, lg_hw4);
   MODIFF_LAUNCH_CHECK("groupnorm_silu_kernel");
   return MODIFF_OK;
 }

@@ -55,10 +55,8 @@ struct SrcView {
   const float* x0;
   const float* x1;
   const float* bias;
-  const float* stats;
-  const float* gamma;
-  const float* beta;
-  int c0, c1, groups, cpg, silu;
+  const float* affine;
+  int c0, c1, silu;
 };
 
 // Four consecutive pixels of channel c of image n, after the source transform.
@@ -72,17 +70,14 @@ __device__ inline void load_src(const SrcView& s, int n, int c, int cin, int p, 
   const float* base = (c < s.c0) ? s.x0 + ((size_t)n * s.c0 + c) * hw
                                  : s.x1 + ((size_t)n * s.c1 + (c - s.c0)) * hw;
   load4<VEC4>(base, p, hw, v);
-  if (s.bias) {
+  if (s.affine) {
+    const float2 ab = __ldg(reinterpret_cast<const float2*>(s.affine) + (size_t)n * cin + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = fmaf(v[j], ab.x, ab.y);
+  } else if (s.bias) {
     const float b = __ldg(s.bias + (size_t)n * cin + c);
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], b);
-  }
-  if (s.stats) {
-    const float* st = s.stats + 2 * ((size_t)n * s.groups + c / s.cpg);
-    const float mean = __ldg(st), rstd = __ldg(st + 1);
-    const float ga = __ldg(s.gamma + c) * rstd, be = __ldg(s.beta + c);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = gn_apply(v[j], mean, ga, be);
   }
   if (s.silu) {
 #pragma unroll
@@ -440,23 +435,15 @@ extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
                    "bad concat split c0=%d for cin=%d", src->c0, g->cin);
-  if (src->gn_stats) {
-    MODIFF_CHECK_ARG(src->groups > 0 && g->cin % src->groups == 0 && src->gamma && src->beta,
-                     "bad GroupNorm description (groups=%d)", src->groups);
-  }
   SrcView v;
   v.x0 = src->x0;
   v.x1 = src->x1;
   v.bias = src->chan_bias;
-  v.stats = src->gn_stats;
-  v.gamma = src->gamma;
-  v.beta = src->beta;
+  v.affine = src->affine;
   v.c0 = src->c0;
   v.c1 = g->cin - src->c0;
-  v.groups = src->gn_stats ? src->groups : 1;
-  v.cpg = g->cin / v.groups;
   v.silu = src->silu;
-  const bool xform = src->x1 || src->chan_bias || src->gn_stats || src->silu;
+  const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
   return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                          (cudaStream_t)stream);
 }

@@ -1,0 +1,61 @@
+"""CUDA-graph replay of the modulated UNet step.
+
+From the third call after a `reset_cache()` every step launches the same kernels on the same
+buffers (the first call is the unquantised step that creates the caches, the second is the
+first quantised one and allocates the code buffers): that launch sequence - several hundred
+small kernels - is captured once per input shape and replayed, which removes the per-launch
+host cost.  The reference has no counterpart (it runs eager PyTorch, with host synchronisations
+in every quantiser call, qdiff/quant_layer.py:197-213).
+
+The tensor returned by a replayed call is a static buffer that the next call overwrites.
+"""
+import torch
+
+from . import _lib
+from ._lib import ModiffError
+
+EAGER_STEPS = 2
+
+
+class GraphedModel:
+    def __init__(self, qnn):
+        self.qnn = qnn
+        self._epoch = None
+        self._calls = 0
+        self._graphs = {}       # (shape, device) -> dict(graph, x, t, out, kernels)
+
+    def __call__(self, x, t=None, context=None):
+        qnn = self.qnn
+        epoch = getattr(qnn, "_cache_epoch", 0)
+        if epoch != self._epoch:
+            self._epoch = epoch
+            self._calls = 0
+        self._calls += 1
+        if self._calls <= EAGER_STEPS or _lib.TIMER is not None or context is not None:
+            return qnn(x, t, context)
+        _lib.require_cuda(x, "model input")
+        key = (tuple(x.shape), str(x.device))
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._capture(x, t)
+            self._graphs[key] = entry
+        entry["x"].copy_(x)
+        entry["t"].copy_(t)
+        entry["graph"].replay()
+        _lib.LAUNCHES[0] += entry["kernels"]
+        return entry["out"]
+
+    def _capture(self, x, t):
+        sx = x.clone()
+        st = t.clone().float()
+        graph = torch.cuda.CUDAGraph()
+        before = _lib.LAUNCHES[0]
+        torch.cuda.synchronize()
+        try:
+            with torch.cuda.graph(graph):
+                out = self.qnn(sx, st)
+        except Exception as e:   # a capture that failed leaves no usable graph: report loudly
+            raise ModiffError(f"CUDA graph capture of the UNet step failed: {e}") from e
+        kernels = _lib.LAUNCHES[0] - before
+        _lib.LAUNCHES[0] = before       # nothing ran during capture
+        return dict(graph=graph, x=sx, t=st, out=out, kernels=kernels)

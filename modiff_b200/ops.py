@@ -79,17 +79,20 @@ class ActSource:
     def trivial(self):
         return self.x1 is None and self.chan_bias is None and self.norm is None and not self.silu
 
-    def stats(self):
-        """[B, groups, 2] (mean, rstd) of the GroupNorm over this source, computed once."""
+    def affine(self):
+        """[B, C, 2] scale / shift of the GroupNorm over this source (bias folded in), computed
+        once per source object."""
         if self._stats is None and self.norm is not None:
             b, c = self.shape[0], self.shape[1]
             hw = self.numel() // (b * c)
-            self._stats = torch.empty((b, self.norm.num_groups, 2), dtype=torch.float32,
-                                      device=self.device)
+            n = self.norm
+            if c != n.num_channels:
+                raise ModiffError(f"GroupNorm expects {n.num_channels} channels, got {c}")
+            self._stats = torch.empty((b, c, 2), dtype=torch.float32, device=self.device)
             _lib.call('modiff_groupnorm_silu', self.x0.data_ptr(), _lib.ptr(self.x1),
                       self.x0.shape[1], _lib.ptr(self.chan_bias), None, self._stats.data_ptr(),
-                      None, None, b, c, hw, self.norm.num_groups, float(self.norm.eps), 0,
-                      _lib.stream_ptr())
+                      n.weight.data_ptr(), n.bias.data_ptr(), b, c, hw, n.num_groups,
+                      float(n.eps), 0, _lib.stream_ptr())
         return self._stats
 
     def materialize(self):
@@ -109,15 +112,10 @@ class ActSource:
     def struct(self):
         """ctypes mirror of modiff_act_source (keeps this object's tensors alive)."""
         if self._struct is None:
-            st = self.stats()
-            n = self.norm
-            if n is not None and self.shape[1] != n.num_channels:
-                raise ModiffError(f"GroupNorm expects {n.num_channels} channels, got {self.shape[1]}")
+            aff = self.affine()
             self._struct = _lib.ActSourceStruct(
-                self.x0.data_ptr(), _lib.ptr(self.x1), self.x0.shape[1],
-                n.num_groups if n is not None else 1, _lib.ptr(self.chan_bias), _lib.ptr(st),
-                n.weight.data_ptr() if n is not None else None,
-                n.bias.data_ptr() if n is not None else None, int(self.silu), 0)
+                self.x0.data_ptr(), _lib.ptr(self.x1), self.x0.shape[1], int(self.silu),
+                _lib.ptr(aff), None if aff is not None else _lib.ptr(self.chan_bias))
         return self._struct
 
 

@@ -177,6 +177,8 @@ class QuantModule(nn.Module):
         self.o_hat = None
 
         # private device state
+        self._a_store = None      # storage of a_hat / o_hat, kept across reset_cache() so that
+        self._o_store = None      # device addresses stay valid for captured CUDA graphs
         self._buffers = {}
         self._wpack = None
         self._org_kn = None
@@ -406,8 +408,14 @@ class QuantModule(nn.Module):
         if self.modulate:
             if self.a_hat is None:
                 # first step: activations pass through unquantised (quant_layer.py:326-327, 358-359)
-                self.a_hat = _owner.a_hat if shared else input.clone()
-                out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
+                if shared:
+                    self.a_hat = _owner.a_hat
+                else:
+                    self._a_store = self._reuse(self._a_store, input.shape, input.device)
+                    self._a_store.copy_(input)
+                    self.a_hat = self._a_store
+                self._o_store = self._reuse(self._o_store, out_shape, input.device)
+                out = self._o_store
                 self._conv_fp32(input, w_kn, bias, g, out)
                 self.o_hat = out
             else:
@@ -425,6 +433,12 @@ class QuantModule(nn.Module):
             self._modq(input, None, buf, g)
             self._igemm(buf, pack, out, False, bias, g)
         return self.activation_function(out)
+
+    @staticmethod
+    def _reuse(store, shape, device):
+        if store is not None and tuple(store.shape) == tuple(shape) and store.device == device:
+            return store
+        return torch.empty(tuple(shape), dtype=torch.float32, device=device)
 
     def _shape_from(self, input, g, ho_wo):
         if self.fwd_func is F.linear:

@@ -57,9 +57,17 @@ class QuantModel(nn.Module):
                 m.set_quant_state(weight_quant, act_quant)
 
     def reset_cache(self):
+        self._cache_epoch = getattr(self, "_cache_epoch", 0) + 1
         for m in self.model.modules():
             if isinstance(m, QuantModule):
                 m.reset_cache()
+
+    def graphed(self):
+        """This model behind a CUDA-graph replay of its steady-state steps (see graph.py)."""
+        from .graph import GraphedModel
+        if getattr(self, "_graphed", None) is None:
+            object.__setattr__(self, "_graphed", GraphedModel(self))
+        return self._graphed
 
     def set_dynamic_state(self, dynamic):
         for m in self.model.modules():

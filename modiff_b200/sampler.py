@@ -3,6 +3,8 @@
 :377-384 timestep sequences).  State stays on the device for the whole loop; the per-step
 coefficients are host scalars computed in fp32 exactly as the reference's tensor ops do.
 """
+import os
+
 import numpy as np
 import torch
 
@@ -76,6 +78,8 @@ def generalized_steps(x, seq, model, b, with_t=False, last_only=True, **kwargs):
     Returns ([x_T, ..., x_0], [x0 predictions]) like the reference when `last_only` is
     False; with `last_only` (default) only the final sample is kept: ([x_0], []).
     Noise for eta > 0 comes from `generator` (a CUDA torch.Generator) when given.
+    `cuda_graph` (default on, or MODIFF_CUDA_GRAPH=0 to turn it off): a QuantModel's steady-state
+    steps are replayed as a CUDA graph (graph.py).
     """
     n = x.size(0)
     seq = list(seq)
@@ -83,6 +87,9 @@ def generalized_steps(x, seq, model, b, with_t=False, last_only=True, **kwargs):
     eta = float(kwargs.get("eta", 0))
     generator = kwargs.get("generator", None)
     alphas = alpha_table(b.detach().cpu() if isinstance(b, torch.Tensor) else b)
+    use_graph = kwargs.get("cuda_graph", os.environ.get("MODIFF_CUDA_GRAPH", "1") != "0")
+    if use_graph and hasattr(model, "graphed") and x.is_cuda:
+        model = model.graphed()
     xs, x0_preds, ts = [x], [], []
     xt = x
     for i, j in zip(reversed(seq), reversed(seq_next)):
