@@ -35,7 +35,7 @@ def sample(c, cuda, keep_eps=0):
         return e
 
     betas = torch.from_numpy(m.get_beta_schedule()).float()
-    xs, _ = m.generalized_steps(cases.unet_noise(c).to(cuda), cases.unet_sequence(c), fn, betas, eta=0.0)
+    xs, _ = m.generalized_steps(cases.unet_noise(c).to(cuda), cases.unet_sequence(c), fn, betas, eta=0.0)   # fn is a plain callable: eager
     torch.cuda.synchronize()
     assert m.device_status() == 0
     return xs[-1].cpu(), [e.cpu() for e in eps]
@@ -85,3 +85,25 @@ def test_fp32_model_matches_reference(cuda, golden_unet):
     finally:
         torch.backends.cudnn.allow_tf32 = prev
     assert oracle.psnr(golden_unet["fp32_b8_s100/final"], final.numpy()) >= 60.0
+
+
+def test_cuda_graph_replay_is_bit_identical(cuda):
+    """Steady-state steps replayed as a CUDA graph launch the same kernels on the same buffers:
+    the samples must equal the eager run bit for bit, also on a second pass that reuses the
+    captured graph after reset_cache()."""
+    import modiff_b200 as m
+    c = next(u for u in cases.UNET_CASES if u["name"] == "w4a4_split_b2_s10")
+    qnn = build(c, cuda)
+    betas = torch.from_numpy(m.get_beta_schedule()).float()
+    x = cases.unet_noise(c).to(cuda)
+    seq = cases.unet_sequence(c)
+    outs = []
+    for use_graph in (False, True, True):
+        qnn.reset_cache()
+        xs, _ = m.generalized_steps(x, seq, qnn, betas, eta=0.0, cuda_graph=use_graph)
+        outs.append(xs[-1].clone())
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2])
+    assert len(qnn.graphed()._graphs) == 1
