@@ -180,12 +180,68 @@ int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                       const modiff_conv_geom* g, int per_sample, int impl,
                       int32_t* acc_out, void* stream);
 
+/* Receptive-field gather of activation codes for layers with very few input channels (the
+ * 3-channel input conv, ddim/models/diffusion.py:321): out[m][c*kh*kw + tap], one row of
+ * out_stride bytes per output pixel m (bytes past cin*kh*kw are left untouched: zero-fill the
+ * buffer once).  The layer then runs as a 1x1 layer over out with the weights packed as
+ * [cout][cin*kh*kw] (PyTorch's own weight order). */
+int modiff_im2col_codes(const int8_t* codes, int8_t* out, const modiff_conv_geom* g, int out_stride,
+                        void* stream);
+
 /* First-step conv / linear: fp32 activations x dequantised weights + bias
  * (qdiff/quant_layer.py:326-327, 358-359; also the weight-only-quant and
  * unquantised paths :309-311, :364-365).
  *   x fp32 NCHW, w_kn fp32 [cin*kh*kw][cout] (K order cin,ky,kx), out fp32 NCHW. */
 int modiff_conv_fp32(const float* x, const float* w_kn, const float* bias, float* out,
                      const modiff_conv_geom* g, void* stream);
+
+/* ---- split-bf16 tensor-core GEMM (first sampling step and attention matmuls) -------------
+ * fp32 values travel as two bf16 planes, hi = bf16(x) and lo = bf16(x - hi); the GEMM adds the
+ * products hi*hi + hi*lo + lo*hi in fp32 (relative error ~1e-5). */
+
+/* fp32 NCHW [batch][cin][h][w] -> bf16 [batch][2][stride^2][hp][wp][round_up(cin,8)] in the
+ * code-plane geometry of g (zero halo: the caller zero-fills the buffer once). */
+int64_t modiff_bf16_planes_bytes(const modiff_conv_geom* g);
+int modiff_split_bf16(const float* x, uint16_t* planes, const modiff_conv_geom* g, void* stream);
+/* x fp32 [nb][inner] -> bf16 [nb][2][inner], no layout change. */
+int modiff_split_bf16_flat(const float* x, uint16_t* out, int64_t nb, int64_t inner, void* stream);
+/* Integer part (q - zp) of the fake-quantised weights, exact in bf16, as
+ * [cout][kh*kw][round_up(cin,8)]; w_scale / w_zp come from modiff_weight_pack
+ * (qdiff/quant_layer.py:345-351). */
+int64_t modiff_weights_bf16_bytes(const modiff_conv_geom* g);
+int modiff_weights_bf16(const float* w, const float* w_scale, const float* w_zp, uint16_t* out,
+                        const modiff_conv_geom* g, int n_bits, void* stream);
+
+typedef struct modiff_gemm_bf16_desc {
+  const uint16_t* a;      /* activation planes (modiff_split_bf16 layout) */
+  const uint16_t* b;      /* [images or 1][b_parts][cout][kh*kw][kb] bf16, K-major */
+  const float* col_scale; /* [2][cout] per-column factor per segment, or NULL */
+  const float* bias;      /* [cout] or NULL */
+  float* out;             /* fp32 NCHW [batch][cout][ho*wo] */
+  int32_t a_parts;        /* 2 = hi and lo planes are used, 1 = hi only */
+  int32_t b_parts;        /* 1 (exact bf16 weights) or 2 */
+  int32_t b_batched;      /* != 0: one B per image (attention), tiles never mix images */
+  int32_t kb;             /* K stride per filter tap of B, elements (multiple of 8, >= cin) */
+  float scale;            /* uniform factor */
+  int32_t reserved;
+} modiff_gemm_bf16_desc;
+
+/* out = scale * col_scale[c] * (A conv B) + bias[c]  on tcgen05 kind::f16, fp32 accumulation.
+ * First step: F.conv2d(input, weight_q, bias) with unquantised input
+ * (qdiff/quant_layer.py:358-359).  Attention: the bmm's of qdiff/quant_block.py:351, 360.
+ * MODIFF_ERR_UNSUPPORTED when the geometry is outside the tensor-core path. */
+int modiff_gemm_bf16(const modiff_gemm_bf16_desc* desc, const modiff_conv_geom* g, void* stream);
+
+/* Whole attention for small token counts (t, tk <= 64) on CUDA cores, fp32:
+ * out[b,:,i] = sum_j softmax_j(q[b,:,i].k[b,:,j] * scale) v[b,:,j]; q, out [batch][c][t],
+ * k, v [batch][c][tk] (qdiff/quant_block.py:344-360; the 4x4 middle block of the pixel UNet). */
+int modiff_attention_small(const float* q, const float* k, const float* v, float* out, int batch,
+                           int c, int t, int tk, float scale, void* stream);
+
+/* Softmax over keys of s fp32 [batch][tk][tq] (the layout modiff_gemm_bf16 writes when the keys
+ * are its output columns) -> probabilities as split bf16 planes p [batch][2][tq][tk]
+ * (softmax of qdiff/quant_block.py:353, ddim/models/diffusion.py:185). */
+int modiff_softmax_split(const float* s, uint16_t* p, int batch, int tk, int tq, void* stream);
 
 /* Stand-alone fake quantiser returning the dequantised tensor
  * (UniformAffineQuantizer.forward, qdiff/quant_layer.py:70-111; scale rules
@@ -205,12 +261,15 @@ int modiff_fake_quant(const float* x, float* y, int64_t slices, int64_t slice_le
  *       which fuses the torch.cat of the up path (ddim/models/diffusion.py:345-349);
  *   chan_bias fp32 [batch][c] or NULL: added to x first (the "+ temb_proj(...)[:, :, None, None]"
  *       of ddim/models/diffusion.py:124);
+ *   film fp32 [batch][2c] or NULL: the norm output becomes gn * (1 + film[:, :c]) + film[:, c:]
+ *       (scale-shift norm, ldm/modules/diffusionmodules/openaimodel.py:267-271);
  *   y may be NULL and affine non-NULL to obtain only the normalisation as a per-(image,
  *   channel) scale / shift with the bias folded in:
  *   affine fp32 [batch][c][2] out (or NULL): gn(x + bias) = x * affine[..][0] + affine[..][1]. */
-int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
-                          float* affine, const float* gamma, const float* beta, int batch, int c,
-                          int hw, int groups, float eps, int silu, void* stream);
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias,
+                          const float* film, float* y, float* affine, const float* gamma,
+                          const float* beta, int batch, int c, int hw, int groups, float eps,
+                          int silu, void* stream);
 
 /* y = x * sigmoid(x)  (ddim/models/diffusion.py:27-29). */
 int modiff_silu(const float* x, float* y, int64_t n, void* stream);
@@ -224,15 +283,20 @@ int modiff_add(const float* a, const float* b, float* out, int batch, int c, int
 /* Nearest-neighbour 2x upsample NCHW (ddim/models/diffusion.py:47-48). */
 int modiff_upsample2x(const float* x, float* y, int batch, int c, int h, int w, void* stream);
 
+/* 2x2 average pooling NCHW (the down-sampling ResBlocks of the latent UNets,
+ * ldm/modules/diffusionmodules/openaimodel.py:134-160 with use_conv=False). */
+int modiff_avgpool2x(const float* x, float* y, int batch, int c, int h, int w, void* stream);
+
 /* Channel concat of two NCHW tensors (ddim/models/diffusion.py:345-349). */
 int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, int batch,
                     int hw, void* stream);
 
 /* Sinusoidal timestep embedding [batch][dim]: sin(t*freq) | cos(t*freq)
  * (ddim/models/diffusion.py:6-24).  freq[dim/2] = exp(-i*log(10000)/(dim/2-1)) is supplied by
- * the caller so that it carries the same bits as the host library's exp. */
+ * the caller so that it carries the same bits as the host library's exp.  cos_first != 0 gives
+ * cos | sin, the order of ldm/modules/diffusionmodules/util.py:151-171. */
 int modiff_timestep_embedding(const float* t, const float* freq, float* emb, int batch, int dim,
-                              void* stream);
+                              int cos_first, void* stream);
 
 /* One DDIM (generalised) update (ddim/functions/denoising.py:30-48):
  *   x0 = (x - e*s1) / s2;  x' = s3*x0 + c1*noise + c2*e
@@ -241,6 +305,11 @@ int modiff_timestep_embedding(const float* t, const float* freq, float* emb, int
 int modiff_ddim_step(const float* x, const float* e, const float* noise, float* x_next,
                      float* x0, int64_t n, float s1, float s2, float s3, float c1, float c2,
                      void* stream);
+
+/* Classifier-free guidance: out = e_uncond + scale * (e_cond - e_uncond)
+ * (ldm/models/diffusion/ddim.py:207-208). */
+int modiff_cfg_combine(const float* e_uncond, const float* e_cond, float* out, int64_t n,
+                       float scale, void* stream);
 
 /* int4 nibble pack / unpack of int8 codes: element 2i -> low nibble, 2i+1 -> high
  * nibble, two's complement (qdiff/quant_layer_int4.py:341-346, 354-366). */

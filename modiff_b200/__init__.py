@@ -5,12 +5,14 @@ from .quant_layer import QuantModule, UniformAffineQuantizer, StraightThrough, r
 from .quant_block import BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, get_specials
 from .quant_model import QuantModel
 from .unet import Model, make_config
+from .ldm_unet import UNetModel, rerandomize_zero_tensors
+from .ldm_sampler import DDIMSampler
 from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
                       make_timestep_sequence)
 
 __all__ = [
     "ModiffError", "lib", "device_status", "QuantModule", "UniformAffineQuantizer",
     "StraightThrough", "round_ste", "BaseQuantBlock", "QuantResnetBlock", "QuantAttnBlock",
-    "get_specials", "QuantModel", "Model", "make_config", "generalized_steps", "compute_alpha",
+    "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
     "get_beta_schedule", "make_timestep_sequence",
 ]

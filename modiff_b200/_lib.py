@@ -41,6 +41,14 @@ class ActSourceStruct(C.Structure):
                 ("affine", C.c_void_p), ("chan_bias", C.c_void_p)]
 
 
+class GemmBf16Desc(C.Structure):
+    """Mirror of `modiff_gemm_bf16_desc`."""
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("col_scale", C.c_void_p),
+                ("bias", C.c_void_p), ("out", C.c_void_p), ("a_parts", C.c_int32),
+                ("b_parts", C.c_int32), ("b_batched", C.c_int32), ("kb", C.c_int32),
+                ("scale", C.c_float), ("reserved", C.c_int32)]
+
+
 _P = C.c_void_p
 _G = C.POINTER(ConvGeom)
 
@@ -62,17 +70,29 @@ SIGNATURES = {
     "modiff_modq_static": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P]),
     "modiff_igemm_conv": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P, _G, C.c_int,
                                     C.c_int, _P, _P]),
+    "modiff_im2col_codes": (C.c_int, [_P, _P, _G, C.c_int, _P]),
     "modiff_conv_fp32": (C.c_int, [_P, _P, _P, _P, _G, _P]),
+    "modiff_bf16_planes_bytes": (C.c_int64, [_G]),
+    "modiff_split_bf16": (C.c_int, [_P, _P, _G, _P]),
+    "modiff_split_bf16_flat": (C.c_int, [_P, _P, C.c_int64, C.c_int64, _P]),
+    "modiff_weights_bf16_bytes": (C.c_int64, [_G]),
+    "modiff_weights_bf16": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, _P]),
+    "modiff_gemm_bf16": (C.c_int, [C.POINTER(GemmBf16Desc), _G, _P]),
+    "modiff_softmax_split": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "modiff_attention_small": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_float, _P]),
     "modiff_fake_quant": (C.c_int, [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int,
                                     C.c_int, C.c_int, _P, _P, _P, _P]),
-    "modiff_groupnorm_silu": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, _P, C.c_int, C.c_int,
+    "modiff_groupnorm_silu": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, _P, _P, C.c_int, C.c_int,
                                         C.c_int, C.c_int, C.c_float, C.c_int, _P]),
+    "modiff_avgpool2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_silu": (C.c_int, [_P, _P, C.c_int64, _P]),
     "modiff_add": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_upsample2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_concat_c": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_int, _P]),
-    "modiff_timestep_embedding": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P]),
+    "modiff_timestep_embedding": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_ddim_step": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64] + [C.c_float] * 5 + [_P]),
+    "modiff_cfg_combine": (C.c_int, [_P, _P, _P, C.c_int64, C.c_float, _P]),
     "modiff_pack_int4": (C.c_int, [_P, _P, C.c_int64, _P]),
     "modiff_unpack_int4": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
     "modiff_quantize_static": (C.c_int, [_P, _P, _P, _G, C.c_int, _P]),
@@ -100,10 +120,11 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1,
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_flat": 1,
+    "modiff_weights_bf16": 1, "modiff_gemm_bf16": 1, "modiff_softmax_split": 1, "modiff_attention_small": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
-    "modiff_upsample2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
-    "modiff_ddim_step": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
+    "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
+    "modiff_ddim_step": 1, "modiff_cfg_combine": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
     "modiff_quantize_static": 1,
 }
 LAUNCHES = [0]        # kernels launched through `call` since import

@@ -26,8 +26,9 @@ __device__ inline float block_sum(float v, float* sh) {
 // Input = channel concat [x0 | x1] plus an optional per-(image, channel) bias.
 __global__ void __launch_bounds__(512)
 groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1, int c0,
-                      const float* __restrict__ chan_bias, float* __restrict__ y,
-                      float* __restrict__ affine, const float* __restrict__ gamma,
+                      const float* __restrict__ chan_bias, const float* __restrict__ film,
+                      float* __restrict__ y, float* __restrict__ affine,
+                      const float* __restrict__ gamma,
                       const float* __restrict__ beta, int c, int hw, int groups, float eps,
                       int silu, int lg_hw4) {
   __shared__ float sh[32];
@@ -83,9 +84,15 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
     // gn(x + b) = x * (gamma*rstd) + (beta + (b - mean) * gamma*rstd)
     for (int k = threadIdx.x; k < cpg; k += blockDim.x) {
       const int ch = cbeg + k;
-      const float ga = gamma[ch] * rstd;
+      float ga = gamma[ch] * rstd;
+      float sh = fmaf(bias_of(ch) - mean, ga, beta[ch]);
+      if (film) {   // gn(x) * (1 + scale) + shift
+        const float f = 1.0f + film[(size_t)n * 2 * c + ch];
+        ga *= f;
+        sh = fmaf(sh, f, film[(size_t)n * 2 * c + c + ch]);
+      }
       affine[2 * ((size_t)n * c + ch)] = ga;
-      affine[2 * ((size_t)n * c + ch) + 1] = fmaf(bias_of(ch) - mean, ga, beta[ch]);
+      affine[2 * ((size_t)n * c + ch) + 1] = sh;
     }
   }
   if (!y) return;
@@ -103,6 +110,10 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
       o.y = gn_apply(__fadd_rn(v.y, b), mean, ga, be);
       o.z = gn_apply(__fadd_rn(v.z, b), mean, ga, be);
       o.w = gn_apply(__fadd_rn(v.w, b), mean, ga, be);
+      if (film) {
+        const float f = 1.0f + film[(size_t)n * 2 * c + ch], sh = film[(size_t)n * 2 * c + c + ch];
+        o.x = fmaf(o.x, f, sh); o.y = fmaf(o.y, f, sh); o.z = fmaf(o.z, f, sh); o.w = fmaf(o.w, f, sh);
+      }
       if (silu) { o.x = silu_f(o.x); o.y = silu_f(o.y); o.z = silu_f(o.z); o.w = silu_f(o.w); }
       reinterpret_cast<float4*>(yn + (size_t)ch * hw)[i % hw4] = o;
     }
@@ -111,9 +122,45 @@ groupnorm_silu_kernel(const float* __restrict__ x0, const float* __restrict__ x1
       const int ch = cbeg + i / hw;
       float o = gn_apply(__fadd_rn(__ldg(src(ch) + i % hw), bias_of(ch)), mean, gamma[ch] * rstd,
                          beta[ch]);
+      if (film) o = fmaf(o, 1.0f + film[(size_t)n * 2 * c + ch], film[(size_t)n * 2 * c + c + ch]);
       if (silu) o = silu_f(o);
       yn[(size_t)ch * hw + i % hw] = o;
     }
+  }
+}
+
+// Attention for small token counts (t, tk <= 64): one block per image, fp32 on CUDA cores.
+// q [c][t], k [c][tk], v [c][tk], out [c][t]  (qdiff/quant_block.py:344-360).
+__global__ void __launch_bounds__(256)
+attention_small_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                       const float* __restrict__ v, float* __restrict__ out, int c, int t, int tk,
+                       float scale) {
+  __shared__ float sc[64][65];
+  const int b = blockIdx.x;
+  const float* qb = q + (size_t)b * c * t;
+  const float* kb = k + (size_t)b * c * tk;
+  const float* vb = v + (size_t)b * c * tk;
+  for (int e = threadIdx.x; e < t * tk; e += blockDim.x) {
+    const int i = e / tk, j = e % tk;
+    float acc = 0.0f;
+    for (int ch = 0; ch < c; ++ch) acc = fmaf(__ldg(qb + (size_t)ch * t + i), __ldg(kb + (size_t)ch * tk + j), acc);
+    sc[i][j] = acc * scale;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < t; i += blockDim.x) {
+    float mx = -INFINITY;
+    for (int j = 0; j < tk; ++j) mx = fmaxf(mx, sc[i][j]);
+    float sum = 0.0f;
+    for (int j = 0; j < tk; ++j) { const float e = expf(sc[i][j] - mx); sc[i][j] = e; sum += e; }
+    const float inv = 1.0f / sum;
+    for (int j = 0; j < tk; ++j) sc[i][j] *= inv;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < c * t; e += blockDim.x) {
+    const int ch = e / t, i = e % t;
+    float acc = 0.0f;
+    for (int j = 0; j < tk; ++j) acc = fmaf(__ldg(vb + (size_t)ch * tk + j), sc[i][j], acc);
+    out[(size_t)b * c * t + e] = acc;
   }
 }
 
@@ -158,6 +205,21 @@ __global__ void upsample2x_kernel(const float* __restrict__ x, float* __restrict
   }
 }
 
+__global__ void avgpool2x_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                 int64_t planes, int h, int w) {
+  const int ho = h / 2, wo = w / 2;
+  const int64_t total = planes * ho * wo;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int xx = (int)(i % wo);
+    const int yy = (int)((i / wo) % ho);
+    const int64_t pl = i / ((int64_t)wo * ho);
+    const float* p = x + (pl * h + 2 * yy) * w + 2 * xx;
+    y[i] = (((p[0] + p[1]) + p[w]) + p[w + 1]) * 0.25f;
+  }
+}
+
 __global__ void concat_c_kernel(const float* __restrict__ a, int64_t ea, const float* __restrict__ b,
                                 int64_t eb, float* __restrict__ y, int64_t total) {
   // per image: ea elements of a followed by eb elements of b
@@ -172,7 +234,8 @@ __global__ void concat_c_kernel(const float* __restrict__ a, int64_t ea, const f
 
 __global__ void timestep_embedding_kernel(const float* __restrict__ t,
                                           const float* __restrict__ freq,
-                                          float* __restrict__ emb, int batch, int dim) {
+                                          float* __restrict__ emb, int batch, int dim,
+                                          int cos_first) {
   const int half = dim / 2;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch * dim) return;
@@ -180,7 +243,7 @@ __global__ void timestep_embedding_kernel(const float* __restrict__ t,
   if (j >= 2 * half) { emb[i] = 0.0f; return; }  // odd dim: zero pad
   const int f = (j < half) ? j : j - half;
   const float arg = __fmul_rn(t[b], freq[f]);
-  emb[i] = (j < half) ? sinf(arg) : cosf(arg);
+  emb[i] = ((j < half) != (cos_first != 0)) ? sinf(arg) : cosf(arg);
 }
 
 __global__ void ddim_step_kernel(const float* __restrict__ x, const float* __restrict__ e,
@@ -198,6 +261,14 @@ __global__ void ddim_step_kernel(const float* __restrict__ x, const float* __res
     x_next[i] = acc;
     if (x0_out) x0_out[i] = x0;
   }
+}
+
+__global__ void cfg_combine_kernel(const float* __restrict__ eu, const float* __restrict__ ec,
+                                   float* __restrict__ out, int64_t n, float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride)
+    out[i] = __fadd_rn(eu[i], __fmul_rn(scale, __fsub_rn(ec[i], eu[i])));
 }
 
 __global__ void pack_int4_kernel(const int8_t* __restrict__ codes, uint8_t* __restrict__ packed,
@@ -242,9 +313,10 @@ using namespace modiff;
 
 extern "C" {
 
-int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias, float* y,
-                          float* affine, const float* gamma, const float* beta, int batch, int c,
-                          int hw, int groups, float eps, int silu, void* stream) {
+int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float* chan_bias,
+                          const float* film, float* y, float* affine, const float* gamma,
+                          const float* beta, int batch, int c, int hw, int groups, float eps,
+                          int silu, void* stream) {
   MODIFF_CHECK_ARG(x0 && (y || affine) && gamma && beta, "NULL pointer argument");
   MODIFF_CHECK_ARG(batch > 0 && c > 0 && hw > 0 && groups > 0 && c % groups == 0,
                    "bad GroupNorm shape: c=%d groups=%d", c, groups);
@@ -262,8 +334,17 @@ int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float*
     }
   }
   groupnorm_silu_kernel<<<batch * groups, threads, 0, (cudaStream_t)stream>>>(
-      x0, x1, c0, chan_bias, y, affine, gamma, beta, c, hw, groups, eps, silu, lg_hw4);
+      x0, x1, c0, chan_bias, film, y, affine, gamma, beta, c, hw, groups, eps, silu, lg_hw4);
   MODIFF_LAUNCH_CHECK("groupnorm_silu_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_attention_small(const float* q, const float* k, const float* v, float* out, int batch,
+                           int c, int t, int tk, float scale, void* stream) {
+  MODIFF_CHECK_ARG(q && k && v && out && batch > 0 && c > 0, "bad argument");
+  MODIFF_CHECK_ARG(t > 0 && tk > 0 && t <= 64 && tk <= 64, "token counts %d x %d exceed 64", t, tk);
+  attention_small_kernel<<<batch, 256, 0, (cudaStream_t)stream>>>(q, k, v, out, c, t, tk, scale);
+  MODIFF_LAUNCH_CHECK("attention_small_kernel");
   return MODIFF_OK;
 }
 
@@ -299,6 +380,16 @@ int modiff_upsample2x(const float* x, float* y, int batch, int c, int h, int w, 
   return MODIFF_OK;
 }
 
+int modiff_avgpool2x(const float* x, float* y, int batch, int c, int h, int w, void* stream) {
+  MODIFF_CHECK_ARG(x && y && batch > 0 && c > 0 && h >= 2 && w >= 2 && h % 2 == 0 && w % 2 == 0,
+                   "bad argument");
+  const int64_t planes = (int64_t)batch * c;
+  avgpool2x_kernel<<<grid_for(planes * (h / 2) * (w / 2), 256), 256, 0, (cudaStream_t)stream>>>(
+      x, y, planes, h, w);
+  MODIFF_LAUNCH_CHECK("avgpool2x_kernel");
+  return MODIFF_OK;
+}
+
 int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, int batch, int hw,
                     void* stream) {
   MODIFF_CHECK_ARG(a && b && y && ca > 0 && cb > 0 && batch > 0 && hw > 0, "bad argument");
@@ -310,9 +401,9 @@ int modiff_concat_c(const float* a, int ca, const float* b, int cb, float* y, in
 }
 
 int modiff_timestep_embedding(const float* t, const float* freq, float* emb, int batch, int dim,
-                              void* stream) {
+                              int cos_first, void* stream) {
   MODIFF_CHECK_ARG(t && freq && emb && batch > 0 && dim >= 4, "bad argument");
-  timestep_embedding_kernel<<<ceil_div(batch * dim, 256), 256, 0, (cudaStream_t)stream>>>(t, freq, emb, batch, dim);
+  timestep_embedding_kernel<<<ceil_div(batch * dim, 256), 256, 0, (cudaStream_t)stream>>>(t, freq, emb, batch, dim, cos_first);
   MODIFF_LAUNCH_CHECK("timestep_embedding_kernel");
   return MODIFF_OK;
 }
@@ -323,6 +414,15 @@ int modiff_ddim_step(const float* x, const float* e, const float* noise, float* 
   ddim_step_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(x, e, noise, x_next, x0, n, s1,
                                                                       s2, s3, c1, c2);
   MODIFF_LAUNCH_CHECK("ddim_step_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_cfg_combine(const float* e_uncond, const float* e_cond, float* out, int64_t n,
+                       float scale, void* stream) {
+  MODIFF_CHECK_ARG(e_uncond && e_cond && out && n > 0, "bad argument");
+  cfg_combine_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(e_uncond, e_cond, out, n,
+                                                                        scale);
+  MODIFF_LAUNCH_CHECK("cfg_combine_kernel");
   return MODIFF_OK;
 }
 

@@ -12,8 +12,7 @@
 //
 // Reference arithmetic: qdiff/quant_layer.py:345-365 (see igemm_simt.cu).
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tc_common.cuh"
 
 namespace modiff {
 
@@ -33,9 +32,7 @@ constexpr int kOHalfBytes = 64 * 128 * 4;
 constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // TMA warp, MMA warp, epilogue warps, store warp
 constexpr int kStoreWarp = 2 + kEpiWarps;
 constexpr int kMaxStages = 6;
-constexpr uint32_t kSpinLimit = 1u << 28;
 
-__device__ int g_device_status = 0;   // sticky: non-zero after a bounded wait ran out
 
 struct TcParams {
   modiff_conv_geom g;
@@ -64,142 +61,6 @@ struct TcParams {
   float* o_hat;
   int32_t* acc_out;
 };
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ inline uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ inline void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ inline void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ inline bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ inline uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait (about two seconds).  Returns false when the limit ran out or another role
-// of this CTA already gave up.
-__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > 2000000000ull) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(&g_device_status, 1);
-  return false;
-}
-
-__device__ inline void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
-                                   int c1, int c2, int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
-      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-      : "memory");
-}
-__device__ inline void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
-                                   int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ inline void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
-                                   int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-      "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ inline void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                   map),
-               "r"(src), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-
-__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ inline void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ inline void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ inline void tc_ld32(uint32_t taddr, int (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ inline void tc_ld1(uint32_t taddr, int& v) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr) : "memory");
-}
-__device__ inline void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
-// 8-row groups 1024 bytes apart.
-__device__ inline uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);       // start address, bits [0,14)
-  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                         // layout type: 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor of kind::i8: s8 x s8 -> s32, both operands K-major.
-__host__ __device__ inline uint32_t make_idesc_i8(int m, int n) {
-  uint32_t d = 0;
-  d |= 2u << 4;                 // D format: s32
-  d |= 1u << 7;                 // A format: signed 8 bit
-  d |= 1u << 10;                // B format: signed 8 bit
-  d |= (uint32_t)(n >> 3) << 17;
-  d |= (uint32_t)(m >> 4) << 24;
-  return d;
-}
 
 struct TileCoord {
   int tn, th, tw, nt;
@@ -545,26 +406,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 }  // namespace
@@ -728,12 +569,15 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   return MODIFF_OK;
 }
 
+int read_device_status_bf16(int* status, int reset);   // gemm_bf16_tc.cu
+
 int read_device_status(int* status, int reset) {
-  MODIFF_CUDA(cudaMemcpyFromSymbol(status, g_device_status, sizeof(int)));
-  if (reset) {
-    int zero = 0;
-    MODIFF_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
-  }
+  int a = 0, b = 0;
+  int rc = read_status_this_unit(&a, reset);
+  if (rc) return rc;
+  rc = read_device_status_bf16(&b, reset);
+  if (rc) return rc;
+  *status = a | b;
   return MODIFF_OK;
 }
 

@@ -503,6 +503,49 @@ extern "C" int modiff_modq_static(const float* x, float* a_hat, int8_t* codes, f
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
 }
 
+namespace modiff {
+namespace {
+// Gathers the receptive field of every output pixel from the code planes into one row:
+// out[m][c * taps + tap] = code of input channel c at filter tap `tap` of output pixel m.
+// Turns a convolution with very few input channels (the 3-channel input conv) into a dense
+// K = cin*kh*kw GEMM that the tensor-core kernel can run as a 1x1 layer.
+__global__ void im2col_codes_kernel(const int8_t* __restrict__ codes, int8_t* __restrict__ out,
+                                    modiff_conv_geom g, Derived d, int out_stride) {
+  const int howo = d.ho * d.wo;
+  const int64_t total = (int64_t)g.batch * howo;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; m < total; m += stride) {
+    const int n = (int)(m / howo), r = (int)(m % howo);
+    const int oy = r / d.wo, ox = r % d.wo;
+    int8_t* row = out + m * out_stride;
+    for (int tap = 0; tap < d.taps; ++tap) {
+      const int ry = tap / g.kw, rx = tap % g.kw;
+      const int plane = (ry % g.stride) * g.stride + (rx % g.stride);
+      const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + oy + ry / g.stride) * d.wp + ox +
+                         rx / g.stride;
+      const int8_t* src = codes + pix * d.cp;
+      for (int c = 0; c < g.cin; ++c) row[c * d.taps + tap] = src[c];
+    }
+  }
+}
+}  // namespace
+}  // namespace modiff
+
+extern "C" int modiff_im2col_codes(const int8_t* codes, int8_t* out, const modiff_conv_geom* g,
+                                   int out_stride, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(codes && out, "NULL pointer argument");
+  Derived d = derive(*g);
+  MODIFF_CHECK_ARG(out_stride >= g->cin * d.taps, "out_stride %d < cin*kh*kw", out_stride);
+  const int64_t total = (int64_t)g->batch * d.ho * d.wo;
+  int64_t blocks = ceil_div64(total, 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  im2col_codes_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(codes, out, *g, d, out_stride);
+  MODIFF_LAUNCH_CHECK("im2col_codes_kernel");
+  return MODIFF_OK;
+}
+
 extern "C" int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
                                       const modiff_conv_geom* g, int n_bits, void* stream) {
   int rc = validate_geom(g);

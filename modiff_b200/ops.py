@@ -3,6 +3,7 @@
 Each function allocates its output with torch (device memory plumbing) and launches one
 hand-written kernel on the current CUDA stream.  CUDA float32 tensors only.
 """
+import ctypes as C
 import math
 
 import torch
@@ -17,10 +18,10 @@ def _req(*ts):
             _lib.require_cuda(t)
 
 
-def groupnorm(x, norm, silu=False, x1=None, chan_bias=None):
+def groupnorm(x, norm, silu=False, x1=None, chan_bias=None, film=None):
     """GroupNorm (+SiLU) of `x` (+ a per-(image, channel) bias), or of the channel concat
     [x, x1] without materialising it.  `norm` is a torch.nn.GroupNorm."""
-    _req(x, x1, chan_bias)
+    _req(x, x1, chan_bias, film)
     x = x.contiguous()
     b, c0 = x.shape[0], x.shape[1]
     hw = x.numel() // (b * c0)
@@ -33,8 +34,12 @@ def groupnorm(x, norm, silu=False, x1=None, chan_bias=None):
     if chan_bias is not None:
         chan_bias = chan_bias.contiguous()
     y = torch.empty((b, c) + tuple(x.shape[2:]), dtype=torch.float32, device=x.device)
+    if film is not None:
+        film = film.contiguous()
+        if tuple(film.shape) != (b, 2 * c):
+            raise ModiffError(f"film shape {tuple(film.shape)} != {(b, 2 * c)}")
     _lib.call('modiff_groupnorm_silu', x.data_ptr(), _lib.ptr(x1), c0, _lib.ptr(chan_bias),
-              y.data_ptr(), None, norm.weight.data_ptr(), norm.bias.data_ptr(),
+              _lib.ptr(film), y.data_ptr(), None, norm.weight.data_ptr(), norm.bias.data_ptr(),
               b, c, hw, norm.num_groups, float(norm.eps), int(silu), _lib.stream_ptr())
     return y
 
@@ -47,8 +52,9 @@ class ActSource:
     normalised tensor is never written); everything else calls `materialize()`.
     """
 
-    def __init__(self, x0, x1=None, chan_bias=None, norm=None, silu=False):
-        _req(x0, x1, chan_bias)
+    def __init__(self, x0, x1=None, chan_bias=None, norm=None, silu=False, film=None):
+        _req(x0, x1, chan_bias, film)
+        self.film = None if film is None else film.contiguous()   # [B, 2C] scale | shift
         self.x0 = x0.contiguous()
         self.x1 = None if x1 is None else x1.contiguous()
         self.chan_bias = None if chan_bias is None else chan_bias.contiguous()
@@ -90,7 +96,8 @@ class ActSource:
                 raise ModiffError(f"GroupNorm expects {n.num_channels} channels, got {c}")
             self._stats = torch.empty((b, c, 2), dtype=torch.float32, device=self.device)
             _lib.call('modiff_groupnorm_silu', self.x0.data_ptr(), _lib.ptr(self.x1),
-                      self.x0.shape[1], _lib.ptr(self.chan_bias), None, self._stats.data_ptr(),
+                      self.x0.shape[1], _lib.ptr(self.chan_bias), _lib.ptr(self.film), None,
+                      self._stats.data_ptr(),
                       n.weight.data_ptr(), n.bias.data_ptr(), b, c, hw, n.num_groups,
                       float(n.eps), 0, _lib.stream_ptr())
         return self._stats
@@ -99,7 +106,8 @@ class ActSource:
         """The transformed tensor, computed once with the stand-alone kernels."""
         if self._tensor is None:
             if self.norm is not None:
-                self._tensor = groupnorm(self.x0, self.norm, self.silu, self.x1, self.chan_bias)
+                self._tensor = groupnorm(self.x0, self.norm, self.silu, self.x1, self.chan_bias,
+                                         self.film)
             else:
                 t = self.x0 if self.x1 is None else concat_channels(self.x0, self.x1)
                 if self.chan_bias is not None:
@@ -162,6 +170,15 @@ def upsample2x(x):
     return y
 
 
+def avgpool2x(x):
+    _req(x)
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    y = torch.empty((b, c, h // 2, w // 2), dtype=torch.float32, device=x.device)
+    _lib.call('modiff_avgpool2x', x.data_ptr(), y.data_ptr(), b, c, h, w, _lib.stream_ptr())
+    return y
+
+
 def concat_channels(a, b):
     _req(a, b)
     a, b = a.contiguous(), b.contiguous()
@@ -176,24 +193,33 @@ def concat_channels(a, b):
 _FREQ_CACHE = {}
 
 
-def _embedding_freqs(dim, device):
-    """exp(arange(half) * -(log(10000) / (half - 1))) evaluated by torch on the host, as the
-    reference does on its device (ddim/models/diffusion.py:17-19), cached per device."""
-    key = (dim, str(device))
+def _embedding_freqs(dim, device, style):
+    """Frequency table evaluated by torch on the host (same bits as the reference's own exp),
+    cached per device.  style 'ddim': exp(arange(half) * -(log(10000) / (half - 1)))
+    (ddim/models/diffusion.py:17-19); style 'ldm': exp(-log(10000) * arange(half) / half)
+    (ldm/modules/diffusionmodules/util.py:160-163)."""
+    key = (dim, str(device), style)
     if key not in _FREQ_CACHE:
         half = dim // 2
-        emb = math.log(10000) / (half - 1)
-        _FREQ_CACHE[key] = torch.exp(torch.arange(half, dtype=torch.float32) * -emb).to(device)
+        if style == "ddim":
+            emb = math.log(10000) / (half - 1)
+            f = torch.exp(torch.arange(half, dtype=torch.float32) * -emb)
+        else:
+            f = torch.exp(-math.log(10000) * torch.arange(start=0, end=half, dtype=torch.float32)
+                          / half)
+        _FREQ_CACHE[key] = f.to(device)
     return _FREQ_CACHE[key]
 
 
-def timestep_embedding(t, dim):
+def timestep_embedding(t, dim, style="ddim"):
+    """Sinusoidal embedding: 'ddim' = sin | cos, 'ldm' = cos | sin with the latent UNets'
+    frequencies."""
     _req(t)
     t = t.contiguous()
-    freq = _embedding_freqs(dim, t.device)
+    freq = _embedding_freqs(dim, t.device, style)
     emb = torch.empty((t.shape[0], dim), dtype=torch.float32, device=t.device)
     _lib.call('modiff_timestep_embedding', t.data_ptr(), freq.data_ptr(), emb.data_ptr(),
-                                                    t.shape[0], dim, _lib.stream_ptr())
+              t.shape[0], dim, int(style == "ldm"), _lib.stream_ptr())
     return emb
 
 
@@ -206,6 +232,17 @@ def ddim_step(x, e, s1, s2, s3, c1, c2, noise=None, want_x0=False):
                                            x_next.data_ptr(), _lib.ptr(x0), x.numel(),
                                            s1, s2, s3, c1, c2, _lib.stream_ptr())
     return (x_next, x0) if want_x0 else x_next
+
+
+def cfg_combine(e_uncond, e_cond, scale):
+    """Classifier-free guidance: e_uncond + scale * (e_cond - e_uncond)
+    (ldm/models/diffusion/ddim.py:207-208)."""
+    _req(e_uncond, e_cond)
+    a, b = e_uncond.contiguous(), e_cond.contiguous()
+    out = torch.empty_like(a)
+    _lib.call('modiff_cfg_combine', a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(),
+              float(scale), _lib.stream_ptr())
+    return out
 
 
 def pack_int4(codes):
@@ -227,10 +264,56 @@ def unpack_int4(packed, n, signed=True):
     return out
 
 
+def _attn_hw(t):
+    """Factor the token count into the (h, w) grid the GEMM tiles walk (powers of two)."""
+    if t & (t - 1):
+        return None
+    w = 1
+    while w * w < t:
+        w *= 2
+    return t // w, w
+
+
 def attention(q, k, v, scale):
-    """Single-head attention over [B, C, T] tensors, fp32 (qdiff/quant_block.py:344-360):
-    out[b,:,i] = sum_j softmax_j(q[b,:,i] . k[b,:,j] * scale) v[b,:,j]."""
+    """Attention over [B, C, T] tensors (one head per batch entry), fp32-accurate
+    (qdiff/quant_block.py:344-360):
+    out[b,:,i] = sum_j softmax_j(q[b,:,i] . k[b,:,j] * scale) v[b,:,j].
+
+    Two split-bf16 tensor-core GEMMs with a softmax between them; small or odd token counts use
+    one CUDA-core kernel."""
     _req(q, k, v)
-    w_ = torch.bmm(q.permute(0, 2, 1), k)
-    w_ = torch.softmax(w_ * scale, dim=2)
-    return torch.bmm(v, w_.permute(0, 2, 1))
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    b, c, t = q.shape
+    tk = k.shape[2]
+    out = torch.empty((b, c, t), dtype=torch.float32, device=q.device)
+    hw = _attn_hw(t)
+    big = (hw is not None and t == tk and t >= 64 and c >= 64 and c % 8 == 0 and t % 8 == 0
+           and hw[1] <= 128)
+    if not big:
+        if t > 64 or tk > 64:
+            raise ModiffError(f"attention with {t} x {tk} tokens, {c} channels is not covered")
+        _lib.call('modiff_attention_small', q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                  out.data_ptr(), b, c, t, tk, float(scale), _lib.stream_ptr())
+        return out
+    l = _lib.lib()
+    dev = q.device
+    h, w = hw
+    gq = _lib.ConvGeom(b, c, t, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
+    nplane = l.modiff_bf16_planes_bytes(C.byref(gq)) // 2
+    qp = torch.empty(nplane, dtype=torch.int16, device=dev)
+    kp = torch.empty(nplane, dtype=torch.int16, device=dev)
+    _lib.call('modiff_split_bf16', q.data_ptr(), qp.data_ptr(), C.byref(gq), _lib.stream_ptr())
+    _lib.call('modiff_split_bf16', k.data_ptr(), kp.data_ptr(), C.byref(gq), _lib.stream_ptr())
+    s = torch.empty((b, t, t), dtype=torch.float32, device=dev)          # [image][key][query]
+    d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, c,
+                           float(scale), 0)
+    _lib.call('modiff_gemm_bf16', C.byref(d1), C.byref(gq), _lib.stream_ptr())
+    pp = torch.empty(b * 2 * t * t, dtype=torch.int16, device=dev)      # [image][2][query][key]
+    _lib.call('modiff_softmax_split', s.data_ptr(), pp.data_ptr(), b, t, t, _lib.stream_ptr())
+    vp = torch.empty(b * 2 * c * t, dtype=torch.int16, device=dev)      # [image][2][c][key]
+    _lib.call('modiff_split_bf16_flat', v.data_ptr(), vp.data_ptr(), b, c * t, _lib.stream_ptr())
+    gv = _lib.ConvGeom(b, t, c, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
+    d2 = _lib.GemmBf16Desc(pp.data_ptr(), vp.data_ptr(), None, None, out.data_ptr(), 2, 2, 1, t,
+                           1.0, 0)
+    _lib.call('modiff_gemm_bf16', C.byref(d2), C.byref(gv), _lib.stream_ptr())
+    return out

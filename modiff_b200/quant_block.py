@@ -9,6 +9,7 @@ import torch.nn as nn
 
 from .quant_layer import QuantModule, UniformAffineQuantizer, StraightThrough
 from . import unet
+from . import ldm_unet
 
 
 class BaseQuantBlock(nn.Module):
@@ -81,12 +82,98 @@ class QuantAttnBlock(BaseQuantBlock):
         self.act_quantizer_w.dynamic = dynamic
 
 
+# ---------------------------------------------------------------- latent UNets (LDM / SD)
+class QuantResBlock(BaseQuantBlock, ldm_unet.TimestepBlock):
+    """Re-hosted latent-UNet residual block (qdiff/quant_block.py:44-111)."""
+
+    def __init__(self, res, act_quant_params: dict = {}):
+        super().__init__(act_quant_params)
+        self.channels = res.channels
+        self.emb_channels = res.emb_channels
+        self.dropout = res.dropout
+        self.out_channels = res.out_channels
+        self.use_conv = res.use_conv
+        self.use_checkpoint = res.use_checkpoint
+        self.use_scale_shift_norm = res.use_scale_shift_norm
+        self.in_layers = res.in_layers
+        self.updown = res.updown
+        self.h_upd = res.h_upd
+        self.x_upd = res.x_upd
+        self.emb_layers = res.emb_layers
+        self.out_layers = res.out_layers
+        self.skip_connection = res.skip_connection
+
+    def forward(self, x, emb=None, split=0):
+        if emb is None:
+            assert len(x) == 2
+            x, emb = x
+        return ldm_unet.resblock_forward(self, x, emb, split)
+
+
+class QuantQKMatMul(BaseQuantBlock):
+    """Holder of the logit scale and of the (never applied) q / k quantisers
+    (qdiff/quant_block.py:114-132): the reference keeps this product in floating point."""
+
+    def __init__(self, act_quant_params: dict = {}):
+        super().__init__(act_quant_params)
+        self.scale = None
+        self.use_act_quant = False
+        self.act_quantizer_q = UniformAffineQuantizer(**act_quant_params)
+        self.act_quantizer_k = UniformAffineQuantizer(**act_quant_params)
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self.use_act_quant = act_quant
+
+
+class QuantSMVMatMul(BaseQuantBlock):
+    """qdiff/quant_block.py:135-151 (quantisers constructed, product in floating point)."""
+
+    def __init__(self, act_quant_params: dict = {}, sm_abit=8):
+        super().__init__(act_quant_params)
+        self.use_act_quant = False
+        self.act_quantizer_v = UniformAffineQuantizer(**act_quant_params)
+        params_w = act_quant_params.copy()
+        params_w['n_bits'] = sm_abit
+        params_w['symmetric'] = False
+        params_w['always_zero'] = True
+        self.act_quantizer_w = UniformAffineQuantizer(**params_w)
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self.use_act_quant = act_quant
+
+
+class QuantAttentionBlock(BaseQuantBlock):
+    """Re-hosted latent-UNet attention block, used when activations are not quantised
+    (qdiff/quant_block.py:154-178)."""
+
+    def __init__(self, attn, act_quant_params: dict = {}):
+        super().__init__(act_quant_params)
+        self.channels = attn.channels
+        self.num_heads = attn.num_heads
+        self.use_checkpoint = attn.use_checkpoint
+        self.norm = attn.norm
+        self.qkv = attn.qkv
+        self.attention = attn.attention
+        self.proj_out = attn.proj_out
+
+    def forward(self, x):
+        return ldm_unet.attention_block_forward(self, x)
+
+
 unet._LAZY_BLOCKS = unet._LAZY_BLOCKS + (QuantResnetBlock,)
+ldm_unet._LAZY_BLOCKS = ldm_unet._LAZY_BLOCKS + (QuantResBlock,)
 
 
 def get_specials(quant_act=False):
-    """Class-name -> quantised block map (qdiff/quant_block.py:372-384, pixel-UNet entries)."""
-    return {
+    """Class-name -> quantised block map (qdiff/quant_block.py:372-384, pixel- and latent-UNet entries)."""
+    specials = {
+        'ResBlock': QuantResBlock,
         'ResnetBlock': QuantResnetBlock,
         'AttnBlock': QuantAttnBlock,
     }
+    if quant_act:
+        specials['QKMatMul'] = QuantQKMatMul
+        specials['SMVMatMul'] = QuantSMVMatMul
+    else:
+        specials['AttentionBlock'] = QuantAttentionBlock
+    return specials

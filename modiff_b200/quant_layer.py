@@ -211,6 +211,13 @@ class QuantModule(nn.Module):
             ph, pw = 0, k['padding'][0]
             b, _, ww = input.shape
             h, kh, kw = 1, 1, w.shape[2]
+            if kw == 1 and sw == 1 and pw == 0 and ww > 1 and (ww & (ww - 1)) == 0:
+                # pointwise over T tokens: any (h, w) factorisation is the same computation;
+                # a near-square one gives the tensor-core kernel its 128-pixel tiles
+                fw = 1
+                while fw * fw < ww:
+                    fw *= 2
+                h, ww = ww // fw, fw
         if sh != sw and not (self.fwd_func is F.conv1d and sw == 1):
             raise ModiffError("anisotropic strides are not supported")
         el, er, et, eb = self.implicit_pad
@@ -306,6 +313,43 @@ class QuantModule(nn.Module):
                   out.data_ptr(), C.byref(g), _lib.stream_ptr(),
                   nbytes=4 * (x.numel() + out.numel() + w_kn.numel()))
 
+    @staticmethod
+    def _bf16_ok(g, ho_wo):
+        """Geometries the split-bf16 tensor-core GEMM covers (mirrors modiff_gemm_bf16)."""
+        def pow2(v):
+            return v > 0 and (v & (v - 1)) == 0
+        ho, wo = ho_wo
+        return (g.cin >= 64 and g.cin % 8 == 0 and g.cout >= 16 and pow2(ho) and pow2(wo)
+                and wo <= 128 and g.split % 64 == 0 and g.kh <= 7 and g.kw <= 7)
+
+    def _conv_first_step(self, x, pack, bias, g, out, ho_wo):
+        """Unquantised activations x fake-quantised weights + bias (quant_layer.py:358-359) on
+        the tensor cores: activations split into two bf16 planes, integer weights exact in bf16,
+        delta_w[c] and the bias applied in the epilogue."""
+        if os.environ.get("MODIFF_FIRST_STEP_FP32", "0") == "1" or not self._bf16_ok(g, ho_wo):
+            return self._conv_fp32(x, pack['w_dq'], bias, g, out)
+        l = _lib.lib()
+        dev = x.device
+        if pack.get('w_bf16') is None:
+            gp = g.copy(batch=1)
+            wb = torch.empty(l.modiff_weights_bf16_bytes(C.byref(gp)) // 2, dtype=torch.int16,
+                             device=dev)
+            wc = self.weight.detach().contiguous()
+            _lib.call('modiff_weights_bf16', wc.data_ptr(), pack['w_scale'].data_ptr(),
+                      pack['w_zp'].data_ptr(), wb.data_ptr(), C.byref(gp),
+                      self.weight_quantizer.n_bits, _lib.stream_ptr())
+            pack['w_bf16'] = wb
+        planes = torch.zeros(l.modiff_bf16_planes_bytes(C.byref(g)) // 2, dtype=torch.int16,
+                             device=dev)
+        _lib.call('modiff_split_bf16', x.data_ptr(), planes.data_ptr(), C.byref(g),
+                  _lib.stream_ptr())
+        kb = -(-g.cin // 8) * 8
+        desc = _lib.GemmBf16Desc(planes.data_ptr(), pack['w_bf16'].data_ptr(),
+                                 pack['w_scale'].data_ptr(), _lib.ptr(bias), out.data_ptr(),
+                                 2, 1, 0, kb, 1.0, 0)
+        _lib.call('modiff_gemm_bf16', C.byref(desc), C.byref(g), _lib.stream_ptr(),
+                  nbytes=4 * (x.numel() + out.numel()), tag=g.key())
+
     def _modq(self, x, a_hat, buf, g, src=None):
         aq = self.act_quantizer
         if not aq.sym:
@@ -325,8 +369,47 @@ class QuantModule(nn.Module):
                   buf.scratch.data_ptr(), _lib.stream_ptr(),
                   nbytes=(13 if a_hat is not None else 5) * x.numel(), tag=g.key())
 
+    def _use_im2col(self, g, buf):
+        """Layers with very few input channels (the 3-channel input conv) run on the tensor
+        cores as a dense K = cin*kh*kw GEMM over gathered codes."""
+        def pow2(v):
+            return v > 0 and (v & (v - 1)) == 0
+        return (g.cin < 16 and g.cin * g.kh * g.kw <= 128 and g.split == 0 and pow2(buf.ho)
+                and pow2(buf.wo) and buf.wo <= 128 and self.igemm_impl != _lib.IMPL_SIMT)
+
+    def _igemm_im2col(self, buf, pack, o_hat, accumulate, bias, g, acc_out):
+        l = _lib.lib()
+        aq = self.act_quantizer
+        taps = g.kh * g.kw
+        if getattr(buf, 'im2col', None) is None:
+            buf.im2col = _zeros(g.batch * buf.ho * buf.wo * 128, torch.int8, buf.codes.device)
+        if pack.get('wcodes_im2col') is None:
+            # same weights read as [cout][cin*kh*kw] (PyTorch's own order): identical scales
+            gp = ConvGeom(1, g.cin * taps, g.cout, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0)
+            dev = buf.codes.device
+            wcodes = torch.empty(l.modiff_wcodes_bytes(C.byref(gp), pack['with_sum']),
+                                 dtype=torch.int8, device=dev)
+            tmp = [_zeros(2 * g.cout, dt, dev) for dt in (torch.float32, torch.float32, torch.int32)]
+            wc = self.weight.detach().contiguous()
+            _lib.call('modiff_weight_pack', wc.data_ptr(), C.byref(gp),
+                      self.weight_quantizer.n_bits, pack['with_sum'], wcodes.data_ptr(),
+                      tmp[0].data_ptr(), tmp[1].data_ptr(), tmp[2].data_ptr(), None,
+                      _lib.stream_ptr())
+            pack['wcodes_im2col'] = wcodes
+        _lib.call('modiff_im2col_codes', buf.codes.data_ptr(), buf.im2col.data_ptr(), C.byref(g),
+                  128, _lib.stream_ptr())
+        g2 = ConvGeom(g.batch, 128, g.cout, buf.ho, buf.wo, 1, 1, 1, 0, 0, 0, 0, 0)
+        _lib.call('modiff_igemm_conv',
+                  buf.im2col.data_ptr(), pack['wcodes_im2col'].data_ptr(), pack['with_sum'],
+                  buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
+                  o_hat.data_ptr(), int(accumulate), _lib.ptr(bias), C.byref(g2),
+                  int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr(),
+                  nbytes=(8 if accumulate else 4) * o_hat.numel(), tag=g.key())
+
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
+        if self._use_im2col(g, buf):
+            return self._igemm_im2col(buf, pack, o_hat, accumulate, bias, g, acc_out)
         # algorithmic bytes: o_hat read + write 8 per output element, 1 per input code, weights
         _lib.call('modiff_igemm_conv',
                   buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
@@ -416,7 +499,7 @@ class QuantModule(nn.Module):
                     self.a_hat = self._a_store
                 self._o_store = self._reuse(self._o_store, out_shape, input.device)
                 out = self._o_store
-                self._conv_fp32(input, w_kn, bias, g, out)
+                self._conv_first_step(input, pack, bias, g, out, ho_wo)
                 self.o_hat = out
             else:
                 if self.a_hat.shape != input.shape:
@@ -444,7 +527,7 @@ class QuantModule(nn.Module):
         if self.fwd_func is F.linear:
             return tuple(input.shape[:-1]) + (g.cout,)
         if self.fwd_func is F.conv1d:
-            return (g.batch, g.cout, ho_wo[1])
+            return (g.batch, g.cout, ho_wo[0] * ho_wo[1])
         return (g.batch, g.cout, ho_wo[0], ho_wo[1])
 
     # ------------------------------------------------------------------ flag setters

@@ -4,7 +4,8 @@ import logging
 
 import torch.nn as nn
 
-from .quant_block import get_specials, BaseQuantBlock, QuantAttnBlock
+from .quant_block import (get_specials, BaseQuantBlock, QuantAttnBlock, QuantQKMatMul,
+                          QuantSMVMatMul)
 from .quant_layer import QuantModule, StraightThrough
 
 logger = logging.getLogger(__name__)
@@ -46,6 +47,10 @@ class QuantModel(nn.Module):
             if special is not None and not isinstance(child, BaseQuantBlock):
                 if special is QuantAttnBlock:
                     setattr(module, name, special(child, act_quant_params, sm_abit=self.sm_abit))
+                elif special is QuantSMVMatMul:
+                    setattr(module, name, special(act_quant_params, sm_abit=self.sm_abit))
+                elif special is QuantQKMatMul:
+                    setattr(module, name, special(act_quant_params))
                 else:
                     setattr(module, name, special(child, act_quant_params))
             else:

@@ -153,7 +153,18 @@ def resnet_forward(blk, x, temb, split=0):
 
     src1 = ops.ActSource(xa, xb, norm=blk.norm1, silu=True)
     h = blk.conv1(src1 if quant else src1.materialize())
-    tb = blk.temb_proj(ops.silu(temb))
+    # every block projects the same swish(temb): computed once per step by the model, and the
+    # projections share one quantisation of it (the first one to run owns the codes)
+    ta = getattr(temb, "_modiff_act", None)
+    if ta is None:
+        ta = ops.silu(temb)
+    owner = getattr(temb, "_modiff_owner", None)
+    if owner is not None and owner is not blk.temb_proj and _is_quant(blk.temb_proj):
+        tb = blk.temb_proj.forward_shared(owner, ta)
+    else:
+        tb = blk.temb_proj(ta)
+        if _is_quant(blk.temb_proj) and hasattr(temb, "_modiff_act"):
+            temb._modiff_owner = blk.temb_proj
     src2 = ops.ActSource(h, chan_bias=tb, norm=blk.norm2, silu=True)
     if quant:
         h = blk.conv2(src2)
@@ -299,6 +310,8 @@ class Model(nn.Module):
         temb = self.temb.dense[0](temb)
         temb = nonlinearity(temb)
         temb = self.temb.dense[1](temb)
+        temb._modiff_act = ops.silu(temb)      # shared by all residual blocks of this step
+        temb._modiff_owner = None
 
         hs = [self.conv_in(x)]
         for lvl in range(self.num_resolutions):

@@ -1,0 +1,211 @@
+"""Restatement of the latent-diffusion UNet forward with quantised blocks and of the latent DDIM
+sampler, as functional torch-CPU code over a state dict (test infrastructure only).
+
+Follows ldm/modules/diffusionmodules/openaimodel.py:447-782 (UNetModel), :163-278 (ResBlock),
+:281-327 (AttentionBlock), :373-406 (QKVAttentionLegacy); qdiff/quant_block.py:83-111
+(QuantResBlock._forward), :114-151 (the attention matmuls stay in floating point);
+ldm/modules/diffusionmodules/util.py:21-74, 151-171; ldm/models/diffusion/ddim.py:25-54, 184-234.
+"""
+import math
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .quant_module import OracleQuantModule
+
+
+def ldm_timestep_embedding(t, dim):
+    """util.py:151-171: cos | sin."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(10000) * torch.arange(start=0, end=half, dtype=torch.float32) / half)
+    args = t[:, None].float() * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+def unet_plan(cfg):
+    """Block structure of UNetModel.__init__ (openaimodel.py:549-720) as lists of
+    ('res', kind) / ('attn',) entries per TimestepEmbedSequential."""
+    mc, mult_list = cfg["model_channels"], cfg["channel_mult"]
+    nrb, ar = cfg["num_res_blocks"], cfg["attention_resolutions"]
+    inputs = [[("conv",)]]
+    ds = 1
+    for level, _ in enumerate(mult_list):
+        for _ in range(nrb):
+            layers = [("res", "plain")]
+            if ds in ar:
+                layers.append(("attn",))
+            inputs.append(layers)
+        if level != len(mult_list) - 1:
+            inputs.append([("res", "down")])
+            ds *= 2
+    middle = [("res", "plain"), ("attn",), ("res", "plain")]
+    outputs = []
+    for level, _ in list(enumerate(mult_list))[::-1]:
+        for i in range(nrb + 1):
+            layers = [("res", "plain")]
+            if ds in ar:
+                layers.append(("attn",))
+            if level and i == nrb:
+                layers.append(("res", "up"))
+                ds //= 2
+            outputs.append(layers)
+    return inputs, middle, outputs
+
+
+class OracleLDMUNet:
+    def __init__(self, state, cfg, w_bits=8, a_bits=8, a_sym=True, modulate=True, split=False,
+                 quant=True):
+        self.state, self.cfg, self.split = state, cfg, split
+        self.layers = {}
+        for name, w in state.items():
+            if not name.endswith(".weight") or w.dim() < 2:
+                continue
+            base = name[:-len(".weight")]
+            pad = 1 if (w.dim() == 4 and w.shape[-1] == 3) else 0
+            m = OracleQuantModule(w, state.get(base + ".bias"), 1, pad, w_bits, a_bits, a_sym,
+                                  False, modulate)
+            m.use_weight_quant = m.use_act_quant = quant
+            if not quant:
+                m.modulate = False
+            self.layers[base] = m
+        self.plan = unet_plan(cfg)
+
+    def reset_cache(self):
+        for m in self.layers.values():
+            m.reset_cache()
+
+    def _gn(self, x, base):
+        """GroupNorm32(32, C), eps 1e-5 (util.py:199-216)."""
+        return F.group_norm(x.float(), 32, self.state[base + ".weight"], self.state[base + ".bias"],
+                            1e-5)
+
+    def _res(self, base, kind, x, emb, split=0):
+        """qdiff/quant_block.py:83-111."""
+        L = self.layers
+        h = F.silu(self._gn(x, base + ".in_layers.0"))
+        if kind == "down":
+            h = F.avg_pool2d(h, 2, 2)
+            x = F.avg_pool2d(x, 2, 2)
+        elif kind == "up":
+            h = F.interpolate(h, scale_factor=2, mode="nearest")
+            x = F.interpolate(x, scale_factor=2, mode="nearest")
+        h = L[base + ".in_layers.2"].forward(h)
+        emb_out = L[base + ".emb_layers.1"].forward(F.silu(emb))[..., None, None]
+        if self.cfg.get("use_scale_shift_norm", False):
+            scale, shift = torch.chunk(emb_out, 2, dim=1)
+            h = self._gn(h, base + ".out_layers.0") * (1 + scale) + shift
+            h = F.silu(h)
+        else:
+            h = h + emb_out
+            h = F.silu(self._gn(h, base + ".out_layers.0"))
+        h = L[base + ".out_layers.3"].forward(h)
+        if (base + ".skip_connection") in L:
+            x = L[base + ".skip_connection"].forward(x, split=split)
+        return x + h
+
+    def _attn(self, base, x):
+        """openaimodel.py:321-327, 384-406."""
+        L = self.layers
+        b, c = x.shape[0], x.shape[1]
+        spatial = x.shape[2:]
+        x3 = x.reshape(b, c, -1)
+        qkv = self._conv1d(base + ".qkv", self._gn(x3, base + ".norm"))
+        heads = self.cfg["num_heads"]
+        bs, width, length = qkv.shape
+        ch = width // (3 * heads)
+        q, k, v = qkv.reshape(bs * heads, ch * 3, length).split(ch, dim=1)
+        scale = 1 / math.sqrt(math.sqrt(ch))
+        weight = torch.einsum("bct,bcs->bts", q * scale, k * scale)
+        weight = torch.softmax(weight.float(), dim=-1)
+        a = torch.einsum("bts,bcs->bct", weight, v).reshape(bs, -1, length)
+        h = self._conv1d(base + ".proj_out", a)
+        return (x3 + h).reshape(b, c, *spatial)
+
+    def _conv1d(self, base, x):
+        """A k=1 Conv1d QuantModule: F.conv1d on [B, C, T]."""
+        m = self.layers[base]
+        w2 = m.weight
+        if w2.dim() == 3:
+            # run the same QuantModule arithmetic through conv2d on [B, C, T, 1]
+            if not hasattr(m, "_as4d"):
+                m.weight = w2.unsqueeze(-1)
+                m._wq = {}
+                m._as4d = True
+        return m.forward(x.unsqueeze(-1)).squeeze(-1)
+
+    def _seq(self, prefix, layers, h, emb, split=0):
+        for j, layer in enumerate(layers):
+            base = f"{prefix}.{j}"
+            if layer[0] == "conv":
+                h = self.layers[base].forward(h)
+            elif layer[0] == "res":
+                h = self._res(base, layer[1], h, emb, split if j == 0 else 0)
+            else:
+                h = self._attn(base, h)
+        return h
+
+    def forward(self, x, t):
+        """openaimodel.py:745-782."""
+        L = self.layers
+        inputs, middle, outputs = self.plan
+        emb = ldm_timestep_embedding(t, self.cfg["model_channels"])
+        emb = L["time_embed.0"].forward(emb)
+        emb = F.silu(emb)
+        emb = L["time_embed.2"].forward(emb)
+        hs = []
+        h = x
+        for i, layers in enumerate(inputs):
+            h = self._seq(f"input_blocks.{i}", layers, h, emb)
+            hs.append(h)
+        h = self._seq("middle_block", middle, h, emb)
+        for i, layers in enumerate(outputs):
+            split = h.shape[1] if self.split else 0
+            h = torch.cat([h, hs.pop()], dim=1)
+            h = self._seq(f"output_blocks.{i}", layers, h, emb, split)
+        h = F.silu(self._gn(h, "out.0"))
+        return L["out.2"].forward(h)
+
+
+# ---------------------------------------------------------------- latent DDIM
+def ldm_schedule(linear_start, linear_end, n_timestep=1000):
+    """alphas_cumprod as LatentDiffusion.register_schedule keeps it (ddpm.py:118-139): float64
+    numpy, cast to float32."""
+    betas = (torch.linspace(linear_start ** 0.5, linear_end ** 0.5, n_timestep,
+                            dtype=torch.float64) ** 2).numpy()
+    return torch.tensor(np.cumprod(1.0 - betas, axis=0), dtype=torch.float32)
+
+
+def ddim_parameters(alphas_cumprod, steps, n_timestep=1000):
+    """util.py:44-74 with the 'uniform' discretisation (c = T // S, +1 offset), eta = 0."""
+    c = n_timestep // steps
+    ts = np.asarray(list(range(0, n_timestep, c))) + 1
+    alphas = alphas_cumprod[ts]
+    alphas_prev = np.asarray([alphas_cumprod[0]] + alphas_cumprod[ts[:-1]].tolist())
+    return ts, alphas, alphas_prev
+
+
+@torch.no_grad()
+def latent_ddim_sample(x, model_fn, alphas_cumprod, steps, max_evals=None, on_step=None):
+    """ldm/models/diffusion/ddim.py:117-234 with eta = 0, no guidance.  `max_evals` stops early
+    (for bounded tests)."""
+    ts, alphas, alphas_prev = ddim_parameters(alphas_cumprod, steps)
+    sqrt_one_minus = np.sqrt(1. - alphas)
+    b = x.shape[0]
+    img = x
+    total = ts.shape[0]
+    for i, step in enumerate(np.flip(ts)):
+        if max_evals is not None and i >= max_evals:
+            break
+        index = total - i - 1
+        t = torch.full((b,), int(step), dtype=torch.long)
+        e_t = model_fn(img, t)
+        a_t = torch.full((b, 1, 1, 1), float(alphas[index]))
+        a_prev = torch.full((b, 1, 1, 1), float(alphas_prev[index]))
+        sqrt_one_minus_at = torch.full((b, 1, 1, 1), float(sqrt_one_minus[index]))
+        pred_x0 = (img - sqrt_one_minus_at * e_t) / a_t.sqrt()
+        dir_xt = (1. - a_prev).sqrt() * e_t
+        img = a_prev.sqrt() * pred_x0 + dir_xt
+        if on_step is not None:
+            on_step(i, e_t, img)
+    return img

@@ -116,3 +116,22 @@ def unet_sequence(c):
     """Quad skip over 1000 timesteps (scripts/sample_diffusion_ddim.py:377-384)."""
     seq = np.linspace(0, np.sqrt(1000 * 0.8), c["steps"]) ** 2
     return [int(s) for s in list(seq)]
+
+
+# ---------------------------------------------------------------- latent UNet (LSUN-churches kl-8)
+LDM_CONFIG = dict(
+    image_size=32, in_channels=4, out_channels=4, model_channels=192,
+    attention_resolutions=[1, 2, 4, 8], num_res_blocks=2, channel_mult=[1, 2, 2, 4, 4],
+    num_heads=8, use_scale_shift_norm=True, resblock_updown=True)
+LDM_SCHEDULE = dict(linear_start=0.0015, linear_end=0.0155)   # lsun_churches-ldm-kl-8.yaml:5-6
+
+LDM_CASES = [
+    # first `evals` UNet evaluations of the 500 that `-c 400` gives (uniform, c = 1000 // 400)
+    dict(name="ldm_w8a8_b2", w_bits=8, a_bits=8, batch=2, ddim_steps=400, evals=6, noise_seed=11,
+         zero_seed=1234),
+]
+
+
+def ldm_noise(c):
+    g = torch.Generator().manual_seed(c["noise_seed"])
+    return torch.randn(c["batch"], 4, 32, 32, generator=g)

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer]
+    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer|ldm]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -163,9 +163,42 @@ def gen_unet():
     print("unet.npz", len(out))
 
 
+def gen_ldm():
+    """Latent UNet (LSUN-churches kl-8 shapes, random init seed 0, zero-initialised tensors redrawn
+    by modiff_b200.ldm_unet.rerandomize_zero_tensors), reference QuantModel with --a_sym."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from modiff_b200.ldm_unet import rerandomize_zero_tensors
+    from oracle.ldm import ldm_schedule, latent_ddim_sample
+    from ldm.modules.diffusionmodules.openaimodel import UNetModel as RefUNet
+    out = {}
+    ac = ldm_schedule(**cases.LDM_SCHEDULE)
+    for c in cases.LDM_CASES:
+        t0 = time.time()
+        torch.manual_seed(0)
+        model = RefUNet(**cases.LDM_CONFIG).eval()
+        rerandomize_zero_tensors(model, seed=c["zero_seed"])
+        wq, aq = cases.quant_params(c)
+        qnn = RefQuantModel(model=model, weight_quant_params=wq, act_quant_params=aq, sm_abit=8,
+                            modulate=True).eval()
+        qnn.set_quant_state(True, True)
+        qnn.set_grad_ckpt(False)
+        qnn.reset_cache()
+        eps = []
+        final = latent_ddim_sample(cases.ldm_noise(c), lambda a, t: qnn(a, t), ac, c["ddim_steps"],
+                                   max_evals=c["evals"],
+                                   on_step=lambda i, e, im: eps.append(e.numpy().copy()))
+        out[c["name"] + "/final"] = final.numpy().copy()
+        for i, e in enumerate(eps):
+            out[f"{c['name']}/eps{i}"] = e
+        print(c["name"], f"{time.time() - t0:.1f}s", float(final.std()))
+    np.savez_compressed(os.path.join(HERE, "ldm.npz"), **out)
+    print("ldm.npz", len(out))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
-    todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet)
+    todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
+                ldm=gen_ldm)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()

@@ -1,0 +1,94 @@
+"""Latent UNet (LSUN-churches kl-8 shapes): oracle vs the reference's fixtures (CPU) and the CUDA
+path vs the same fixtures (GPU).  W8A8 modulated, symmetric dynamic activations, random init
+seed 0 with the zero-initialised tensors redrawn by `rerandomize_zero_tensors`."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle
+from oracle.ldm import OracleLDMUNet, ldm_schedule, latent_ddim_sample
+
+GOLDEN = os.path.dirname(os.path.abspath(cases.__file__))
+
+
+@pytest.fixture(scope="module")
+def golden_ldm():
+    return np.load(os.path.join(GOLDEN, "ldm.npz"))
+
+
+def _build():
+    import modiff_b200 as m
+    torch.manual_seed(0)
+    net = m.UNetModel(**cases.LDM_CONFIG).eval()
+    m.rerandomize_zero_tensors(net, seed=cases.LDM_CASES[0]["zero_seed"])
+    return net
+
+
+def test_structure_matches_reference_counts():
+    """295 M parameters, 168 quantised layers, 21 attention blocks, 206 zero-initialised tensors
+    (the figures measured on the reference model)."""
+    import modiff_b200 as m
+    torch.manual_seed(0)
+    net = m.UNetModel(**cases.LDM_CONFIG)
+    assert sum(p.numel() for p in net.parameters()) == 294966916
+    assert m.rerandomize_zero_tensors(net) == 206
+    wq, aq = cases.quant_params(cases.LDM_CASES[0])
+    q = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True)
+    assert sum(isinstance(x, m.QuantModule) for x in q.modules()) == 168
+    assert sum(type(x).__name__ == "QuantQKMatMul" for x in q.modules()) == 21
+    assert sum(type(x).__name__ == "QuantResBlock" for x in q.modules()) == 35
+
+
+def test_ddim_schedule_rule():
+    from modiff_b200.ldm_sampler import make_ddim_timesteps
+    ts = make_ddim_timesteps("uniform", 400, 1000)
+    assert len(ts) == 500 and ts[0] == 1 and ts[-1] == 999      # c = 1000 // 400 = 2
+    assert len(make_ddim_timesteps("uniform", 50, 1000)) == 50
+
+
+def test_oracle_matches_reference(golden_ldm):
+    c = cases.LDM_CASES[0]
+    net = _build()
+    state = {k: v.detach().clone() for k, v in net.state_dict().items()}
+    o = OracleLDMUNet(state, cases.LDM_CONFIG, c["w_bits"], c["a_bits"])
+    eps = []
+    final = latent_ddim_sample(cases.ldm_noise(c), o.forward, ldm_schedule(**cases.LDM_SCHEDULE),
+                               c["ddim_steps"], max_evals=3,
+                               on_step=lambda i, e, im: eps.append(e.numpy().copy()))
+    ref0 = golden_ldm[c["name"] + "/eps0"]
+    assert np.abs(eps[0] - ref0).max() < 1e-4 * np.abs(ref0).max()
+    for i in (1, 2):
+        assert oracle.psnr(golden_ldm[f"{c['name']}/eps{i}"], eps[i]) > 40.0
+
+
+@pytest.mark.gpu
+def test_cuda_path_matches_reference(cuda, golden_ldm):
+    import modiff_b200 as m
+    c = cases.LDM_CASES[0]
+    net = _build()
+    wq, aq = cases.quant_params(c)
+    qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(cuda).eval()
+    qnn.set_quant_state(True, True)
+    qnn.set_grad_ckpt(False)
+    qnn.reset_cache()
+    sampler = m.DDIMSampler(qnn, **cases.LDM_SCHEDULE)
+    eps = []
+    final, _ = sampler.sample(c["ddim_steps"], c["batch"], (4, 32, 32), eta=0.0,
+                              x_T=cases.ldm_noise(c).to(cuda), max_evals=c["evals"],
+                              img_callback=lambda e, i: eps.append(e.clone()))
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    for i, e in enumerate(eps):
+        ref = golden_ldm[f"{c['name']}/eps{i}"]
+        err = np.abs(e.cpu().numpy() - ref).max() / np.abs(ref).max()
+        p = oracle.psnr(ref, e.cpu().numpy())
+        print(f"ldm eval {i}: max|eps-ref|/max|ref| = {err:.2e}, PSNR {p:.1f} dB")
+        if i == 0:
+            assert err < 1e-4, err       # unquantised first evaluation
+        else:
+            assert p >= 35.0, (i, p)
+    ref = golden_ldm[c["name"] + "/final"]
+    assert oracle.psnr(ref, final.cpu().numpy()) >= 40.0
