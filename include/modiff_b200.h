@@ -199,14 +199,15 @@ int modiff_conv_fp32(const float* x, const float* w_kn, const float* bias, float
  * fp32 values travel as two bf16 planes, hi = bf16(x) and lo = bf16(x - hi); the GEMM adds the
  * products hi*hi + hi*lo + lo*hi in fp32 (relative error ~1e-5). */
 
-/* fp32 NCHW [batch][cin][h][w] -> bf16 [batch][2][stride^2][hp][wp][round_up(cin,8)] in the
+/* fp32 NCHW [batch][cin][h][w] -> bf16 [batch][2][stride^2][hp][wp][max(64, round_up(cin,8))] in the
  * code-plane geometry of g (zero halo: the caller zero-fills the buffer once). */
 int64_t modiff_bf16_planes_bytes(const modiff_conv_geom* g);
 int modiff_split_bf16(const float* x, uint16_t* planes, const modiff_conv_geom* g, void* stream);
-/* x fp32 [nb][inner] -> bf16 [nb][2][inner], no layout change. */
-int modiff_split_bf16_flat(const float* x, uint16_t* out, int64_t nb, int64_t inner, void* stream);
+/* x fp32 [nb][rows][len] -> bf16 [nb][2][rows_pad][len_pad], zero padded, no layout change. */
+int modiff_split_bf16_rows(const float* x, uint16_t* out, int64_t nb, int rows, int len,
+                           int rows_pad, int len_pad, void* stream);
 /* Integer part (q - zp) of the fake-quantised weights, exact in bf16, as
- * [cout][kh*kw][round_up(cin,8)]; w_scale / w_zp come from modiff_weight_pack
+ * [cout][kh*kw][max(64, round_up(cin,8))]; w_scale / w_zp come from modiff_weight_pack
  * (qdiff/quant_layer.py:345-351). */
 int64_t modiff_weights_bf16_bytes(const modiff_conv_geom* g);
 int modiff_weights_bf16(const float* w, const float* w_scale, const float* w_zp, uint16_t* out,
@@ -223,7 +224,7 @@ typedef struct modiff_gemm_bf16_desc {
   int32_t b_batched;      /* != 0: one B per image (attention), tiles never mix images */
   int32_t kb;             /* K stride per filter tap of B, elements (multiple of 8, >= cin) */
   float scale;            /* uniform factor */
-  int32_t reserved;
+  int32_t b_rows;         /* physical rows of B per part (>= cout rounded up to 16); 0 = cout */
 } modiff_gemm_bf16_desc;
 
 /* out = scale * col_scale[c] * (A conv B) + bias[c]  on tcgen05 kind::f16, fp32 accumulation.
@@ -239,9 +240,10 @@ int modiff_attention_small(const float* q, const float* k, const float* v, float
                            int c, int t, int tk, float scale, void* stream);
 
 /* Softmax over keys of s fp32 [batch][tk][tq] (the layout modiff_gemm_bf16 writes when the keys
- * are its output columns) -> probabilities as split bf16 planes p [batch][2][tq][tk]
- * (softmax of qdiff/quant_block.py:353, ddim/models/diffusion.py:185). */
-int modiff_softmax_split(const float* s, uint16_t* p, int batch, int tk, int tq, void* stream);
+ * are its output columns) -> probabilities as split bf16 planes p [batch][2][tq][tk_pad], zero
+ * beyond tk (softmax of qdiff/quant_block.py:197, 353, ddim/models/diffusion.py:185). */
+int modiff_softmax_split(const float* s, uint16_t* p, int batch, int tk, int tq, int tk_pad,
+                         void* stream);
 
 /* Stand-alone fake quantiser returning the dequantised tensor
  * (UniformAffineQuantizer.forward, qdiff/quant_layer.py:70-111; scale rules

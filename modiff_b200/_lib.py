@@ -46,7 +46,7 @@ class GemmBf16Desc(C.Structure):
     _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("col_scale", C.c_void_p),
                 ("bias", C.c_void_p), ("out", C.c_void_p), ("a_parts", C.c_int32),
                 ("b_parts", C.c_int32), ("b_batched", C.c_int32), ("kb", C.c_int32),
-                ("scale", C.c_float), ("reserved", C.c_int32)]
+                ("scale", C.c_float), ("b_rows", C.c_int32)]
 
 
 _P = C.c_void_p
@@ -74,11 +74,11 @@ SIGNATURES = {
     "modiff_conv_fp32": (C.c_int, [_P, _P, _P, _P, _G, _P]),
     "modiff_bf16_planes_bytes": (C.c_int64, [_G]),
     "modiff_split_bf16": (C.c_int, [_P, _P, _G, _P]),
-    "modiff_split_bf16_flat": (C.c_int, [_P, _P, C.c_int64, C.c_int64, _P]),
+    "modiff_split_bf16_rows": (C.c_int, [_P, _P, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_weights_bf16_bytes": (C.c_int64, [_G]),
     "modiff_weights_bf16": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, _P]),
     "modiff_gemm_bf16": (C.c_int, [C.POINTER(GemmBf16Desc), _G, _P]),
-    "modiff_softmax_split": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "modiff_softmax_split": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_attention_small": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int,
                                          C.c_float, _P]),
     "modiff_fake_quant": (C.c_int, [_P, _P, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int,
@@ -120,7 +120,7 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_flat": 1,
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
     "modiff_weights_bf16": 1, "modiff_gemm_bf16": 1, "modiff_softmax_split": 1, "modiff_attention_small": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,

@@ -340,17 +340,21 @@ split_bf16_planes_kernel(const float* __restrict__ x, uint16_t* __restrict__ out
   }
 }
 
-// x[nb][inner] fp32 -> out[nb][2][inner] bf16 (no layout change).
-__global__ void split_bf16_flat_kernel(const float* __restrict__ x, uint16_t* __restrict__ out,
-                                       int64_t nb, int64_t inner) {
-  const int64_t total = nb * inner;
+// x[nb][rows][len] fp32 -> out[nb][2][rows_pad][len_pad] bf16 (zero padding, no transposition).
+__global__ void split_bf16_rows_kernel(const float* __restrict__ x, uint16_t* __restrict__ out,
+                                       int64_t nb, int rows, int len, int rows_pad, int len_pad) {
+  const int64_t total = nb * rows_pad * len_pad;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int64_t b = i / inner, r = i % inner;
-    const float v = __ldg(x + i);
+    const int c = (int)(i % len_pad);
+    const int r = (int)((i / len_pad) % rows_pad);
+    const int64_t b = i / ((int64_t)len_pad * rows_pad);
+    float v = 0.0f;
+    if (r < rows && c < len) v = __ldg(x + (b * rows + r) * len + c);
     const uint16_t h = bf16_rn(v);
-    out[(b * 2) * inner + r] = h;
-    out[(b * 2 + 1) * inner + r] = bf16_rn(v - bf16_to_f(h));
+    const int64_t o = ((b * 2) * rows_pad + r) * len_pad + c;
+    out[o] = h;
+    out[o + (int64_t)rows_pad * len_pad] = bf16_rn(v - bf16_to_f(h));
   }
 }
 
@@ -359,7 +363,8 @@ __global__ void split_bf16_flat_kernel(const float* __restrict__ x, uint16_t* __
 // operand of the second attention GEMM (qdiff/quant_block.py:353-358).
 constexpr int kSmQ = 32, kSmKeys = 256;
 __global__ void __launch_bounds__(256)
-softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int tk, int tq) {
+softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int tk, int tq,
+                     int tk_pad) {
   __shared__ float red[8][kSmQ];
   __shared__ uint16_t stage[2][kSmQ][kSmKeys + 8];
   const int b = blockIdx.y;
@@ -384,21 +389,21 @@ softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int 
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum += red[i][q];
   const float inv = 1.0f / sum;
-  for (int k0 = 0; k0 < tk; k0 += kSmKeys) {
+  for (int k0 = 0; k0 < tk_pad; k0 += kSmKeys) {
     __syncthreads();
-    for (int k = kg; k < kSmKeys && k0 + k < tk; k += 8) {
-      const float pv = qv ? expf(__ldg(sb + (size_t)(k0 + k) * tq) - mx) * inv : 0.0f;
+    for (int k = kg; k < kSmKeys && k0 + k < tk_pad; k += 8) {
+      const float pv = (qv && k0 + k < tk) ? expf(__ldg(sb + (size_t)(k0 + k) * tq) - mx) * inv : 0.0f;
       const uint16_t h = bf16_rn(pv);
       stage[0][q][k] = h;
       stage[1][q][k] = bf16_rn(pv - bf16_to_f(h));
     }
     __syncthreads();
     // each warp writes whole query rows: contiguous keys
-    const int nk = min(kSmKeys, tk - k0);
+    const int nk = min(kSmKeys, tk_pad - k0);
     for (int r = kg; r < kSmQ; r += 8) {
       if (q0 + r >= tq) continue;
       for (int part = 0; part < 2; ++part) {
-        uint16_t* dst = p + (((size_t)b * 2 + part) * tq + q0 + r) * tk + k0;
+        uint16_t* dst = p + (((size_t)b * 2 + part) * tq + q0 + r) * tk_pad + k0;
         for (int k = q; k < nk; k += 32) dst[k] = stage[part][r][k];
       }
     }
@@ -433,7 +438,7 @@ int read_device_status_bf16(int* status, int reset) { return read_status_this_un
 
 namespace {
 inline bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
-inline int bf16_cp(int cin) { return round_up(cin, 8); }
+inline int bf16_cp(int cin) { return cin < 64 ? 64 : round_up(cin, 8); }   // >= one K chunk
 }  // namespace
 
 }  // namespace modiff
@@ -470,13 +475,15 @@ extern "C" int modiff_split_bf16(const float* x, uint16_t* planes, const modiff_
   return MODIFF_OK;
 }
 
-extern "C" int modiff_split_bf16_flat(const float* x, uint16_t* out, int64_t nb, int64_t inner,
-                                      void* stream) {
-  MODIFF_CHECK_ARG(x && out && nb > 0 && inner > 0, "bad argument");
-  int64_t blocks = ceil_div64(nb * inner, 256);
+extern "C" int modiff_split_bf16_rows(const float* x, uint16_t* out, int64_t nb, int rows, int len,
+                                      int rows_pad, int len_pad, void* stream) {
+  MODIFF_CHECK_ARG(x && out && nb > 0 && rows > 0 && len > 0 && rows_pad >= rows && len_pad >= len,
+                   "bad argument");
+  int64_t blocks = ceil_div64(nb * rows_pad * len_pad, 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  split_bf16_flat_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(x, out, nb, inner);
-  MODIFF_LAUNCH_CHECK("split_bf16_flat_kernel");
+  split_bf16_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(x, out, nb, rows, len,
+                                                                       rows_pad, len_pad);
+  MODIFF_LAUNCH_CHECK("split_bf16_rows_kernel");
   return MODIFF_OK;
 }
 
@@ -497,11 +504,11 @@ extern "C" int modiff_weights_bf16(const float* w, const float* w_scale, const f
 }
 
 extern "C" int modiff_softmax_split(const float* s, uint16_t* p, int batch, int tk, int tq,
-                                    void* stream) {
-  MODIFF_CHECK_ARG(s && p && batch > 0 && tk > 0 && tq > 0, "bad argument");
+                                    int tk_pad, void* stream) {
+  MODIFF_CHECK_ARG(s && p && batch > 0 && tk > 0 && tq > 0 && tk_pad >= tk, "bad argument");
   MODIFF_CHECK_ARG(batch <= 65535, "batch*heads %d exceeds the grid limit 65535", batch);
   dim3 grid(ceil_div(tq, kSmQ), batch);
-  softmax_split_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(s, p, tk, tq);
+  softmax_split_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(s, p, tk, tq, tk_pad);
   MODIFF_LAUNCH_CHECK("softmax_split_kernel");
   return MODIFF_OK;
 }
@@ -516,11 +523,12 @@ extern "C" int modiff_gemm_bf16(const modiff_gemm_bf16_desc* desc, const modiff_
                    "operand parts must be 1 or 2");
   Derived d = derive(*g);
   const int cp = bf16_cp(g->cin);
-  if (g->cin < 64 || g->cin % 8 || g->cout < 16 || !pow2(d.wo) || !pow2(d.ho) || d.wo > 128 ||
+  const int b_rows = desc->b_rows > 0 ? desc->b_rows : g->cout;
+  if (g->cin < 8 || g->cin % 8 || g->cout < 16 || b_rows < (g->cout >= 128 ? g->cout : round_up(g->cout, 16)) || !pow2(d.wo) || !pow2(d.ho) || d.wo > 128 ||
       g->split % 64 || g->kh > 7 || g->kw > 7 || desc->kb % 8 || desc->kb < g->cin)
     return set_error(MODIFF_ERR_UNSUPPORTED,
-                     "bf16 tensor-core path needs cin >= 64 (multiple of 8), cout >= 16, power-of-two "
-                     "output sizes <= 128, split %% 64 == 0");
+                     "bf16 tensor-core path needs cin a multiple of 8, cout >= 16 (B rows padded to a "
+                     "multiple of 16), power-of-two output sizes <= 128, split %% 64 == 0");
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
 
@@ -578,8 +586,8 @@ extern "C" int modiff_gemm_bf16(const modiff_gemm_bf16_desc* desc, const modiff_
   {
     const cuuint64_t row_b = (cuuint64_t)d.taps * p.kb * 2;
     const int zcount = (p.b_batched ? g->batch : 1) * p.b_parts;
-    cuuint64_t dims[3] = {(cuuint64_t)d.taps * p.kb, (cuuint64_t)g->cout, (cuuint64_t)zcount};
-    cuuint64_t strides[2] = {row_b, row_b * g->cout};
+    cuuint64_t dims[3] = {(cuuint64_t)d.taps * p.kb, (cuuint64_t)b_rows, (cuuint64_t)zcount};
+    cuuint64_t strides[2] = {row_b, row_b * b_rows};
     cuuint32_t box[3] = {(cuuint32_t)kChunkElems, (cuuint32_t)p.umma_n, 1u};
     cuuint32_t estr[3] = {1, 1, 1};
     p.b_bytes = p.umma_n * kChunkBytes;

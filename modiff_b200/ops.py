@@ -274,21 +274,24 @@ def _attn_hw(t):
     return t // w, w
 
 
+def _up(v, m):
+    return -(-v // m) * m
+
+
 def attention(q, k, v, scale):
-    """Attention over [B, C, T] tensors (one head per batch entry), fp32-accurate
-    (qdiff/quant_block.py:344-360):
+    """Attention over channel-major tensors, one head per batch entry, fp32-accurate
+    (qdiff/quant_block.py:191-203, 344-360): q [B, C, Tq], k and v [B, C, Tk];
     out[b,:,i] = sum_j softmax_j(q[b,:,i] . k[b,:,j] * scale) v[b,:,j].
 
-    Two split-bf16 tensor-core GEMMs with a softmax between them; small or odd token counts use
-    one CUDA-core kernel."""
+    Two split-bf16 tensor-core GEMMs with a softmax between them (keys padded to a multiple of
+    64 with zero probability); small token counts use one CUDA-core kernel."""
     _req(q, k, v)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     b, c, t = q.shape
     tk = k.shape[2]
     out = torch.empty((b, c, t), dtype=torch.float32, device=q.device)
     hw = _attn_hw(t)
-    big = (hw is not None and t == tk and t >= 64 and c >= 64 and c % 8 == 0 and t % 8 == 0
-           and hw[1] <= 128)
+    big = hw is not None and t >= 64 and hw[1] <= 128 and c % 8 == 0 and c >= 8 and tk >= 16
     if not big:
         if t > 64 or tk > 64:
             raise ModiffError(f"attention with {t} x {tk} tokens, {c} channels is not covered")
@@ -298,22 +301,31 @@ def attention(q, k, v, scale):
     l = _lib.lib()
     dev = q.device
     h, w = hw
-    gq = _lib.ConvGeom(b, c, t, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
-    nplane = l.modiff_bf16_planes_bytes(C.byref(gq)) // 2
-    qp = torch.empty(nplane, dtype=torch.int16, device=dev)
-    kp = torch.empty(nplane, dtype=torch.int16, device=dev)
+    cp = max(64, _up(c, 8))                 # channels per token in the bf16 planes
+    tkp = _up(tk, 64)                       # keys padded: rows of K, K-extent of P and V
+    crow = c if c >= 128 else _up(c, 16)    # rows of V the second GEMM's tile reads
+    # GEMM1: S[image][key][query] = scale * q . k
+    gq = _lib.ConvGeom(b, c, tk, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
+    qp = torch.empty(l.modiff_bf16_planes_bytes(C.byref(gq)) // 2, dtype=torch.int16, device=dev)
     _lib.call('modiff_split_bf16', q.data_ptr(), qp.data_ptr(), C.byref(gq), _lib.stream_ptr())
-    _lib.call('modiff_split_bf16', k.data_ptr(), kp.data_ptr(), C.byref(gq), _lib.stream_ptr())
-    s = torch.empty((b, t, t), dtype=torch.float32, device=dev)          # [image][key][query]
-    d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, c,
-                           float(scale), 0)
+    gk = _lib.ConvGeom(b, c, tk, 1, tkp, 1, 1, 1, 0, 0, 0, 0, 0)     # keys as a 1 x tkp row
+    kp = torch.zeros(b * 2 * tkp * cp, dtype=torch.int16, device=dev) if tkp != tk else \
+        torch.empty(b * 2 * tkp * cp, dtype=torch.int16, device=dev)
+    gk_src = _lib.ConvGeom(b, c, tk, 1, tk, 1, 1, 1, 0, 0, 0, tkp - tk, 0)  # right pad -> tkp
+    _lib.call('modiff_split_bf16', k.data_ptr(), kp.data_ptr(), C.byref(gk_src), _lib.stream_ptr())
+    s = torch.empty((b, tk, t), dtype=torch.float32, device=dev)
+    d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, cp,
+                           float(scale), tkp)
     _lib.call('modiff_gemm_bf16', C.byref(d1), C.byref(gq), _lib.stream_ptr())
-    pp = torch.empty(b * 2 * t * t, dtype=torch.int16, device=dev)      # [image][2][query][key]
-    _lib.call('modiff_softmax_split', s.data_ptr(), pp.data_ptr(), b, t, t, _lib.stream_ptr())
-    vp = torch.empty(b * 2 * c * t, dtype=torch.int16, device=dev)      # [image][2][c][key]
-    _lib.call('modiff_split_bf16_flat', v.data_ptr(), vp.data_ptr(), b, c * t, _lib.stream_ptr())
-    gv = _lib.ConvGeom(b, t, c, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
-    d2 = _lib.GemmBf16Desc(pp.data_ptr(), vp.data_ptr(), None, None, out.data_ptr(), 2, 2, 1, t,
-                           1.0, 0)
+    # softmax over keys -> P[image][2][query][tkp]
+    pp = torch.empty(b * 2 * t * tkp, dtype=torch.int16, device=dev)
+    _lib.call('modiff_softmax_split', s.data_ptr(), pp.data_ptr(), b, tk, t, tkp, _lib.stream_ptr())
+    # GEMM2: out[image][c][query] = P . v
+    vp = torch.empty(b * 2 * crow * tkp, dtype=torch.int16, device=dev)
+    _lib.call('modiff_split_bf16_rows', v.data_ptr(), vp.data_ptr(), b, c, tk, crow, tkp,
+              _lib.stream_ptr())
+    gv = _lib.ConvGeom(b, tkp, c, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
+    d2 = _lib.GemmBf16Desc(pp.data_ptr(), vp.data_ptr(), None, None, out.data_ptr(), 2, 2, 1, tkp,
+                           1.0, crow)
     _lib.call('modiff_gemm_bf16', C.byref(d2), C.byref(gv), _lib.stream_ptr())
     return out

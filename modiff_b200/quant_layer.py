@@ -343,7 +343,7 @@ class QuantModule(nn.Module):
                              device=dev)
         _lib.call('modiff_split_bf16', x.data_ptr(), planes.data_ptr(), C.byref(g),
                   _lib.stream_ptr())
-        kb = -(-g.cin // 8) * 8
+        kb = max(64, -(-g.cin // 8) * 8)
         desc = _lib.GemmBf16Desc(planes.data_ptr(), pack['w_bf16'].data_ptr(),
                                  pack['w_scale'].data_ptr(), _lib.ptr(bias), out.data_ptr(),
                                  2, 1, 0, kb, 1.0, 0)

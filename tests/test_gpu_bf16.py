@@ -51,7 +51,7 @@ def test_first_step_conv_on_tensor_cores(cuda, case, bits):
     L.check(l.modiff_split_bf16(x_d.data_ptr(), planes.data_ptr(), C.byref(g), L.stream_ptr()))
     ho, wo = L.out_hw(g)
     out = torch.full((b, cout, ho, wo), float("nan"), device=cuda)
-    kb = -(-cin // 8) * 8
+    kb = max(64, -(-cin // 8) * 8)
     desc = L.GemmBf16Desc(planes.data_ptr(), wb.data_ptr(), ws.data_ptr(), bias_d.data_ptr(),
                           out.data_ptr(), 2, 1, 0, kb, 1.0, 0)
     L.check(l.modiff_gemm_bf16(C.byref(desc), C.byref(g), L.stream_ptr()))
@@ -65,12 +65,14 @@ def test_first_step_conv_on_tensor_cores(cuda, case, bits):
     assert err < 1e-4, err
 
 
-@pytest.mark.parametrize("b,c,t", [(3, 256, 256), (2, 64, 64), (5, 256, 16), (2, 128, 1024)])
-def test_attention_matches_float64(cuda, b, c, t):
+@pytest.mark.parametrize("b,c,t,tk", [(3, 256, 256, 256), (2, 64, 64, 64), (5, 256, 16, 16),
+                                      (2, 128, 1024, 1024), (16, 24, 1024, 1024), (8, 40, 256, 77),
+                                      (4, 160, 64, 77), (8, 96, 4, 4)])
+def test_attention_matches_float64(cuda, b, c, t, tk):
     from modiff_b200 import ops
     import modiff_b200 as m
     torch.manual_seed(22)
-    q, k, v = torch.randn(b, c, t), torch.randn(b, c, t), torch.randn(b, c, t)
+    q, k, v = torch.randn(b, c, t), torch.randn(b, c, tk), torch.randn(b, c, tk)
     scale = float(c) ** -0.5
     w_ = torch.softmax(torch.bmm(q.double().permute(0, 2, 1), k.double()) * scale, dim=2)
     exp = torch.bmm(v.double(), w_.permute(0, 2, 1))
