@@ -273,6 +273,16 @@ int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float*
                           const float* beta, int batch, int c, int hw, int groups, float eps,
                           int silu, void* stream);
 
+/* LayerNorm over the last dimension of x [rows][c] (nn.LayerNorm of
+ * ldm/modules/attention.py:229-231). */
+int modiff_layernorm(const float* x, float* y, const float* gamma, const float* beta, int64_t rows,
+                     int c, float eps, void* stream);
+/* GEGLU gate: y[rows][n] = x[:, :n] * gelu(x[:, n:]), x [rows][2n] (ldm/modules/attention.py:37-44). */
+int modiff_geglu(const float* x, float* y, int64_t rows, int n, void* stream);
+/* Batched transpose x [batch][r][c] -> y [batch][c][r] (the b c (h w) <-> b (h w) c rearranges of
+ * ldm/modules/attention.py:276-280 and the head split of :176). */
+int modiff_transpose(const float* x, float* y, int batch, int r, int c, void* stream);
+
 /* y = x * sigmoid(x)  (ddim/models/diffusion.py:27-29). */
 int modiff_silu(const float* x, float* y, int64_t n, void* stream);
 

@@ -2,7 +2,9 @@
 behind qdiff's Python API.  See include/modiff_b200.h for the C ABI the modules call into."""
 from ._lib import ModiffError, lib, device_status
 from .quant_layer import QuantModule, UniformAffineQuantizer, StraightThrough, round_ste
-from .quant_block import BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, get_specials
+from .quant_block import (BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, QuantResBlock,
+                          QuantBasicTransformerBlock, QuantQKMatMul, QuantSMVMatMul,
+                          QuantAttentionBlock, get_specials)
 from .quant_model import QuantModel
 from .unet import Model, make_config
 from .ldm_unet import UNetModel, rerandomize_zero_tensors
@@ -13,6 +15,8 @@ from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
 __all__ = [
     "ModiffError", "lib", "device_status", "QuantModule", "UniformAffineQuantizer",
     "StraightThrough", "round_ste", "BaseQuantBlock", "QuantResnetBlock", "QuantAttnBlock",
+    "QuantResBlock", "QuantBasicTransformerBlock", "QuantQKMatMul", "QuantSMVMatMul",
+    "QuantAttentionBlock",
     "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
     "get_beta_schedule", "make_timestep_sequence",
 ]

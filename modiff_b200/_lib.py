@@ -87,6 +87,9 @@ SIGNATURES = {
                                         C.c_int, C.c_int, C.c_float, C.c_int, _P]),
     "modiff_avgpool2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_silu": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "modiff_layernorm": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int, C.c_float, _P]),
+    "modiff_geglu": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
+    "modiff_transpose": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_add": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_upsample2x": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "modiff_concat_c": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_int, _P]),
@@ -122,7 +125,7 @@ def lib():
 KERNELS_PER_CALL = {
     "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
     "modiff_weights_bf16": 1, "modiff_gemm_bf16": 1, "modiff_softmax_split": 1, "modiff_attention_small": 1,
-    "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_add": 1,
+    "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_layernorm": 1, "modiff_geglu": 1, "modiff_transpose": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
     "modiff_ddim_step": 1, "modiff_cfg_combine": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
     "modiff_quantize_static": 1,

@@ -164,6 +164,56 @@ attention_small_kernel(const float* __restrict__ q, const float* __restrict__ k,
   }
 }
 
+// LayerNorm over the last dimension: one warp per row (ldm/modules/attention.py:229-231).
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ gamma,
+                 const float* __restrict__ beta, int64_t rows, int c, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* xr = x + row * c;
+  float s = 0.0f;
+  for (int i = lane; i < c; i += 32) s += xr[i];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  const float mean = s / (float)c;
+  float q = 0.0f;
+  for (int i = lane; i < c; i += 32) { const float d = xr[i] - mean; q += d * d; }
+  for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+  const float rstd = 1.0f / sqrtf(q / (float)c + eps);
+  float* yr = y + row * c;
+  for (int i = lane; i < c; i += 32) yr[i] = fmaf((xr[i] - mean) * rstd, gamma[i], beta[i]);
+}
+
+// GEGLU: y[r][j] = x[r][j] * gelu(x[r][n + j]), exact (erf) gelu (ldm/modules/attention.py:37-44).
+__global__ void geglu_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int n) {
+  const int64_t total = rows * n;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int64_t r = i / n;
+    const int j = (int)(i % n);
+    const float a = x[r * 2 * n + j], g = x[r * 2 * n + n + j];
+    y[i] = a * (0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)));
+  }
+}
+
+// Batched 2-D transpose x[b][r][c] -> y[b][c][r] through a padded shared-memory tile.
+__global__ void transpose_kernel(const float* __restrict__ x, float* __restrict__ y, int r, int c) {
+  __shared__ float tile[32][33];
+  const float* xb = x + (size_t)blockIdx.z * r * c;
+  float* yb = y + (size_t)blockIdx.z * r * c;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int rr = r0 + i, cc = c0 + threadIdx.x;
+    if (rr < r && cc < c) tile[i][threadIdx.x] = xb[(size_t)rr * c + cc];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int cc = c0 + i, rr = r0 + threadIdx.x;
+    if (rr < r && cc < c) yb[(size_t)cc * r + rr] = tile[threadIdx.x][i];
+  }
+}
+
 __global__ void silu_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -345,6 +395,32 @@ int modiff_attention_small(const float* q, const float* k, const float* v, float
   MODIFF_CHECK_ARG(t > 0 && tk > 0 && t <= 64 && tk <= 64, "token counts %d x %d exceed 64", t, tk);
   attention_small_kernel<<<batch, 256, 0, (cudaStream_t)stream>>>(q, k, v, out, c, t, tk, scale);
   MODIFF_LAUNCH_CHECK("attention_small_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_layernorm(const float* x, float* y, const float* gamma, const float* beta, int64_t rows,
+                     int c, float eps, void* stream) {
+  MODIFF_CHECK_ARG(x && y && gamma && beta && rows > 0 && c > 0, "bad argument");
+  const int64_t blocks = ceil_div64(rows, 8);
+  MODIFF_CHECK_ARG(blocks < (1ll << 31), "too many rows");
+  layernorm_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, y, gamma, beta, rows, c, eps);
+  MODIFF_LAUNCH_CHECK("layernorm_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_geglu(const float* x, float* y, int64_t rows, int n, void* stream) {
+  MODIFF_CHECK_ARG(x && y && rows > 0 && n > 0, "bad argument");
+  geglu_kernel<<<grid_for(rows * n, 256), 256, 0, (cudaStream_t)stream>>>(x, y, rows, n);
+  MODIFF_LAUNCH_CHECK("geglu_kernel");
+  return MODIFF_OK;
+}
+
+int modiff_transpose(const float* x, float* y, int batch, int r, int c, void* stream) {
+  MODIFF_CHECK_ARG(x && y && batch > 0 && r > 0 && c > 0 && batch <= 65535, "bad argument");
+  dim3 grid(ceil_div(c, 32), ceil_div(r, 32), batch);
+  MODIFF_CHECK_ARG(grid.y <= 65535, "too many rows");
+  transpose_kernel<<<grid, dim3(32, 8), 0, (cudaStream_t)stream>>>(x, y, r, c);
+  MODIFF_LAUNCH_CHECK("transpose_kernel");
   return MODIFF_OK;
 }
 

@@ -5,7 +5,8 @@ ldm/modules/diffusionmodules/openaimodel.py:447-782 (UNetModel with ResBlock, At
 QKVAttentionLegacy), so `torch.manual_seed(s); UNetModel(**cfg)` yields the same random-init
 weights and reference `state_dict`s load unchanged.  Covers what that config uses: 2-D
 convolutions, GroupNorm32 (eps 1e-5), scale-shift norm, up/down-sampling ResBlocks, multi-head
-legacy attention; no class conditioning, no spatial transformer (cross-attention), no fp16.
+legacy attention; and (for the SD-v1 config) the spatial transformer with cross-attention; no class conditioning,
+no fp16.
 
 The graph between the conv / linear layers runs on the library's CUDA kernels (`ops`); conv /
 linear children are torch modules until `QuantModel` swaps them for `QuantModule`s.
@@ -16,6 +17,11 @@ import torch
 import torch.nn as nn
 
 from . import ops
+
+SD_V1 = dict(
+    image_size=32, in_channels=4, out_channels=4, model_channels=320,
+    attention_resolutions=[4, 2, 1], num_res_blocks=2, channel_mult=[1, 2, 4, 4], num_heads=8,
+    use_spatial_transformer=True, transformer_depth=1, context_dim=768, legacy=False)
 
 LSUN_CHURCHES_KL8 = dict(
     image_size=32, in_channels=4, out_channels=4, model_channels=192,
@@ -65,6 +71,8 @@ class TimestepEmbedSequential(nn.Sequential, TimestepBlock):
         for layer in self:
             if isinstance(layer, TimestepBlock) or getattr(layer, "takes_emb", False):
                 x = layer(x, emb, split=split)
+            elif isinstance(layer, SpatialTransformer):
+                x = layer(x, context)
             else:
                 if isinstance(x, ops.ActSource):
                     x = x.materialize()
@@ -271,6 +279,146 @@ def attention_block_forward(blk, x):
     return ops.add(x3, h).reshape((b, c) + spatial)
 
 
+# ---------------------------------------------------------------- spatial transformer (SD)
+class GEGLU(nn.Module):
+    """ldm/modules/attention.py:37-44."""
+
+    def __init__(self, dim_in, dim_out):
+        super().__init__()
+        self.proj = nn.Linear(dim_in, dim_out * 2)
+
+    def forward(self, x):
+        return ops.geglu(self.proj(x))
+
+
+class FeedForward(nn.Module):
+    """ldm/modules/attention.py:47-64 (gated variant only)."""
+
+    def __init__(self, dim, dim_out=None, mult=4, glu=False, dropout=0.):
+        super().__init__()
+        if not glu:
+            raise NotImplementedError("only the gated feed-forward of the covered configs")
+        inner_dim = int(dim * mult)
+        dim_out = dim if dim_out is None else dim_out
+        self.net = nn.Sequential(GEGLU(dim, inner_dim), nn.Dropout(dropout),
+                                 nn.Linear(inner_dim, dim_out))
+
+    def forward(self, x):
+        return self.net[2](self.net[0](x))
+
+
+class CrossQKMatMul(nn.Module):
+    def __init__(self, scale):
+        super().__init__()
+        self.scale = scale
+
+
+class CrossSMVMatMul(nn.Module):
+    pass
+
+
+class CrossAttention(nn.Module):
+    """ldm/modules/attention.py:152-198; the quantised model runs the same arithmetic
+    (qdiff/quant_block.py:181-204): projections are quantised layers, the two attention matmuls
+    and the softmax stay in floating point."""
+
+    def __init__(self, query_dim, context_dim=None, heads=8, dim_head=64, dropout=0.):
+        super().__init__()
+        inner_dim = dim_head * heads
+        context_dim = query_dim if context_dim is None else context_dim
+        self.scale = dim_head ** -0.5
+        self.heads = heads
+        self.to_q = nn.Linear(query_dim, inner_dim, bias=False)
+        self.to_k = nn.Linear(context_dim, inner_dim, bias=False)
+        self.to_v = nn.Linear(context_dim, inner_dim, bias=False)
+        self.qk_matmul = CrossQKMatMul(self.scale)
+        self.smv_matmul = CrossSMVMatMul()
+        self.to_out = nn.Sequential(nn.Linear(inner_dim, query_dim), nn.Dropout(dropout))
+
+    def forward(self, x, context=None, mask=None):
+        return cross_attention_forward(self, x, context, mask)
+
+
+def cross_attention_forward(blk, x, context=None, mask=None):
+    if mask is not None:
+        raise NotImplementedError("attention masks are not used on the sampling path")
+    h = blk.heads
+    q = blk.to_q(x)
+    if context is None:
+        if _is_quant(blk.to_k) and _is_quant(blk.to_q) and _is_quant(blk.to_v):
+            k = blk.to_k.forward_shared(blk.to_q, x)      # self-attention: q, k, v read one tensor
+            v = blk.to_v.forward_shared(blk.to_q, x)
+        else:
+            k, v = blk.to_k(x), blk.to_v(x)
+    else:
+        k = blk.to_k(context)
+        v = blk.to_v(context) if not (_is_quant(blk.to_k) and _is_quant(blk.to_v)) \
+            else blk.to_v.forward_shared(blk.to_k, context)
+    b, n, inner = q.shape
+    d = inner // h
+    # 'b n (h d) -> (b h) d n': one transpose per tensor gives the channel-major heads
+    qt = ops.transpose_last2(q).reshape(b * h, d, n)
+    kt = ops.transpose_last2(k).reshape(b * h, d, k.shape[1])
+    vt = ops.transpose_last2(v).reshape(b * h, d, v.shape[1])
+    out = ops.attention(qt, kt, vt, blk.scale)                    # [(b h), d, n]
+    out = ops.transpose_last2(out.reshape(b, inner, n))           # b n (h d)
+    return blk.to_out[0](out)
+
+
+class BasicTransformerBlock(nn.Module):
+    """ldm/modules/attention.py:218-241."""
+
+    def __init__(self, dim, n_heads, d_head, dropout=0., context_dim=None, gated_ff=True,
+                 checkpoint=True):
+        super().__init__()
+        self.attn1 = CrossAttention(query_dim=dim, heads=n_heads, dim_head=d_head, dropout=dropout)
+        self.ff = FeedForward(dim, dropout=dropout, glu=gated_ff)
+        self.attn2 = CrossAttention(query_dim=dim, context_dim=context_dim, heads=n_heads,
+                                    dim_head=d_head, dropout=dropout)
+        self.norm1 = nn.LayerNorm(dim)
+        self.norm2 = nn.LayerNorm(dim)
+        self.norm3 = nn.LayerNorm(dim)
+        self.checkpoint = checkpoint
+
+    def forward(self, x, context=None):
+        return transformer_block_forward(self, x, context)
+
+
+def transformer_block_forward(blk, x, context=None):
+    """qdiff/quant_block.py:249-256."""
+    x = ops.add(cross_attention_forward(blk.attn1, ops.layernorm(x, blk.norm1)), x)
+    x = ops.add(cross_attention_forward(blk.attn2, ops.layernorm(x, blk.norm2), context), x)
+    x = ops.add(blk.ff(ops.layernorm(x, blk.norm3)), x)
+    return x
+
+
+class SpatialTransformer(nn.Module):
+    """ldm/modules/attention.py:244-287."""
+
+    def __init__(self, in_channels, n_heads, d_head, depth=1, dropout=0., context_dim=None):
+        super().__init__()
+        self.in_channels = in_channels
+        inner_dim = n_heads * d_head
+        self.norm = nn.GroupNorm(num_groups=32, num_channels=in_channels, eps=1e-6, affine=True)
+        self.proj_in = nn.Conv2d(in_channels, inner_dim, kernel_size=1, stride=1, padding=0)
+        self.transformer_blocks = nn.ModuleList(
+            [BasicTransformerBlock(inner_dim, n_heads, d_head, dropout=dropout,
+                                   context_dim=context_dim) for _ in range(depth)])
+        self.proj_out = zero_module(nn.Conv2d(inner_dim, in_channels, kernel_size=1, stride=1,
+                                              padding=0))
+
+    def forward(self, x, context=None):
+        b, c, h, w = x.shape
+        src = ops.ActSource(x, norm=self.norm, silu=False)
+        t = self.proj_in(src if _is_quant(self.proj_in) else src.materialize())
+        inner = t.shape[1]
+        t = ops.transpose_last2(t.reshape(b, inner, h * w))          # b (h w) c
+        for block in self.transformer_blocks:
+            t = block(t, context)
+        t = ops.transpose_last2(t).reshape(b, inner, h, w)
+        return ops.add(self.proj_out(t), x)
+
+
 class UNetModel(nn.Module):
     """openaimodel.py:447-782 for the covered options."""
 
@@ -282,8 +430,12 @@ class UNetModel(nn.Module):
                  use_spatial_transformer=False, transformer_depth=1, context_dim=None,
                  n_embed=None, legacy=True):
         super().__init__()
-        if use_spatial_transformer or num_classes is not None or dims != 2 or use_fp16 or n_embed:
-            raise NotImplementedError("option outside the covered latent-UNet configuration")
+        if num_classes is not None or dims != 2 or use_fp16 or n_embed:
+            raise NotImplementedError("option outside the covered latent-UNet configurations")
+        if use_spatial_transformer:
+            assert context_dim is not None
+            if not isinstance(context_dim, int):
+                context_dim = list(context_dim)[0] if len(context_dim) == 1 else list(context_dim)
         if num_heads_upsample == -1:
             num_heads_upsample = num_heads
         assert num_heads != -1 or num_head_channels != -1
@@ -318,7 +470,10 @@ class UNetModel(nn.Module):
                 heads = ch // num_head_channels
                 dim_head = num_head_channels
             if legacy:
-                dim_head = num_head_channels
+                dim_head = ch // heads if use_spatial_transformer else num_head_channels
+            if use_spatial_transformer:
+                return SpatialTransformer(ch, heads, dim_head, depth=transformer_depth,
+                                          context_dim=context_dim)
             return AttentionBlock(ch, use_checkpoint=use_checkpoint, num_heads=heads,
                                   num_head_channels=dim_head,
                                   use_new_attention_order=use_new_attention_order)

@@ -135,6 +135,38 @@ def silu(x):
     return y
 
 
+def layernorm(x, norm):
+    """nn.LayerNorm over the last dimension."""
+    _req(x)
+    x = x.contiguous()
+    c = x.shape[-1]
+    y = torch.empty_like(x)
+    _lib.call('modiff_layernorm', x.data_ptr(), y.data_ptr(), norm.weight.data_ptr(),
+              norm.bias.data_ptr(), x.numel() // c, c, float(norm.eps), _lib.stream_ptr())
+    return y
+
+
+def geglu(x):
+    """x[..., :n] * gelu(x[..., n:])."""
+    _req(x)
+    x = x.contiguous()
+    n = x.shape[-1] // 2
+    y = torch.empty(tuple(x.shape[:-1]) + (n,), dtype=torch.float32, device=x.device)
+    _lib.call('modiff_geglu', x.data_ptr(), y.data_ptr(), x.numel() // (2 * n), n,
+              _lib.stream_ptr())
+    return y
+
+
+def transpose_last2(x):
+    """[B, R, C] -> [B, C, R] (contiguous)."""
+    _req(x)
+    x = x.contiguous()
+    b, r, c = x.shape
+    y = torch.empty((b, c, r), dtype=torch.float32, device=x.device)
+    _lib.call('modiff_transpose', x.data_ptr(), y.data_ptr(), b, r, c, _lib.stream_ptr())
+    return y
+
+
 def add(a, b):
     """a + b for equal shapes."""
     _req(a, b)

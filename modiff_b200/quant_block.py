@@ -160,6 +160,46 @@ class QuantAttentionBlock(BaseQuantBlock):
         return ldm_unet.attention_block_forward(self, x)
 
 
+class QuantBasicTransformerBlock(BaseQuantBlock):
+    """Re-hosted SD transformer block (qdiff/quant_block.py:207-265).  As in the reference the
+    q / k / v / softmax quantisers are constructed on the attention modules but the attention
+    matmuls run in floating point; the projections and feed-forward layers are QuantModules."""
+
+    def __init__(self, tran, act_quant_params: dict = {}, sm_abit: int = 8):
+        super().__init__(act_quant_params)
+        self.attn1 = tran.attn1
+        self.ff = tran.ff
+        self.attn2 = tran.attn2
+        self.norm1 = tran.norm1
+        self.norm2 = tran.norm2
+        self.norm3 = tran.norm3
+        self.checkpoint = tran.checkpoint
+        params_w = act_quant_params.copy()
+        params_w['n_bits'] = sm_abit
+        params_w['always_zero'] = True
+        for attn in (self.attn1, self.attn2):
+            attn.act_quantizer_q = UniformAffineQuantizer(**act_quant_params)
+            attn.act_quantizer_k = UniformAffineQuantizer(**act_quant_params)
+            attn.act_quantizer_v = UniformAffineQuantizer(**act_quant_params)
+            attn.act_quantizer_w = UniformAffineQuantizer(**params_w)
+            attn.use_act_quant = False
+
+    def forward(self, x, context=None):
+        if context is None and isinstance(x, (tuple, list)):
+            assert len(x) == 2
+            x, context = x
+        return ldm_unet.transformer_block_forward(self, x, context)
+
+    def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self.attn1.use_act_quant = act_quant
+        self.attn2.use_act_quant = act_quant
+        self.use_weight_quant = weight_quant
+        self.use_act_quant = act_quant
+        for m in self.modules():
+            if isinstance(m, QuantModule):
+                m.set_quant_state(weight_quant, act_quant)
+
+
 unet._LAZY_BLOCKS = unet._LAZY_BLOCKS + (QuantResnetBlock,)
 ldm_unet._LAZY_BLOCKS = ldm_unet._LAZY_BLOCKS + (QuantResBlock,)
 
@@ -168,6 +208,7 @@ def get_specials(quant_act=False):
     """Class-name -> quantised block map (qdiff/quant_block.py:372-384, pixel- and latent-UNet entries)."""
     specials = {
         'ResBlock': QuantResBlock,
+        'BasicTransformerBlock': QuantBasicTransformerBlock,
         'ResnetBlock': QuantResnetBlock,
         'AttnBlock': QuantAttnBlock,
     }

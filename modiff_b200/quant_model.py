@@ -5,7 +5,7 @@ import logging
 import torch.nn as nn
 
 from .quant_block import (get_specials, BaseQuantBlock, QuantAttnBlock, QuantQKMatMul,
-                          QuantSMVMatMul)
+                          QuantSMVMatMul, QuantBasicTransformerBlock)
 from .quant_layer import QuantModule, StraightThrough
 
 logger = logging.getLogger(__name__)
@@ -45,7 +45,7 @@ class QuantModel(nn.Module):
         for name, child in module.named_children():
             special = self.specials.get(type(child).__name__)
             if special is not None and not isinstance(child, BaseQuantBlock):
-                if special is QuantAttnBlock:
+                if special in (QuantAttnBlock, QuantBasicTransformerBlock):
                     setattr(module, name, special(child, act_quant_params, sm_abit=self.sm_abit))
                 elif special is QuantSMVMatMul:
                     setattr(module, name, special(act_quant_params, sm_abit=self.sm_abit))
@@ -89,6 +89,13 @@ class QuantModel(nn.Module):
 
     def set_running_stat(self, running_stat: bool, sm_only=False):
         for m in self.model.modules():
+            if isinstance(m, QuantBasicTransformerBlock):
+                for attn in (m.attn1, m.attn2):
+                    attn.act_quantizer_w.running_stat = running_stat
+                    if not sm_only:
+                        attn.act_quantizer_q.running_stat = running_stat
+                        attn.act_quantizer_k.running_stat = running_stat
+                        attn.act_quantizer_v.running_stat = running_stat
             if isinstance(m, QuantModule) and not sm_only:
                 m.set_running_stat(running_stat)
 

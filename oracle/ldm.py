@@ -28,26 +28,28 @@ def unet_plan(cfg):
     ('res', kind) / ('attn',) entries per TimestepEmbedSequential."""
     mc, mult_list = cfg["model_channels"], cfg["channel_mult"]
     nrb, ar = cfg["num_res_blocks"], cfg["attention_resolutions"]
+    attn_kind = "st" if cfg.get("use_spatial_transformer", False) else "attn"
+    updown = cfg.get("resblock_updown", False)
     inputs = [[("conv",)]]
     ds = 1
     for level, _ in enumerate(mult_list):
         for _ in range(nrb):
             layers = [("res", "plain")]
             if ds in ar:
-                layers.append(("attn",))
+                layers.append((attn_kind,))
             inputs.append(layers)
         if level != len(mult_list) - 1:
-            inputs.append([("res", "down")])
+            inputs.append([("res", "down")] if updown else [("downsample",)])
             ds *= 2
-    middle = [("res", "plain"), ("attn",), ("res", "plain")]
+    middle = [("res", "plain"), (attn_kind,), ("res", "plain")]
     outputs = []
     for level, _ in list(enumerate(mult_list))[::-1]:
         for i in range(nrb + 1):
             layers = [("res", "plain")]
             if ds in ar:
-                layers.append(("attn",))
+                layers.append((attn_kind,))
             if level and i == nrb:
-                layers.append(("res", "up"))
+                layers.append(("res", "up") if updown else ("upsample",))
                 ds //= 2
             outputs.append(layers)
     return inputs, middle, outputs
@@ -63,7 +65,8 @@ class OracleLDMUNet:
                 continue
             base = name[:-len(".weight")]
             pad = 1 if (w.dim() == 4 and w.shape[-1] == 3) else 0
-            m = OracleQuantModule(w, state.get(base + ".bias"), 1, pad, w_bits, a_bits, a_sym,
+            stride = 2 if base.endswith(".op") else 1          # Downsample.op (openaimodel.py:148-151)
+            m = OracleQuantModule(w, state.get(base + ".bias"), stride, pad, w_bits, a_bits, a_sym,
                                   False, modulate)
             m.use_weight_quant = m.use_act_quant = quant
             if not quant:
@@ -134,18 +137,70 @@ class OracleLDMUNet:
                 m._as4d = True
         return m.forward(x.unsqueeze(-1)).squeeze(-1)
 
-    def _seq(self, prefix, layers, h, emb, split=0):
+    def _ln(self, x, base):
+        return F.layer_norm(x, (x.shape[-1],), self.state[base + ".weight"],
+                            self.state[base + ".bias"], 1e-5)
+
+    def _cross_attn(self, base, x, context=None):
+        """qdiff/quant_block.py:181-204."""
+        L = self.layers
+        h = self.cfg["num_heads"]
+        q = L[base + ".to_q"].forward(x)
+        ctx = x if context is None else context
+        k = L[base + ".to_k"].forward(ctx)
+        v = L[base + ".to_v"].forward(ctx)
+        b, n, inner = q.shape
+        d = inner // h
+
+        def heads(t):
+            return t.reshape(b, t.shape[1], h, d).permute(0, 2, 1, 3).reshape(b * h, t.shape[1], d)
+
+        q, k, v = heads(q), heads(k), heads(v)
+        sim = torch.einsum('b i d, b j d -> b i j', q, k) * (d ** -0.5)
+        attn = sim.softmax(dim=-1)
+        out = torch.einsum('b i j, b j d -> b i d', attn, v)
+        out = out.reshape(b, h, n, d).permute(0, 2, 1, 3).reshape(b, n, inner)
+        return L[base + ".to_out.0"].forward(out)
+
+    def _st(self, base, x, context):
+        """ldm/modules/attention.py:270-287 with qdiff/quant_block.py:249-256 blocks."""
+        L = self.layers
+        b, c, hh, ww = x.shape
+        x_in = x
+        t = F.group_norm(x, 32, self.state[base + ".norm.weight"], self.state[base + ".norm.bias"], 1e-6)
+        t = L[base + ".proj_in"].forward(t)
+        inner = t.shape[1]
+        t = t.reshape(b, inner, hh * ww).permute(0, 2, 1)
+        j = 0
+        while f"{base}.transformer_blocks.{j}.attn1.to_q" in L:
+            tb = f"{base}.transformer_blocks.{j}"
+            t = self._cross_attn(tb + ".attn1", self._ln(t, tb + ".norm1")) + t
+            t = self._cross_attn(tb + ".attn2", self._ln(t, tb + ".norm2"), context) + t
+            ff = L[tb + ".ff.net.0.proj"].forward(self._ln(t, tb + ".norm3"))
+            a, gate = ff.chunk(2, dim=-1)
+            t = L[tb + ".ff.net.2"].forward(a * F.gelu(gate)) + t
+            j += 1
+        t = t.permute(0, 2, 1).reshape(b, inner, hh, ww)
+        return L[base + ".proj_out"].forward(t) + x_in
+
+    def _seq(self, prefix, layers, h, emb, split=0, context=None):
         for j, layer in enumerate(layers):
             base = f"{prefix}.{j}"
             if layer[0] == "conv":
                 h = self.layers[base].forward(h)
             elif layer[0] == "res":
                 h = self._res(base, layer[1], h, emb, split if j == 0 else 0)
+            elif layer[0] == "st":
+                h = self._st(base, h, context)
+            elif layer[0] == "downsample":
+                h = self.layers[base + ".op"].forward(h)
+            elif layer[0] == "upsample":
+                h = self.layers[base + ".conv"].forward(F.interpolate(h, scale_factor=2, mode="nearest"))
             else:
                 h = self._attn(base, h)
         return h
 
-    def forward(self, x, t):
+    def forward(self, x, t, context=None):
         """openaimodel.py:745-782."""
         L = self.layers
         inputs, middle, outputs = self.plan
@@ -156,13 +211,13 @@ class OracleLDMUNet:
         hs = []
         h = x
         for i, layers in enumerate(inputs):
-            h = self._seq(f"input_blocks.{i}", layers, h, emb)
+            h = self._seq(f"input_blocks.{i}", layers, h, emb, context=context)
             hs.append(h)
-        h = self._seq("middle_block", middle, h, emb)
+        h = self._seq("middle_block", middle, h, emb, context=context)
         for i, layers in enumerate(outputs):
             split = h.shape[1] if self.split else 0
             h = torch.cat([h, hs.pop()], dim=1)
-            h = self._seq(f"output_blocks.{i}", layers, h, emb, split)
+            h = self._seq(f"output_blocks.{i}", layers, h, emb, split, context=context)
         h = F.silu(self._gn(h, "out.0"))
         return L["out.2"].forward(h)
 
@@ -186,9 +241,11 @@ def ddim_parameters(alphas_cumprod, steps, n_timestep=1000):
 
 
 @torch.no_grad()
-def latent_ddim_sample(x, model_fn, alphas_cumprod, steps, max_evals=None, on_step=None):
-    """ldm/models/diffusion/ddim.py:117-234 with eta = 0, no guidance.  `max_evals` stops early
-    (for bounded tests)."""
+def latent_ddim_sample(x, model_fn, alphas_cumprod, steps, max_evals=None, on_step=None,
+                       cond=None, uncond=None, guidance=1.0):
+    """ldm/models/diffusion/ddim.py:117-234 with eta = 0.  With `uncond` and guidance != 1 the
+    batch is doubled and e = e_uc + s * (e_c - e_uc) (:192-208).  `max_evals` stops early (for
+    bounded tests)."""
     ts, alphas, alphas_prev = ddim_parameters(alphas_cumprod, steps)
     sqrt_one_minus = np.sqrt(1. - alphas)
     b = x.shape[0]
@@ -199,7 +256,12 @@ def latent_ddim_sample(x, model_fn, alphas_cumprod, steps, max_evals=None, on_st
             break
         index = total - i - 1
         t = torch.full((b,), int(step), dtype=torch.long)
-        e_t = model_fn(img, t)
+        if uncond is None or guidance == 1.0:
+            e_t = model_fn(img, t) if cond is None else model_fn(img, t, cond)
+        else:
+            e_all = model_fn(torch.cat([img] * 2), torch.cat([t] * 2), torch.cat([uncond, cond]))
+            e_uc, e_c = e_all.chunk(2)
+            e_t = e_uc + guidance * (e_c - e_uc)
         a_t = torch.full((b, 1, 1, 1), float(alphas[index]))
         a_prev = torch.full((b, 1, 1, 1), float(alphas_prev[index]))
         sqrt_one_minus_at = torch.full((b, 1, 1, 1), float(sqrt_one_minus[index]))

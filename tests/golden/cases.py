@@ -135,3 +135,26 @@ LDM_CASES = [
 def ldm_noise(c):
     g = torch.Generator().manual_seed(c["noise_seed"])
     return torch.randn(c["batch"], 4, 32, 32, generator=g)
+
+
+# ---------------------------------------------------------------- SD-v1 UNet (v1-inference.yaml)
+SD_CONFIG = dict(
+    image_size=32, in_channels=4, out_channels=4, model_channels=320,
+    attention_resolutions=[4, 2, 1], num_res_blocks=2, channel_mult=[1, 2, 4, 4], num_heads=8,
+    use_spatial_transformer=True, transformer_depth=1, context_dim=768, legacy=False)
+SD_SCHEDULE = dict(linear_start=0.00085, linear_end=0.0120)    # v1-inference.yaml:5-6
+
+SD_CASES = [
+    # latent 4x64x64, context 77x768 ~ N(0,1), classifier-free guidance 7.5 (2x effective batch),
+    # first `evals` of the 50 DDIM evaluations
+    dict(name="sd_w8a8_b1", w_bits=8, a_bits=8, batch=1, latent=64, ddim_steps=50, evals=3,
+         guidance=7.5, noise_seed=21, zero_seed=1234),
+]
+
+
+def sd_inputs(c):
+    g = torch.Generator().manual_seed(c["noise_seed"])
+    x = torch.randn(c["batch"], 4, c["latent"], c["latent"], generator=g)
+    cond = torch.randn(c["batch"], 77, 768, generator=g)
+    uncond = torch.randn(c["batch"], 77, 768, generator=g)
+    return x, cond, uncond

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer|ldm]
+    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer|ldm|sd]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -195,10 +195,54 @@ def gen_ldm():
     print("ldm.npz", len(out))
 
 
+def gen_sd():
+    """SD-v1 UNet shapes (random init seed 0, zero tensors redrawn), reference QuantModel with
+    --a_sym, classifier-free guidance as ldm/models/diffusion/ddim.py:192-208."""
+    import types
+    oc, lc = types.ModuleType('omegaconf'), types.ModuleType('omegaconf.listconfig')
+
+    class ListConfig(list):
+        pass
+
+    lc.ListConfig = ListConfig
+    oc.listconfig = lc
+    sys.modules.setdefault('omegaconf', oc)
+    sys.modules.setdefault('omegaconf.listconfig', lc)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from modiff_b200.ldm_unet import rerandomize_zero_tensors
+    from oracle.ldm import ldm_schedule, latent_ddim_sample
+    from ldm.modules.diffusionmodules.openaimodel import UNetModel as RefUNet
+    out = {}
+    ac = ldm_schedule(**cases.SD_SCHEDULE)
+    for c in cases.SD_CASES:
+        t0 = time.time()
+        torch.manual_seed(0)
+        model = RefUNet(**cases.SD_CONFIG).eval()
+        rerandomize_zero_tensors(model, seed=c["zero_seed"])
+        wq, aq = cases.quant_params(c)
+        qnn = RefQuantModel(model=model, weight_quant_params=wq, act_quant_params=aq, sm_abit=8,
+                            modulate=True).eval()
+        qnn.set_quant_state(True, True)
+        qnn.set_grad_ckpt(False)
+        qnn.reset_cache()
+        x, cond, uncond = cases.sd_inputs(c)
+        eps = []
+        final = latent_ddim_sample(x, lambda a, t, ctx: qnn(a, t, ctx), ac, c["ddim_steps"],
+                                   max_evals=c["evals"], cond=cond, uncond=uncond,
+                                   guidance=c["guidance"],
+                                   on_step=lambda i, e, im: eps.append(e.numpy().copy()))
+        out[c["name"] + "/final"] = final.numpy().copy()
+        for i, e in enumerate(eps):
+            out[f"{c['name']}/eps{i}"] = e
+        print(c["name"], f"{time.time() - t0:.1f}s", float(final.std()))
+    np.savez_compressed(os.path.join(HERE, "sd.npz"), **out)
+    print("sd.npz", len(out))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
-                ldm=gen_ldm)
+                ldm=gen_ldm, sd=gen_sd)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()

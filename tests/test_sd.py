@@ -1,0 +1,87 @@
+"""SD-v1 UNet shapes (spatial transformer, cross-attention with a 77x768 context, classifier-free
+guidance): oracle vs the reference's fixtures (CPU) and the CUDA path vs the same fixtures (GPU).
+W8A8 modulated, symmetric dynamic activations, random init seed 0 with zero tensors redrawn."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle
+from oracle.ldm import OracleLDMUNet, ldm_schedule, latent_ddim_sample
+
+GOLDEN = os.path.dirname(os.path.abspath(cases.__file__))
+
+
+@pytest.fixture(scope="module")
+def golden_sd():
+    return np.load(os.path.join(GOLDEN, "sd.npz"))
+
+
+def _build():
+    import modiff_b200 as m
+    torch.manual_seed(0)
+    net = m.UNetModel(**cases.SD_CONFIG).eval()
+    m.rerandomize_zero_tensors(net, seed=cases.SD_CASES[0]["zero_seed"])
+    return net
+
+
+def test_structure_matches_reference_counts():
+    """860 M parameters, 282 quantised layers, 16 transformer blocks, 187 zero tensors."""
+    import modiff_b200 as m
+    torch.manual_seed(0)
+    net = m.UNetModel(**cases.SD_CONFIG)
+    assert sum(p.numel() for p in net.parameters()) == 859520964
+    assert m.rerandomize_zero_tensors(net) == 187
+    wq, aq = cases.quant_params(cases.SD_CASES[0])
+    q = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True)
+    assert sum(isinstance(x, m.QuantModule) for x in q.modules()) == 282
+    assert sum(isinstance(x, m.QuantBasicTransformerBlock) for x in q.modules()) == 16
+
+
+def test_oracle_matches_reference_first_eval(golden_sd):
+    """One guided evaluation of the oracle (unquantised first step) against the reference."""
+    c = cases.SD_CASES[0]
+    net = _build()
+    state = {k: v.detach().clone() for k, v in net.state_dict().items()}
+    o = OracleLDMUNet(state, cases.SD_CONFIG, c["w_bits"], c["a_bits"])
+    x, cond, uncond = cases.sd_inputs(c)
+    eps = []
+    latent_ddim_sample(x, o.forward, ldm_schedule(**cases.SD_SCHEDULE), c["ddim_steps"],
+                       max_evals=1, cond=cond, uncond=uncond, guidance=c["guidance"],
+                       on_step=lambda i, e, im: eps.append(e.numpy().copy()))
+    ref0 = golden_sd[c["name"] + "/eps0"]
+    assert np.abs(eps[0] - ref0).max() < 1e-4 * np.abs(ref0).max()
+
+
+@pytest.mark.gpu
+def test_cuda_path_matches_reference(cuda, golden_sd):
+    import modiff_b200 as m
+    c = cases.SD_CASES[0]
+    net = _build()
+    wq, aq = cases.quant_params(c)
+    qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(cuda).eval()
+    qnn.set_quant_state(True, True)
+    qnn.set_grad_ckpt(False)
+    qnn.reset_cache()
+    x, cond, uncond = cases.sd_inputs(c)
+    sampler = m.DDIMSampler(qnn, **cases.SD_SCHEDULE)
+    eps = []
+    final, _ = sampler.sample(c["ddim_steps"], c["batch"], tuple(x.shape[1:]), eta=0.0,
+                              conditioning=cond.to(cuda), x_T=x.to(cuda), max_evals=c["evals"],
+                              unconditional_guidance_scale=c["guidance"],
+                              unconditional_conditioning=uncond.to(cuda),
+                              img_callback=lambda e, i: eps.append(e.clone()))
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    for i, e in enumerate(eps):
+        ref = golden_sd[f"{c['name']}/eps{i}"]
+        err = np.abs(e.cpu().numpy() - ref).max() / np.abs(ref).max()
+        p = oracle.psnr(ref, e.cpu().numpy())
+        print(f"sd eval {i}: max|eps-ref|/max|ref| = {err:.2e}, PSNR {p:.1f} dB")
+        if i == 0:
+            assert err < 1e-4, err
+        else:
+            assert p >= 35.0, (i, p)
+    assert oracle.psnr(golden_sd[c["name"] + "/final"], final.cpu().numpy()) >= 40.0
