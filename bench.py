@@ -28,6 +28,10 @@ W_BITS, A_BITS = 4, 4
 METRIC = "UNet sampling images/sec"
 WORKLOAD = "pixel UNet 3x32x32 W4A4 modulated, split shortcut, 100 DDIM quad steps, batch 256/GPU"
 
+# measured DRAM bytes / algorithmic bytes of one launch (ncu captures summarised in profiles/):
+# the quantiser reads x and a_hat twice (two passes), 21 B moved per 13 B algorithmic
+DRAM_TRAFFIC_RATIO = {"modiff_modq_src": 1.52, "modiff_modq": 1.52, "modiff_igemm_conv": 0.83}
+
 WQ = {'n_bits': W_BITS, 'channel_wise': True, 'scale_method': 'max'}
 AQ = {'n_bits': A_BITS, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
       'leaf_param': True, 'dynamic': True}
@@ -228,8 +232,14 @@ def main():
     dom = max(summ, key=lambda k: summ[k]["ms"])
     d = summ[dom]
     achieved = d["bytes"] / (d["ms"] / 1000.0) / 1e9
+    # DRAM traffic per launch: ncu's dram__bytes_read + dram__bytes_write of one captured launch
+    # (profiles/), expressed as a ratio to that launch's algorithmic bytes and scaled to this
+    # run's average launch; null for entry points that were not captured.
+    ratio = DRAM_TRAFFIC_RATIO.get(dom)
+    traffic = None if ratio is None else ratio * d["bytes"] / d["launches"]
     roofline = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": d["bytes"] / d["launches"],
                 "launches": d["launches"], "share_of_kernel_time": d["ms"] / total_ms,
                 "per_entry_point_ms": {k: round(v["ms"], 2) for k, v in summ.items()}}
 

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py [/path/to/reference] [--only layers|unet|weights|quantizer|ldm|sd]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|sd]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -23,7 +23,8 @@ sys.path.insert(0, HERE)
 sys.dont_write_bytecode = True
 import cases  # noqa: E402
 
-REF = next((a for a in sys.argv[1:] if not a.startswith("--")), "/root/reference")
+REF = next((a for a in sys.argv[1:] if not a.startswith("--") and os.path.isdir(a)),
+           os.environ.get("MODIFF_REFERENCE", "reference"))
 ONLY = sys.argv[sys.argv.index("--only") + 1] if "--only" in sys.argv else None
 sys.path.insert(0, REF)
 warnings.filterwarnings("ignore", category=SyntaxWarning)
