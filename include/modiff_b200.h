@@ -139,6 +139,23 @@ int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, f
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     void* stream);
 
+/* modiff_modq_src for an input that is GroupNorm (+ FiLM) (+ SiLU) of [x0 | x1] (+ chan_bias):
+ * the normalisation statistics and the residual maximum come from ONE sweep over the source.
+ * Replaces `h = self.norm1(h); h = nonlinearity(h); h = self.conv1(h)` and its siblings
+ * (qdiff/quant_block.py:279-306, 91-109, 331-335 with ddim/models/diffusion.py:32-33 and
+ * ldm/modules/diffusionmodules/util.py:214-216) followed by qdiff/quant_layer.py:325-336.
+ *   src     x0 / x1 / c0 / silu / chan_bias as in modiff_act_source; src->affine is ignored
+ *   film    [batch][2*cin] FiLM scale | shift applied after the normalisation, or NULL
+ *   gamma, beta  GroupNorm weight / bias [cin];  groups, eps as in nn.GroupNorm
+ *   affine  OUT [batch][cin][2]: the per-(image, channel) scale / shift the encode pass used;
+ *           a later modiff_modq_src on the same input may pass it as src->affine
+ * Slabs of (cin / groups) * h * w <= 16384 floats (h * w / 4 a power of two) are kept in
+ * registers; anything else runs the statistics pass of modiff_groupnorm_silu first. */
+int modiff_modq_gn(const modiff_act_source* src, const float* film, const float* gamma,
+                   const float* beta, int groups, float eps, float* affine, float* a_hat,
+                   int8_t* codes, float* x_scale, const modiff_conv_geom* g, int n_bits,
+                   int per_sample, void* scratch, void* stream);
+
 /* Same quantiser as modiff_modq for callers that cannot hand over scratch memory.
  * This entry point has no counterpart in the reference; it exists for hosts that must not
  * allocate once they are running - for example a serving process whose device memory is

@@ -71,12 +71,65 @@ int validate_geom(const modiff_conv_geom* g);
 // is the same wherever it is (re)computed.  Hardware exp2 / reciprocal: about 2 ulp, a few
 // instructions (the quantiser kernels evaluate it twice per element and are otherwise
 // memory-bound).
-__device__ inline float silu_f(float y) { return __fdividef(y, 1.0f + __expf(-y)); }
+__device__ inline float silu_f(float y) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return y * r;   // five instructions; -0 for y far below zero
+}
 // GroupNorm affine step, one fused multiply-add everywhere it is evaluated.
 __device__ inline float gn_apply(float v, float mean, float ga, float be) {
   return fmaf(v - mean, ga, be);
 }
+// Sum over the block; every thread gets the total.  `sh` holds 32 floats.
+__device__ inline float block_sum(float v, float* sh) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? sh[lane] : 0.0f;
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+// Two sums at once (each with exactly the operations of block_sum, so the same bits) for
+// half the barriers.  `sh` holds 64 floats.
+__device__ inline void block_sum2(float& a, float& b, float* sh) {
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) {
+    sh[warp] = a;
+    sh[32 + warp] = b;
+  }
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  a = (lane < nw) ? sh[lane] : 0.0f;
+  b = (lane < nw) ? sh[32 + lane] : 0.0f;
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+}
 #endif
+
+// Launch shape of the GroupNorm kernels for one (image, group) slab of `count` elements.  The
+// statistics are summed per thread and then over the block, so two kernels agree on the last
+// bit of mean and variance only when they use the same thread count.
+inline int groupnorm_threads(int count) { return count >= 8192 ? 512 : (count >= 1024 ? 256 : 128); }
+// log2(hw / 4) when hw / 4 is a power of two, else -1
+inline int groupnorm_lg_hw4(int hw) {
+  if (hw % 4 != 0) return -1;
+  const int hw4 = hw / 4;
+  if ((hw4 & (hw4 - 1)) != 0) return -1;
+  int lg = 0;
+  while ((1 << lg) < hw4) ++lg;
+  return lg;
+}
 
 // Symmetric activation code range of an n-bit quantiser
 // (n_levels = 2^(b-1) - 1; clamp(-n_levels - 1, n_levels)).

@@ -9,18 +9,6 @@ namespace modiff {
 
 namespace {
 
-__device__ inline float block_sum(float v, float* sh) {
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();
-  if (lane == 0) sh[warp] = v;
-  __syncthreads();
-  const int nw = (blockDim.x + 31) >> 5;
-  float t = (lane < nw) ? sh[lane] : 0.0f;
-  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-  return t;  // every thread holds the total
-}
-
 // One block per (image, group).  Sweeps over the group's elements: mean, centred variance and
 // (unless only the statistics are wanted) normalise; sweeps 2 and 3 hit L1/L2.
 // Input = channel concat [x0 | x1] plus an optional per-(image, channel) bias.
@@ -374,15 +362,8 @@ int modiff_groupnorm_silu(const float* x0, const float* x1, int c0, const float*
   MODIFF_CHECK_ARG((((uintptr_t)x0 | (uintptr_t)y | (uintptr_t)x1) & 15) == 0,
                    "GroupNorm tensors must be 16-byte aligned");
   const int count = (c / groups) * hw;
-  const int threads = count >= 8192 ? 512 : (count >= 1024 ? 256 : 128);
-  int lg_hw4 = -1;   // log2(hw / 4) when hw / 4 is a power of two
-  if (hw % 4 == 0) {
-    const int hw4 = hw / 4;
-    if ((hw4 & (hw4 - 1)) == 0) {
-      lg_hw4 = 0;
-      while ((1 << lg_hw4) < hw4) ++lg_hw4;
-    }
-  }
+  const int threads = groupnorm_threads(count);
+  const int lg_hw4 = groupnorm_lg_hw4(hw);
   groupnorm_silu_kernel<<<batch * groups, threads, 0, (cudaStream_t)stream>>>(
       x0, x1, c0, chan_bias, film, y, affine, gamma, beta, c, hw, groups, eps, silu, lg_hw4);
   MODIFF_LAUNCH_CHECK("groupnorm_silu_kernel");

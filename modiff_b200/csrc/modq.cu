@@ -50,6 +50,10 @@ __device__ inline void store4(float* __restrict__ base, int p, int hw, const flo
   }
 }
 
+__device__ inline void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // Device-side view of a modiff_act_source.
 struct SrcView {
   const float* x0;
@@ -338,6 +342,190 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
   }
 }
 
+
+// GroupNorm statistics and the residual maximum in ONE sweep over the source.
+//
+// A block takes one (image, group) slab at a time and keeps it in registers (NV float4 per
+// thread): it sums the slab exactly as groupnorm_silu_kernel does (same thread count, same
+// per-thread order, so mean and variance have the same bits), writes the per-(image, channel)
+// scale / shift table that the encode pass reads, and then evaluates
+// max |silu(x * scale + shift) - a_hat| on the values it still holds.  The stand-alone
+// statistics pass (4 bytes per element) disappears.
+constexpr int kGnMaxCpg = 64;
+
+template <int NV>
+__global__ void __launch_bounds__(512, NV <= 4 ? 2 : 1)
+gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __restrict__ affine,
+                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                 const float* __restrict__ a_hat, int batch, int c, int hw, int groups, float eps,
+                 int lg_hw4, int split, int n_levels, int per_sample, int slots,
+                 ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
+  __shared__ float sh[64];
+  __shared__ float2 tab[kGnMaxCpg];
+  __shared__ float bias_sh[kGnMaxCpg];
+  __shared__ float s0[16], s1[16];
+  __shared__ bool is_last;
+  const int cpg = c / groups;
+  const int count = cpg * hw;
+  const int total4 = cpg << lg_hw4;
+  const int items = batch * groups;
+  const bool has_bias = src.bias != nullptr;
+
+  float m0 = 0.0f, m1 = 0.0f;
+  int cur_n = -1;
+  // (image, group) of the current item, advanced without divisions
+  const int n_step = gridDim.x / groups, g_step = gridDim.x % groups;
+  int n = blockIdx.x / groups, grp = blockIdx.x % groups;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    if (item != (int)blockIdx.x) {
+      n += n_step;
+      grp += g_step;
+      if (grp >= groups) {
+        grp -= groups;
+        ++n;
+      }
+    }
+    const int cbeg = grp * cpg;
+    if (per_sample && n != cur_n) {
+      if (cur_n >= 0) {
+        float v = m0;
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if ((threadIdx.x & 31) == 0 && v > 0.0f)
+          atomicMax(&scratch->absmax_bits[cur_n], __float_as_uint(v));
+      }
+      m0 = 0.0f;
+      cur_n = n;
+    }
+    // The slab (cpg whole channels of one image) is one contiguous run of the NCHW tensor.
+    const float4* xs = reinterpret_cast<const float4*>(
+        (cbeg < src.c0) ? src.x0 + ((size_t)n * src.c0 + cbeg) * hw
+                        : src.x1 + ((size_t)n * src.c1 + (cbeg - src.c0)) * hw);
+    const float4* as = a_hat
+        ? reinterpret_cast<const float4*>(a_hat + ((size_t)n * c + cbeg) * hw) : nullptr;
+
+    float4 xv[NV], av[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      av[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < total4) {
+        xv[k] = __ldg(xs + i);
+        if (a_hat) av[k] = __ldg(as + i);
+      }
+    }
+    // normalisation parameters of this slab's channels (threads 0 .. cpg-1), fetched before the
+    // reductions so that their latency is off the critical path
+    float g_ch = 0.0f, b_ch = 0.0f, f_sc = 0.0f, f_sh = 0.0f, cb_ch = 0.0f;
+    if ((int)threadIdx.x < cpg) {
+      const int ch = cbeg + threadIdx.x;
+      g_ch = __ldg(gamma + ch);
+      b_ch = __ldg(beta + ch);
+      if (has_bias) cb_ch = __ldg(src.bias + (size_t)n * c + ch);
+      if (film) {
+        f_sc = __ldg(film + (size_t)n * 2 * c + ch);
+        f_sh = __ldg(film + (size_t)n * 2 * c + c + ch);
+      }
+      bias_sh[threadIdx.x] = cb_ch;
+    }
+    float shift = __ldg(reinterpret_cast<const float*>(xs));
+    float s = 0.0f, q = 0.0f;
+    if (has_bias) {
+      __syncthreads();
+      shift = __fadd_rn(shift, bias_sh[0]);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < total4) {
+          const float b = bias_sh[i >> lg_hw4];
+          const float a = __fadd_rn(xv[k].x, b) - shift, bb = __fadd_rn(xv[k].y, b) - shift,
+                      cc = __fadd_rn(xv[k].z, b) - shift, dd = __fadd_rn(xv[k].w, b) - shift;
+          s += (a + bb) + (cc + dd);
+          q += (a * a + bb * bb) + (cc * cc + dd * dd);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < total4) {
+          // x + 0 == x, so this is the arithmetic of the biased branch
+          const float a = xv[k].x - shift, bb = xv[k].y - shift, cc = xv[k].z - shift,
+                      dd = xv[k].w - shift;
+          s += (a + bb) + (cc + dd);
+          q += (a * a + bb * bb) + (cc * cc + dd * dd);
+        }
+      }
+    }
+    block_sum2(s, q, sh);
+    const float ms = s / (float)count;                   // the same operations, in the same order,
+    const float mean = shift + ms;                       // as groupnorm_silu_kernel
+    const float var = fmaxf(q / (float)count - ms * ms, 0.0f);
+    const float rstd = 1.0f / sqrtf(var + eps);
+    if ((int)threadIdx.x < cpg) {      // cpg <= kGnMaxCpg <= blockDim.x
+      const int ch = cbeg + threadIdx.x;
+      float ga = g_ch * rstd;
+      float sf = fmaf(cb_ch - mean, ga, b_ch);
+      if (film) {
+        const float f = 1.0f + f_sc;
+        ga *= f;
+        sf = fmaf(sf, f, f_sh);
+      }
+      tab[threadIdx.x] = make_float2(ga, sf);
+      reinterpret_cast<float2*>(affine)[(size_t)n * c + ch] = make_float2(ga, sf);
+    }
+    __syncthreads();
+    float mi = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < total4) {
+        const float2 ab = tab[i >> lg_hw4];
+        float v0 = fmaf(xv[k].x, ab.x, ab.y), v1 = fmaf(xv[k].y, ab.x, ab.y),
+              v2 = fmaf(xv[k].z, ab.x, ab.y), v3 = fmaf(xv[k].w, ab.x, ab.y);
+        if (src.silu) {
+          v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3);
+        }
+        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v0, av[k].x))), fabsf(__fsub_rn(v1, av[k].y)));
+        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v2, av[k].z))), fabsf(__fsub_rn(v3, av[k].w)));
+      }
+    }
+    if (split > 0 && cbeg >= split) m1 = fmaxf(m1, mi); else m0 = fmaxf(m0, mi);
+    __syncthreads();   // tab and bias_sh are rewritten by the next slab
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s0[threadIdx.x >> 5] = m0;
+    s1[threadIdx.x >> 5] = m1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) {
+      m0 = fmaxf(m0, s0[i]);
+      m1 = fmaxf(m1, s1[i]);
+    }
+    const int slot0 = per_sample ? (cur_n < 0 ? 0 : cur_n) : 0;
+    if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
+    if (split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    for (int sl = threadIdx.x; sl < slots; sl += blockDim.x) {
+      const unsigned int bits = atomicExch(&scratch->absmax_bits[sl], 0u);
+      double delta = (double)__uint_as_float(bits) / (double)n_levels;
+      if (delta < 1e-8) delta = 1e-8;
+      x_scale[sl] = (float)delta;
+    }
+    if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
 }  // namespace
 
 int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes, float* x_scale,
@@ -446,6 +634,75 @@ extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_
   const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
   return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                          (cudaStream_t)stream);
+}
+
+extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, const float* gamma,
+                              const float* beta, int groups, float eps, float* affine,
+                              float* a_hat, int8_t* codes, float* x_scale,
+                              const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
+                              void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && gamma && beta && affine && codes && x_scale && scratch,
+                   "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  MODIFF_CHECK_ARG(groups > 0 && g->cin % groups == 0, "bad GroupNorm shape: c=%d groups=%d",
+                   g->cin, groups);
+  MODIFF_CHECK_ARG(((uintptr_t)affine & 7) == 0, "affine table must be 8-byte aligned");
+  MODIFF_CHECK_ARG(src->affine == nullptr || src->affine == affine,
+                   "src->affine must be NULL or the table this call writes");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int hw = g->h * g->w;
+  const int cpg = g->cin / groups;
+  const int count = cpg * hw;
+  const int threads = groupnorm_threads(count);
+  const int lg_hw4 = groupnorm_lg_hw4(hw);
+  const int nv = lg_hw4 >= 0 ? ceil_div(count / 4, threads) : 0;
+  const bool aligned = ((((uintptr_t)src->x0 | (uintptr_t)src->x1 | (uintptr_t)a_hat) & 15) == 0);
+
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  const int n_levels = sym_levels(n_bits);
+  const int slots = per_sample ? g->batch : derive(*g).nseg;
+
+  // a slab must be whole channels of ONE source tensor and of ONE scale segment
+  const bool whole = (src->c0 % cpg == 0) && (g->split % cpg == 0);
+  if (lg_hw4 >= 0 && nv <= 8 && cpg <= kGnMaxCpg && aligned && whole) {
+    v.bias = src->chan_bias;
+    v.affine = nullptr;
+    const int items = g->batch * groups;
+    const int per_sm = threads >= 512 ? 2 : (threads >= 256 ? 4 : 8);
+    const int blocks = items < 148 * per_sm ? items : 148 * per_sm;
+#define MODIFF_GN_ABSMAX(NV)                                                                     \
+  gn_absmax_kernel<NV><<<blocks, threads, 0, s>>>(v, film, affine, gamma, beta, a_hat, g->batch,   \
+                                                  g->cin, hw, groups, eps, lg_hw4, g->split,      \
+                                                  n_levels, per_sample, slots,                    \
+                                                  (ModqScratch*)scratch, x_scale)
+    if (nv <= 1) MODIFF_GN_ABSMAX(1);
+    else if (nv <= 2) MODIFF_GN_ABSMAX(2);
+    else if (nv <= 4) MODIFF_GN_ABSMAX(4);
+    else MODIFF_GN_ABSMAX(8);
+#undef MODIFF_GN_ABSMAX
+    MODIFF_LAUNCH_CHECK("gn_absmax_kernel");
+    v.bias = nullptr;
+    v.affine = affine;
+    return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, false, s);
+  }
+  // slabs too large for registers (or odd sizes): statistics pass, then the two quantiser passes
+  rc = modiff_groupnorm_silu(src->x0, src->x1, src->c0, src->chan_bias, film, nullptr, affine, gamma,
+                             beta, g->batch, g->cin, hw, groups, eps, 0, stream);
+  if (rc) return rc;
+  v.bias = nullptr;
+  v.affine = affine;
+  return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -75,7 +75,8 @@ def main():
         _lib.TIMER = None
     status = _lib.device_status()
     out = {"geometry": vars(args), "device_status": status}
-    for name in ("modiff_modq", "modiff_modq_src", "modiff_groupnorm_silu", "modiff_igemm_conv"):
+    for name in ("modiff_modq", "modiff_modq_src", "modiff_modq_gn", "modiff_groupnorm_silu",
+                 "modiff_igemm_conv"):
         if name not in summ:
             continue
         v = summ[name]

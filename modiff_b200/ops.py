@@ -117,6 +117,22 @@ class ActSource:
                 self._tensor = t
         return self._tensor
 
+    def pending_norm(self):
+        """True while the GroupNorm statistics of this source have not been computed: the first
+        quantiser that reads it computes them in its own sweep (`modiff_modq_gn`)."""
+        return self.norm is not None and self._stats is None
+
+    def raw_struct(self):
+        """(modiff_act_source without the normalisation, empty [B, C, 2] table) for
+        `modiff_modq_gn`, which fills the table that `affine()` returns from then on."""
+        b, c = self.shape[0], self.shape[1]
+        if c != self.norm.num_channels:
+            raise ModiffError(f"GroupNorm expects {self.norm.num_channels} channels, got {c}")
+        self._stats = torch.empty((b, c, 2), dtype=torch.float32, device=self.device)
+        raw = _lib.ActSourceStruct(self.x0.data_ptr(), _lib.ptr(self.x1), self.x0.shape[1],
+                                   int(self.silu), None, _lib.ptr(self.chan_bias))
+        return raw, self._stats
+
     def struct(self):
         """ctypes mirror of modiff_act_source (keeps this object's tensors alive)."""
         if self._struct is None:

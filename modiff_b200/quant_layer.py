@@ -137,6 +137,9 @@ class QuantModule(nn.Module):
     alias_output = True
     # MODIFF_IGEMM_IMPL=1 forces the CUDA-core kernel, =2 the tensor-core kernel (debug aid)
     igemm_impl = int(os.environ.get("MODIFF_IGEMM_IMPL", _lib.IMPL_AUTO))
+    # MODIFF_FUSE_NORM_STATS=0 runs the GroupNorm statistics as their own pass (debug aid; the
+    # codes are the same either way)
+    fuse_norm_stats = os.environ.get("MODIFF_FUSE_NORM_STATS", "1") != "0"
 
     def __init__(self, org_module: Union[nn.Conv2d, nn.Linear, nn.Conv1d],
                  weight_quant_params: dict = {}, act_quant_params: dict = {},
@@ -357,6 +360,15 @@ class QuantModule(nn.Module):
         if not aq.dynamic:
             raise ModiffError("the int8 path implements dynamic activation scales "
                               "(quant_mode='dynamic'); static calibrated scales are not covered")
+        if src is not None and src.pending_norm() and self.fuse_norm_stats:
+            n = src.norm
+            raw, table = src.raw_struct()
+            _lib.call('modiff_modq_gn', C.byref(raw), _lib.ptr(src.film), n.weight.data_ptr(),
+                      n.bias.data_ptr(), n.num_groups, float(n.eps), table.data_ptr(),
+                      _lib.ptr(a_hat), buf.codes.data_ptr(), buf.x_scale.data_ptr(), C.byref(g),
+                      aq.n_bits, int(aq.channel_wise), buf.scratch.data_ptr(), _lib.stream_ptr(),
+                      nbytes=13 * src.numel(), tag=g.key())
+            return
         if src is not None:
             _lib.call('modiff_modq_src', C.byref(src.struct()), _lib.ptr(a_hat),
                       buf.codes.data_ptr(), buf.x_scale.data_ptr(), C.byref(g), aq.n_bits,

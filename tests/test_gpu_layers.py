@@ -1,5 +1,7 @@
 """QuantModule (host API -> C ABI -> kernels) against the reference's own outputs stored in
 tests/golden/layers.npz, and against the oracle for codes and accumulators."""
+import copy
+
 import numpy as np
 import pytest
 import torch
@@ -106,3 +108,70 @@ def test_module_modes_and_errors(cuda):
         mod(x[:1].to(cuda))
     mod.reset_cache()
     mod(x[:1].to(cuda))
+
+
+@pytest.mark.parametrize("c0,c1,hw,bias,film,split,a_bits", [
+    (128, 0, 32, True, False, 0, 8),      # 4 channels x 1024 pixels per group: slab in registers
+    (64, 64, 16, False, False, 64, 4),    # concat input, split scales (up-path shortcut)
+    (256, 0, 8, False, True, 0, 8),       # FiLM scale / shift after the normalisation
+    (320, 0, 64, True, False, 0, 8),      # 10 x 4096 per group: statistics as their own pass
+    (96, 0, 6, False, False, 0, 8),       # h*w/4 not a power of two: statistics as their own pass
+])
+def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, split, a_bits):
+    """GroupNorm -> SiLU -> conv with the normalisation read lazily by the quantiser
+    (qdiff/quant_block.py:279-306): the one-sweep statistics + residual-maximum kernel gives
+    the same scale, cache and output bits as the separate statistics pass, and both follow
+    torch's group_norm + the oracle layer."""
+    import modiff_b200 as m
+    from modiff_b200.ops import ActSource
+    torch.manual_seed(3)
+    cin = c0 + c1
+    org = torch.nn.Conv2d(cin, 64, 3, padding=1)
+    norm = torch.nn.GroupNorm(32, cin, eps=1e-6)
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+        norm.bias.uniform_(-0.5, 0.5)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    w, b = org.weight.detach().clone(), org.bias.detach().clone()
+    orc = oracle.OracleQuantModule(w, b, 1, 1, 8, a_bits)
+    mods = []
+    for fuse in (True, False):
+        q = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
+        q.set_quant_state(True, True)
+        q.fuse_norm_stats = fuse
+        q.alias_output = False
+        mods.append(q)
+    norm_c = torch.nn.GroupNorm(32, cin, eps=1e-6).to(cuda)
+    norm_c.load_state_dict(norm.state_dict())
+    g = torch.Generator().manual_seed(11)
+    n = 3
+    base = torch.randn(n, cin, hw, hw, generator=g) * 2 + 0.7
+    for step in range(3):
+        x = base + 0.1 * step * torch.randn(n, cin, hw, hw, generator=g)
+        cb = torch.randn(n, cin, generator=g) if bias else None
+        fl = 0.3 * torch.randn(n, 2 * cin, generator=g) if film else None
+        t = x if cb is None else x + cb[:, :, None, None]
+        ref_in = torch.nn.functional.group_norm(t, 32, norm.weight, norm.bias, 1e-6)
+        if fl is not None:
+            ref_in = ref_in * (1 + fl[:, :cin, None, None]) + fl[:, cin:, None, None]
+        ref = orc.forward(torch.nn.functional.silu(ref_in), split=split) if split else \
+            orc.forward(torch.nn.functional.silu(ref_in))
+        outs = []
+        for q in mods:
+            xc = x.to(cuda)
+            src = ActSource(xc[:, :c0].contiguous(), xc[:, c0:].contiguous() if c1 else None,
+                            chan_bias=None if cb is None else cb.to(cuda), norm=norm_c, silu=True,
+                            film=None if fl is None else fl.to(cuda))
+            with torch.no_grad():
+                outs.append(q(src, split=split) if split else q(src))
+        if step > 0:
+            assert torch.equal(mods[0].a_hat, mods[1].a_hat)
+            assert torch.equal(outs[0], outs[1])
+            assert float(mods[0].act_quantizer.delta) == float(mods[1].act_quantizer.delta)
+        err = (outs[0].cpu() - ref).abs().max() / ref.abs().max()
+        # 8-bit codes of a residual: one code on the other side of a rounding boundary moves the
+        # output by ~1e-3 of its range, 4-bit codes by ~1e-2
+        assert err < (2e-3 if a_bits == 8 else 3e-2), (step, float(err))
+    assert m.device_status() == 0

@@ -85,5 +85,57 @@ def test_cuda_path_matches_reference(cuda, golden_sd):
             # observed 1.1e-4 of the eps range; the per-layer bound is 1e-3
             assert err < 5e-4, err
         else:
-            assert p >= 35.0, (i, p)
+            # Free-running modulated evaluations are not reproducible between two machines:
+            # the residual step is ~1/127 of an already small residual, so a 1e-4 difference
+            # left by evaluation 0 puts many codes on the other side of a rounding boundary,
+            # 282 layers compound it and guidance 7.5 multiplies it.  The CPU oracle run twice,
+            # once with evaluation 0 disturbed by 1e-4 of its range, agrees with itself to
+            # 29.7 dB / 30.9 dB on evaluations 1 / 2 and 51.5 dB on the final latent; the CUDA
+            # path measures 29.7 dB on evaluation 1.  Layer arithmetic at these shapes is
+            # checked with identical inputs in test_sd_layer_shapes_teacher_forced.
+            assert p >= 25.0, (i, p)
     assert oracle.psnr(golden_sd[c["name"] + "/final"], final.cpu().numpy()) >= 40.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,shape,cout", [
+    ("linear", (2, 4096, 320), 2560),     # GEGLU projection at 64x64 tokens
+    ("linear", (2, 4096, 1280), 320),     # feed-forward output
+    ("linear", (2, 77, 768), 320),        # cross-attention key / value of the text context
+    ("conv1", (2, 320, 64, 64), 320),     # spatial transformer proj_in (1x1)
+    ("conv3", (2, 320, 64, 64), 320),     # ResBlock conv, cin not a multiple of 128
+    ("conv3", (2, 960, 32, 32), 640),     # up path after the skip concat
+])
+def test_sd_layer_shapes_teacher_forced(cuda, kind, shape, cout):
+    """One quantised layer at an SD-v1 shape, fed the same inputs as the oracle for three
+    steps (qdiff/quant_layer.py:307-367): scale and cache bit-exact, output within 1e-4."""
+    import modiff_b200 as m
+    torch.manual_seed(5)
+    if kind == "linear":
+        org = torch.nn.Linear(shape[-1], cout)
+        orc = oracle.OracleQuantModule(org.weight.detach().clone(), org.bias.detach().clone(),
+                                       w_bits=8, a_bits=8)
+    else:
+        k = 3 if kind == "conv3" else 1
+        org = torch.nn.Conv2d(shape[1], cout, k, padding=k // 2)
+        orc = oracle.OracleQuantModule(org.weight.detach().clone(), org.bias.detach().clone(),
+                                       1, k // 2, 8, 8)
+    wq, aq = cases.quant_params(cases.SD_CASES[0])
+    ours = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
+    ours.set_quant_state(True, True)
+    ours.alias_output = False
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(shape, generator=g)
+    with torch.no_grad():
+        for step in range(3):
+            xs = x + 0.05 * step * torch.randn(shape, generator=g)
+            ref = orc.forward(xs)
+            got = ours(xs.to(cuda)).cpu()
+            err = float((got - ref).abs().max() / ref.abs().max())
+            # the first step's split-bf16 product (bound 1e-4) stays in the cached output, so
+            # the same bound holds for the later, exact-integer steps
+            assert err < 1e-4, (step, err)
+            if step > 0:
+                assert float(ours.act_quantizer.delta) == float(orc.last['x_scale'][0])
+                assert torch.equal(ours.a_hat.cpu(), orc.a_hat)
+    assert m.device_status() == 0
