@@ -66,6 +66,30 @@ __host__ __device__ inline Derived derive(const modiff_conv_geom& g) {
 
 int validate_geom(const modiff_conv_geom* g);
 
+// Division of 0 <= x < 2^31 by a divisor fixed at launch: one wide multiply and a shift instead
+// of the ~20-instruction software division.  m = floor(2^k / d) + 1 with k = 31 + ceil(log2 d)
+// gives floor(x * m / 2^k) == floor(x / d) for every such x.
+struct FastDiv {
+  uint32_t d, m;
+  int k;
+  FastDiv() : d(1), m(0x80000001u), k(31) {}
+  explicit FastDiv(int div) : d((uint32_t)div) {
+    int s = 0;
+    while ((1u << s) < d) ++s;
+    k = 31 + s;
+    m = (uint32_t)((((uint64_t)1) << k) / d + 1);
+  }
+  __host__ __device__ inline int div(int x) const {
+    return (int)(((uint64_t)(uint32_t)x * m) >> k);
+  }
+  // quotient and remainder
+  __host__ __device__ inline int divmod(int x, int& r) const {
+    const int q = div(x);
+    r = x - q * (int)d;
+    return q;
+  }
+};
+
 #ifdef __CUDACC__
 // x * sigmoid(x), shared by every kernel that applies the UNet's nonlinearity, so that a value
 // is the same wherever it is (re)computed.  Hardware exp2 / reciprocal: about 2 ulp, a few

@@ -12,6 +12,7 @@
 // contraction, true division) so codes and the cache are bit-identical to PyTorch.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace modiff {
@@ -52,6 +53,20 @@ __device__ inline void store4(float* __restrict__ base, int p, int hw, const flo
 
 __device__ inline void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// clamp(rne(t), lo, hi) for integer lo, hi with |lo|, |hi| < 2^22, without the conversion pipe:
+// clamping first gives the same result (rne is monotonic and keeps integers), and adding
+// 1.5 * 2^23 rounds to nearest-even at unit spacing.  The low byte of the sum's bit pattern is
+// the two's-complement code.
+__device__ inline float round_clamp(float t, float lo, float hi, uint32_t& bits) {
+  const float u = __fadd_rn(fminf(fmaxf(t, lo), hi), 12582912.0f);
+  bits = __float_as_uint(u);
+  return __fadd_rn(u, -12582912.0f);
+}
+// low bytes of four words -> one word
+__device__ inline uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // Device-side view of a modiff_act_source.
@@ -97,6 +112,19 @@ __device__ inline int slot_of(int n, int c, int split, int per_sample) {
 
 struct TileGrid {
   int pb, cb, total;   // pixel blocks, channel blocks, pb * cb * batch
+  FastDiv per_image;   // / (pb * cb)
+  FastDiv by_pb;       // / pb
+  FastDiv by_w;        // / g.w
+  FastDiv by_stride;   // / g.stride
+  // tile -> image, first channel, first pixel
+  __device__ inline void decode(int tile, int& n, int& c0, int& p0) const {
+    int rem;
+    n = per_image.divmod(tile, rem);
+    int pbi;
+    const int cbi = by_pb.divmod(rem, pbi);
+    c0 = cbi * kTileC;
+    p0 = pbi * kTileP;
+  }
 };
 
 template <bool VEC4, bool XFORM>
@@ -115,10 +143,9 @@ modq_absmax_kernel(const SrcView src, const float* __restrict__ a_hat,
   // Each block walks a strided list of tiles and publishes one maximum per scale slot, so the
   // number of same-address atomics is bounded by the grid size, not by the tensor size.
   for (int tile = blockIdx.x; tile < tg.total; tile += gridDim.x) {
-    const int n = tile / (tg.pb * tg.cb);
-    const int rem = tile % (tg.pb * tg.cb);
-    const int c0 = (rem / tg.pb) * kTileC;
-    const int p = (rem % tg.pb) * kTileP + 4 * pq;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    const int p = p0 + 4 * pq;
     if (per_sample && n != cur_n) {
       // flush the running maximum of the previous image
       if (cur_n >= 0) {
@@ -199,13 +226,11 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
   // last is still in L2 and is consumed first.
   for (int it = blockIdx.x; it < tg.total; it += gridDim.x) {
     const int tile = tg.total - 1 - it;
-    const int n = tile / (tg.pb * tg.cb);
-    const int rem = tile % (tg.pb * tg.cb);
-    const int c0 = (rem / tg.pb) * kTileC;
-    const int p0 = (rem % tg.pb) * kTileP;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
     const int p = p0 + 4 * pq;
 
-    int q[4][4];
+    uint32_t q[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -224,9 +249,7 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
-            float qf = rintf(__fdiv_rn(r, delta));
-            qf = fminf(fmaxf(qf, lo), hi);
-            q[i][j] = (int)qf;
+            const float qf = round_clamp(__fdiv_rn(r, delta), lo, hi, q[i][j]);
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
@@ -235,9 +258,7 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t word = (uint32_t)(q[0][j] & 0xff) | ((uint32_t)(q[1][j] & 0xff) << 8) |
-                            ((uint32_t)(q[2][j] & 0xff) << 16) | ((uint32_t)(q[3][j] & 0xff) << 24);
-      tile_sh[4 * pq + j][cg] = word;
+      tile_sh[4 * pq + j][cg] = pack_low_bytes(q[0][j], q[1][j], q[2][j], q[3][j]);
     }
     __syncthreads();
     // 4 threads per pixel, 16 bytes each.
@@ -246,16 +267,162 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
     const int pp = p0 + px;
     const int cbase = c0 + 16 * piece;
     if (pp < hw && cbase < d.cp) {
-      const int y = pp / g.w + g.pad_t;
-      const int xq = pp % g.w + g.pad_l;
-      const int plane = (y % g.stride) * g.stride + (xq % g.stride);
-      const size_t pix =
-          (((size_t)n * d.nplanes + plane) * d.hp + y / g.stride) * d.wp + xq / g.stride;
+      int y, xq, ys, xs;
+      y = tg.by_w.divmod(pp, xq);
+      const int yq = tg.by_stride.divmod(y + g.pad_t, ys);
+      const int xqq = tg.by_stride.divmod(xq + g.pad_l, xs);
+      const int plane = ys * g.stride + xs;
+      const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + yq) * d.wp + xqq;
       int4 v = make_int4(tile_sh[px][4 * piece], tile_sh[px][4 * piece + 1],
                          tile_sh[px][4 * piece + 2], tile_sh[px][4 * piece + 3]);
       *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
     }
     __syncthreads();
+  }
+}
+
+// Encode pass with its inputs staged through shared memory by cp.async: the x and a_hat tiles
+// of the NEXT tile are in flight while the current one is quantised, so the bytes in flight do
+// not depend on how many registers or warps the arithmetic needs.  Same arithmetic, tile order
+// and outputs as modq_encode_kernel<true, XFORM>.
+constexpr int kStages = 2;
+constexpr int kStageFloats = 2 * kTileC * kTileP;              // x tile | a_hat tile
+constexpr int kStagedSmem = kStages * kStageFloats * 4;        // bytes of dynamic shared memory
+
+__device__ inline void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned int dst = (unsigned int)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;     // 0: the 16 bytes are zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes)
+               : "memory");
+}
+
+template <bool XFORM>
+__global__ void __launch_bounds__(kThreads)
+modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
+                          int8_t* __restrict__ codes, const float* __restrict__ x_scale,
+                          modiff_conv_geom g, Derived d, TileGrid tg, int n_levels,
+                          int per_sample) {
+  extern __shared__ __align__(16) float stage_sh[];
+  __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
+  const int hw = g.h * g.w;
+  const int cg = threadIdx.x >> 4;
+  const int pq = threadIdx.x & 15;
+  const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+  auto issue = [&](int it, int stage) {
+    const int tile = tg.total - 1 - it;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    float* sx = stage_sh + stage * kStageFloats;
+    float* sa = sx + kTileC * kTileP;
+#pragma unroll
+    for (int r = 0; r < (kTileC * kTileP / 4) / kThreads; ++r) {
+      const int chunk = threadIdx.x + r * kThreads;
+      const int row = chunk >> 4, col = (chunk & 15) * 4;
+      const int c = c0 + row, p = p0 + col;
+      const bool valid = (c < g.cin) && (p < hw);
+      const float* xp = src.x0;
+      if (valid) {
+        if (XFORM)
+          xp = (c < src.c0) ? src.x0 + ((size_t)n * src.c0 + c) * hw + p
+                            : src.x1 + ((size_t)n * src.c1 + (c - src.c0)) * hw + p;
+        else
+          xp = src.x0 + ((size_t)n * g.cin + c) * hw + p;
+      }
+      cp_async16(sx + row * kTileP + col, xp, valid);
+      if (a_hat)
+        cp_async16(sa + row * kTileP + col,
+                   valid ? a_hat + ((size_t)n * g.cin + c) * hw + p : a_hat, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int k = 0;
+  if ((int)blockIdx.x < tg.total) issue(blockIdx.x, 0);
+  for (int it = blockIdx.x; it < tg.total; it += gridDim.x, ++k) {
+    const int stage = k % kStages;
+    if (it + (int)gridDim.x < tg.total) {
+      issue(it + gridDim.x, (k + 1) % kStages);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int tile = tg.total - 1 - it;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    const int p = p0 + 4 * pq;
+    const float* sx = stage_sh + stage * kStageFloats;
+    const float* sa = sx + kTileC * kTileP;
+
+    uint32_t q[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[i][j] = 0;
+
+    if (p < hw) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = 4 * cg + i;
+        const int c = c0 + row;
+        if (c < g.cin) {
+          const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
+          const float4 xt = *reinterpret_cast<const float4*>(sx + row * kTileP + 4 * pq);
+          float xv[4] = {xt.x, xt.y, xt.z, xt.w}, av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
+          if (a_hat) {
+            const float4 at = *reinterpret_cast<const float4*>(sa + row * kTileP + 4 * pq);
+            av[0] = at.x; av[1] = at.y; av[2] = at.z; av[3] = at.w;
+          }
+          if (XFORM) {
+            if (src.affine) {
+              const float2 ab =
+                  __ldg(reinterpret_cast<const float2*>(src.affine) + (size_t)n * g.cin + c);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) xv[j] = fmaf(xv[j], ab.x, ab.y);
+            } else if (src.bias) {
+              const float b = __ldg(src.bias + (size_t)n * g.cin + c);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) xv[j] = __fadd_rn(xv[j], b);
+            }
+            if (src.silu) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) xv[j] = silu_f(xv[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float r = __fsub_rn(xv[j], av[j]);
+            const float qf = round_clamp(__fdiv_rn(r, delta), lo, hi, q[i][j]);
+            nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
+          }
+          if (a_hat)
+            *reinterpret_cast<float4*>(a_hat + ((size_t)n * g.cin + c) * hw + p) =
+                make_float4(nv[0], nv[1], nv[2], nv[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      tile_sh[4 * pq + j][cg] = pack_low_bytes(q[0][j], q[1][j], q[2][j], q[3][j]);
+    }
+    __syncthreads();
+    const int px = threadIdx.x >> 2;
+    const int piece = threadIdx.x & 3;
+    const int pp = p0 + px;
+    const int cbase = c0 + 16 * piece;
+    if (pp < hw && cbase < d.cp) {
+      int y, xq, ys, xs;
+      y = tg.by_w.divmod(pp, xq);
+      const int yq = tg.by_stride.divmod(y + g.pad_t, ys);
+      const int xqq = tg.by_stride.divmod(xq + g.pad_l, xs);
+      const int plane = ys * g.stride + xs;
+      const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + yq) * d.wp + xqq;
+      int4 v = make_int4(tile_sh[px][4 * piece], tile_sh[px][4 * piece + 1],
+                         tile_sh[px][4 * piece + 2], tile_sh[px][4 * piece + 3]);
+      *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+    }
+    __syncthreads();   // tile_sh and the stage just read are rewritten next
   }
 }
 
@@ -329,16 +496,14 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
     float4 xv = __ldg(x + i);
     float4 av = a_hat ? a_hat[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     float xs[4] = {xv.x, xv.y, xv.z, xv.w}, as[4] = {av.x, av.y, av.z, av.w}, nv[4];
-    uint32_t word = 0;
+    uint32_t qb[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float qf = rintf(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta));
-      qf = fminf(fmaxf(qf, lo), hi);
-      word |= (uint32_t)((int)qf & 0xff) << (8 * j);
+      const float qf = round_clamp(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta), lo, hi, qb[j]);
       nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
     }
     if (a_hat) a_hat[i] = make_float4(nv[0], nv[1], nv[2], nv[3]);
-    codes[i] = word;
+    codes[i] = pack_low_bytes(qb[0], qb[1], qb[2], qb[3]);
   }
 }
 
@@ -528,6 +693,15 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
 }
 }  // namespace
 
+// MODIFF_MODQ_STAGED=0 selects the register-path encode kernel (debug aid, same outputs)
+static bool staged_encode_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("MODIFF_MODQ_STAGED");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes, float* x_scale,
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     bool compute_scale, cudaStream_t s) {
@@ -561,6 +735,10 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
   TileGrid tg;
   tg.pb = ceil_div(hw, kTileP);
   tg.cb = ceil_div(g->cin, kTileC);
+  tg.per_image = FastDiv(tg.pb * tg.cb);
+  tg.by_pb = FastDiv(tg.pb);
+  tg.by_w = FastDiv(g->w);
+  tg.by_stride = FastDiv(g->stride);
   const int64_t total = (int64_t)tg.pb * tg.cb * g->batch;
   if (total >= (1ll << 31)) return set_error(MODIFF_ERR_INVALID, "activation tensor too large");
   tg.total = (int)total;
@@ -576,6 +754,40 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
     modq_encode_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, codes, x_scale, *g, d, tg,    \
                                                         n_levels, per_sample);                   \
     MODIFF_LAUNCH_CHECK("modq_encode_kernel");                                                   \
+  }
+  if (vec && staged_encode_enabled()) {
+    // three 68 KB blocks per SM keep three tiles of input in flight
+    const int sblocks = tg.total < 148 * 3 ? tg.total : 148 * 3;
+    if (compute_scale) {
+      if (xform) {
+        modq_absmax_kernel<true, true><<<blocks, kThreads, 0, s>>>(
+            src, a_hat, *g, tg, n_levels, per_sample, slots, (ModqScratch*)scratch, x_scale);
+      } else {
+        modq_absmax_kernel<true, false><<<blocks, kThreads, 0, s>>>(
+            src, a_hat, *g, tg, n_levels, per_sample, slots, (ModqScratch*)scratch, x_scale);
+      }
+      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    }
+    static bool attr_set[2] = {false, false};
+    if (xform) {
+      if (!attr_set[1]) {
+        MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_staged_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStagedSmem));
+        attr_set[1] = true;
+      }
+      modq_encode_staged_kernel<true><<<sblocks, kThreads, kStagedSmem, s>>>(
+          src, a_hat, codes, x_scale, *g, d, tg, n_levels, per_sample);
+    } else {
+      if (!attr_set[0]) {
+        MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_staged_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStagedSmem));
+        attr_set[0] = true;
+      }
+      modq_encode_staged_kernel<false><<<sblocks, kThreads, kStagedSmem, s>>>(
+          src, a_hat, codes, x_scale, *g, d, tg, n_levels, per_sample);
+    }
+    MODIFF_LAUNCH_CHECK("modq_encode_staged_kernel");
+    return MODIFF_OK;
   }
   if (vec && xform) MODIFF_MODQ_LAUNCH(true, true)
   else if (vec) MODIFF_MODQ_LAUNCH(true, false)
