@@ -1,0 +1,445 @@
+// Int8 implicit-GEMM for 3x3, stride-1, pad-1 convolutions with activation-tile reuse.
+//
+// igemm_tc_kernel fetches one activation tile per filter tap (nine copies of almost the same
+// pixels) and one weight tile per tap for every 128 output pixels; at these layer sizes the
+// kernel is bound by that shared-memory fill traffic, not by the tensor cores or by HBM.
+// This variant cuts the fill traffic per output pixel by about 40 %:
+//   - an output tile is `rows` full image rows (128 or 256 pixels of ONE image).  For each of
+//     the three horizontal taps dx one copy of rows+2 input rows (shifted by dx) arrives by
+//     TMA; the three vertical taps are the same copy read at a row offset of dy*w*128 bytes,
+//     which is a multiple of the 1024-byte swizzle period, so the UMMA descriptor just starts
+//     later.  3 activation copies per K chunk instead of 9.
+//   - with 256 pixels per tile two M=128 MMAs share every weight tile.
+// Accumulators: int32 in tensor memory, [buffer][m-half][128 columns], double buffered.
+// Epilogue as in igemm_tc_kernel: cached-output half tiles (64 channels x 128 pixels) travel
+// by bulk tensor copies through a small ring, out = o_hat + acc * (delta_x * delta_w[c]).
+// Roles: warp 0 operand TMA, warp 1 MMA issue, warps 2-9 epilogue, warp 10 cached-output
+// stores, warp 11 cached-output loads.  Every mbarrier wait is bounded.
+//
+// Reference arithmetic: qdiff/quant_layer.py:345-365.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace modiff {
+namespace {
+
+constexpr int kChunkK = 128;                     // bytes of K per weight tile row
+constexpr int kBTileBytes = 128 * kChunkK;       // 128 output channels x 128 bytes
+constexpr int kEpiWarps = 8;
+constexpr int kASlots = 2;
+constexpr int kOSlots = 2;
+constexpr int kOHalfBytes = 64 * 128 * 4;        // 64 channels x 128 pixels fp32
+constexpr int kMaxBStages = 6;
+constexpr int kStoreWarp = 2 + kEpiWarps;
+constexpr int kLoadWarp = 3 + kEpiWarps;
+constexpr int kThreads = 32 * (4 + kEpiWarps);
+
+struct HaloParams {
+  int w, h, batch, cout;
+  int rows;             // output rows per tile
+  int mh;               // 128-pixel halves per tile: 1 or 2
+  int half_rows;        // rows / mh
+  int tiles_h;          // h / rows
+  int n_tiles;          // cout / 128
+  int total_tiles;
+  int chunks;           // 128-byte K chunks per tap
+  int kp;               // weight K stride per tap
+  int b_stages;
+  int a_bytes;          // bytes of one activation copy: (rows + 2) * w * 128
+  int a_slot_bytes;
+  int tmem_cols;
+  int accumulate;
+  const float* x_scale;
+  const float* w_scale;
+};
+
+struct HaloTile {
+  int n, th, nt;
+};
+__device__ inline HaloTile decode(int tile, const HaloParams& p) {
+  HaloTile t;
+  t.nt = tile % p.n_tiles;
+  const int m = tile / p.n_tiles;
+  t.th = m % p.tiles_h;
+  t.n = m / p.tiles_h;
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
+                  const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_o, const HaloParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_a_full[kASlots], bar_a_empty[kASlots];
+  __shared__ __align__(8) uint64_t bar_b_full[kMaxBStages], bar_b_empty[kMaxBStages];
+  __shared__ __align__(8) uint64_t bar_tmem_full[2], bar_tmem_empty[2];
+  __shared__ __align__(8) uint64_t bar_o_full[kOSlots], bar_o_empty[kOSlots], bar_o_ready[kOSlots];
+  __shared__ uint32_t tmem_base_sh;
+  __shared__ int abort_sh;
+  __shared__ float ep_scale[128];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &abort_sh;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t a_ring = raw;
+  const uint32_t b_ring = a_ring + kASlots * (uint32_t)p.a_slot_bytes;
+  const uint32_t obuf = b_ring + (uint32_t)p.b_stages * kBTileBytes;
+  float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
+
+  if (threadIdx.x == 0) {
+    abort_sh = 0;
+    for (int s = 0; s < kASlots; ++s) {
+      mbar_init(smem_u32(&bar_a_full[s]), 1);
+      mbar_init(smem_u32(&bar_a_empty[s]), 1);
+    }
+    for (int s = 0; s < p.b_stages; ++s) {
+      mbar_init(smem_u32(&bar_b_full[s]), 1);
+      mbar_init(smem_u32(&bar_b_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[b]), kEpiWarps);
+    }
+    for (int b = 0; b < kOSlots; ++b) {
+      mbar_init(smem_u32(&bar_o_full[b]), 1);
+      mbar_init(smem_u32(&bar_o_empty[b]), 1);
+      mbar_init(smem_u32(&bar_o_ready[b]), kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_base_sh)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_sh;
+  const int buf_cols = p.mh * 128;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ operand TMA producer
+    if (lane == 0) {
+      int aslot = 0, bst = 0;
+      uint32_t aphase = 0, bphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const HaloTile t = decode(tile, p);
+        for (int ch = 0; ch < p.chunks && ok; ++ch) {
+          for (int dx = 0; dx < 3 && ok; ++dx) {
+            ok = mbar_wait(smem_u32(&bar_a_empty[aslot]), aphase ^ 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t afull = smem_u32(&bar_a_full[aslot]);
+            mbar_arrive_expect_tx(afull, (uint32_t)p.a_bytes);
+            // padded input rows th*rows .. th*rows+rows+1, padded columns dx .. dx+w-1
+            tma_load_5d(a_ring + aslot * (uint32_t)p.a_slot_bytes, &map_a, afull, ch * kChunkK, dx,
+                        t.th * p.rows, 0, t.n);
+            if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+            for (int dy = 0; dy < 3; ++dy) {
+              ok = mbar_wait(smem_u32(&bar_b_empty[bst]), bphase ^ 1u, abort_flag);
+              if (!ok) break;
+              const uint32_t bfull = smem_u32(&bar_b_full[bst]);
+              mbar_arrive_expect_tx(bfull, (uint32_t)kBTileBytes);
+              tma_load_2d(b_ring + bst * kBTileBytes, &map_b, bfull,
+                          (dy * 3 + dx) * p.kp + ch * kChunkK, t.nt * 128);
+              if (++bst == p.b_stages) { bst = 0; bphase ^= 1u; }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_i8(128, 128);
+      int aslot = 0, bst = 0, buf = 0;
+      uint32_t aphase = 0, bphase = 0, tphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), tphase ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        bool first = true;
+        for (int ch = 0; ch < p.chunks && ok; ++ch) {
+          for (int dx = 0; dx < 3 && ok; ++dx) {
+            ok = mbar_wait(smem_u32(&bar_a_full[aslot]), aphase, abort_flag);
+            if (!ok) break;
+            const uint32_t a_base = a_ring + aslot * (uint32_t)p.a_slot_bytes;
+            for (int dy = 0; dy < 3; ++dy) {
+              ok = mbar_wait(smem_u32(&bar_b_full[bst]), bphase, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              const uint64_t bdesc = make_smem_desc(b_ring + bst * kBTileBytes);
+              for (int m = 0; m < p.mh; ++m) {
+                // rows m*half_rows+dy .. of the copy: a whole number of 1024-byte swizzle periods
+                const uint64_t adesc = make_smem_desc(
+                    a_base + (uint32_t)((m * p.half_rows + dy) * p.w) * (uint32_t)kChunkK);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * buf_cols + m * 128);
+#pragma unroll
+                for (int k = 0; k < kChunkK / 32; ++k)
+                  tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            (first && k == 0) ? 0u : 1u);
+              }
+              first = false;
+              tc_commit(smem_u32(&bar_b_empty[bst]));
+              if (++bst == p.b_stages) { bst = 0; bphase ^= 1u; }
+            }
+            if (!ok) break;
+            tc_commit(smem_u32(&bar_a_empty[aslot]));
+            if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+          }
+        }
+        if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        if (++buf == 2) { buf = 0; tphase ^= 1u; }
+      }
+    }
+  } else if (warp == kLoadWarp) {
+    // ------------------------------------------------------------ cached-output loads
+    if (lane == 0) {
+      int oslot = 0;
+      uint32_t ophase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const HaloTile t = decode(tile, p);
+        for (int m = 0; m < p.mh && ok; ++m) {
+          for (int hh = 0; hh < 2; ++hh) {
+            ok = mbar_wait(smem_u32(&bar_o_empty[oslot]), ophase ^ 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t ofull = smem_u32(&bar_o_full[oslot]);
+            if (p.accumulate) {
+              mbar_arrive_expect_tx(ofull, (uint32_t)kOHalfBytes);
+              tma_load_3d(obuf + oslot * kOHalfBytes, &map_o, ofull,
+                          (t.th * p.rows + m * p.half_rows) * p.w, t.nt * 128 + hh * 64, t.n);
+            } else {
+              mbar_arrive(ofull);
+            }
+            if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == kStoreWarp) {
+    // ------------------------------------------------------------ cached-output stores
+    if (lane == 0) {
+      int oslot = 0;
+      uint32_t ophase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const HaloTile t = decode(tile, p);
+        for (int m = 0; m < p.mh && ok; ++m) {
+          for (int hh = 0; hh < 2; ++hh) {
+            ok = mbar_wait(smem_u32(&bar_o_ready[oslot]), ophase, abort_flag);
+            if (!ok) break;
+            tma_store_3d(&map_o, obuf + oslot * kOHalfBytes,
+                         (t.th * p.rows + m * p.half_rows) * p.w, t.nt * 128 + hh * 64, t.n);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            mbar_arrive(smem_u32(&bar_o_empty[oslot]));
+            if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+          }
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Two warps share each tensor-memory lane quarter; each takes 32 of the 64 channels of a
+    // half tile.  A lane is one output pixel, so shared-memory accesses of a warp are 32
+    // consecutive floats of one channel row.
+    const int quarter = warp & 3;
+    const int sub = (warp - 2) >> 2;
+    const int ep_tid = threadIdx.x - 64;
+    const int row = quarter * 32 + lane;
+    int buf = 0, oslot = 0, last_nt = -1;
+    uint32_t tphase = 0, ophase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      const HaloTile t = decode(tile, p);
+      if (t.nt != last_nt) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ep_tid < 128)
+          ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * 128 + ep_tid]);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        last_nt = t.nt;
+      }
+      if (ok) ok = mbar_wait(smem_u32(&bar_tmem_full[buf]), tphase, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      for (int m = 0; m < p.mh && ok; ++m) {
+        const uint32_t t_row =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * buf_cols + m * 128);
+        for (int hh = 0; hh < 2; ++hh) {
+          ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
+          if (!ok) break;
+          float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)(sub * 32) * 128 + row;
+          const int colbase = hh * 64 + sub * 32;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * 128] : 0.0f;
+          int a[32];
+          tc_ld32(t_row + colbase, a);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) orow[j * 128] = v[j];
+          const bool last = (m == p.mh - 1) && (hh == 1);
+          if (last) tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&bar_o_ready[oslot]));
+            if (last) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+          }
+          if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+        }
+      }
+      if (!ok) break;
+      if (++buf == 2) { buf = 0; tphase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (abort_sh) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);   // let copies in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+  }
+}
+
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// share of the last wave that does work when `tiles` tiles run on `sms` persistent CTAs
+double wave_efficiency(int tiles, int sms) {
+  const int waves = (tiles + sms - 1) / sms;
+  return (double)tiles / ((double)waves * sms);
+}
+
+}  // namespace
+
+// Whether the activation-reuse kernel covers this call.
+bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
+                    const int32_t* acc_out, const float* o_hat) {
+  if (g->kh != 3 || g->kw != 3 || g->stride != 1) return false;
+  if (g->pad_t != 1 || g->pad_b != 1 || g->pad_l != 1 || g->pad_r != 1) return false;
+  if (with_sum_rows || per_sample || bias || acc_out || g->split != 0) return false;
+  if (g->cout % 128 != 0 || g->cin < 128 || g->cin % 16 != 0) return false;
+  if (!is_pow2(g->w) || !is_pow2(g->h) || g->w < 16 || g->w > 64) return false;
+  if (g->h * g->w < 128 || (128 / g->w) > g->h) return false;
+  if (((uintptr_t)o_hat & 15) != 0) return false;
+  return true;
+}
+
+int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_scale,
+                      const float* w_scale, float* o_hat, int accumulate,
+                      const modiff_conv_geom* g, cudaStream_t s) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    MODIFF_CUDA(cudaGetDevice(&dev));
+    MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  Derived d = derive(*g);
+  HaloParams p;
+  p.w = g->w;
+  p.h = g->h;
+  p.batch = g->batch;
+  p.cout = g->cout;
+  p.n_tiles = g->cout / 128;
+  // 256-pixel tiles halve the weight traffic but can leave the last wave emptier: compare
+  // shared-memory fill bytes per 128 output pixels divided by the wave efficiency
+  const int rows1 = 128 / g->w, rows2 = 256 / g->w;
+  const int chunks = ceil_div(g->cin, kChunkK);
+  auto cost = [&](int mh) {
+    const int rows = mh * rows1;
+    const double fill = (3.0 * chunks * (rows + 2) * g->w * kChunkK + 9.0 * chunks * kBTileBytes) / mh +
+                        4.0 * kOHalfBytes;
+    return fill / wave_efficiency(g->batch * (g->h / rows) * p.n_tiles, sm_count);
+  };
+  p.mh = 1;
+  if (rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
+  p.rows = p.mh * rows1;
+  p.half_rows = rows1;
+  p.tiles_h = g->h / p.rows;
+  p.total_tiles = g->batch * p.tiles_h * p.n_tiles;
+  p.chunks = chunks;
+  p.kp = d.kp;
+  p.a_bytes = (p.rows + 2) * g->w * kChunkK;
+  p.a_slot_bytes = round_up(p.a_bytes, 1024);
+  const int fixed = kASlots * p.a_slot_bytes + kOSlots * kOHalfBytes;
+  p.b_stages = (224 * 1024 - fixed) / kBTileBytes;
+  if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
+  if (p.b_stages < 3) return set_error(MODIFF_ERR_UNSUPPORTED, "tile does not fit shared memory");
+  p.tmem_cols = p.mh == 2 ? 512 : 256;
+  p.accumulate = accumulate;
+  p.x_scale = x_scale;
+  p.w_scale = w_scale;
+  const size_t smem = (size_t)fixed + (size_t)p.b_stages * kBTileBytes;
+
+  CUtensorMap map_a, map_b, map_o;
+  {
+    cuuint64_t dims[5] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp, (cuuint64_t)d.hp, 1u,
+                          (cuuint64_t)g->batch};
+    cuuint64_t strides[4] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp * d.cp,
+                             (cuuint64_t)d.hp * d.wp * d.cp, (cuuint64_t)d.hp * d.wp * d.cp};
+    cuuint32_t box[5] = {(cuuint32_t)kChunkK, (cuuint32_t)g->w, (cuuint32_t)(p.rows + 2), 1u, 1u};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void*)codes, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(activation codes) failed: %d", (int)r);
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp, (cuuint64_t)g->cout};
+    cuuint64_t strides[1] = {(cuuint64_t)d.taps * d.kp};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkK, 128u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)wcodes, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(weight codes) failed: %d", (int)r);
+  }
+  {
+    const int hw = g->h * g->w;
+    cuuint64_t dims[3] = {(cuuint64_t)hw, (cuuint64_t)g->cout, (cuuint64_t)g->batch};
+    cuuint64_t strides[2] = {(cuuint64_t)hw * 4, (cuuint64_t)g->cout * hw * 4};
+    cuuint32_t box[3] = {128u, 64u, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&map_o, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)o_hat, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output) failed: %d", (int)r);
+  }
+
+  static size_t attr_bytes = 0;
+  if (smem > attr_bytes) {
+    MODIFF_CUDA(cudaFuncSetAttribute(igemm_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+    attr_bytes = smem;
+  }
+  const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
+  igemm_halo_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);
+  MODIFF_LAUNCH_CHECK("igemm_halo_kernel");
+  return MODIFF_OK;
+}
+
+int read_device_status_halo(int* status, int reset) { return read_status_this_unit(status, reset); }
+
+}  // namespace modiff

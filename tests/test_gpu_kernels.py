@@ -165,7 +165,8 @@ def test_weight_pack_bit_exact(cuda, bits, split, with_sum):
         assert int(codes[129:144].abs().sum()) == 0
 
 
-def _run_igemm(x_codes, w, g, bits_w, impl, dev, x_scale=(0.01, 0.02), accumulate=True, bias=None):
+def _run_igemm(x_codes, w, g, bits_w, impl, dev, x_scale=(0.01, 0.02), accumulate=True, bias=None,
+               want_acc=True):
     """x_codes: [B, C, H, W] int8 (host).  Returns (out, acc) from the device."""
     L = _lib()
     l = L.lib()
@@ -191,7 +192,7 @@ def _run_igemm(x_codes, w, g, bits_w, impl, dev, x_scale=(0.01, 0.02), accumulat
     L.check(l.modiff_igemm_conv(codes.data_ptr(), wcodes.data_ptr(), with_sum, xs.data_ptr(),
                                 ws.data_ptr(), wc.data_ptr() if need_corr else None,
                                 o_hat.data_ptr(), int(accumulate), L.ptr(bias), C.byref(g), 0, impl,
-                                acc.data_ptr(), L.stream_ptr()))
+                                acc.data_ptr() if want_acc else None, L.stream_ptr()))
     torch.cuda.synchronize()
     assert L.device_status() == 0, "a bounded wait ran out inside the kernel"
     return o_hat.cpu(), acc.cpu().view(nseg, g.batch, ho, wo, g.cout), o_prev, ws.cpu()
@@ -246,6 +247,41 @@ def test_igemm_accumulators_exact(cuda, case, impl):
         exp = exp + a.double() * (float(np.float32(xs[s])) * dw.double().view(1, -1, 1, 1))
     err = (out.double() - exp).abs().max() / exp.abs().max()
     assert err < 1e-5, err    # fp32 epilogue vs float64 evaluation of the same integers
+
+
+HALO_CASES = [
+    # batch, cin, cout, hw: 3x3 stride-1 pad-1 layers that take the activation-reuse kernel
+    (5, 128, 128, 32),      # 256-pixel tiles (8 rows), one K chunk
+    (3, 256, 256, 16),      # whole image per tile or 8-row tiles, two K chunks, two channel tiles
+    (1, 320, 128, 64),      # 4-row tiles, last K chunk partly beyond cin
+    (2, 192, 384, 16),      # three channel tiles
+    (150, 128, 128, 16),    # more tiles than SMs: every CTA walks several tiles
+]
+
+
+@pytest.mark.parametrize("accumulate", [True, False])
+@pytest.mark.parametrize("case", HALO_CASES, ids=lambda c: "b%d_c%d_o%d_hw%d" % c)
+def test_igemm_activation_reuse_kernel(cuda, case, accumulate, monkeypatch):
+    """The 3x3 kernel that reuses one activation copy for three filter taps gives the same
+    bits as the one-copy-per-tap kernel and matches the exact integer convolution."""
+    b, cin, cout, hw = case
+    L = _lib()
+    g = _geom(b, cin, cout, hw, hw, k=3, stride=1, pad=(1, 1, 1, 1))
+    torch.manual_seed(12)
+    x_codes = torch.randint(-8, 8, (b, cin, hw, hw), dtype=torch.int8)
+    w = torch.randn(cout, cin, 3, 3) * 0.05
+    outs = []
+    for halo in ("1", "0"):
+        monkeypatch.setenv("MODIFF_IGEMM_HALO", halo)
+        out, _, o_prev, ws = _run_igemm(x_codes, w, g, 4, L.IMPL_TCGEN05, cuda, accumulate=accumulate,
+                                        want_acc=False)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    exp_acc, dws = _expected_acc(x_codes, w, g, 4)
+    exp = o_prev.double() if accumulate else torch.zeros_like(o_prev).double()
+    exp = exp + exp_acc[0].double() * (float(np.float32(0.01)) * dws[0].double().view(1, -1, 1, 1))
+    err = (outs[0].double() - exp).abs().max() / exp.abs().max()
+    assert err < 1e-5, err
 
 
 def test_conv_fp32_matches_torch(cuda):
