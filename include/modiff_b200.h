@@ -156,6 +156,28 @@ int modiff_modq_gn(const modiff_act_source* src, const float* film, const float*
                    int8_t* codes, float* x_scale, const modiff_conv_geom* g, int n_bits,
                    int per_sample, void* scratch, void* stream);
 
+/* One launch for several modulated linear layers that read the same activation codes (every
+ * residual block's projection of swish(temb): ddim/models/diffusion.py:121-123, 297-301;
+ * ldm/modules/diffusionmodules/openaimodel.py:236-262): for each item
+ *   o_hat[row][c] += (sum_k codes[row][k] * wcode[c][k] + w_corr[c] * sum_k codes[row][k])
+ *                    * x_scale[0] * w_scale[c]                  (qdiff/quant_layer.py:345-365).
+ *   codes     [rows][cin] int8, from modiff_modq of a linear geometry (cin a multiple of 16)
+ *   items     DEVICE array, one per layer; wcodes / w_scale / w_corr as modiff_weight_pack
+ *             wrote them for a (cin -> cout, 1x1) geometry, o_hat [rows][cout] fp32
+ *   block_map DEVICE int32 [n_blocks][2]: (item index, first output channel) of each block;
+ *             a block covers 16 output channels, so an item needs ceil(cout / 16) entries */
+typedef struct modiff_linear_item {
+  const int8_t* wcodes;
+  const float* w_scale;
+  const int32_t* w_corr;      /* NULL when the layer needs no correction */
+  float* o_hat;
+  int32_t cout;
+  int32_t with_sum_rows;      /* layout flag given to modiff_weight_pack */
+} modiff_linear_item;
+int modiff_linear_group(const int8_t* codes, const float* x_scale, int rows, int cin,
+                        const modiff_linear_item* items, const int32_t* block_map, int n_blocks,
+                        void* stream);
+
 /* Same quantiser as modiff_modq for callers that cannot hand over scratch memory.
  * This entry point has no counterpart in the reference; it exists for hosts that must not
  * allocate once they are running - for example a serving process whose device memory is

@@ -41,6 +41,12 @@ class ActSourceStruct(C.Structure):
                 ("affine", C.c_void_p), ("chan_bias", C.c_void_p)]
 
 
+class LinearItem(C.Structure):
+    """Mirror of `modiff_linear_item`."""
+    _fields_ = [("wcodes", C.c_void_p), ("w_scale", C.c_void_p), ("w_corr", C.c_void_p),
+                ("o_hat", C.c_void_p), ("cout", C.c_int32), ("with_sum_rows", C.c_int32)]
+
+
 class GemmBf16Desc(C.Structure):
     """Mirror of `modiff_gemm_bf16_desc`."""
     _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("col_scale", C.c_void_p),
@@ -70,6 +76,7 @@ SIGNATURES = {
     "modiff_modq_gn": (C.c_int, [C.POINTER(ActSourceStruct), _P, _P, _P, C.c_int, C.c_float, _P, _P,
                                  _P, _P, _G, C.c_int, C.c_int, _P, _P]),
     "modiff_modq_static": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P]),
+    "modiff_linear_group": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, C.c_int, _P]),
     "modiff_igemm_conv": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, _P, _G, C.c_int,
                                     C.c_int, _P, _P]),
     "modiff_im2col_codes": (C.c_int, [_P, _P, _G, C.c_int, _P]),
@@ -125,7 +132,7 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_gn": 2, "modiff_modq_static": 2, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
+    "modiff_weight_pack": 2, "modiff_modq": 2, "modiff_modq_src": 2, "modiff_modq_gn": 2, "modiff_modq_static": 2, "modiff_linear_group": 1, "modiff_igemm_conv": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
     "modiff_weights_bf16": 1, "modiff_gemm_bf16": 1, "modiff_softmax_split": 1, "modiff_attention_small": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_layernorm": 1, "modiff_geglu": 1, "modiff_transpose": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,

@@ -182,6 +182,12 @@ class QuantModule(nn.Module):
         # private device state
         self._a_store = None      # storage of a_hat / o_hat, kept across reset_cache() so that
         self._o_store = None      # device addresses stay valid for captured CUDA graphs
+        # small linear layers that share this layer's residual codes (forward_shared) are
+        # computed together with it in one launch; see _group_launch
+        self._group_members = []
+        self._group_table = None
+        self._group_served = None   # (owner id, owner step) of the grouped launch that wrote o_hat
+        self._group_step = 0
         self._buffers = {}
         self._wpack = None
         self._org_kn = None
@@ -322,7 +328,8 @@ class QuantModule(nn.Module):
         def pow2(v):
             return v > 0 and (v & (v - 1)) == 0
         ho, wo = ho_wo
-        return (g.cin >= 64 and g.cin % 8 == 0 and g.cout >= 16 and pow2(ho) and pow2(wo)
+        return (g.cin >= 64 and g.cin % 8 == 0 and g.cout >= 16
+                and (g.cout >= 128 or g.cout % 16 == 0) and pow2(ho) and pow2(wo)
                 and wo <= 128 and g.split % 64 == 0 and g.kh <= 7 and g.kw <= 7)
 
     def _conv_first_step(self, x, pack, bias, g, out, ho_wo):
@@ -505,6 +512,7 @@ class QuantModule(nn.Module):
                 # first step: activations pass through unquantised (quant_layer.py:326-327, 358-359)
                 if shared:
                     self.a_hat = _owner.a_hat
+                    _owner._group_register(self, g)
                 else:
                     self._a_store = self._reuse(self._a_store, input.shape, input.device)
                     self._a_store.copy_(input)
@@ -519,15 +527,72 @@ class QuantModule(nn.Module):
                                       f"{tuple(self.a_hat.shape)}; call reset_cache() first")
                 if shared and self.a_hat is _owner.a_hat:
                     buf = obuf             # the owner's quantiser already ran on this input
+                    if self._group_served != (id(_owner), _owner._group_step):
+                        self._igemm(buf, pack, self.o_hat, True, None, g)
                 else:
                     self._modq(input, self.a_hat, buf, g, src)
-                self._igemm(buf, pack, self.o_hat, True, None, g)
+                    if not self._group_launch(buf, pack, g):
+                        self._igemm(buf, pack, self.o_hat, True, None, g)
             out = self.o_hat if self.alias_output else self.o_hat.clone()
         else:
             out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
             self._modq(input, None, buf, g)
             self._igemm(buf, pack, out, False, bias, g)
         return self.activation_function(out)
+
+    # ------------------------------------------------------------------ grouped small linears
+    group_small_linears = os.environ.get("MODIFF_LINEAR_GROUP", "1") != "0"
+    _GROUP_MAX_ROWS = 512
+
+    def _group_register(self, member, g):
+        """Called on the first step by a layer that shares this layer's codes.  Small linear
+        layers (every residual block's projection of the same swish(temb)) are remembered; from
+        the next step on they are evaluated together with this layer in one launch."""
+        if not (self.group_small_linears and g.h == 1 and g.w == 1 and g.kh == 1 and g.kw == 1
+                and g.split == 0 and g.batch <= self._GROUP_MAX_ROWS and g.cin % 16 == 0
+                and not self.act_quantizer.channel_wise and self.fwd_func is F.linear
+                and member.fwd_func is F.linear):
+            return
+        if all(m is not member for m in self._group_members):
+            self._group_members.append(member)
+            self._group_table = None
+
+    def _group_launch(self, buf, pack, g):
+        """One launch for this layer and the registered layers that share its codes
+        (`modiff_linear_group`); False when there is nothing to group."""
+        members = self._group_members
+        if not members or self.fwd_func is not F.linear or g.split != 0:
+            return False
+        layers = [self] + members
+        for m in members:
+            if m.a_hat is not self.a_hat or m.o_hat is None or m._wpack is None:
+                return False
+        sig = tuple((m.o_hat.data_ptr(), m._wpack['wcodes'].data_ptr()) for m in layers)
+        if self._group_table is None or self._group_table['sig'] != sig:
+            items = (_lib.LinearItem * len(layers))()
+            block_map = []
+            for i, m in enumerate(layers):
+                p = m._wpack
+                cout = m.weight.shape[0]
+                items[i] = _lib.LinearItem(p['wcodes'].data_ptr(), p['w_scale'].data_ptr(),
+                                           _lib.ptr(p['w_corr']), m.o_hat.data_ptr(), cout,
+                                           int(p['with_sum']))
+                block_map += [(i, c0) for c0 in range(0, cout, 16)]
+            raw = torch.frombuffer(bytearray(bytes(items)), dtype=torch.uint8).to(buf.codes.device)
+            bm = torch.tensor(block_map, dtype=torch.int32, device=buf.codes.device)
+            torch.cuda.current_stream().synchronize()
+            self._group_table = dict(sig=sig, items=raw, block_map=bm, n_blocks=len(block_map),
+                                     keep=[m._wpack for m in layers])
+        tab = self._group_table
+        rows = g.batch
+        nbytes = sum(8 * rows * m.weight.shape[0] for m in layers) + rows * g.cin
+        _lib.call('modiff_linear_group', buf.codes.data_ptr(), buf.x_scale.data_ptr(), rows, g.cin,
+                  tab['items'].data_ptr(), tab['block_map'].data_ptr(), tab['n_blocks'],
+                  _lib.stream_ptr(), nbytes=nbytes, tag=g.key())
+        self._group_step += 1
+        for m in members:
+            m._group_served = (id(self), self._group_step)
+        return True
 
     @staticmethod
     def _reuse(store, shape, device):

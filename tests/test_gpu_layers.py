@@ -175,3 +175,47 @@ def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, spli
         # output by ~1e-3 of its range, 4-bit codes by ~1e-2
         assert err < (2e-3 if a_bits == 8 else 3e-2), (step, float(err))
     assert m.device_status() == 0
+
+
+@pytest.mark.parametrize("w_bits", [4, 8])
+def test_small_linears_sharing_codes_run_in_one_launch(cuda, w_bits):
+    """Projections of the same swish(temb) by several residual blocks
+    (ddim/models/diffusion.py:121-123): evaluated in one grouped launch they give the same
+    outputs as one launch per layer, and both follow the oracle."""
+    import modiff_b200 as m
+    torch.manual_seed(21)
+    couts = [256, 128, 40, 256]
+    orgs = [torch.nn.Linear(512, c) for c in couts]
+    wq = {'n_bits': w_bits, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    orcs = [oracle.OracleQuantModule(o.weight.detach().clone(), o.bias.detach().clone(),
+                                     w_bits=w_bits, a_bits=8) for o in orgs]
+    sets = []
+    for grouped in (True, False):
+        mods = [m.QuantModule(copy.deepcopy(o), wq, aq, modulate=True).to(cuda) for o in orgs]
+        for q in mods:
+            q.set_quant_state(True, True)
+            q.alias_output = False
+            q.group_small_linears = grouped
+        sets.append(mods)
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(48, 512, generator=g)
+    launches = []
+    for step in range(4):
+        xs = x + 0.03 * step * torch.randn(48, 512, generator=g)
+        refs = [o.forward(xs) for o in orcs]
+        outs = []
+        for mods in sets:
+            before = m._lib.LAUNCHES[0]
+            xc = xs.to(cuda)
+            with torch.no_grad():
+                ys = [mods[0](xc)] + [q.forward_shared(mods[0], xc) for q in mods[1:]]
+            launches.append(m._lib.LAUNCHES[0] - before)
+            outs.append([y.cpu() for y in ys])
+        for a, b, r in zip(outs[0], outs[1], refs):
+            assert (a - b).abs().max() <= 1e-6 * b.abs().max()
+            assert (a - r).abs().max() <= 2e-5 * r.abs().max()
+    # steps >= 1: quantiser (2 kernels) + 1 grouped launch, against quantiser + 4 GEMM launches
+    assert launches[-2:] == [3, 6]
+    assert m.device_status() == 0
