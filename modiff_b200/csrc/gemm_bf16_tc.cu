@@ -341,48 +341,109 @@ split_bf16_planes_kernel(const float* __restrict__ x, uint16_t* __restrict__ out
 }
 
 // x[nb][rows][len] fp32 -> out[nb][2][rows_pad][len_pad] bf16 (zero padding, no transposition).
-__global__ void split_bf16_rows_kernel(const float* __restrict__ x, uint16_t* __restrict__ out,
-                                       int64_t nb, int rows, int len, int rows_pad, int len_pad) {
-  const int64_t total = nb * rows_pad * len_pad;
+// One thread converts eight consecutive elements of a row (two 16-byte loads, two 16-byte
+// stores); VEC8 needs len and len_pad to be multiples of 8 and 16-byte aligned buffers.
+template <bool VEC8>
+__global__ void __launch_bounds__(256)
+split_bf16_rows_kernel(const float* __restrict__ x, uint16_t* __restrict__ out, int64_t nb,
+                       int rows, int len, int rows_pad, int len_pad) {
+  const int groups = (len_pad + 7) / 8;                 // 8-element groups per padded row
+  const int64_t total = nb * rows_pad * groups;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t plane = (int64_t)rows_pad * len_pad;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int c = (int)(i % len_pad);
-    const int r = (int)((i / len_pad) % rows_pad);
-    const int64_t b = i / ((int64_t)len_pad * rows_pad);
-    float v = 0.0f;
-    if (r < rows && c < len) v = __ldg(x + (b * rows + r) * len + c);
-    const uint16_t h = bf16_rn(v);
-    const int64_t o = ((b * 2) * rows_pad + r) * len_pad + c;
-    out[o] = h;
-    out[o + (int64_t)rows_pad * len_pad] = bf16_rn(v - bf16_to_f(h));
+    const int64_t row = i / groups;                     // b * rows_pad + r
+    const int c0 = (int)(i - row * groups) * 8;
+    const int64_t b = row / rows_pad;
+    const int r = (int)(row - b * rows_pad);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+    if (r < rows) {
+      const float* src = x + (b * rows + r) * (int64_t)len + c0;
+      if (VEC8) {
+        if (c0 < len) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+          const float4 c = __ldg(reinterpret_cast<const float4*>(src) + 1);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+          v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (c0 + k < len) v[k] = __ldg(src + k);
+      }
+    }
+    uint16_t h[8], l[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      h[k] = bf16_rn(v[k]);
+      l[k] = bf16_rn(v[k] - bf16_to_f(h[k]));
+    }
+    uint16_t* dst = out + (b * 2 * rows_pad + r) * (int64_t)len_pad + c0;
+    if (VEC8) {
+      uint4 hv, lv;
+      hv.x = h[0] | ((uint32_t)h[1] << 16); hv.y = h[2] | ((uint32_t)h[3] << 16);
+      hv.z = h[4] | ((uint32_t)h[5] << 16); hv.w = h[6] | ((uint32_t)h[7] << 16);
+      lv.x = l[0] | ((uint32_t)l[1] << 16); lv.y = l[2] | ((uint32_t)l[3] << 16);
+      lv.z = l[4] | ((uint32_t)l[5] << 16); lv.w = l[6] | ((uint32_t)l[7] << 16);
+      *reinterpret_cast<uint4*>(dst) = hv;
+      *reinterpret_cast<uint4*>(dst + plane) = lv;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (c0 + k < len_pad) {
+          dst[k] = h[k];
+          dst[k + plane] = l[k];
+        }
+    }
   }
 }
 
 // Softmax over keys of S[image][key][query] (the layout the GEMM epilogue writes: keys are the
 // output "channels") -> probabilities as split bf16 planes P[image][2][query][key], the A
 // operand of the second attention GEMM (qdiff/quant_block.py:353-358).
-constexpr int kSmQ = 32, kSmKeys = 256;
+// A block owns 32 queries; a thread owns one query and every eighth key.  With at most
+// kSmRegKeys keys the scores are read ONCE into registers (exp evaluated once per score).
+constexpr int kSmQ = 32, kSmKeys = 256, kSmRegKeys = 256;
+template <bool IN_REGS>
 __global__ void __launch_bounds__(256)
 softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int tk, int tq,
                      int tk_pad) {
   __shared__ float red[8][kSmQ];
-  __shared__ uint16_t stage[2][kSmQ][kSmKeys + 8];
+  __shared__ uint16_t stage[2][kSmQ][kSmKeys + 2];   // odd word pitch: conflict-free columns
   const int b = blockIdx.y;
   const int q0 = blockIdx.x * kSmQ;
   const int q = threadIdx.x & 31, kg = threadIdx.x >> 5;
   const bool qv = (q0 + q) < tq;
   const float* sb = s + (size_t)b * tk * tq + q0 + q;
+  float e[IN_REGS ? kSmRegKeys / 8 : 1];
   float mx = -INFINITY;
-  if (qv)
+  if (IN_REGS) {
+#pragma unroll
+    for (int i = 0; i < kSmRegKeys / 8; ++i) {
+      const int k = kg + 8 * i;
+      e[i] = (qv && k < tk) ? __ldg(sb + (size_t)k * tq) : -INFINITY;
+      mx = fmaxf(mx, e[i]);
+    }
+  } else if (qv) {
     for (int k = kg; k < tk; k += 8) mx = fmaxf(mx, __ldg(sb + (size_t)k * tq));
+  }
   red[kg][q] = mx;
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < 8; ++i) mx = fmaxf(mx, red[i][q]);
   __syncthreads();
   float sum = 0.0f;
-  if (qv)
+  if (IN_REGS) {
+#pragma unroll
+    for (int i = 0; i < kSmRegKeys / 8; ++i) {
+      e[i] = (qv && kg + 8 * i < tk) ? expf(e[i] - mx) : 0.0f;
+      sum += e[i];
+    }
+  } else if (qv) {
     for (int k = kg; k < tk; k += 8) sum += expf(__ldg(sb + (size_t)k * tq) - mx);
+  }
   red[kg][q] = sum;
   __syncthreads();
   sum = 0.0f;
@@ -391,20 +452,40 @@ softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int 
   const float inv = 1.0f / sum;
   for (int k0 = 0; k0 < tk_pad; k0 += kSmKeys) {
     __syncthreads();
-    for (int k = kg; k < kSmKeys && k0 + k < tk_pad; k += 8) {
-      const float pv = (qv && k0 + k < tk) ? expf(__ldg(sb + (size_t)(k0 + k) * tq) - mx) * inv : 0.0f;
-      const uint16_t h = bf16_rn(pv);
-      stage[0][q][k] = h;
-      stage[1][q][k] = bf16_rn(pv - bf16_to_f(h));
+    if (IN_REGS) {
+#pragma unroll
+      for (int i = 0; i < kSmRegKeys / 8; ++i) {
+        const int k = kg + 8 * i;
+        if (k < tk_pad) {
+          const float pv = e[i] * inv;
+          const uint16_t h = bf16_rn(pv);
+          stage[0][q][k] = h;
+          stage[1][q][k] = bf16_rn(pv - bf16_to_f(h));
+        }
+      }
+    } else {
+      for (int k = kg; k < kSmKeys && k0 + k < tk_pad; k += 8) {
+        const float pv =
+            (qv && k0 + k < tk) ? expf(__ldg(sb + (size_t)(k0 + k) * tq) - mx) * inv : 0.0f;
+        const uint16_t h = bf16_rn(pv);
+        stage[0][q][k] = h;
+        stage[1][q][k] = bf16_rn(pv - bf16_to_f(h));
+      }
     }
     __syncthreads();
-    // each warp writes whole query rows: contiguous keys
+    // each warp writes whole query rows: contiguous keys, 4 bytes per lane when aligned
     const int nk = min(kSmKeys, tk_pad - k0);
     for (int r = kg; r < kSmQ; r += 8) {
       if (q0 + r >= tq) continue;
       for (int part = 0; part < 2; ++part) {
         uint16_t* dst = p + (((size_t)b * 2 + part) * tq + q0 + r) * tk_pad + k0;
-        for (int k = q; k < nk; k += 32) dst[k] = stage[part][r][k];
+        if ((nk & 1) == 0 && (tk_pad & 1) == 0) {
+          for (int k = 2 * q; k < nk; k += 64)
+            *reinterpret_cast<uint32_t*>(dst + k) =
+                *reinterpret_cast<const uint32_t*>(&stage[part][r][k]);
+        } else {
+          for (int k = q; k < nk; k += 32) dst[k] = stage[part][r][k];
+        }
       }
     }
   }
@@ -479,10 +560,16 @@ extern "C" int modiff_split_bf16_rows(const float* x, uint16_t* out, int64_t nb,
                                       int rows_pad, int len_pad, void* stream) {
   MODIFF_CHECK_ARG(x && out && nb > 0 && rows > 0 && len > 0 && rows_pad >= rows && len_pad >= len,
                    "bad argument");
-  int64_t blocks = ceil_div64(nb * rows_pad * len_pad, 256);
+  int64_t blocks = ceil_div64(nb * rows_pad * ((len_pad + 7) / 8), 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  split_bf16_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(x, out, nb, rows, len,
-                                                                       rows_pad, len_pad);
+  const bool vec = (len % 8 == 0) && (len_pad % 8 == 0) &&
+                   ((((uintptr_t)x | (uintptr_t)out) & 15) == 0);
+  if (vec)
+    split_bf16_rows_kernel<true><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+        x, out, nb, rows, len, rows_pad, len_pad);
+  else
+    split_bf16_rows_kernel<false><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+        x, out, nb, rows, len, rows_pad, len_pad);
   MODIFF_LAUNCH_CHECK("split_bf16_rows_kernel");
   return MODIFF_OK;
 }
@@ -508,7 +595,10 @@ extern "C" int modiff_softmax_split(const float* s, uint16_t* p, int batch, int 
   MODIFF_CHECK_ARG(s && p && batch > 0 && tk > 0 && tq > 0 && tk_pad >= tk, "bad argument");
   MODIFF_CHECK_ARG(batch <= 65535, "batch*heads %d exceeds the grid limit 65535", batch);
   dim3 grid(ceil_div(tq, kSmQ), batch);
-  softmax_split_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(s, p, tk, tq, tk_pad);
+  if (tk_pad <= kSmRegKeys)
+    softmax_split_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(s, p, tk, tq, tk_pad);
+  else
+    softmax_split_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(s, p, tk, tq, tk_pad);
   MODIFF_LAUNCH_CHECK("softmax_split_kernel");
   return MODIFF_OK;
 }
