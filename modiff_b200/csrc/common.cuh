@@ -144,7 +144,8 @@ __device__ inline void block_sum2(float& a, float& b, float* sh) {
 // Launch shape of the GroupNorm kernels for one (image, group) slab of `count` elements.  The
 // statistics are summed per thread and then over the block, so two kernels agree on the last
 // bit of mean and variance only when they use the same thread count.
-inline int groupnorm_threads(int count) { return count >= 8192 ? 512 : (count >= 1024 ? 256 : 128); }
+// Slabs under 1024 elements are summed by ONE warp (no block barrier on the critical path).
+inline int groupnorm_threads(int count) { return count >= 8192 ? 512 : (count >= 1024 ? 256 : 32); }
 // log2(hw / 4) when hw / 4 is a power of two, else -1
 inline int groupnorm_lg_hw4(int hw) {
   if (hw % 4 != 0) return -1;

@@ -691,6 +691,154 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
     if (threadIdx.x == 0) scratch->counter = 0u;
   }
 }
+
+// The same sweep for slabs under 1024 elements (the 4x4 and 8x8 levels of the UNet): one WARP
+// per slab, eight independent slabs per block, warp shuffles instead of block barriers.  The
+// per-lane order and the butterfly are those of a 32-thread groupnorm_silu_kernel block.
+template <int NV>
+__global__ void __launch_bounds__(256)
+gn_absmax_warp_kernel(const SrcView src, const float* __restrict__ film, float* __restrict__ affine,
+                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                      const float* __restrict__ a_hat, int batch, int c, int hw, int groups,
+                      float eps, int lg_hw4, int split, int n_levels, int per_sample, int slots,
+                      ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
+  __shared__ float s0[8], s1[8];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int cpg = c / groups;            // <= 32: lane k keeps the parameters of channel k
+  const int count = cpg * hw;
+  const int total4 = cpg << lg_hw4;
+  const int items = batch * groups;
+  const bool has_bias = src.bias != nullptr;
+
+  float m0 = 0.0f, m1 = 0.0f;
+  int cur_n = -1;
+  for (int item = blockIdx.x * wpb + warp; item < items; item += gridDim.x * wpb) {
+    const int n = item / groups;
+    const int cbeg = (item - n * groups) * cpg;
+    if (per_sample && n != cur_n) {
+      if (cur_n >= 0) {
+        float v = m0;
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0 && v > 0.0f) atomicMax(&scratch->absmax_bits[cur_n], __float_as_uint(v));
+      }
+      m0 = 0.0f;
+      cur_n = n;
+    }
+    const float4* xs = reinterpret_cast<const float4*>(
+        (cbeg < src.c0) ? src.x0 + ((size_t)n * src.c0 + cbeg) * hw
+                        : src.x1 + ((size_t)n * src.c1 + (cbeg - src.c0)) * hw);
+    const float4* as = a_hat
+        ? reinterpret_cast<const float4*>(a_hat + ((size_t)n * c + cbeg) * hw) : nullptr;
+    float4 xv[NV], av[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + 32 * k;
+      xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      av[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < total4) {
+        xv[k] = __ldg(xs + i);
+        if (a_hat) av[k] = __ldg(as + i);
+      }
+    }
+    float g_ch = 0.0f, b_ch = 0.0f, f_sc = 0.0f, f_sh = 0.0f, cb_ch = 0.0f;
+    if (lane < cpg) {
+      const int ch = cbeg + lane;
+      g_ch = __ldg(gamma + ch);
+      b_ch = __ldg(beta + ch);
+      if (has_bias) cb_ch = __ldg(src.bias + (size_t)n * c + ch);
+      if (film) {
+        f_sc = __ldg(film + (size_t)n * 2 * c + ch);
+        f_sh = __ldg(film + (size_t)n * 2 * c + c + ch);
+      }
+    }
+    const float shift =
+        __fadd_rn(__ldg(reinterpret_cast<const float*>(xs)), __shfl_sync(0xffffffffu, cb_ch, 0));
+    float s = 0.0f, q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + 32 * k;
+      const float b = __shfl_sync(0xffffffffu, cb_ch, min(i >> lg_hw4, cpg - 1));
+      if (i < total4) {
+        const float a = __fadd_rn(xv[k].x, b) - shift, bb = __fadd_rn(xv[k].y, b) - shift,
+                    cc = __fadd_rn(xv[k].z, b) - shift, dd = __fadd_rn(xv[k].w, b) - shift;
+        s += (a + bb) + (cc + dd);
+        q += (a * a + bb * bb) + (cc * cc + dd * dd);
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    const float ms = s / (float)count;
+    const float mean = shift + ms;
+    const float var = fmaxf(q / (float)count - ms * ms, 0.0f);
+    const float rstd = 1.0f / sqrtf(var + eps);
+    float ga = g_ch * rstd;
+    float sf = fmaf(cb_ch - mean, ga, b_ch);
+    if (film) {
+      const float f = 1.0f + f_sc;
+      ga *= f;
+      sf = fmaf(sf, f, f_sh);
+    }
+    if (lane < cpg)
+      reinterpret_cast<float2*>(affine)[(size_t)n * c + cbeg + lane] = make_float2(ga, sf);
+    float mi = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = lane + 32 * k;
+      const int kc = min(i >> lg_hw4, cpg - 1);
+      const float ax = __shfl_sync(0xffffffffu, ga, kc), ay = __shfl_sync(0xffffffffu, sf, kc);
+      if (i < total4) {
+        float v0 = fmaf(xv[k].x, ax, ay), v1 = fmaf(xv[k].y, ax, ay), v2 = fmaf(xv[k].z, ax, ay),
+              v3 = fmaf(xv[k].w, ax, ay);
+        if (src.silu) {
+          v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3);
+        }
+        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v0, av[k].x))), fabsf(__fsub_rn(v1, av[k].y)));
+        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v2, av[k].z))), fabsf(__fsub_rn(v3, av[k].w)));
+      }
+    }
+    if (split > 0 && cbeg >= split) m1 = fmaxf(m1, mi); else m0 = fmaxf(m0, mi);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+  }
+  if (per_sample) {
+    // images differ between the warps of a block: every warp publishes its own maximum
+    if (lane == 0 && cur_n >= 0 && m0 > 0.0f)
+      atomicMax(&scratch->absmax_bits[cur_n], __float_as_uint(m0));
+    m0 = 0.0f;
+  }
+  if (lane == 0) {
+    s0[warp] = m0;
+    s1[warp] = m1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < wpb; ++i) {
+      m0 = fmaxf(m0, s0[i]);
+      m1 = fmaxf(m1, s1[i]);
+    }
+    if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[0], __float_as_uint(m0));
+    if (split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    for (int sl = threadIdx.x; sl < slots; sl += blockDim.x) {
+      const unsigned int bits = atomicExch(&scratch->absmax_bits[sl], 0u);
+      double delta = (double)__uint_as_float(bits) / (double)n_levels;
+      if (delta < 1e-8) delta = 1e-8;
+      x_scale[sl] = (float)delta;
+    }
+    if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
 }  // namespace
 
 // MODIFF_MODQ_STAGED=0 selects the register-path encode kernel (debug aid, same outputs)
@@ -887,7 +1035,29 @@ extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, c
 
   // a slab must be whole channels of ONE source tensor and of ONE scale segment
   const bool whole = (src->c0 % cpg == 0) && (g->split % cpg == 0);
-  if (lg_hw4 >= 0 && nv <= 8 && cpg <= kGnMaxCpg && aligned && whole) {
+  if (lg_hw4 >= 0 && threads == 32 && cpg <= 32 && aligned && whole) {
+    // small slabs: one warp each
+    v.bias = src->chan_bias;
+    v.affine = nullptr;
+    const int items = g->batch * groups;
+    const int nvw = ceil_div(count / 4, 32);
+    const int blocks = ceil_div(items, 8) < 148 * 8 ? ceil_div(items, 8) : 148 * 8;
+#define MODIFF_GN_ABSMAX_WARP(NV)                                                                \
+  gn_absmax_warp_kernel<NV><<<blocks, 256, 0, s>>>(v, film, affine, gamma, beta, a_hat, g->batch,  \
+                                                   g->cin, hw, groups, eps, lg_hw4, g->split,     \
+                                                   n_levels, per_sample, slots,                   \
+                                                   (ModqScratch*)scratch, x_scale)
+    if (nvw <= 1) MODIFF_GN_ABSMAX_WARP(1);
+    else if (nvw <= 2) MODIFF_GN_ABSMAX_WARP(2);
+    else if (nvw <= 4) MODIFF_GN_ABSMAX_WARP(4);
+    else MODIFF_GN_ABSMAX_WARP(8);
+#undef MODIFF_GN_ABSMAX_WARP
+    MODIFF_LAUNCH_CHECK("gn_absmax_warp_kernel");
+    v.bias = nullptr;
+    v.affine = affine;
+    return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, false, s);
+  }
+  if (lg_hw4 >= 0 && threads >= 256 && nv <= 8 && cpg <= kGnMaxCpg && aligned && whole) {
     v.bias = src->chan_bias;
     v.affine = nullptr;
     const int items = g->batch * groups;

@@ -113,7 +113,8 @@ def test_module_modes_and_errors(cuda):
 @pytest.mark.parametrize("c0,c1,hw,bias,film,split,a_bits", [
     (128, 0, 32, True, False, 0, 8),      # 4 channels x 1024 pixels per group: slab in registers
     (64, 64, 16, False, False, 64, 4),    # concat input, split scales (up-path shortcut)
-    (256, 0, 8, False, True, 0, 8),       # FiLM scale / shift after the normalisation
+    (256, 0, 8, False, True, 0, 8),       # FiLM scale / shift after the normalisation; warp per slab
+    (256, 256, 4, True, False, 256, 8),   # 16 x 16 per group: one float4 per lane, concat + split
     (320, 0, 64, True, False, 0, 8),      # 10 x 4096 per group: statistics as their own pass
     (96, 0, 6, False, False, 0, 8),       # h*w/4 not a power of two: statistics as their own pass
 ])
