@@ -24,7 +24,6 @@ namespace modiff {
 namespace {
 
 constexpr int kChunkK = 128;                     // bytes of K per weight tile row
-constexpr int kBTileBytes = 128 * kChunkK;       // 128 output channels x 128 bytes
 constexpr int kEpiWarps = 8;
 constexpr int kASlots = 2;
 constexpr int kOSlots = 2;
@@ -49,8 +48,11 @@ struct HaloParams {
   int a_slot_bytes;
   int tmem_cols;
   int accumulate;
+  int umma_n;           // 128, or 144 with the receptive-field-sum rows (zero-point correction)
+  int b_tile_bytes;     // umma_n * 128
   const float* x_scale;
   const float* w_scale;
+  const int32_t* w_corr;
 };
 
 struct HaloTile {
@@ -77,6 +79,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ float ep_scale[128];
+  __shared__ int ep_corr[128];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -85,7 +88,8 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t a_ring = raw;
   const uint32_t b_ring = a_ring + kASlots * (uint32_t)p.a_slot_bytes;
-  const uint32_t obuf = b_ring + (uint32_t)p.b_stages * kBTileBytes;
+  const uint32_t b_tile = (uint32_t)p.b_tile_bytes;
+  const uint32_t obuf = b_ring + (uint32_t)p.b_stages * b_tile;
   float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
 
   if (threadIdx.x == 0) {
@@ -120,7 +124,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_sh;
-  const int buf_cols = p.mh * 128;
+  const int buf_cols = p.mh * p.umma_n;
 
   if (warp == 0) {
     // ------------------------------------------------------------ operand TMA producer
@@ -144,9 +148,9 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
               ok = mbar_wait(smem_u32(&bar_b_empty[bst]), bphase ^ 1u, abort_flag);
               if (!ok) break;
               const uint32_t bfull = smem_u32(&bar_b_full[bst]);
-              mbar_arrive_expect_tx(bfull, (uint32_t)kBTileBytes);
-              tma_load_2d(b_ring + bst * kBTileBytes, &map_b, bfull,
-                          (dy * 3 + dx) * p.kp + ch * kChunkK, t.nt * 128);
+              mbar_arrive_expect_tx(bfull, b_tile);
+              tma_load_2d(b_ring + bst * b_tile, &map_b, bfull,
+                          (dy * 3 + dx) * p.kp + ch * kChunkK, t.nt * p.umma_n);
               if (++bst == p.b_stages) { bst = 0; bphase ^= 1u; }
             }
           }
@@ -156,7 +160,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_i8(128, 128);
+      const uint32_t idesc = make_idesc_i8(128, p.umma_n);
       int aslot = 0, bst = 0, buf = 0;
       uint32_t aphase = 0, bphase = 0, tphase = 0;
       bool ok = true;
@@ -174,12 +178,12 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
               ok = mbar_wait(smem_u32(&bar_b_full[bst]), bphase, abort_flag);
               if (!ok) break;
               tc_fence_after();
-              const uint64_t bdesc = make_smem_desc(b_ring + bst * kBTileBytes);
+              const uint64_t bdesc = make_smem_desc(b_ring + bst * b_tile);
               for (int m = 0; m < p.mh; ++m) {
                 // rows m*half_rows+dy .. of the copy: a whole number of 1024-byte swizzle periods
                 const uint64_t adesc = make_smem_desc(
                     a_base + (uint32_t)((m * p.half_rows + dy) * p.w) * (uint32_t)kChunkK);
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * buf_cols + m * 128);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * buf_cols + m * p.umma_n);
 #pragma unroll
                 for (int k = 0; k < kChunkK / 32; ++k)
                   tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
@@ -262,8 +266,10 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       const HaloTile t = decode(tile, p);
       if (t.nt != last_nt) {
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ep_tid < 128)
+        if (ep_tid < 128) {
           ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * 128 + ep_tid]);
+          ep_corr[ep_tid] = p.w_corr ? p.w_corr[t.nt * 128 + ep_tid] : 0;
+        }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         last_nt = t.nt;
       }
@@ -272,7 +278,12 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after();
       for (int m = 0; m < p.mh && ok; ++m) {
         const uint32_t t_row =
-            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * buf_cols + m * 128);
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * buf_cols + m * p.umma_n);
+        int rsum = 0;
+        if (p.w_corr) {      // column 128: sum of the receptive field's activation codes
+          tc_ld1(t_row + 128, rsum);
+          tc_wait_ld();
+        }
         for (int hh = 0; hh < 2; ++hh) {
           ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
@@ -284,6 +295,10 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           int a[32];
           tc_ld32(t_row + colbase, a);
           tc_wait_ld();
+          if (p.w_corr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a[j] += ep_corr[colbase + j] * rsum;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
 #pragma unroll
@@ -332,9 +347,12 @@ double wave_efficiency(int tiles, int sms) {
 // Whether the activation-reuse kernel covers this call.
 bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
                     const int32_t* acc_out, const float* o_hat) {
+  // with correction rows only 128-pixel tiles fit tensor memory; at 16 pixels per row they were
+  // measured no faster than one copy per tap
+  if (with_sum_rows && g->w < 32) return false;
   if (g->kh != 3 || g->kw != 3 || g->stride != 1) return false;
   if (g->pad_t != 1 || g->pad_b != 1 || g->pad_l != 1 || g->pad_r != 1) return false;
-  if (with_sum_rows || per_sample || bias || acc_out || g->split != 0) return false;
+  if (per_sample || bias || acc_out || g->split != 0) return false;
   if (g->cout % 128 != 0 || g->cin < 128 || g->cin % 16 != 0) return false;
   if (!is_pow2(g->w) || !is_pow2(g->h) || g->w < 16 || g->w > 64) return false;
   if (g->h * g->w < 128 || (128 / g->w) > g->h) return false;
@@ -342,9 +360,9 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
   return true;
 }
 
-int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_scale,
-                      const float* w_scale, float* o_hat, int accumulate,
-                      const modiff_conv_geom* g, cudaStream_t s) {
+int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                      const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s) {
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   static int sm_count = 0;
@@ -364,14 +382,17 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_
   // shared-memory fill bytes per 128 output pixels divided by the wave efficiency
   const int rows1 = 128 / g->w, rows2 = 256 / g->w;
   const int chunks = ceil_div(g->cin, kChunkK);
+  p.umma_n = with_sum_rows ? 144 : 128;
+  p.b_tile_bytes = p.umma_n * kChunkK;
   auto cost = [&](int mh) {
     const int rows = mh * rows1;
-    const double fill = (3.0 * chunks * (rows + 2) * g->w * kChunkK + 9.0 * chunks * kBTileBytes) / mh +
+    const double fill = (3.0 * chunks * (rows + 2) * g->w * kChunkK + 9.0 * chunks * p.b_tile_bytes) / mh +
                         4.0 * kOHalfBytes;
     return fill / wave_efficiency(g->batch * (g->h / rows) * p.n_tiles, sm_count);
   };
   p.mh = 1;
-  if (rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
+  // two m-halves of 144 columns, double buffered, would need 576 of the 512 tensor-memory columns
+  if (!with_sum_rows && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
   p.rows = p.mh * rows1;
   p.half_rows = rows1;
   p.tiles_h = g->h / p.rows;
@@ -381,14 +402,15 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_
   p.a_bytes = (p.rows + 2) * g->w * kChunkK;
   p.a_slot_bytes = round_up(p.a_bytes, 1024);
   const int fixed = kASlots * p.a_slot_bytes + kOSlots * kOHalfBytes;
-  p.b_stages = (224 * 1024 - fixed) / kBTileBytes;
+  p.b_stages = (224 * 1024 - fixed) / p.b_tile_bytes;
   if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
   if (p.b_stages < 3) return set_error(MODIFF_ERR_UNSUPPORTED, "tile does not fit shared memory");
-  p.tmem_cols = p.mh == 2 ? 512 : 256;
+  p.tmem_cols = (2 * p.mh * p.umma_n) > 256 ? 512 : 256;
   p.accumulate = accumulate;
   p.x_scale = x_scale;
   p.w_scale = w_scale;
-  const size_t smem = (size_t)fixed + (size_t)p.b_stages * kBTileBytes;
+  p.w_corr = w_corr;
+  const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes;
 
   CUtensorMap map_a, map_b, map_o;
   {
@@ -405,9 +427,9 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(activation codes) failed: %d", (int)r);
   }
   {
-    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp, (cuuint64_t)g->cout};
+    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp, (cuuint64_t)p.n_tiles * p.umma_n};
     cuuint64_t strides[1] = {(cuuint64_t)d.taps * d.kp};
-    cuuint32_t box[2] = {(cuuint32_t)kChunkK, 128u};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)p.umma_n};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)wcodes, dims, strides, box,
                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -575,9 +575,9 @@ int read_device_status_bf16(int* status, int reset);   // gemm_bf16_tc.cu
 int read_device_status_halo(int* status, int reset);   // igemm_halo.cu
 bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
                     const int32_t* acc_out, const float* o_hat);
-int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, const float* x_scale,
-                      const float* w_scale, float* o_hat, int accumulate,
-                      const modiff_conv_geom* g, cudaStream_t s);
+int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                      const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s);
 
 // MODIFF_IGEMM_HALO=0 keeps 3x3 layers on the one-copy-per-tap kernel (debug aid, same results)
 static bool halo_enabled() {
@@ -622,7 +622,8 @@ extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int 
                              accumulate, bias, g, per_sample, acc_out, s);
   MODIFF_CHECK_ARG(impl == MODIFF_IMPL_AUTO || impl == MODIFF_IMPL_TCGEN05, "unknown impl %d", impl);
   if (halo_enabled() && halo_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
-    return launch_igemm_halo(codes, wcodes, x_scale, w_scale, o_hat, accumulate, g, s);
+    return launch_igemm_halo(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                             g, s);
   return launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
                          bias, g, per_sample, acc_out, s);
 }

@@ -259,9 +259,10 @@ HALO_CASES = [
 ]
 
 
+@pytest.mark.parametrize("w_bits", [4, 8])
 @pytest.mark.parametrize("accumulate", [True, False])
 @pytest.mark.parametrize("case", HALO_CASES, ids=lambda c: "b%d_c%d_o%d_hw%d" % c)
-def test_igemm_activation_reuse_kernel(cuda, case, accumulate, monkeypatch):
+def test_igemm_activation_reuse_kernel(cuda, case, accumulate, w_bits, monkeypatch):
     """The 3x3 kernel that reuses one activation copy for three filter taps gives the same
     bits as the one-copy-per-tap kernel and matches the exact integer convolution."""
     b, cin, cout, hw = case
@@ -270,14 +271,15 @@ def test_igemm_activation_reuse_kernel(cuda, case, accumulate, monkeypatch):
     torch.manual_seed(12)
     x_codes = torch.randint(-8, 8, (b, cin, hw, hw), dtype=torch.int8)
     w = torch.randn(cout, cin, 3, 3) * 0.05
+    w[1] = w[1].abs() + 0.01   # an all-positive channel: zero point outside the code range
     outs = []
     for halo in ("1", "0"):
         monkeypatch.setenv("MODIFF_IGEMM_HALO", halo)
-        out, _, o_prev, ws = _run_igemm(x_codes, w, g, 4, L.IMPL_TCGEN05, cuda, accumulate=accumulate,
-                                        want_acc=False)
+        out, _, o_prev, ws = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda,
+                                        accumulate=accumulate, want_acc=False)
         outs.append(out)
     assert torch.equal(outs[0], outs[1])
-    exp_acc, dws = _expected_acc(x_codes, w, g, 4)
+    exp_acc, dws = _expected_acc(x_codes, w, g, w_bits)
     exp = o_prev.double() if accumulate else torch.zeros_like(o_prev).double()
     exp = exp + exp_acc[0].double() * (float(np.float32(0.01)) * dws[0].double().view(1, -1, 1, 1))
     err = (outs[0].double() - exp).abs().max() / exp.abs().max()
