@@ -289,13 +289,6 @@ constexpr int kStages = 2;
 constexpr int kStageFloats = 2 * kTileC * kTileP;              // x tile | a_hat tile
 constexpr int kStagedSmem = kStages * kStageFloats * 4;        // bytes of dynamic shared memory
 
-__device__ inline void cp_async16(void* smem, const void* gmem, bool valid) {
-  const unsigned int dst = (unsigned int)__cvta_generic_to_shared(smem);
-  const int bytes = valid ? 16 : 0;     // 0: the 16 bytes are zero-filled, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes)
-               : "memory");
-}
-
 template <bool XFORM>
 __global__ void __launch_bounds__(kThreads)
 modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
@@ -308,30 +301,38 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
   const int cg = threadIdx.x >> 4;
   const int pq = threadIdx.x & 15;
   const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+  // One thread moves the same 16-byte column of four rows (16 rows apart) of both tensors:
+  // per-image base pointers once per tile, 32-bit offsets inside the image.
+  const int lrow = threadIdx.x >> 4, lcol = (threadIdx.x & 15) * 4;
+  const uint32_t sdst0 =
+      (uint32_t)__cvta_generic_to_shared(stage_sh) + (uint32_t)(lrow * kTileP + lcol) * 4u;
   auto issue = [&](int it, int stage) {
     const int tile = tg.total - 1 - it;
     int n, c0, p0;
     tg.decode(tile, n, c0, p0);
-    float* sx = stage_sh + stage * kStageFloats;
-    float* sa = sx + kTileC * kTileP;
+    const int p = p0 + lcol;
+    const float* xb0 = XFORM ? src.x0 + (size_t)n * src.c0 * hw : src.x0 + (size_t)n * g.cin * hw;
+    const float* xb1 = XFORM && src.x1 ? src.x1 + (size_t)n * src.c1 * hw : xb0;
+    const float* ab = a_hat ? a_hat + (size_t)n * g.cin * hw : nullptr;
+    const int split_c = XFORM ? src.c0 : g.cin;
+    const uint32_t sdst = sdst0 + (uint32_t)(stage * kStageFloats) * 4u;
 #pragma unroll
     for (int r = 0; r < (kTileC * kTileP / 4) / kThreads; ++r) {
-      const int chunk = threadIdx.x + r * kThreads;
-      const int row = chunk >> 4, col = (chunk & 15) * 4;
-      const int c = c0 + row, p = p0 + col;
+      const int c = c0 + lrow + 16 * r;
       const bool valid = (c < g.cin) && (p < hw);
-      const float* xp = src.x0;
-      if (valid) {
-        if (XFORM)
-          xp = (c < src.c0) ? src.x0 + ((size_t)n * src.c0 + c) * hw + p
-                            : src.x1 + ((size_t)n * src.c1 + (c - src.c0)) * hw + p;
-        else
-          xp = src.x0 + ((size_t)n * g.cin + c) * hw + p;
+      const int bytes = valid ? 16 : 0;     // 0: the 16 bytes are zero-filled, nothing is read
+      const float* xp = xb0;
+      if (valid) xp = (c < split_c) ? xb0 + (c * hw + p) : xb1 + ((c - split_c) * hw + p);
+      const uint32_t d = sdst + (uint32_t)(16 * r * kTileP) * 4u;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(xp), "r"(bytes)
+                   : "memory");
+      if (a_hat) {
+        const float* ap = valid ? ab + (c * hw + p) : ab;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                         d + (uint32_t)(kTileC * kTileP) * 4u),
+                     "l"(ap), "r"(bytes)
+                     : "memory");
       }
-      cp_async16(sx + row * kTileP + col, xp, valid);
-      if (a_hat)
-        cp_async16(sa + row * kTileP + col,
-                   valid ? a_hat + ((size_t)n * g.cin + c) * hw + p : a_hat, valid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -354,6 +355,9 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
     const int p = p0 + 4 * pq;
     const float* sx = stage_sh + stage * kStageFloats;
     const float* sa = sx + kTileC * kTileP;
+    const size_t img = (size_t)n * g.cin;          // first (image, channel) row of this image
+    const bool one_scale = !per_sample && g.split == 0;
+    const float delta0 = x_scale[per_sample ? n : 0];
 
     uint32_t q[4][4];
 #pragma unroll
@@ -367,7 +371,7 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
         const int row = 4 * cg + i;
         const int c = c0 + row;
         if (c < g.cin) {
-          const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
+          const float delta = (one_scale || per_sample) ? delta0 : x_scale[c >= g.split ? 1 : 0];
           const float4 xt = *reinterpret_cast<const float4*>(sx + row * kTileP + 4 * pq);
           float xv[4] = {xt.x, xt.y, xt.z, xt.w}, av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
           if (a_hat) {
@@ -377,11 +381,11 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
           if (XFORM) {
             if (src.affine) {
               const float2 ab =
-                  __ldg(reinterpret_cast<const float2*>(src.affine) + (size_t)n * g.cin + c);
+                  __ldg(reinterpret_cast<const float2*>(src.affine) + img + c);
 #pragma unroll
               for (int j = 0; j < 4; ++j) xv[j] = fmaf(xv[j], ab.x, ab.y);
             } else if (src.bias) {
-              const float b = __ldg(src.bias + (size_t)n * g.cin + c);
+              const float b = __ldg(src.bias + img + c);
 #pragma unroll
               for (int j = 0; j < 4; ++j) xv[j] = __fadd_rn(xv[j], b);
             }
@@ -397,7 +401,7 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat)
-            *reinterpret_cast<float4*>(a_hat + ((size_t)n * g.cin + c) * hw + p) =
+            *reinterpret_cast<float4*>(a_hat + (img + c) * hw + p) =
                 make_float4(nv[0], nv[1], nv[2], nv[3]);
         }
       }
