@@ -64,6 +64,26 @@ __device__ inline float round_clamp(float t, float lo, float hi, uint32_t& bits)
   bits = __float_as_uint(u);
   return __fadd_rn(u, -12582912.0f);
 }
+// clamp(rne(fl(r / delta)), lo, hi) with the division done as a multiplication by
+// inv = rn(1 / delta) wherever that provably cannot change the result.  t = fl(r * inv) differs
+// from the correctly rounded quotient by at most 1.5 * 2^-23 * |quotient| (one rounding each for
+// inv, the product and the quotient itself), i.e. by less than 2^-14 wherever the clamp does
+// not decide (|quotient| <= 256).  So unless t lies within 2^-14 of a tie both round to the same
+// integer; the few elements that do (about one in 4000) take the true division.  Beyond the
+// clamp range both saturate.
+__device__ inline float quantise_clamp(float r, float delta, float inv, float lo, float hi,
+                                       uint32_t& bits) {
+  const float tc = fminf(fmaxf(__fmul_rn(r, inv), lo), hi);
+  float u = __fadd_rn(tc, 12582912.0f);
+  float qf = __fadd_rn(u, -12582912.0f);
+  if (fabsf(__fsub_rn(tc, qf)) > 0.5f - 6.103515625e-5f) {
+    const float te = fminf(fmaxf(__fdiv_rn(r, delta), lo), hi);
+    u = __fadd_rn(te, 12582912.0f);
+    qf = __fadd_rn(u, -12582912.0f);
+  }
+  bits = __float_as_uint(u);
+  return qf;
+}
 // low bytes of four words -> one word
 __device__ inline uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -358,6 +378,8 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
     const size_t img = (size_t)n * g.cin;          // first (image, channel) row of this image
     const bool one_scale = !per_sample && g.split == 0;
     const float delta0 = x_scale[per_sample ? n : 0];
+    const float delta1 = one_scale || per_sample ? delta0 : x_scale[1];
+    const float inv0 = __frcp_rn(delta0), inv1 = __frcp_rn(delta1);
 
     uint32_t q[4][4];
 #pragma unroll
@@ -371,7 +393,9 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
         const int row = 4 * cg + i;
         const int c = c0 + row;
         if (c < g.cin) {
-          const float delta = (one_scale || per_sample) ? delta0 : x_scale[c >= g.split ? 1 : 0];
+          const bool seg1 = !(one_scale || per_sample) && c >= g.split;
+          const float delta = seg1 ? delta1 : delta0;
+          const float inv = seg1 ? inv1 : inv0;
           const float4 xt = *reinterpret_cast<const float4*>(sx + row * kTileP + 4 * pq);
           float xv[4] = {xt.x, xt.y, xt.z, xt.w}, av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
           if (a_hat) {
@@ -397,7 +421,7 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
-            const float qf = round_clamp(__fdiv_rn(r, delta), lo, hi, q[i][j]);
+            const float qf = quantise_clamp(r, delta, inv, lo, hi, q[i][j]);
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat)

@@ -174,3 +174,45 @@ def test_sampler_schedule_helpers():
     assert float(al[801]) == float(ref)
     s1, s2, s3, c1, c2 = step_coefficients(al, 0, -1, 0.0)
     assert s3 == 1.0 and c1 == 0.0 and c2 == 0.0
+
+
+def test_reciprocal_multiply_with_tie_guard_equals_division():
+    """The quantiser's encode pass divides by multiplying with rn(1/delta) and falls back to the
+    true division only within 2^-14 of a rounding tie (csrc/modq.cu: quantise_clamp).  The same
+    steps in IEEE float32 (numpy) give clamp(rne(r / delta)) for every input, including residuals
+    placed a few ulps around every tie (qdiff/quant_layer.py:94-99)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    f32 = np.float32
+
+    def reference(r, d, lo, hi):
+        return np.clip(np.rint(r / d), lo, hi)
+
+    def fast(r, d, lo, hi):
+        inv = f32(1.0) / d
+        tc = np.clip(r * inv, lo, hi)
+        magic = f32(12582912.0)
+        q = (tc + magic) - magic
+        near_tie = np.abs(tc - q) > f32(0.5) - f32(6.103515625e-5)
+        te = np.clip(r / d, lo, hi)
+        qe = (te + magic) - magic
+        return np.where(near_tie, qe, q), near_tie.mean()
+
+    for bits in (8, 4, 3):
+        n = (1 << (bits - 1)) - 1
+        lo, hi = f32(-n - 1), f32(n)
+        d = np.exp(rng.uniform(np.log(1e-8), np.log(10.0), 4000)).astype(f32)
+        # random residuals over +-1.5x the code range
+        r = (rng.uniform(-1.5 * (n + 1), 1.5 * (n + 1), (4000, 512)).astype(f32) * d[:, None]).astype(f32)
+        got, frac = fast(r, d[:, None], lo, hi)
+        assert np.array_equal(got, reference(r, d[:, None], lo, hi))
+        assert frac < 1e-3
+        # residuals a few ulps around every tie k + 0.5
+        k = np.arange(-n - 3, n + 3, dtype=np.float64) + 0.5
+        r0 = (k[None, :] * d[:, None].astype(np.float64)).astype(f32)
+        for step in range(-4, 5):
+            r = r0.copy()
+            for _ in range(abs(step)):
+                r = np.nextafter(r, f32(np.inf) if step > 0 else f32(-np.inf)).astype(f32)
+            got, _ = fast(r, d[:, None], lo, hi)
+            assert np.array_equal(got, reference(r, d[:, None], lo, hi)), (bits, step)
