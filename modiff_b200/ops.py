@@ -6,6 +6,8 @@ hand-written kernel on the current CUDA stream.  CUDA float32 tensors only.
 import ctypes as C
 import math
 
+import os
+
 import torch
 
 from . import _lib
@@ -326,6 +328,10 @@ def _up(v, m):
     return -(-v // m) * m
 
 
+# MODIFF_FUSED_ATTENTION=0 keeps the three-kernel pipeline for every shape (debug aid)
+FUSED_ATTENTION = os.environ.get("MODIFF_FUSED_ATTENTION", "1") != "0"
+
+
 def attention(q, k, v, scale):
     """Attention over channel-major tensors, one head per batch entry, fp32-accurate
     (qdiff/quant_block.py:191-203, 344-360): q [B, C, Tq], k and v [B, C, Tk];
@@ -361,6 +367,14 @@ def attention(q, k, v, scale):
         torch.empty(b * 2 * tkp * cp, dtype=torch.int16, device=dev)
     gk_src = _lib.ConvGeom(b, c, tk, 1, tk, 1, 1, 1, 0, 0, 0, tkp - tk, 0)  # right pad -> tkp
     _lib.call('modiff_split_bf16', k.data_ptr(), kp.data_ptr(), C.byref(gk_src), _lib.stream_ptr())
+    if FUSED_ATTENTION and tkp <= 256 and c % 64 == 0 and c <= 256:
+        # one kernel: scores and probabilities stay in tensor / shared memory
+        vp = torch.empty(b * 2 * c * tkp, dtype=torch.int16, device=dev)
+        _lib.call('modiff_split_bf16_rows', v.data_ptr(), vp.data_ptr(), b, c, tk, c, tkp,
+                  _lib.stream_ptr())
+        _lib.call('modiff_attention_tc', qp.data_ptr(), kp.data_ptr(), vp.data_ptr(), out.data_ptr(),
+                  b, c, t, tk, cp, tkp, c, float(scale), _lib.stream_ptr())
+        return out
     s = torch.empty((b, tk, t), dtype=torch.float32, device=dev)
     d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, cp,
                            float(scale), tkp)

@@ -67,7 +67,11 @@ def test_first_step_conv_on_tensor_cores(cuda, case, bits):
 
 @pytest.mark.parametrize("b,c,t,tk", [(3, 256, 256, 256), (2, 64, 64, 64), (5, 256, 16, 16),
                                       (2, 128, 1024, 1024), (16, 24, 1024, 1024), (8, 40, 256, 77),
-                                      (4, 160, 64, 77), (8, 96, 4, 4)])
+                                      (4, 160, 64, 77), (8, 96, 4, 4),
+                                      # single-kernel path: many tiles per CTA, masked padded keys,
+                                      # 192 channels, ragged query tile
+                                      (300, 256, 256, 256), (4, 128, 256, 200), (3, 192, 128, 128),
+                                      (2, 64, 128, 150)])
 def test_attention_matches_float64(cuda, b, c, t, tk):
     from modiff_b200 import ops
     import modiff_b200 as m
