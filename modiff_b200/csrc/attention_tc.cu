@@ -46,13 +46,19 @@ struct AttnParams {
 __device__ inline int prod_a(int pr) { return pr == 2 ? 1 : 0; }
 __device__ inline int prod_b(int pr) { return pr == 1 ? 1 : 0; }
 
-__device__ inline uint32_t bf16_bits(float x) {   // round to nearest even, NaN/Inf passed through
-  uint32_t u = __float_as_uint(x);
-  if ((u & 0x7f800000u) == 0x7f800000u) return u >> 16;
-  u += 0x7fffu + ((u >> 16) & 1u);
-  return u >> 16;
+// two floats -> packed bf16 pair (round to nearest even), first argument in the low half
+__device__ inline uint32_t bf16_pair(float lo_half, float hi_half) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi_half), "f"(lo_half));
+  return r;
 }
-__device__ inline float bf16_value(uint32_t h) { return __uint_as_float(h << 16); }
+// exp(x) for x <= 0 through the hardware exp2 (relative error ~2^-22, far below the 2^-16 the
+// split probabilities keep)
+__device__ inline float exp_neg(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x * 1.4426950408889634f));
+  return r;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -236,13 +242,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int u = 0; u < 2; ++u) {
               const int j = g8 * 8 + e + u;
               const float sv = __int_as_float(a[j]) * p.scale;
-              pv[u] = (key0 + j < p.tk) ? expf(sv - mx) : 0.0f;
+              pv[u] = (key0 + j < p.tk) ? exp_neg(sv - mx) : 0.0f;
               sum += pv[u];
             }
-            const uint32_t h0 = bf16_bits(pv[0]), h1 = bf16_bits(pv[1]);
-            const uint32_t l0 = bf16_bits(pv[0] - bf16_value(h0)), l1 = bf16_bits(pv[1] - bf16_value(h1));
-            hw[e >> 1] = h0 | (h1 << 16);
-            lw[e >> 1] = l0 | (l1 << 16);
+            const uint32_t h = bf16_pair(pv[0], pv[1]);
+            hw[e >> 1] = h;
+            lw[e >> 1] = bf16_pair(pv[0] - __uint_as_float(h << 16),
+                                   pv[1] - __uint_as_float(h & 0xffff0000u));
           }
           const int chunk = (chunk0 + g8) ^ (row & 7);
           *reinterpret_cast<uint4*>(hi_row + chunk * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
