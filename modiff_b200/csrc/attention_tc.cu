@@ -25,8 +25,8 @@ constexpr int kChunkBytes = 128;                 // 64 bf16 of K per tile row
 constexpr int kATile = 128 * kChunkBytes;        // 16 KB: 128 queries
 constexpr int kBTileMax = 256 * kChunkBytes;     // 32 KB: up to 256 keys / channels
 constexpr int kStage = kATile + kBTileMax;       // 48 KB
-constexpr int kStages = 2;
-constexpr int kPBytes = 2 * 4 * kATile;          // two planes x four 64-key chunks x 16 KB
+constexpr int kStages = 3;
+constexpr int kPBytes = 2 * 2 * kATile;          // two planes x two 64-key chunks (128 keys) x 16 KB
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 
@@ -36,6 +36,7 @@ struct AttnParams {
   int crow;                     // channel rows of the v planes (multiple of 64, <= 256)
   int cch;                      // 64-element K chunks of phase 1: ceil(cp / 64)
   int kch;                      // 64-key K chunks of phase 3: tkp / 64
+  int khalves;                  // 128-key halves: ceil(kch / 2)
   int q_tiles;                  // ceil(t / 128)
   int total_tiles;
   float scale;
@@ -65,7 +66,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages];
-  __shared__ __align__(8) uint64_t bar_s_full, bar_p_ready, bar_o_full, bar_o_empty;
+  __shared__ __align__(8) uint64_t bar_s_full, bar_p_ready, bar_p_free, bar_o_full, bar_o_empty;
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ float red_max[2][128], red_sum[2][128];
@@ -85,6 +86,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     mbar_init(smem_u32(&bar_s_full), 1);
     mbar_init(smem_u32(&bar_p_ready), kEpiWarps);
+    mbar_init(smem_u32(&bar_p_free), 1);
     mbar_init(smem_u32(&bar_o_full), 1);
     mbar_init(smem_u32(&bar_o_empty), kEpiWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -142,7 +144,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t idesc_s = make_idesc_bf16(128, p.tkp);
       const uint32_t idesc_o = make_idesc_bf16(128, p.crow);
       int stage = 0;
-      uint32_t phase = 0, tphase = 0;
+      uint32_t phase = 0, tphase = 0, pphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         // phase 1: scores.  The previous tile's softmax has finished reading them (the MMAs of
@@ -163,26 +165,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         if (!ok) break;
         tc_commit(smem_u32(&bar_s_full));
-        // phase 3 needs the probabilities in shared memory and the previous output drained
-        ok = mbar_wait(smem_u32(&bar_p_ready), tphase, abort_flag);
-        if (ok) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        for (int kc = 0; kc < p.kch && ok; ++kc) {
-          for (int pr = 0; pr < 3; ++pr) {
-            ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const uint64_t adesc =
-                make_smem_desc(p_smem + (uint32_t)((prod_a(pr) * 4 + kc) * kATile));
-            const uint64_t bdesc = make_smem_desc(ring + stage * kStage + kATile);
+        // phase 3, 128 keys at a time: the probability planes of one half sit in shared memory
+        // while the epilogue warps wait to write the next half; the first half also needs the
+        // previous tile's output drained
+        for (int kh = 0; kh < p.khalves && ok; ++kh) {
+          ok = mbar_wait(smem_u32(&bar_p_ready), pphase, abort_flag);
+          pphase ^= 1u;
+          if (ok && kh == 0) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const int kc_end = min(p.kch, 2 * kh + 2);
+          for (int kc = 2 * kh; kc < kc_end && ok; ++kc) {
+            for (int pr = 0; pr < 3; ++pr) {
+              ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              const uint64_t adesc =
+                  make_smem_desc(p_smem + (uint32_t)((prod_a(pr) * 2 + (kc & 1)) * kATile));
+              const uint64_t bdesc = make_smem_desc(ring + stage * kStage + kATile);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                          idesc_o, (kc > 0 || pr > 0 || k > 0) ? 1u : 0u);
-            tc_commit(smem_u32(&bar_empty[stage]));
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+              for (int k = 0; k < 4; ++k)
+                tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                            idesc_o, (kc > 0 || pr > 0 || k > 0) ? 1u : 0u);
+              tc_commit(smem_u32(&bar_empty[stage]));
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
           }
+          if (ok) tc_commit(smem_u32(&bar_p_free));
         }
         if (ok) tc_commit(smem_u32(&bar_o_full));
         tphase ^= 1u;
@@ -196,10 +205,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const int kcols = p.tkp >> 1;            // key columns of this warp (multiple of 32)
     const int ccols = p.crow >> 1;           // channel columns of this warp (multiple of 32)
     uint8_t* p_ptr = smem_raw;
-    uint32_t tphase = 0;
+    uint32_t tphase = 0, fphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const int img = tile / p.q_tiles, qt = tile % p.q_tiles;
@@ -207,15 +215,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       ok = mbar_wait(smem_u32(&bar_s_full), tphase, abort_flag);
       if (!ok) break;
       tc_fence_after();
+      // Keys are handled 128 at a time (kh); inside a half the two warps of a lane quarter take
+      // half of its keys each (32 or 64 columns).
       // ---- row maximum
       float mx = -INFINITY;
-      for (int c0 = 0; c0 < kcols; c0 += 32) {
-        int a[32];
-        tc_ld32(t_lane + (uint32_t)(half * kcols + c0), a);
-        tc_wait_ld();
+      for (int kh = 0; kh < p.khalves; ++kh) {
+        const int nk = min(128, p.tkp - 128 * kh) >> 1;
+        for (int c0 = 0; c0 < nk; c0 += 32) {
+          const int key0 = 128 * kh + half * nk + c0;
+          int a[32];
+          tc_ld32(t_lane + (uint32_t)key0, a);
+          tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (half * kcols + c0 + j < p.tk) mx = fmaxf(mx, __int_as_float(a[j]) * p.scale);
+          for (int j = 0; j < 32; ++j)
+            if (key0 + j < p.tk) mx = fmaxf(mx, __int_as_float(a[j]) * p.scale);
+        }
       }
       red_max[half][row] = mx;
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -223,44 +237,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // ---- exp, row sum, probabilities -> shared memory (K-major rows of 128 bytes, the
       //      16-byte chunk index XORed with row % 8: the layout TMA writes with 128-byte swizzle)
       float sum = 0.0f;
-      for (int c0 = 0; c0 < kcols; c0 += 32) {
-        int a[32];
-        tc_ld32(t_lane + (uint32_t)(half * kcols + c0), a);
-        tc_wait_ld();
-        const int key0 = half * kcols + c0;             // multiple of 32
-        const int kc = key0 >> 6;                       // 64-key chunk
-        const int chunk0 = (key0 & 63) >> 3;            // first 16-byte chunk inside the row: 0 or 4
-        uint8_t* hi_row = p_ptr + (size_t)(0 * 4 + kc) * kATile + (size_t)row * 128;
-        uint8_t* lo_row = p_ptr + (size_t)(1 * 4 + kc) * kATile + (size_t)row * 128;
+      for (int kh = 0; kh < p.khalves && ok; ++kh) {
+        // the MMAs that read the previous contents of the planes have completed
+        ok = mbar_wait(smem_u32(&bar_p_free), fphase ^ 1u, abort_flag);
+        fphase ^= 1u;
+        if (!ok) break;
+        const int nk = min(128, p.tkp - 128 * kh) >> 1;
+        for (int c0 = 0; c0 < nk; c0 += 32) {
+          const int key0 = 128 * kh + half * nk + c0;       // multiple of 32
+          int a[32];
+          tc_ld32(t_lane + (uint32_t)key0, a);
+          tc_wait_ld();
+          const int kc = (key0 >> 6) & 1;                   // 64-key chunk inside the half
+          const int chunk0 = (key0 & 63) >> 3;              // first 16-byte chunk of the row: 0 or 4
+          uint8_t* hi_row = p_ptr + (size_t)(0 * 2 + kc) * kATile + (size_t)row * 128;
+          uint8_t* lo_row = p_ptr + (size_t)(1 * 2 + kc) * kATile + (size_t)row * 128;
 #pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          uint32_t hw[4], lw[4];
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint32_t hw[4], lw[4];
 #pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            float pv[2];
+            for (int e = 0; e < 8; e += 2) {
+              float pv[2];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int j = g8 * 8 + e + u;
-              const float sv = __int_as_float(a[j]) * p.scale;
-              pv[u] = (key0 + j < p.tk) ? exp_neg(sv - mx) : 0.0f;
-              sum += pv[u];
+              for (int u = 0; u < 2; ++u) {
+                const int j = g8 * 8 + e + u;
+                const float sv = __int_as_float(a[j]) * p.scale;
+                pv[u] = (key0 + j < p.tk) ? exp_neg(sv - mx) : 0.0f;
+                sum += pv[u];
+              }
+              const uint32_t h = bf16_pair(pv[0], pv[1]);
+              hw[e >> 1] = h;
+              lw[e >> 1] = bf16_pair(pv[0] - __uint_as_float(h << 16),
+                                     pv[1] - __uint_as_float(h & 0xffff0000u));
             }
-            const uint32_t h = bf16_pair(pv[0], pv[1]);
-            hw[e >> 1] = h;
-            lw[e >> 1] = bf16_pair(pv[0] - __uint_as_float(h << 16),
-                                   pv[1] - __uint_as_float(h & 0xffff0000u));
+            const int chunk = (chunk0 + g8) ^ (row & 7);
+            *reinterpret_cast<uint4*>(hi_row + chunk * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4*>(lo_row + chunk * 16) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
           }
-          const int chunk = (chunk0 + g8) ^ (row & 7);
-          *reinterpret_cast<uint4*>(hi_row + chunk * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-          *reinterpret_cast<uint4*>(lo_row + chunk * 16) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
         }
+        if (kh == p.khalves - 1) red_sum[half][row] = sum;
+        // the MMA reads the planes through the async proxy
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
       }
-      red_sum[half][row] = sum;
-      // the MMA reads the planes through the async proxy
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
+      if (!ok) break;
       const float inv = 1.0f / (red_sum[0][row] + red_sum[1][row]);
       // ---- output
       ok = mbar_wait(smem_u32(&bar_o_full), tphase, abort_flag);
@@ -332,6 +354,7 @@ extern "C" int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_p
   p.crow = crow;
   p.cch = ceil_div(cp, 64);
   p.kch = tkp / 64;
+  p.khalves = (p.kch + 1) / 2;
   p.q_tiles = ceil_div(t, 128);
   p.total_tiles = batch * p.q_tiles;
   p.scale = scale;

@@ -290,6 +290,7 @@ split_bf16_planes_kernel(const float* __restrict__ x, uint16_t* __restrict__ out
   const int cg = threadIdx.x >> 4;   // channel group: 4 channels
   const int pq = threadIdx.x & 15;   // pixel quad
   const size_t part_stride = (size_t)d.nplanes * d.hp * d.wp * cp;
+  const bool vec4 = (hw % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
     const int n = tile / (pb * cb);
     const int rem = tile % (pb * cb);
@@ -297,15 +298,25 @@ split_bf16_planes_kernel(const float* __restrict__ x, uint16_t* __restrict__ out
     const int p0 = (rem % pb) * kSplitTileP;
     const int p = p0 + 4 * pq;
     uint16_t hi[4][4], lo[4][4];
+    float xv[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {      // all loads first: sixteen values, four 16-byte loads
+      const int c = c0 + 4 * cg + i;
+      const float* src = x + ((size_t)n * g.cin + c) * hw + p;
+      if (vec4 && c < g.cin && p < hw) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(src));
+        xv[i][0] = f.x; xv[i][1] = f.y; xv[i][2] = f.z; xv[i][3] = f.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xv[i][j] = (c < g.cin && p + j < hw) ? __ldg(src + j) : 0.0f;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int c = c0 + 4 * cg + i;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float v = 0.0f;
-        if (c < g.cin && p + j < hw) v = __ldg(x + ((size_t)n * g.cin + c) * hw + p + j);
-        hi[i][j] = bf16_rn(v);
-        lo[i][j] = bf16_rn(v - bf16_to_f(hi[i][j]));
+        hi[i][j] = bf16_rn(xv[i][j]);
+        lo[i][j] = bf16_rn(xv[i][j] - bf16_to_f(hi[i][j]));
       }
     }
 #pragma unroll
