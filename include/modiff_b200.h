@@ -139,6 +139,22 @@ int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, f
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     void* stream);
 
+/* modiff_modq_src with ASYMMETRIC activation codes (the reference's quantiser without --a_sym:
+ * sym=False in qdiff/quant_layer.py:191-214, 160-190, 94-102):
+ *   delta = (max - min) / (2^b - 1), zero_point = round(-min / delta),
+ *   q = clamp(round(r / delta) + zero_point, 0, 2^b - 1), dequantised (q - zero_point) * delta.
+ * The code planes receive the CENTRED code q - zero_point, which is what the convolution
+ * multiplies, so modiff_igemm_conv and the zero halo are used unchanged.  That range must fit
+ * int8: n_bits <= 7, and a scale slot whose [-zero_point, 2^b - 1 - zero_point] leaves
+ * [-128, 127] (a residual that does not straddle zero by far) sets bit 2 of
+ * modiff_device_status.
+ *   x_zp     fp32 out, same slots as x_scale: the zero points
+ *   scratch  at least 16 + 8 * slots bytes (slots = 2, or batch with per_sample), zero-filled
+ *            once by the caller */
+int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes, float* x_scale,
+                     float* x_zp, const modiff_conv_geom* g, int n_bits, int per_sample,
+                     void* scratch, void* stream);
+
 /* modiff_modq_src for an input that is GroupNorm (+ FiLM) (+ SiLU) of [x0 | x1] (+ chan_bias):
  * the normalisation statistics and the residual maximum come from ONE sweep over the source.
  * Replaces `h = self.norm1(h); h = nonlinearity(h); h = self.conv1(h)` and its siblings

@@ -574,6 +574,7 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
 int read_device_status_bf16(int* status, int reset);   // gemm_bf16_tc.cu
 int read_device_status_halo(int* status, int reset);   // igemm_halo.cu
 int read_device_status_attention(int* status, int reset);   // attention_tc.cu
+int read_device_status_modq(int* status, int reset);        // modq.cu
 bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
                     const int32_t* acc_out, const float* o_hat);
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
@@ -597,7 +598,10 @@ int read_device_status(int* status, int reset) {
   int d = 0;
   rc = read_device_status_attention(&d, reset);
   if (rc) return rc;
-  *status = a | b | c | d;
+  int e = 0;
+  rc = read_device_status_modq(&e, reset);
+  if (rc) return rc;
+  *status = a | b | c | d | e;
   return MODIFF_OK;
 }
 

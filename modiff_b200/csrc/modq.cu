@@ -235,7 +235,8 @@ template <bool VEC4, bool XFORM>
 __global__ void __launch_bounds__(kThreads)
 modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
                    int8_t* __restrict__ codes, const float* __restrict__ x_scale,
-                   modiff_conv_geom g, Derived d, TileGrid tg, int n_levels, int per_sample) {
+                   const float* __restrict__ x_zp, modiff_conv_geom g, Derived d, TileGrid tg,
+                   int n_levels, int per_sample) {
   __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
   const int hw = g.h * g.w;
   const int cg = threadIdx.x >> 4;
@@ -261,7 +262,11 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
       for (int i = 0; i < 4; ++i) {
         const int c = c0 + 4 * cg + i;
         if (c < g.cin) {
-          const float delta = x_scale[slot_of(n, c, g.split, per_sample)];
+          const int slot = slot_of(n, c, g.split, per_sample);
+          const float delta = x_scale[slot];
+          // asymmetric codes: centred range [-zp, 2^b - 1 - zp]
+          const float lo_s = x_zp ? -x_zp[slot] : lo;
+          const float hi_s = x_zp ? (float)(2 * n_levels + 1) - x_zp[slot] : hi;
           const size_t off = ((size_t)n * g.cin + c) * hw;
           float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
           load_src<VEC4, XFORM>(src, n, c, g.cin, p, hw, xv);
@@ -269,7 +274,7 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
-            const float qf = round_clamp(__fdiv_rn(r, delta), lo, hi, q[i][j]);
+            const float qf = round_clamp(__fdiv_rn(r, delta), lo_s, hi_s, q[i][j]);
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
@@ -313,8 +318,8 @@ template <bool XFORM>
 __global__ void __launch_bounds__(kThreads)
 modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
                           int8_t* __restrict__ codes, const float* __restrict__ x_scale,
-                          modiff_conv_geom g, Derived d, TileGrid tg, int n_levels,
-                          int per_sample) {
+                          const float* __restrict__ x_zp, modiff_conv_geom g, Derived d,
+                          TileGrid tg, int n_levels, int per_sample) {
   extern __shared__ __align__(16) float stage_sh[];
   __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
   const int hw = g.h * g.w;
@@ -380,6 +385,12 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
     const float delta0 = x_scale[per_sample ? n : 0];
     const float delta1 = one_scale || per_sample ? delta0 : x_scale[1];
     const float inv0 = __frcp_rn(delta0), inv1 = __frcp_rn(delta1);
+    // asymmetric codes: centred range [-zp, 2^b - 1 - zp] per scale slot
+    const float zp0 = x_zp ? x_zp[per_sample ? n : 0] : 0.0f;
+    const float zp1 = (x_zp && !(one_scale || per_sample)) ? x_zp[1] : zp0;
+    const float top = (float)(2 * n_levels + 1);
+    const float lo0 = x_zp ? -zp0 : lo, hi0 = x_zp ? top - zp0 : hi;
+    const float lo1 = x_zp ? -zp1 : lo, hi1 = x_zp ? top - zp1 : hi;
 
     uint32_t q[4][4];
 #pragma unroll
@@ -421,7 +432,7 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
-            const float qf = quantise_clamp(r, delta, inv, lo, hi, q[i][j]);
+            const float qf = quantise_clamp(r, delta, inv, seg1 ? lo1 : lo0, seg1 ? hi1 : hi0, q[i][j]);
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat)
@@ -451,6 +462,183 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
       *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
     }
     __syncthreads();   // tile_sh and the stage just read are rewritten next
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Asymmetric activation codes (the reference's default without --a_sym,
+// qdiff/quant_layer.py:191-214 with sym=False): delta = (max - min) / (2^b - 1),
+// zero_point = round(-min / delta), q = clamp(round(r / delta) + zp, 0, 2^b - 1).
+// The planes hold the CENTRED code q - zp (what the convolution multiplies), so the GEMM
+// kernels and the zero halo are those of the symmetric path; that needs the centred range
+// [-zp, 2^b - 1 - zp] inside int8, which holds for b <= 7 whenever the residual straddles zero.
+// A scale slot whose range does not fit sets the sticky status word (bit 2).
+__device__ int g_modq_status = 0;
+
+__device__ inline unsigned int f2ord(float f) {     // order-preserving float -> unsigned
+  const unsigned int b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ inline float ord2f(unsigned int o) {
+  return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+
+// scratch as {counter, pad[3], mm[2 * slots]}: mm[2s] = max key, mm[2s+1] = ~(min key), both
+// accumulated with atomicMax from zero and left zeroed again.
+__device__ inline void publish_range(ModqScratch* scratch, int slot, float mn, float mx) {
+  atomicMax(&scratch->absmax_bits[2 * slot], f2ord(mx));
+  atomicMax(&scratch->absmax_bits[2 * slot + 1], ~f2ord(mn));
+}
+
+// last block: ranges -> delta, zero point (per tensor in Python-float arithmetic, per sample in
+// fp32 tensor arithmetic, as the reference does)
+__device__ inline void finalise_ranges(ModqScratch* scratch, int slots, int n_bits, int per_sample,
+                                       float* x_scale, float* x_zp) {
+  const int top = (1 << n_bits) - 1;
+  for (int s = threadIdx.x; s < slots; s += blockDim.x) {
+    const unsigned int kmax = atomicExch(&scratch->absmax_bits[2 * s], 0u);
+    const unsigned int kmin = atomicExch(&scratch->absmax_bits[2 * s + 1], 0u);
+    const float xmax = kmax ? ord2f(kmax) : 0.0f;
+    const float xmin = kmin ? ord2f(~kmin) : 0.0f;
+    float delta, zp;
+    if (!per_sample) {
+      double d = ((double)xmax - (double)xmin) / (double)top;
+      if (d < 1e-8) d = 1e-8;
+      zp = (float)rint(-(double)xmin / d);
+      delta = (float)d;
+    } else {
+      delta = __fdiv_rn(__fsub_rn(xmax, xmin), (float)top);
+      if (delta < 1e-8f) delta = 1e-8f;
+      zp = rintf(__fdiv_rn(-xmin, delta));
+    }
+    if (!(-zp >= -128.0f && (float)top - zp <= 127.0f)) atomicOr(&g_modq_status, 4);
+    x_scale[s] = delta;
+    x_zp[s] = zp;
+  }
+}
+
+template <bool VEC4, bool XFORM>
+__global__ void __launch_bounds__(kThreads)
+modq_minmax_kernel(const SrcView src, const float* __restrict__ a_hat, modiff_conv_geom g,
+                   TileGrid tg, int n_bits, int per_sample, int slots,
+                   ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
+                   float* __restrict__ x_zp) {
+  const int hw = g.h * g.w;
+  const int cg = threadIdx.x >> 4;
+  const int pq = threadIdx.x & 15;
+  __shared__ bool is_last;
+  float mx0 = -INFINITY, mn0 = INFINITY, mx1 = -INFINITY, mn1 = INFINITY;
+  bool any0 = false, any1 = false;
+  int cur_n = -1;
+  auto flush = [&](int slot, float mn, float mx, bool any) {
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    any = __any_sync(0xffffffffu, any);
+    if ((threadIdx.x & 31) == 0 && any) publish_range(scratch, slot, mn, mx);
+  };
+  for (int tile = blockIdx.x; tile < tg.total; tile += gridDim.x) {
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    const int p = p0 + 4 * pq;
+    if (per_sample && n != cur_n) {
+      if (cur_n >= 0) flush(cur_n, mn0, mx0, any0);
+      mx0 = -INFINITY; mn0 = INFINITY; any0 = false;
+      cur_n = n;
+    }
+    if (p < hw) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + 4 * cg + i;
+        if (c < g.cin) {
+          const size_t off = ((size_t)n * g.cin + c) * hw;
+          float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f};
+          load_src<VEC4, XFORM>(src, n, c, g.cin, p, hw, xv);
+          if (a_hat) load4<VEC4>(a_hat + off, p, hw, av);
+          float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (VEC4 || p + j < hw) {
+              const float r = __fsub_rn(xv[j], av[j]);
+              lo = fminf(lo, r);
+              hi = fmaxf(hi, r);
+            }
+          }
+          if (g.split > 0 && c >= g.split) {
+            mn1 = fminf(mn1, lo); mx1 = fmaxf(mx1, hi); any1 = true;
+          } else {
+            mn0 = fminf(mn0, lo); mx0 = fmaxf(mx0, hi); any0 = true;
+          }
+        }
+      }
+    }
+  }
+  flush(per_sample ? (cur_n < 0 ? 0 : cur_n) : 0, mn0, mx0, any0);
+  if (g.split > 0) flush(1, mn1, mx1, any1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp);
+    if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+modq_flat_minmax_kernel(const float4* __restrict__ x, const float4* __restrict__ a_hat, int64_t n4,
+                        int cin, int split, int n_bits, int per_sample, int slots,
+                        ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
+                        float* __restrict__ x_zp) {
+  __shared__ bool is_last;
+  float mx0 = -INFINITY, mn0 = INFINITY, mx1 = -INFINITY, mn1 = INFINITY;
+  bool any0 = false, any1 = false;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 xv = __ldg(x + i);
+    const float4 av = a_hat ? __ldg(a_hat + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float r0 = __fsub_rn(xv.x, av.x), r1 = __fsub_rn(xv.y, av.y), r2 = __fsub_rn(xv.z, av.z),
+                r3 = __fsub_rn(xv.w, av.w);
+    const float lo = fminf(fminf(r0, r1), fminf(r2, r3)), hi = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
+    const int c = (int)((i * 4) % cin);
+    if (per_sample) {
+      publish_range(scratch, (int)((i * 4) / cin), lo, hi);
+    } else if (split > 0 && c >= split) {
+      mn1 = fminf(mn1, lo); mx1 = fmaxf(mx1, hi); any1 = true;
+    } else {
+      mn0 = fminf(mn0, lo); mx0 = fmaxf(mx0, hi); any0 = true;
+    }
+  }
+  if (!per_sample) {
+    for (int o = 16; o > 0; o >>= 1) {
+      mn0 = fminf(mn0, __shfl_xor_sync(0xffffffffu, mn0, o));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mn1 = fminf(mn1, __shfl_xor_sync(0xffffffffu, mn1, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    any0 = __any_sync(0xffffffffu, any0);
+    any1 = __any_sync(0xffffffffu, any1);
+    if ((threadIdx.x & 31) == 0) {
+      if (any0) publish_range(scratch, 0, mn0, mx0);
+      if (any1) publish_range(scratch, 1, mn1, mx1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp);
+    if (threadIdx.x == 0) scratch->counter = 0u;
   }
 }
 
@@ -513,21 +701,24 @@ modq_flat_absmax_kernel(const float4* __restrict__ x, const float4* __restrict__
 
 __global__ void __launch_bounds__(kThreads)
 modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat,
-                        uint32_t* __restrict__ codes, const float* __restrict__ x_scale, int64_t n4,
-                        int cin, int split, int n_levels, int per_sample) {
+                        uint32_t* __restrict__ codes, const float* __restrict__ x_scale,
+                        const float* __restrict__ x_zp, int64_t n4, int cin, int split, int n_levels,
+                        int per_sample) {
   const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     const int c = (int)((i * 4) % cin);
     const int slot = per_sample ? (int)((i * 4) / cin) : ((split > 0 && c >= split) ? 1 : 0);
     const float delta = x_scale[slot];
+    const float lo_s = x_zp ? -x_zp[slot] : lo;
+    const float hi_s = x_zp ? (float)(2 * n_levels + 1) - x_zp[slot] : hi;
     float4 xv = __ldg(x + i);
     float4 av = a_hat ? a_hat[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     float xs[4] = {xv.x, xv.y, xv.z, xv.w}, as[4] = {av.x, av.y, av.z, av.w}, nv[4];
     uint32_t qb[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float qf = round_clamp(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta), lo, hi, qb[j]);
+      const float qf = round_clamp(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta), lo_s, hi_s, qb[j]);
       nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
     }
     if (a_hat) a_hat[i] = make_float4(nv[0], nv[1], nv[2], nv[3]);
@@ -878,9 +1069,10 @@ static bool staged_encode_enabled() {
   return on;
 }
 
+// x_zp != nullptr selects asymmetric codes (range pass instead of the maximum pass).
 int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes, float* x_scale,
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
-                    bool compute_scale, cudaStream_t s) {
+                    bool compute_scale, cudaStream_t s, float* x_zp = nullptr) {
   Derived d = derive(*g);
   const int hw = g->h * g->w;
   const int n_levels = sym_levels(n_bits);
@@ -895,14 +1087,19 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
     const int64_t n4 = (int64_t)g->batch * g->cin / 4;
     int blocks = (int)ceil_div64(n4, kThreads);
     if (blocks > kMaxBlocks) blocks = kMaxBlocks;
-    if (compute_scale) {
+    if (compute_scale && x_zp) {
+      modq_flat_minmax_kernel<<<blocks, kThreads, 0, s>>>(
+          (const float4*)x, (const float4*)a_hat, n4, g->cin, g->split, n_bits, per_sample, slots,
+          (ModqScratch*)scratch, x_scale, x_zp);
+      MODIFF_LAUNCH_CHECK("modq_flat_minmax_kernel");
+    } else if (compute_scale) {
       modq_flat_absmax_kernel<<<blocks, kThreads, 0, s>>>(
           (const float4*)x, (const float4*)a_hat, n4, g->cin, g->split, n_levels, per_sample, slots,
           (ModqScratch*)scratch, x_scale);
       MODIFF_LAUNCH_CHECK("modq_flat_absmax_kernel");
     }
     modq_flat_encode_kernel<<<blocks, kThreads, 0, s>>>((const float4*)x, (float4*)a_hat,
-                                                        (uint32_t*)codes, x_scale, n4, g->cin,
+                                                        (uint32_t*)codes, x_scale, x_zp, n4, g->cin,
                                                         g->split, n_levels, per_sample);
     MODIFF_LAUNCH_CHECK("modq_flat_encode_kernel");
     return MODIFF_OK;
@@ -920,29 +1117,31 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
   tg.total = (int)total;
   const int blocks = tg.total < kMaxBlocks ? tg.total : kMaxBlocks;
   const bool vec = (hw % 4 == 0) && aligned;
+#define MODIFF_MODQ_SCALE(V, X)                                                                    \
+  if (compute_scale && x_zp) {                                                                   \
+    modq_minmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_bits, per_sample,   \
+                                                        slots, (ModqScratch*)scratch, x_scale,   \
+                                                        x_zp);                                   \
+    MODIFF_LAUNCH_CHECK("modq_minmax_kernel");                                                   \
+  } else if (compute_scale) {                                                                    \
+    modq_absmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_levels, per_sample, \
+                                                        slots, (ModqScratch*)scratch, x_scale);  \
+    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");                                                   \
+  }
 #define MODIFF_MODQ_LAUNCH(V, X)                                                                   \
   {                                                                                              \
-    if (compute_scale) {                                                                         \
-      modq_absmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_levels, per_sample, \
-                                                          slots, (ModqScratch*)scratch, x_scale); \
-      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");                                                 \
-    }                                                                                            \
-    modq_encode_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, codes, x_scale, *g, d, tg,    \
-                                                        n_levels, per_sample);                   \
+    MODIFF_MODQ_SCALE(V, X)                                                                      \
+    modq_encode_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, codes, x_scale, x_zp, *g, d,  \
+                                                        tg, n_levels, per_sample);               \
     MODIFF_LAUNCH_CHECK("modq_encode_kernel");                                                   \
   }
   if (vec && staged_encode_enabled()) {
     // three 68 KB blocks per SM keep three tiles of input in flight
     const int sblocks = tg.total < 148 * 3 ? tg.total : 148 * 3;
-    if (compute_scale) {
-      if (xform) {
-        modq_absmax_kernel<true, true><<<blocks, kThreads, 0, s>>>(
-            src, a_hat, *g, tg, n_levels, per_sample, slots, (ModqScratch*)scratch, x_scale);
-      } else {
-        modq_absmax_kernel<true, false><<<blocks, kThreads, 0, s>>>(
-            src, a_hat, *g, tg, n_levels, per_sample, slots, (ModqScratch*)scratch, x_scale);
-      }
-      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    if (xform) {
+      MODIFF_MODQ_SCALE(true, true)
+    } else {
+      MODIFF_MODQ_SCALE(true, false)
     }
     static bool attr_set[2] = {false, false};
     if (xform) {
@@ -952,7 +1151,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
         attr_set[1] = true;
       }
       modq_encode_staged_kernel<true><<<sblocks, kThreads, kStagedSmem, s>>>(
-          src, a_hat, codes, x_scale, *g, d, tg, n_levels, per_sample);
+          src, a_hat, codes, x_scale, x_zp, *g, d, tg, n_levels, per_sample);
     } else {
       if (!attr_set[0]) {
         MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_staged_kernel<false>,
@@ -960,7 +1159,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
         attr_set[0] = true;
       }
       modq_encode_staged_kernel<false><<<sblocks, kThreads, kStagedSmem, s>>>(
-          src, a_hat, codes, x_scale, *g, d, tg, n_levels, per_sample);
+          src, a_hat, codes, x_scale, x_zp, *g, d, tg, n_levels, per_sample);
     }
     MODIFF_LAUNCH_CHECK("modq_encode_staged_kernel");
     return MODIFF_OK;
@@ -970,6 +1169,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
   else if (xform) MODIFF_MODQ_LAUNCH(false, true)
   else MODIFF_MODQ_LAUNCH(false, false)
 #undef MODIFF_MODQ_LAUNCH
+#undef MODIFF_MODQ_SCALE
   return MODIFF_OK;
 }
 
@@ -1114,6 +1314,43 @@ extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, c
   v.affine = affine;
   return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
 }
+
+extern "C" int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes,
+                                float* x_scale, float* x_zp, const modiff_conv_geom* g, int n_bits,
+                                int per_sample, void* scratch, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale && x_zp && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 7,
+                   "asymmetric activation codes are stored centred (q - zero_point) in int8 planes: "
+                   "n_bits %d outside [2, 7]", n_bits);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.bias = src->chan_bias;
+  v.affine = src->affine;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
+  return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
+                         (cudaStream_t)stream, x_zp);
+}
+
+namespace modiff {
+int read_device_status_modq(int* status, int reset) {
+  MODIFF_CUDA(cudaMemcpyFromSymbol(status, g_modq_status, sizeof(int)));
+  if (reset) {
+    int zero = 0;
+    MODIFF_CUDA(cudaMemcpyToSymbol(g_modq_status, &zero, sizeof(int)));
+  }
+  return MODIFF_OK;
+}
+}  // namespace modiff
 
 // ---------------------------------------------------------------------------------------
 // Built-in scratch for callers that cannot allocate.

@@ -120,7 +120,8 @@ class _Buffers:
         self.g = g
         self.codes = _zeros(l.modiff_codes_bytes(C.byref(g)), torch.int8, device)
         self.x_scale = _zeros(max(2, g.batch if per_sample else 2), torch.float32, device)
-        self.scratch = _zeros(_lib.MODQ_SCRATCH_BYTES + 4 * g.batch, torch.uint8, device)
+        self.x_zp = _zeros(max(2, g.batch if per_sample else 2), torch.float32, device)
+        self.scratch = _zeros(_lib.MODQ_SCRATCH_BYTES + 8 * g.batch, torch.uint8, device)
         self.ho, self.wo = _lib.out_hw(g)
 
 
@@ -243,11 +244,13 @@ class QuantModule(nn.Module):
             n = g.batch if per_sample else 1
             self.act_quantizer.delta = buf.x_scale[0:n].view([n] + [1] * 3) if per_sample \
                 else buf.x_scale[0:1].view([])
-            self.act_quantizer.zero_point = 0
+            asym = not self.act_quantizer.sym
+            self.act_quantizer.zero_point = 0 if not asym else (
+                buf.x_zp[0:n].view([n] + [1] * 3) if per_sample else buf.x_zp[0:1].view([]))
             self.act_quantizer.inited = True
             if g.split:
                 self.act_quantizer_0.delta = buf.x_scale[1:2].view([])
-                self.act_quantizer_0.zero_point = 0
+                self.act_quantizer_0.zero_point = 0 if not asym else buf.x_zp[1:2].view([])
                 self.act_quantizer_0.inited = True
         return buf
 
@@ -362,11 +365,25 @@ class QuantModule(nn.Module):
 
     def _modq(self, x, a_hat, buf, g, src=None):
         aq = self.act_quantizer
-        if not aq.sym:
-            raise ModiffError("the int8 path implements symmetric activation codes (--a_sym)")
         if not aq.dynamic:
             raise ModiffError("the int8 path implements dynamic activation scales "
                               "(quant_mode='dynamic'); static calibrated scales are not covered")
+        if not aq.sym:
+            # asymmetric codes (the reference's default without --a_sym): centred codes in the
+            # same int8 planes, which bounds them to 7 bits
+            if aq.n_bits > 7:
+                raise ModiffError("asymmetric activation codes are implemented for up to 7 bits "
+                                  "(centred codes in int8 planes); use --a_sym for 8-bit activations")
+            if src is not None:
+                st = src.struct()
+            else:
+                st = _lib.ActSourceStruct(x.data_ptr(), None, g.cin, 0, None, None)
+            n = src.numel() if src is not None else x.numel()
+            _lib.call('modiff_modq_asym', C.byref(st), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                      buf.x_scale.data_ptr(), buf.x_zp.data_ptr(), C.byref(g), aq.n_bits,
+                      int(aq.channel_wise), buf.scratch.data_ptr(), _lib.stream_ptr(),
+                      nbytes=(13 if a_hat is not None else 5) * n, tag=g.key())
+            return
         if src is not None and src.pending_norm() and self.fuse_norm_stats:
             n = src.norm
             raw, table = src.raw_struct()

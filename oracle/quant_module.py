@@ -111,6 +111,7 @@ class OracleQuantModule:
             accs.append(self._fwd(a, w_int, None).round().to(torch.int64))
         return dict(codes=[a[1].to(torch.int32) for a in acts],
                     x_scale=[a[2] for a in acts],
+                    x_zp=[a[3] for a in acts],
                     w_codes=[p[1].to(torch.int32) for p in wparts],
                     w_scale=[p[2].reshape(-1) for p in wparts],
                     w_zp=[p[3].reshape(-1) for p in wparts],

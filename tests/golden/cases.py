@@ -60,6 +60,13 @@ LAYER_CASES = [
          w_bits=4, a_bits=4, seed=110),
     dict(name="c3_32_w8a8", kind="conv", cin=128, cout=16, k=3, stride=1, pad=1, hw=32, batch=1,
          w_bits=8, a_bits=8, seed=111, skip_a_hat=True),
+    # asymmetric activation codes: the LDM / SD drivers' default (no --a_sym)
+    dict(name="c3_w4a4_asym", kind="conv", cin=128, cout=128, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=4, a_bits=4, a_sym=False, seed=112),
+    dict(name="c1_split_w8a4_asym", kind="conv", cin=256, cout=128, k=1, stride=1, pad=0, hw=8,
+         batch=2, w_bits=8, a_bits=4, a_sym=False, split=128, seed=113),
+    dict(name="lin_w8a6_asym", kind="linear", cin=256, cout=128, batch=6, w_bits=8, a_bits=6,
+         a_sym=False, seed=114),
 ]
 
 
@@ -86,7 +93,8 @@ def quant_params(c):
     """The dicts scripts/sample_diffusion_ddim.py:143-146 builds for
     --ptq --quant_act --quant_mode dynamic --a_sym."""
     wq = {'n_bits': c["w_bits"], 'channel_wise': True, 'scale_method': 'max'}
-    aq = {'n_bits': c["a_bits"], 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+    aq = {'n_bits': c["a_bits"], 'symmetric': c.get("a_sym", True), 'channel_wise': False,
+          'scale_method': 'max',
           'leaf_param': True, 'dynamic': True}
     return wq, aq
 

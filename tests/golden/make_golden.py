@@ -88,6 +88,11 @@ def gen_layers():
                     if c.get("split", 0):
                         d.append(float(m.act_quantizer_0.delta))
                     out[f"{c['name']}/delta{s}"] = np.asarray(d, dtype=np.float32)
+                    if not c.get("a_sym", True):
+                        z = [float(m.act_quantizer.zero_point)]
+                        if c.get("split", 0):
+                            z.append(float(m.act_quantizer_0.zero_point))
+                        out[f"{c['name']}/zp{s}"] = np.asarray(z, dtype=np.float32)
             if not c.get("skip_a_hat"):
                 out[f"{c['name']}/a_hat"] = m.a_hat.numpy().copy()
         wd = m.weight_quantizer.delta.detach().reshape(-1).numpy()

@@ -20,9 +20,11 @@ def _modules(c, cuda):
     ours.set_quant_state(True, True)
     w, b = org.weight.detach().cpu(), org.bias.detach().cpu()
     if c["kind"] == "linear":
-        orc = oracle.OracleQuantModule(w, b, w_bits=c["w_bits"], a_bits=c["a_bits"])
+        orc = oracle.OracleQuantModule(w, b, w_bits=c["w_bits"], a_bits=c["a_bits"],
+                                       a_sym=c.get("a_sym", True))
     else:
-        orc = oracle.OracleQuantModule(w, b, c["stride"], c["pad"], c["w_bits"], c["a_bits"])
+        orc = oracle.OracleQuantModule(w, b, c["stride"], c["pad"], c["w_bits"], c["a_bits"],
+                                       c.get("a_sym", True))
     return ours, orc
 
 
@@ -51,6 +53,12 @@ def test_layer_against_reference_fixture(cuda, c, impl, golden_layers):
                 if split:
                     d.append(float(ours.act_quantizer_0.delta))
                 np.testing.assert_array_equal(np.asarray(d, dtype=np.float32), g[f"{c['name']}/delta{s}"])
+                if not c.get("a_sym", True):
+                    z = [float(ours.act_quantizer.zero_point)]
+                    if split:
+                        z.append(float(ours.act_quantizer_0.zero_point))
+                    np.testing.assert_array_equal(np.asarray(z, dtype=np.float32),
+                                                  g[f"{c['name']}/zp{s}"])
     if not c.get("skip_a_hat"):
         np.testing.assert_array_equal(ours.a_hat.cpu().numpy(), g[f"{c['name']}/a_hat"])
     np.testing.assert_array_equal(ours.weight_quantizer.delta.cpu().numpy().reshape(-1),
@@ -220,3 +228,71 @@ def test_small_linears_sharing_codes_run_in_one_launch(cuda, w_bits):
     # steps >= 1: quantiser (2 kernels) + 1 grouped launch, against quantiser + 4 GEMM launches
     assert launches[-2:] == [3, 6]
     assert m.device_status() == 0
+
+
+@pytest.mark.parametrize("kind,shape,cout,split,per_sample,a_bits", [
+    ("conv3", (3, 128, 16, 16), 128, 0, False, 4),     # staged encode, tensor-core GEMM
+    ("conv3", (2, 192, 8, 8), 64, 128, False, 4),      # split scales
+    ("conv1", (4, 64, 6, 6), 32, 0, False, 6),         # odd size: scalar loads, CUDA-core GEMM
+    ("linear", (5, 77, 256), 128, 0, False, 4),        # tokens x channels
+    ("conv3", (4, 128, 8, 8), 128, 0, True, 4),        # one scale per image (--act_tensor)
+    ("linear", (6, 256), 64, 0, True, 7),
+])
+def test_asymmetric_activation_codes(cuda, kind, shape, cout, split, per_sample, a_bits):
+    """The reference's activation quantiser without --a_sym (sym=False,
+    qdiff/quant_layer.py:191-214, 160-190): scales, zero points and the cache are bit-exact
+    against the oracle on identical inputs, outputs within 2e-5 after the first step."""
+    import modiff_b200 as m
+    torch.manual_seed(31)
+    cin = shape[1] if kind != "linear" else shape[-1]
+    if kind == "linear":
+        org = torch.nn.Linear(cin, cout)
+        orc = oracle.OracleQuantModule(org.weight.detach().clone(), org.bias.detach().clone(), 1, 0,
+                                       8, a_bits, False, per_sample)
+    else:
+        k = 3 if kind == "conv3" else 1
+        org = torch.nn.Conv2d(cin, cout, k, padding=k // 2)
+        orc = oracle.OracleQuantModule(org.weight.detach().clone(), org.bias.detach().clone(), 1,
+                                       k // 2, 8, a_bits, False, per_sample)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': a_bits, 'symmetric': False, 'channel_wise': per_sample, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    ours = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
+    ours.set_quant_state(True, True)
+    ours.alias_output = False
+    g = torch.Generator().manual_seed(32)
+    x = torch.randn(shape, generator=g)
+    kw = dict(split=split) if split else {}
+    with torch.no_grad():
+        for step in range(4):
+            # residuals with a non-zero mean, so the zero point is far from the middle
+            xs = x + 0.05 * step * (torch.randn(shape, generator=g) + 0.7)
+            ref = orc.forward(xs, **kw)
+            got = ours(xs.to(cuda), **kw).cpu()
+            err = float((got - ref).abs().max() / ref.abs().max())
+            assert err < 1e-4, (step, err)
+            if step > 0:
+                d = [ours.act_quantizer.delta.reshape(-1).cpu()]
+                z = [ours.act_quantizer.zero_point.reshape(-1).cpu()]
+                if split:
+                    d.append(ours.act_quantizer_0.delta.reshape(-1).cpu())
+                    z.append(ours.act_quantizer_0.zero_point.reshape(-1).cpu())
+                for s_, (dd, zz) in enumerate(zip(d, z)):
+                    assert torch.equal(dd, torch.as_tensor(orc.last['x_scale'][s_]).reshape(-1).float())
+                    assert torch.equal(zz, torch.as_tensor(orc.last['x_zp'][s_]).reshape(-1).float())
+                assert torch.equal(ours.a_hat.cpu(), orc.a_hat)
+    assert m.device_status() == 0
+
+
+def test_asymmetric_codes_refuse_eight_bits(cuda):
+    import modiff_b200 as m
+    org = torch.nn.Conv2d(64, 64, 3, padding=1)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': False, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    q = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
+    q.set_quant_state(True, True)
+    x = torch.randn(2, 64, 8, 8, device=cuda)
+    q(x)
+    with pytest.raises(m.ModiffError):
+        q(x + 0.1)

@@ -31,8 +31,10 @@ def _oracle_layer(c):
     w = org.weight.detach()
     b = org.bias.detach()
     if c["kind"] == "linear":
-        return oracle.OracleQuantModule(w, b, w_bits=c["w_bits"], a_bits=c["a_bits"])
-    return oracle.OracleQuantModule(w, b, c["stride"], c["pad"], c["w_bits"], c["a_bits"])
+        return oracle.OracleQuantModule(w, b, w_bits=c["w_bits"], a_bits=c["a_bits"],
+                                        a_sym=c.get("a_sym", True))
+    return oracle.OracleQuantModule(w, b, c["stride"], c["pad"], c["w_bits"], c["a_bits"],
+                                    c.get("a_sym", True))
 
 
 @pytest.mark.parametrize("c", cases.LAYER_CASES, ids=lambda c: c["name"])
@@ -49,6 +51,9 @@ def test_layer_matches_reference(c, golden_layers):
             if s > 0:
                 d = np.asarray([float(v) for v in m.last["x_scale"]], dtype=np.float32)
                 np.testing.assert_array_equal(d, g[f"{c['name']}/delta{s}"])
+                if not c.get("a_sym", True):
+                    z = np.asarray([float(v) for v in m.last["x_zp"]], dtype=np.float32)
+                    np.testing.assert_array_equal(z, g[f"{c['name']}/zp{s}"])
     if not c.get("skip_a_hat"):
         np.testing.assert_array_equal(m.a_hat.numpy(), g[f"{c['name']}/a_hat"])
     np.testing.assert_array_equal(m.last["w_scale"][0].numpy(), g[f"{c['name']}/w_delta"])
