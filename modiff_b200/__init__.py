@@ -8,7 +8,7 @@ from .quant_block import (BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, Quan
 from .quant_model import QuantModel
 from .unet import Model, make_config
 from .ldm_unet import UNetModel, rerandomize_zero_tensors
-from .ldm_sampler import DDIMSampler
+from .ldm_sampler import DDIMSampler, PLMSSampler
 from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
                       make_timestep_sequence)
 
@@ -17,6 +17,6 @@ __all__ = [
     "StraightThrough", "round_ste", "BaseQuantBlock", "QuantResnetBlock", "QuantAttnBlock",
     "QuantResBlock", "QuantBasicTransformerBlock", "QuantQKMatMul", "QuantSMVMatMul",
     "QuantAttentionBlock",
-    "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
+    "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "PLMSSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
     "get_beta_schedule", "make_timestep_sequence",
 ]

@@ -118,3 +118,78 @@ class DDIMSampler:
                 img_callback(e_t, i)
             img = ops.ddim_step(img, e_t, s1, s2, s3, sigma, c2, noise=noise)
         return img, {}
+
+
+class PLMSSampler(DDIMSampler):
+    """Pseudo linear multistep sampler (ldm/models/diffusion/plms.py:12-240), what the reference's
+    Stable-Diffusion command runs (`txt2img.py --plms`).  Same schedule and update as DDIM with
+    eta = 0, but the eps that enters the update is an Adams-Bashforth combination of the last up
+    to four model outputs; the first step evaluates the model twice."""
+
+    def make_schedule(self, ddim_num_steps, ddim_discretize="uniform", ddim_eta=0., verbose=False):
+        if ddim_eta != 0:
+            raise ValueError('ddim_eta must be 0 for PLMS')          # plms.py:27-28
+        super().make_schedule(ddim_num_steps, ddim_discretize, ddim_eta, verbose)
+
+    @torch.no_grad()
+    def sample(self, S, batch_size, shape, conditioning=None, eta=0., x_T=None,
+               unconditional_guidance_scale=1., unconditional_conditioning=None, max_steps=None,
+               img_callback=None, cuda_graph=None, **kwargs):
+        """Returns (samples, intermediates); `img_callback(e, k)` sees every model output in
+        evaluation order; `max_steps` stops early."""
+        self.make_schedule(S, ddim_eta=eta)
+        model = self.model
+        if cuda_graph is None:
+            cuda_graph = os.environ.get("MODIFF_CUDA_GRAPH", "1") != "0"
+        img = x_T
+        if img is None:
+            raise ValueError("x_T is required (noise is drawn by the caller so shards can be "
+                             "re-created)")
+        guided = unconditional_conditioning is not None and unconditional_guidance_scale != 1.
+        if cuda_graph and hasattr(model, "graphed") and img.is_cuda and conditioning is None:
+            model = model.graphed()
+        b = img.shape[0]
+        time_range = np.flip(self.ddim_timesteps)
+        total = time_range.shape[0]
+        n_eval = [0]
+
+        def model_output(x, step):
+            t = torch.full((b,), float(step), dtype=torch.float32, device=x.device)
+            if not guided:
+                e = model(x, t, conditioning) if conditioning is not None else model(x, t)
+                e = e.clone()          # the graphed model and aliased caches reuse their output buffer
+            else:
+                e_all = model(torch.cat([x] * 2), torch.cat([t] * 2),
+                              torch.cat([unconditional_conditioning, conditioning]))
+                e = ops.cfg_combine(e_all[:b], e_all[b:], float(unconditional_guidance_scale))
+            if img_callback is not None:
+                img_callback(e, n_eval[0])
+            n_eval[0] += 1
+            return e
+
+        old_eps = []
+        for i, step in enumerate(time_range):
+            if max_steps is not None and i >= max_steps:
+                break
+            index = total - i - 1
+            step_next = time_range[min(i + 1, total - 1)]
+            s1, s2, s3, sigma, c2 = self._coefficients(index)
+            e_t = model_output(img, step)
+            # the combinations below are the reference's own tensor expressions, one rounding
+            # per operation (plms.py:221-234)
+            if len(old_eps) == 0:
+                x_prev = ops.ddim_step(img, e_t, s1, s2, s3, 0.0, c2)
+                e_t_next = model_output(x_prev, step_next)
+                e_prime = (e_t + e_t_next) / 2
+            elif len(old_eps) == 1:
+                e_prime = (3 * e_t - old_eps[-1]) / 2
+            elif len(old_eps) == 2:
+                e_prime = (23 * e_t - 16 * old_eps[-1] + 5 * old_eps[-2]) / 12
+            else:
+                e_prime = (55 * e_t - 59 * old_eps[-1] + 37 * old_eps[-2] - 9 * old_eps[-3]) / 24
+            img = ops.ddim_step(img, e_prime, s1, s2, s3, 0.0, c2)
+            old_eps.append(e_t)
+            if len(old_eps) >= 4:
+                old_eps.pop(0)
+        return img, {}
+

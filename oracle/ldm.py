@@ -271,3 +271,63 @@ def latent_ddim_sample(x, model_fn, alphas_cumprod, steps, max_evals=None, on_st
         if on_step is not None:
             on_step(i, e_t, img)
     return img
+
+
+@torch.no_grad()
+def latent_plms_sample(x, model_fn, alphas_cumprod, steps, max_steps=None, on_eval=None,
+                       cond=None, uncond=None, guidance=1.0):
+    """ldm/models/diffusion/plms.py:114-240 (eta = 0): pseudo linear multistep over the DDIM
+    schedule.  The first step evaluates the model twice (improved Euler, :221-225), later steps
+    combine the last up to four eps with Adams-Bashforth weights (:226-234).  `on_eval(k, e)`
+    sees every model output in evaluation order; `max_steps` stops early."""
+    ts, alphas, alphas_prev = ddim_parameters(alphas_cumprod, steps)
+    sqrt_one_minus = np.sqrt(1. - alphas)
+    b = x.shape[0]
+    img = x
+    time_range = np.flip(ts)
+    total = ts.shape[0]
+    old_eps = []
+    n_eval = [0]
+
+    def model_output(xx, step):
+        t = torch.full((b,), int(step), dtype=torch.long)
+        if uncond is None or guidance == 1.0:
+            e = model_fn(xx, t) if cond is None else model_fn(xx, t, cond)
+        else:
+            e_all = model_fn(torch.cat([xx] * 2), torch.cat([t] * 2), torch.cat([uncond, cond]))
+            e_uc, e_c = e_all.chunk(2)
+            e = e_uc + guidance * (e_c - e_uc)
+        if on_eval is not None:
+            on_eval(n_eval[0], e)
+        n_eval[0] += 1
+        return e
+
+    def x_prev_of(e, index):
+        a_t = torch.full((b, 1, 1, 1), float(alphas[index]))
+        a_prev = torch.full((b, 1, 1, 1), float(alphas_prev[index]))
+        sqrt_one_minus_at = torch.full((b, 1, 1, 1), float(sqrt_one_minus[index]))
+        pred_x0 = (img - sqrt_one_minus_at * e) / a_t.sqrt()
+        dir_xt = (1. - a_prev).sqrt() * e
+        return a_prev.sqrt() * pred_x0 + dir_xt
+
+    for i, step in enumerate(time_range):
+        if max_steps is not None and i >= max_steps:
+            break
+        index = total - i - 1
+        step_next = time_range[min(i + 1, len(time_range) - 1)]
+        e_t = model_output(img, step)
+        if len(old_eps) == 0:
+            e_t_next = model_output(x_prev_of(e_t, index), step_next)
+            e_prime = (e_t + e_t_next) / 2
+        elif len(old_eps) == 1:
+            e_prime = (3 * e_t - old_eps[-1]) / 2
+        elif len(old_eps) == 2:
+            e_prime = (23 * e_t - 16 * old_eps[-1] + 5 * old_eps[-2]) / 12
+        else:
+            e_prime = (55 * e_t - 59 * old_eps[-1] + 37 * old_eps[-2] - 9 * old_eps[-3]) / 24
+        img = x_prev_of(e_prime, index)
+        old_eps.append(e_t)
+        if len(old_eps) >= 4:
+            old_eps.pop(0)
+    return img
+

@@ -140,6 +140,14 @@ LDM_CASES = [
 ]
 
 
+PLMS_CASES = [
+    # pseudo linear multistep over 50 DDIM timesteps: 4 steps = 5 UNet evaluations (the first step
+    # evaluates twice), Adams-Bashforth orders 2, 3 and 4 all taken
+    dict(name="ldm_plms_w8a8_b2", w_bits=8, a_bits=8, batch=2, ddim_steps=50, steps=4, noise_seed=12,
+         zero_seed=1234),
+]
+
+
 def ldm_noise(c):
     g = torch.Generator().manual_seed(c["noise_seed"])
     return torch.randn(c["batch"], 4, 32, 32, generator=g)

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|sd]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -201,6 +201,37 @@ def gen_ldm():
     print("ldm.npz", len(out))
 
 
+def gen_plms():
+    """The latent UNet of gen_ldm under the PLMS loop (ldm/models/diffusion/plms.py:114-240)."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from modiff_b200.ldm_unet import rerandomize_zero_tensors
+    from oracle.ldm import ldm_schedule, latent_plms_sample
+    from ldm.modules.diffusionmodules.openaimodel import UNetModel as RefUNet
+    out = {}
+    ac = ldm_schedule(**cases.LDM_SCHEDULE)
+    for c in cases.PLMS_CASES:
+        t0 = time.time()
+        torch.manual_seed(0)
+        model = RefUNet(**cases.LDM_CONFIG).eval()
+        rerandomize_zero_tensors(model, seed=c["zero_seed"])
+        wq, aq = cases.quant_params(c)
+        qnn = RefQuantModel(model=model, weight_quant_params=wq, act_quant_params=aq, sm_abit=8,
+                            modulate=True).eval()
+        qnn.set_quant_state(True, True)
+        qnn.set_grad_ckpt(False)
+        qnn.reset_cache()
+        eps = []
+        final = latent_plms_sample(cases.ldm_noise(c), lambda a, t: qnn(a, t), ac, c["ddim_steps"],
+                                   max_steps=c["steps"],
+                                   on_eval=lambda k, e: eps.append(e.numpy().copy()))
+        out[c["name"] + "/final"] = final.numpy().copy()
+        for i, e in enumerate(eps):
+            out[f"{c['name']}/eps{i}"] = e
+        print(c["name"], f"{time.time() - t0:.1f}s", len(eps), float(final.std()))
+    np.savez_compressed(os.path.join(HERE, "plms.npz"), **out)
+    print("plms.npz", len(out))
+
+
 def gen_sd():
     """SD-v1 UNet shapes (random init seed 0, zero tensors redrawn), reference QuantModel with
     --a_sym, classifier-free guidance as ldm/models/diffusion/ddim.py:192-208."""
@@ -248,7 +279,7 @@ def gen_sd():
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
-                ldm=gen_ldm, sd=gen_sd)
+                ldm=gen_ldm, plms=gen_plms, sd=gen_sd)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()
