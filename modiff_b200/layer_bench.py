@@ -5,6 +5,7 @@
 Prints one JSON line: device time per call and achieved algorithmic GB/s of `modiff_modq`
 and `modiff_igemm_conv` (CUDA events on the launching stream; the tensors of one layer at
 batch 256 exceed L2).  Small enough to sit under `ncu -k regex:... -c 1`.
+`--attention` times `ops.attention` (plane splits + attention kernel) at [batch, cin, hw*hw].
 """
 import argparse
 import json
@@ -33,10 +34,28 @@ def main():
     ap.add_argument("--linear", action="store_true")
     ap.add_argument("--fused", action="store_true",
                     help="feed the layer GroupNorm(32)+SiLU of the input as a lazy source")
+    ap.add_argument("--attention", action="store_true",
+                    help="time ops.attention on [batch, cin, hw*hw] tensors instead of a layer")
     args = ap.parse_args()
 
     dev = torch.device("cuda")
     torch.manual_seed(0)
+    if args.attention:
+        from . import ops
+        t = args.hw * args.hw
+        q, k, v = (torch.randn(args.batch, args.cin, t, device=dev) for _ in range(3))
+        scale = float(args.cin) ** -0.5
+        for _ in range(args.warmup):
+            ops.attention(q, k, v, scale)
+        _lib.TIMER = _lib.KernelTimer()
+        for _ in range(args.iters):
+            ops.attention(q, k, v, scale)
+        summ = _lib.TIMER.summary()
+        _lib.TIMER = None
+        print(json.dumps({"geometry": vars(args), "device_status": _lib.device_status(),
+                          "us_per_call": {n: 1000.0 * v_["ms"] / v_["launches"]
+                                          for n, v_ in summ.items()}}))
+        return
     if args.linear:
         org = nn.Linear(args.cin, args.cout)
         shape = (args.batch, args.cin)
