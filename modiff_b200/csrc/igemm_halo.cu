@@ -25,7 +25,7 @@ namespace {
 
 constexpr int kChunkK = 128;                     // bytes of K per weight tile row
 constexpr int kEpiWarps = 8;
-constexpr int kASlots = 2;
+constexpr int kMaxASlots = 3;
 constexpr int kOSlots = 2;
 constexpr int kOHalfBytes = 64 * 128 * 4;        // 64 channels x 128 pixels fp32
 constexpr int kMaxBStages = 6;
@@ -46,6 +46,7 @@ struct HaloParams {
   int b_stages;
   int a_bytes;          // bytes of one activation copy: (rows + 2) * w * 128
   int a_slot_bytes;
+  int a_slots;          // activation copies in flight (2..4)
   int tmem_cols;
   int accumulate;
   int umma_n;           // 128, or 144 with the receptive-field-sum rows (zero-point correction)
@@ -72,7 +73,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_o, const HaloParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_a_full[kASlots], bar_a_empty[kASlots];
+  __shared__ __align__(8) uint64_t bar_a_full[kMaxASlots], bar_a_empty[kMaxASlots];
   __shared__ __align__(8) uint64_t bar_b_full[kMaxBStages], bar_b_empty[kMaxBStages];
   __shared__ __align__(8) uint64_t bar_tmem_full[2], bar_tmem_empty[2];
   __shared__ __align__(8) uint64_t bar_o_full[kOSlots], bar_o_empty[kOSlots], bar_o_ready[kOSlots];
@@ -87,14 +88,14 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t a_ring = raw;
-  const uint32_t b_ring = a_ring + kASlots * (uint32_t)p.a_slot_bytes;
+  const uint32_t b_ring = a_ring + (uint32_t)p.a_slots * (uint32_t)p.a_slot_bytes;
   const uint32_t b_tile = (uint32_t)p.b_tile_bytes;
   const uint32_t obuf = b_ring + (uint32_t)p.b_stages * b_tile;
   float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
 
   if (threadIdx.x == 0) {
     abort_sh = 0;
-    for (int s = 0; s < kASlots; ++s) {
+    for (int s = 0; s < p.a_slots; ++s) {
       mbar_init(smem_u32(&bar_a_full[s]), 1);
       mbar_init(smem_u32(&bar_a_empty[s]), 1);
     }
@@ -143,7 +144,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
             // padded input rows th*rows .. th*rows+rows+1, padded columns dx .. dx+w-1
             tma_load_5d(a_ring + aslot * (uint32_t)p.a_slot_bytes, &map_a, afull, ch * kChunkK, dx,
                         t.th * p.rows, 0, t.n);
-            if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+            if (++aslot == p.a_slots) { aslot = 0; aphase ^= 1u; }
             for (int dy = 0; dy < 3; ++dy) {
               ok = mbar_wait(smem_u32(&bar_b_empty[bst]), bphase ^ 1u, abort_flag);
               if (!ok) break;
@@ -195,7 +196,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             if (!ok) break;
             tc_commit(smem_u32(&bar_a_empty[aslot]));
-            if (++aslot == kASlots) { aslot = 0; aphase ^= 1u; }
+            if (++aslot == p.a_slots) { aslot = 0; aphase ^= 1u; }
           }
         }
         if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
@@ -401,10 +402,15 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.kp = d.kp;
   p.a_bytes = (p.rows + 2) * g->w * kChunkK;
   p.a_slot_bytes = round_up(p.a_bytes, 1024);
-  const int fixed = kASlots * p.a_slot_bytes + kOSlots * kOHalfBytes;
+  // a third activation copy in flight where it leaves four weight stages (measured: 80 -> 76 us
+  // with 128-pixel tiles; a fourth gains nothing: the kernel is bound by the shared-memory fill
+  // bandwidth, not by the latency of a copy)
+  p.a_slots = 2;
+  if (224 * 1024 - 3 * p.a_slot_bytes - kOSlots * kOHalfBytes >= 4 * p.b_tile_bytes) p.a_slots = 3;
+  const int fixed = p.a_slots * p.a_slot_bytes + kOSlots * kOHalfBytes;
   p.b_stages = (224 * 1024 - fixed) / p.b_tile_bytes;
   if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
-  if (p.b_stages < 3) return set_error(MODIFF_ERR_UNSUPPORTED, "tile does not fit shared memory");
+  if (p.b_stages < 2) return set_error(MODIFF_ERR_UNSUPPORTED, "tile does not fit shared memory");
   p.tmem_cols = (2 * p.mh * p.umma_n) > 256 ? 512 : 256;
   p.accumulate = accumulate;
   p.x_scale = x_scale;
