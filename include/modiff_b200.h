@@ -139,6 +139,19 @@ int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, f
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     void* stream);
 
+/* Two quantisers of ONE tensor in two sweeps instead of four: layer A reads
+ * nonlinearity(norm(x)) (modiff_modq_gn), layer B reads x itself (modiff_modq_src) - a residual
+ * block's first convolution and its shortcut convolution (qdiff/quant_block.py:279-283 and
+ * 306-311 over qdiff/quant_layer.py:325-336).  x = [x0 | x1] as in modiff_act_source (no channel
+ * bias).  Each layer keeps its own cache, scales (B may be split), scratch and code planes; the
+ * results equal the two separate calls bit for bit.  Layer A must have split == 0; shapes the
+ * paired kernels do not cover run the two calls one after the other. */
+int modiff_modq_pair(const modiff_act_source* src, const float* gamma, const float* beta, int groups,
+                     float eps, float* affine, float* a_hat_a, int8_t* codes_a, float* x_scale_a,
+                     const modiff_conv_geom* g_a, int n_bits_a, void* scratch_a, float* a_hat_b,
+                     int8_t* codes_b, float* x_scale_b, const modiff_conv_geom* g_b, int n_bits_b,
+                     void* scratch_b, void* stream);
+
 /* modiff_modq_src with ASYMMETRIC activation codes (the reference's quantiser without --a_sym:
  * sym=False in qdiff/quant_layer.py:191-214, 160-190, 94-102):
  *   delta = (max - min) / (2^b - 1), zero_point = round(-min / delta),

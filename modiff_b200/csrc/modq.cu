@@ -737,13 +737,25 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
 // statistics pass (4 bytes per element) disappears.
 constexpr int kGnMaxCpg = 64;
 
-template <int NV>
+// Second quantiser of the same tensor (DUAL): a layer that reads the RAW source next to the one
+// that reads its GroupNorm (a residual block's shortcut convolution next to its first
+// convolution).  Its residual maximum is taken in the same sweep from the values already held.
+struct SecondQuantiser {
+  const float* a_hat;       // cached input of the second layer
+  int split;                // its scale segments: channels >= split use slot 1
+  int n_levels;
+  ModqScratch* scratch;
+  float* x_scale;
+};
+
+template <int NV, bool DUAL>
 __global__ void __launch_bounds__(512, NV <= 4 ? 2 : 1)
 gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __restrict__ affine,
                  const float* __restrict__ gamma, const float* __restrict__ beta,
                  const float* __restrict__ a_hat, int batch, int c, int hw, int groups, float eps,
                  int lg_hw4, int split, int n_levels, int per_sample, int slots,
-                 ModqScratch* __restrict__ scratch, float* __restrict__ x_scale) {
+                 ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
+                 const SecondQuantiser second) {
   __shared__ float sh[64];
   __shared__ float2 tab[kGnMaxCpg];
   __shared__ float bias_sh[kGnMaxCpg];
@@ -756,6 +768,7 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
   const bool has_bias = src.bias != nullptr;
 
   float m0 = 0.0f, m1 = 0.0f;
+  float r0 = 0.0f, r1 = 0.0f;     // second quantiser: raw residual maxima of its two segments
   int cur_n = -1;
   // (image, group) of the current item, advanced without divisions
   const int n_step = gridDim.x / groups, g_step = gridDim.x % groups;
@@ -797,6 +810,21 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
         xv[k] = __ldg(xs + i);
         if (a_hat) av[k] = __ldg(as + i);
       }
+    }
+    if (DUAL) {
+      const float4* bs =
+          reinterpret_cast<const float4*>(second.a_hat + ((size_t)n * c + cbeg) * hw);
+      float ri = 0.0f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < total4) {
+          const float4 b = __ldg(bs + i);
+          ri = fmaxf(fmaxf(ri, fabsf(__fsub_rn(xv[k].x, b.x))), fabsf(__fsub_rn(xv[k].y, b.y)));
+          ri = fmaxf(fmaxf(ri, fabsf(__fsub_rn(xv[k].z, b.z))), fabsf(__fsub_rn(xv[k].w, b.w)));
+        }
+      }
+      if (second.split > 0 && cbeg >= second.split) r1 = fmaxf(r1, ri); else r0 = fmaxf(r0, ri);
     }
     // normalisation parameters of this slab's channels (threads 0 .. cpg-1), fetched before the
     // reductions so that their latency is off the critical path
@@ -881,19 +909,39 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
     m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
   }
+  __shared__ float s2[16], s3[16];
+  if (DUAL) {
+    for (int o = 16; o > 0; o >>= 1) {
+      r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
+      r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
+    }
+  }
   if ((threadIdx.x & 31) == 0) {
     s0[threadIdx.x >> 5] = m0;
     s1[threadIdx.x >> 5] = m1;
+    if (DUAL) {
+      s2[threadIdx.x >> 5] = r0;
+      s3[threadIdx.x >> 5] = r1;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int i = 1; i < (int)(blockDim.x >> 5); ++i) {
       m0 = fmaxf(m0, s0[i]);
       m1 = fmaxf(m1, s1[i]);
+      if (DUAL) {
+        r0 = fmaxf(r0, s2[i]);
+        r1 = fmaxf(r1, s3[i]);
+      }
     }
     const int slot0 = per_sample ? (cur_n < 0 ? 0 : cur_n) : 0;
     if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
     if (split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    if (DUAL) {
+      if (r0 > 0.0f) atomicMax(&second.scratch->absmax_bits[0], __float_as_uint(r0));
+      if (second.split > 0 && r1 > 0.0f)
+        atomicMax(&second.scratch->absmax_bits[1], __float_as_uint(r1));
+    }
     __threadfence();
     const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
     is_last = (ticket == gridDim.x - 1);
@@ -906,6 +954,15 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
       double delta = (double)__uint_as_float(bits) / (double)n_levels;
       if (delta < 1e-8) delta = 1e-8;
       x_scale[sl] = (float)delta;
+    }
+    if (DUAL) {
+      const int slots2 = second.split > 0 ? 2 : 1;
+      for (int sl = threadIdx.x; sl < slots2; sl += blockDim.x) {
+        const unsigned int bits = atomicExch(&second.scratch->absmax_bits[sl], 0u);
+        double delta = (double)__uint_as_float(bits) / (double)second.n_levels;
+        if (delta < 1e-8) delta = 1e-8;
+        second.x_scale[sl] = (float)delta;
+      }
     }
     if (threadIdx.x == 0) scratch->counter = 0u;
   }
@@ -1056,6 +1113,171 @@ gn_absmax_warp_kernel(const SrcView src, const float* __restrict__ film, float* 
       x_scale[sl] = (float)delta;
     }
     if (threadIdx.x == 0) scratch->counter = 0u;
+  }
+}
+
+// Encode pass for TWO layers that read the same tensor: layer A through GroupNorm (+ SiLU), from
+// the scale / shift table, layer B raw (a residual block's first convolution and its shortcut
+// convolution).  One read of x serves both; each layer keeps its own cache, scale slots and
+// code planes.  Tile walk, staging and arithmetic are those of modq_encode_staged_kernel.
+struct EncodeTarget {
+  float* a_hat;
+  int8_t* codes;
+  const float* x_scale;
+  modiff_conv_geom g;
+  Derived d;
+  int n_levels;
+};
+constexpr int kPairStageFloats = 2 * kTileC * kTileP;          // x | a_hat A (B comes by registers)
+constexpr int kPairSmem = kStages * kPairStageFloats * 4;
+
+__global__ void __launch_bounds__(kThreads, 3)
+modq_encode_pair_kernel(const SrcView src, const EncodeTarget ta, const EncodeTarget tb,
+                        TileGrid tg) {
+  extern __shared__ __align__(16) float stage_sh[];
+  __shared__ uint32_t tile_a[kTileP][kTileC / 4 + 1];
+  __shared__ uint32_t tile_b[kTileP][kTileC / 4 + 1];
+  const modiff_conv_geom& g = ta.g;
+  const int hw = g.h * g.w;
+  const int cg = threadIdx.x >> 4;
+  const int pq = threadIdx.x & 15;
+  const float lo_a = (float)(-ta.n_levels - 1), hi_a = (float)ta.n_levels;
+  const float lo_b = (float)(-tb.n_levels - 1), hi_b = (float)tb.n_levels;
+  const int lrow = threadIdx.x >> 4, lcol = (threadIdx.x & 15) * 4;
+  const uint32_t sdst0 =
+      (uint32_t)__cvta_generic_to_shared(stage_sh) + (uint32_t)(lrow * kTileP + lcol) * 4u;
+  auto issue = [&](int it, int stage) {
+    const int tile = tg.total - 1 - it;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    const int p = p0 + lcol;
+    const float* xb0 = src.x0 + (size_t)n * src.c0 * hw;
+    const float* xb1 = src.x1 ? src.x1 + (size_t)n * src.c1 * hw : xb0;
+    const float* aa = ta.a_hat + (size_t)n * g.cin * hw;
+    const uint32_t sdst = sdst0 + (uint32_t)(stage * kPairStageFloats) * 4u;
+#pragma unroll
+    for (int r = 0; r < (kTileC * kTileP / 4) / kThreads; ++r) {
+      const int c = c0 + lrow + 16 * r;
+      const bool valid = (c < g.cin) && (p < hw);
+      const int bytes = valid ? 16 : 0;
+      const float* xp = xb0;
+      const float* pa = aa;
+      if (valid) {
+        xp = (c < src.c0) ? xb0 + (c * hw + p) : xb1 + ((c - src.c0) * hw + p);
+        pa = aa + (c * hw + p);
+      }
+      const uint32_t d = sdst + (uint32_t)(16 * r * kTileP) * 4u;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(xp), "r"(bytes)
+                   : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                       d + (uint32_t)(kTileC * kTileP) * 4u),
+                   "l"(pa), "r"(bytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // code -> plane address of layer t for pixel pp of image n
+  auto plane_pixel = [&](const EncodeTarget& t, int n, int pp) -> size_t {
+    int y, xq, ys, xs;
+    y = tg.by_w.divmod(pp, xq);
+    const int yq = tg.by_stride.divmod(y + t.g.pad_t, ys);
+    const int xqq = tg.by_stride.divmod(xq + t.g.pad_l, xs);
+    const int plane = ys * t.g.stride + xs;
+    return (((size_t)n * t.d.nplanes + plane) * t.d.hp + yq) * t.d.wp + xqq;
+  };
+
+  int k = 0;
+  if ((int)blockIdx.x < tg.total) issue(blockIdx.x, 0);
+  for (int it = blockIdx.x; it < tg.total; it += gridDim.x, ++k) {
+    const int stage = k % kStages;
+    const bool more = it + (int)gridDim.x < tg.total;
+    if (more) issue(it + gridDim.x, (k + 1) % kStages);
+    const int tile = tg.total - 1 - it;
+    int n, c0, p0;
+    tg.decode(tile, n, c0, p0);
+    const int p = p0 + 4 * pq;
+    const size_t img = (size_t)n * g.cin;
+    // layer B's cached rows travel through registers, in flight while the staged tile lands
+    float4 brow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + 4 * cg + i;
+      brow[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p < hw && c < g.cin)
+        brow[i] = __ldg(reinterpret_cast<const float4*>(tb.a_hat + (img + c) * hw + p));
+    }
+    if (more) {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float* sx = stage_sh + stage * kPairStageFloats;
+    const float* sa = sx + kTileC * kTileP;
+    const float da = ta.x_scale[0], ia = __frcp_rn(da);
+    const float db0 = tb.x_scale[0], db1 = tb.g.split > 0 ? tb.x_scale[1] : db0;
+    const float ib0 = __frcp_rn(db0), ib1 = __frcp_rn(db1);
+
+    uint32_t qa[4][4], qb[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        qa[i][j] = 0;
+        qb[i][j] = 0;
+      }
+    if (p < hw) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = 4 * cg + i;
+        const int c = c0 + row;
+        if (c < g.cin) {
+          const float4 xt = *reinterpret_cast<const float4*>(sx + row * kTileP + 4 * pq);
+          const float4 at = *reinterpret_cast<const float4*>(sa + row * kTileP + 4 * pq);
+          const float4 bt = brow[i];
+          const float xr[4] = {xt.x, xt.y, xt.z, xt.w};
+          const float av[4] = {at.x, at.y, at.z, at.w};
+          const float bv[4] = {bt.x, bt.y, bt.z, bt.w};
+          const float2 aff = __ldg(reinterpret_cast<const float2*>(src.affine) + img + c);
+          const bool seg1 = tb.g.split > 0 && c >= tb.g.split;
+          const float db = seg1 ? db1 : db0, ib = seg1 ? ib1 : ib0;
+          float na[4], nb[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float va = fmaf(xr[j], aff.x, aff.y);
+            if (src.silu) va = silu_f(va);
+            const float fa = quantise_clamp(__fsub_rn(va, av[j]), da, ia, lo_a, hi_a, qa[i][j]);
+            na[j] = __fadd_rn(av[j], __fmul_rn(fa, da));
+            const float fb = quantise_clamp(__fsub_rn(xr[j], bv[j]), db, ib, lo_b, hi_b, qb[i][j]);
+            nb[j] = __fadd_rn(bv[j], __fmul_rn(fb, db));
+          }
+          *reinterpret_cast<float4*>(ta.a_hat + (img + c) * hw + p) =
+              make_float4(na[0], na[1], na[2], na[3]);
+          *reinterpret_cast<float4*>(tb.a_hat + (img + c) * hw + p) =
+              make_float4(nb[0], nb[1], nb[2], nb[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      tile_a[4 * pq + j][cg] = pack_low_bytes(qa[0][j], qa[1][j], qa[2][j], qa[3][j]);
+      tile_b[4 * pq + j][cg] = pack_low_bytes(qb[0][j], qb[1][j], qb[2][j], qb[3][j]);
+    }
+    __syncthreads();
+    const int px = threadIdx.x >> 2;
+    const int piece = threadIdx.x & 3;
+    const int pp = p0 + px;
+    const int cbase = c0 + 16 * piece;
+    if (pp < hw && cbase < ta.d.cp) {
+      const size_t pix_a = plane_pixel(ta, n, pp), pix_b = plane_pixel(tb, n, pp);
+      *reinterpret_cast<int4*>(ta.codes + pix_a * ta.d.cp + cbase) =
+          make_int4(tile_a[px][4 * piece], tile_a[px][4 * piece + 1], tile_a[px][4 * piece + 2],
+                    tile_a[px][4 * piece + 3]);
+      *reinterpret_cast<int4*>(tb.codes + pix_b * tb.d.cp + cbase) =
+          make_int4(tile_b[px][4 * piece], tile_b[px][4 * piece + 1], tile_b[px][4 * piece + 2],
+                    tile_b[px][4 * piece + 3]);
+    }
+    __syncthreads();
   }
 }
 }  // namespace
@@ -1292,10 +1514,9 @@ extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, c
     const int per_sm = threads >= 512 ? 2 : (threads >= 256 ? 4 : 8);
     const int blocks = items < 148 * per_sm ? items : 148 * per_sm;
 #define MODIFF_GN_ABSMAX(NV)                                                                     \
-  gn_absmax_kernel<NV><<<blocks, threads, 0, s>>>(v, film, affine, gamma, beta, a_hat, g->batch,   \
-                                                  g->cin, hw, groups, eps, lg_hw4, g->split,      \
-                                                  n_levels, per_sample, slots,                    \
-                                                  (ModqScratch*)scratch, x_scale)
+  gn_absmax_kernel<NV, false><<<blocks, threads, 0, s>>>(                                         \
+      v, film, affine, gamma, beta, a_hat, g->batch, g->cin, hw, groups, eps, lg_hw4, g->split,    \
+      n_levels, per_sample, slots, (ModqScratch*)scratch, x_scale, SecondQuantiser{})
     if (nv <= 1) MODIFF_GN_ABSMAX(1);
     else if (nv <= 2) MODIFF_GN_ABSMAX(2);
     else if (nv <= 4) MODIFF_GN_ABSMAX(4);
@@ -1313,6 +1534,109 @@ extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, c
   v.bias = nullptr;
   v.affine = affine;
   return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
+}
+
+extern "C" int modiff_modq_pair(const modiff_act_source* src, const float* gamma, const float* beta,
+                                int groups, float eps, float* affine, float* a_hat_a,
+                                int8_t* codes_a, float* x_scale_a, const modiff_conv_geom* g_a,
+                                int n_bits_a, void* scratch_a, float* a_hat_b, int8_t* codes_b,
+                                float* x_scale_b, const modiff_conv_geom* g_b, int n_bits_b,
+                                void* scratch_b, void* stream) {
+  int rc = validate_geom(g_a);
+  if (rc) return rc;
+  rc = validate_geom(g_b);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && gamma && beta && affine && a_hat_a && codes_a && x_scale_a &&
+                       scratch_a && a_hat_b && codes_b && x_scale_b && scratch_b,
+                   "NULL pointer argument");
+  MODIFF_CHECK_ARG(g_a->batch == g_b->batch && g_a->cin == g_b->cin && g_a->h == g_b->h &&
+                       g_a->w == g_b->w,
+                   "the two layers must read the same tensor");
+  MODIFF_CHECK_ARG(g_a->split == 0 && g_a->stride == 1 && g_b->stride == 1,
+                   "layer A must have one scale; both layers stride 1");
+  MODIFF_CHECK_ARG(n_bits_a >= 2 && n_bits_a <= 8 && n_bits_b >= 2 && n_bits_b <= 8,
+                   "activation n_bits outside [2, 8]");
+  MODIFF_CHECK_ARG(src->chan_bias == nullptr && (src->affine == nullptr || src->affine == affine),
+                   "the paired quantiser takes no channel bias");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g_a->cin && (src->c0 == g_a->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g_a->cin);
+  MODIFF_CHECK_ARG(groups > 0 && g_a->cin % groups == 0, "bad GroupNorm shape");
+  MODIFF_CHECK_ARG(((((uintptr_t)codes_a | (uintptr_t)codes_b) & 15) == 0) &&
+                       (((uintptr_t)affine & 7) == 0),
+                   "buffers must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const modiff_conv_geom* g = g_a;
+  const int hw = g->h * g->w;
+  const int cpg = g->cin / groups;
+  const int count = cpg * hw;
+  const int threads = groupnorm_threads(count);
+  const int lg_hw4 = groupnorm_lg_hw4(hw);
+  const int nv = lg_hw4 >= 0 ? ceil_div(count / 4, threads) : 0;
+  const bool aligned = ((((uintptr_t)src->x0 | (uintptr_t)src->x1 | (uintptr_t)a_hat_a |
+                          (uintptr_t)a_hat_b) & 15) == 0);
+  const bool whole = (src->c0 % cpg == 0) && (g_b->split % cpg == 0);
+  if (!(lg_hw4 >= 0 && threads >= 256 && nv <= 8 && cpg <= kGnMaxCpg && aligned && whole)) {
+    // shapes outside the paired kernels: the two quantisers one after the other
+    modiff_act_source raw = *src;
+    raw.affine = nullptr;
+    rc = modiff_modq_gn(&raw, nullptr, gamma, beta, groups, eps, affine, a_hat_a, codes_a, x_scale_a,
+                        g_a, n_bits_a, 0, scratch_a, stream);
+    if (rc) return rc;
+    raw.silu = 0;
+    return modiff_modq_src(&raw, a_hat_b, codes_b, x_scale_b, g_b, n_bits_b, 0, scratch_b, stream);
+  }
+  SrcView v = {};
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  SecondQuantiser second;
+  second.a_hat = a_hat_b;
+  second.split = g_b->split;
+  second.n_levels = sym_levels(n_bits_b);
+  second.scratch = (ModqScratch*)scratch_b;
+  second.x_scale = x_scale_b;
+  const int items = g->batch * groups;
+  const int per_sm = threads >= 512 ? 2 : 4;
+  const int blocks = items < 148 * per_sm ? items : 148 * per_sm;
+#define MODIFF_GN_ABSMAX2(NV)                                                                    \
+  gn_absmax_kernel<NV, true><<<blocks, threads, 0, s>>>(                                          \
+      v, nullptr, affine, gamma, beta, a_hat_a, g->batch, g->cin, hw, groups, eps, lg_hw4, 0,      \
+      sym_levels(n_bits_a), 0, 1, (ModqScratch*)scratch_a, x_scale_a, second)
+  if (nv <= 1) MODIFF_GN_ABSMAX2(1);
+  else if (nv <= 2) MODIFF_GN_ABSMAX2(2);
+  else if (nv <= 4) MODIFF_GN_ABSMAX2(4);
+  else MODIFF_GN_ABSMAX2(8);
+#undef MODIFF_GN_ABSMAX2
+  MODIFF_LAUNCH_CHECK("gn_absmax_kernel (paired)");
+
+  v.affine = affine;
+  EncodeTarget ta, tb;
+  ta.a_hat = a_hat_a; ta.codes = codes_a; ta.x_scale = x_scale_a; ta.g = *g_a; ta.d = derive(*g_a);
+  ta.n_levels = sym_levels(n_bits_a);
+  tb.a_hat = a_hat_b; tb.codes = codes_b; tb.x_scale = x_scale_b; tb.g = *g_b; tb.d = derive(*g_b);
+  tb.n_levels = sym_levels(n_bits_b);
+  TileGrid tg;
+  tg.pb = ceil_div(hw, kTileP);
+  tg.cb = ceil_div(g->cin, kTileC);
+  tg.per_image = FastDiv(tg.pb * tg.cb);
+  tg.by_pb = FastDiv(tg.pb);
+  tg.by_w = FastDiv(g->w);
+  tg.by_stride = FastDiv(1);
+  const int64_t total = (int64_t)tg.pb * tg.cb * g->batch;
+  if (total >= (1ll << 31)) return set_error(MODIFF_ERR_INVALID, "activation tensor too large");
+  tg.total = (int)total;
+  static bool attr_set = false;
+  if (!attr_set) {
+    MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_pair_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
+    attr_set = true;
+  }
+  const int eblocks = tg.total < 148 * 3 ? tg.total : 148 * 3;
+  modq_encode_pair_kernel<<<eblocks, kThreads, kPairSmem, s>>>(v, ta, tb, tg);
+  MODIFF_LAUNCH_CHECK("modq_encode_pair_kernel");
+  return MODIFF_OK;
 }
 
 extern "C" int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes,

@@ -557,6 +557,51 @@ class QuantModule(nn.Module):
             self._igemm(buf, pack, out, False, bias, g)
         return self.activation_function(out)
 
+    # ------------------------------------------------------------------ two layers, one tensor
+    pair_quantisers = os.environ.get("MODIFF_PAIR_QUANTISERS", "1") != "0"
+
+    def forward_pair(self, src, other, other_split=0):
+        """This layer on nonlinearity(norm(x)) (`src`, an `ops.ActSource` with a pending norm)
+        and `other` on the raw x of the same source, e.g. a residual block's conv1 and its
+        shortcut convolution (qdiff/quant_block.py:279-283, 306-311): x is read once per
+        quantiser pass for both.  Returns (out_self, out_other), or None when the pair is not in
+        the steady modulated state the fused kernels cover (the caller then runs the two layers
+        the ordinary way)."""
+        def steady(m):
+            return (isinstance(m, QuantModule) and m.modulate and m.use_act_quant and
+                    m.use_weight_quant and not m.disable_act_quant and m.a_hat is not None and
+                    m.o_hat is not None and m.act_quantizer.sym and m.act_quantizer.dynamic and
+                    not m.act_quantizer.channel_wise and m.fwd_func is F.conv2d)
+        if not (self.pair_quantisers and self.fuse_norm_stats and steady(self) and steady(other)
+                and self.split == 0 and src.pending_norm() and src.chan_bias is None
+                and src.film is None and (other_split == other.split or other.split == 0)):
+            return None
+        if other_split and other.split == 0:
+            return None          # the ordinary path registers the split on its first use
+        ga = self._geom(src, 0)
+        gb = other._geom(src, other.split)
+        if (ga.stride != 1 or gb.stride != 1 or tuple(self.a_hat.shape) != tuple(src.shape)
+                or tuple(other.a_hat.shape) != tuple(src.shape)):
+            return None
+        packa, packb = self._pack_weights(ga), other._pack_weights(gb)
+        bufa, bufb = self._get_buffers(ga, src.device), other._get_buffers(gb, src.device)
+        n = src.norm
+        raw, table = src.raw_struct()
+        _lib.call('modiff_modq_pair', C.byref(raw), n.weight.data_ptr(), n.bias.data_ptr(),
+                  n.num_groups, float(n.eps), table.data_ptr(),
+                  self.a_hat.data_ptr(), bufa.codes.data_ptr(), bufa.x_scale.data_ptr(),
+                  C.byref(ga), self.act_quantizer.n_bits, bufa.scratch.data_ptr(),
+                  other.a_hat.data_ptr(), bufb.codes.data_ptr(), bufb.x_scale.data_ptr(),
+                  C.byref(gb), other.act_quantizer.n_bits, bufb.scratch.data_ptr(),
+                  _lib.stream_ptr(), nbytes=26 * src.numel(), tag=ga.key())
+        self._igemm(bufa, packa, self.o_hat, True, None, ga)
+        other._igemm(bufb, packb, other.o_hat, True, None, gb)
+        outs = []
+        for m in (self, other):
+            o = m.o_hat if m.alias_output else m.o_hat.clone()
+            outs.append(m.activation_function(o))
+        return outs[0], outs[1]
+
     # ------------------------------------------------------------------ grouped small linears
     group_small_linears = os.environ.get("MODIFF_LINEAR_GROUP", "1") != "0"
     _GROUP_MAX_ROWS = 512

@@ -152,7 +152,15 @@ def resnet_forward(blk, x, temb, split=0):
         quant = False   # dropout needs the materialised tensor
 
     src1 = ops.ActSource(xa, xb, norm=blk.norm1, silu=True)
-    h = blk.conv1(src1 if quant else src1.materialize())
+    xs_pair = None
+    if (quant and blk.in_channels != blk.out_channels and not blk.use_conv_shortcut
+            and _is_quant(blk.nin_shortcut)):
+        # conv1 reads norm1(x), the shortcut reads x: both quantisers share their sweeps over x
+        pair = blk.conv1.forward_pair(src1, blk.nin_shortcut, split)
+        if pair is not None:
+            h, xs_pair = pair
+    if xs_pair is None:
+        h = blk.conv1(src1 if quant else src1.materialize())
     # every block projects the same swish(temb): computed once per step by the model, and the
     # projections share one quantisation of it (the first one to run owns the codes)
     ta = getattr(temb, "_modiff_act", None)
@@ -174,7 +182,9 @@ def resnet_forward(blk, x, temb, split=0):
             h2 = blk.dropout(h2)
         h = blk.conv2(h2)
 
-    if blk.in_channels != blk.out_channels:
+    if xs_pair is not None:
+        xs = xs_pair
+    elif blk.in_channels != blk.out_channels:
         xin = ops.ActSource(xa, xb)
         short = blk.conv_shortcut if blk.use_conv_shortcut else blk.nin_shortcut
         if not _is_quant(short):

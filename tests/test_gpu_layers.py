@@ -296,3 +296,62 @@ def test_asymmetric_codes_refuse_eight_bits(cuda):
     q(x)
     with pytest.raises(m.ModiffError):
         q(x + 0.1)
+
+
+@pytest.mark.parametrize("c0,c1,hw,split,cout,a_bits", [
+    (128, 64, 16, 128, 128, 4),     # up-path block: concat input, split shortcut scales
+    (128, 0, 32, 0, 256, 8),        # down-path block: single tensor, one shortcut scale
+    (256, 256, 8, 256, 256, 4),     # slabs under 1024 elements: the two quantisers run in turn
+])
+def test_two_quantisers_of_one_tensor(cuda, c0, c1, hw, split, cout, a_bits):
+    """A residual block's conv1 (on GroupNorm + SiLU of x) and its shortcut convolution (on x)
+    quantised in shared sweeps over x (qdiff/quant_block.py:279-283, 306-311): outputs, caches
+    and scales equal the two separate layers bit for bit."""
+    import modiff_b200 as m
+    from modiff_b200.ops import ActSource
+    torch.manual_seed(41)
+    cin = c0 + c1
+    conv1 = torch.nn.Conv2d(cin, cout, 3, padding=1)
+    short = torch.nn.Conv2d(cin, cout, 1)
+    norm = torch.nn.GroupNorm(32, cin, eps=1e-6).to(cuda)
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+        norm.bias.uniform_(-0.5, 0.5)
+    wq = {'n_bits': 4, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    sets = []
+    for _ in range(2):
+        a = m.QuantModule(copy.deepcopy(conv1), wq, aq, modulate=True).to(cuda)
+        b = m.QuantModule(copy.deepcopy(short), wq, aq, modulate=True).to(cuda)
+        for q in (a, b):
+            q.set_quant_state(True, True)
+            q.alias_output = False
+        sets.append((a, b))
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(3, cin, hw, hw, generator=g) * 1.5 + 0.3
+    used_pair = []
+    for step in range(4):
+        xs = (x + 0.08 * step * torch.randn(3, cin, hw, hw, generator=g)).to(cuda)
+        xa, xb = xs[:, :c0].contiguous(), (xs[:, c0:].contiguous() if c1 else None)
+        outs = []
+        for k, (a, b) in enumerate(sets):
+            src = ActSource(xa, xb, norm=norm, silu=True)
+            kw = dict(split=split) if split else {}
+            with torch.no_grad():
+                pair = a.forward_pair(src, b, split) if k == 0 else None
+                if k == 0:
+                    used_pair.append(pair is not None)
+                if pair is None:
+                    ya = a(src)
+                    yb = b(ActSource(xa, xb), **kw)
+                else:
+                    ya, yb = pair
+            outs.append((ya.clone(), yb.clone()))
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+        for qa, qb in zip(sets[0], sets[1]):
+            assert torch.equal(qa.a_hat, qb.a_hat)
+            if step > 0:
+                assert float(qa.act_quantizer.delta) == float(qb.act_quantizer.delta)
+    assert used_pair == [False, True, True, True]     # step 0 is the unquantised first step
+    assert m.device_status() == 0
