@@ -383,12 +383,8 @@ extern "C" int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_p
     MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const size_t smem = (size_t)kPBytes + (size_t)kStages * kStage;
-  static bool attr_set = false;
-  if (!attr_set) {
-    MODIFF_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-    attr_set = true;
-  }
+  static SmemLimit smem_limit;
+  MODIFF_CUDA(raise_smem_limit(attention_tc_kernel, smem, smem_limit));
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
   attention_tc_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
   MODIFF_LAUNCH_CHECK("attention_tc_kernel");

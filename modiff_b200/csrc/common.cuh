@@ -141,6 +141,26 @@ __device__ inline void block_sum2(float& a, float& b, float* sh) {
 }
 #endif
 
+#ifdef __CUDACC__
+// Raises a kernel's dynamic shared-memory limit to `bytes` on the CURRENT device, once per
+// device and size (function attributes belong to a device; one SmemLimit per kernel).
+struct SmemLimit {
+  size_t done[64] = {};
+};
+template <typename K>
+inline cudaError_t raise_smem_limit(K kernel, size_t bytes, SmemLimit& st) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (bytes > st.done[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) st.done[dev] = bytes;
+  }
+  return e;
+}
+#endif
+
 // Launch shape of the GroupNorm kernels for one (image, group) slab of `count` elements.  The
 // statistics are summed per thread and then over the block, so two kernels agree on the last
 // bit of mean and variance only when they use the same thread count.

@@ -700,18 +700,14 @@ extern "C" int modiff_gemm_bf16(const modiff_gemm_bf16_desc* desc, const modiff_
   }
 
   static int sm_count = 0;
-  static bool attr_set = false;
   if (!sm_count) {
     int dev = 0;
     MODIFF_CUDA(cudaGetDevice(&dev));
     MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const size_t smem = (size_t)kStages * kStageBytes;
-  if (!attr_set) {
-    MODIFF_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-    attr_set = true;
-  }
+  static SmemLimit smem_limit;
+  MODIFF_CUDA(raise_smem_limit(gemm_bf16_kernel, smem, smem_limit));
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
   gemm_bf16_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(map_a, map_b, p);
   MODIFF_LAUNCH_CHECK("gemm_bf16_kernel");

@@ -456,12 +456,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output) failed: %d", (int)r);
   }
 
-  static size_t attr_bytes = 0;
-  if (smem > attr_bytes) {
-    MODIFF_CUDA(cudaFuncSetAttribute(igemm_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
-    attr_bytes = smem;
-  }
+  static SmemLimit smem_limit;
+  MODIFF_CUDA(raise_smem_limit(igemm_halo_kernel, smem, smem_limit));
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
   igemm_halo_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);
   MODIFF_LAUNCH_CHECK("igemm_halo_kernel");

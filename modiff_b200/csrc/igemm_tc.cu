@@ -548,12 +548,8 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   const int variant = (p.nseg == 2 ? 4 : 0) | (p.with_sum ? 2 : 0) | (use_tma_epi ? 1 : 0);
 #define MODIFF_TC_LAUNCH(NSEG, SUM, EPI)                                                       \
   {                                                                                            \
-    static size_t attr_bytes = 0;                                                              \
-    if (smem > attr_bytes) {                                                                   \
-      MODIFF_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<NSEG, SUM, EPI>,                        \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      attr_bytes = smem;                                                                       \
-    }                                                                                          \
+    static SmemLimit smem_limit;                                                               \
+    MODIFF_CUDA(raise_smem_limit(igemm_tc_kernel<NSEG, SUM, EPI>, smem, smem_limit));          \
     igemm_tc_kernel<NSEG, SUM, EPI><<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);      \
   }
   switch (variant) {

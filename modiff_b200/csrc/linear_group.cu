@@ -90,12 +90,8 @@ extern "C" int modiff_linear_group(const int8_t* codes, const float* x_scale, in
   const int kp = round_up(cin, 128);
   const size_t smem = (size_t)kGroupChannels * kp;
   if (smem > 48 * 1024) {
-    static size_t attr_bytes = 0;
-    if (smem > attr_bytes) {
-      MODIFF_CUDA(cudaFuncSetAttribute(linear_group_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_bytes = smem;
-    }
+    static SmemLimit smem_limit;
+    MODIFF_CUDA(raise_smem_limit(linear_group_kernel, smem, smem_limit));
   }
   dim3 grid(n_blocks, ceil_div(rows, kGroupThreads));
   linear_group_kernel<<<grid, kGroupThreads, smem, (cudaStream_t)stream>>>(codes, x_scale, rows, cin,

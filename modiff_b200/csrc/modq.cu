@@ -1365,21 +1365,13 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
     } else {
       MODIFF_MODQ_SCALE(true, false)
     }
-    static bool attr_set[2] = {false, false};
+    static SmemLimit smem_limit[2];
     if (xform) {
-      if (!attr_set[1]) {
-        MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_staged_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStagedSmem));
-        attr_set[1] = true;
-      }
+      MODIFF_CUDA(raise_smem_limit(modq_encode_staged_kernel<true>, kStagedSmem, smem_limit[1]));
       modq_encode_staged_kernel<true><<<sblocks, kThreads, kStagedSmem, s>>>(
           src, a_hat, codes, x_scale, x_zp, *g, d, tg, n_levels, per_sample);
     } else {
-      if (!attr_set[0]) {
-        MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_staged_kernel<false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStagedSmem));
-        attr_set[0] = true;
-      }
+      MODIFF_CUDA(raise_smem_limit(modq_encode_staged_kernel<false>, kStagedSmem, smem_limit[0]));
       modq_encode_staged_kernel<false><<<sblocks, kThreads, kStagedSmem, s>>>(
           src, a_hat, codes, x_scale, x_zp, *g, d, tg, n_levels, per_sample);
     }
@@ -1627,12 +1619,8 @@ extern "C" int modiff_modq_pair(const modiff_act_source* src, const float* gamma
   const int64_t total = (int64_t)tg.pb * tg.cb * g->batch;
   if (total >= (1ll << 31)) return set_error(MODIFF_ERR_INVALID, "activation tensor too large");
   tg.total = (int)total;
-  static bool attr_set = false;
-  if (!attr_set) {
-    MODIFF_CUDA(cudaFuncSetAttribute(modq_encode_pair_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
-    attr_set = true;
-  }
+  static SmemLimit smem_limit;
+  MODIFF_CUDA(raise_smem_limit(modq_encode_pair_kernel, kPairSmem, smem_limit));
   const int eblocks = tg.total < 148 * 3 ? tg.total : 148 * 3;
   modq_encode_pair_kernel<<<eblocks, kThreads, kPairSmem, s>>>(v, ta, tb, tg);
   MODIFF_LAUNCH_CHECK("modq_encode_pair_kernel");
