@@ -248,6 +248,15 @@ int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                       const modiff_conv_geom* g, int per_sample, int impl,
                       int32_t* acc_out, void* stream);
 
+/* modiff_igemm_conv (per-tensor scales, no bias) that also writes sum_out = residual + new output,
+ * the `x + h` that ends a residual block (qdiff/quant_block.py:313; ddim/models/diffusion.py:128):
+ * on the activation-reuse 3x3 kernel the sum is formed in the epilogue from the values it holds,
+ * elsewhere modiff_add runs after the GEMM.  residual and sum_out are fp32 [batch][cout][ho*wo]. */
+int modiff_igemm_conv_add(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                          const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                          float* o_hat, int accumulate, const modiff_conv_geom* g, int impl,
+                          const float* residual, float* sum_out, void* stream);
+
 /* Receptive-field gather of activation codes for layers with very few input channels (the
  * 3-channel input conv, ddim/models/diffusion.py:321): out[m][c*kh*kw + tap], one row of
  * out_stride bytes per output pixel m (bytes past cin*kh*kw are left untouched: zero-fill the

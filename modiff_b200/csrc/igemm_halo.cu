@@ -54,6 +54,8 @@ struct HaloParams {
   const float* x_scale;
   const float* w_scale;
   const int32_t* w_corr;
+  const float* residual;   // optional [batch][cout][h*w]: sum_out = new output + residual
+  float* sum_out;
 };
 
 struct HaloTile {
@@ -286,10 +288,21 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           tc_wait_ld();
         }
         for (int hh = 0; hh < 2; ++hh) {
+          const int colbase = hh * 64 + sub * 32;
+          // residual of the block (x + h, qdiff/quant_block.py:313): a lane is a pixel, so the 32
+          // lanes of a warp read 128 consecutive bytes per channel; issued before the wait below
+          // so that the loads are in flight while the cached-output tile arrives
+          float res[32];
+          size_t res_off = 0;
+          if (p.residual) {
+            res_off = ((size_t)t.n * p.cout + t.nt * 128 + colbase) * (size_t)(p.h * p.w) +
+                      (size_t)(t.th * p.rows + m * p.half_rows) * p.w + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = __ldg(p.residual + res_off + (size_t)j * (p.h * p.w));
+          }
           ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
           float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)(sub * 32) * 128 + row;
-          const int colbase = hh * 64 + sub * 32;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * 128] : 0.0f;
@@ -304,6 +317,11 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
 #pragma unroll
           for (int j = 0; j < 32; ++j) orow[j * 128] = v[j];
+          if (p.residual) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              p.sum_out[res_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+          }
           const bool last = (m == p.mh - 1) && (hh == 1);
           if (last) tc_fence_before();
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -363,7 +381,8 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
 
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
-                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s) {
+                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
+                      const float* residual, float* sum_out) {
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   static int sm_count = 0;
@@ -416,6 +435,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.x_scale = x_scale;
   p.w_scale = w_scale;
   p.w_corr = w_corr;
+  p.residual = residual;
+  p.sum_out = sum_out;
   const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes;
 
   CUtensorMap map_a, map_b, map_o;

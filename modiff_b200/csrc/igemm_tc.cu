@@ -575,7 +575,8 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
                     const int32_t* acc_out, const float* o_hat);
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
-                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s);
+                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
+                      const float* residual, float* sum_out);
 
 // MODIFF_IGEMM_HALO=0 keeps 3x3 layers on the one-copy-per-tap kernel (debug aid, same results)
 static bool halo_enabled() {
@@ -605,11 +606,11 @@ int read_device_status(int* status, int reset) {
 
 using namespace modiff;
 
-extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
-                                 const float* x_scale, const float* w_scale,
-                                 const int32_t* w_corr, float* o_hat, int accumulate,
-                                 const float* bias, const modiff_conv_geom* g, int per_sample,
-                                 int impl, int32_t* acc_out, void* stream) {
+static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                           const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                           float* o_hat, int accumulate, const float* bias,
+                           const modiff_conv_geom* g, int per_sample, int impl, int32_t* acc_out,
+                           const float* residual, float* sum_out, void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(codes && wcodes && x_scale && w_scale && o_hat, "NULL pointer argument");
@@ -621,15 +622,43 @@ extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int 
   const bool tc_ok = tc_supported(g, per_sample, &why);
   if (impl == MODIFF_IMPL_TCGEN05 && !tc_ok)
     return set_error(MODIFF_ERR_UNSUPPORTED, "tcgen05 path does not cover this layer: %s", why);
-  if (impl == MODIFF_IMPL_SIMT || !tc_ok)
-    return launch_igemm_simt(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat,
-                             accumulate, bias, g, per_sample, acc_out, s);
+  if (impl == MODIFF_IMPL_SIMT || !tc_ok) {
+    const int rc1 = launch_igemm_simt(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat,
+                                      accumulate, bias, g, per_sample, acc_out, s);
+    if (rc1 || !residual) return rc1;
+    const Derived ds = derive(*g);
+    return modiff_add(residual, o_hat, sum_out, g->batch, g->cout, ds.ho * ds.wo, 0, stream);
+  }
   MODIFF_CHECK_ARG(impl == MODIFF_IMPL_AUTO || impl == MODIFF_IMPL_TCGEN05, "unknown impl %d", impl);
   if (halo_enabled() && halo_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
     return launch_igemm_halo(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                             g, s);
-  return launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                         bias, g, per_sample, acc_out, s);
+                             g, s, residual, sum_out);
+  int rc2 = launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                            bias, g, per_sample, acc_out, s);
+  if (rc2 || !residual) return rc2;
+  const Derived dd = derive(*g);
+  return modiff_add(residual, o_hat, sum_out, g->batch, g->cout, dd.ho * dd.wo, 0, stream);
+}
+
+extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                                 const float* x_scale, const float* w_scale,
+                                 const int32_t* w_corr, float* o_hat, int accumulate,
+                                 const float* bias, const modiff_conv_geom* g, int per_sample,
+                                 int impl, int32_t* acc_out, void* stream) {
+  return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                         bias, g, per_sample, impl, acc_out, nullptr, nullptr, stream);
+}
+
+extern "C" int modiff_igemm_conv_add(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                                     const float* x_scale, const float* w_scale,
+                                     const int32_t* w_corr, float* o_hat, int accumulate,
+                                     const modiff_conv_geom* g, int impl, const float* residual,
+                                     float* sum_out, void* stream) {
+  MODIFF_CHECK_ARG(residual && sum_out, "NULL pointer argument");
+  MODIFF_CHECK_ARG((((uintptr_t)residual | (uintptr_t)sum_out) & 15) == 0,
+                   "residual and sum must be 16-byte aligned");
+  return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                         nullptr, g, 0, impl, nullptr, residual, sum_out, stream);
 }
 
 extern "C" int modiff_device_status(int* status, int reset) {

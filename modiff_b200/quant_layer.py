@@ -456,6 +456,46 @@ class QuantModule(nn.Module):
                   + g.cout * g.cin * g.kh * g.kw, tag=g.key())
 
     # ------------------------------------------------------------------ forward
+    fuse_residual_add = os.environ.get("MODIFF_FUSE_RESIDUAL_ADD", "1") != "0"
+
+    def forward_add(self, input, residual):
+        """`residual + self(input)`: the sum that ends a residual block
+        (qdiff/quant_block.py:313).  In the steady modulated state the GEMM's epilogue writes
+        the sum next to the cached output; otherwise the layer runs the ordinary way and the
+        sum is a separate kernel."""
+        from .ops import ActSource, add
+        steady = (self.fuse_residual_add and self.modulate and self.use_act_quant
+                  and self.use_weight_quant and not self.disable_act_quant
+                  and self.a_hat is not None and self.o_hat is not None and self.split == 0
+                  and self.fwd_func is F.conv2d and not self.act_quantizer.channel_wise
+                  and self.activation_function.__class__.__name__ == "StraightThrough"
+                  and torch.is_tensor(residual) and residual.is_cuda
+                  and residual.dtype == torch.float32)
+        if steady:
+            g = self._geom(input, 0)
+            steady = (tuple(residual.shape) == tuple(self.o_hat.shape)
+                      and tuple(self.a_hat.shape) == tuple(input.shape)
+                      and not self._use_im2col(g, self._get_buffers(g, residual.device)))
+        if not steady:
+            return add(residual, self.forward(input))
+        src = input if isinstance(input, ActSource) and not input.trivial else None
+        x = None
+        if src is None:
+            x = (input.x0 if isinstance(input, ActSource) else input).contiguous()
+        pack = self._pack_weights(g)
+        buf = self._get_buffers(g, residual.device)
+        self._modq(x, self.a_hat, buf, g, src)
+        residual = residual.contiguous()
+        out = torch.empty_like(residual)
+        _lib.call('modiff_igemm_conv_add',
+                  buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
+                  buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
+                  self.o_hat.data_ptr(), 1, C.byref(g), self.igemm_impl, residual.data_ptr(),
+                  out.data_ptr(), _lib.stream_ptr(),
+                  nbytes=16 * self.o_hat.numel() + g.batch * g.cin * g.h * g.w
+                  + g.cout * g.cin * g.kh * g.kw, tag=g.key())
+        return out
+
     def forward_shared(self, owner, input):
         """Forward of a layer whose input equals `owner`'s input at every step (the k and v
         projections next to q in an attention block): the residual codes, their scale and the

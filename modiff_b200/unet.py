@@ -173,15 +173,6 @@ def resnet_forward(blk, x, temb, split=0):
         tb = blk.temb_proj(ta)
         if _is_quant(blk.temb_proj) and hasattr(temb, "_modiff_act"):
             temb._modiff_owner = blk.temb_proj
-    src2 = ops.ActSource(h, chan_bias=tb, norm=blk.norm2, silu=True)
-    if quant:
-        h = blk.conv2(src2)
-    else:
-        h2 = src2.materialize()
-        if blk.dropout.training and blk.dropout.p > 0:
-            h2 = blk.dropout(h2)
-        h = blk.conv2(h2)
-
     if xs_pair is not None:
         xs = xs_pair
     elif blk.in_channels != blk.out_channels:
@@ -195,6 +186,18 @@ def resnet_forward(blk, x, temb, split=0):
             xs = short(xin, split)
     else:
         xs = xa if xb is None else ops.concat_channels(xa, xb)
+
+    src2 = ops.ActSource(h, chan_bias=tb, norm=blk.norm2, silu=True)
+    if quant and _is_quant(blk.conv2):
+        # x + conv2(...): the sum is written by conv2's GEMM epilogue where that kernel allows it
+        return blk.conv2.forward_add(src2, xs)
+    if quant:
+        h = blk.conv2(src2)
+    else:
+        h2 = src2.materialize()
+        if blk.dropout.training and blk.dropout.p > 0:
+            h2 = blk.dropout(h2)
+        h = blk.conv2(h2)
     return ops.add(xs, h)
 
 

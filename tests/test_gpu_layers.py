@@ -355,3 +355,34 @@ def test_two_quantisers_of_one_tensor(cuda, c0, c1, hw, split, cout, a_bits):
                 assert float(qa.act_quantizer.delta) == float(qb.act_quantizer.delta)
     assert used_pair == [False, True, True, True]     # step 0 is the unquantised first step
     assert m.device_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout,hw,w_bits", [(128, 128, 32, 4), (256, 256, 16, 8), (128, 256, 8, 4),
+                                              (64, 48, 8, 4)])
+def test_residual_sum_in_the_gemm_epilogue(cuda, cin, cout, hw, w_bits):
+    """`x + conv2(h)` (qdiff/quant_block.py:313) with the sum written by the GEMM epilogue
+    (activation-reuse kernel) or by a following add (other shapes): same bits as
+    add(x, conv2(h)) from the ordinary forward."""
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(51)
+    conv = torch.nn.Conv2d(cin, cout, 3, padding=1)
+    wq = {'n_bits': w_bits, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    mods = []
+    for _ in range(2):
+        q = m.QuantModule(copy.deepcopy(conv), wq, aq, modulate=True).to(cuda)
+        q.set_quant_state(True, True)
+        mods.append(q)
+    g = torch.Generator().manual_seed(52)
+    x = torch.randn(5, cin, hw, hw, generator=g)
+    for step in range(3):
+        xs = (x + 0.05 * step * torch.randn(5, cin, hw, hw, generator=g)).to(cuda)
+        res = torch.randn(5, cout, hw, hw, generator=g).to(cuda)
+        with torch.no_grad():
+            fused = mods[0].forward_add(xs, res)
+            plain = ops.add(res, mods[1](xs))
+        assert torch.equal(fused, plain)
+        assert torch.equal(mods[0].o_hat, mods[1].o_hat)
+    assert m.device_status() == 0
