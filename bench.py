@@ -30,7 +30,7 @@ WORKLOAD = "pixel UNet 3x32x32 W4A4 modulated, split shortcut, 100 DDIM quad ste
 
 # measured DRAM bytes / algorithmic bytes of one launch (ncu captures summarised in profiles/):
 # the quantiser reads x and a_hat twice (two passes), 21 B moved per 13 B algorithmic
-DRAM_TRAFFIC_RATIO = {"modiff_modq_src": 1.52, "modiff_modq_gn": 1.52, "modiff_modq": 1.52, "modiff_igemm_conv": 0.83}
+DRAM_TRAFFIC_RATIO = {"modiff_modq_src": 1.52, "modiff_modq_gn": 1.52, "modiff_modq_pair": 1.28, "modiff_modq": 1.52, "modiff_igemm_conv": 0.83}
 
 WQ = {'n_bits': W_BITS, 'channel_wise': True, 'scale_method': 'max'}
 AQ = {'n_bits': A_BITS, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',

@@ -34,6 +34,9 @@ def main():
     ap.add_argument("--linear", action="store_true")
     ap.add_argument("--fused", action="store_true",
                     help="feed the layer GroupNorm(32)+SiLU of the input as a lazy source")
+    ap.add_argument("--pair", action="store_true",
+                    help="a residual block's conv1 (3x3 on GroupNorm+SiLU of x) and 1x1 shortcut on "
+                         "the same x, quantised in shared sweeps (modiff_modq_pair)")
     ap.add_argument("--attention", action="store_true",
                     help="time ops.attention on [batch, cin, hw*hw] tensors instead of a layer")
     args = ap.parse_args()
@@ -55,6 +58,43 @@ def main():
         print(json.dumps({"geometry": vars(args), "device_status": _lib.device_status(),
                           "us_per_call": {n: 1000.0 * v_["ms"] / v_["launches"]
                                           for n, v_ in summ.items()}}))
+        return
+    if args.pair:
+        from .ops import ActSource
+        wq = {'n_bits': args.w_bits, 'channel_wise': True, 'scale_method': 'max'}
+        aq = {'n_bits': args.a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+              'leaf_param': True, 'dynamic': True}
+        conv1 = QuantModule(nn.Conv2d(args.cin, args.cout, 3, padding=1), wq, aq, modulate=True).to(dev)
+        short = QuantModule(nn.Conv2d(args.cin, args.cout, 1), wq, aq, modulate=True).to(dev)
+        for q in (conv1, short):
+            q.set_quant_state(True, True)
+        norm = nn.GroupNorm(32, args.cin, eps=1e-6).to(dev)
+        shape = (args.batch, args.cin, args.hw, args.hw)
+        x = torch.randn(shape, device=dev)
+        drift = [0.05 * torch.randn(shape, device=dev) for _ in range(2)]
+        kw = dict(split=args.split) if args.split else {}
+
+        def step(t):
+            src = ActSource(t, norm=norm, silu=True)
+            pair = conv1.forward_pair(src, short, args.split)
+            if pair is None:
+                conv1(src)
+                short(t, **kw)
+
+        with torch.no_grad():
+            step(x)
+            for i in range(args.warmup):
+                step(x + drift[i % 2])
+            _lib.TIMER = _lib.KernelTimer()
+            for i in range(args.iters):
+                step(x + drift[i % 2])
+            summ = _lib.TIMER.summary()
+            _lib.TIMER = None
+        print(json.dumps({"geometry": vars(args), "device_status": _lib.device_status(),
+                          "us_per_call": {n: 1000.0 * v_["ms"] / v_["launches"]
+                                          for n, v_ in summ.items()},
+                          "algorithmic_bytes_per_call": {n: v_["bytes"] // v_["launches"]
+                                                         for n, v_ in summ.items()}}))
         return
     if args.linear:
         org = nn.Linear(args.cin, args.cout)
