@@ -163,13 +163,22 @@ def resblock_forward(blk, x, emb, split=0):
     in_norm, in_conv = blk.in_layers[0], blk.in_layers[-1]
     quant = _is_quant(in_conv)
     src = ops.ActSource(xa, xb, norm=in_norm, silu=True)
+    xs_pair = None
     if blk.updown:
         h = blk.h_upd(src.materialize())
         xs_in = blk.x_upd(xa if xb is None else ops.concat_channels(xa, xb))
         xa, xb = xs_in, None
         h = in_conv(h)
     else:
-        h = in_conv(src if quant else src.materialize())
+        skip0 = blk.skip_connection
+        if (quant and _is_quant(skip0) and skip0.fwd_func is nn.functional.conv2d
+                and skip0.weight.shape[-1] == 1):
+            # in_conv reads norm(x), the 1x1 skip connection reads x: shared quantiser sweeps
+            pair = in_conv.forward_pair(src, skip0, split)
+            if pair is not None:
+                h, xs_pair = pair
+        if xs_pair is None:
+            h = in_conv(src if quant else src.materialize())
     ta = getattr(emb, "_modiff_act", None)
     if ta is None:
         ta = ops.silu(emb)
@@ -186,22 +195,27 @@ def resblock_forward(blk, x, emb, split=0):
         src2 = ops.ActSource(h, norm=out_norm, silu=True, film=emb_out)
     else:
         src2 = ops.ActSource(h, chan_bias=emb_out, norm=out_norm, silu=True)
-    drop = blk.out_layers[2]
-    if quant and not (drop.training and drop.p > 0):
-        h = out_conv(src2)
-    else:
-        h2 = src2.materialize()
-        if drop.training and drop.p > 0:
-            h2 = drop(h2)
-        h = out_conv(h2)
     skip = blk.skip_connection
-    if isinstance(skip, nn.Identity):
+    if xs_pair is not None:
+        xs = xs_pair
+    elif isinstance(skip, nn.Identity):
         xs = xa if xb is None else ops.concat_channels(xa, xb)
     else:
         xin = ops.ActSource(xa, xb)
         if not _is_quant(skip):
             xin = xin.x0 if xin.trivial else xin.materialize()
         xs = skip(xin, split=split) if split != 0 else skip(xin)
+    drop = blk.out_layers[2]
+    if quant and not (drop.training and drop.p > 0):
+        if _is_quant(out_conv):
+            # x + out_conv(...): the sum is written by the GEMM epilogue where that kernel allows it
+            return out_conv.forward_add(src2, xs)
+        h = out_conv(src2)
+    else:
+        h2 = src2.materialize()
+        if drop.training and drop.p > 0:
+            h2 = drop(h2)
+        h = out_conv(h2)
     return ops.add(xs, h)
 
 
