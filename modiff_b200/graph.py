@@ -22,7 +22,7 @@ class GraphedModel:
         self.qnn = qnn
         self._epoch = None
         self._calls = 0
-        self._graphs = {}       # (shape, device) -> dict(graph, x, t, out, kernels)
+        self._graphs = {}       # (shape, context shape, device) -> dict(graph, x, t, c, out, kernels)
 
     def __call__(self, x, t=None, context=None):
         qnn = self.qnn
@@ -31,31 +31,34 @@ class GraphedModel:
             self._epoch = epoch
             self._calls = 0
         self._calls += 1
-        if self._calls <= EAGER_STEPS or _lib.TIMER is not None or context is not None:
+        if self._calls <= EAGER_STEPS or _lib.TIMER is not None:
             return qnn(x, t, context)
         _lib.require_cuda(x, "model input")
-        key = (tuple(x.shape), str(x.device))
+        key = (tuple(x.shape), None if context is None else tuple(context.shape), str(x.device))
         entry = self._graphs.get(key)
         if entry is None:
-            entry = self._capture(x, t)
+            entry = self._capture(x, t, context)
             self._graphs[key] = entry
         entry["x"].copy_(x)
         entry["t"].copy_(t)
+        if context is not None:
+            entry["c"].copy_(context)
         entry["graph"].replay()
         _lib.LAUNCHES[0] += entry["kernels"]
         return entry["out"]
 
-    def _capture(self, x, t):
+    def _capture(self, x, t, context=None):
         sx = x.clone()
         st = t.clone().float()
+        sc = None if context is None else context.clone()
         graph = torch.cuda.CUDAGraph()
         before = _lib.LAUNCHES[0]
         torch.cuda.synchronize()
         try:
             with torch.cuda.graph(graph):
-                out = self.qnn(sx, st)
+                out = self.qnn(sx, st, sc) if sc is not None else self.qnn(sx, st)
         except Exception as e:   # a capture that failed leaves no usable graph: report loudly
             raise ModiffError(f"CUDA graph capture of the UNet step failed: {e}") from e
         kernels = _lib.LAUNCHES[0] - before
         _lib.LAUNCHES[0] = before       # nothing ran during capture
-        return dict(graph=graph, x=sx, t=st, out=out, kernels=kernels)
+        return dict(graph=graph, x=sx, t=st, c=sc, out=out, kernels=kernels)

@@ -92,7 +92,7 @@ class DDIMSampler:
             raise ValueError("x_T is required (noise is drawn by the caller so shards can be "
                              "re-created)")
         guided = unconditional_conditioning is not None and unconditional_guidance_scale != 1.
-        if cuda_graph and hasattr(model, "graphed") and img.is_cuda and conditioning is None:
+        if cuda_graph and hasattr(model, "graphed") and img.is_cuda:
             model = model.graphed()
         b = img.shape[0]
         timesteps = self.ddim_timesteps
@@ -146,7 +146,7 @@ class PLMSSampler(DDIMSampler):
             raise ValueError("x_T is required (noise is drawn by the caller so shards can be "
                              "re-created)")
         guided = unconditional_conditioning is not None and unconditional_guidance_scale != 1.
-        if cuda_graph and hasattr(model, "graphed") and img.is_cuda and conditioning is None:
+        if cuda_graph and hasattr(model, "graphed") and img.is_cuda:
             model = model.graphed()
         b = img.shape[0]
         time_range = np.flip(self.ddim_timesteps)
