@@ -316,15 +316,15 @@ int modiff_gemm_bf16(const modiff_gemm_bf16_desc* desc, const modiff_conv_geom* 
 int modiff_attention_small(const float* q, const float* k, const float* v, float* out, int batch,
                            int c, int t, int tk, float scale, void* stream);
 
-/* Attention with at most 256 keys in one kernel: scores, softmax and the weighted sum of v on
- * the tensor cores, scores and probabilities kept on chip (qdiff/quant_block.py:344-360, 191-203;
+/* Attention in one kernel: scores, online softmax and the weighted sum of v on the tensor cores,
+ * scores and probabilities kept on chip (qdiff/quant_block.py:344-360, 191-203;
  * ldm/modules/diffusionmodules/openaimodel.py:384-406).  Operands are split-bf16 planes:
  *   q_planes [batch][2][t][cp]      from modiff_split_bf16 of q (tokens as pixels)
  *   k_planes [batch][2][tkp][cp]    from modiff_split_bf16 of k, keys padded with zero rows
- *   v_planes [batch][2][crow][tkp]  from modiff_split_bf16_rows of v
+ *   v_planes [batch][2][crow][tkp]  from modiff_split_bf16_rows of v (channel rows padded to crow)
  *   out      [batch][c][t] fp32:  out[b][:, i] = sum_j softmax_j(scale * q[b][:, i] . k[b][:, j]) v[b][:, j]
- * `batch` counts images x heads.  Needs tkp <= 256, tkp % 64 == 0, crow <= 256, crow % 64 == 0,
- * cp >= 64; otherwise MODIFF_ERR_UNSUPPORTED (use modiff_gemm_bf16 / modiff_softmax_split). */
+ * `batch` counts images x heads.  Needs tkp % 64 == 0, crow % 64 == 0, c <= crow <= 256,
+ * 64 <= cp <= 256; otherwise MODIFF_ERR_UNSUPPORTED (use modiff_gemm_bf16 / modiff_softmax_split). */
 int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_planes, const uint16_t* v_planes,
                         float* out, int batch, int c, int t, int tk, int cp, int tkp, int crow,
                         float scale, void* stream);

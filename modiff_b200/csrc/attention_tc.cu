@@ -1,19 +1,22 @@
-// Attention for up to 256 keys in ONE kernel on the 5th-generation tensor cores (sm_100a):
+// Attention in ONE kernel on the 5th-generation tensor cores (sm_100a):
 //   S = scale * q^T k  ->  softmax over keys  ->  out = P v            (per image / head)
-// (qdiff/quant_block.py:344-360 and 191-203: the reference keeps both matmuls and the softmax in
-// floating point).  fp32 accuracy comes from split-bf16 operands as in gemm_bf16_tc.cu
-// (hi*hi + hi*lo + lo*hi, fp32 accumulation in tensor memory).
+// (qdiff/quant_block.py:344-360 and 191-203, ldm/modules/diffusionmodules/openaimodel.py:384-406:
+// the reference keeps both matmuls and the softmax in floating point).  fp32 accuracy comes from
+// split-bf16 operands as in gemm_bf16_tc.cu (hi*hi + hi*lo + lo*hi, fp32 accumulation in tensor
+// memory).  Scores and probabilities never touch global memory.
 //
-// A CTA owns 128 queries of one image at a time:
-//   phase 1  tcgen05.mma (M=128, N=keys<=256) accumulates S in tensor-memory columns [0, 256)
-//            from TMA-fed q / k plane tiles;
-//   phase 2  the epilogue warps read S, take the row maximum and exp, and write the
-//            UNNORMALISED probabilities as two bf16 planes straight into shared memory in the
-//            128-byte-swizzled K-major layout an MMA A operand needs (scores and probabilities
-//            never touch global memory);
+// A CTA owns 128 queries of one image at a time and walks the keys in blocks of 256:
+//   phase 1  tcgen05.mma (M=128, N=256) accumulates the block's scores in tensor-memory columns
+//            [0, 256) from TMA-fed q / k plane tiles;
+//   phase 2  the epilogue warps take the block's row maximum, fold it into the running maximum
+//            (online softmax: the output accumulator is rescaled in tensor memory when the
+//            maximum grows), and write the UNNORMALISED probabilities exp(s - max), 128 keys at a
+//            time, as two bf16 planes straight into shared memory in the 128-byte-swizzled
+//            K-major layout an MMA A operand needs;
 //   phase 3  tcgen05.mma (N=channels<=256) accumulates P v in columns [256, 512), A operand
 //            = those shared-memory planes, B operand = TMA-fed v plane tiles;
-//   phase 4  the epilogue divides by the row sum and writes out[image][channel][query].
+//   phase 4  after the last key block the epilogue divides by the row sum and writes
+//            out[image][channel][query].
 // Phase 1 of the next tile overlaps phase 4 of this one.  Every mbarrier wait is bounded.
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -32,11 +35,11 @@ constexpr int kThreads = 64 + 32 * kEpiWarps;
 
 struct AttnParams {
   int batch, c, t, tk;          // images*heads, channels per head, queries, keys
-  int tkp;                      // keys padded to a multiple of 64 (<= 256)
+  int tkp;                      // keys padded to a multiple of 64
   int crow;                     // channel rows of the v planes (multiple of 64, <= 256)
   int cch;                      // 64-element K chunks of phase 1: ceil(cp / 64)
-  int kch;                      // 64-key K chunks of phase 3: tkp / 64
-  int khalves;                  // 128-key halves: ceil(kch / 2)
+  int n_s;                      // score columns per key block: min(256, tkp)
+  int nsb;                      // key blocks: ceil(tkp / 256)
   int q_tiles;                  // ceil(t / 128)
   int total_tiles;
   float scale;
@@ -102,7 +105,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_sh;
-  const uint32_t k_tile_bytes = (uint32_t)p.tkp * kChunkBytes;
+  const uint32_t k_tile_bytes = (uint32_t)p.n_s * kChunkBytes;
   const uint32_t v_tile_bytes = (uint32_t)p.crow * kChunkBytes;
 
   if (warp == 0) {
@@ -113,27 +116,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const int img = tile / p.q_tiles, qt = tile % p.q_tiles;
-        for (int ch = 0; ch < p.cch && ok; ++ch) {
-          for (int pr = 0; pr < 3; ++pr) {
-            ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
-            if (!ok) break;
-            const uint32_t full = smem_u32(&bar_full[stage]);
-            const uint32_t dst = ring + stage * kStage;
-            mbar_arrive_expect_tx(full, (uint32_t)kATile + k_tile_bytes);
-            tma_load_3d(dst, &map_q, full, ch * 64, qt * 128, img * 2 + prod_a(pr));
-            tma_load_3d(dst + kATile, &map_k, full, ch * 64, 0, img * 2 + prod_b(pr));
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        for (int sb = 0; sb < p.nsb && ok; ++sb) {
+          for (int ch = 0; ch < p.cch && ok; ++ch) {
+            for (int pr = 0; pr < 3; ++pr) {
+              ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
+              if (!ok) break;
+              const uint32_t full = smem_u32(&bar_full[stage]);
+              const uint32_t dst = ring + stage * kStage;
+              mbar_arrive_expect_tx(full, (uint32_t)kATile + k_tile_bytes);
+              tma_load_3d(dst, &map_q, full, ch * 64, qt * 128, img * 2 + prod_a(pr));
+              // key rows beyond tkp are filled with zeros by the copy and masked in the softmax
+              tma_load_3d(dst + kATile, &map_k, full, ch * 64, sb * 256, img * 2 + prod_b(pr));
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
           }
-        }
-        for (int kc = 0; kc < p.kch && ok; ++kc) {
-          for (int pr = 0; pr < 3; ++pr) {
-            ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
-            if (!ok) break;
-            const uint32_t full = smem_u32(&bar_full[stage]);
-            mbar_arrive_expect_tx(full, v_tile_bytes);
-            tma_load_3d(ring + stage * kStage + kATile, &map_v, full, kc * 64, 0,
-                        img * 2 + prod_b(pr));
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          const int kch = min(4, (p.tkp - sb * 256) >> 6);
+          for (int kc = 0; kc < kch && ok; ++kc) {
+            for (int pr = 0; pr < 3; ++pr) {
+              ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
+              if (!ok) break;
+              const uint32_t full = smem_u32(&bar_full[stage]);
+              mbar_arrive_expect_tx(full, v_tile_bytes);
+              tma_load_3d(ring + stage * kStage + kATile, &map_v, full, sb * 256 + kc * 64, 0,
+                          img * 2 + prod_b(pr));
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
           }
         }
       }
@@ -141,57 +148,64 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, p.tkp);
+      const uint32_t idesc_s = make_idesc_bf16(128, p.n_s);
       const uint32_t idesc_o = make_idesc_bf16(128, p.crow);
       int stage = 0;
       uint32_t phase = 0, tphase = 0, pphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        // phase 1: scores.  The previous tile's softmax has finished reading them (the MMAs of
-        // its phase 3 were only issued after bar_p_ready).
-        for (int it = 0; it < 3 * p.cch && ok; ++it) {
-          ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_src = ring + stage * kStage;
-          const uint64_t adesc = make_smem_desc(a_src);
-          const uint64_t bdesc = make_smem_desc(a_src + kATile);
+        bool first_pv = true;
+        for (int sb = 0; sb < p.nsb && ok; ++sb) {
+          // phase 1: scores of this key block.  The softmax has finished reading the previous
+          // block's scores (its last p_ready preceded the MMAs issued just before this point).
+          for (int it = 0; it < 3 * p.cch && ok; ++it) {
+            ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_src = ring + stage * kStage;
+            const uint64_t adesc = make_smem_desc(a_src);
+            const uint64_t bdesc = make_smem_desc(a_src + kATile);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc_s,
-                        (it > 0 || k > 0) ? 1u : 0u);
-          tc_commit(smem_u32(&bar_empty[stage]));
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-        }
-        if (!ok) break;
-        tc_commit(smem_u32(&bar_s_full));
-        // phase 3, 128 keys at a time: the probability planes of one half sit in shared memory
-        // while the epilogue warps wait to write the next half; the first half also needs the
-        // previous tile's output drained
-        for (int kh = 0; kh < p.khalves && ok; ++kh) {
-          ok = mbar_wait(smem_u32(&bar_p_ready), pphase, abort_flag);
-          pphase ^= 1u;
-          if (ok && kh == 0) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const int kc_end = min(p.kch, 2 * kh + 2);
-          for (int kc = 2 * kh; kc < kc_end && ok; ++kc) {
-            for (int pr = 0; pr < 3; ++pr) {
-              ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              const uint64_t adesc =
-                  make_smem_desc(p_smem + (uint32_t)((prod_a(pr) * 2 + (kc & 1)) * kATile));
-              const uint64_t bdesc = make_smem_desc(ring + stage * kStage + kATile);
-#pragma unroll
-              for (int k = 0; k < 4; ++k)
-                tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                            idesc_o, (kc > 0 || pr > 0 || k > 0) ? 1u : 0u);
-              tc_commit(smem_u32(&bar_empty[stage]));
-              if (++stage == kStages) { stage = 0; phase ^= 1u; }
-            }
+            for (int k = 0; k < 4; ++k)
+              tc_mma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc_s,
+                          (it > 0 || k > 0) ? 1u : 0u);
+            tc_commit(smem_u32(&bar_empty[stage]));
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
-          if (ok) tc_commit(smem_u32(&bar_p_free));
+          if (!ok) break;
+          tc_commit(smem_u32(&bar_s_full));
+          // phase 3, 128 keys at a time: the probability planes of one half sit in shared memory
+          // while the epilogue warps wait to write the next half; the tile's first product also
+          // needs the previous tile's output drained
+          const int kch = min(4, (p.tkp - sb * 256) >> 6);
+          const int halves = (kch + 1) >> 1;
+          for (int kh = 0; kh < halves && ok; ++kh) {
+            ok = mbar_wait(smem_u32(&bar_p_ready), pphase, abort_flag);
+            pphase ^= 1u;
+            if (ok && first_pv) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int kc_end = min(kch, 2 * kh + 2);
+            for (int kc = 2 * kh; kc < kc_end && ok; ++kc) {
+              for (int pr = 0; pr < 3; ++pr) {
+                ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t adesc =
+                    make_smem_desc(p_smem + (uint32_t)((prod_a(pr) * 2 + (kc & 1)) * kATile));
+                const uint64_t bdesc = make_smem_desc(ring + stage * kStage + kATile);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                              idesc_o, (first_pv && k == 0) ? 0u : 1u);
+                  first_pv = false;
+                }
+                tc_commit(smem_u32(&bar_empty[stage]));
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+              }
+            }
+            if (ok) tc_commit(smem_u32(&bar_p_free));
+          }
         }
         if (ok) tc_commit(smem_u32(&bar_o_full));
         tphase ^= 1u;
@@ -207,82 +221,108 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int ccols = p.crow >> 1;           // channel columns of this warp (multiple of 32)
     uint8_t* p_ptr = smem_raw;
-    uint32_t tphase = 0, fphase = 0;
+    uint32_t tphase = 0, sphase = 0, fphase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const int img = tile / p.q_tiles, qt = tile % p.q_tiles;
       const int q = qt * 128 + row;
-      ok = mbar_wait(smem_u32(&bar_s_full), tphase, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      // Keys are handled 128 at a time (kh); inside a half the two warps of a lane quarter take
-      // half of its keys each (32 or 64 columns).
-      // ---- row maximum
-      float mx = -INFINITY;
-      for (int kh = 0; kh < p.khalves; ++kh) {
-        const int nk = min(128, p.tkp - 128 * kh) >> 1;
-        for (int c0 = 0; c0 < nk; c0 += 32) {
-          const int key0 = 128 * kh + half * nk + c0;
-          int a[32];
-          tc_ld32(t_lane + (uint32_t)key0, a);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (key0 + j < p.tk) mx = fmaxf(mx, __int_as_float(a[j]) * p.scale);
-        }
-      }
-      red_max[half][row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(red_max[0][row], red_max[1][row]);
-      // ---- exp, row sum, probabilities -> shared memory (K-major rows of 128 bytes, the
-      //      16-byte chunk index XORed with row % 8: the layout TMA writes with 128-byte swizzle)
-      float sum = 0.0f;
-      for (int kh = 0; kh < p.khalves && ok; ++kh) {
-        // the MMAs that read the previous contents of the planes have completed
-        ok = mbar_wait(smem_u32(&bar_p_free), fphase ^ 1u, abort_flag);
-        fphase ^= 1u;
+      float m_run = -INFINITY;      // running row maximum (the same in both warps of a pair)
+      float l_part = 0.0f;          // running sum of this warp's columns, in units of exp(-m_run)
+      for (int sb = 0; sb < p.nsb && ok; ++sb) {
+        const int keys_sb = min(256, p.tkp - sb * 256);
+        const int halves = (keys_sb + 127) >> 7;
+        ok = mbar_wait(smem_u32(&bar_s_full), sphase, abort_flag);
+        sphase ^= 1u;
         if (!ok) break;
-        const int nk = min(128, p.tkp - 128 * kh) >> 1;
-        for (int c0 = 0; c0 < nk; c0 += 32) {
-          const int key0 = 128 * kh + half * nk + c0;       // multiple of 32
-          int a[32];
-          tc_ld32(t_lane + (uint32_t)key0, a);
-          tc_wait_ld();
-          const int kc = (key0 >> 6) & 1;                   // 64-key chunk inside the half
-          const int chunk0 = (key0 & 63) >> 3;              // first 16-byte chunk of the row: 0 or 4
-          uint8_t* hi_row = p_ptr + (size_t)(0 * 2 + kc) * kATile + (size_t)row * 128;
-          uint8_t* lo_row = p_ptr + (size_t)(1 * 2 + kc) * kATile + (size_t)row * 128;
+        tc_fence_after();
+        // Keys are handled 128 at a time (kh); inside a half the two warps of a lane quarter
+        // take half of its keys each (32 or 64 columns).
+        // ---- row maximum of this key block, folded into the running maximum
+        float mx = -INFINITY;
+        for (int kh = 0; kh < halves; ++kh) {
+          const int nk = min(128, keys_sb - 128 * kh) >> 1;
+          for (int c0 = 0; c0 < nk; c0 += 32) {
+            const int col0 = 128 * kh + half * nk + c0;
+            int a[32];
+            tc_ld32(t_lane + (uint32_t)col0, a);
+            tc_wait_ld();
 #pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            uint32_t hw[4], lw[4];
-#pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              float pv[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int j = g8 * 8 + e + u;
-                const float sv = __int_as_float(a[j]) * p.scale;
-                pv[u] = (key0 + j < p.tk) ? exp_neg(sv - mx) : 0.0f;
-                sum += pv[u];
-              }
-              const uint32_t h = bf16_pair(pv[0], pv[1]);
-              hw[e >> 1] = h;
-              lw[e >> 1] = bf16_pair(pv[0] - __uint_as_float(h << 16),
-                                     pv[1] - __uint_as_float(h & 0xffff0000u));
-            }
-            const int chunk = (chunk0 + g8) ^ (row & 7);
-            *reinterpret_cast<uint4*>(hi_row + chunk * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-            *reinterpret_cast<uint4*>(lo_row + chunk * 16) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            for (int j = 0; j < 32; ++j)
+              if (sb * 256 + col0 + j < p.tk) mx = fmaxf(mx, __int_as_float(a[j]) * p.scale);
           }
         }
-        if (kh == p.khalves - 1) red_sum[half][row] = sum;
-        // the MMA reads the planes through the async proxy
-        tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        red_max[half][row] = mx;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
+        const float m_new = fmaxf(m_run, fmaxf(red_max[0][row], red_max[1][row]));
+        // exp(m_run - m_new): 0 for the first block (m_run = -inf), 1 while the maximum stands
+        const float alpha = exp_neg(m_run - m_new);
+        l_part *= alpha;
+        m_run = m_new;
+        // ---- exp, row sum, probabilities -> shared memory (K-major rows of 128 bytes, the
+        //      16-byte chunk index XORed with row % 8: the layout TMA writes with 128-byte swizzle)
+        for (int kh = 0; kh < halves && ok; ++kh) {
+          // the MMAs that read the previous contents of the planes (and accumulated into the
+          // output columns) have completed
+          ok = mbar_wait(smem_u32(&bar_p_free), fphase ^ 1u, abort_flag);
+          fphase ^= 1u;
+          if (!ok) break;
+          if (kh == 0 && sb > 0) {
+            // online softmax: bring the accumulated output to the new maximum
+            tc_fence_after();
+            for (int c0 = 0; c0 < ccols; c0 += 32) {
+              int a[32];
+              tc_ld32(t_lane + 256u + (uint32_t)(half * ccols + c0), a);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) a[j] = __float_as_int(__int_as_float(a[j]) * alpha);
+              tc_st32(t_lane + 256u + (uint32_t)(half * ccols + c0), a);
+            }
+            tc_wait_st();
+          }
+          const int nk = min(128, keys_sb - 128 * kh) >> 1;
+          for (int c0 = 0; c0 < nk; c0 += 32) {
+            const int col0 = 128 * kh + half * nk + c0;       // multiple of 32
+            const int key0 = sb * 256 + col0;
+            int a[32];
+            tc_ld32(t_lane + (uint32_t)col0, a);
+            tc_wait_ld();
+            const int kc = (col0 >> 6) & 1;                   // 64-key chunk inside the half
+            const int chunk0 = (col0 & 63) >> 3;              // first 16-byte chunk of the row: 0 or 4
+            uint8_t* hi_row = p_ptr + (size_t)(0 * 2 + kc) * kATile + (size_t)row * 128;
+            uint8_t* lo_row = p_ptr + (size_t)(1 * 2 + kc) * kATile + (size_t)row * 128;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              uint32_t hw[4], lw[4];
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                float pv[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const int j = g8 * 8 + e + u;
+                  const float sv = __int_as_float(a[j]) * p.scale;
+                  pv[u] = (key0 + j < p.tk) ? exp_neg(sv - m_run) : 0.0f;
+                  l_part += pv[u];
+                }
+                const uint32_t h = bf16_pair(pv[0], pv[1]);
+                hw[e >> 1] = h;
+                lw[e >> 1] = bf16_pair(pv[0] - __uint_as_float(h << 16),
+                                       pv[1] - __uint_as_float(h & 0xffff0000u));
+              }
+              const int chunk = (chunk0 + g8) ^ (row & 7);
+              *reinterpret_cast<uint4*>(hi_row + chunk * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+              *reinterpret_cast<uint4*>(lo_row + chunk * 16) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
+          }
+          // a half with 64 keys fills one chunk; the MMA of this half then reads one chunk only
+          tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
+        }
       }
       if (!ok) break;
+      red_sum[half][row] = l_part;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       const float inv = 1.0f / (red_sum[0][row] + red_sum[1][row]);
       // ---- output
       ok = mbar_wait(smem_u32(&bar_o_full), tphase, abort_flag);
@@ -335,11 +375,12 @@ extern "C" int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_p
                                    int tk, int cp, int tkp, int crow, float scale, void* stream) {
   MODIFF_CHECK_ARG(q_planes && k_planes && v_planes && out, "NULL pointer argument");
   MODIFF_CHECK_ARG(batch > 0 && c > 0 && t > 0 && tk > 0, "bad shape");
-  if (tkp < tk || tkp > 256 || tkp % 64 || crow < c || crow > 256 || crow % 64 || cp < c || cp % 8 ||
-      cp < 64)
+  if (tkp < tk || tkp % 64 || crow < c || crow > 256 || crow % 64 || cp < c || cp % 8 || cp < 64 ||
+      cp > 256)
     return set_error(MODIFF_ERR_UNSUPPORTED,
-                     "single-kernel attention needs keys padded to a multiple of 64 <= 256 and channel "
-                     "rows a multiple of 64 <= 256 (got tkp=%d crow=%d cp=%d)", tkp, crow, cp);
+                     "single-kernel attention needs keys padded to a multiple of 64, channel rows a "
+                     "multiple of 64 <= 256 and 64 <= cp <= 256 (got tkp=%d crow=%d cp=%d)", tkp, crow,
+                     cp);
   MODIFF_CHECK_ARG((((uintptr_t)q_planes | (uintptr_t)k_planes | (uintptr_t)v_planes) & 15) == 0,
                    "plane buffers must be 16-byte aligned");
   EncodeTiledFn encode = get_encode_fn();
@@ -353,8 +394,8 @@ extern "C" int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_p
   p.tkp = tkp;
   p.crow = crow;
   p.cch = ceil_div(cp, 64);
-  p.kch = tkp / 64;
-  p.khalves = (p.kch + 1) / 2;
+  p.n_s = tkp < 256 ? tkp : 256;
+  p.nsb = ceil_div(tkp, 256);
   p.q_tiles = ceil_div(t, 128);
   p.total_tiles = batch * p.q_tiles;
   p.scale = scale;
@@ -371,7 +412,7 @@ extern "C" int modiff_attention_tc(const uint16_t* q_planes, const uint16_t* k_p
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
   CUresult r = make(&map_q, q_planes, cp, t, 128);            // [image*2+part][query][cp]
-  if (r == CUDA_SUCCESS) r = make(&map_k, k_planes, cp, tkp, tkp);   // [image*2+part][key][cp]
+  if (r == CUDA_SUCCESS) r = make(&map_k, k_planes, cp, tkp, p.n_s);   // [image*2+part][key][cp]
   if (r == CUDA_SUCCESS) r = make(&map_v, v_planes, tkp, crow, crow);  // [image*2+part][channel][key]
   if (r != CUDA_SUCCESS)
     return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(attention operands) failed: %d", (int)r);

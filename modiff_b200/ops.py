@@ -367,13 +367,14 @@ def attention(q, k, v, scale):
         torch.empty(b * 2 * tkp * cp, dtype=torch.int16, device=dev)
     gk_src = _lib.ConvGeom(b, c, tk, 1, tk, 1, 1, 1, 0, 0, 0, tkp - tk, 0)  # right pad -> tkp
     _lib.call('modiff_split_bf16', k.data_ptr(), kp.data_ptr(), C.byref(gk_src), _lib.stream_ptr())
-    if FUSED_ATTENTION and tkp <= 256 and c % 64 == 0 and c <= 256:
+    if FUSED_ATTENTION and c <= 256:
         # one kernel: scores and probabilities stay in tensor / shared memory
-        vp = torch.empty(b * 2 * c * tkp, dtype=torch.int16, device=dev)
-        _lib.call('modiff_split_bf16_rows', v.data_ptr(), vp.data_ptr(), b, c, tk, c, tkp,
+        cr = _up(c, 64)                     # channel rows of the v planes (zero rows beyond c)
+        vp = torch.empty(b * 2 * cr * tkp, dtype=torch.int16, device=dev)
+        _lib.call('modiff_split_bf16_rows', v.data_ptr(), vp.data_ptr(), b, c, tk, cr, tkp,
                   _lib.stream_ptr())
         _lib.call('modiff_attention_tc', qp.data_ptr(), kp.data_ptr(), vp.data_ptr(), out.data_ptr(),
-                  b, c, t, tk, cp, tkp, c, float(scale), _lib.stream_ptr())
+                  b, c, t, tk, cp, tkp, cr, float(scale), _lib.stream_ptr())
         return out
     s = torch.empty((b, tk, t), dtype=torch.float32, device=dev)
     d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, cp,
