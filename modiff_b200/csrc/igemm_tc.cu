@@ -358,10 +358,22 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int co0 = t.nt * 128 + col0 + c2 * 32;
           const int ncols = min(32, p.g.cout - co0);   // <= 0 on a ragged last tile
           float* obase = p.o_hat + ((size_t)n * p.g.cout + co0) * howo + hw;
+          // linear layers (one pixel per row): a thread's 32 channels are 128 contiguous bytes
+          const bool row_vec = (howo == 1) && (ncols == 32) && ((p.g.cout & 3) == 0) &&
+                               ((reinterpret_cast<uintptr_t>(p.o_hat) & 15) == 0);
           float v[32];
+          if (row_vec) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = (p.accumulate && valid && j < ncols) ? obase[(size_t)j * howo] : 0.0f;
+            for (int j4 = 0; j4 < 8; ++j4) {
+              float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.accumulate && valid) f = *reinterpret_cast<const float4*>(obase + 4 * j4);
+              v[4 * j4] = f.x; v[4 * j4 + 1] = f.y; v[4 * j4 + 2] = f.z; v[4 * j4 + 3] = f.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = (p.accumulate && valid && j < ncols) ? obase[(size_t)j * howo] : 0.0f;
+          }
 #pragma unroll
           for (int seg = 0; seg < NSEG; ++seg) {
             int a[32];
@@ -377,7 +389,15 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 p.acc_out[((size_t)seg * M + m) * p.g.cout + co0 + j] = iv;
             }
           }
-          if (valid) {
+          if (valid && row_vec) {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const int cb = col0 + c2 * 32 + 4 * j4;
+              *reinterpret_cast<float4*>(obase + 4 * j4) =
+                  make_float4(v[4 * j4] + ep_bias[cb], v[4 * j4 + 1] + ep_bias[cb + 1],
+                              v[4 * j4 + 2] + ep_bias[cb + 2], v[4 * j4 + 3] + ep_bias[cb + 3]);
+            }
+          } else if (valid) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (j < ncols) obase[(size_t)j * howo] = v[j] + ep_bias[col0 + c2 * 32 + j];
