@@ -101,6 +101,19 @@ int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
                        int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
                        int32_t* w_corr, float* w_dq, void* stream);
 
+/* modiff_weight_pack for a weight tensor with LEARNED rounding (AdaRound, hard targets) and
+ * given scales, as a calibrated checkpoint stores them:
+ *   q = clamp(floor(w / delta[c]) + (alpha >= 0) + zero_point[c], 0, 2^b - 1)
+ * (qdiff/adaptive_rounding.py:49-58 with soft_targets False; the quantisers that
+ * qdiff/utils.py:511-539 installs and :567 fills from the checkpoint).
+ *   alpha     fp32, same layout as w; NULL = round to nearest (quant_layer.py:94)
+ *   delta_in, zp_in  fp32 [2][cout] per segment like w_scale / w_zp; NULL = min/max rule
+ * Outputs exactly as modiff_weight_pack (w_scale / w_zp receive the scales used). */
+int modiff_weight_pack_rounded(const float* w, const float* alpha, const float* delta_in,
+                               const float* zp_in, const modiff_conv_geom* g, int n_bits,
+                               int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
+                               int32_t* w_corr, float* w_dq, void* stream);
+
 /* Modulated activation quantiser: r = x - a_hat, dynamic symmetric per-tensor (or
  * per-segment with split) scale, round-half-even codes, a_hat += code * delta.
  * Replaces QuantModule.forward lines qdiff/quant_layer.py:325-336 together with
@@ -167,6 +180,19 @@ int modiff_modq_pair(const modiff_act_source* src, const float* gamma, const flo
 int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes, float* x_scale,
                      float* x_zp, const modiff_conv_geom* g, int n_bits, int per_sample,
                      void* scratch, void* stream);
+
+/* modiff_modq_src / modiff_modq_asym with scales that are GIVEN instead of measured: the
+ * reference's quantiser with dynamic=False (quant_mode 'qdiff'), whose delta / zero_point were
+ * set by its first call or loaded from a calibrated checkpoint and are then only read
+ * (qdiff/quant_layer.py:72-79 skipped, :94-102 applied; loaded by qdiff/utils.py:606-611).
+ * One pass over the tensor: no maximum / range sweep, no scratch.
+ *   x_scale  fp32 in, delta of segment 0 / 1 (or one per image with per_sample)
+ *   x_zp     fp32 in, zero points in the same slots: asymmetric codes, stored centred
+ *            (q - zero_point), so n_bits <= 7 and 0 <= zero_point <= 128 are the caller's to
+ *            check; NULL = symmetric codes clamp(round(r / delta), -2^(b-1), 2^(b-1) - 1) */
+int modiff_modq_fixed(const modiff_act_source* src, float* a_hat, int8_t* codes,
+                      const float* x_scale, const float* x_zp, const modiff_conv_geom* g,
+                      int n_bits, int per_sample, void* stream);
 
 /* modiff_modq_src for an input that is GroupNorm (+ FiLM) (+ SiLU) of [x0 | x1] (+ chan_bias):
  * the normalisation statistics and the residual maximum come from ONE sweep over the source.
@@ -289,6 +315,11 @@ int modiff_split_bf16_rows(const float* x, uint16_t* out, int64_t nb, int rows, 
 int64_t modiff_weights_bf16_bytes(const modiff_conv_geom* g);
 int modiff_weights_bf16(const float* w, const float* w_scale, const float* w_zp, uint16_t* out,
                         const modiff_conv_geom* g, int n_bits, void* stream);
+/* The same with AdaRound hard rounding floor(w / delta) + (alpha >= 0) when alpha (layout of w)
+ * is not NULL (qdiff/adaptive_rounding.py:49-58); scales as modiff_weight_pack_rounded left them. */
+int modiff_weights_bf16_rounded(const float* w, const float* alpha, const float* w_scale,
+                                const float* w_zp, uint16_t* out, const modiff_conv_geom* g,
+                                int n_bits, void* stream);
 
 typedef struct modiff_gemm_bf16_desc {
   const uint16_t* a;      /* activation planes (modiff_split_bf16 layout) */

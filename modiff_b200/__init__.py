@@ -6,6 +6,8 @@ from .quant_block import (BaseQuantBlock, QuantResnetBlock, QuantAttnBlock, Quan
                           QuantBasicTransformerBlock, QuantQKMatMul, QuantSMVMatMul,
                           QuantAttentionBlock, get_specials)
 from .quant_model import QuantModel
+from .adaptive_rounding import AdaRoundQuantizer
+from .utils import convert_adaround, resume_cali_model, load_calibrated_state
 from .unet import Model, make_config
 from .ldm_unet import UNetModel, rerandomize_zero_tensors
 from .ldm_sampler import DDIMSampler, PLMSSampler
@@ -16,7 +18,8 @@ __all__ = [
     "ModiffError", "lib", "device_status", "QuantModule", "UniformAffineQuantizer",
     "StraightThrough", "round_ste", "BaseQuantBlock", "QuantResnetBlock", "QuantAttnBlock",
     "QuantResBlock", "QuantBasicTransformerBlock", "QuantQKMatMul", "QuantSMVMatMul",
-    "QuantAttentionBlock",
+    "QuantAttentionBlock", "AdaRoundQuantizer", "convert_adaround", "resume_cali_model",
+    "load_calibrated_state",
     "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "PLMSSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
     "get_beta_schedule", "make_timestep_sequence",
 ]

@@ -503,7 +503,8 @@ softmax_split_kernel(const float* __restrict__ s, uint16_t* __restrict__ p, int 
 }
 
 // Integer weight values (q - zp, exact in bf16) as the B operand: out[cout][taps][kb].
-__global__ void weights_bf16_kernel(const float* __restrict__ w, const float* __restrict__ w_scale,
+__global__ void weights_bf16_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
+                                    const float* __restrict__ w_scale,
                                     const float* __restrict__ w_zp, uint16_t* __restrict__ out,
                                     modiff_conv_geom g, int taps, int kb, int n_bits) {
   const int co = blockIdx.x;
@@ -513,7 +514,11 @@ __global__ void weights_bf16_kernel(const float* __restrict__ w, const float* __
     const int seg = (g.split > 0 && c >= g.split) ? 1 : 0;
     const float delta = w_scale[seg * g.cout + co], zp = w_zp[seg * g.cout + co];
     const float v = w[((size_t)co * g.cin + c) * taps + tap];
-    const float q = fminf(fmaxf(__fadd_rn(rintf(__fdiv_rn(v, delta)), zp), 0.0f), qmax);
+    float xi = rintf(__fdiv_rn(v, delta));
+    if (alpha)   // learned rounding: floor plus the hard target
+      xi = __fadd_rn(floorf(__fdiv_rn(v, delta)),
+                     alpha[((size_t)co * g.cin + c) * taps + tap] >= 0.0f ? 1.0f : 0.0f);
+    const float q = fminf(fmaxf(__fadd_rn(xi, zp), 0.0f), qmax);
     out[((size_t)co * taps + tap) * kb + c] = bf16_rn(__fsub_rn(q, zp));
   }
 }
@@ -588,6 +593,12 @@ extern "C" int modiff_split_bf16_rows(const float* x, uint16_t* out, int64_t nb,
 extern "C" int modiff_weights_bf16(const float* w, const float* w_scale, const float* w_zp,
                                    uint16_t* out, const modiff_conv_geom* g, int n_bits,
                                    void* stream) {
+  return modiff_weights_bf16_rounded(w, nullptr, w_scale, w_zp, out, g, n_bits, stream);
+}
+
+extern "C" int modiff_weights_bf16_rounded(const float* w, const float* alpha, const float* w_scale,
+                                           const float* w_zp, uint16_t* out,
+                                           const modiff_conv_geom* g, int n_bits, void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(w && w_scale && w_zp && out, "NULL pointer argument");
@@ -595,8 +606,8 @@ extern "C" int modiff_weights_bf16(const float* w, const float* w_scale, const f
   Derived d = derive(*g);
   cudaStream_t s = (cudaStream_t)stream;
   MODIFF_CUDA(cudaMemsetAsync(out, 0, (size_t)modiff_weights_bf16_bytes(g), s));
-  weights_bf16_kernel<<<g->cout, 256, 0, s>>>(w, w_scale, w_zp, out, *g, d.taps, bf16_cp(g->cin),
-                                             n_bits);
+  weights_bf16_kernel<<<g->cout, 256, 0, s>>>(w, alpha, w_scale, w_zp, out, *g, d.taps,
+                                             bf16_cp(g->cin), n_bits);
   MODIFF_LAUNCH_CHECK("weights_bf16_kernel");
   return MODIFF_OK;
 }

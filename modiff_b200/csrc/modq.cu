@@ -1653,6 +1653,33 @@ extern "C" int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8
                          (cudaStream_t)stream, x_zp);
 }
 
+extern "C" int modiff_modq_fixed(const modiff_act_source* src, float* a_hat, int8_t* codes,
+                                 const float* x_scale, const float* x_zp,
+                                 const modiff_conv_geom* g, int n_bits, int per_sample,
+                                 void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= (x_zp ? 7 : 8),
+                   "activation n_bits %d outside [2, %d]", n_bits, x_zp ? 7 : 8);
+  MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.bias = src->chan_bias;
+  v.affine = src->affine;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
+  // the scale pass is skipped: the encode pass only reads x_scale / x_zp
+  return launch_modq_src(v, xform, a_hat, codes, const_cast<float*>(x_scale), g, n_bits, per_sample,
+                         nullptr, false, (cudaStream_t)stream, const_cast<float*>(x_zp));
+}
+
 namespace modiff {
 int read_device_status_modq(int* status, int reset) {
   MODIFF_CUDA(cudaMemcpyFromSymbol(status, g_modq_status, sizeof(int)));

@@ -21,7 +21,9 @@ __device__ inline float warp_max(float v) {
 
 // One block per (output channel, segment).
 __global__ void __launch_bounds__(256)
-weight_pack_kernel(const float* __restrict__ w, modiff_conv_geom g, Derived d, int n_bits,
+weight_pack_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
+                   const float* __restrict__ delta_in, const float* __restrict__ zp_in,
+                   modiff_conv_geom g, Derived d, int n_bits,
                    int with_sum_rows, int8_t* __restrict__ wcodes, float* __restrict__ w_scale,
                    float* __restrict__ w_zp, int32_t* __restrict__ w_corr,
                    float* __restrict__ w_dq) {
@@ -32,15 +34,18 @@ weight_pack_kernel(const float* __restrict__ w, modiff_conv_geom g, Derived d, i
   const int taps = d.taps;
   const int n = (ce - cb) * taps;
   const float* wrow = w + ((size_t)co * g.cin + cb) * taps;  // contiguous [ce-cb][taps]
+  const float* arow = alpha ? alpha + ((size_t)co * g.cin + cb) * taps : nullptr;
 
   __shared__ float s_min[8], s_max[8];
   __shared__ float s_delta, s_zp;
 
   float mn = INFINITY, mx = -INFINITY;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = wrow[i];
-    mn = fminf(mn, v);
-    mx = fmaxf(mx, v);
+  if (!delta_in) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float v = wrow[i];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
   }
   mn = warp_min(mn);
   mx = warp_max(mx);
@@ -58,6 +63,10 @@ weight_pack_kernel(const float* __restrict__ w, modiff_conv_geom g, Derived d, i
     float delta = __fdiv_rn(__fsub_rn(mx, mn), __fsub_rn(n_levels, 1.0f));
     if (delta < 1e-8f) delta = 1e-8f;
     float zp = rintf(__fdiv_rn(-mn, delta));
+    if (delta_in) {
+      delta = delta_in[seg * g.cout + co];
+      zp = zp_in[seg * g.cout + co];
+    }
     s_delta = delta;
     s_zp = zp;
     int zpi = (int)zp;
@@ -77,7 +86,12 @@ weight_pack_kernel(const float* __restrict__ w, modiff_conv_geom g, Derived d, i
     const int c = cb + i / taps;
     const int tap = i % taps;
     float v = wrow[i];
-    float xi = __fadd_rn(rintf(__fdiv_rn(v, delta)), zp);
+    float xi;
+    if (arow) {   // learned rounding: floor plus the hard target
+      xi = __fadd_rn(__fadd_rn(floorf(__fdiv_rn(v, delta)), arow[i] >= 0.0f ? 1.0f : 0.0f), zp);
+    } else {
+      xi = __fadd_rn(rintf(__fdiv_rn(v, delta)), zp);
+    }
     float q = fminf(fmaxf(xi, 0.0f), qmax);
     crow[(size_t)tap * d.kp + c] = (int8_t)((int)q - zoff);
     if (w_dq) {
@@ -104,23 +118,34 @@ __global__ void weight_sum_rows_kernel(int8_t* __restrict__ wcodes, modiff_conv_
 
 using namespace modiff;
 
-extern "C" int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
-                                  int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
-                                  int32_t* w_corr, float* w_dq, void* stream) {
+extern "C" int modiff_weight_pack_rounded(const float* w, const float* alpha, const float* delta_in,
+                                          const float* zp_in, const modiff_conv_geom* g, int n_bits,
+                                          int with_sum_rows, int8_t* wcodes, float* w_scale,
+                                          float* w_zp, int32_t* w_corr, float* w_dq,
+                                          void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(w && wcodes && w_scale && w_zp && w_corr, "NULL pointer argument");
+  MODIFF_CHECK_ARG((delta_in == nullptr) == (zp_in == nullptr),
+                   "delta_in and zp_in must be given together");
   MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "weight n_bits %d outside [2, 8]", n_bits);
   cudaStream_t s = (cudaStream_t)stream;
   Derived d = derive(*g);
   MODIFF_CUDA(cudaMemsetAsync(wcodes, 0, (size_t)modiff_wcodes_bytes(g, with_sum_rows), s));
   dim3 grid(g->cout, d.nseg);
-  weight_pack_kernel<<<grid, 256, 0, s>>>(w, *g, d, n_bits, with_sum_rows, wcodes, w_scale, w_zp,
-                                          w_corr, w_dq);
+  weight_pack_kernel<<<grid, 256, 0, s>>>(w, alpha, delta_in, zp_in, *g, d, n_bits, with_sum_rows,
+                                          wcodes, w_scale, w_zp, w_corr, w_dq);
   MODIFF_LAUNCH_CHECK("weight_pack_kernel");
   if (with_sum_rows) {
     weight_sum_rows_kernel<<<ceil_div(g->cout, 128), 256, 0, s>>>(wcodes, *g, d);
     MODIFF_LAUNCH_CHECK("weight_sum_rows_kernel");
   }
   return MODIFF_OK;
+}
+
+extern "C" int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
+                                  int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
+                                  int32_t* w_corr, float* w_dq, void* stream) {
+  return modiff_weight_pack_rounded(w, nullptr, nullptr, nullptr, g, n_bits, with_sum_rows, wcodes,
+                                    w_scale, w_zp, w_corr, w_dq, stream);
 }

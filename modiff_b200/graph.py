@@ -21,11 +21,17 @@ class GraphedModel:
     def __init__(self, qnn):
         self.qnn = qnn
         self._epoch = None
+        self._config = None
         self._calls = 0
         self._graphs = {}       # (shape, context shape, device) -> dict(graph, x, t, c, out, kernels)
 
     def __call__(self, x, t=None, context=None):
         qnn = self.qnn
+        config = getattr(qnn, "_config_epoch", 0)
+        if config != self._config:          # flags changed: the captured launch lists are stale
+            self._config = config
+            self._graphs = {}
+            self._calls = 0
         epoch = getattr(qnn, "_cache_epoch", 0)
         if epoch != self._epoch:
             self._epoch = epoch

@@ -123,6 +123,9 @@ class _Buffers:
         self.x_zp = _zeros(max(2, g.batch if per_sample else 2), torch.float32, device)
         self.scratch = _zeros(_lib.MODQ_SCRATCH_BYTES + 8 * g.batch, torch.uint8, device)
         self.ho, self.wo = _lib.out_hw(g)
+        # non-dynamic quantisers: True once x_scale / x_zp hold the scale that stays
+        # (set by the first quantised call or by QuantModule.load_act_scale)
+        self.scale_set = False
 
 
 class QuantModule(nn.Module):
@@ -189,9 +192,10 @@ class QuantModule(nn.Module):
         self._group_table = None
         self._group_served = None   # (owner id, owner step) of the grouped launch that wrote o_hat
         self._group_step = 0
-        self._buffers = {}
+        self._geom_buffers = {}
         self._wpack = None
         self._org_kn = None
+        self._loaded_act_scale = None   # (delta per segment, zero point per segment) to install
         self.implicit_pad = (0, 0, 0, 0)   # extra (left, right, top, bottom) zero padding
 
     # ------------------------------------------------------------------ geometry
@@ -236,11 +240,11 @@ class QuantModule(nn.Module):
 
     def _get_buffers(self, g, device):
         key = g.key()
-        buf = self._buffers.get(key)
+        buf = self._geom_buffers.get(key)
         if buf is None or buf.codes.device != device:
             per_sample = bool(self.act_quantizer.channel_wise)
             buf = _Buffers(g, device, per_sample)
-            self._buffers = {key: buf}   # one live geometry per layer
+            self._geom_buffers = {key: buf}   # one live geometry per layer
             n = g.batch if per_sample else 1
             self.act_quantizer.delta = buf.x_scale[0:n].view([n] + [1] * 3) if per_sample \
                 else buf.x_scale[0:1].view([])
@@ -252,17 +256,64 @@ class QuantModule(nn.Module):
                 self.act_quantizer_0.delta = buf.x_scale[1:2].view([])
                 self.act_quantizer_0.zero_point = 0 if not asym else buf.x_zp[1:2].view([])
                 self.act_quantizer_0.inited = True
+            if not self.act_quantizer.dynamic:
+                self.act_quantizer.inited = False      # until the first quantised call
+                if g.split:
+                    self.act_quantizer_0.inited = False
+            self._install_act_scale(buf)
         return buf
+
+    def load_act_scale(self, delta, zero_point=None):
+        """Install calibrated activation scales for a non-dynamic quantiser (what loading a
+        checkpoint does to `act_quantizer.delta` / `.zero_point` in qdiff/utils.py:606-611).
+        `delta` / `zero_point`: one value, or two with split (segment 0, segment 1)."""
+        d = [float(v) for v in (delta if isinstance(delta, (list, tuple)) else [delta])]
+        z = zero_point if zero_point is not None else [0.0] * len(d)
+        z = [float(v) for v in (z if isinstance(z, (list, tuple)) else [z])]
+        if len(d) != len(z) or len(d) not in (1, 2):
+            raise ModiffError("load_act_scale expects one scale, or two for a split layer")
+        aq = self.act_quantizer
+        if aq.channel_wise:
+            raise ModiffError("calibrated scales are per tensor; per-sample quantisers are dynamic")
+        for v in z:
+            if v != int(v):
+                raise ModiffError(f"zero point {v} is not an integer")
+            if aq.sym and v != 0:
+                raise ModiffError("a symmetric quantiser has zero point 0")
+            if not aq.sym and not 0 <= v <= 128:
+                raise ModiffError(f"zero point {v}: the centred codes q - zero_point of a "
+                                  f"{aq.n_bits}-bit quantiser leave the int8 planes")
+        if any(not v > 0 for v in d):
+            raise ModiffError("activation scales must be positive")
+        self._loaded_act_scale = (d, z)
+        for buf in self._geom_buffers.values():
+            self._install_act_scale(buf)
+
+    def _install_act_scale(self, buf):
+        if self._loaded_act_scale is None:
+            return
+        d, z = self._loaded_act_scale
+        segs = 2 if buf.g.split else 1
+        if len(d) != segs:
+            raise ModiffError(f"{len(d)} calibrated scale(s) for a layer with {segs} segment(s)")
+        buf.x_scale[:segs].copy_(torch.tensor(d, dtype=torch.float32), non_blocking=False)
+        buf.x_zp[:segs].copy_(torch.tensor(z, dtype=torch.float32), non_blocking=False)
+        buf.scale_set = True
+        self.act_quantizer.inited = True
+        if segs == 2:
+            self.act_quantizer_0.inited = True
 
     # ------------------------------------------------------------------ weights
     def _pack_weights(self, g):
         """Quantise + pack the weights once per (weight version, bits, split)."""
         w = self.weight
         n_bits = self.weight_quantizer.n_bits
-        key = (w.data_ptr(), w._version, n_bits, g.split, str(w.device))
+        wq = self.weight_quantizer
+        learned = hasattr(wq, 'alpha')        # AdaRound quantiser from a calibrated checkpoint
+        key = (w.data_ptr(), w._version, n_bits, g.split, str(w.device),
+               (wq.alpha.data_ptr(), wq.alpha._version) if learned else None)
         if self._wpack is not None and self._wpack['key'] == key:
             return self._wpack
-        wq = self.weight_quantizer
         if wq.sym or not wq.channel_wise or 'max' not in wq.scale_method:
             raise ModiffError("the accelerated path expects per-output-channel asymmetric 'max' "
                               "weight quantisation (the reference's wq_params)")
@@ -273,6 +324,24 @@ class QuantModule(nn.Module):
         gp = g.copy(batch=1)
         taps = g.kh * g.kw
         pack = None
+        alpha = delta_in = zp_in = None
+        if learned:
+            if wq.round_mode != 'learned_hard_sigmoid' or wq.soft_targets:
+                raise ModiffError("only hard AdaRound targets are packed (inference)")
+            qs = [wq] + ([self.weight_quantizer_0] if g.split else [])
+            if any(not hasattr(q, 'alpha') for q in qs):
+                raise ModiffError("split layer with one AdaRound and one uniform weight quantiser")
+            alpha = torch.cat([q.alpha.detach().to(dev) for q in qs], dim=1).contiguous() \
+                if g.split else wq.alpha.detach().to(dev).contiguous()
+            if tuple(alpha.shape) != tuple(w.shape):
+                raise ModiffError(f"AdaRound alpha {tuple(alpha.shape)} does not match the weight "
+                                  f"{tuple(w.shape)}")
+            delta_in = _zeros(2 * g.cout, torch.float32, dev)
+            zp_in = _zeros(2 * g.cout, torch.float32, dev)
+            for i, q in enumerate(qs):
+                delta_in[i * g.cout:(i + 1) * g.cout] = q.delta.to(dev).reshape(-1)
+                zp_in[i * g.cout:(i + 1) * g.cout] = torch.as_tensor(
+                    q.zero_point, dtype=torch.float32, device=dev).reshape(-1)
         for with_sum in ((1,) if n_bits >= 8 else (0, 1)):
             wcodes = torch.empty(l.modiff_wcodes_bytes(C.byref(gp), with_sum), dtype=torch.int8,
                                  device=dev)
@@ -280,14 +349,19 @@ class QuantModule(nn.Module):
             w_zp = _zeros(2 * g.cout, torch.float32, dev)
             w_corr = _zeros(2 * g.cout, torch.int32, dev)
             w_dq = torch.empty(g.cin * taps * g.cout, dtype=torch.float32, device=dev)
-            _lib.call('modiff_weight_pack', wc.data_ptr(), C.byref(gp), n_bits, with_sum,
+            _lib.call('modiff_weight_pack_rounded', wc.data_ptr(), _lib.ptr(alpha),
+                      _lib.ptr(delta_in), _lib.ptr(zp_in), C.byref(gp), n_bits, with_sum,
                       wcodes.data_ptr(), w_scale.data_ptr(), w_zp.data_ptr(),
                       w_corr.data_ptr(), w_dq.data_ptr(), _lib.stream_ptr())
             need_corr = bool(w_corr.any().item())      # one-time host read at pack time
             pack = dict(key=key, wcodes=wcodes, w_scale=w_scale, w_zp=w_zp,
-                        w_corr=w_corr if need_corr else None, w_dq=w_dq, with_sum=with_sum)
+                        w_corr=w_corr if need_corr else None, w_dq=w_dq, with_sum=with_sum,
+                        alpha=alpha)
             if not need_corr or with_sum:
                 break
+        self._wpack = pack
+        if learned:
+            return pack                     # the AdaRound quantisers keep their own tensors
         shape = [g.cout] + [1] * (w.dim() - 1)
         self.weight_quantizer.delta = pack['w_scale'][:g.cout].view(shape)
         self.weight_quantizer.zero_point = pack['w_zp'][:g.cout].view(shape)
@@ -313,9 +387,9 @@ class QuantModule(nn.Module):
 
     def packed_weights(self, split=0):
         """Weight codes / scales as the kernels consume them (test and tooling hook)."""
-        g = ConvGeom(1, self.weight.shape[1], self.weight.shape[0], 1, 1,
-                     *(self.weight.shape[2:] if self.weight.dim() == 4 else
-                       (1, self.weight.shape[2]) if self.weight.dim() == 3 else (1, 1)),
+        kh, kw = (self.weight.shape[2:] if self.weight.dim() == 4 else
+                  (1, self.weight.shape[2]) if self.weight.dim() == 3 else (1, 1))
+        g = ConvGeom(1, self.weight.shape[1], self.weight.shape[0], kh, kw, kh, kw,
                      1, 0, 0, 0, 0, split)
         return self._pack_weights(g)
 
@@ -348,9 +422,9 @@ class QuantModule(nn.Module):
             wb = torch.empty(l.modiff_weights_bf16_bytes(C.byref(gp)) // 2, dtype=torch.int16,
                              device=dev)
             wc = self.weight.detach().contiguous()
-            _lib.call('modiff_weights_bf16', wc.data_ptr(), pack['w_scale'].data_ptr(),
-                      pack['w_zp'].data_ptr(), wb.data_ptr(), C.byref(gp),
-                      self.weight_quantizer.n_bits, _lib.stream_ptr())
+            _lib.call('modiff_weights_bf16_rounded', wc.data_ptr(), _lib.ptr(pack.get('alpha')),
+                      pack['w_scale'].data_ptr(), pack['w_zp'].data_ptr(), wb.data_ptr(),
+                      C.byref(gp), self.weight_quantizer.n_bits, _lib.stream_ptr())
             pack['w_bf16'] = wb
         planes = torch.zeros(l.modiff_bf16_planes_bytes(C.byref(g)) // 2, dtype=torch.int16,
                              device=dev)
@@ -365,9 +439,33 @@ class QuantModule(nn.Module):
 
     def _modq(self, x, a_hat, buf, g, src=None):
         aq = self.act_quantizer
+        if aq.running_stat:
+            raise ModiffError("running_stat (moving-average ranges) is a calibration-time mode and "
+                              "is not part of the accelerated sampling path")
+        if not aq.dynamic and buf.scale_set:
+            # scale fixed by the first quantised call or a checkpoint: one encode pass
+            if aq.channel_wise:
+                raise ModiffError("non-dynamic per-sample activation scales are not supported")
+            if not aq.sym and aq.n_bits > 7:
+                raise ModiffError("asymmetric activation codes are implemented for up to 7 bits "
+                                  "(centred codes in int8 planes); use --a_sym for 8-bit activations")
+            if src is not None:
+                st = src.struct()
+            else:
+                st = _lib.ActSourceStruct(x.data_ptr(), None, g.cin, 0, None, None)
+            n = src.numel() if src is not None else x.numel()
+            _lib.call('modiff_modq_fixed', C.byref(st), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                      buf.x_scale.data_ptr(), None if aq.sym else buf.x_zp.data_ptr(),
+                      C.byref(g), aq.n_bits, 0, _lib.stream_ptr(),
+                      nbytes=(13 if a_hat is not None else 5) * n, tag=g.key())
+            return
         if not aq.dynamic:
-            raise ModiffError("the int8 path implements dynamic activation scales "
-                              "(quant_mode='dynamic'); static calibrated scales are not covered")
+            # first quantised call of a non-dynamic quantiser measures its scale like a dynamic
+            # one and keeps it (quant_layer.py:72-79)
+            buf.scale_set = True
+            aq.inited = True
+            if g.split:
+                self.act_quantizer_0.inited = True
         if not aq.sym:
             # asymmetric codes (the reference's default without --a_sym): centred codes in the
             # same int8 planes, which bounds them to 7 bits
@@ -558,11 +656,14 @@ class QuantModule(nn.Module):
             raise ModiffError("activation quantisation without weight quantisation is not "
                               "part of the accelerated path (call set_quant_state(True, True))")
 
+        # layers with the same input share one quantiser run only while their scales are the
+        # same by construction, i.e. measured from that input at every step
         shared = (_owner is not None and self.modulate and _owner.modulate and
-                  _owner.a_hat is not None and _owner is not self)
+                  _owner.a_hat is not None and _owner is not self and
+                  self.act_quantizer.dynamic and _owner.act_quantizer.dynamic)
         buf = self._get_buffers(g, input.device)
         if shared:
-            obuf = _owner._buffers.get(g.copy(cout=_owner.weight.shape[0]).key())
+            obuf = _owner._geom_buffers.get(g.copy(cout=_owner.weight.shape[0]).key())
             shared = obuf is not None and _owner.act_quantizer.n_bits == self.act_quantizer.n_bits
         if self.modulate:
             if self.a_hat is None:

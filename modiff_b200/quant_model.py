@@ -56,7 +56,12 @@ class QuantModel(nn.Module):
             else:
                 self.quant_block_refactor(child, weight_quant_params, act_quant_params)
 
+    def _config_changed(self):
+        # captured CUDA graphs replay the kernels of the configuration they were captured in
+        self._config_epoch = getattr(self, "_config_epoch", 0) + 1
+
     def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        self._config_changed()
         for m in self.model.modules():
             if isinstance(m, (QuantModule, BaseQuantBlock)):
                 m.set_quant_state(weight_quant, act_quant)
@@ -75,11 +80,13 @@ class QuantModel(nn.Module):
         return self._graphed
 
     def set_dynamic_state(self, dynamic):
+        self._config_changed()
         for m in self.model.modules():
             if isinstance(m, (QuantModule, QuantAttnBlock)):
                 m.set_dynamic_state(dynamic)
 
     def set_modulation(self, modulation):
+        self._config_changed()
         for m in self.model.modules():
             if isinstance(m, QuantModule):
                 m.set_modualtion(modulation)

@@ -3,7 +3,7 @@ plus the exact-integer view of the same computation used to check codes and accu
 import torch
 import torch.nn.functional as F
 
-from .quantizer import fake_quant, weight_codes
+from .quantizer import fake_quant, weight_codes, adaround_codes
 
 
 class OracleQuantModule:
@@ -15,7 +15,7 @@ class OracleQuantModule:
     """
 
     def __init__(self, weight, bias, stride=1, padding=0, w_bits=8, a_bits=8, a_sym=True,
-                 a_channel_wise=False, modulate=True):
+                 a_channel_wise=False, modulate=True, a_dynamic=True):
         self.weight = weight
         self.bias = bias
         self.stride = stride
@@ -30,6 +30,12 @@ class OracleQuantModule:
         self.o_hat = None
         self.last = {}
         self._wq = {}
+        # non-dynamic activation quantisers (quant_mode 'qdiff'): the scale of the first
+        # quantised call, or a loaded one, stays (qdiff/quant_layer.py:72-79)
+        self.a_dynamic = a_dynamic
+        self.act_scale = None       # per segment (delta tensor, zero point)
+        # AdaRound weight quantisers of a calibrated checkpoint: per segment (alpha, delta, zp)
+        self.adaround = None
 
     def reset_cache(self):
         """qdiff/quant_layer.py:381-383."""
@@ -44,6 +50,12 @@ class OracleQuantModule:
     def _quant_weight(self):
         """qdiff/quant_layer.py:345-351: each segment has its own per-channel quantiser."""
         key = self.split
+        if key not in self._wq and self.adaround is not None:
+            segs = [self.weight[:, :self.split, ...], self.weight[:, self.split:, ...]] \
+                if self.split else [self.weight]
+            assert len(segs) == len(self.adaround)
+            self._wq[key] = [adaround_codes(s.contiguous(), a, d, z, self.w_bits)
+                             for s, (a, d, z) in zip(segs, self.adaround)]
         if key not in self._wq:
             if self.split:
                 parts = [weight_codes(self.weight[:, :self.split, ...].contiguous(), self.w_bits),
@@ -59,8 +71,16 @@ class OracleQuantModule:
             segs = [x[:, :self.split, ...], x[:, self.split:, ...]]
         else:
             segs = [x]
-        return [fake_quant(s, self.a_bits, self.a_sym, channel_wise=self.a_channel_wise)
-                for s in segs]
+        if self.a_dynamic:
+            return [fake_quant(s, self.a_bits, self.a_sym, channel_wise=self.a_channel_wise)
+                    for s in segs]
+        if self.act_scale is None:
+            first = [fake_quant(s, self.a_bits, self.a_sym) for s in segs]
+            self.act_scale = [(f[2], f[3]) for f in first]
+            return first
+        assert len(self.act_scale) == len(segs)
+        return [fake_quant(s, self.a_bits, self.a_sym, scale=sc)
+                for s, sc in zip(segs, self.act_scale)]
 
     def forward(self, x, split=0):
         if not self.use_weight_quant and not self.use_act_quant and not self.modulate:

@@ -69,3 +69,12 @@ def weight_codes(w, n_bits):
     (scripts/sample_diffusion_ddim.py:143; qdiff/quant_layer.py:160-190, 94-102).
     Returns (dequantised weights, unsigned codes, delta[c], zero_point[c])."""
     return fake_quant(w, n_bits, sym=False, channel_wise=True)
+
+
+def adaround_codes(w, alpha, delta, zero_point, n_bits):
+    """AdaRound hard rounding of a loaded checkpoint (qdiff/adaptive_rounding.py:49-58 with
+    soft_targets False): floor(w / delta) + (alpha >= 0), shifted by the zero point and clamped.
+    Returns (dequantised weights, unsigned codes, delta, zero_point) like weight_codes."""
+    x_int = torch.floor(w / delta) + (alpha >= 0).float()
+    q = torch.clamp(x_int + zero_point, 0, 2 ** n_bits - 1)
+    return (q - zero_point) * delta, q, delta, zero_point

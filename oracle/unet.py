@@ -36,7 +36,7 @@ class OracleUNet:
     """`state` maps the reference Model's parameter names to CPU fp32 tensors."""
 
     def __init__(self, state, cfg=None, w_bits=8, a_bits=8, a_sym=True, modulate=True,
-                 split_shortcut=False, a_channel_wise=False, quant=True):
+                 split_shortcut=False, a_channel_wise=False, quant=True, a_dynamic=True):
         self.cfg = cfg or pixel_unet_config()
         self.state = state
         self.split_shortcut = split_shortcut
@@ -51,7 +51,7 @@ class OracleUNet:
                 if base.endswith("downsample.conv"):
                     stride, padding = 2, 0
             m = OracleQuantModule(w, state.get(base + ".bias"), stride, padding, w_bits, a_bits,
-                                  a_sym, a_channel_wise, modulate)
+                                  a_sym, a_channel_wise, modulate, a_dynamic)
             m.use_weight_quant = m.use_act_quant = quant
             if not quant:
                 m.modulate = False
@@ -60,6 +60,28 @@ class OracleUNet:
     def reset_cache(self):
         for m in self.layers.values():
             m.reset_cache()
+
+    def load_calibrated(self, ckpt, split_of=None, load_act=True, prefix="model."):
+        """Install the quantiser tensors of a calibrated checkpoint (the state dict that
+        qdiff/utils.py:542-628 loads): per layer `weight_quantizer[_0].alpha / delta /
+        zero_point` and, with `load_act`, `act_quantizer[_0].delta / zero_point`.  `split_of`
+        maps a layer name to its concat split (layers whose checkpoint has `_0` quantisers)."""
+        for base, m in self.layers.items():
+            k = prefix + base
+            if k + ".weight_quantizer.alpha" not in ckpt:
+                continue
+            slots = ["weight_quantizer"]
+            if k + ".weight_quantizer_0.alpha" in ckpt:
+                slots.append("weight_quantizer_0")
+                m.split = (split_of or {}).get(base, ckpt[k + ".weight_quantizer.alpha"].shape[1])
+            m.adaround = [(ckpt[f"{k}.{s}.alpha"], ckpt[f"{k}.{s}.delta"],
+                           ckpt[f"{k}.{s}.zero_point"]) for s in slots]
+            m._wq = {}
+            if load_act and k + ".act_quantizer.delta" in ckpt:
+                aslots = ["act_quantizer"] + (["act_quantizer_0"] if len(slots) == 2 else [])
+                m.act_scale = [(ckpt[f"{k}.{s}.delta"].reshape(()).float(),
+                                int(ckpt.get(f"{k}.{s}.zero_point", torch.zeros(())).item()))
+                               for s in aslots]
 
     # -------------------------------------------------------------- blocks
     def _gn(self, x, base):

@@ -174,3 +174,55 @@ def sd_inputs(c):
     cond = torch.randn(c["batch"], 77, 768, generator=g)
     uncond = torch.randn(c["batch"], 77, 768, generator=g)
     return x, cond, uncond
+
+
+# ---------------------------------------------------------------- calibrated checkpoints
+CALI_CASES = [
+    # pixel UNet, static (quant_mode 'qdiff') activation scales and AdaRound weights loaded from
+    # a synthetic checkpoint in the reference's format; first `evals` of a 10-step quad run
+    dict(name="cali_w4a8_split_b2", w_bits=4, a_bits=8, a_sym=True, split=True, batch=2, steps=100,
+         first=30, evals=5, noise_seed=31, cali_seed=32, alpha_seed=33, scale_margin=1.5),
+    dict(name="cali_w8a6_asym_b2", w_bits=8, a_bits=6, a_sym=False, split=False, batch=2, steps=100,
+         first=30, evals=4, noise_seed=34, cali_seed=35, alpha_seed=36, scale_margin=1.25),
+]
+
+
+def cali_sequence(c):
+    """`evals` consecutive timesteps from the middle of the 100-step quad sequence (t about
+    70..90): step-to-step changes there are small against the activations, as in a real run,
+    whereas a random-init UNet makes the first steps from pure noise jump."""
+    return unet_sequence(c)[c["first"]:c["first"] + c["evals"]]
+
+
+def cali_data(c):
+    """The (x, t) pair scripts/sample_diffusion_ddim.py:160-162 hands to resume_cali_model."""
+    g = torch.Generator().manual_seed(c["cali_seed"])
+    return torch.randn(1, 3, 32, 32, generator=g), torch.randint(0, 1000, (1,), generator=g)
+
+
+def cali_alpha(key, shape, seed):
+    """AdaRound logits of the synthetic checkpoint: seeded noise, i.e. every weight is rounded up
+    or down at random - a harder case than a trained checkpoint, whose logits mostly keep
+    round-to-nearest."""
+    import zlib
+    g = torch.Generator().manual_seed(seed + zlib.crc32(key.encode()) % 100000)
+    return torch.randn(tuple(shape), generator=g)
+
+
+def cali_checkpoint(c, model_state, fixture, prefix):
+    """The synthetic calibrated checkpoint of a case: UNet parameters from `model_state` (keys as
+    the float model names them), AdaRound logits from seeds, quantiser scales from the fixture
+    (entries `<prefix>/ckpt/<key>`), under the reference QuantModel's key names."""
+    import json
+    ckpt = {}
+    for key, shape in json.loads(str(fixture[prefix + "/keys"])):
+        stored = f"{prefix}/ckpt/{key}"
+        if key.endswith(".alpha"):
+            ckpt[key] = cali_alpha(key, shape, c["alpha_seed"])
+        elif stored in fixture:
+            ckpt[key] = torch.from_numpy(np.asarray(fixture[stored])).reshape(shape).clone()
+        else:
+            name = key[len("model."):]
+            ckpt[key] = model_state[name].detach().cpu().clone()
+        assert list(ckpt[key].shape) == list(shape), key
+    return ckpt

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -232,6 +232,111 @@ def gen_plms():
     print("plms.npz", len(out))
 
 
+def gen_cali():
+    """Calibrated-checkpoint path: reference QuantModel with non-dynamic activation quantisers,
+    weight quantisers converted to AdaRound, a synthetic checkpoint loaded by the steps of
+    qdiff/utils.py:542-628 (its .cuda() calls left out), then modulated sampling."""
+    from qdiff.utils import convert_adaround
+    from qdiff.adaptive_rounding import AdaRoundQuantizer
+    out = {}
+    betas = torch.from_numpy(np.linspace(1e-4, 2e-2, 1000, dtype=np.float64)).float()
+
+    def params_on(qnn, also_act):
+        for m in qnn.model.modules():
+            if isinstance(m, AdaRoundQuantizer):
+                m.zero_point = nn.Parameter(m.zero_point)
+                m.delta = nn.Parameter(m.delta)
+            elif also_act and isinstance(m, RefQuantizer) and m.zero_point is not None:
+                zp = m.zero_point
+                m.zero_point = nn.Parameter(zp if torch.is_tensor(zp) else torch.tensor(float(zp)))
+
+    def params_off(qnn, also_act):
+        for m in qnn.model.modules():
+            if isinstance(m, AdaRoundQuantizer):
+                z, d = m.zero_point.data, m.delta.data
+                delattr(m, "zero_point")
+                delattr(m, "delta")
+                m.zero_point, m.delta = z, d
+            elif also_act and isinstance(m, RefQuantizer) and m.zero_point is not None:
+                z = m.zero_point.item()
+                delattr(m, "zero_point")
+                assert int(z) == z
+                m.zero_point = int(z)
+
+    for c in cases.CALI_CASES:
+        t0 = time.time()
+        wq, aq = cases.quant_params(c)
+        x = cases.unet_noise(c)
+        seq = cases.cali_sequence(c)
+
+        # plausible activation scales: those of a dynamic run at its third evaluation
+        torch.manual_seed(0)
+        qd = RefQuantModel(model=RefModel(ref_config(c["split"])).eval(), weight_quant_params=wq,
+                           act_quant_params=dict(aq), sm_abit=8, modulate=True).eval()
+        qd.set_quant_state(True, True)
+        qd.reset_cache()
+        ref_sample(qd, x, seq[-3:], betas)
+        scales = {}
+        for name, m in qd.named_modules():
+            if isinstance(m, RefQuantModule):
+                for slot in ("act_quantizer", "act_quantizer_0"):
+                    q = getattr(m, slot, None)
+                    if q is not None and q.delta is not None:
+                        scales[f"{name}.{slot}"] = (float(q.delta) * c["scale_margin"],
+                                                    float(q.zero_point))
+        del qd
+
+        torch.manual_seed(0)
+        model = RefModel(ref_config(c["split"])).eval()
+        qnn = RefQuantModel(model=model, weight_quant_params=wq,
+                            act_quant_params=dict(aq, dynamic=False), sm_abit=8,
+                            modulate=True).eval()
+        cx, ct = cases.cali_data(c)
+        with torch.no_grad():
+            qnn.set_quant_state(True, False)
+            qnn(cx, ct)
+            convert_adaround(qnn)
+            params_on(qnn, False)
+            qnn.set_quant_state(True, True)
+            qnn(cx, ct)
+            qnn(cx, ct)
+            params_on_act = True
+            params_off(qnn, False)
+            params_on(qnn, params_on_act)
+        sd = qnn.state_dict()
+        keys = [[k, list(v.shape)] for k, v in sd.items()]
+        ckpt = {}
+        for k, v in sd.items():
+            if k.endswith(".alpha"):
+                ckpt[k] = cases.cali_alpha(k, v.shape, c["alpha_seed"])
+                continue
+            ckpt[k] = v.detach().clone()
+            parts = k.split(".")
+            if parts[-2].startswith("act_quantizer"):
+                d, z = scales[".".join(parts[:-1])]
+                ckpt[k] = torch.tensor(d if parts[-1] == "delta" else z, dtype=torch.float32)
+            if parts[-2].startswith(("act_quantizer", "weight_quantizer")):
+                out[f"{c['name']}/ckpt/{k}"] = ckpt[k].numpy().copy()
+        out[c["name"] + "/keys"] = np.asarray(json.dumps(keys))
+        # weights-only load (strict), then the full load, as the reference does in two stages
+        qnn.load_state_dict(ckpt, strict=True)
+        params_off(qnn, True)
+        qnn.set_quant_state(True, True)
+        qnn.reset_cache()
+        eps = []
+
+        def grab(step, et, xt):
+            eps.append(et.numpy().copy())
+
+        final = ref_sample(qnn, x, seq, betas, grab)
+        out[c["name"] + "/final"] = final.numpy().copy()
+        for s, e in enumerate(eps):
+            out[f"{c['name']}/eps{s}"] = e
+        print(c["name"], f"{time.time() - t0:.1f}s", len(keys), "keys", float(final.std()))
+    np.savez_compressed(os.path.join(HERE, "cali.npz"), **out)
+    print("cali.npz", len(out))
+
+
 def gen_sd():
     """SD-v1 UNet shapes (random init seed 0, zero tensors redrawn), reference QuantModel with
     --a_sym, classifier-free guidance as ldm/models/diffusion/ddim.py:192-208."""
@@ -279,7 +384,7 @@ def gen_sd():
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
-                ldm=gen_ldm, plms=gen_plms, sd=gen_sd)
+                ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()
