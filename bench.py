@@ -137,6 +137,10 @@ def main():
     ap.add_argument("--ddim-steps", type=int, default=DDIM_STEPS,
                     help="profiling aid: keep only the last n timesteps of the 100-step schedule")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quant-mode", choices=["dynamic", "qdiff"], default="dynamic",
+                    help="'qdiff': non-dynamic activation scales (each layer keeps the scale of its "
+                         "first quantised call), the mode of a calibrated checkpoint; not the "
+                         "headline configuration")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -154,12 +158,15 @@ def main():
 
     torch.manual_seed(0)
     net = m.Model(m.make_config(split_shortcut=True)).eval()
-    qnn = m.QuantModel(net, WQ, AQ, sm_abit=8, modulate=True).to(dev).eval()
+    aq = dict(AQ, dynamic=(args.quant_mode == "dynamic"))
+    qnn = m.QuantModel(net, WQ, aq, sm_abit=8, modulate=True).to(dev).eval()
     qnn.set_quant_state(True, True)
     betas = torch.from_numpy(m.get_beta_schedule()).float()
     seq = m.make_timestep_sequence(1000, DDIM_STEPS, "quad")[-args.ddim_steps:]
     workload = WORKLOAD if (args.ddim_steps == DDIM_STEPS and batch == BATCH_PER_GPU) else \
         f"REDUCED (profiling) {args.ddim_steps} DDIM steps, batch {batch}/GPU: " + WORKLOAD
+    if args.quant_mode != "dynamic":
+        workload = "STATIC activation scales (quant_mode qdiff): " + workload
 
     g = torch.Generator().manual_seed(D.rank_seed(1, rank))
     x_host = torch.randn(batch, 3, 32, 32, generator=g).pin_memory()

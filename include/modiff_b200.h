@@ -108,11 +108,13 @@ int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int n_bits,
  * qdiff/utils.py:511-539 installs and :567 fills from the checkpoint).
  *   alpha     fp32, same layout as w; NULL = round to nearest (quant_layer.py:94)
  *   delta_in, zp_in  fp32 [2][cout] per segment like w_scale / w_zp; NULL = min/max rule
- * Outputs exactly as modiff_weight_pack (w_scale / w_zp receive the scales used). */
+ * Outputs exactly as modiff_weight_pack (w_scale / w_zp receive the scales used), plus
+ *   w_csum    int32 [2][cout] out, or NULL: sum over the segment's inputs of (q - zero_point),
+ *             the factor modiff_asym_bias needs */
 int modiff_weight_pack_rounded(const float* w, const float* alpha, const float* delta_in,
                                const float* zp_in, const modiff_conv_geom* g, int n_bits,
                                int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
-                               int32_t* w_corr, float* w_dq, void* stream);
+                               int32_t* w_corr, float* w_dq, int32_t* w_csum, void* stream);
 
 /* Modulated activation quantiser: r = x - a_hat, dynamic symmetric per-tensor (or
  * per-segment with split) scale, round-half-even codes, a_hat += code * delta.
@@ -176,10 +178,31 @@ int modiff_modq_pair(const modiff_act_source* src, const float* gamma, const flo
  * modiff_device_status.
  *   x_zp     fp32 out, same slots as x_scale: the zero points
  *   scratch  at least 16 + 8 * slots bytes (slots = 2, or batch with per_sample), zero-filled
- *            once by the caller */
+ *            once by the caller
+ * n_bits == 8 (the latent-diffusion drivers' default, W8A8 without --a_sym): q - zero_point spans
+ * nine bits, so the planes receive q - 128 instead, i.e. every code is offset by
+ * z' = zero_point - 128.  The caller then (1) writes z' into the planes' padding cells
+ * (modiff_codes_fill_halo), so that padded positions still stand for the value 0, and (2) passes
+ * modiff_igemm_conv the per-channel constant -z' * sum(q_w - zp_w) * delta_x * delta_w[c] as its
+ * bias (modiff_asym_bias).  Not available with per_sample. */
 int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes, float* x_scale,
                      float* x_zp, const modiff_conv_geom* g, int n_bits, int per_sample,
                      void* scratch, void* stream);
+
+/* Companions of 8-bit asymmetric codes (planes hold q - 128, see modiff_modq_asym).
+ * modiff_codes_fill_halo: every code-plane cell that is not an input pixel (the zero padding of
+ * F.conv2d, qdiff/quant_layer.py:271) receives zero_point - 128 of its channel's segment, the
+ * code of the value 0; call it after each quantiser run of a padded layer (the zero point moves
+ * every step).  modiff_asym_bias:
+ *   bias_out[c] = (bias_in ? bias_in[c] : 0)
+ *                 - sum_seg (zero_point[seg] - 128) * w_csum[seg][c] * x_scale[seg] * w_scale[seg][c],
+ * the constant that the offset codes add to channel c of the layer's output, with the sign that
+ * removes it; pass it as `bias` to modiff_igemm_conv (honoured with accumulate too). */
+int modiff_codes_fill_halo(int8_t* codes, const float* x_zp, const modiff_conv_geom* g,
+                           void* stream);
+int modiff_asym_bias(const float* x_scale, const float* x_zp, const float* w_scale,
+                     const int32_t* w_csum, const float* bias_in, float* bias_out, int cout,
+                     int nseg, void* stream);
 
 /* modiff_modq_src / modiff_modq_asym with scales that are GIVEN instead of measured: the
  * reference's quantiser with dynamic=False (quant_mode 'qdiff'), whose delta / zero_point were
@@ -188,8 +211,9 @@ int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes, 
  * One pass over the tensor: no maximum / range sweep, no scratch.
  *   x_scale  fp32 in, delta of segment 0 / 1 (or one per image with per_sample)
  *   x_zp     fp32 in, zero points in the same slots: asymmetric codes, stored centred
- *            (q - zero_point), so n_bits <= 7 and 0 <= zero_point <= 128 are the caller's to
- *            check; NULL = symmetric codes clamp(round(r / delta), -2^(b-1), 2^(b-1) - 1) */
+ *            (q - zero_point) for n_bits <= 7 (0 <= zero_point <= 128 is the caller's to
+ *            check) and as q - 128 for n_bits == 8 (see modiff_modq_asym);
+ *            NULL = symmetric codes clamp(round(r / delta), -2^(b-1), 2^(b-1) - 1) */
 int modiff_modq_fixed(const modiff_act_source* src, float* a_hat, int8_t* codes,
                       const float* x_scale, const float* x_zp, const modiff_conv_geom* g,
                       int n_bits, int per_sample, void* stream);

@@ -84,6 +84,13 @@ __device__ inline float quantise_clamp(float r, float delta, float inv, float lo
   bits = __float_as_uint(u);
   return qf;
 }
+// 8-bit asymmetric codes q in [0, 255] do not fit an int8 plane centred (q - zp spans 9 bits), so
+// the planes hold q - 128 = (q - zp) + (zp - 128): this is the integer added to the centred
+// code's bit pattern before its low byte is stored.  The convolution's epilogue takes the
+// constant (zp - 128) * sum(w) back out (modiff_asym_bias).  Narrower codes stay centred.
+__device__ inline uint32_t plane_shift(const float* x_zp, int slot, int n_levels) {
+  return (x_zp && n_levels == 127) ? (uint32_t)((int)x_zp[slot] - 128) : 0u;
+}
 // low bytes of four words -> one word
 __device__ inline uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -267,6 +274,7 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
           // asymmetric codes: centred range [-zp, 2^b - 1 - zp]
           const float lo_s = x_zp ? -x_zp[slot] : lo;
           const float hi_s = x_zp ? (float)(2 * n_levels + 1) - x_zp[slot] : hi;
+          const uint32_t zshift = plane_shift(x_zp, slot, n_levels);
           const size_t off = ((size_t)n * g.cin + c) * hw;
           float xv[4], av[4] = {0.f, 0.f, 0.f, 0.f}, nv[4];
           load_src<VEC4, XFORM>(src, n, c, g.cin, p, hw, xv);
@@ -275,6 +283,7 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
             const float qf = round_clamp(__fdiv_rn(r, delta), lo_s, hi_s, q[i][j]);
+            q[i][j] += zshift;
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat) store4<VEC4>(a_hat + off, p, hw, nv);
@@ -391,6 +400,9 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
     const float top = (float)(2 * n_levels + 1);
     const float lo0 = x_zp ? -zp0 : lo, hi0 = x_zp ? top - zp0 : hi;
     const float lo1 = x_zp ? -zp1 : lo, hi1 = x_zp ? top - zp1 : hi;
+    const bool shifted = x_zp && n_levels == 127;       // 8-bit asymmetric: planes hold q - 128
+    const uint32_t zs0 = shifted ? (uint32_t)((int)zp0 - 128) : 0u;
+    const uint32_t zs1 = shifted ? (uint32_t)((int)zp1 - 128) : 0u;
 
     uint32_t q[4][4];
 #pragma unroll
@@ -433,6 +445,7 @@ modq_encode_staged_kernel(const SrcView src, float* __restrict__ a_hat,
           for (int j = 0; j < 4; ++j) {
             const float r = __fsub_rn(xv[j], av[j]);
             const float qf = quantise_clamp(r, delta, inv, seg1 ? lo1 : lo0, seg1 ? hi1 : hi0, q[i][j]);
+            q[i][j] += seg1 ? zs1 : zs0;
             nv[j] = __fadd_rn(av[j], __fmul_rn(qf, delta));
           }
           if (a_hat)
@@ -511,7 +524,7 @@ __device__ inline void finalise_ranges(ModqScratch* scratch, int slots, int n_bi
       if (delta < 1e-8f) delta = 1e-8f;
       zp = rintf(__fdiv_rn(-xmin, delta));
     }
-    if (!(-zp >= -128.0f && (float)top - zp <= 127.0f)) atomicOr(&g_modq_status, 4);
+    if (n_bits < 8 && !(-zp >= -128.0f && (float)top - zp <= 127.0f)) atomicOr(&g_modq_status, 4);
     x_scale[s] = delta;
     x_zp[s] = zp;
   }
@@ -712,6 +725,7 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
     const float delta = x_scale[slot];
     const float lo_s = x_zp ? -x_zp[slot] : lo;
     const float hi_s = x_zp ? (float)(2 * n_levels + 1) - x_zp[slot] : hi;
+    const uint32_t zshift = plane_shift(x_zp, slot, n_levels);
     float4 xv = __ldg(x + i);
     float4 av = a_hat ? a_hat[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     float xs[4] = {xv.x, xv.y, xv.z, xv.w}, as[4] = {av.x, av.y, av.z, av.w}, nv[4];
@@ -719,6 +733,7 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float qf = round_clamp(__fdiv_rn(__fsub_rn(xs[j], as[j]), delta), lo_s, hi_s, qb[j]);
+      qb[j] += zshift;
       nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
     }
     if (a_hat) a_hat[i] = make_float4(nv[0], nv[1], nv[2], nv[3]);
@@ -1633,9 +1648,9 @@ extern "C" int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale && x_zp && scratch, "NULL pointer argument");
-  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 7,
-                   "asymmetric activation codes are stored centred (q - zero_point) in int8 planes: "
-                   "n_bits %d outside [2, 7]", n_bits);
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(!(n_bits == 8 && per_sample),
+                   "8-bit asymmetric codes need one zero point per scale segment, not per image");
   MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
@@ -1660,8 +1675,7 @@ extern "C" int modiff_modq_fixed(const modiff_act_source* src, float* a_hat, int
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale, "NULL pointer argument");
-  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= (x_zp ? 7 : 8),
-                   "activation n_bits %d outside [2, %d]", n_bits, x_zp ? 7 : 8);
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
   MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
@@ -1786,6 +1800,87 @@ extern "C" int modiff_im2col_codes(const int8_t* codes, int8_t* out, const modif
   if (blocks > 148 * 16) blocks = 148 * 16;
   im2col_codes_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(codes, out, *g, d, out_stride);
   MODIFF_LAUNCH_CHECK("im2col_codes_kernel");
+  return MODIFF_OK;
+}
+
+namespace modiff {
+namespace {
+// 16 channels of one plane cell per thread; cells that hold an input pixel are skipped.
+__global__ void codes_fill_halo_kernel(int8_t* __restrict__ codes, const float* __restrict__ x_zp,
+                                       modiff_conv_geom g, Derived d) {
+  const int pieces = d.cp / 16;
+  const int64_t total = (int64_t)g.batch * d.nplanes * d.hp * d.wp * pieces;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int z0 = (int)x_zp[0] - 128;
+  const int z1 = g.split > 0 ? (int)x_zp[1] - 128 : z0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int piece = (int)(i % pieces);
+    int64_t cell = i / pieces;
+    const int xq = (int)(cell % d.wp);
+    int64_t t = cell / d.wp;
+    const int yq = (int)(t % d.hp);
+    const int plane = (int)((t / d.hp) % d.nplanes);
+    const int y = yq * g.stride + plane / g.stride - g.pad_t;
+    const int x = xq * g.stride + plane % g.stride - g.pad_l;
+    if (y >= 0 && y < g.h && x >= 0 && x < g.w) continue;
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int c = piece * 16 + 4 * k + b;
+        const int v = c < g.cin ? ((g.split > 0 && c >= g.split) ? z1 : z0) : 0;
+        word |= (uint32_t)(v & 0xff) << (8 * b);
+      }
+      w[k] = word;
+    }
+    *reinterpret_cast<int4*>(codes + cell * d.cp + piece * 16) =
+        make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+  }
+}
+
+__global__ void asym_bias_kernel(const float* __restrict__ x_scale, const float* __restrict__ x_zp,
+                                 const float* __restrict__ w_scale,
+                                 const int32_t* __restrict__ w_csum,
+                                 const float* __restrict__ bias_in, float* __restrict__ bias_out,
+                                 int cout, int nseg) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cout) return;
+  float acc = bias_in ? bias_in[c] : 0.0f;
+  for (int seg = 0; seg < nseg; ++seg) {
+    const long long k = -(long long)((int)x_zp[seg] - 128) * (long long)w_csum[seg * cout + c];
+    acc = __fadd_rn(acc, __fmul_rn((float)k, __fmul_rn(x_scale[seg], w_scale[seg * cout + c])));
+  }
+  bias_out[c] = acc;
+}
+}  // namespace
+}  // namespace modiff
+
+extern "C" int modiff_codes_fill_halo(int8_t* codes, const float* x_zp, const modiff_conv_geom* g,
+                                      void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(codes && x_zp, "NULL pointer argument");
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  Derived d = derive(*g);
+  if ((int64_t)d.nplanes * d.hp * d.wp == (int64_t)g->h * g->w) return MODIFF_OK;   // no padding cell
+  const int64_t total = (int64_t)g->batch * d.nplanes * d.hp * d.wp * (d.cp / 16);
+  int64_t blocks = ceil_div64(total, 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  codes_fill_halo_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(codes, x_zp, *g, d);
+  MODIFF_LAUNCH_CHECK("codes_fill_halo_kernel");
+  return MODIFF_OK;
+}
+
+extern "C" int modiff_asym_bias(const float* x_scale, const float* x_zp, const float* w_scale,
+                                const int32_t* w_csum, const float* bias_in, float* bias_out,
+                                int cout, int nseg, void* stream) {
+  MODIFF_CHECK_ARG(x_scale && x_zp && w_scale && w_csum && bias_out, "NULL pointer argument");
+  MODIFF_CHECK_ARG(cout > 0 && (nseg == 1 || nseg == 2), "bad cout %d / nseg %d", cout, nseg);
+  asym_bias_kernel<<<ceil_div(cout, 128), 128, 0, (cudaStream_t)stream>>>(
+      x_scale, x_zp, w_scale, w_csum, bias_in, bias_out, cout, nseg);
+  MODIFF_LAUNCH_CHECK("asym_bias_kernel");
   return MODIFF_OK;
 }
 

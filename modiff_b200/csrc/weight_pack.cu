@@ -26,7 +26,7 @@ weight_pack_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
                    modiff_conv_geom g, Derived d, int n_bits,
                    int with_sum_rows, int8_t* __restrict__ wcodes, float* __restrict__ w_scale,
                    float* __restrict__ w_zp, int32_t* __restrict__ w_corr,
-                   float* __restrict__ w_dq) {
+                   float* __restrict__ w_dq, int32_t* __restrict__ w_csum) {
   const int co = blockIdx.x;
   const int seg = blockIdx.y;
   const int cb = (seg == 0) ? 0 : g.split;
@@ -38,6 +38,8 @@ weight_pack_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
 
   __shared__ float s_min[8], s_max[8];
   __shared__ float s_delta, s_zp;
+  __shared__ int s_sum;
+  if (threadIdx.x == 0) s_sum = 0;
 
   float mn = INFINITY, mx = -INFINITY;
   if (!delta_in) {
@@ -82,6 +84,8 @@ weight_pack_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
   const float qmax = (float)((1 << n_bits) - 1);
   const int row = with_sum_rows ? (co / 128) * 144 + (co % 128) : co;
   int8_t* crow = wcodes + (size_t)row * taps * d.kp;
+  int centred_sum = 0;     // sum of q - zp over this (channel, segment): the factor of an
+                           // activation-code offset in the layer's output
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int c = cb + i / taps;
     const int tap = i % taps;
@@ -94,9 +98,16 @@ weight_pack_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
     }
     float q = fminf(fmaxf(xi, 0.0f), qmax);
     crow[(size_t)tap * d.kp + c] = (int8_t)((int)q - zoff);
+    centred_sum += (int)q - zpi;
     if (w_dq) {
       w_dq[((size_t)c * taps + tap) * g.cout + co] = __fmul_rn(__fsub_rn(q, zp), delta);
     }
+  }
+  if (w_csum) {
+    for (int o = 16; o > 0; o >>= 1) centred_sum += __shfl_xor_sync(0xffffffffu, centred_sum, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&s_sum, centred_sum);
+    __syncthreads();
+    if (threadIdx.x == 0) w_csum[seg * g.cout + co] = s_sum;
   }
 }
 
@@ -122,7 +133,7 @@ extern "C" int modiff_weight_pack_rounded(const float* w, const float* alpha, co
                                           const float* zp_in, const modiff_conv_geom* g, int n_bits,
                                           int with_sum_rows, int8_t* wcodes, float* w_scale,
                                           float* w_zp, int32_t* w_corr, float* w_dq,
-                                          void* stream) {
+                                          int32_t* w_csum, void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(w && wcodes && w_scale && w_zp && w_corr, "NULL pointer argument");
@@ -134,7 +145,7 @@ extern "C" int modiff_weight_pack_rounded(const float* w, const float* alpha, co
   MODIFF_CUDA(cudaMemsetAsync(wcodes, 0, (size_t)modiff_wcodes_bytes(g, with_sum_rows), s));
   dim3 grid(g->cout, d.nseg);
   weight_pack_kernel<<<grid, 256, 0, s>>>(w, alpha, delta_in, zp_in, *g, d, n_bits, with_sum_rows,
-                                          wcodes, w_scale, w_zp, w_corr, w_dq);
+                                          wcodes, w_scale, w_zp, w_corr, w_dq, w_csum);
   MODIFF_LAUNCH_CHECK("weight_pack_kernel");
   if (with_sum_rows) {
     weight_sum_rows_kernel<<<ceil_div(g->cout, 128), 256, 0, s>>>(wcodes, *g, d);
@@ -147,5 +158,5 @@ extern "C" int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int
                                   int with_sum_rows, int8_t* wcodes, float* w_scale, float* w_zp,
                                   int32_t* w_corr, float* w_dq, void* stream) {
   return modiff_weight_pack_rounded(w, nullptr, nullptr, nullptr, g, n_bits, with_sum_rows, wcodes,
-                                    w_scale, w_zp, w_corr, w_dq, stream);
+                                    w_scale, w_zp, w_corr, w_dq, nullptr, stream);
 }

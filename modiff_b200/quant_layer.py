@@ -196,6 +196,7 @@ class QuantModule(nn.Module):
         self._wpack = None
         self._org_kn = None
         self._loaded_act_scale = None   # (delta per segment, zero point per segment) to install
+        self._step_bias = None          # per-step output constant of offset (8-bit asymmetric) codes
         self.implicit_pad = (0, 0, 0, 0)   # extra (left, right, top, bottom) zero padding
 
     # ------------------------------------------------------------------ geometry
@@ -280,9 +281,9 @@ class QuantModule(nn.Module):
                 raise ModiffError(f"zero point {v} is not an integer")
             if aq.sym and v != 0:
                 raise ModiffError("a symmetric quantiser has zero point 0")
-            if not aq.sym and not 0 <= v <= 128:
-                raise ModiffError(f"zero point {v}: the centred codes q - zero_point of a "
-                                  f"{aq.n_bits}-bit quantiser leave the int8 planes")
+            if not aq.sym and not 0 <= v <= (255 if aq.n_bits == 8 else 128):
+                raise ModiffError(f"zero point {v} of a {aq.n_bits}-bit quantiser cannot be stored "
+                                  "in the int8 code planes")
         if any(not v > 0 for v in d):
             raise ModiffError("activation scales must be positive")
         self._loaded_act_scale = (d, z)
@@ -349,14 +350,15 @@ class QuantModule(nn.Module):
             w_zp = _zeros(2 * g.cout, torch.float32, dev)
             w_corr = _zeros(2 * g.cout, torch.int32, dev)
             w_dq = torch.empty(g.cin * taps * g.cout, dtype=torch.float32, device=dev)
+            w_csum = _zeros(2 * g.cout, torch.int32, dev)
             _lib.call('modiff_weight_pack_rounded', wc.data_ptr(), _lib.ptr(alpha),
                       _lib.ptr(delta_in), _lib.ptr(zp_in), C.byref(gp), n_bits, with_sum,
                       wcodes.data_ptr(), w_scale.data_ptr(), w_zp.data_ptr(),
-                      w_corr.data_ptr(), w_dq.data_ptr(), _lib.stream_ptr())
+                      w_corr.data_ptr(), w_dq.data_ptr(), w_csum.data_ptr(), _lib.stream_ptr())
             need_corr = bool(w_corr.any().item())      # one-time host read at pack time
             pack = dict(key=key, wcodes=wcodes, w_scale=w_scale, w_zp=w_zp,
                         w_corr=w_corr if need_corr else None, w_dq=w_dq, with_sum=with_sum,
-                        alpha=alpha)
+                        alpha=alpha, w_csum=w_csum)
             if not need_corr or with_sum:
                 break
         self._wpack = pack
@@ -446,9 +448,6 @@ class QuantModule(nn.Module):
             # scale fixed by the first quantised call or a checkpoint: one encode pass
             if aq.channel_wise:
                 raise ModiffError("non-dynamic per-sample activation scales are not supported")
-            if not aq.sym and aq.n_bits > 7:
-                raise ModiffError("asymmetric activation codes are implemented for up to 7 bits "
-                                  "(centred codes in int8 planes); use --a_sym for 8-bit activations")
             if src is not None:
                 st = src.struct()
             else:
@@ -458,6 +457,7 @@ class QuantModule(nn.Module):
                       buf.x_scale.data_ptr(), None if aq.sym else buf.x_zp.data_ptr(),
                       C.byref(g), aq.n_bits, 0, _lib.stream_ptr(),
                       nbytes=(13 if a_hat is not None else 5) * n, tag=g.key())
+            self._offset_codes_halo(buf, g)
             return
         if not aq.dynamic:
             # first quantised call of a non-dynamic quantiser measures its scale like a dynamic
@@ -467,11 +467,12 @@ class QuantModule(nn.Module):
             if g.split:
                 self.act_quantizer_0.inited = True
         if not aq.sym:
-            # asymmetric codes (the reference's default without --a_sym): centred codes in the
-            # same int8 planes, which bounds them to 7 bits
-            if aq.n_bits > 7:
-                raise ModiffError("asymmetric activation codes are implemented for up to 7 bits "
-                                  "(centred codes in int8 planes); use --a_sym for 8-bit activations")
+            # asymmetric codes (the reference's default without --a_sym): centred codes
+            # q - zero_point in the same int8 planes up to 7 bits, q - 128 at 8 bits
+            if aq.n_bits > 7 and aq.channel_wise:
+                raise ModiffError("8-bit asymmetric activation codes are stored offset by one zero "
+                                  "point per tensor; per-sample (--act_tensor) scales need --a_sym "
+                                  "or at most 7 bits")
             if src is not None:
                 st = src.struct()
             else:
@@ -481,6 +482,7 @@ class QuantModule(nn.Module):
                       buf.x_scale.data_ptr(), buf.x_zp.data_ptr(), C.byref(g), aq.n_bits,
                       int(aq.channel_wise), buf.scratch.data_ptr(), _lib.stream_ptr(),
                       nbytes=(13 if a_hat is not None else 5) * n, tag=g.key())
+            self._offset_codes_halo(buf, g)
             return
         if src is not None and src.pending_norm() and self.fuse_norm_stats:
             n = src.norm
@@ -502,6 +504,28 @@ class QuantModule(nn.Module):
                   buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, int(aq.channel_wise),
                   buf.scratch.data_ptr(), _lib.stream_ptr(),
                   nbytes=(13 if a_hat is not None else 5) * x.numel(), tag=g.key())
+
+    def _offset_codes(self):
+        """8-bit asymmetric activation codes: the planes hold q - 128 (see modiff_modq_asym)."""
+        aq = self.act_quantizer
+        return (not aq.sym) and aq.n_bits == 8
+
+    def _offset_codes_halo(self, buf, g):
+        if self._offset_codes() and (g.pad_t or g.pad_b or g.pad_l or g.pad_r):
+            _lib.call('modiff_codes_fill_halo', buf.codes.data_ptr(), buf.x_zp.data_ptr(),
+                      C.byref(g), _lib.stream_ptr())
+
+    def _offset_codes_bias(self, buf, pack, bias, g):
+        """Per-step constant that takes the code offset back out of this layer's output; `buf`
+        is the buffer set the codes came from (another layer's when the quantiser is shared)."""
+        dev = buf.codes.device
+        if self._step_bias is None or self._step_bias.numel() != g.cout or \
+                self._step_bias.device != dev:
+            self._step_bias = _zeros(g.cout, torch.float32, dev)
+        _lib.call('modiff_asym_bias', buf.x_scale.data_ptr(), buf.x_zp.data_ptr(),
+                  pack['w_scale'].data_ptr(), pack['w_csum'].data_ptr(), _lib.ptr(bias),
+                  self._step_bias.data_ptr(), g.cout, 2 if g.split else 1, _lib.stream_ptr())
+        return self._step_bias
 
     def _use_im2col(self, g, buf):
         """Layers with very few input channels (the 3-channel input conv) run on the tensor
@@ -525,9 +549,12 @@ class QuantModule(nn.Module):
                                  dtype=torch.int8, device=dev)
             tmp = [_zeros(2 * g.cout, dt, dev) for dt in (torch.float32, torch.float32, torch.int32)]
             wc = self.weight.detach().contiguous()
-            _lib.call('modiff_weight_pack', wc.data_ptr(), C.byref(gp),
+            # the layer's own scales (and learned rounding, if any) so both layouts hold one set
+            # of integer weights
+            _lib.call('modiff_weight_pack_rounded', wc.data_ptr(), _lib.ptr(pack.get('alpha')),
+                      pack['w_scale'].data_ptr(), pack['w_zp'].data_ptr(), C.byref(gp),
                       self.weight_quantizer.n_bits, pack['with_sum'], wcodes.data_ptr(),
-                      tmp[0].data_ptr(), tmp[1].data_ptr(), tmp[2].data_ptr(), None,
+                      tmp[0].data_ptr(), tmp[1].data_ptr(), tmp[2].data_ptr(), None, None,
                       _lib.stream_ptr())
             pack['wcodes_im2col'] = wcodes
         _lib.call('modiff_im2col_codes', buf.codes.data_ptr(), buf.im2col.data_ptr(), C.byref(g),
@@ -542,6 +569,8 @@ class QuantModule(nn.Module):
 
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
+        if self._offset_codes():
+            bias = self._offset_codes_bias(buf, pack, bias, g)
         if self._use_im2col(g, buf):
             return self._igemm_im2col(buf, pack, o_hat, accumulate, bias, g, acc_out)
         # algorithmic bytes: o_hat read + write 8 per output element, 1 per input code, weights
@@ -565,6 +594,7 @@ class QuantModule(nn.Module):
         steady = (self.fuse_residual_add and self.modulate and self.use_act_quant
                   and self.use_weight_quant and not self.disable_act_quant
                   and self.a_hat is not None and self.o_hat is not None and self.split == 0
+                  and not self._offset_codes()
                   and self.fwd_func is F.conv2d and not self.act_quantizer.channel_wise
                   and self.activation_function.__class__.__name__ == "StraightThrough"
                   and torch.is_tensor(residual) and residual.is_cuda
@@ -754,7 +784,7 @@ class QuantModule(nn.Module):
         if not (self.group_small_linears and g.h == 1 and g.w == 1 and g.kh == 1 and g.kw == 1
                 and g.split == 0 and g.batch <= self._GROUP_MAX_ROWS and g.cin % 16 == 0
                 and not self.act_quantizer.channel_wise and self.fwd_func is F.linear
-                and member.fwd_func is F.linear):
+                and member.fwd_func is F.linear and not self._offset_codes()):
             return
         if all(m is not member for m in self._group_members):
             self._group_members.append(member)

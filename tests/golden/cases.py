@@ -67,6 +67,15 @@ LAYER_CASES = [
          batch=2, w_bits=8, a_bits=4, a_sym=False, split=128, seed=113),
     dict(name="lin_w8a6_asym", kind="linear", cin=256, cout=128, batch=6, w_bits=8, a_bits=6,
          a_sym=False, seed=114),
+    # 8-bit asymmetric activations: what the latent-diffusion drivers run without --a_sym
+    dict(name="c3_w8a8_asym", kind="conv", cin=128, cout=128, k=3, stride=1, pad=1, hw=8, batch=2,
+         w_bits=8, a_bits=8, a_sym=False, seed=115),
+    dict(name="c1_split_w4a8_asym", kind="conv", cin=256, cout=128, k=1, stride=1, pad=0, hw=8,
+         batch=2, w_bits=4, a_bits=8, a_sym=False, split=128, seed=116),
+    dict(name="down_w8a8_asym", kind="conv", cin=128, cout=128, k=3, stride=2, pad=0, hw=8, batch=2,
+         w_bits=8, a_bits=8, a_sym=False, pad_br=True, seed=117),
+    dict(name="lin_w8a8_asym", kind="linear", cin=256, cout=128, batch=6, w_bits=8, a_bits=8,
+         a_sym=False, seed=118),
 ]
 
 
@@ -137,6 +146,9 @@ LDM_CASES = [
     # first `evals` UNet evaluations of the 500 that `-c 400` gives (uniform, c = 1000 // 400)
     dict(name="ldm_w8a8_b2", w_bits=8, a_bits=8, batch=2, ddim_steps=400, evals=6, noise_seed=11,
          zero_seed=1234),
+    # the driver's default quantiser (no --a_sym): asymmetric per-tensor 8-bit activations
+    dict(name="ldm_w8a8_asym_b2", w_bits=8, a_bits=8, a_sym=False, batch=2, ddim_steps=400, evals=5,
+         noise_seed=13, zero_seed=1234),
 ]
 
 

@@ -237,6 +237,12 @@ def test_small_linears_sharing_codes_run_in_one_launch(cuda, w_bits):
     ("linear", (5, 77, 256), 128, 0, False, 4),        # tokens x channels
     ("conv3", (4, 128, 8, 8), 128, 0, True, 4),        # one scale per image (--act_tensor)
     ("linear", (6, 256), 64, 0, True, 7),
+    # 8 bits: planes hold q - 128, padding cells the offset, the GEMM a per-step channel constant
+    ("conv3", (3, 128, 16, 16), 128, 0, False, 8),
+    ("conv3", (2, 192, 8, 8), 64, 128, False, 8),
+    ("conv1", (4, 64, 6, 6), 32, 0, False, 8),
+    ("linear", (5, 77, 256), 128, 0, False, 8),
+    ("conv3", (2, 3, 16, 16), 128, 0, False, 8),       # few input channels: gathered-codes GEMM
 ])
 def test_asymmetric_activation_codes(cuda, kind, shape, cout, split, per_sample, a_bits):
     """The reference's activation quantiser without --a_sym (sym=False,
@@ -284,11 +290,12 @@ def test_asymmetric_activation_codes(cuda, kind, shape, cout, split, per_sample,
     assert m.device_status() == 0
 
 
-def test_asymmetric_codes_refuse_eight_bits(cuda):
+def test_asymmetric_per_sample_codes_refuse_eight_bits(cuda):
+    """One zero point per image would need one output constant per image."""
     import modiff_b200 as m
     org = torch.nn.Conv2d(64, 64, 3, padding=1)
     wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
-    aq = {'n_bits': 8, 'symmetric': False, 'channel_wise': False, 'scale_method': 'max',
+    aq = {'n_bits': 8, 'symmetric': False, 'channel_wise': True, 'scale_method': 'max',
           'leaf_param': True, 'dynamic': True}
     q = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
     q.set_quant_state(True, True)

@@ -49,11 +49,11 @@ def test_ddim_schedule_rule():
     assert len(make_ddim_timesteps("uniform", 50, 1000)) == 50
 
 
-def test_oracle_matches_reference(golden_ldm):
-    c = cases.LDM_CASES[0]
+@pytest.mark.parametrize("c", cases.LDM_CASES, ids=lambda c: c["name"])
+def test_oracle_matches_reference(c, golden_ldm):
     net = _build()
     state = {k: v.detach().clone() for k, v in net.state_dict().items()}
-    o = OracleLDMUNet(state, cases.LDM_CONFIG, c["w_bits"], c["a_bits"])
+    o = OracleLDMUNet(state, cases.LDM_CONFIG, c["w_bits"], c["a_bits"], c.get("a_sym", True))
     eps = []
     final = latent_ddim_sample(cases.ldm_noise(c), o.forward, ldm_schedule(**cases.LDM_SCHEDULE),
                                c["ddim_steps"], max_evals=3,
@@ -65,9 +65,9 @@ def test_oracle_matches_reference(golden_ldm):
 
 
 @pytest.mark.gpu
-def test_cuda_path_matches_reference(cuda, golden_ldm):
+@pytest.mark.parametrize("c", cases.LDM_CASES, ids=lambda c: c["name"])
+def test_cuda_path_matches_reference(c, cuda, golden_ldm):
     import modiff_b200 as m
-    c = cases.LDM_CASES[0]
     net = _build()
     wq, aq = cases.quant_params(c)
     qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(cuda).eval()
