@@ -204,6 +204,21 @@ int modiff_asym_bias(const float* x_scale, const float* x_zp, const float* w_sca
                      const int32_t* w_csum, const float* bias_in, float* bias_out, int cout,
                      int nseg, void* stream);
 
+/* modiff_igemm_conv (and, with residual / sum_out not NULL, modiff_igemm_conv_add) for OFFSET
+ * activation codes, i.e. 8-bit asymmetric ones stored as q - 128 by modiff_modq_asym /
+ * modiff_modq_fixed with the padding cells set by modiff_codes_fill_halo:
+ *   out[c] = o_hat[c] + (acc[c] + w_corr[c] * rowsum - (zp[seg] - 128) * w_csum[seg][c])
+ *            * x_scale[seg] * w_scale[seg][c]  (+ bias[c]),
+ * the same value as qdiff/quant_layer.py:359-365 computes from (q - zp) * delta, with the offset
+ * taken out of the integer accumulator (no separate bias vector, every kernel variant available).
+ *   x_zp    fp32 [2]: zero point per scale segment;  w_csum int32 [2][cout] from
+ *           modiff_weight_pack_rounded */
+int modiff_igemm_conv_offset(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                             const float* x_scale, const float* x_zp, const float* w_scale,
+                             const int32_t* w_corr, const int32_t* w_csum, float* o_hat,
+                             int accumulate, const float* bias, const modiff_conv_geom* g, int impl,
+                             const float* residual, float* sum_out, void* stream);
+
 /* modiff_modq_src / modiff_modq_asym with scales that are GIVEN instead of measured: the
  * reference's quantiser with dynamic=False (quant_mode 'qdiff'), whose delta / zero_point were
  * set by its first call or loaded from a calibrated checkpoint and are then only read

@@ -54,6 +54,8 @@ struct HaloParams {
   const float* x_scale;
   const float* w_scale;
   const int32_t* w_corr;
+  const float* x_zp;          // offset (8-bit asymmetric) activation codes, else NULL
+  const int32_t* w_csum;
   const float* residual;   // optional [batch][cout][h*w]: sum_out = new output + residual
   float* sum_out;
 };
@@ -83,6 +85,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ int abort_sh;
   __shared__ float ep_scale[128];
   __shared__ int ep_corr[128];
+  __shared__ int ep_off[128];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -272,6 +275,7 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ep_tid < 128) {
           ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * 128 + ep_tid]);
           ep_corr[ep_tid] = p.w_corr ? p.w_corr[t.nt * 128 + ep_tid] : 0;
+          ep_off[ep_tid] = p.x_zp ? -((int)p.x_zp[0] - 128) * p.w_csum[t.nt * 128 + ep_tid] : 0;
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         last_nt = t.nt;
@@ -312,6 +316,10 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           if (p.w_corr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) a[j] += ep_corr[colbase + j] * rsum;
+          }
+          if (p.x_zp) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) a[j] += ep_off[colbase + j];
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
@@ -382,7 +390,8 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
-                      const float* residual, float* sum_out) {
+                      const float* residual, float* sum_out, const float* x_zp,
+                      const int32_t* w_csum) {
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   static int sm_count = 0;
@@ -435,6 +444,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.x_scale = x_scale;
   p.w_scale = w_scale;
   p.w_corr = w_corr;
+  p.x_zp = x_zp;
+  p.w_csum = w_csum;
   p.residual = residual;
   p.sum_out = sum_out;
   const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes;

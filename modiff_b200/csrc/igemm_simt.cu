@@ -20,7 +20,8 @@ igemm_simt_kernel(const int8_t* __restrict__ codes, const int8_t* __restrict__ w
                   int with_sum_rows, const float* __restrict__ x_scale,
                   const float* __restrict__ w_scale, const int32_t* __restrict__ w_corr,
                   float* __restrict__ o_hat, int accumulate, const float* __restrict__ bias,
-                  modiff_conv_geom g, Derived d, int per_sample, int32_t* __restrict__ acc_out) {
+                  modiff_conv_geom g, Derived d, int per_sample, int32_t* __restrict__ acc_out,
+                  const float* __restrict__ x_zp, const int32_t* __restrict__ w_csum) {
   __shared__ uint32_t As[BM][BK / 4 + 1];
   __shared__ uint32_t Bs[BN][BK / 4 + 1];
 
@@ -133,11 +134,13 @@ igemm_simt_kernel(const int8_t* __restrict__ codes, const int8_t* __restrict__ w
       if (co >= g.cout) continue;
       const float ws = w_scale[seg * g.cout + co];
       const int corr = w_corr ? w_corr[seg * g.cout + co] : 0;
+      // offset (8-bit asymmetric) activation codes: take (zp - 128) * sum(w) back out
+      const int off = x_zp ? -((int)x_zp[seg] - 128) * w_csum[seg * g.cout + co] : 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int m = m0 + tx + 16 * i;
         if (m >= M) continue;
-        const int a = acc[i][j] + corr * rsum[i];
+        const int a = acc[i][j] + corr * rsum[i] + off;
         const float xs = per_sample ? x_scale[m / howo] : x_scale[seg];
         facc[i][j] += (float)a * __fmul_rn(xs, ws);
         if (acc_out) acc_out[((size_t)seg * M + m) * g.cout + co] = a;
@@ -168,12 +171,14 @@ igemm_simt_kernel(const int8_t* __restrict__ codes, const int8_t* __restrict__ w
 int launch_igemm_simt(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const float* bias, const modiff_conv_geom* g,
-                      int per_sample, int32_t* acc_out, cudaStream_t s) {
+                      int per_sample, int32_t* acc_out, cudaStream_t s, const float* x_zp,
+                      const int32_t* w_csum) {
   Derived d = derive(*g);
   const int M = g->batch * d.ho * d.wo;
   dim3 grid(ceil_div(M, BM), ceil_div(g->cout, BN));
   igemm_simt_kernel<<<grid, kThreads, 0, s>>>(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr,
-                                              o_hat, accumulate, bias, *g, d, per_sample, acc_out);
+                                              o_hat, accumulate, bias, *g, d, per_sample, acc_out,
+                                              x_zp, w_csum);
   MODIFF_LAUNCH_CHECK("igemm_simt_kernel");
   return MODIFF_OK;
 }

@@ -21,7 +21,8 @@ namespace modiff {
 int launch_igemm_simt(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const float* bias, const modiff_conv_geom* g,
-                      int per_sample, int32_t* acc_out, cudaStream_t s);
+                      int per_sample, int32_t* acc_out, cudaStream_t s, const float* x_zp,
+                      const int32_t* w_csum);
 
 namespace {
 
@@ -59,6 +60,8 @@ struct TcParams {
   const float* x_scale;
   const float* w_scale;
   const int32_t* w_corr;
+  const float* x_zp;             // offset (8-bit asymmetric) activation codes, else NULL
+  const int32_t* w_csum;         // [2][cout] sum of centred weight codes per segment
   const float* bias;
   float* o_hat;
   int32_t* acc_out;
@@ -98,6 +101,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __shared__ int abort_sh;
   __shared__ float ep_scale[2][128];
   __shared__ int ep_corr[2][128];
+  __shared__ int ep_off[2][128];
   __shared__ float ep_bias[128];
 
   const int warp = threadIdx.x >> 5;
@@ -289,6 +293,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (TMA_EPI) sc = __fmul_rn(p.x_scale[seg], sc);
             ep_scale[seg][ep_tid] = sc;
             ep_corr[seg][ep_tid] = (cv && p.w_corr) ? p.w_corr[seg * p.g.cout + co] : 0;
+            // codes stored as q - 128: (zp - 128) * sum of the channel's centred weights comes
+            // back out of the integer accumulator
+            ep_off[seg][ep_tid] = (cv && p.x_zp)
+                ? -((int)p.x_zp[seg] - 128) * p.w_csum[seg * p.g.cout + co] : 0;
           }
           ep_bias[ep_tid] = (cv && p.bias) ? p.bias[co] : 0.0f;
         }
@@ -301,6 +309,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.buf_cols);
       int rsum[2] = {0, 0};
+      const bool offset_codes = p.x_zp != nullptr;
       if (WITH_SUM) {
 #pragma unroll
         for (int seg = 0; seg < NSEG; ++seg) tc_ld1(t_row + seg * p.umma_n + 128, rsum[seg]);
@@ -329,6 +338,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int j = 0; j < 32; ++j) {
               int iv = a[j];
               if (WITH_SUM) iv += ep_corr[seg][colbase + j] * rsum[seg];
+              if (offset_codes) iv += ep_off[seg][colbase + j];
               v[j] = fmaf((float)iv, ep_scale[seg][colbase + j], v[j]);
             }
           }
@@ -384,6 +394,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               const int cl = col0 + c2 * 32 + j;
               int iv = a[j];
               if (WITH_SUM) iv += ep_corr[seg][cl] * rsum[seg];
+              if (offset_codes) iv += ep_off[seg][cl];
               v[j] += (float)iv * __fmul_rn(xs[seg], ep_scale[seg][cl]);
               if (p.acc_out && valid && j < ncols)
                 p.acc_out[((size_t)seg * M + m) * p.g.cout + co0 + j] = iv;
@@ -450,7 +461,8 @@ bool tc_supported(const modiff_conv_geom* g, int per_sample, const char** why) {
 int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                     const float* x_scale, const float* w_scale, const int32_t* w_corr,
                     float* o_hat, int accumulate, const float* bias, const modiff_conv_geom* g,
-                    int per_sample, int32_t* acc_out, cudaStream_t s) {
+                    int per_sample, int32_t* acc_out, cudaStream_t s, const float* x_zp,
+                    const int32_t* w_csum) {
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   MODIFF_CHECK_ARG(w_corr == nullptr || with_sum_rows,
@@ -485,6 +497,8 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   p.x_scale = x_scale;
   p.w_scale = w_scale;
   p.w_corr = w_corr;
+  p.x_zp = x_zp;
+  p.w_csum = w_csum;
   p.bias = bias;
   p.o_hat = o_hat;
   p.acc_out = acc_out;
@@ -596,7 +610,8 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
-                      const float* residual, float* sum_out);
+                      const float* residual, float* sum_out, const float* x_zp,
+                      const int32_t* w_csum);
 
 // MODIFF_IGEMM_HALO=0 keeps 3x3 layers on the one-copy-per-tap kernel (debug aid, same results)
 static bool halo_enabled() {
@@ -630,13 +645,16 @@ static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_s
                            const float* x_scale, const float* w_scale, const int32_t* w_corr,
                            float* o_hat, int accumulate, const float* bias,
                            const modiff_conv_geom* g, int per_sample, int impl, int32_t* acc_out,
-                           const float* residual, float* sum_out, void* stream) {
+                           const float* residual, float* sum_out, const float* x_zp,
+                           const int32_t* w_csum, void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
   MODIFF_CHECK_ARG(codes && wcodes && x_scale && w_scale && o_hat, "NULL pointer argument");
   MODIFF_CHECK_ARG((((uintptr_t)codes | (uintptr_t)wcodes) & 15) == 0,
                    "code buffers must be 16-byte aligned");
   MODIFF_CHECK_ARG(!(per_sample && g->split > 0), "per-sample scales cannot be combined with split");
+  MODIFF_CHECK_ARG((x_zp == nullptr) == (w_csum == nullptr), "x_zp and w_csum go together");
+  MODIFF_CHECK_ARG(!(x_zp && per_sample), "offset codes have one zero point per scale segment");
   cudaStream_t s = (cudaStream_t)stream;
   const char* why = "";
   const bool tc_ok = tc_supported(g, per_sample, &why);
@@ -644,7 +662,7 @@ static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_s
     return set_error(MODIFF_ERR_UNSUPPORTED, "tcgen05 path does not cover this layer: %s", why);
   if (impl == MODIFF_IMPL_SIMT || !tc_ok) {
     const int rc1 = launch_igemm_simt(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat,
-                                      accumulate, bias, g, per_sample, acc_out, s);
+                                      accumulate, bias, g, per_sample, acc_out, s, x_zp, w_csum);
     if (rc1 || !residual) return rc1;
     const Derived ds = derive(*g);
     return modiff_add(residual, o_hat, sum_out, g->batch, g->cout, ds.ho * ds.wo, 0, stream);
@@ -652,9 +670,9 @@ static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_s
   MODIFF_CHECK_ARG(impl == MODIFF_IMPL_AUTO || impl == MODIFF_IMPL_TCGEN05, "unknown impl %d", impl);
   if (halo_enabled() && halo_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
     return launch_igemm_halo(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                             g, s, residual, sum_out);
+                             g, s, residual, sum_out, x_zp, w_csum);
   int rc2 = launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                            bias, g, per_sample, acc_out, s);
+                            bias, g, per_sample, acc_out, s, x_zp, w_csum);
   if (rc2 || !residual) return rc2;
   const Derived dd = derive(*g);
   return modiff_add(residual, o_hat, sum_out, g->batch, g->cout, dd.ho * dd.wo, 0, stream);
@@ -666,7 +684,8 @@ extern "C" int modiff_igemm_conv(const int8_t* codes, const int8_t* wcodes, int 
                                  const float* bias, const modiff_conv_geom* g, int per_sample,
                                  int impl, int32_t* acc_out, void* stream) {
   return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                         bias, g, per_sample, impl, acc_out, nullptr, nullptr, stream);
+                         bias, g, per_sample, impl, acc_out, nullptr, nullptr, nullptr, nullptr,
+                         stream);
 }
 
 extern "C" int modiff_igemm_conv_add(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
@@ -678,7 +697,21 @@ extern "C" int modiff_igemm_conv_add(const int8_t* codes, const int8_t* wcodes, 
   MODIFF_CHECK_ARG((((uintptr_t)residual | (uintptr_t)sum_out) & 15) == 0,
                    "residual and sum must be 16-byte aligned");
   return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                         nullptr, g, 0, impl, nullptr, residual, sum_out, stream);
+                         nullptr, g, 0, impl, nullptr, residual, sum_out, nullptr, nullptr, stream);
+}
+
+extern "C" int modiff_igemm_conv_offset(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                                        const float* x_scale, const float* x_zp,
+                                        const float* w_scale, const int32_t* w_corr,
+                                        const int32_t* w_csum, float* o_hat, int accumulate,
+                                        const float* bias, const modiff_conv_geom* g, int impl,
+                                        const float* residual, float* sum_out, void* stream) {
+  MODIFF_CHECK_ARG(x_zp && w_csum, "NULL pointer argument");
+  MODIFF_CHECK_ARG((residual == nullptr) == (sum_out == nullptr), "residual and sum go together");
+  MODIFF_CHECK_ARG((((uintptr_t)residual | (uintptr_t)sum_out) & 15) == 0,
+                   "residual and sum must be 16-byte aligned");
+  return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                         bias, g, 0, impl, nullptr, residual, sum_out, x_zp, w_csum, stream);
 }
 
 extern "C" int modiff_device_status(int* status, int reset) {

@@ -1,5 +1,6 @@
 """Steady-state time of one UNet evaluation for the latent (LSUN-churches kl-8) and the SD-v1
-graphs, random-init weights, W8A8 modulated with symmetric dynamic activations.
+graphs, random-init weights, W8A8 modulated with symmetric (or, with --asym, asymmetric) dynamic
+activation quantisers.
 
     python -m modiff_b200.model_bench --model ldm --batch 32 --evals 12
     python -m modiff_b200.model_bench --model sd --batch 8 --evals 8     # guidance: 2x effective batch
@@ -27,6 +28,8 @@ def main():
     ap.add_argument("--evals", type=int, default=12)
     ap.add_argument("--w-bits", type=int, default=8)
     ap.add_argument("--a-bits", type=int, default=8)
+    ap.add_argument("--asym", action="store_true",
+                    help="asymmetric activation quantisers (the drivers' default without --a_sym)")
     ap.add_argument("--breakdown", action="store_true",
                     help="also time every entry point with CUDA events (eager; one more evaluation)")
     args = ap.parse_args()
@@ -40,7 +43,7 @@ def main():
     net = UNetModel(**cfg).eval()
     rerandomize_zero_tensors(net)
     wq = {'n_bits': args.w_bits, 'channel_wise': True, 'scale_method': 'max'}
-    aq = {'n_bits': args.a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+    aq = {'n_bits': args.a_bits, 'symmetric': not args.asym, 'channel_wise': False, 'scale_method': 'max',
           'leaf_param': True, 'dynamic': True}
     qnn = QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(dev).eval()
     qnn.set_quant_state(True, True)
@@ -80,7 +83,7 @@ def main():
         per_entry = {n: round(v["ms"], 2) for n, v in _lib.TIMER.summary().items()}
         _lib.TIMER = None
     print(json.dumps({"model": args.model, "per_entry_point_ms": per_entry, "batch": batch, "effective_batch": batch * (2 if sd else 1),
-                      "w_bits": args.w_bits, "a_bits": args.a_bits, "ms_per_eval": ms,
+                      "w_bits": args.w_bits, "a_bits": args.a_bits, "a_sym": not args.asym, "ms_per_eval": ms,
                       "evals_per_sample": n_evals,
                       "images_per_s": batch / (ms * n_evals / 1000.0),
                       "device_status": _lib.device_status()}))

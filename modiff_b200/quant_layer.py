@@ -196,7 +196,6 @@ class QuantModule(nn.Module):
         self._wpack = None
         self._org_kn = None
         self._loaded_act_scale = None   # (delta per segment, zero point per segment) to install
-        self._step_bias = None          # per-step output constant of offset (8-bit asymmetric) codes
         self.implicit_pad = (0, 0, 0, 0)   # extra (left, right, top, bottom) zero padding
 
     # ------------------------------------------------------------------ geometry
@@ -515,18 +514,6 @@ class QuantModule(nn.Module):
             _lib.call('modiff_codes_fill_halo', buf.codes.data_ptr(), buf.x_zp.data_ptr(),
                       C.byref(g), _lib.stream_ptr())
 
-    def _offset_codes_bias(self, buf, pack, bias, g):
-        """Per-step constant that takes the code offset back out of this layer's output; `buf`
-        is the buffer set the codes came from (another layer's when the quantiser is shared)."""
-        dev = buf.codes.device
-        if self._step_bias is None or self._step_bias.numel() != g.cout or \
-                self._step_bias.device != dev:
-            self._step_bias = _zeros(g.cout, torch.float32, dev)
-        _lib.call('modiff_asym_bias', buf.x_scale.data_ptr(), buf.x_zp.data_ptr(),
-                  pack['w_scale'].data_ptr(), pack['w_csum'].data_ptr(), _lib.ptr(bias),
-                  self._step_bias.data_ptr(), g.cout, 2 if g.split else 1, _lib.stream_ptr())
-        return self._step_bias
-
     def _use_im2col(self, g, buf):
         """Layers with very few input channels (the 3-channel input conv) run on the tensor
         cores as a dense K = cin*kh*kw GEMM over gathered codes."""
@@ -560,6 +547,9 @@ class QuantModule(nn.Module):
         _lib.call('modiff_im2col_codes', buf.codes.data_ptr(), buf.im2col.data_ptr(), C.byref(g),
                   128, _lib.stream_ptr())
         g2 = ConvGeom(g.batch, 128, g.cout, buf.ho, buf.wo, 1, 1, 1, 0, 0, 0, 0, 0)
+        if self._offset_codes():
+            return self._igemm_offset(buf.im2col, pack['wcodes_im2col'], buf, pack, o_hat,
+                                      accumulate, bias, g2, None, None)
         _lib.call('modiff_igemm_conv',
                   buf.im2col.data_ptr(), pack['wcodes_im2col'].data_ptr(), pack['with_sum'],
                   buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),
@@ -567,12 +557,25 @@ class QuantModule(nn.Module):
                   int(aq.channel_wise), self.igemm_impl, _lib.ptr(acc_out), _lib.stream_ptr(),
                   nbytes=(8 if accumulate else 4) * o_hat.numel(), tag=g.key())
 
+    def _igemm_offset(self, codes, wcodes, buf, pack, o_hat, accumulate, bias, g, residual, out):
+        """GEMM over offset (8-bit asymmetric, q - 128) codes; `buf` holds their scale and zero
+        point, `residual` / `out` optionally the block's residual sum."""
+        n_out = o_hat.numel()
+        _lib.call('modiff_igemm_conv_offset', codes.data_ptr(), wcodes.data_ptr(), pack['with_sum'],
+                  buf.x_scale.data_ptr(), buf.x_zp.data_ptr(), pack['w_scale'].data_ptr(),
+                  _lib.ptr(pack['w_corr']), pack['w_csum'].data_ptr(), o_hat.data_ptr(),
+                  int(accumulate), _lib.ptr(bias), C.byref(g), self.igemm_impl, _lib.ptr(residual),
+                  _lib.ptr(out), _lib.stream_ptr(),
+                  nbytes=((8 if accumulate else 4) + (8 if residual is not None else 0)) * n_out
+                  + g.batch * g.cin * g.h * g.w + g.cout * g.cin * g.kh * g.kw, tag=g.key())
+
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
-        if self._offset_codes():
-            bias = self._offset_codes_bias(buf, pack, bias, g)
         if self._use_im2col(g, buf):
             return self._igemm_im2col(buf, pack, o_hat, accumulate, bias, g, acc_out)
+        if self._offset_codes():
+            return self._igemm_offset(buf.codes, pack['wcodes'], buf, pack, o_hat, accumulate, bias,
+                                      g, None, None)
         # algorithmic bytes: o_hat read + write 8 per output element, 1 per input code, weights
         _lib.call('modiff_igemm_conv',
                   buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
@@ -594,7 +597,6 @@ class QuantModule(nn.Module):
         steady = (self.fuse_residual_add and self.modulate and self.use_act_quant
                   and self.use_weight_quant and not self.disable_act_quant
                   and self.a_hat is not None and self.o_hat is not None and self.split == 0
-                  and not self._offset_codes()
                   and self.fwd_func is F.conv2d and not self.act_quantizer.channel_wise
                   and self.activation_function.__class__.__name__ == "StraightThrough"
                   and torch.is_tensor(residual) and residual.is_cuda
@@ -615,6 +617,10 @@ class QuantModule(nn.Module):
         self._modq(x, self.a_hat, buf, g, src)
         residual = residual.contiguous()
         out = torch.empty_like(residual)
+        if self._offset_codes():
+            self._igemm_offset(buf.codes, pack['wcodes'], buf, pack, self.o_hat, True, None, g,
+                               residual, out)
+            return out
         _lib.call('modiff_igemm_conv_add',
                   buf.codes.data_ptr(), pack['wcodes'].data_ptr(), pack['with_sum'],
                   buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(), _lib.ptr(pack['w_corr']),

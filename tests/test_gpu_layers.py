@@ -393,3 +393,42 @@ def test_residual_sum_in_the_gemm_epilogue(cuda, cin, cout, hw, w_bits):
         assert torch.equal(fused, plain)
         assert torch.equal(mods[0].o_hat, mods[1].o_hat)
     assert m.device_status() == 0
+
+
+def test_offset_code_constant_as_bias_vector(cuda):
+    """The two ways of taking the offset of 8-bit asymmetric codes back out agree: inside the
+    GEMM's integer accumulator (`modiff_igemm_conv_offset`, what QuantModule uses) and as a
+    per-step bias vector (`modiff_asym_bias` + `modiff_igemm_conv`, for callers that cannot
+    change their GEMM call)."""
+    import ctypes as C
+    import modiff_b200 as m
+    from modiff_b200 import _lib
+    torch.manual_seed(41)
+    org = torch.nn.Conv2d(128, 128, 3, padding=1)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': False, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    mod = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
+    mod.set_quant_state(True, True)
+    mod.alias_output = False
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(2, 128, 16, 16, generator=g)
+    with torch.no_grad():
+        mod(x.to(cuda))
+        before = mod.o_hat.clone()
+        got = mod((x + 0.1 * torch.randn(x.shape, generator=g) + 0.05).to(cuda))
+    buf = next(iter(mod._geom_buffers.values()))
+    pack = mod._wpack
+    assert float(buf.x_zp[0]) != 128.0          # a real offset
+    bias = torch.zeros(128, device=cuda)
+    _lib.call('modiff_asym_bias', buf.x_scale.data_ptr(), buf.x_zp.data_ptr(),
+              pack['w_scale'].data_ptr(), pack['w_csum'].data_ptr(), None, bias.data_ptr(), 128, 1,
+              _lib.stream_ptr())
+    o = before.clone()
+    _lib.call('modiff_igemm_conv', buf.codes.data_ptr(), pack['wcodes'].data_ptr(),
+              pack['with_sum'], buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(),
+              _lib.ptr(pack['w_corr']), o.data_ptr(), 1, bias.data_ptr(), C.byref(buf.g), 0, 0, None,
+              _lib.stream_ptr())
+    torch.cuda.synchronize()
+    assert (o - got).abs().max() <= 2e-6 * got.abs().max()
+    assert m.device_status() == 0
