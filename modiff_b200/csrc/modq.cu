@@ -1840,6 +1840,51 @@ __global__ void codes_fill_halo_kernel(int8_t* __restrict__ codes, const float* 
   }
 }
 
+// stride 1: the padding cells are pad_t + pad_b full rows and pad_l + pad_r cells of every other
+// row, enumerated directly (one thread per 16 channels of a padding cell)
+__global__ void codes_fill_border_kernel(int8_t* __restrict__ codes, const float* __restrict__ x_zp,
+                                         modiff_conv_geom g, Derived d, int cells_per_image) {
+  const int pieces = d.cp / 16;
+  const int per_image = cells_per_image * pieces;
+  const int total = g.batch * per_image;
+  const int z0 = (int)x_zp[0] - 128;
+  const int z1 = g.split > 0 ? (int)x_zp[1] - 128 : z0;
+  const int rows_full = (g.pad_t + g.pad_b) * d.wp;
+  const int side = g.pad_l + g.pad_r;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int n = i / per_image;
+    int k = i - n * per_image;
+    const int piece = k % pieces;
+    k /= pieces;
+    int y, x;
+    if (k < rows_full) {
+      y = k / d.wp;
+      x = k - y * d.wp;
+      if (y >= g.pad_t) y += g.h;                 // bottom rows
+    } else {
+      k -= rows_full;
+      y = g.pad_t + k / side;
+      x = k % side;
+      if (x >= g.pad_l) x += g.w;                 // right columns
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int c = piece * 16 + 4 * q + b;
+        const int v = c < g.cin ? ((g.split > 0 && c >= g.split) ? z1 : z0) : 0;
+        word |= (uint32_t)(v & 0xff) << (8 * b);
+      }
+      w[q] = word;
+    }
+    const size_t cell = ((size_t)n * d.hp + y) * d.wp + x;
+    *reinterpret_cast<int4*>(codes + cell * d.cp + piece * 16) =
+        make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+  }
+}
+
 __global__ void asym_bias_kernel(const float* __restrict__ x_scale, const float* __restrict__ x_zp,
                                  const float* __restrict__ w_scale,
                                  const int32_t* __restrict__ w_csum,
@@ -1865,6 +1910,17 @@ extern "C" int modiff_codes_fill_halo(int8_t* codes, const float* x_zp, const mo
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   Derived d = derive(*g);
   if ((int64_t)d.nplanes * d.hp * d.wp == (int64_t)g->h * g->w) return MODIFF_OK;   // no padding cell
+  if (g->stride == 1) {
+    const int cells = d.hp * d.wp - g->h * g->w;
+    const int64_t n = (int64_t)g->batch * cells * (d.cp / 16);
+    if (n < (1ll << 31)) {
+      int nb = (int)ceil_div64(n, 256);
+      if (nb > 148 * 8) nb = 148 * 8;
+      codes_fill_border_kernel<<<nb, 256, 0, (cudaStream_t)stream>>>(codes, x_zp, *g, d, cells);
+      MODIFF_LAUNCH_CHECK("codes_fill_border_kernel");
+      return MODIFF_OK;
+    }
+  }
   const int64_t total = (int64_t)g->batch * d.nplanes * d.hp * d.wp * (d.cp / 16);
   int64_t blocks = ceil_div64(total, 256);
   if (blocks > 148 * 8) blocks = 148 * 8;

@@ -32,6 +32,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=int, default=_lib.IMPL_AUTO)
     ap.add_argument("--linear", action="store_true")
+    ap.add_argument("--static", action="store_true",
+                    help="non-dynamic activation quantiser: the scale of the first quantised call "
+                         "stays and later calls are the one-pass modiff_modq_fixed")
+    ap.add_argument("--asym", action="store_true", help="asymmetric activation codes")
     ap.add_argument("--fused", action="store_true",
                     help="feed the layer GroupNorm(32)+SiLU of the input as a lazy source")
     ap.add_argument("--pair", action="store_true",
@@ -104,8 +108,8 @@ def main():
         org = nn.Conv2d(args.cin, args.cout, args.k, stride=args.stride, padding=pad)
         shape = (args.batch, args.cin, args.hw, args.hw)
     wq = {'n_bits': args.w_bits, 'channel_wise': True, 'scale_method': 'max'}
-    aq = {'n_bits': args.a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
-          'leaf_param': True, 'dynamic': True}
+    aq = {'n_bits': args.a_bits, 'symmetric': not args.asym, 'channel_wise': False,
+          'scale_method': 'max', 'leaf_param': True, 'dynamic': not args.static}
     mod = QuantModule(org, wq, aq, modulate=True).to(dev)
     mod.set_quant_state(True, True)
     mod.igemm_impl = args.impl
@@ -134,8 +138,9 @@ def main():
         _lib.TIMER = None
     status = _lib.device_status()
     out = {"geometry": vars(args), "device_status": status}
-    for name in ("modiff_modq", "modiff_modq_src", "modiff_modq_gn", "modiff_groupnorm_silu",
-                 "modiff_igemm_conv"):
+    for name in ("modiff_modq", "modiff_modq_src", "modiff_modq_gn", "modiff_modq_fixed",
+                 "modiff_modq_asym", "modiff_codes_fill_halo", "modiff_groupnorm_silu",
+                 "modiff_igemm_conv", "modiff_igemm_conv_offset"):
         if name not in summ:
             continue
         v = summ[name]
