@@ -250,6 +250,14 @@ int modiff_modq_gn(const modiff_act_source* src, const float* film, const float*
                    int8_t* codes, float* x_scale, const modiff_conv_geom* g, int n_bits,
                    int per_sample, void* scratch, void* stream);
 
+/* modiff_modq_gn with asymmetric codes (modiff_modq_asym's arithmetic, per-tensor scales): the
+ * GroupNorm statistics and the residual's minimum / maximum come from one sweep.  x_zp as in
+ * modiff_modq_asym; n_bits == 8 stores q - 128 (see there). */
+int modiff_modq_gn_asym(const modiff_act_source* src, const float* film, const float* gamma,
+                        const float* beta, int groups, float eps, float* affine, float* a_hat,
+                        int8_t* codes, float* x_scale, float* x_zp, const modiff_conv_geom* g,
+                        int n_bits, void* scratch, void* stream);
+
 /* One launch for several modulated linear layers that read the same activation codes (every
  * residual block's projection of swish(temb): ddim/models/diffusion.py:121-123, 297-301;
  * ldm/modules/diffusionmodules/openaimodel.py:236-262): for each item

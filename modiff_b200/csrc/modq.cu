@@ -763,14 +763,18 @@ struct SecondQuantiser {
   float* x_scale;
 };
 
-template <int NV, bool DUAL>
+// ASYM (never with DUAL or per_sample): the sweep tracks the residual's true minimum and maximum
+// per scale segment instead of its largest magnitude (m0 / m1 hold the maxima, r0 / r1 the
+// minima) and the last block derives delta and the zero point (finalise_ranges); `n_levels`
+// then carries n_bits.
+template <int NV, bool DUAL, bool ASYM = false>
 __global__ void __launch_bounds__(512, NV <= 4 ? 2 : 1)
 gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __restrict__ affine,
                  const float* __restrict__ gamma, const float* __restrict__ beta,
                  const float* __restrict__ a_hat, int batch, int c, int hw, int groups, float eps,
                  int lg_hw4, int split, int n_levels, int per_sample, int slots,
                  ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
-                 const SecondQuantiser second) {
+                 const SecondQuantiser second, float* __restrict__ x_zp = nullptr) {
   __shared__ float sh[64];
   __shared__ float2 tab[kGnMaxCpg];
   __shared__ float bias_sh[kGnMaxCpg];
@@ -782,8 +786,9 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
   const int items = batch * groups;
   const bool has_bias = src.bias != nullptr;
 
-  float m0 = 0.0f, m1 = 0.0f;
-  float r0 = 0.0f, r1 = 0.0f;     // second quantiser: raw residual maxima of its two segments
+  float m0 = ASYM ? -INFINITY : 0.0f, m1 = m0;
+  float r0 = ASYM ? INFINITY : 0.0f, r1 = r0;   // second quantiser: raw residual maxima of its
+                                                // two segments (ASYM: this quantiser's minima)
   int cur_n = -1;
   // (image, group) of the current item, advanced without divisions
   const int n_step = gridDim.x / groups, g_step = gridDim.x % groups;
@@ -902,7 +907,7 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
       reinterpret_cast<float2*>(affine)[(size_t)n * c + ch] = make_float2(ga, sf);
     }
     __syncthreads();
-    float mi = 0.0f;
+    float mi = ASYM ? -INFINITY : 0.0f, mlo = INFINITY;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
@@ -913,11 +918,24 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
         if (src.silu) {
           v0 = silu_f(v0); v1 = silu_f(v1); v2 = silu_f(v2); v3 = silu_f(v3);
         }
-        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v0, av[k].x))), fabsf(__fsub_rn(v1, av[k].y)));
-        mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v2, av[k].z))), fabsf(__fsub_rn(v3, av[k].w)));
+        if (ASYM) {
+          const float d0 = __fsub_rn(v0, av[k].x), d1 = __fsub_rn(v1, av[k].y),
+                      d2 = __fsub_rn(v2, av[k].z), d3 = __fsub_rn(v3, av[k].w);
+          mi = fmaxf(fmaxf(fmaxf(mi, d0), d1), fmaxf(d2, d3));
+          mlo = fminf(fminf(fminf(mlo, d0), d1), fminf(d2, d3));
+        } else {
+          mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v0, av[k].x))), fabsf(__fsub_rn(v1, av[k].y)));
+          mi = fmaxf(fmaxf(mi, fabsf(__fsub_rn(v2, av[k].z))), fabsf(__fsub_rn(v3, av[k].w)));
+        }
       }
     }
-    if (split > 0 && cbeg >= split) m1 = fmaxf(m1, mi); else m0 = fmaxf(m0, mi);
+    if (split > 0 && cbeg >= split) {
+      m1 = fmaxf(m1, mi);
+      if (ASYM) r1 = fminf(r1, mlo);
+    } else {
+      m0 = fmaxf(m0, mi);
+      if (ASYM) r0 = fminf(r0, mlo);
+    }
     __syncthreads();   // tab and bias_sh are rewritten by the next slab
   }
   for (int o = 16; o > 0; o >>= 1) {
@@ -931,10 +949,16 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
       r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
     }
   }
+  if (ASYM) {
+    for (int o = 16; o > 0; o >>= 1) {
+      r0 = fminf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
+      r1 = fminf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
+    }
+  }
   if ((threadIdx.x & 31) == 0) {
     s0[threadIdx.x >> 5] = m0;
     s1[threadIdx.x >> 5] = m1;
-    if (DUAL) {
+    if (DUAL || ASYM) {
       s2[threadIdx.x >> 5] = r0;
       s3[threadIdx.x >> 5] = r1;
     }
@@ -948,10 +972,20 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
         r0 = fmaxf(r0, s2[i]);
         r1 = fmaxf(r1, s3[i]);
       }
+      if (ASYM) {
+        r0 = fminf(r0, s2[i]);
+        r1 = fminf(r1, s3[i]);
+      }
     }
     const int slot0 = per_sample ? (cur_n < 0 ? 0 : cur_n) : 0;
-    if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
-    if (split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    if (ASYM) {
+      // a block that saw no element of a segment still holds the initial (+inf, -inf) pair
+      if (m0 >= r0) publish_range(scratch, 0, r0, m0);
+      if (split > 0 && m1 >= r1) publish_range(scratch, 1, r1, m1);
+    } else {
+      if (m0 > 0.0f) atomicMax(&scratch->absmax_bits[slot0], __float_as_uint(m0));
+      if (split > 0 && m1 > 0.0f) atomicMax(&scratch->absmax_bits[1], __float_as_uint(m1));
+    }
     if (DUAL) {
       if (r0 > 0.0f) atomicMax(&second.scratch->absmax_bits[0], __float_as_uint(r0));
       if (second.split > 0 && r1 > 0.0f)
@@ -964,11 +998,15 @@ gn_absmax_kernel(const SrcView src, const float* __restrict__ film, float* __res
   __syncthreads();
   if (is_last) {
     __threadfence();
-    for (int sl = threadIdx.x; sl < slots; sl += blockDim.x) {
-      const unsigned int bits = atomicExch(&scratch->absmax_bits[sl], 0u);
-      double delta = (double)__uint_as_float(bits) / (double)n_levels;
-      if (delta < 1e-8) delta = 1e-8;
-      x_scale[sl] = (float)delta;
+    if (ASYM) {
+      finalise_ranges(scratch, slots, n_levels, 0, x_scale, x_zp);   // n_levels carries n_bits
+    } else {
+      for (int sl = threadIdx.x; sl < slots; sl += blockDim.x) {
+        const unsigned int bits = atomicExch(&scratch->absmax_bits[sl], 0u);
+        double delta = (double)__uint_as_float(bits) / (double)n_levels;
+        if (delta < 1e-8) delta = 1e-8;
+        x_scale[sl] = (float)delta;
+      }
     }
     if (DUAL) {
       const int slots2 = second.split > 0 ? 2 : 1;
@@ -1541,6 +1579,69 @@ extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, c
   v.bias = nullptr;
   v.affine = affine;
   return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true, s);
+}
+
+extern "C" int modiff_modq_gn_asym(const modiff_act_source* src, const float* film,
+                                   const float* gamma, const float* beta, int groups, float eps,
+                                   float* affine, float* a_hat, int8_t* codes, float* x_scale,
+                                   float* x_zp, const modiff_conv_geom* g, int n_bits, void* scratch,
+                                   void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && gamma && beta && affine && codes && x_scale && x_zp && scratch,
+                   "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  MODIFF_CHECK_ARG(groups > 0 && g->cin % groups == 0, "bad GroupNorm shape: c=%d groups=%d",
+                   g->cin, groups);
+  MODIFF_CHECK_ARG(((uintptr_t)affine & 7) == 0, "affine table must be 8-byte aligned");
+  MODIFF_CHECK_ARG(src->affine == nullptr || src->affine == affine,
+                   "src->affine must be NULL or the table this call writes");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int hw = g->h * g->w;
+  const int cpg = g->cin / groups;
+  const int count = cpg * hw;
+  const int threads = groupnorm_threads(count);
+  const int lg_hw4 = groupnorm_lg_hw4(hw);
+  const int nv = lg_hw4 >= 0 ? ceil_div(count / 4, threads) : 0;
+  const bool aligned = ((((uintptr_t)src->x0 | (uintptr_t)src->x1 | (uintptr_t)a_hat) & 15) == 0);
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  const int slots = derive(*g).nseg;
+  const bool whole = (src->c0 % cpg == 0) && (g->split % cpg == 0);
+  if (lg_hw4 >= 0 && threads >= 256 && nv <= 8 && cpg <= kGnMaxCpg && aligned && whole) {
+    v.bias = src->chan_bias;
+    v.affine = nullptr;
+    const int items = g->batch * groups;
+    const int per_sm = threads >= 512 ? 2 : 4;
+    const int blocks = items < 148 * per_sm ? items : 148 * per_sm;
+#define MODIFF_GN_RANGE(NV)                                                                       \
+  gn_absmax_kernel<NV, false, true><<<blocks, threads, 0, s>>>(                                    \
+      v, film, affine, gamma, beta, a_hat, g->batch, g->cin, hw, groups, eps, lg_hw4, g->split,    \
+      n_bits, 0, slots, (ModqScratch*)scratch, x_scale, SecondQuantiser{}, x_zp)
+    if (nv <= 1) MODIFF_GN_RANGE(1);
+    else if (nv <= 2) MODIFF_GN_RANGE(2);
+    else if (nv <= 4) MODIFF_GN_RANGE(4);
+    else MODIFF_GN_RANGE(8);
+#undef MODIFF_GN_RANGE
+    MODIFF_LAUNCH_CHECK("gn_absmax_kernel (range)");
+    v.bias = nullptr;
+    v.affine = affine;
+    return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, 0, scratch, false, s, x_zp);
+  }
+  // small or odd slabs: statistics pass, then the range and encode passes
+  rc = modiff_groupnorm_silu(src->x0, src->x1, src->c0, src->chan_bias, film, nullptr, affine, gamma,
+                             beta, g->batch, g->cin, hw, groups, eps, 0, stream);
+  if (rc) return rc;
+  v.bias = nullptr;
+  v.affine = affine;
+  return launch_modq_src(v, true, a_hat, codes, x_scale, g, n_bits, 0, scratch, true, s, x_zp);
 }
 
 extern "C" int modiff_modq_pair(const modiff_act_source* src, const float* gamma, const float* beta,

@@ -472,6 +472,18 @@ class QuantModule(nn.Module):
                 raise ModiffError("8-bit asymmetric activation codes are stored offset by one zero "
                                   "point per tensor; per-sample (--act_tensor) scales need --a_sym "
                                   "or at most 7 bits")
+            if src is not None and src.pending_norm() and self.fuse_norm_stats and \
+                    not aq.channel_wise:
+                nrm = src.norm
+                raw, table = src.raw_struct()
+                _lib.call('modiff_modq_gn_asym', C.byref(raw), _lib.ptr(src.film),
+                          nrm.weight.data_ptr(), nrm.bias.data_ptr(), nrm.num_groups,
+                          float(nrm.eps), table.data_ptr(), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                          buf.x_scale.data_ptr(), buf.x_zp.data_ptr(), C.byref(g), aq.n_bits,
+                          buf.scratch.data_ptr(), _lib.stream_ptr(), nbytes=13 * src.numel(),
+                          tag=g.key())
+                self._offset_codes_halo(buf, g)
+                return
             if src is not None:
                 st = src.struct()
             else:

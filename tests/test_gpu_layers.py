@@ -126,7 +126,8 @@ def test_module_modes_and_errors(cuda):
     (320, 0, 64, True, False, 0, 8),      # 10 x 4096 per group: statistics as their own pass
     (96, 0, 6, False, False, 0, 8),       # h*w/4 not a power of two: statistics as their own pass
 ])
-def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, split, a_bits):
+@pytest.mark.parametrize("a_sym", [True, False], ids=["sym", "asym"])
+def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, split, a_bits, a_sym):
     """GroupNorm -> SiLU -> conv with the normalisation read lazily by the quantiser
     (qdiff/quant_block.py:279-306): the one-sweep statistics + residual-maximum kernel gives
     the same scale, cache and output bits as the separate statistics pass, and both follow
@@ -141,10 +142,10 @@ def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, spli
         norm.weight.uniform_(0.5, 1.5)
         norm.bias.uniform_(-0.5, 0.5)
     wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
-    aq = {'n_bits': a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+    aq = {'n_bits': a_bits, 'symmetric': a_sym, 'channel_wise': False, 'scale_method': 'max',
           'leaf_param': True, 'dynamic': True}
     w, b = org.weight.detach().clone(), org.bias.detach().clone()
-    orc = oracle.OracleQuantModule(w, b, 1, 1, 8, a_bits)
+    orc = oracle.OracleQuantModule(w, b, 1, 1, 8, a_bits, a_sym)
     mods = []
     for fuse in (True, False):
         q = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
@@ -179,6 +180,9 @@ def test_norm_statistics_inside_the_quantiser(cuda, c0, c1, hw, bias, film, spli
             assert torch.equal(mods[0].a_hat, mods[1].a_hat)
             assert torch.equal(outs[0], outs[1])
             assert float(mods[0].act_quantizer.delta) == float(mods[1].act_quantizer.delta)
+            if not a_sym:
+                assert float(mods[0].act_quantizer.zero_point) == \
+                    float(mods[1].act_quantizer.zero_point)
         err = (outs[0].cpu() - ref).abs().max() / ref.abs().max()
         # 8-bit codes of a residual: one code on the other side of a rounding boundary moves the
         # output by ~1e-3 of its range, 4-bit codes by ~1e-2
