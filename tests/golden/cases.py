@@ -177,6 +177,9 @@ SD_CASES = [
     # first `evals` of the 50 DDIM evaluations
     dict(name="sd_w8a8_b1", w_bits=8, a_bits=8, batch=1, latent=64, ddim_steps=50, evals=3,
          guidance=7.5, noise_seed=21, zero_seed=1234),
+    # the txt2img driver's default quantiser (no --a_sym): asymmetric 8-bit activations
+    dict(name="sd_w8a8_asym_b1", w_bits=8, a_bits=8, a_sym=False, batch=1, latent=64, ddim_steps=50,
+         evals=2, guidance=7.5, noise_seed=22, zero_seed=1234),
 ]
 
 

@@ -56,9 +56,9 @@ def test_oracle_matches_reference_first_eval(golden_sd):
 
 
 @pytest.mark.gpu
-def test_cuda_path_matches_reference(cuda, golden_sd):
+@pytest.mark.parametrize("c", cases.SD_CASES, ids=lambda c: c["name"])
+def test_cuda_path_matches_reference(c, cuda, golden_sd):
     import modiff_b200 as m
-    c = cases.SD_CASES[0]
     net = _build()
     wq, aq = cases.quant_params(c)
     qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(cuda).eval()
