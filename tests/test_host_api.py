@@ -216,3 +216,56 @@ def test_reciprocal_multiply_with_tie_guard_equals_division():
                 r = np.nextafter(r, f32(np.inf) if step > 0 else f32(-np.inf)).astype(f32)
             got, _ = fast(r, d[:, None], lo, hi)
             assert np.array_equal(got, reference(r, d[:, None], lo, hi)), (bits, step)
+
+
+def test_calibrated_scale_validation():
+    """`load_act_scale` (what a checkpoint's act_quantizer.delta / zero_point become) checks what
+    the int8 code planes can hold before anything reaches the GPU."""
+    def layer(bits, sym, per_sample=False):
+        aq = {'n_bits': bits, 'symmetric': sym, 'channel_wise': per_sample, 'scale_method': 'max',
+              'leaf_param': True, 'dynamic': False}
+        return m.QuantModule(nn.Conv2d(16, 16, 3, padding=1),
+                             {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}, aq,
+                             modulate=True)
+    layer(8, True).load_act_scale(0.01)                       # symmetric: zero point 0
+    layer(8, False).load_act_scale(0.01, 255)                 # 8-bit asymmetric: planes hold q - 128
+    layer(6, False).load_act_scale([0.01], [63])
+    with pytest.raises(m.ModiffError):
+        layer(8, True).load_act_scale(0.01, 3)                # symmetric with a zero point
+    with pytest.raises(m.ModiffError):
+        layer(6, False).load_act_scale(0.01, 129)             # centred 6-bit code leaves int8
+    with pytest.raises(m.ModiffError):
+        layer(8, False).load_act_scale(0.01, 256)
+    with pytest.raises(m.ModiffError):
+        layer(8, False).load_act_scale(0.01, 12.5)            # not an integer
+    with pytest.raises(m.ModiffError):
+        layer(8, True).load_act_scale(0.0)                    # scale must be positive
+    with pytest.raises(m.ModiffError):
+        layer(8, True).load_act_scale([0.1, 0.2, 0.3])
+    with pytest.raises(m.ModiffError):
+        layer(8, True, per_sample=True).load_act_scale(0.01)  # calibrated scales are per tensor
+
+
+def test_checkpoint_key_routing(qnn):
+    """Quantiser tensors are told from ordinary parameters by their last two name parts; a key
+    that points at no quantised layer is an error, as with strict loading in the reference."""
+    from modiff_b200.utils import _split_key, load_calibrated_state
+    assert _split_key("model.down.0.block.0.conv1.weight_quantizer.alpha") == \
+        ("model.down.0.block.0.conv1", "weight_quantizer", "alpha")
+    assert _split_key("model.up.1.block.0.nin_shortcut.act_quantizer_0.zero_point") == \
+        ("model.up.1.block.0.nin_shortcut", "act_quantizer_0", "zero_point")
+    assert _split_key("model.down.0.block.0.conv1.weight") is None
+    assert _split_key("model.mid.attn_1.act_quantizer_w.delta") is None
+    with pytest.raises(m.ModiffError):
+        load_calibrated_state(qnn, {"model.nowhere.weight_quantizer.alpha": torch.zeros(1)})
+    with pytest.raises(m.ModiffError):      # layer exists, but was not converted to AdaRound
+        load_calibrated_state(qnn, {"model.conv_in.weight_quantizer.alpha": torch.zeros(1)})
+
+
+def test_flag_setters_invalidate_captured_graphs(qnn):
+    e0 = getattr(qnn, "_config_epoch", 0)
+    qnn.set_dynamic_state(False)
+    qnn.set_quant_state(True, True)
+    qnn.set_modulation(True)
+    assert qnn._config_epoch == e0 + 3
+    qnn.set_dynamic_state(True)
