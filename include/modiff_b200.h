@@ -258,6 +258,17 @@ int modiff_modq_gn_asym(const modiff_act_source* src, const float* film, const f
                         int8_t* codes, float* x_scale, float* x_zp, const modiff_conv_geom* g,
                         int n_bits, void* scratch, void* stream);
 
+/* modiff_modq for a layer whose input is the nearest-neighbour 2x upsample of x (the conv of
+ * `Upsample`: ddim/models/diffusion.py:45-51, ldm/modules/diffusionmodules/openaimodel.py:105-115,
+ * followed by qdiff/quant_layer.py:325-336).  The upsampled input, the cached input and so the
+ * residual repeat every value in 2x2 blocks; the quantiser therefore runs on the SOURCE tensor and
+ * writes each code to its four cells.  Same scale, codes and cache values as upsampling first.
+ *   x, a_hat  fp32 [batch][cin][h/2][w/2]; a_hat is the cache AT SOURCE RESOLUTION, updated in place
+ *   g         the convolution's geometry (h, w the upsampled size; stride 1, no split)
+ *   codes, x_scale, scratch  as for modiff_modq (symmetric per-tensor scale) */
+int modiff_modq_up2(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                    const modiff_conv_geom* g, int n_bits, void* scratch, void* stream);
+
 /* One launch for several modulated linear layers that read the same activation codes (every
  * residual block's projection of swish(temb): ddim/models/diffusion.py:121-123, 297-301;
  * ldm/modules/diffusionmodules/openaimodel.py:236-262): for each item

@@ -238,14 +238,17 @@ modq_absmax_kernel(const SrcView src, const float* __restrict__ a_hat,
   }
 }
 
-template <bool VEC4, bool XFORM>
+// UP2: the layer's input is the nearest-neighbour 2x upsample of `src` (g is the convolution's
+// geometry at the doubled size, stride 1).  Input, cache and residual then repeat every value in
+// 2x2 blocks, so the quantiser works at the source resolution and writes each code four times.
+template <bool VEC4, bool XFORM, bool UP2 = false>
 __global__ void __launch_bounds__(kThreads)
 modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
                    int8_t* __restrict__ codes, const float* __restrict__ x_scale,
                    const float* __restrict__ x_zp, modiff_conv_geom g, Derived d, TileGrid tg,
                    int n_levels, int per_sample) {
   __shared__ uint32_t tile_sh[kTileP][kTileC / 4 + 1];
-  const int hw = g.h * g.w;
+  const int hw = UP2 ? (g.h >> 1) * (g.w >> 1) : g.h * g.w;
   const int cg = threadIdx.x >> 4;
   const int pq = threadIdx.x & 15;
   const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
@@ -302,14 +305,25 @@ modq_encode_kernel(const SrcView src, float* __restrict__ a_hat,
     const int cbase = c0 + 16 * piece;
     if (pp < hw && cbase < d.cp) {
       int y, xq, ys, xs;
-      y = tg.by_w.divmod(pp, xq);
-      const int yq = tg.by_stride.divmod(y + g.pad_t, ys);
-      const int xqq = tg.by_stride.divmod(xq + g.pad_l, xs);
-      const int plane = ys * g.stride + xs;
-      const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + yq) * d.wp + xqq;
+      y = tg.by_w.divmod(pp, xq);          // UP2: by_w divides by the source width
       int4 v = make_int4(tile_sh[px][4 * piece], tile_sh[px][4 * piece + 1],
                          tile_sh[px][4 * piece + 2], tile_sh[px][4 * piece + 3]);
-      *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+      if (UP2) {
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy)
+#pragma unroll
+          for (int dx = 0; dx < 2; ++dx) {
+            const size_t pix = ((size_t)n * d.hp + (2 * y + dy + g.pad_t)) * d.wp +
+                               (2 * xq + dx + g.pad_l);
+            *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+          }
+      } else {
+        const int yq = tg.by_stride.divmod(y + g.pad_t, ys);
+        const int xqq = tg.by_stride.divmod(xq + g.pad_l, xs);
+        const int plane = ys * g.stride + xs;
+        const size_t pix = (((size_t)n * d.nplanes + plane) * d.hp + yq) * d.wp + xqq;
+        *reinterpret_cast<int4*>(codes + pix * d.cp + cbase) = v;
+      }
     }
     __syncthreads();
   }
@@ -1489,6 +1503,54 @@ extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_
   const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
   return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                          (cudaStream_t)stream);
+}
+
+extern "C" int modiff_modq_up2(const float* x, float* a_hat, int8_t* codes, float* x_scale,
+                               const modiff_conv_geom* g, int n_bits, void* scratch, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(x && a_hat && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(g->stride == 1 && g->split == 0 && g->h % 2 == 0 && g->w % 2 == 0,
+                   "upsampled input needs stride 1, no split and even h, w (got %d x %d)", g->h, g->w);
+  cudaStream_t s = (cudaStream_t)stream;
+  Derived d = derive(*g);
+  modiff_conv_geom gs = *g;          // the source tensor as a layer input of its own
+  gs.h = g->h / 2;
+  gs.w = g->w / 2;
+  const int hw = gs.h * gs.w;
+  const int n_levels = sym_levels(n_bits);
+  SrcView v = {};
+  v.x0 = x;
+  v.c0 = g->cin;
+  TileGrid tg;
+  tg.pb = ceil_div(hw, kTileP);
+  tg.cb = ceil_div(g->cin, kTileC);
+  tg.per_image = FastDiv(tg.pb * tg.cb);
+  tg.by_pb = FastDiv(tg.pb);
+  tg.by_w = FastDiv(gs.w);
+  tg.by_stride = FastDiv(1);
+  const int64_t total = (int64_t)tg.pb * tg.cb * g->batch;
+  if (total >= (1ll << 31)) return set_error(MODIFF_ERR_INVALID, "activation tensor too large");
+  tg.total = (int)total;
+  const int blocks = tg.total < 148 * 8 ? tg.total : 148 * 8;
+  const bool vec = (hw % 4 == 0) && ((((uintptr_t)x | (uintptr_t)a_hat) & 15) == 0);
+  if (vec) {
+    modq_absmax_kernel<true, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
+                                                               (ModqScratch*)scratch, x_scale);
+    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    modq_encode_kernel<true, false, true><<<blocks, kThreads, 0, s>>>(v, a_hat, codes, x_scale,
+                                                                     nullptr, *g, d, tg, n_levels, 0);
+  } else {
+    modq_absmax_kernel<false, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
+                                                                (ModqScratch*)scratch, x_scale);
+    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    modq_encode_kernel<false, false, true><<<blocks, kThreads, 0, s>>>(v, a_hat, codes, x_scale,
+                                                                      nullptr, *g, d, tg, n_levels, 0);
+  }
+  MODIFF_LAUNCH_CHECK("modq_encode_kernel (upsampled input)");
+  return MODIFF_OK;
 }
 
 extern "C" int modiff_modq_gn(const modiff_act_source* src, const float* film, const float* gamma,

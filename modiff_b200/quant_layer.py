@@ -196,6 +196,7 @@ class QuantModule(nn.Module):
         self._wpack = None
         self._org_kn = None
         self._loaded_act_scale = None   # (delta per segment, zero point per segment) to install
+        self._a_hat_half = False        # a_hat held at the input resolution of an Upsample block
         self.implicit_pad = (0, 0, 0, 0)   # extra (left, right, top, bottom) zero padding
 
     # ------------------------------------------------------------------ geometry
@@ -642,6 +643,59 @@ class QuantModule(nn.Module):
                   + g.cout * g.cin * g.kh * g.kw, tag=g.key())
         return out
 
+    # ------------------------------------------------------------------ upsampled input
+    upsampled_input_fusion = os.environ.get("MODIFF_FUSE_UPSAMPLE", "1") != "0"
+
+    def forward_upsampled(self, x):
+        """`self(upsample2x(x))` for the convolution of an `Upsample` block
+        (ddim/models/diffusion.py:45-51).  In the steady modulated state the upsampled tensor is
+        never written: input, cached input and residual repeat every value in 2x2 blocks, so the
+        quantiser runs on `x` itself and writes each code four times (`modiff_modq_up2`).  The
+        cache `a_hat` of such a layer is kept at the resolution of `x` (each value stands for its
+        2x2 block); scale, codes and output are those of the ordinary path."""
+        from .ops import upsample2x
+        aq = self.act_quantizer
+        k = self.fwd_kwargs
+        ok = (self.upsampled_input_fusion and self.modulate and self.use_act_quant
+              and self.use_weight_quant and not self.disable_act_quant and self.split == 0
+              and self.fwd_func is F.conv2d and aq.sym and aq.dynamic and not aq.channel_wise
+              and not aq.running_stat and torch.is_tensor(x) and x.is_cuda
+              and x.dtype == torch.float32 and x.dim() == 4 and tuple(k['stride']) == (1, 1)
+              and self.weight.shape[1] >= 16)
+        if not ok:
+            if self._a_hat_half and self.a_hat is not None:
+                raise ModiffError("this layer's cache is held at the resolution of its upsample "
+                                  "block's input; call reset_cache() before changing its mode")
+            return self.forward(upsample2x(x))
+        x = x.contiguous()
+        b, c, h, w = x.shape
+        g = self._geom(torch.empty((b, c, 2 * h, 2 * w), device='meta'), 0)
+        ho_wo = _lib.out_hw(g)
+        out_shape = (g.batch, g.cout, ho_wo[0], ho_wo[1])
+        pack = self._pack_weights(g)
+        buf = self._get_buffers(g, x.device)
+        if self.a_hat is None:
+            # first step: unquantised activations (quant_layer.py:326-327, 358-359)
+            self._a_store = self._reuse(self._a_store, x.shape, x.device)
+            self._a_store.copy_(x)
+            self.a_hat = self._a_store
+            self._a_hat_half = True
+            self._o_store = self._reuse(self._o_store, out_shape, x.device)
+            self._conv_first_step(upsample2x(x), pack, self.bias, g, self._o_store, ho_wo)
+            self.o_hat = self._o_store
+        else:
+            if not self._a_hat_half or tuple(self.a_hat.shape) != tuple(x.shape):
+                raise ModiffError(f"input shape {tuple(x.shape)} does not match the cached "
+                                  f"{tuple(self.a_hat.shape)}; call reset_cache() first")
+            n = x.numel()
+            # algorithmic bytes per SOURCE element: x 4 + a_hat read/write 8 + four codes
+            _lib.call('modiff_modq_up2', x.data_ptr(), self.a_hat.data_ptr(), buf.codes.data_ptr(),
+                      buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, buf.scratch.data_ptr(),
+                      _lib.stream_ptr(), nbytes=16 * n, tag=g.key())
+            self._igemm(buf, pack, self.o_hat, True, None, g)
+        out = self.o_hat if self.alias_output else self.o_hat.clone()
+        return self.activation_function(out)
+
     def forward_shared(self, owner, input):
         """Forward of a layer whose input equals `owner`'s input at every step (the k and v
         projections next to q in an attention block): the residual codes, their scale and the
@@ -874,6 +928,7 @@ class QuantModule(nn.Module):
     def reset_cache(self):
         self.a_hat = None
         self.o_hat = None
+        self._a_hat_half = False
 
     def set_split(self):
         self.weight_quantizer_0 = UniformAffineQuantizer(**self.weight_quant_params)

@@ -436,3 +436,51 @@ def test_offset_code_constant_as_bias_vector(cuda):
     torch.cuda.synchronize()
     assert (o - got).abs().max() <= 2e-6 * got.abs().max()
     assert m.device_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout,hw,w_bits,a_bits", [
+    (128, 128, 16, 4, 4),       # 16x16 -> 32x32: activation-reuse GEMM on the doubled size
+    (256, 256, 4, 8, 8),        # 4x4 -> 8x8
+    (64, 32, 6, 8, 8),          # odd source size (scalar loads), small channel counts
+])
+def test_quantiser_of_an_upsampled_input(cuda, cin, cout, hw, w_bits, a_bits):
+    """The convolution of an Upsample block (ddim/models/diffusion.py:45-51): quantising at the
+    source resolution and writing every code to its 2x2 block gives the same scale, the same
+    output bits and - upsampled - the same cache as running the layer on the upsampled tensor."""
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(51)
+    org = torch.nn.Conv2d(cin, cout, 3, padding=1)
+    wq = {'n_bits': w_bits, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    fused = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
+    plain = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
+    for q in (fused, plain):
+        q.set_quant_state(True, True)
+        q.alias_output = False
+    g = torch.Generator().manual_seed(52)
+    x = torch.randn(3, cin, hw, hw, generator=g)
+    before = _lib_launches()
+    with torch.no_grad():
+        for step in range(4):
+            xs = (x + 0.07 * step * torch.randn(x.shape, generator=g)).to(cuda)
+            a = fused.forward_upsampled(xs)
+            b = plain(ops.upsample2x(xs))
+            assert torch.equal(a, b), step
+            assert tuple(fused.a_hat.shape) == tuple(xs.shape)
+            assert torch.equal(ops.upsample2x(fused.a_hat), plain.a_hat), step
+            if step:
+                assert float(fused.act_quantizer.delta) == float(plain.act_quantizer.delta)
+    assert _lib_launches() > before
+    # the ordinary call on such a layer reports the cache mismatch instead of mixing resolutions
+    with pytest.raises(m.ModiffError):
+        fused(ops.upsample2x(x.to(cuda)))
+    fused.reset_cache()
+    fused(ops.upsample2x(x.to(cuda)))
+    assert m.device_status() == 0
+
+
+def _lib_launches():
+    from modiff_b200 import _lib
+    return _lib.LAUNCHES[0]
