@@ -265,9 +265,12 @@ int modiff_modq_gn_asym(const modiff_act_source* src, const float* film, const f
  * writes each code to its four cells.  Same scale, codes and cache values as upsampling first.
  *   x, a_hat  fp32 [batch][cin][h/2][w/2]; a_hat is the cache AT SOURCE RESOLUTION, updated in place
  *   g         the convolution's geometry (h, w the upsampled size; stride 1, no split)
- *   codes, x_scale, scratch  as for modiff_modq (symmetric per-tensor scale) */
+ *   codes, x_scale, scratch  as for modiff_modq (symmetric per-tensor scale)
+ *   fixed_scale  non-zero: x_scale[0] is read, not measured (a non-dynamic quantiser, see
+ *                modiff_modq_fixed); scratch may then be NULL */
 int modiff_modq_up2(const float* x, float* a_hat, int8_t* codes, float* x_scale,
-                    const modiff_conv_geom* g, int n_bits, void* scratch, void* stream);
+                    const modiff_conv_geom* g, int n_bits, int fixed_scale, void* scratch,
+                    void* stream);
 
 /* One launch for several modulated linear layers that read the same activation codes (every
  * residual block's projection of swish(temb): ddim/models/diffusion.py:121-123, 297-301;

@@ -89,7 +89,7 @@ SIGNATURES = {
                                  _P, _P, _G, C.c_int, C.c_int, _P, _P]),
     "modiff_modq_gn_asym": (C.c_int, [C.POINTER(ActSourceStruct), _P, _P, _P, C.c_int, C.c_float, _P,
                                       _P, _P, _P, _P, _G, C.c_int, _P, _P]),
-    "modiff_modq_up2": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, _P, _P]),
+    "modiff_modq_up2": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P, _P]),
     "modiff_modq_static": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P]),
     "modiff_attention_tc": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                       C.c_int, C.c_int, C.c_float, _P]),

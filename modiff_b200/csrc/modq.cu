@@ -51,10 +51,6 @@ __device__ inline void store4(float* __restrict__ base, int p, int hw, const flo
   }
 }
 
-__device__ inline void prefetch_l2(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
-
 // clamp(rne(t), lo, hi) for integer lo, hi with |lo|, |hi| < 2^22, without the conversion pipe:
 // clamping first gives the same result (rne is monotonic and keeps integers), and adding
 // 1.5 * 2^23 rounds to nearest-even at unit spacing.  The low byte of the sum's bit pattern is
@@ -1506,10 +1502,12 @@ extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_
 }
 
 extern "C" int modiff_modq_up2(const float* x, float* a_hat, int8_t* codes, float* x_scale,
-                               const modiff_conv_geom* g, int n_bits, void* scratch, void* stream) {
+                               const modiff_conv_geom* g, int n_bits, int fixed_scale, void* scratch,
+                               void* stream) {
   int rc = validate_geom(g);
   if (rc) return rc;
-  MODIFF_CHECK_ARG(x && a_hat && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(x && a_hat && codes && x_scale && (scratch || fixed_scale),
+                   "NULL pointer argument");
   MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   MODIFF_CHECK_ARG(g->stride == 1 && g->split == 0 && g->h % 2 == 0 && g->w % 2 == 0,
@@ -1537,15 +1535,19 @@ extern "C" int modiff_modq_up2(const float* x, float* a_hat, int8_t* codes, floa
   const int blocks = tg.total < 148 * 8 ? tg.total : 148 * 8;
   const bool vec = (hw % 4 == 0) && ((((uintptr_t)x | (uintptr_t)a_hat) & 15) == 0);
   if (vec) {
-    modq_absmax_kernel<true, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
-                                                               (ModqScratch*)scratch, x_scale);
-    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    if (!fixed_scale) {
+      modq_absmax_kernel<true, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
+                                                                 (ModqScratch*)scratch, x_scale);
+      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    }
     modq_encode_kernel<true, false, true><<<blocks, kThreads, 0, s>>>(v, a_hat, codes, x_scale,
                                                                      nullptr, *g, d, tg, n_levels, 0);
   } else {
-    modq_absmax_kernel<false, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
-                                                                (ModqScratch*)scratch, x_scale);
-    MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    if (!fixed_scale) {
+      modq_absmax_kernel<false, false><<<blocks, kThreads, 0, s>>>(v, a_hat, gs, tg, n_levels, 0, 1,
+                                                                  (ModqScratch*)scratch, x_scale);
+      MODIFF_LAUNCH_CHECK("modq_absmax_kernel");
+    }
     modq_encode_kernel<false, false, true><<<blocks, kThreads, 0, s>>>(v, a_hat, codes, x_scale,
                                                                       nullptr, *g, d, tg, n_levels, 0);
   }

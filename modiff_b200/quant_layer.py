@@ -658,7 +658,7 @@ class QuantModule(nn.Module):
         k = self.fwd_kwargs
         ok = (self.upsampled_input_fusion and self.modulate and self.use_act_quant
               and self.use_weight_quant and not self.disable_act_quant and self.split == 0
-              and self.fwd_func is F.conv2d and aq.sym and aq.dynamic and not aq.channel_wise
+              and self.fwd_func is F.conv2d and aq.sym and not aq.channel_wise
               and not aq.running_stat and torch.is_tensor(x) and x.is_cuda
               and x.dtype == torch.float32 and x.dim() == 4 and tuple(k['stride']) == (1, 1)
               and self.weight.shape[1] >= 16)
@@ -689,9 +689,13 @@ class QuantModule(nn.Module):
                                   f"{tuple(self.a_hat.shape)}; call reset_cache() first")
             n = x.numel()
             # algorithmic bytes per SOURCE element: x 4 + a_hat read/write 8 + four codes
+            fixed = (not aq.dynamic) and buf.scale_set
+            if not aq.dynamic:      # the first quantised call measures the scale that stays
+                buf.scale_set = True
+                aq.inited = True
             _lib.call('modiff_modq_up2', x.data_ptr(), self.a_hat.data_ptr(), buf.codes.data_ptr(),
-                      buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, buf.scratch.data_ptr(),
-                      _lib.stream_ptr(), nbytes=16 * n, tag=g.key())
+                      buf.x_scale.data_ptr(), C.byref(g), aq.n_bits, int(fixed),
+                      buf.scratch.data_ptr(), _lib.stream_ptr(), nbytes=16 * n, tag=g.key())
             self._igemm(buf, pack, self.o_hat, True, None, g)
         out = self.o_hat if self.alias_output else self.o_hat.clone()
         return self.activation_function(out)

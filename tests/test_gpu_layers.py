@@ -438,12 +438,13 @@ def test_offset_code_constant_as_bias_vector(cuda):
     assert m.device_status() == 0
 
 
-@pytest.mark.parametrize("cin,cout,hw,w_bits,a_bits", [
-    (128, 128, 16, 4, 4),       # 16x16 -> 32x32: activation-reuse GEMM on the doubled size
-    (256, 256, 4, 8, 8),        # 4x4 -> 8x8
-    (64, 32, 6, 8, 8),          # odd source size (scalar loads), small channel counts
+@pytest.mark.parametrize("cin,cout,hw,w_bits,a_bits,dynamic", [
+    (128, 128, 16, 4, 4, True),     # 16x16 -> 32x32: activation-reuse GEMM on the doubled size
+    (256, 256, 4, 8, 8, True),      # 4x4 -> 8x8
+    (64, 32, 6, 8, 8, True),        # odd source size (scalar loads), small channel counts
+    (128, 128, 8, 8, 8, False),     # scale kept from the first quantised call
 ])
-def test_quantiser_of_an_upsampled_input(cuda, cin, cout, hw, w_bits, a_bits):
+def test_quantiser_of_an_upsampled_input(cuda, cin, cout, hw, w_bits, a_bits, dynamic):
     """The convolution of an Upsample block (ddim/models/diffusion.py:45-51): quantising at the
     source resolution and writing every code to its 2x2 block gives the same scale, the same
     output bits and - upsampled - the same cache as running the layer on the upsampled tensor."""
@@ -453,7 +454,7 @@ def test_quantiser_of_an_upsampled_input(cuda, cin, cout, hw, w_bits, a_bits):
     org = torch.nn.Conv2d(cin, cout, 3, padding=1)
     wq = {'n_bits': w_bits, 'channel_wise': True, 'scale_method': 'max'}
     aq = {'n_bits': a_bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
-          'leaf_param': True, 'dynamic': True}
+          'leaf_param': True, 'dynamic': dynamic}
     fused = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
     plain = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
     for q in (fused, plain):
