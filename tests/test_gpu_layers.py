@@ -368,16 +368,20 @@ def test_two_quantisers_of_one_tensor(cuda, c0, c1, hw, split, cout, a_bits):
     assert m.device_status() == 0
 
 
-@pytest.mark.parametrize("cin,cout,hw,w_bits", [(128, 128, 32, 4), (256, 256, 16, 8), (128, 256, 8, 4),
-                                              (64, 48, 8, 4)])
-def test_residual_sum_in_the_gemm_epilogue(cuda, cin, cout, hw, w_bits):
+@pytest.mark.parametrize("cin,cout,hw,w_bits,k", [
+    (128, 128, 32, 4, 3), (256, 256, 16, 8, 3),     # activation-reuse kernel
+    (128, 256, 8, 4, 3), (256, 256, 4, 4, 3),       # one-copy-per-tap kernel + separate add
+    (256, 256, 16, 4, 1),                           # 1x1 layer
+    (64, 48, 8, 4, 3),                              # CUDA-core kernel + separate add
+])
+def test_residual_sum_in_the_gemm_epilogue(cuda, cin, cout, hw, w_bits, k):
     """`x + conv2(h)` (qdiff/quant_block.py:313) with the sum written by the GEMM epilogue
     (activation-reuse kernel) or by a following add (other shapes): same bits as
     add(x, conv2(h)) from the ordinary forward."""
     import modiff_b200 as m
     from modiff_b200 import ops
     torch.manual_seed(51)
-    conv = torch.nn.Conv2d(cin, cout, 3, padding=1)
+    conv = torch.nn.Conv2d(cin, cout, k, padding=k // 2)
     wq = {'n_bits': w_bits, 'channel_wise': True, 'scale_method': 'max'}
     aq = {'n_bits': 8, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
           'leaf_param': True, 'dynamic': True}
