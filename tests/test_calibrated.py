@@ -194,7 +194,8 @@ def test_static_scale_set_by_first_quantised_call(cuda):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("lname", ["c3_w4a4", "c1_split_w4a4", "c3_w4a4_asym",
-                                   "c1_split_w8a4_asym", "lin_w8a6_asym", "down_w8a8"])
+                                   "c1_split_w8a4_asym", "lin_w8a6_asym", "down_w8a8",
+                                   "c3_w8a8_asym", "c1_split_w4a8_asym", "down_w8a8_asym"])
 def test_layer_with_loaded_scales_and_adaround(cuda, lname):
     """One layer, teacher-forced inputs: AdaRound logits and activation scales installed the
     way the checkpoint loader does.  Codes are integers, so the cached input a_hat must equal
