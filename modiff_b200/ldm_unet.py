@@ -167,10 +167,14 @@ def resblock_forward(blk, x, emb, split=0):
     src = ops.ActSource(xa, xb, norm=in_norm, silu=True)
     xs_pair = None
     if blk.updown:
-        h = blk.h_upd(src.materialize())
         xs_in = blk.x_upd(xa if xb is None else ops.concat_channels(xa, xb))
+        if (quant and isinstance(blk.h_upd, Upsample) and not blk.h_upd.use_conv
+                and hasattr(in_conv, 'forward_upsampled')):
+            # in_conv(upsample(silu(norm(x)))): quantised at the resolution of x
+            h = in_conv.forward_upsampled(src.materialize())
+        else:
+            h = in_conv(blk.h_upd(src.materialize()))
         xa, xb = xs_in, None
-        h = in_conv(h)
     else:
         skip0 = blk.skip_connection
         if (quant and _is_quant(skip0) and skip0.fwd_func is nn.functional.conv2d
