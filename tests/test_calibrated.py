@@ -260,3 +260,29 @@ def test_layer_with_loaded_scales_and_adaround(cuda, lname):
                                                     (2 ** (lc["a_bits"] - 1) - 1 if sym else n_lv))
         assert clamped
     assert m.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_resume_weights_with_dynamic_activation_scales(cuda, golden_cali):
+    """`--resume --quant_mode dynamic`: AdaRound weights from the checkpoint, activation scales
+    still measured every step (the checkpoint's activation entries are not used,
+    qdiff/utils.py:606-611).  Checked against the oracle with the same checkpoint."""
+    import modiff_b200 as m
+    c = cases.CALI_CASES[0]
+    qnn, ckpt = _resumed(c, cuda, golden_cali, act_quant_mode="dynamic")
+    assert all(q.dynamic for q in qnn.modules() if isinstance(q, m.UniformAffineQuantizer)
+               and q.n_bits == c["a_bits"] and q.leaf_param)
+    final, eps = _run(qnn, c, cuda, graph=True)
+    state = {k[len("model."):]: v for k, v in ckpt.items()
+             if ".weight_quantizer" not in k and ".act_quantizer" not in k}
+    net = oracle.OracleUNet(state, w_bits=c["w_bits"], a_bits=c["a_bits"], a_sym=c["a_sym"],
+                            split_shortcut=c["split"])
+    net.load_calibrated(ckpt, load_act=False)
+    want = []
+    oracle.ddim_sample(cases.unet_noise(c), cases.cali_sequence(c), net.forward,
+                       oracle.linear_betas(),
+                       on_step=lambda s, i, xt, et: want.append(et.numpy().copy()))
+    for s, (e, w) in enumerate(zip(eps, want)):
+        p = oracle.psnr(w, e.numpy())
+        print(f"dynamic scales, evaluation {s}: PSNR {p:.1f} dB")
+        assert p >= (100.0 if s == 0 else 40.0), (s, p)
