@@ -189,6 +189,22 @@ int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8_t* codes, 
                      float* x_zp, const modiff_conv_geom* g, int n_bits, int per_sample,
                      void* scratch, void* stream);
 
+/* Quantiser with MOVING-AVERAGE ranges (`--running_stat`: act_momentum_update,
+ * qdiff/quant_layer.py:113-132, switched on by qdiff/quant_model.py:104-117 while activations are
+ * calibrated): the range of this call's residual updates x_min / x_max,
+ *   x_min = x_min * momentum + min(r) * (1 - momentum)   (same for x_max, fp32),
+ * delta = max(|x_min|, |x_max|) / n_levels (symmetric) or (x_max - x_min) / (n_levels - 1) with
+ * zero_point = round(-x_min / delta), floor 1e-8, and the call quantises with that scale.
+ *   x_range    fp32 [8], caller-owned state: [0..3] moving (min, max) of segment 0 / 1,
+ *              [4..7] work area
+ *   init       non-zero on the quantiser's FIRST call: records min(r) / max(r) as the state and
+ *              takes delta / zero_point from them by the per-tensor 'max' rule (:191-214)
+ *   x_zp       fp32 [2] out (zero for symmetric); codes, a_hat, scratch as for modiff_modq_asym;
+ *              8-bit asymmetric codes are stored as q - 128 (see modiff_modq_asym) */
+int modiff_modq_running(const modiff_act_source* src, float* a_hat, int8_t* codes, float* x_scale,
+                        float* x_zp, float* x_range, const modiff_conv_geom* g, int n_bits,
+                        int symmetric, int init, double momentum, void* scratch, void* stream);
+
 /* Companions of 8-bit asymmetric codes (planes hold q - 128, see modiff_modq_asym).
  * modiff_codes_fill_halo: every code-plane cell that is not an input pixel (the zero padding of
  * F.conv2d, qdiff/quant_layer.py:271) receives zero_point - 128 of its channel's segment, the

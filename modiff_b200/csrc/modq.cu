@@ -516,13 +516,17 @@ __device__ inline void publish_range(ModqScratch* scratch, int slot, float mn, f
 // last block: ranges -> delta, zero point (per tensor in Python-float arithmetic, per sample in
 // fp32 tensor arithmetic, as the reference does)
 __device__ inline void finalise_ranges(ModqScratch* scratch, int slots, int n_bits, int per_sample,
-                                       float* x_scale, float* x_zp) {
+                                       float* x_scale, float* x_zp, float* range_out = nullptr) {
   const int top = (1 << n_bits) - 1;
   for (int s = threadIdx.x; s < slots; s += blockDim.x) {
     const unsigned int kmax = atomicExch(&scratch->absmax_bits[2 * s], 0u);
     const unsigned int kmin = atomicExch(&scratch->absmax_bits[2 * s + 1], 0u);
     const float xmax = kmax ? ord2f(kmax) : 0.0f;
     const float xmin = kmin ? ord2f(~kmin) : 0.0f;
+    if (range_out) {              // the raw range, for the moving-average update
+      range_out[2 * s] = xmin;
+      range_out[2 * s + 1] = xmax;
+    }
     float delta, zp;
     if (!per_sample) {
       double d = ((double)xmax - (double)xmin) / (double)top;
@@ -534,7 +538,9 @@ __device__ inline void finalise_ranges(ModqScratch* scratch, int slots, int n_bi
       if (delta < 1e-8f) delta = 1e-8f;
       zp = rintf(__fdiv_rn(-xmin, delta));
     }
-    if (n_bits < 8 && !(-zp >= -128.0f && (float)top - zp <= 127.0f)) atomicOr(&g_modq_status, 4);
+    // (with range_out the caller derives its own scale and checks it)
+    if (!range_out && n_bits < 8 && !(-zp >= -128.0f && (float)top - zp <= 127.0f))
+      atomicOr(&g_modq_status, 4);
     x_scale[s] = delta;
     x_zp[s] = zp;
   }
@@ -545,7 +551,7 @@ __global__ void __launch_bounds__(kThreads)
 modq_minmax_kernel(const SrcView src, const float* __restrict__ a_hat, modiff_conv_geom g,
                    TileGrid tg, int n_bits, int per_sample, int slots,
                    ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
-                   float* __restrict__ x_zp) {
+                   float* __restrict__ x_zp, float* __restrict__ range_out = nullptr) {
   const int hw = g.h * g.w;
   const int cg = threadIdx.x >> 4;
   const int pq = threadIdx.x & 15;
@@ -608,7 +614,7 @@ modq_minmax_kernel(const SrcView src, const float* __restrict__ a_hat, modiff_co
   __syncthreads();
   if (is_last) {
     __threadfence();
-    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp);
+    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp, range_out);
     if (threadIdx.x == 0) scratch->counter = 0u;
   }
 }
@@ -617,7 +623,7 @@ __global__ void __launch_bounds__(kThreads)
 modq_flat_minmax_kernel(const float4* __restrict__ x, const float4* __restrict__ a_hat, int64_t n4,
                         int cin, int split, int n_bits, int per_sample, int slots,
                         ModqScratch* __restrict__ scratch, float* __restrict__ x_scale,
-                        float* __restrict__ x_zp) {
+                        float* __restrict__ x_zp, float* __restrict__ range_out = nullptr) {
   __shared__ bool is_last;
   float mx0 = -INFINITY, mn0 = INFINITY, mx1 = -INFINITY, mn1 = INFINITY;
   bool any0 = false, any1 = false;
@@ -660,7 +666,7 @@ modq_flat_minmax_kernel(const float4* __restrict__ x, const float4* __restrict__
   __syncthreads();
   if (is_last) {
     __threadfence();
-    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp);
+    finalise_ranges(scratch, slots, n_bits, per_sample, x_scale, x_zp, range_out);
     if (threadIdx.x == 0) scratch->counter = 0u;
   }
 }
@@ -1357,7 +1363,8 @@ static bool staged_encode_enabled() {
 // x_zp != nullptr selects asymmetric codes (range pass instead of the maximum pass).
 int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes, float* x_scale,
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
-                    bool compute_scale, cudaStream_t s, float* x_zp = nullptr) {
+                    bool compute_scale, cudaStream_t s, float* x_zp = nullptr,
+                    float* range_out = nullptr, bool do_encode = true) {
   Derived d = derive(*g);
   const int hw = g->h * g->w;
   const int n_levels = sym_levels(n_bits);
@@ -1375,7 +1382,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
     if (compute_scale && x_zp) {
       modq_flat_minmax_kernel<<<blocks, kThreads, 0, s>>>(
           (const float4*)x, (const float4*)a_hat, n4, g->cin, g->split, n_bits, per_sample, slots,
-          (ModqScratch*)scratch, x_scale, x_zp);
+          (ModqScratch*)scratch, x_scale, x_zp, range_out);
       MODIFF_LAUNCH_CHECK("modq_flat_minmax_kernel");
     } else if (compute_scale) {
       modq_flat_absmax_kernel<<<blocks, kThreads, 0, s>>>(
@@ -1383,6 +1390,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
           (ModqScratch*)scratch, x_scale);
       MODIFF_LAUNCH_CHECK("modq_flat_absmax_kernel");
     }
+    if (!do_encode) return MODIFF_OK;
     modq_flat_encode_kernel<<<blocks, kThreads, 0, s>>>((const float4*)x, (float4*)a_hat,
                                                         (uint32_t*)codes, x_scale, x_zp, n4, g->cin,
                                                         g->split, n_levels, per_sample);
@@ -1406,7 +1414,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
   if (compute_scale && x_zp) {                                                                   \
     modq_minmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_bits, per_sample,   \
                                                         slots, (ModqScratch*)scratch, x_scale,   \
-                                                        x_zp);                                   \
+                                                        x_zp, range_out);                        \
     MODIFF_LAUNCH_CHECK("modq_minmax_kernel");                                                   \
   } else if (compute_scale) {                                                                    \
     modq_absmax_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, *g, tg, n_levels, per_sample, \
@@ -1416,6 +1424,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
 #define MODIFF_MODQ_LAUNCH(V, X)                                                                   \
   {                                                                                              \
     MODIFF_MODQ_SCALE(V, X)                                                                      \
+    if (!do_encode) return MODIFF_OK;                                                            \
     modq_encode_kernel<V, X><<<blocks, kThreads, 0, s>>>(src, a_hat, codes, x_scale, x_zp, *g, d,  \
                                                         tg, n_levels, per_sample);               \
     MODIFF_LAUNCH_CHECK("modq_encode_kernel");                                                   \
@@ -1428,6 +1437,7 @@ int launch_modq_src(const SrcView& src, bool xform, float* a_hat, int8_t* codes,
     } else {
       MODIFF_MODQ_SCALE(true, false)
     }
+    if (!do_encode) return MODIFF_OK;
     static SmemLimit smem_limit[2];
     if (xform) {
       MODIFF_CUDA(raise_smem_limit(modq_encode_staged_kernel<true>, kStagedSmem, smem_limit[1]));
@@ -1831,6 +1841,93 @@ extern "C" int modiff_modq_asym(const modiff_act_source* src, float* a_hat, int8
   const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
   return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                          (cudaStream_t)stream, x_zp);
+}
+
+namespace modiff {
+namespace {
+// act_momentum_update (qdiff/quant_layer.py:113-132) on device state: range[0..3] holds the
+// moving (min, max) of segment 0 / 1, range[4..7] the range of the current call.  `init`: the
+// first call of the quantiser, which records the range and takes its scale from it with the
+// per-tensor 'max' rule in Python-float arithmetic (:191-214); otherwise fp32 tensor arithmetic
+// exactly as the reference's EMA lines.
+__global__ void running_scale_kernel(float* __restrict__ range, float* __restrict__ x_scale,
+                                     float* __restrict__ x_zp, int slots, int n_bits, int sym,
+                                     int init, float momentum, float one_minus) {
+  const int s = threadIdx.x;
+  if (s >= slots) return;
+  const float cmin = range[4 + 2 * s], cmax = range[4 + 2 * s + 1];
+  const int n_levels = sym ? (1 << (n_bits - 1)) - 1 : (1 << n_bits);
+  float delta, zp = 0.0f;
+  if (init) {
+    range[2 * s] = cmin;
+    range[2 * s + 1] = cmax;
+    double d;
+    if (sym) {
+      const double lo = cmin < 0.0f ? (double)cmin : 0.0, hi = cmax > 0.0f ? (double)cmax : 0.0;
+      d = fmax(fabs(lo), hi) / (double)n_levels;
+    } else {
+      d = ((double)cmax - (double)cmin) / (double)(n_levels - 1);
+    }
+    if (d < 1e-8) d = 1e-8;
+    if (!sym) zp = (float)rint(-(double)cmin / d);
+    delta = (float)d;
+  } else {
+    const float emin = __fadd_rn(__fmul_rn(range[2 * s], momentum), __fmul_rn(cmin, one_minus));
+    const float emax = __fadd_rn(__fmul_rn(range[2 * s + 1], momentum), __fmul_rn(cmax, one_minus));
+    range[2 * s] = emin;
+    range[2 * s + 1] = emax;
+    if (sym) {
+      delta = __fdiv_rn(fmaxf(fabsf(emin), fabsf(emax)), (float)n_levels);
+    } else {
+      delta = __fdiv_rn(__fsub_rn(emax, emin), (float)(n_levels - 1));
+    }
+    if (delta < 1e-8f) delta = 1e-8f;
+    if (!sym) zp = rintf(__fdiv_rn(-emin, delta));
+  }
+  if (!sym && n_bits < 8 && !(-zp >= -128.0f && (float)(n_levels - 1) - zp <= 127.0f))
+    atomicOr(&g_modq_status, 4);
+  x_scale[s] = delta;
+  x_zp[s] = zp;
+}
+}  // namespace
+}  // namespace modiff
+
+extern "C" int modiff_modq_running(const modiff_act_source* src, float* a_hat, int8_t* codes,
+                                   float* x_scale, float* x_zp, float* x_range,
+                                   const modiff_conv_geom* g, int n_bits, int symmetric, int init,
+                                   double momentum, void* scratch, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(src && src->x0 && codes && x_scale && x_zp && x_range && scratch,
+                   "NULL pointer argument");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+  MODIFF_CHECK_ARG(src->c0 > 0 && src->c0 <= g->cin && (src->c0 == g->cin || src->x1),
+                   "bad concat split c0=%d for cin=%d", src->c0, g->cin);
+  MODIFF_CHECK_ARG(momentum >= 0.0 && momentum <= 1.0, "momentum %f outside [0, 1]", momentum);
+  SrcView v;
+  v.x0 = src->x0;
+  v.x1 = src->x1;
+  v.bias = src->chan_bias;
+  v.affine = src->affine;
+  v.c0 = src->c0;
+  v.c1 = g->cin - src->c0;
+  v.silu = src->silu;
+  const bool xform = src->x1 || src->chan_bias || src->affine || src->silu;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int slots = derive(*g).nseg;
+  // range pass only (its own delta / zero point are overwritten below)
+  rc = launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, 0, scratch, true, s, x_zp,
+                       x_range + 4, false);
+  if (rc) return rc;
+  // the reference's momentum and 1 - momentum are Python floats (doubles), each rounded to
+  // fp32 when it meets the fp32 tensor
+  const float one_minus = (float)(1.0 - momentum);
+  running_scale_kernel<<<1, 32, 0, s>>>(x_range, x_scale, x_zp, slots, n_bits, symmetric, init,
+                                        (float)momentum, one_minus);
+  MODIFF_LAUNCH_CHECK("running_scale_kernel");
+  return launch_modq_src(v, xform, a_hat, codes, x_scale, g, n_bits, 0, nullptr, false, s,
+                         symmetric ? nullptr : x_zp);
 }
 
 extern "C" int modiff_modq_fixed(const modiff_act_source* src, float* a_hat, int8_t* codes,

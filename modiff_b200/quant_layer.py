@@ -126,6 +126,9 @@ class _Buffers:
         # non-dynamic quantisers: True once x_scale / x_zp hold the scale that stays
         # (set by the first quantised call or by QuantModule.load_act_scale)
         self.scale_set = False
+        # moving (min, max) per segment of a quantiser with running statistics + work area
+        self.x_range = _zeros(8, torch.float32, device)
+        self.range_set = False
 
 
 class QuantModule(nn.Module):
@@ -441,9 +444,35 @@ class QuantModule(nn.Module):
 
     def _modq(self, x, a_hat, buf, g, src=None):
         aq = self.act_quantizer
-        if aq.running_stat:
-            raise ModiffError("running_stat (moving-average ranges) is a calibration-time mode and "
-                              "is not part of the accelerated sampling path")
+        first_static = (not aq.dynamic) and not buf.scale_set
+        if aq.running_stat or (first_static and aq.leaf_param and not aq.channel_wise):
+            # moving-average ranges (act_momentum_update, quant_layer.py:113-132), and the first
+            # call of a non-dynamic leaf quantiser, which records the range they start from
+            if aq.running_stat and (aq.dynamic or aq.channel_wise or not aq.leaf_param):
+                raise ModiffError("running_stat needs a non-dynamic per-tensor leaf_param quantiser "
+                                  "(quant_mode 'qdiff'), as in the reference's calibration flow")
+            if aq.running_stat and not (buf.scale_set and buf.range_set):
+                raise ModiffError("running_stat before the quantiser's first call (or after loading "
+                                  "scales without ranges): x_min / x_max are not initialised")
+            if src is not None:
+                st = src.struct()
+            else:
+                st = _lib.ActSourceStruct(x.data_ptr(), None, g.cin, 0, None, None)
+            n = src.numel() if src is not None else x.numel()
+            _lib.call('modiff_modq_running', C.byref(st), _lib.ptr(a_hat), buf.codes.data_ptr(),
+                      buf.x_scale.data_ptr(), buf.x_zp.data_ptr(), buf.x_range.data_ptr(),
+                      C.byref(g), aq.n_bits, int(aq.sym), int(first_static), 0.95,
+                      buf.scratch.data_ptr(), _lib.stream_ptr(),
+                      nbytes=(13 if a_hat is not None else 5) * n, tag=g.key())
+            buf.scale_set = buf.range_set = True
+            aq.inited = True
+            aq.x_min, aq.x_max = buf.x_range[0:1].view([]), buf.x_range[1:2].view([])
+            if g.split:
+                q0 = self.act_quantizer_0
+                q0.inited = True
+                q0.x_min, q0.x_max = buf.x_range[2:3].view([]), buf.x_range[3:4].view([])
+            self._offset_codes_halo(buf, g)
+            return
         if not aq.dynamic and buf.scale_set:
             # scale fixed by the first quantised call or a checkpoint: one encode pass
             if aq.channel_wise:

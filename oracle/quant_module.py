@@ -34,6 +34,8 @@ class OracleQuantModule:
         # quantised call, or a loaded one, stays (qdiff/quant_layer.py:72-79)
         self.a_dynamic = a_dynamic
         self.act_scale = None       # per segment (delta tensor, zero point)
+        self.act_range = None       # per segment (x_min, x_max) of a leaf_param quantiser
+        self.running_stat = False   # set_running_stat (:389-392): moving-average ranges
         # AdaRound weight quantisers of a calibrated checkpoint: per segment (alpha, delta, zp)
         self.adaround = None
 
@@ -77,10 +79,33 @@ class OracleQuantModule:
         if self.act_scale is None:
             first = [fake_quant(s, self.a_bits, self.a_sym) for s in segs]
             self.act_scale = [(f[2], f[3]) for f in first]
+            # leaf_param quantisers record the range of their first call (:192-194)
+            self.act_range = [(s.min(), s.max()) for s in segs]
             return first
         assert len(self.act_scale) == len(segs)
+        if self.running_stat:
+            self._momentum_update(segs)
         return [fake_quant(s, self.a_bits, self.a_sym, scale=sc)
                 for s, sc in zip(segs, self.act_scale)]
+
+    def _momentum_update(self, segs, momentum=0.95):
+        """act_momentum_update (qdiff/quant_layer.py:113-132), per segment quantiser."""
+        from .quantizer import n_levels_of
+        n_levels = n_levels_of(self.a_bits, self.a_sym)
+        for i, s in enumerate(segs):
+            x_min, x_max = self.act_range[i]
+            x_min = x_min * momentum + s.min() * (1 - momentum)
+            x_max = x_max * momentum + s.max() * (1 - momentum)
+            self.act_range[i] = (x_min, x_max)
+            if self.a_sym:
+                delta = torch.max(x_min.abs(), x_max.abs()) / n_levels
+            else:
+                delta = (x_max - x_min) / (n_levels - 1)
+            delta = torch.clamp(delta, min=1e-8)
+            zp = self.act_scale[i][1]
+            if not self.a_sym:
+                zp = int((-x_min / delta).round().item())
+            self.act_scale[i] = (delta, zp)
 
     def forward(self, x, split=0):
         if not self.use_weight_quant and not self.use_act_quant and not self.modulate:

@@ -241,3 +241,19 @@ def cali_checkpoint(c, model_state, fixture, prefix):
             ckpt[key] = model_state[name].detach().cpu().clone()
         assert list(ckpt[key].shape) == list(shape), key
     return ckpt
+
+
+# ---------------------------------------------------------------- moving-average ranges
+# Layers of LAYER_CASES run with non-dynamic leaf quantisers: call 0 unquantised, call 1 sets the
+# scale and the range, calls 2..4 with set_running_stat(True), call 5 with it off again.
+RUNNING_CASES = ["c3_w8a8", "c1_split_w4a4", "c3_w4a4_asym", "lin_w8a8_asym", "down_w8a8_asym"]
+
+
+def running_inputs(c):
+    g = torch.Generator().manual_seed(c["seed"] + 2000)
+    shape = (c["batch"], c["cin"]) if c["kind"] == "linear" else \
+        (c["batch"], c["cin"], c["hw"], c["hw"])
+    xs = [torch.randn(shape, generator=g)]
+    for k in range(5):
+        xs.append(xs[-1] + (0.08 - 0.01 * k) * (torch.randn(shape, generator=g) + 0.2 * (k % 2)))
+    return xs

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali|running]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -337,6 +337,34 @@ def gen_cali():
     print("cali.npz", len(out))
 
 
+def gen_running():
+    """Single layers with moving-average activation ranges (`--running_stat`)."""
+    out = {}
+    for name in cases.RUNNING_CASES:
+        c = next(x for x in cases.LAYER_CASES if x["name"] == name)
+        org = cases.layer_module(c)
+        wq, aq = cases.quant_params(c)
+        m = RefQuantModule(org, wq, dict(aq, dynamic=False), modulate=True)
+        m.set_quant_state(True, True)
+        with torch.no_grad():
+            for s, x in enumerate(cases.running_inputs(c)):
+                if c.get("pad_br"):
+                    x = F.pad(x, (0, 1, 0, 1))
+                m.set_running_stat(s in (2, 3, 4))
+                y = m(x, split=c.get("split", 0)) if c.get("split", 0) else m(x)
+                if s >= 4:
+                    out[f"{name}/out{s}"] = y.numpy().copy()
+                if s > 0:
+                    qs = [m.act_quantizer] + ([m.act_quantizer_0] if c.get("split", 0) else [])
+                    out[f"{name}/delta{s}"] = np.asarray([float(q.delta) for q in qs], np.float32)
+                    out[f"{name}/zp{s}"] = np.asarray([float(q.zero_point) for q in qs], np.float32)
+                    out[f"{name}/range{s}"] = np.asarray(
+                        [[float(q.x_min), float(q.x_max)] for q in qs], np.float32)
+        out[f"{name}/a_hat"] = m.a_hat.numpy().copy()
+    np.savez_compressed(os.path.join(HERE, "running.npz"), **out)
+    print("running.npz", len(out))
+
+
 def gen_sd():
     """SD-v1 UNet shapes (random init seed 0, zero tensors redrawn), reference QuantModel with
     --a_sym, classifier-free guidance as ldm/models/diffusion/ddim.py:192-208."""
@@ -384,7 +412,7 @@ def gen_sd():
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
-                ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali)
+                ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali, running=gen_running)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()
