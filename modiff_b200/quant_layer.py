@@ -694,7 +694,9 @@ class QuantModule(nn.Module):
         if not ok:
             if self._a_hat_half and self.a_hat is not None:
                 raise ModiffError("this layer's cache is held at the resolution of its upsample "
-                                  "block's input; call reset_cache() before changing its mode")
+                                  "block's input; call reset_cache() before changing its mode (for "
+                                  "running statistics set QuantModule.upsampled_input_fusion = False "
+                                  "or MODIFF_FUSE_UPSAMPLE=0 first)")
             return self.forward(upsample2x(x))
         x = x.contiguous()
         b, c, h, w = x.shape
