@@ -698,6 +698,9 @@ class QuantModule(nn.Module):
                                   "running statistics set QuantModule.upsampled_input_fusion = False "
                                   "or MODIFF_FUSE_UPSAMPLE=0 first)")
             return self.forward(upsample2x(x))
+        if self.a_hat is not None and not self._a_hat_half:
+            # this epoch's cache was created by the ordinary path: stay on it
+            return self.forward(upsample2x(x))
         x = x.contiguous()
         b, c, h, w = x.shape
         g = self._geom(torch.empty((b, c, 2 * h, 2 * w), device='meta'), 0)

@@ -95,6 +95,7 @@ class QuantModel(nn.Module):
         return self.model(x, timesteps, context)
 
     def set_running_stat(self, running_stat: bool, sm_only=False):
+        self._config_changed()
         for m in self.model.modules():
             if isinstance(m, QuantBasicTransformerBlock):
                 for attn in (m.attn1, m.attn2):

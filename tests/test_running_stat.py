@@ -104,3 +104,37 @@ def test_running_stat_needs_an_initialised_leaf_quantiser(cuda):
     mod.set_running_stat(True)
     with pytest.raises(m.ModiffError):
         mod(xs[1].to(cuda))
+
+
+@pytest.mark.gpu
+def test_running_stat_on_an_upsample_convolution(cuda):
+    """With the source-resolution quantiser switched off, `forward_upsampled` is the ordinary
+    layer on the upsampled tensor and takes running statistics like any other layer."""
+    import copy
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(61)
+    org = torch.nn.Conv2d(64, 64, 3, padding=1)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': False}
+    a = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
+    b = m.QuantModule(copy.deepcopy(org), wq, aq, modulate=True).to(cuda)
+    a.upsampled_input_fusion = False
+    for q in (a, b):
+        q.set_quant_state(True, True)
+        q.alias_output = False
+    g = torch.Generator().manual_seed(62)
+    x = torch.randn(2, 64, 8, 8, generator=g)
+    with torch.no_grad():
+        for s in range(5):
+            xs = (x + 0.05 * s * torch.randn(x.shape, generator=g)).to(cuda)
+            for q in (a, b):
+                q.set_running_stat(s >= 2)
+            ya = a.forward_upsampled(xs)
+            yb = b(ops.upsample2x(xs))
+            assert torch.equal(ya, yb), s
+            if s >= 1:
+                assert float(a.act_quantizer.x_min) == float(b.act_quantizer.x_min)
+                assert float(a.act_quantizer.delta) == float(b.act_quantizer.delta)
+    assert m.device_status() == 0
