@@ -323,6 +323,9 @@ int modiff_linear_group(const int8_t* codes, const float* x_scale, int rows, int
  *   - nothing is allocated or freed, here or in any routine it calls.
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress
  *     with that device current) and caches it; make that first call before any stream capture.
+ *     The cached address belongs to the device's primary context: after cudaDeviceReset (or any
+ *     other teardown of that context) it is stale and this entry point must not be used again
+ *     in the process.
  *   - per_sample != 0 needs one slot per image: batch > MODIFF_MODQ_STATIC_MAX_BATCH is
  *     rejected with MODIFF_ERR_INVALID (use modiff_modq with your own scratch instead).
  *   - all calls on a device share the one array and it keeps the previous call's contents; the
@@ -531,6 +534,19 @@ int modiff_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n, int is_s
  * with a given scale (layout transform used by tests and by static-scale callers). */
 int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
                            const modiff_conv_geom* g, int n_bits, void* stream);
+
+/* Tensor-pipe probe of tcgen05.mma kind::i8 (measurement aid; no counterpart in the reference,
+ * whose convolutions are PyTorch fp32, qdiff/quant_layer.py:345-365).  Every unit holds a
+ * 128-row A tile per CTA and the B tile in shared memory (K = 128 bytes) and repeats the four
+ * K = 32 steps `iters` times, accumulating in tensor memory; timing the call with CUDA events
+ * over `units` = the SM count (mode 1) or half of it (mode 2) gives the int8 ceiling the GEMM
+ * kernels' achieved TOPS are reported against: ops = units * iters * 4 * 2 * M * umma_n * 32.
+ *   mode    1: cta_group::1 (M = 128 per unit); 2: cta_group::2, a two-CTA cluster (M = 256)
+ *   a       int8 [units * M][128] row-major;  b  int8 [umma_n][128] row-major
+ *   acc_out optional int32 [M][umma_n]: unit 0's accumulators = iters * a b^T (layout check)
+ *   debug   optional int32 [4]: tensor-memory base address seen by each CTA of unit 0 */
+int modiff_i8_mma_probe(int mode, int umma_n, int iters, int units, const int8_t* a,
+                        const int8_t* b, int32_t* acc_out, int* debug, void* stream);
 
 #ifdef __cplusplus
 }

@@ -130,6 +130,7 @@ SIGNATURES = {
     "modiff_pack_int4": (C.c_int, [_P, _P, C.c_int64, _P]),
     "modiff_unpack_int4": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
     "modiff_quantize_static": (C.c_int, [_P, _P, _P, _G, C.c_int, _P]),
+    "modiff_i8_mma_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, _P]),
 }
 
 _lib = None
@@ -159,9 +160,18 @@ KERNELS_PER_CALL = {
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_layernorm": 1, "modiff_geglu": 1, "modiff_transpose": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
     "modiff_ddim_step": 1, "modiff_cfg_combine": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
-    "modiff_quantize_static": 1,
+    "modiff_quantize_static": 1, "modiff_i8_mma_probe": 1,
 }
 LAUNCHES = [0]        # kernels launched through `call` since import
+# Bumped whenever a layer allocates or replaces a device buffer that kernels address directly
+# (caches, code planes, scales, packed weights) or a flag is set on a single layer: a captured
+# CUDA graph holds those addresses, so it is only replayed while this number is unchanged.
+GENERATION = [0]
+
+
+def bump_generation():
+    GENERATION[0] += 1
+
 TIMER = None          # a KernelTimer while per-kernel timing is on
 
 
@@ -243,3 +253,32 @@ def device_status(reset=True):
 
 def out_hw(g):
     return lib().modiff_out_h(C.byref(g)), lib().modiff_out_w(C.byref(g))
+
+
+def measure_i8_peak(mode=1, umma_n=256, iters=4096, repeats=5):
+    """Int8 tensor-pipe ceiling of the current device in TOPS: `modiff_i8_mma_probe` on every SM
+    (mode 2: every SM pair), operands resident in shared memory, best of `repeats` CUDA-event
+    timings after one warm-up launch."""
+    sms = C.c_int(0)
+    check(lib().modiff_device_info(C.byref(sms), None, None))
+    units = sms.value // mode
+    m = 128 * mode
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(5)
+    a = torch.randint(-127, 128, (units * m, 128), generator=g, dtype=torch.int8).to(dev)
+    b = torch.randint(-127, 128, (umma_n, 128), generator=g, dtype=torch.int8).to(dev)
+    best = None
+    for i in range(repeats + 1):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        call('modiff_i8_mma_probe', mode, umma_n, iters, units, a.data_ptr(), b.data_ptr(), None,
+             None, stream_ptr())
+        end.record()
+        end.synchronize()
+        ms = start.elapsed_time(end)
+        if i > 0 and (best is None or ms < best):
+            best = ms
+    if device_status(reset=True):
+        raise ModiffError("the int8 probe gave up on a bounded wait")
+    ops = units * iters * 4 * 2.0 * m * umma_n * 32
+    return ops / (best / 1000.0) / 1e12

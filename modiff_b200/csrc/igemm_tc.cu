@@ -605,6 +605,7 @@ int read_device_status_bf16(int* status, int reset);   // gemm_bf16_tc.cu
 int read_device_status_halo(int* status, int reset);   // igemm_halo.cu
 int read_device_status_attention(int* status, int reset);   // attention_tc.cu
 int read_device_status_modq(int* status, int reset);        // modq.cu
+int read_device_status_probe(int* status, int reset);       // i8_probe.cu
 bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
                     const int32_t* acc_out, const float* o_hat);
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
@@ -633,7 +634,10 @@ int read_device_status(int* status, int reset) {
   int e = 0;
   rc = read_device_status_modq(&e, reset);
   if (rc) return rc;
-  *status = a | b | c | d | e;
+  int f = 0;
+  rc = read_device_status_probe(&f, reset);
+  if (rc) return rc;
+  *status = a | b | c | d | e | f;
   return MODIFF_OK;
 }
 

@@ -8,6 +8,12 @@ host cost.  The reference has no counterpart (it runs eager PyTorch, with host s
 in every quantiser call, qdiff/quant_layer.py:197-213).
 
 The tensor returned by a replayed call is a static buffer that the next call overwrites.
+
+A captured graph holds raw device addresses (each layer's caches, code planes, scale words and
+packed weights).  Layers replace those buffers when they meet another input shape, when their
+weights are repacked, or when a flag is set on a single layer; every such event bumps
+`_lib.GENERATION`, and a graph captured under another generation is dropped and captured again
+instead of being replayed.
 """
 import torch
 
@@ -42,6 +48,11 @@ class GraphedModel:
         _lib.require_cuda(x, "model input")
         key = (tuple(x.shape), None if context is None else tuple(context.shape), str(x.device))
         entry = self._graphs.get(key)
+        if entry is not None and entry["generation"] != _lib.GENERATION[0]:
+            # some layer moved a buffer since the capture (another input shape in between, a
+            # repacked weight, a flag set on one layer): the recorded addresses are stale
+            del self._graphs[key]
+            entry = None
         if entry is None:
             entry = self._capture(x, t, context)
             self._graphs[key] = entry
@@ -67,4 +78,5 @@ class GraphedModel:
             raise ModiffError(f"CUDA graph capture of the UNet step failed: {e}") from e
         kernels = _lib.LAUNCHES[0] - before
         _lib.LAUNCHES[0] = before       # nothing ran during capture
-        return dict(graph=graph, x=sx, t=st, c=sc, out=out, kernels=kernels)
+        return dict(graph=graph, x=sx, t=st, c=sc, out=out, kernels=kernels,
+                    generation=_lib.GENERATION[0])

@@ -11,6 +11,7 @@ import numpy as np
 import torch
 
 from . import ops
+from .sampler import raise_on_device_status
 
 
 def make_beta_schedule(schedule, n_timestep, linear_start=1e-4, linear_end=2e-2, cosine_s=8e-3):
@@ -81,8 +82,13 @@ class DDIMSampler:
     @torch.no_grad()
     def sample(self, S, batch_size, shape, conditioning=None, eta=0., x_T=None,
                unconditional_guidance_scale=1., unconditional_conditioning=None, generator=None,
-               max_evals=None, img_callback=None, cuda_graph=None, **kwargs):
-        """Returns (samples, intermediates) like the reference; `max_evals` stops early."""
+               max_evals=None, img_callback=None, eps_callback=None, cuda_graph=None,
+               check_status=True, **kwargs):
+        """Returns (samples, intermediates) like the reference; `max_evals` stops early.
+        `img_callback(pred_x0, i)` as in the reference (ddim.py:165); `eps_callback(e_t, i)` sees
+        the model output of every evaluation.  After the loop the device status word is read once
+        (`check_status`): a kernel that gave up on a bounded wait, or an activation zero point
+        that did not fit its code plane, raises instead of returning wrong samples."""
         self.make_schedule(S, ddim_eta=eta)
         model = self.model
         if cuda_graph is None:
@@ -114,9 +120,16 @@ class DDIMSampler:
             noise = None
             if sigma != 0.0:
                 noise = torch.randn(img.shape, generator=generator, device=img.device)
+            if eps_callback is not None:
+                eps_callback(e_t, i)
             if img_callback is not None:
-                img_callback(e_t, i)
-            img = ops.ddim_step(img, e_t, s1, s2, s3, sigma, c2, noise=noise)
+                img, pred_x0 = ops.ddim_step(img, e_t, s1, s2, s3, sigma, c2, noise=noise,
+                                             want_x0=True)
+                img_callback(pred_x0, i)
+            else:
+                img = ops.ddim_step(img, e_t, s1, s2, s3, sigma, c2, noise=noise)
+        if check_status:
+            raise_on_device_status()
         return img, {}
 
 
@@ -134,9 +147,11 @@ class PLMSSampler(DDIMSampler):
     @torch.no_grad()
     def sample(self, S, batch_size, shape, conditioning=None, eta=0., x_T=None,
                unconditional_guidance_scale=1., unconditional_conditioning=None, max_steps=None,
-               img_callback=None, cuda_graph=None, **kwargs):
-        """Returns (samples, intermediates); `img_callback(e, k)` sees every model output in
-        evaluation order; `max_steps` stops early."""
+               img_callback=None, eps_callback=None, cuda_graph=None, check_status=True,
+               **kwargs):
+        """Returns (samples, intermediates); `eps_callback(e, k)` sees every model output in
+        evaluation order, `img_callback(pred_x0, i)` every step's x0 prediction (plms.py:165);
+        `max_steps` stops early; `check_status` as in DDIMSampler.sample."""
         self.make_schedule(S, ddim_eta=eta)
         model = self.model
         if cuda_graph is None:
@@ -162,8 +177,8 @@ class PLMSSampler(DDIMSampler):
                 e_all = model(torch.cat([x] * 2), torch.cat([t] * 2),
                               torch.cat([unconditional_conditioning, conditioning]))
                 e = ops.cfg_combine(e_all[:b], e_all[b:], float(unconditional_guidance_scale))
-            if img_callback is not None:
-                img_callback(e, n_eval[0])
+            if eps_callback is not None:
+                eps_callback(e, n_eval[0])
             n_eval[0] += 1
             return e
 
@@ -187,9 +202,15 @@ class PLMSSampler(DDIMSampler):
                 e_prime = (23 * e_t - 16 * old_eps[-1] + 5 * old_eps[-2]) / 12
             else:
                 e_prime = (55 * e_t - 59 * old_eps[-1] + 37 * old_eps[-2] - 9 * old_eps[-3]) / 24
-            img = ops.ddim_step(img, e_prime, s1, s2, s3, 0.0, c2)
+            if img_callback is not None:
+                img, pred_x0 = ops.ddim_step(img, e_prime, s1, s2, s3, 0.0, c2, want_x0=True)
+                img_callback(pred_x0, i)
+            else:
+                img = ops.ddim_step(img, e_prime, s1, s2, s3, 0.0, c2)
             old_eps.append(e_t)
             if len(old_eps) >= 4:
                 old_eps.pop(0)
+        if check_status:
+            raise_on_device_status()
         return img, {}
 

@@ -67,7 +67,7 @@ def main():
         marks.append(ev)
 
     sampler.sample(steps, batch, (4, latent, latent), eta=0.0, x_T=x, max_evals=args.evals,
-                   img_callback=mark, **kw)
+                   eps_callback=mark, **kw)
     torch.cuda.synchronize()
     skip = 3
     ms = marks[skip].elapsed_time(marks[-1]) / (len(marks) - 1 - skip)

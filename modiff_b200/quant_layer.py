@@ -43,6 +43,29 @@ def _zeros(n, dtype, device):
     return torch.zeros(n, dtype=dtype, device=device)
 
 
+def check_scale_method(scale_method, channel_wise):
+    """Which `scale_method` strings mean the min / max rule this library implements.
+
+    Channel-wise scales: the reference takes its per-channel search only for the literal string
+    'mse:' (qdiff/quant_layer.py:137) and the min / max rule for every other value, so the
+    `'mse'` the latent-diffusion drivers put into their weight parameters
+    (scripts/sample_diffusion_ldm.py:549, scripts/txt2img.py:380) IS min / max there, and here.
+    Per-tensor scales: any name containing 'max' (:192), except the '..scale' variants, which
+    shrink the range by (n_bits + 2) / 8 (:199-201) and are not implemented; per-tensor 'mse' is
+    a calibration-time search (:215-231) outside the sampling path."""
+    if channel_wise:
+        if scale_method == 'mse:':
+            raise ModiffError("scale_method 'mse:' (the per-channel search) is a calibration-time "
+                              "procedure and is not part of the accelerated sampling path")
+        return
+    if 'max' not in scale_method:
+        raise ModiffError(f"per-tensor scale_method {scale_method!r} is a calibration-time search "
+                          "and is not part of the accelerated sampling path")
+    if 'scale' in scale_method:
+        raise ModiffError(f"scale_method {scale_method!r} shrinks the range by (n_bits + 2) / 8 in "
+                          "the reference; only the plain 'max' rule is implemented")
+
+
 class UniformAffineQuantizer(nn.Module):
     """Uniform affine fake quantiser (qdiff/quant_layer.py:36-111, scale rules :134-235).
 
@@ -73,9 +96,7 @@ class UniformAffineQuantizer(nn.Module):
 
     def forward(self, x: torch.Tensor):
         _lib.require_cuda(x, "quantiser input")
-        if 'max' not in self.scale_method:
-            raise ModiffError(f"scale_method {self.scale_method!r} is a calibration-time search "
-                              "and is not part of the accelerated sampling path")
+        check_scale_method(self.scale_method, self.channel_wise)
         if self.running_stat:
             raise ModiffError("running_stat (EMA ranges) is not part of the accelerated path")
         x = x.contiguous()
@@ -247,7 +268,20 @@ class QuantModule(nn.Module):
         buf = self._geom_buffers.get(key)
         if buf is None or buf.codes.device != device:
             per_sample = bool(self.act_quantizer.channel_wise)
+            old = next(iter(self._geom_buffers.values()), None)
             buf = _Buffers(g, device, per_sample)
+            _lib.bump_generation()
+            if (old is not None and not per_sample and not self.act_quantizer.dynamic
+                    and old.codes.device == device and bool(old.g.split) == bool(g.split)
+                    and (old.scale_set or old.range_set)):
+                # a non-dynamic quantiser's scale, zero point and moving range belong to the
+                # quantiser, not to an input shape (qdiff/quant_layer.py:72-79): they carry over
+                # when the layer meets another batch size or resolution
+                buf.x_scale.copy_(old.x_scale[:buf.x_scale.numel()])
+                buf.x_zp.copy_(old.x_zp[:buf.x_zp.numel()])
+                buf.x_range.copy_(old.x_range)
+                buf.scale_set, buf.range_set = old.scale_set, old.range_set
+            carried = buf.scale_set
             self._geom_buffers = {key: buf}   # one live geometry per layer
             n = g.batch if per_sample else 1
             self.act_quantizer.delta = buf.x_scale[0:n].view([n] + [1] * 3) if per_sample \
@@ -260,10 +294,16 @@ class QuantModule(nn.Module):
                 self.act_quantizer_0.delta = buf.x_scale[1:2].view([])
                 self.act_quantizer_0.zero_point = 0 if not asym else buf.x_zp[1:2].view([])
                 self.act_quantizer_0.inited = True
-            if not self.act_quantizer.dynamic:
+            if not self.act_quantizer.dynamic and not carried:
                 self.act_quantizer.inited = False      # until the first quantised call
                 if g.split:
                     self.act_quantizer_0.inited = False
+            if carried and buf.range_set:
+                aq = self.act_quantizer
+                aq.x_min, aq.x_max = buf.x_range[0:1].view([]), buf.x_range[1:2].view([])
+                if g.split:
+                    q0 = self.act_quantizer_0
+                    q0.x_min, q0.x_max = buf.x_range[2:3].view([]), buf.x_range[3:4].view([])
             self._install_act_scale(buf)
         return buf
 
@@ -318,9 +358,10 @@ class QuantModule(nn.Module):
                (wq.alpha.data_ptr(), wq.alpha._version) if learned else None)
         if self._wpack is not None and self._wpack['key'] == key:
             return self._wpack
-        if wq.sym or not wq.channel_wise or 'max' not in wq.scale_method:
-            raise ModiffError("the accelerated path expects per-output-channel asymmetric 'max' "
+        if wq.sym or not wq.channel_wise:
+            raise ModiffError("the accelerated path expects per-output-channel asymmetric "
                               "weight quantisation (the reference's wq_params)")
+        check_scale_method(wq.scale_method, True)
         _lib.require_cuda(w, "weight")
         l = _lib.lib()
         dev = w.device
@@ -365,6 +406,7 @@ class QuantModule(nn.Module):
             if not need_corr or with_sum:
                 break
         self._wpack = pack
+        _lib.bump_generation()
         if learned:
             return pack                     # the AdaRound quantisers keep their own tensors
         shape = [g.cout] + [1] * (w.dim() - 1)
@@ -787,9 +829,19 @@ class QuantModule(nn.Module):
         if not act_q:
             # weight-only quantisation or fully unquantised weights with modulate flag set
             out = torch.empty(out_shape, dtype=torch.float32, device=input.device)
-            self._conv_fp32(input, w_kn, bias, g, out)
             if self.modulate and self.use_act_quant:
+                # disable_act_quant with modulation on: the reference still runs its cached-output
+                # branch on the UNMODIFIED input, i.e. from the second call on it adds the
+                # bias-free convolution to the previous output (qdiff/quant_layer.py:357-363)
+                if self.o_hat is None:
+                    self._conv_fp32(input, w_kn, bias, g, out)
+                else:
+                    from .ops import add
+                    self._conv_fp32(input, w_kn, None, g, out)
+                    out = add(self.o_hat, out)
                 self.o_hat = out
+                return self.activation_function(out if self.alias_output else out.clone())
+            self._conv_fp32(input, w_kn, bias, g, out)
             return self.activation_function(out)
 
         if pack is None:
@@ -941,6 +993,7 @@ class QuantModule(nn.Module):
     def _reuse(store, shape, device):
         if store is not None and tuple(store.shape) == tuple(shape) and store.device == device:
             return store
+        _lib.bump_generation()
         return torch.empty(tuple(shape), dtype=torch.float32, device=device)
 
     def _shape_from(self, input, g, ho_wo):
@@ -951,16 +1004,21 @@ class QuantModule(nn.Module):
         return (g.batch, g.cout, ho_wo[0], ho_wo[1])
 
     # ------------------------------------------------------------------ flag setters
+    # A flag set on one layer changes which kernels its next call launches; captured CUDA graphs
+    # are dropped through the generation counter (graph.py).
     def set_quant_state(self, weight_quant: bool = False, act_quant: bool = False):
+        _lib.bump_generation()
         self.use_weight_quant = weight_quant
         self.use_act_quant = act_quant
 
     def set_dynamic_state(self, dynamic):
+        _lib.bump_generation()
         self.act_quantizer.dynamic = dynamic
         if self.split != 0:
             self.act_quantizer_0.dynamic = dynamic
 
     def set_modualtion(self, modulation):
+        _lib.bump_generation()
         self.modulate = modulation
 
     def reset_cache(self):
@@ -969,10 +1027,12 @@ class QuantModule(nn.Module):
         self._a_hat_half = False
 
     def set_split(self):
+        _lib.bump_generation()
         self.weight_quantizer_0 = UniformAffineQuantizer(**self.weight_quant_params)
         self.act_quantizer_0 = UniformAffineQuantizer(**self.act_quant_params)
 
     def set_running_stat(self, running_stat: bool):
+        _lib.bump_generation()
         self.act_quantizer.running_stat = running_stat
         if self.split != 0:
             self.act_quantizer_0.running_stat = running_stat

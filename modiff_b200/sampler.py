@@ -8,7 +8,7 @@ import os
 import numpy as np
 import torch
 
-from . import ops
+from . import ops, _lib
 
 
 def get_beta_schedule(beta_schedule="linear", *, beta_start=0.0001, beta_end=0.02,
@@ -71,6 +71,18 @@ def step_coefficients(alphas, i, j, eta=0.0):
     return tuple(float(v) for v in (s1, s2, s3, c1, c2))
 
 
+def raise_on_device_status():
+    """Reads (and clears) the library's sticky device status word - one 4-byte device-to-host
+    copy, which waits for the stream - and raises when a kernel reported a failure: bit 0 a
+    bounded wait that ran out (the kernel returned early, its outputs are incomplete), bit 2 an
+    asymmetric zero point that did not fit the int8 code planes."""
+    status = _lib.device_status(reset=True)
+    if status:
+        raise _lib.ModiffError(
+            f"device status {status:#x} after sampling: a kernel gave up on a bounded wait or an "
+            "activation zero point did not fit its code plane; the samples are not valid")
+
+
 @torch.no_grad()
 def generalized_steps(x, seq, model, b, with_t=False, last_only=True, **kwargs):
     """DDIM sampling (ddim/functions/denoising.py:10-55).
@@ -80,6 +92,9 @@ def generalized_steps(x, seq, model, b, with_t=False, last_only=True, **kwargs):
     Noise for eta > 0 comes from `generator` (a CUDA torch.Generator) when given.
     `cuda_graph` (default on, or MODIFF_CUDA_GRAPH=0 to turn it off): a QuantModel's steady-state
     steps are replayed as a CUDA graph (graph.py).
+    `check_status` (default on): after the loop the device status word is read once and a
+    non-zero value raises (`raise_on_device_status`); callers that time the loop on the device
+    pass False and check once afterwards.
     """
     n = x.size(0)
     seq = list(seq)
@@ -108,6 +123,8 @@ def generalized_steps(x, seq, model, b, with_t=False, last_only=True, **kwargs):
             ts.append(t)
     if last_only:
         xs = [xt]
+    if kwargs.get("check_status", True) and x.is_cuda:
+        raise_on_device_status()
     if with_t:
         return xs, ts, x0_preds
     return xs, x0_preds

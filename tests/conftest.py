@@ -36,3 +36,21 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session")
+def golden_sens():
+    return np.load(os.path.join(GOLDEN, "sens.npz"))
+
+
+# A free-running modulated evaluation is compared with the reference's stored output.  How close
+# two exact implementations can be is MEASURED, not guessed: sens.npz holds, per case and
+# evaluation, the PSNR between two runs of the reference itself that differ only by a
+# perturbation of 1e-4 of the range on the first evaluation's output (tests/golden/cases.py,
+# SENS_REL).  The CUDA path's own first-evaluation difference is below that perturbation, so it
+# must stay within SENS_MARGIN_DB of the reference's self-agreement at every later evaluation.
+SENS_MARGIN_DB = 6.0
+
+
+def sens_floor(golden_sens, name, k):
+    return float(golden_sens[name + "/sens_db"][k]) - SENS_MARGIN_DB

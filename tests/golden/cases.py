@@ -257,3 +257,41 @@ def running_inputs(c):
     for k in range(5):
         xs.append(xs[-1] + (0.08 - 0.01 * k) * (torch.randn(shape, generator=g) + 0.2 * (k % 2)))
     return xs
+
+
+# ---------------------------------------------------------------- full-length runs and sensitivity
+# Full sampler loops at the sizes the throughput figures are quoted on (pixel UNet: batch 256,
+# the benchmarked batch; latent UNet: all 500 evaluations of `-c 400`; SD-v1: all 50 guided
+# evaluations).  Only the final tensor and a few trajectory points are stored.
+FULL_CASES = [
+    dict(name="pixel_w4a4_split_b256_s100", kind="pixel", quant=True, split=True, w_bits=4, a_bits=4,
+         batch=256, steps=100, noise_seed=1),
+    dict(name="ldm_w8a8_b2_full", kind="ldm", w_bits=8, a_bits=8, batch=2, ddim_steps=400,
+         noise_seed=11, zero_seed=1234),
+    dict(name="sd_w8a8_b1_full", kind="sd", w_bits=8, a_bits=8, batch=1, latent=64, ddim_steps=50,
+         guidance=7.5, noise_seed=21, zero_seed=1234),
+    dict(name="pixel_w4a3_split_b256_s100", kind="pixel", quant=True, split=True, w_bits=4, a_bits=3,
+         batch=256, steps=100, noise_seed=2),
+]
+
+# Self-sensitivity of the reference: the same run repeated with the FIRST evaluation's output
+# perturbed by Gaussian noise of standard deviation SENS_REL x (max - min of that output).  The
+# PSNR between the two runs, per evaluation, is what a last-bit-different but otherwise exact
+# implementation can be expected to reach; tests derive their per-evaluation floors from it.
+SENS_REL = 1e-4
+SENS_SEED = 777
+
+
+def perturb_first_call(fn, rel=SENS_REL, seed=SENS_SEED):
+    """`fn` with the output of its first call perturbed (see SENS_REL)."""
+    state = {"n": 0}
+
+    def wrapped(*args):
+        out = fn(*args)
+        if state["n"] == 0:
+            g = torch.Generator().manual_seed(seed)
+            span = float(out.max() - out.min())
+            out = out + rel * span * torch.randn(out.shape, generator=g)
+        state["n"] += 1
+        return out
+    return wrapped

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali|running]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali|running|sens|full [--case NAME]]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -409,10 +409,139 @@ def gen_sd():
     print("sd.npz", len(out))
 
 
+def _psnr(a, b):
+    """trt/benchmark_comparison.py:186-191."""
+    a = np.asarray(a, dtype=np.float32).ravel()
+    b = np.asarray(b, dtype=np.float32).ravel()
+    mse = np.mean((a - b) ** 2)
+    peak = max(np.abs(a).max(), np.abs(b).max())
+    return float(20 * np.log10(peak / np.sqrt(mse))) if mse > 0 and peak > 0 else float("inf")
+
+
+def _sd_stub():
+    import types
+    oc, lc = types.ModuleType('omegaconf'), types.ModuleType('omegaconf.listconfig')
+
+    class ListConfig(list):
+        pass
+
+    lc.ListConfig = ListConfig
+    oc.listconfig = lc
+    sys.modules.setdefault('omegaconf', oc)
+    sys.modules.setdefault('omegaconf.listconfig', lc)
+
+
+def _runner(c):
+    """`run(perturbed, on_eval) -> final` for any case: builds the reference model once; every
+    run starts from reset caches.  `on_eval(i, eps, x)` sees each evaluation."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    kind = c.get("kind", "pixel")
+    wq, aq = cases.quant_params(c)
+    if kind == "pixel":
+        betas = torch.from_numpy(np.linspace(1e-4, 2e-2, 1000, dtype=np.float64)).float()
+        torch.manual_seed(0)
+        qnn = RefQuantModel(model=RefModel(ref_config(c["split"])).eval(), weight_quant_params=wq,
+                            act_quant_params=aq, sm_abit=8, modulate=True).eval()
+        qnn.set_quant_state(True, True)
+
+        def run(perturbed, on_eval=None):
+            qnn.reset_cache()
+            fn = cases.perturb_first_call(qnn) if perturbed else qnn
+            return ref_sample(fn, cases.unet_noise(c), cases.unet_sequence(c), betas, on_eval)
+        return run
+    from modiff_b200.ldm_unet import rerandomize_zero_tensors
+    from oracle.ldm import ldm_schedule, latent_ddim_sample, latent_plms_sample
+    if kind == "sd":
+        _sd_stub()
+    from ldm.modules.diffusionmodules.openaimodel import UNetModel as RefUNet
+    torch.manual_seed(0)
+    model = RefUNet(**(cases.SD_CONFIG if kind == "sd" else cases.LDM_CONFIG)).eval()
+    rerandomize_zero_tensors(model, seed=c["zero_seed"])
+    qnn = RefQuantModel(model=model, weight_quant_params=wq, act_quant_params=aq, sm_abit=8,
+                        modulate=True).eval()
+    qnn.set_quant_state(True, True)
+    qnn.set_grad_ckpt(False)
+    ac = ldm_schedule(**(cases.SD_SCHEDULE if kind == "sd" else cases.LDM_SCHEDULE))
+
+    def run(perturbed, on_eval=None):
+        qnn.reset_cache()
+        if kind == "sd":
+            x, cond, uncond = cases.sd_inputs(c)
+            fn = lambda a, t, ctx: qnn(a, t, ctx)  # noqa: E731
+            fn = cases.perturb_first_call(fn) if perturbed else fn
+            return latent_ddim_sample(x, fn, ac, c["ddim_steps"], max_evals=c.get("evals"),
+                                      cond=cond, uncond=uncond, guidance=c["guidance"],
+                                      on_step=on_eval)
+        fn = lambda a, t: qnn(a, t)  # noqa: E731
+        fn = cases.perturb_first_call(fn) if perturbed else fn
+        if kind == "plms":
+            return latent_plms_sample(cases.ldm_noise(c), fn, ac, c["ddim_steps"],
+                                      max_steps=c["steps"],
+                                      on_eval=(lambda k, e: on_eval(k, e, None)) if on_eval else None)
+        return latent_ddim_sample(cases.ldm_noise(c), fn, ac, c["ddim_steps"],
+                                  max_evals=c.get("evals"), on_step=on_eval)
+    return run
+
+
+def _sens(run, keep):
+    """Runs the reference twice (second time with the first evaluation perturbed, cases.SENS_REL)
+    and returns (final, kept trajectory points, per-evaluation PSNR between the runs, PSNR of
+    the finals)."""
+    base, kept = [], {}
+
+    def on_base(i, e, x):
+        base.append(e.numpy().copy())
+        if i in keep and x is not None:
+            kept[i] = x.numpy().copy()
+
+    final = run(False, on_base)
+    db = []
+    final_p = run(True, lambda i, e, x: db.append(_psnr(base[i], e.numpy())))
+    return final, kept, np.asarray(db, dtype=np.float32), _psnr(final.numpy(), final_p.numpy())
+
+
+def gen_sens():
+    """Self-sensitivity of the reference on the short whole-model cases (sens.npz)."""
+    out = {}
+    todo = [dict(c, kind="pixel") for c in cases.UNET_CASES if c["quant"]]
+    todo += [dict(c, kind="ldm") for c in cases.LDM_CASES]
+    todo += [dict(c, kind="plms") for c in cases.PLMS_CASES]
+    todo += [dict(c, kind="sd") for c in cases.SD_CASES]
+    for c in todo:
+        t0 = time.time()
+        _, _, db, fin = _sens(_runner(c), ())
+        out[c["name"] + "/sens_db"] = db
+        out[c["name"] + "/final_sens_db"] = np.float32(fin)
+        print(c["name"], f"{time.time() - t0:.1f}s", np.round(db[:12], 1), round(fin, 1), flush=True)
+        np.savez_compressed(os.path.join(HERE, "sens.npz"), **out)
+    print("sens.npz", len(out))
+
+
+def gen_full():
+    """Full-length sampler loops (cases.FULL_CASES), one file per case: the final tensor, the
+    state after a few evaluations, and the reference's self-sensitivity along the whole run.
+    `--case NAME` limits the run to one case."""
+    pick = sys.argv[sys.argv.index("--case") + 1] if "--case" in sys.argv else None
+    for c in cases.FULL_CASES:
+        if pick not in (None, c["name"]):
+            continue
+        t0 = time.time()
+        n = {"pixel": c.get("steps"), "ldm": 500, "sd": c.get("ddim_steps")}[c["kind"]]
+        keep = sorted({n // 10, n // 4, n // 2, 3 * n // 4})
+        final, kept, db, fin = _sens(_runner(c), keep)
+        out = {"final": final.numpy().copy(), "sens_db": db, "final_sens_db": np.float32(fin)}
+        for i, x in kept.items():
+            out[f"x_after{i}"] = x
+        np.savez_compressed(os.path.join(HERE, f"full_{c['name']}.npz"), **out)
+        print(c["name"], f"{time.time() - t0:.1f}s", float(final.std()), "final sens", round(fin, 1),
+              "min sens", float(db.min()), flush=True)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(os.cpu_count())
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
-                ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali, running=gen_running)
+                ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali, running=gen_running,
+                sens=gen_sens, full=gen_full)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()

@@ -398,3 +398,36 @@ def test_int4_pack_roundtrip(cuda):
     assert torch.equal(ops.unpack_int4(packed, 1001).cpu(), codes)
     u = torch.randint(0, 16, (64,), dtype=torch.int8)
     assert torch.equal(ops.unpack_int4(ops.pack_int4(u.to(cuda)), 64, signed=False).cpu(), u)
+
+
+@pytest.mark.parametrize("mode,n", [(1, 128), (1, 256), (2, 128), (2, 256)])
+def test_i8_mma_probe_layout(cuda, mode, n):
+    """The tensor-pipe probe's accumulators equal iters * A B^T exactly, for a single CTA
+    (cta_group::1, M = 128) and for a CTA pair (cta_group::2, M = 256 with A's rows and B's
+    rows split between the two CTAs' shared memory): pins the operand and accumulator layout
+    both GEMM issue modes rely on."""
+    L = _lib()
+    units, iters = 2, 3
+    m = 128 * mode
+    g = torch.Generator().manual_seed(40 + n + mode)
+    a = torch.randint(-127, 128, (units * m, 128), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, 128), generator=g, dtype=torch.int8)
+    acc = torch.zeros(m, n, dtype=torch.int32, device=cuda)
+    dbg = torch.full((4,), -1, dtype=torch.int32, device=cuda)
+    a_d, b_d = a.to(cuda), b.to(cuda)
+    L.call('modiff_i8_mma_probe', mode, n, iters, units, a_d.data_ptr(), b_d.data_ptr(),
+           acc.data_ptr(), dbg.data_ptr(), L.stream_ptr())
+    torch.cuda.synchronize()
+    assert L.device_status() == 0, "the probe gave up on a bounded wait"
+    print("tensor-memory bases / ranks of unit 0:", dbg.cpu().tolist())
+    want = iters * (a[:m].to(torch.int64) @ b.to(torch.int64).t())
+    assert torch.equal(acc.cpu().to(torch.int64), want)
+
+
+def test_i8_peak_is_plausible(cuda):
+    """The measured kind::i8 ceiling lies between a quarter of and a little above the nominal
+    4.5 POPS (a sanity check of the probe's operation count, not a performance assertion)."""
+    L = _lib()
+    tops = L.measure_i8_peak(mode=1, umma_n=256, iters=2048, repeats=3)
+    print(f"kind::i8 ceiling, cta_group::1 N=256: {tops:.0f} TOPS")
+    assert 1100 < tops < 5500, tops

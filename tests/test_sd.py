@@ -9,6 +9,7 @@ import torch
 
 import cases
 import oracle
+from conftest import sens_floor
 from oracle.ldm import OracleLDMUNet, ldm_schedule, latent_ddim_sample
 
 GOLDEN = os.path.dirname(os.path.abspath(cases.__file__))
@@ -57,7 +58,7 @@ def test_oracle_matches_reference_first_eval(golden_sd):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("c", cases.SD_CASES, ids=lambda c: c["name"])
-def test_cuda_path_matches_reference(c, cuda, golden_sd):
+def test_cuda_path_matches_reference(c, cuda, golden_sd, golden_sens):
     import modiff_b200 as m
     net = _build()
     wq, aq = cases.quant_params(c)
@@ -72,7 +73,7 @@ def test_cuda_path_matches_reference(c, cuda, golden_sd):
                               conditioning=cond.to(cuda), x_T=x.to(cuda), max_evals=c["evals"],
                               unconditional_guidance_scale=c["guidance"],
                               unconditional_conditioning=uncond.to(cuda),
-                              img_callback=lambda e, i: eps.append(e.clone()))
+                              eps_callback=lambda e, i: eps.append(e.clone()))
     torch.cuda.synchronize()
     assert m.device_status() == 0
     for i, e in enumerate(eps):
@@ -88,12 +89,14 @@ def test_cuda_path_matches_reference(c, cuda, golden_sd):
             # Free-running modulated evaluations are not reproducible between two machines:
             # the residual step is ~1/127 of an already small residual, so a 1e-4 difference
             # left by evaluation 0 puts many codes on the other side of a rounding boundary,
-            # 282 layers compound it and guidance 7.5 multiplies it.  The CPU oracle run twice,
-            # once with evaluation 0 disturbed by 1e-4 of its range, agrees with itself to
-            # 29.7 dB / 30.9 dB on evaluations 1 / 2 and 51.5 dB on the final latent; the CUDA
-            # path measures 29.7 dB on evaluation 1.  Layer arithmetic at these shapes is
-            # checked with identical inputs in test_sd_layer_shapes_teacher_forced.
-            assert p >= 25.0, (i, p)
+            # 282 layers compound it and guidance 7.5 multiplies it.  The floor is what the
+            # REFERENCE itself reaches against a copy of itself whose evaluation 0 was disturbed
+            # by 1e-4 of its range (sens.npz, written by make_golden.py: about 30 dB on
+            # evaluations 1 and 2, 51.5 dB on the final latent), minus a margin.  Layer
+            # arithmetic at these shapes is checked with identical inputs in
+            # test_sd_layer_shapes_teacher_forced.
+            floor_db = sens_floor(golden_sens, c["name"], i)
+            assert p >= floor_db, (i, p, floor_db)
     assert oracle.psnr(golden_sd[c["name"] + "/final"], final.cpu().numpy()) >= 40.0
 
 

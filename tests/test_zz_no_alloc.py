@@ -4,8 +4,9 @@ Some hosts of this library may not allocate device memory while they run (their 
 partitioned once at start-up, and a cudaMalloc in the hot loop both stalls the device and can
 fail against that fixed budget), and they have no spare buffer to lend as scratch.  For them the
 library carries a small built-in scratch array.  This test drives that entry point through the
-C ABI and requires bit-identical codes, cache and scales to modiff_modq (caller-owned scratch)
-on two consecutive calls, because the built-in array is shared and keeps the previous call's
+C ABI and requires bit-identical codes, cache and scales to modiff_modq (caller-owned scratch),
+and the same scales and cache as the CPU restatement of the reference quantiser, on two
+consecutive calls, because the built-in array is shared and keeps the previous call's
 contents.  The file name sorts last so every other test has already run when this one does.
 """
 import ctypes as C
@@ -49,12 +50,23 @@ def test_static_scratch_matches_caller_scratch_twice(cuda, shape, bits, split, p
     a_ref, a_new = a0.clone(), a0.clone()
     for call in range(2):          # two calls in a row: the second sees the first one's leftovers
         x = a0 + 0.1 * (call + 1) * torch.randn(shape, device=cuda)
+        a_before = a_new.clone()
         codes_ref, scale_ref = _run("modiff_modq", x, a_ref, g, bits, per_sample, cuda)
         codes_new, scale_new = _run("modiff_modq_static", x, a_new, g, bits, per_sample, cuda)
         assert torch.equal(codes_new, codes_ref), f"codes differ on call {call}"
         assert torch.equal(scale_new, scale_ref), f"scales differ on call {call}"
         assert torch.equal(a_new, a_ref), f"a_hat differs on call {call}"
         assert int(codes_ref.to(torch.int32).abs().sum()) > 0
+        if not per_sample:
+            # and directly against the CPU restatement of the reference quantiser: the scale of
+            # every segment and the updated cache (cache + codes * scale) must be the same bits
+            from oracle.quantizer import fake_quant
+            r = (x - a_before).cpu()
+            segs = [r[:, :split], r[:, split:]] if split else [r]
+            outs = [fake_quant(sg, bits, True) for sg in segs]
+            assert [float(v) for v in scale_new[:len(segs)].cpu()] == [float(o[2]) for o in outs]
+            upd = torch.cat([o[1] * o[2] for o in outs], dim=1)
+            assert torch.equal(a_new.cpu(), a_before.cpu() + upd), f"a_hat vs oracle, call {call}"
 
 
 def test_static_scratch_rejects_oversized_batch(cuda):
