@@ -244,6 +244,9 @@ def main():
     ap.add_argument("--asym", action="store_true",
                     help="asymmetric activation quantisers (the latent drivers' default without "
                          "--a_sym); the headline lines use symmetric ones")
+    ap.add_argument("--int8-attention", action="store_true",
+                    help="integer attention kernel (q / k / v / softmax quantisers applied; the "
+                         "reference leaves them unapplied, so the headline lines keep it off)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-full", action="store_true",
                     help="time the CPU baseline on ALL steps of a batch-8 pass instead of the "
@@ -276,7 +279,8 @@ def main():
     host_in = []
     if kind == "pixel":
         net = m.Model(m.make_config(split_shortcut=cfg["split"])).eval()
-        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(dev).eval()
+        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True,
+                           int8_attention=args.int8_attention).to(dev).eval()
         qnn.set_quant_state(True, True)
         betas = torch.from_numpy(m.get_beta_schedule()).float()
         seq = m.make_timestep_sequence(1000, cfg["evals"], "quad")[-evals:]
@@ -291,7 +295,8 @@ def main():
         sd = kind == "sd"
         net = m.UNetModel(**(SD_V1 if sd else LSUN_CHURCHES_KL8)).eval()
         m.rerandomize_zero_tensors(net)
-        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True).to(dev).eval()
+        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True,
+                           int8_attention=args.int8_attention).to(dev).eval()
         qnn.set_quant_state(True, True)
         qnn.set_grad_ckpt(False)
         sched = dict(linear_start=0.00085, linear_end=0.0120) if sd else \
@@ -321,6 +326,8 @@ def main():
         workload = "STATIC activation scales (quant_mode qdiff): " + workload
     if args.asym:
         workload += ", asymmetric activation codes"
+    if args.int8_attention:
+        workload += ", INT8 attention (q / k / v / softmax quantisers applied)"
 
     out_host = torch.empty((world * batch,) + tuple(shape[1:])).pin_memory()
     dev_in = [t.to(dev) for t in host_in]

@@ -535,6 +535,42 @@ int modiff_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n, int is_s
 int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
                            const modiff_conv_geom* g, int n_bits, void* stream);
 
+/* Stand-alone fake quantisation of a weight tensor with learned (AdaRound) hard rounding
+ * (qdiff/adaptive_rounding.py:49-61, soft_targets False), what AdaRoundQuantizer.forward returns:
+ *   out = (clamp(floor(w / delta) + (alpha >= 0) + zero_point, 0, 2^b - 1) - zero_point) * delta
+ *   w, alpha, out  fp32 [rows][row_len];  delta, zero_point fp32 [rows] (per_row != 0) or [1] */
+int modiff_adaround_fake_quant(const float* w, const float* alpha, const float* delta,
+                               const float* zero_point, float* out, int64_t rows, int64_t row_len,
+                               int per_row, int n_bits, void* stream);
+
+/* Integer attention (opt-in).  The reference constructs 8-bit quantisers for q, k, v and for the
+ * softmax output on every attention block (qdiff/quant_block.py:120-121, 139-144, 223-235,
+ * 331-335) but never applies them (:123-128, 146-148, 181-203, 338-366 stay in floating point);
+ * these two entry points apply them.  Exact definition: oracle/attention_i8.py.
+ *
+ * modiff_attn_quantize: per-tensor symmetric dynamic codes of q, k, v (absmax over the whole
+ * tensor, delta = absmax / (2^(n_bits-1) - 1), floor 1e-8) in the layouts the MMAs read.
+ *   q, k, v       fp32, addressed as x[b*s0 + h*s1 + c*s2 + t*s3] with the four element strides
+ *                 of strides_q (q) / strides_kv (k and v); channels or tokens contiguous
+ *   q_codes       int8 [batch*heads][tq][dp], dp = 128 (c <= 128) or 256, zero padded
+ *   k_codes       int8 [batch*heads][tk][dp]
+ *   v_codes       int8 [batch*heads][round_up(c,16)][round_up(tk,128)], zero padded
+ *                 (sizes: modiff_attn_codes_bytes(batch*heads, c, tq, tk, which = 0 / 1 / 2))
+ *   scales        fp32 [3] out: delta of q, k, v
+ *   scratch       16 bytes, zero on entry, left zero
+ * modiff_attention_i8: out = softmax(scale * q k^T) v from those codes: both products as int8
+ * tensor-core MMAs with int32 accumulation, fp32 softmax with the exact row maximum, softmax
+ * weights as unsigned 8-bit codes rne(255 * exp(s - max)), renormalised by their integer sum.
+ *   out           fp32, addressed with the four element strides of strides_out like q */
+int64_t modiff_attn_codes_bytes(int heads_total, int c, int tq, int tk, int which);
+int modiff_attn_quantize(const float* q, const float* k, const float* v, int batch, int heads,
+                         int c, int tq, int tk, const int64_t* strides_q,
+                         const int64_t* strides_kv, int n_bits, int8_t* q_codes, int8_t* k_codes,
+                         int8_t* v_codes, float* scales, void* scratch, void* stream);
+int modiff_attention_i8(const int8_t* q_codes, const int8_t* k_codes, const int8_t* v_codes,
+                        const float* scales, float* out, int batch, int heads, int c, int tq,
+                        int tk, const int64_t* strides_out, float scale, void* stream);
+
 /* Tensor-pipe probe of tcgen05.mma kind::i8 (measurement aid; no counterpart in the reference,
  * whose convolutions are PyTorch fp32, qdiff/quant_layer.py:345-365).  Every unit holds a
  * 128-row A tile per CTA and the B tile in shared memory (K = 128 bytes) and repeats the four
@@ -547,6 +583,13 @@ int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
  *   debug   optional int32 [4]: tensor-memory base address seen by each CTA of unit 0 */
 int modiff_i8_mma_probe(int mode, int umma_n, int iters, int units, const int8_t* a,
                         const int8_t* b, int32_t* acc_out, int* debug, void* stream);
+
+/* Failure-path probe (no counterpart in the reference): one thread waits, with the same bounded
+ * wait the tensor-core kernels use, on a barrier that nothing ever signals.  After `limit_ns`
+ * (at most 1e9) it gives up, sets bit 0 of the device status word and the kernel returns
+ * normally; `gave_up` (device int, may be NULL) receives 1.  Lets a host check its handling of
+ * modiff_device_status without a copy, a peer or tensor memory being involved. */
+int modiff_wait_probe(int64_t limit_ns, int* gave_up, void* stream);
 
 #ifdef __cplusplus
 }

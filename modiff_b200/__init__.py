@@ -13,6 +13,7 @@ from .ldm_unet import UNetModel, rerandomize_zero_tensors
 from .ldm_sampler import DDIMSampler, PLMSSampler
 from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
                       make_timestep_sequence)
+from .calibration import generate_calibration_data, select_calibration_points
 
 __all__ = [
     "ModiffError", "lib", "device_status", "QuantModule", "UniformAffineQuantizer",
@@ -21,5 +22,6 @@ __all__ = [
     "QuantAttentionBlock", "AdaRoundQuantizer", "convert_adaround", "resume_cali_model",
     "load_calibrated_state",
     "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "PLMSSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
-    "get_beta_schedule", "make_timestep_sequence",
+    "get_beta_schedule", "make_timestep_sequence", "generate_calibration_data",
+    "select_calibration_points",
 ]

@@ -131,6 +131,13 @@ SIGNATURES = {
     "modiff_unpack_int4": (C.c_int, [_P, _P, C.c_int64, C.c_int, _P]),
     "modiff_quantize_static": (C.c_int, [_P, _P, _P, _G, C.c_int, _P]),
     "modiff_i8_mma_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, _P]),
+    "modiff_wait_probe": (C.c_int, [C.c_int64, _P, _P]),
+    "modiff_adaround_fake_quant": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int,
+                                             C.c_int, _P]),
+    "modiff_attn_codes_bytes": (C.c_int64, [C.c_int] * 5),
+    "modiff_attn_quantize": (C.c_int, [_P, _P, _P] + [C.c_int] * 5 + [_P, _P, C.c_int, _P, _P, _P,
+                                                                   _P, _P, _P]),
+    "modiff_attention_i8": (C.c_int, [_P, _P, _P, _P, _P] + [C.c_int] * 5 + [_P, C.c_float, _P]),
 }
 
 _lib = None
@@ -160,7 +167,8 @@ KERNELS_PER_CALL = {
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_layernorm": 1, "modiff_geglu": 1, "modiff_transpose": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,
     "modiff_ddim_step": 1, "modiff_cfg_combine": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
-    "modiff_quantize_static": 1, "modiff_i8_mma_probe": 1,
+    "modiff_quantize_static": 1, "modiff_i8_mma_probe": 1, "modiff_wait_probe": 1,
+    "modiff_attn_quantize": 2, "modiff_attention_i8": 1, "modiff_adaround_fake_quant": 1,
 }
 LAUNCHES = [0]        # kernels launched through `call` since import
 # Bumped whenever a layer allocates or replaces a device buffer that kernels address directly

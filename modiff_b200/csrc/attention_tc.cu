@@ -147,46 +147,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All lanes walk the loop (descriptors and addresses stay warp-uniform values); one
+    // elected lane issues the MMAs and commits.
+    {
       const uint32_t idesc_s = make_idesc_bf16(128, p.n_s);
       const uint32_t idesc_o = make_idesc_bf16(128, p.crow);
       int stage = 0;
       uint32_t phase = 0, tphase = 0, pphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        bool first_pv = true;
-        for (int sb = 0; sb < p.nsb && ok; ++sb) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        uint32_t fresh_pv = 1u;
+        for (int sb = 0; sb < p.nsb; ++sb) {
           // phase 1: scores of this key block.  The softmax has finished reading the previous
           // block's scores (its last p_ready preceded the MMAs issued just before this point).
-          for (int it = 0; it < 3 * p.cch && ok; ++it) {
+          for (int it = 0; it < 3 * p.cch; ++it) {
             ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t a_src = ring + stage * kStage;
             const uint64_t adesc = make_smem_desc(a_src);
             const uint64_t bdesc = make_smem_desc(a_src + kATile);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc_mma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc_s,
-                          (it > 0 || k > 0) ? 1u : 0u);
-            tc_commit(smem_u32(&bar_empty[stage]));
+              for (int k = 0; k < 4; ++k)
+                tc_mma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc_s,
+                            (it > 0 || k > 0) ? 1u : 0u);
+              tc_commit(smem_u32(&bar_empty[stage]));
+            }
+            __syncwarp();
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          tc_commit(smem_u32(&bar_s_full));
+          if (elect_one()) tc_commit(smem_u32(&bar_s_full));
+          __syncwarp();
           // phase 3, 128 keys at a time: the probability planes of one half sit in shared memory
           // while the epilogue warps wait to write the next half; the tile's first product also
           // needs the previous tile's output drained
           const int kch = min(4, (p.tkp - sb * 256) >> 6);
           const int halves = (kch + 1) >> 1;
-          for (int kh = 0; kh < halves && ok; ++kh) {
+          for (int kh = 0; kh < halves; ++kh) {
             ok = mbar_wait(smem_u32(&bar_p_ready), pphase, abort_flag);
             pphase ^= 1u;
-            if (ok && first_pv) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
+            if (ok && fresh_pv) ok = mbar_wait(smem_u32(&bar_o_empty), tphase ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int kc_end = min(kch, 2 * kh + 2);
-            for (int kc = 2 * kh; kc < kc_end && ok; ++kc) {
+            for (int kc = 2 * kh; kc < kc_end; ++kc) {
               for (int pr = 0; pr < 3; ++pr) {
                 ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
                 if (!ok) break;
@@ -194,20 +200,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const uint64_t adesc =
                     make_smem_desc(p_smem + (uint32_t)((prod_a(pr) * 2 + (kc & 1)) * kATile));
                 const uint64_t bdesc = make_smem_desc(ring + stage * kStage + kATile);
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                              idesc_o, (first_pv && k == 0) ? 0u : 1u);
-                  first_pv = false;
+                  for (int k = 0; k < 4; ++k)
+                    tc_mma_bf16(tmem_base + 256u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                                idesc_o, (fresh_pv && k == 0) ? 0u : 1u);
+                  tc_commit(smem_u32(&bar_empty[stage]));
                 }
-                tc_commit(smem_u32(&bar_empty[stage]));
+                __syncwarp();
+                fresh_pv = 0u;
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
               }
+              if (!ok) break;
             }
-            if (ok) tc_commit(smem_u32(&bar_p_free));
+            if (!ok) break;
+            if (elect_one()) tc_commit(smem_u32(&bar_p_free));
+            __syncwarp();
           }
+          if (!ok) break;
         }
-        if (ok) tc_commit(smem_u32(&bar_o_full));
+        if (!ok) break;
+        if (elect_one()) tc_commit(smem_u32(&bar_o_full));
+        __syncwarp();
         tphase ^= 1u;
       }
     }

@@ -146,18 +146,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All lanes walk the loop (descriptors and addresses stay warp-uniform values); one
+    // elected lane issues the MMAs and commits.
+    {
       const uint32_t idesc = make_idesc_bf16(kTileM, p.umma_n);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t bphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
         ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), bphase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        for (int seg = 0; seg < p.nseg && ok; ++seg) {
+        for (int seg = 0; seg < p.nseg; ++seg) {
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.buf_cols + seg * p.umma_n);
           const int iters = products * p.d.taps * p.chunks[seg];
           for (int it = 0; it < iters; ++it) {
@@ -167,15 +169,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t a_src = ring + stage * kStageBytes;
             const uint64_t adesc = make_smem_desc(a_src);
             const uint64_t bdesc = make_smem_desc(a_src + kATileBytes);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < kChunkBytes / 32; ++k)
-              tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                          (it > 0 || k > 0) ? 1u : 0u);
-            tc_commit(smem_u32(&bar_empty[stage]));
+              for (int k = 0; k < kChunkBytes / 32; ++k)
+                tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            (it > 0 || k > 0) ? 1u : 0u);
+              tc_commit(smem_u32(&bar_empty[stage]));
+            }
+            __syncwarp();
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
+          if (!ok) break;
         }
-        if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        if (!ok) break;
+        if (elect_one()) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        __syncwarp();
         if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
       }
     }

@@ -152,6 +152,26 @@ __global__ void __launch_bounds__(kProbeThreads, 1) i8_probe_kernel(const ProbeP
   }
 }
 
+// A wait that nothing satisfies: the barrier expects one arrival and no thread arrives.  The
+// waiting thread gives up after `limit_ns`, records it in the status word and the kernel
+// returns normally: the path every tensor-core kernel takes when a copy or a peer never
+// signals, exercised here without any copy or tensor-memory allocation in flight.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_sh;
+  if (threadIdx.x == 0) {
+    abort_sh = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_limit(smem_u32(&bar), 0u, &abort_sh, limit_ns);
+    if (gave_up) *gave_up = ok ? 0 : 1;
+  }
+  __syncthreads();
+}
+
 }  // namespace
 
 int read_device_status_probe(int* status, int reset) { return read_status_this_unit(status, reset); }
@@ -200,5 +220,13 @@ extern "C" int modiff_i8_mma_probe(int mode, int umma_n, int iters, int units, c
     MODIFF_CUDA(cudaLaunchKernelEx(&cfg, i8_probe_kernel<2>, p));
   }
   MODIFF_LAUNCH_CHECK("i8_probe_kernel");
+  return MODIFF_OK;
+}
+
+extern "C" int modiff_wait_probe(int64_t limit_ns, int* gave_up, void* stream) {
+  MODIFF_CHECK_ARG(limit_ns > 0 && limit_ns <= 1000000000ll,
+                   "limit_ns must lie in (0, 1e9]: the probe is meant to give up quickly");
+  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, gave_up);
+  MODIFF_LAUNCH_CHECK("wait_probe_kernel");
   return MODIFF_OK;
 }

@@ -11,14 +11,22 @@
 //     later.  3 activation copies per K chunk instead of 9.
 //   - with 256 pixels per tile two M=128 MMAs share every weight tile.
 // Accumulators: int32 in tensor memory, [buffer][m-half][128 columns], double buffered.
-// Epilogue as in igemm_tc_kernel: cached-output half tiles (64 channels x 128 pixels) travel
-// by bulk tensor copies through a small ring, out = o_hat + acc * (delta_x * delta_w[c]).
-// Roles: warp 0 operand TMA, warp 1 MMA issue, warps 2-9 epilogue, warp 10 cached-output
-// stores, warp 11 cached-output loads.  Every mbarrier wait is bounded.
+// Epilogue: the cached output o_hat arrives in half tiles (64 channels x 128 pixels) by bulk
+// tensor copies through a ring of two or three shared-memory slots; a slot is released as soon
+// as the epilogue warps have read it into registers, and out = o_hat + acc * (delta_x *
+// delta_w[c]) is stored straight from registers (a lane is a pixel: 128 consecutive bytes per
+// channel and warp).  An earlier version sent the new values back through the same slot with a
+// bulk store; the slot then stayed busy for load latency + epilogue + store drain, and that round
+// trip, not the operand feed or the tensor pipe, set the kernel's pace (the L2-to-SM port was
+// 17 % busy, the tensor pipe 31 %).
+// Roles: warp 0 operand TMA, warp 1 MMA issue, warps 2-9 epilogue, warp 10 cached-output loads.
+// Every mbarrier wait is bounded.
 //
 // Reference arithmetic: qdiff/quant_layer.py:345-365.
 #include "common.cuh"
 #include "tc_common.cuh"
+
+#include <cstdlib>
 
 namespace modiff {
 namespace {
@@ -26,12 +34,11 @@ namespace {
 constexpr int kChunkK = 128;                     // bytes of K per weight tile row
 constexpr int kEpiWarps = 8;
 constexpr int kMaxASlots = 3;
-constexpr int kOSlots = 2;
+constexpr int kMaxOSlots = 3;
 constexpr int kOHalfBytes = 64 * 128 * 4;        // 64 channels x 128 pixels fp32
 constexpr int kMaxBStages = 6;
-constexpr int kStoreWarp = 2 + kEpiWarps;
-constexpr int kLoadWarp = 3 + kEpiWarps;
-constexpr int kThreads = 32 * (4 + kEpiWarps);
+constexpr int kLoadWarp = 2 + kEpiWarps;
+constexpr int kThreads = 32 * (3 + kEpiWarps);
 
 struct HaloParams {
   int w, h, batch, cout;
@@ -39,7 +46,9 @@ struct HaloParams {
   int mh;               // 128-pixel halves per tile: 1 or 2
   int half_rows;        // rows / mh
   int tiles_h;          // h / rows
-  int n_tiles;          // cout / 128
+  int n_tiles;          // cout / n_real
+  int n_real;           // output channels per tile: 128, or 256 (plain 128-row weight tiles only)
+  int nbuf;             // accumulator buffers in tensor memory: 2, or 1 when mh * umma_n = 512
   int total_tiles;
   int chunks;           // 128-byte K chunks per tap
   int kp;               // weight K stride per tap
@@ -48,8 +57,10 @@ struct HaloParams {
   int a_slot_bytes;
   int a_slots;          // activation copies in flight (2..4)
   int tmem_cols;
+  int o_slots;          // cached-output half tiles in flight (2 or 3)
+  float* o_out;         // the cached output itself: new values are stored straight from registers
   int accumulate;
-  int umma_n;           // 128, or 144 with the receptive-field-sum rows (zero-point correction)
+  int umma_n;           // 128 or 256, or 144 with the receptive-field-sum rows (zero-point correction)
   int b_tile_bytes;     // umma_n * 128
   const float* x_scale;
   const float* w_scale;
@@ -80,12 +91,12 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ __align__(8) uint64_t bar_a_full[kMaxASlots], bar_a_empty[kMaxASlots];
   __shared__ __align__(8) uint64_t bar_b_full[kMaxBStages], bar_b_empty[kMaxBStages];
   __shared__ __align__(8) uint64_t bar_tmem_full[2], bar_tmem_empty[2];
-  __shared__ __align__(8) uint64_t bar_o_full[kOSlots], bar_o_empty[kOSlots], bar_o_ready[kOSlots];
+  __shared__ __align__(8) uint64_t bar_o_full[kMaxOSlots], bar_o_empty[kMaxOSlots];
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
-  __shared__ float ep_scale[128];
-  __shared__ int ep_corr[128];
-  __shared__ int ep_off[128];
+  __shared__ float ep_scale[256];
+  __shared__ int ep_corr[256];
+  __shared__ int ep_off[256];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -112,10 +123,9 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[b]), kEpiWarps);
     }
-    for (int b = 0; b < kOSlots; ++b) {
+    for (int b = 0; b < p.o_slots; ++b) {
       mbar_init(smem_u32(&bar_o_full[b]), 1);
-      mbar_init(smem_u32(&bar_o_empty[b]), 1);
-      mbar_init(smem_u32(&bar_o_ready[b]), kEpiWarps);
+      mbar_init(smem_u32(&bar_o_empty[b]), kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -165,18 +175,23 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (waits included) and one elected lane issues: descriptors
+    // and addresses are then warp-uniform values.  With a single lane running the loop the
+    // issue of one MMA took about 130 cycles, twice the 64 cycles the MMA occupies the tensor
+    // pipe, and the issuing thread - not the operand feed, the epilogue or the tensor pipe -
+    // set the pace of the kernel.
+    {
       const uint32_t idesc = make_idesc_i8(128, p.umma_n);
       int aslot = 0, bst = 0, buf = 0;
       uint32_t aphase = 0, bphase = 0, tphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
         ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), tphase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        bool first = true;
-        for (int ch = 0; ch < p.chunks && ok; ++ch) {
-          for (int dx = 0; dx < 3 && ok; ++dx) {
+        uint32_t fresh = 1u;        // the tile's first MMA overwrites the accumulator
+        for (int ch = 0; ch < p.chunks; ++ch) {
+          for (int dx = 0; dx < 3; ++dx) {
             ok = mbar_wait(smem_u32(&bar_a_full[aslot]), aphase, abort_flag);
             if (!ok) break;
             const uint32_t a_base = a_ring + aslot * (uint32_t)p.a_slot_bytes;
@@ -185,27 +200,38 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
               if (!ok) break;
               tc_fence_after();
               const uint64_t bdesc = make_smem_desc(b_ring + bst * b_tile);
-              for (int m = 0; m < p.mh; ++m) {
-                // rows m*half_rows+dy .. of the copy: a whole number of 1024-byte swizzle periods
-                const uint64_t adesc = make_smem_desc(
-                    a_base + (uint32_t)((m * p.half_rows + dy) * p.w) * (uint32_t)kChunkK);
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * buf_cols + m * p.umma_n);
+              // rows dy .. of the copy: a whole number of 1024-byte swizzle periods
+              const uint64_t adesc0 = make_smem_desc(a_base + (uint32_t)(dy * p.w) * (uint32_t)kChunkK);
+              const uint64_t adesc1 =
+                  make_smem_desc(a_base + (uint32_t)((p.half_rows + dy) * p.w) * (uint32_t)kChunkK);
+              const uint32_t d_tmem = tmem_base + (uint32_t)(buf * buf_cols);
+              if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < kChunkK / 32; ++k)
-                  tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                            (first && k == 0) ? 0u : 1u);
+                  tc_mma_i8(d_tmem, adesc0 + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                            (fresh && k == 0) ? 0u : 1u);
+                if (p.mh == 2) {
+#pragma unroll
+                  for (int k = 0; k < kChunkK / 32; ++k)
+                    tc_mma_i8(d_tmem + (uint32_t)p.umma_n, adesc1 + (uint64_t)(2 * k),
+                              bdesc + (uint64_t)(2 * k), idesc, (fresh && k == 0) ? 0u : 1u);
+                }
+                tc_commit(smem_u32(&bar_b_empty[bst]));
+                if (dy == 2) tc_commit(smem_u32(&bar_a_empty[aslot]));
               }
-              first = false;
-              tc_commit(smem_u32(&bar_b_empty[bst]));
+              __syncwarp();
+              fresh = 0u;
               if (++bst == p.b_stages) { bst = 0; bphase ^= 1u; }
             }
             if (!ok) break;
-            tc_commit(smem_u32(&bar_a_empty[aslot]));
             if (++aslot == p.a_slots) { aslot = 0; aphase ^= 1u; }
           }
+          if (!ok) break;
         }
-        if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
-        if (++buf == 2) { buf = 0; tphase ^= 1u; }
+        if (!ok) break;
+        if (elect_one()) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        __syncwarp();
+        if (++buf == p.nbuf) { buf = 0; tphase ^= 1u; }
       }
     }
   } else if (warp == kLoadWarp) {
@@ -217,44 +243,21 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const HaloTile t = decode(tile, p);
         for (int m = 0; m < p.mh && ok; ++m) {
-          for (int hh = 0; hh < 2; ++hh) {
+          for (int hh = 0; hh < p.n_real / 64; ++hh) {
             ok = mbar_wait(smem_u32(&bar_o_empty[oslot]), ophase ^ 1u, abort_flag);
             if (!ok) break;
             const uint32_t ofull = smem_u32(&bar_o_full[oslot]);
             if (p.accumulate) {
               mbar_arrive_expect_tx(ofull, (uint32_t)kOHalfBytes);
               tma_load_3d(obuf + oslot * kOHalfBytes, &map_o, ofull,
-                          (t.th * p.rows + m * p.half_rows) * p.w, t.nt * 128 + hh * 64, t.n);
+                          (t.th * p.rows + m * p.half_rows) * p.w, t.nt * p.n_real + hh * 64, t.n);
             } else {
               mbar_arrive(ofull);
             }
-            if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+            if (++oslot == p.o_slots) { oslot = 0; ophase ^= 1u; }
           }
         }
       }
-    }
-  } else if (warp == kStoreWarp) {
-    // ------------------------------------------------------------ cached-output stores
-    if (lane == 0) {
-      int oslot = 0;
-      uint32_t ophase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        const HaloTile t = decode(tile, p);
-        for (int m = 0; m < p.mh && ok; ++m) {
-          for (int hh = 0; hh < 2; ++hh) {
-            ok = mbar_wait(smem_u32(&bar_o_ready[oslot]), ophase, abort_flag);
-            if (!ok) break;
-            tma_store_3d(&map_o, obuf + oslot * kOHalfBytes,
-                         (t.th * p.rows + m * p.half_rows) * p.w, t.nt * 128 + hh * 64, t.n);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            mbar_arrive(smem_u32(&bar_o_empty[oslot]));
-            if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
-          }
-        }
-      }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
@@ -272,10 +275,10 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       const HaloTile t = decode(tile, p);
       if (t.nt != last_nt) {
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ep_tid < 128) {
-          ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * 128 + ep_tid]);
-          ep_corr[ep_tid] = p.w_corr ? p.w_corr[t.nt * 128 + ep_tid] : 0;
-          ep_off[ep_tid] = p.x_zp ? -((int)p.x_zp[0] - 128) * p.w_csum[t.nt * 128 + ep_tid] : 0;
+        if (ep_tid < p.n_real) {
+          ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * p.n_real + ep_tid]);
+          ep_corr[ep_tid] = p.w_corr ? p.w_corr[t.nt * p.n_real + ep_tid] : 0;
+          ep_off[ep_tid] = p.x_zp ? -((int)p.x_zp[0] - 128) * p.w_csum[t.nt * p.n_real + ep_tid] : 0;
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         last_nt = t.nt;
@@ -291,28 +294,39 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           tc_ld1(t_row + 128, rsum);
           tc_wait_ld();
         }
-        for (int hh = 0; hh < 2; ++hh) {
+        for (int hh = 0; hh < p.n_real / 64; ++hh) {
           const int colbase = hh * 64 + sub * 32;
-          // residual of the block (x + h, qdiff/quant_block.py:313): a lane is a pixel, so the 32
-          // lanes of a warp read 128 consecutive bytes per channel; issued before the wait below
+          // a lane is a pixel: for every channel the 32 lanes of a warp touch 128 consecutive
+          // bytes of the NCHW tensors
+          const size_t out_off = ((size_t)t.n * p.cout + t.nt * p.n_real + colbase) * (size_t)(p.h * p.w) +
+                                 (size_t)(t.th * p.rows + m * p.half_rows) * p.w + row;
+          // residual of the block (x + h, qdiff/quant_block.py:313): issued before the wait below
           // so that the loads are in flight while the cached-output tile arrives
           float res[32];
-          size_t res_off = 0;
           if (p.residual) {
-            res_off = ((size_t)t.n * p.cout + t.nt * 128 + colbase) * (size_t)(p.h * p.w) +
-                      (size_t)(t.th * p.rows + m * p.half_rows) * p.w + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) res[j] = __ldg(p.residual + res_off + (size_t)j * (p.h * p.w));
+            for (int j = 0; j < 32; ++j) res[j] = __ldg(p.residual + out_off + (size_t)j * (p.h * p.w));
           }
           ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
-          float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)(sub * 32) * 128 + row;
+          const float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)(sub * 32) * 128 + row;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * 128] : 0.0f;
+          // the slot is free for the next cached-output tile as soon as it has been read: the new
+          // values leave straight from registers, so no store has to drain from shared memory
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_o_empty[oslot]));
           int a[32];
           tc_ld32(t_row + colbase, a);
           tc_wait_ld();
+          const bool last = (m == p.mh - 1) && (hh == p.n_real / 64 - 1);
+          if (last) {
+            // the accumulator buffer can be overwritten once every warp has read its last columns
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+          }
           if (p.w_corr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) a[j] += ep_corr[colbase + j] * rsum;
@@ -324,25 +338,17 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) orow[j * 128] = v[j];
+          for (int j = 0; j < 32; ++j) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
           if (p.residual) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              p.sum_out[res_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+              p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
           }
-          const bool last = (m == p.mh - 1) && (hh == 1);
-          if (last) tc_fence_before();
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(smem_u32(&bar_o_ready[oslot]));
-            if (last) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-          }
-          if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
+          if (++oslot == p.o_slots) { oslot = 0; ophase ^= 1u; }
         }
       }
       if (!ok) break;
-      if (++buf == 2) { buf = 0; tphase ^= 1u; }
+      if (++buf == p.nbuf) { buf = 0; tphase ^= 1u; }
     }
   }
 
@@ -406,13 +412,22 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.h = g->h;
   p.batch = g->batch;
   p.cout = g->cout;
-  p.n_tiles = g->cout / 128;
-  // 256-pixel tiles halve the weight traffic but can leave the last wave emptier: compare
-  // shared-memory fill bytes per 128 output pixels divided by the wave efficiency
+  // Tile shape.  The pace of this kernel is set by how fast one thread can issue MMAs, so the
+  // fewer and larger they are the better: 256 output channels per MMA (UMMA N = 256, 128 cycles
+  // of the tensor pipe each) wherever the packed weights are plain 128-row tiles and the layer
+  // has a multiple of 256 channels, with 128-pixel tiles so that two accumulator buffers fit
+  // tensor memory (2 x 256 columns) and the epilogue overlaps the next tile's MMAs.  Otherwise
+  // 128 channels (144 rows with the receptive-field-sum rows) and 128 or 256 pixels.
   const int rows1 = 128 / g->w, rows2 = 256 / g->w;
   const int chunks = ceil_div(g->cin, kChunkK);
-  p.umma_n = with_sum_rows ? 144 : 128;
+  const char* force_n = getenv("MODIFF_HALO_N");      // measurement aid: "128" keeps N = 128
+  const bool wide = !with_sum_rows && g->cout % 256 == 0 && !(force_n && force_n[0] == '1');
+  p.umma_n = with_sum_rows ? 144 : (wide ? 256 : 128);
+  p.n_real = wide ? 256 : 128;
+  p.n_tiles = g->cout / p.n_real;
   p.b_tile_bytes = p.umma_n * kChunkK;
+  // 256-pixel tiles halve the weight traffic but can leave the last wave emptier: compare
+  // shared-memory fill bytes per 128 output pixels divided by the wave efficiency
   auto cost = [&](int mh) {
     const int rows = mh * rows1;
     const double fill = (3.0 * chunks * (rows + 2) * g->w * kChunkK + 9.0 * chunks * p.b_tile_bytes) / mh +
@@ -421,7 +436,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   };
   p.mh = 1;
   // two m-halves of 144 columns, double buffered, would need 576 of the 512 tensor-memory columns
-  if (!with_sum_rows && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
+  if (!with_sum_rows && !wide && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
+  p.nbuf = 2;
   p.rows = p.mh * rows1;
   p.half_rows = rows1;
   p.tiles_h = g->h / p.rows;
@@ -430,16 +446,20 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.kp = d.kp;
   p.a_bytes = (p.rows + 2) * g->w * kChunkK;
   p.a_slot_bytes = round_up(p.a_bytes, 1024);
-  // a third activation copy in flight where it leaves four weight stages (measured: 80 -> 76 us
-  // with 128-pixel tiles; a fourth gains nothing: the kernel is bound by the shared-memory fill
-  // bandwidth, not by the latency of a copy)
+  // shared memory: at least two activation copies, two cached-output half tiles and four weight
+  // stages; what is left goes first to a third cached-output tile (its load latency from HBM is
+  // the longest in the kernel), then to a third activation copy, then to weight stages
+  const int budget = 222 * 1024;
   p.a_slots = 2;
-  if (224 * 1024 - 3 * p.a_slot_bytes - kOSlots * kOHalfBytes >= 4 * p.b_tile_bytes) p.a_slots = 3;
-  const int fixed = p.a_slots * p.a_slot_bytes + kOSlots * kOHalfBytes;
-  p.b_stages = (224 * 1024 - fixed) / p.b_tile_bytes;
+  p.o_slots = 2;
+  auto left = [&]() { return budget - p.a_slots * p.a_slot_bytes - p.o_slots * kOHalfBytes; };
+  if (left() - kOHalfBytes >= 3 * p.b_tile_bytes) p.o_slots = 3;
+  if (left() - p.a_slot_bytes >= 4 * p.b_tile_bytes) p.a_slots = 3;
+  const int fixed = p.a_slots * p.a_slot_bytes + p.o_slots * kOHalfBytes;
+  p.b_stages = (budget - fixed) / p.b_tile_bytes;
   if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
   if (p.b_stages < 2) return set_error(MODIFF_ERR_UNSUPPORTED, "tile does not fit shared memory");
-  p.tmem_cols = (2 * p.mh * p.umma_n) > 256 ? 512 : 256;
+  p.tmem_cols = (p.nbuf * p.mh * p.umma_n) > 256 ? 512 : 256;
   p.accumulate = accumulate;
   p.x_scale = x_scale;
   p.w_scale = w_scale;
@@ -448,6 +468,7 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.w_csum = w_csum;
   p.residual = residual;
   p.sum_out = sum_out;
+  p.o_out = o_hat;
   const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes;
 
   CUtensorMap map_a, map_b, map_o;
@@ -497,5 +518,6 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
 }
 
 int read_device_status_halo(int* status, int reset) { return read_status_this_unit(status, reset); }
+
 
 }  // namespace modiff

@@ -202,18 +202,20 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // All lanes walk the loop (descriptors and addresses stay warp-uniform values); one
+    // elected lane issues the MMAs and commits.
+    {
       const uint32_t idesc = make_idesc_i8(kTileM, p.umma_n);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t bphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
         ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), bphase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        for (int seg = 0; seg < p.nseg && ok; ++seg) {
+        for (int seg = 0; seg < p.nseg; ++seg) {
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.buf_cols + seg * p.umma_n);
           const int iters = seg == 0 ? k_iters_seg0 : k_iters_seg1;
           for (int it = 0; it < iters; ++it) {
@@ -223,17 +225,23 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t a_src = ring + stage * stage_bytes;
             const uint64_t adesc = make_smem_desc(a_src);
             const uint64_t bdesc = make_smem_desc(a_src + kATileBytes);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < kChunkK / 32; ++k) {
-              // advancing K by 32 bytes inside the swizzle atom = +2 in the address field
-              tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                        (it > 0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kChunkK / 32; ++k) {
+                // advancing K by 32 bytes inside the swizzle atom = +2 in the address field
+                tc_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                          (it > 0 || k > 0) ? 1u : 0u);
+              }
+              tc_commit(smem_u32(&bar_empty[stage]));
             }
-            tc_commit(smem_u32(&bar_empty[stage]));
+            __syncwarp();
             if (++stage == p.stages) { stage = 0; phase ^= 1u; }
           }
+          if (!ok) break;
         }
-        if (ok) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        if (!ok) break;
+        if (elect_one()) tc_commit(smem_u32(&bar_tmem_full[buf]));
+        __syncwarp();
         if (++buf == p.nbuf) { buf = 0; bphase ^= 1u; }
       }
     }
@@ -606,6 +614,15 @@ int read_device_status_halo(int* status, int reset);   // igemm_halo.cu
 int read_device_status_attention(int* status, int reset);   // attention_tc.cu
 int read_device_status_modq(int* status, int reset);        // modq.cu
 int read_device_status_probe(int* status, int reset);       // i8_probe.cu
+int read_device_status_pair(int* status, int reset);        // igemm_pair.cu
+int read_device_status_attention_i8(int* status, int reset);   // attention_i8.cu
+bool pair_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
+                    const int32_t* acc_out, const float* o_hat);
+int launch_igemm_pair(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
+                      const float* x_scale, const float* w_scale, const int32_t* w_corr,
+                      float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
+                      const float* residual, float* sum_out, const float* x_zp,
+                      const int32_t* w_csum);
 bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample, const float* bias,
                     const int32_t* acc_out, const float* o_hat);
 int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_rows,
@@ -613,6 +630,14 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                       float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
                       const float* residual, float* sum_out, const float* x_zp,
                       const int32_t* w_csum);
+
+// MODIFF_IGEMM_PAIR=1 sends 3x3 layers to the two-SM kernel (cta_group::2, igemm_pair.cu): same
+// results, measured slower than the single-CTA kernel at every layer of the covered models, so
+// it is off unless asked for
+static bool pair_enabled() {
+  const char* e = getenv("MODIFF_IGEMM_PAIR");   // read per call: tests switch it at run time
+  return e && e[0] == '1';
+}
 
 // MODIFF_IGEMM_HALO=0 keeps 3x3 layers on the one-copy-per-tap kernel (debug aid, same results)
 static bool halo_enabled() {
@@ -637,7 +662,13 @@ int read_device_status(int* status, int reset) {
   int f = 0;
   rc = read_device_status_probe(&f, reset);
   if (rc) return rc;
-  *status = a | b | c | d | e | f;
+  int h = 0;
+  rc = read_device_status_pair(&h, reset);
+  if (rc) return rc;
+  int i8 = 0;
+  rc = read_device_status_attention_i8(&i8, reset);
+  if (rc) return rc;
+  *status = a | b | c | d | e | f | h | i8;
   return MODIFF_OK;
 }
 
@@ -672,6 +703,10 @@ static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_s
     return modiff_add(residual, o_hat, sum_out, g->batch, g->cout, ds.ho * ds.wo, 0, stream);
   }
   MODIFF_CHECK_ARG(impl == MODIFF_IMPL_AUTO || impl == MODIFF_IMPL_TCGEN05, "unknown impl %d", impl);
+  if (pair_enabled() && halo_enabled() &&
+      pair_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
+    return launch_igemm_pair(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
+                             g, s, residual, sum_out, x_zp, w_csum);
   if (halo_enabled() && halo_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
     return launch_igemm_halo(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
                              g, s, residual, sum_out, x_zp, w_csum);

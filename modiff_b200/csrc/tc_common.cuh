@@ -44,21 +44,26 @@ __device__ inline uint64_t global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait (about two seconds).  Returns false when the limit ran out or another role
-// of this CTA already gave up.
-__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait.  Returns false when `limit_ns` (or the iteration limit) ran out or another
+// role of this CTA already gave up; the status word then has bit 0 set for the host to read.
+__device__ inline bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                       uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > 2000000000ull) break;
+      if (global_ns() - t0 > limit_ns) break;
     }
   }
   *abort_flag = 1;
   atomicExch(&g_device_status, 1);
   return false;
+}
+// The kernels' waits: about two seconds.
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, 2000000000ull);
 }
 
 __device__ inline void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
@@ -91,6 +96,19 @@ __device__ inline void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0
                    map),
                "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
+}
+
+// One lane of a fully active warp (the same lane every time it is asked).  The tensor-core
+// roles run their loops with ALL lanes, so that addresses and descriptors are warp-uniform
+// values the compiler can keep in uniform registers, and only the issue itself is elected.
+__device__ inline bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -160,3 +160,41 @@ extern "C" int modiff_weight_pack(const float* w, const modiff_conv_geom* g, int
   return modiff_weight_pack_rounded(w, nullptr, nullptr, nullptr, g, n_bits, with_sum_rows, wcodes,
                                     w_scale, w_zp, w_corr, w_dq, nullptr, stream);
 }
+
+// Stand-alone fake quantisation with learned (AdaRound) hard rounding, elementwise over a
+// [rows][row_len] weight whose scale and zero point belong to the row:
+//   out = (clamp(floor(w / delta[r]) + (alpha >= 0) + zp[r], 0, 2^b - 1) - zp[r]) * delta[r]
+// (qdiff/adaptive_rounding.py:49-61 with soft_targets False; every step one rounded fp32
+// operation, as the reference's tensor expression).
+namespace modiff {
+namespace {
+__global__ void adaround_fake_quant_kernel(const float* __restrict__ w, const float* __restrict__ alpha,
+                                           const float* __restrict__ delta, const float* __restrict__ zp,
+                                           float* __restrict__ out, long long n, int row_len,
+                                           int per_row, float top) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = per_row ? i / row_len : 0;
+    const float d = delta[r], z = zp[r];
+    const float up = alpha[i] >= 0.0f ? 1.0f : 0.0f;
+    const float x_int = __fadd_rn(floorf(__fdiv_rn(w[i], d)), up);
+    const float q = fminf(fmaxf(__fadd_rn(x_int, z), 0.0f), top);
+    out[i] = __fmul_rn(__fsub_rn(q, z), d);
+  }
+}
+}  // namespace
+}  // namespace modiff
+
+extern "C" int modiff_adaround_fake_quant(const float* w, const float* alpha, const float* delta,
+                                          const float* zero_point, float* out, int64_t rows,
+                                          int64_t row_len, int per_row, int n_bits, void* stream) {
+  MODIFF_CHECK_ARG(w && alpha && delta && zero_point && out, "NULL pointer argument");
+  MODIFF_CHECK_ARG(rows > 0 && row_len > 0 && row_len < (1ll << 31), "bad shape");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "weight n_bits %d outside [2, 8]", n_bits);
+  const long long n = rows * row_len;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  modiff::adaround_fake_quant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+      w, alpha, delta, zero_point, out, n, (int)row_len, per_row, (float)((1 << n_bits) - 1));
+  MODIFF_LAUNCH_CHECK("adaround_fake_quant_kernel");
+  return MODIFF_OK;
+}

@@ -8,10 +8,13 @@ Per-tensor dynamic activation scales couple the images of one shard (the scale i
 over the whole batch tensor, qdiff/quant_layer.py:197-206), so a rank's samples equal a
 single-process run on exactly that shard, not a slice of one big batch.
 """
+import datetime
 import os
 
 import torch
 import torch.distributed as dist
+
+from ._lib import ModiffError
 
 
 def env_world():
@@ -79,3 +82,36 @@ def gather_ragged(local, total, group=None):
         local = torch.cat([local, local.new_zeros((pad,) + tuple(local.shape[1:]))], dim=0)
     full = gather_samples(local, group).view((world, biggest) + tuple(local.shape[1:]))
     return torch.cat([full[r, :hi - lo] for r, (lo, hi) in enumerate(sizes)], dim=0)
+
+
+def await_peers(tag, timeout_s=30.0, group=None):
+    """Host-side check, between sampling passes, that every rank has reached the gather named
+    `tag`: each rank posts a key in the process group's store and waits for the others' keys.
+    A rank that raised, exited or never arrived makes the wait run out, and the survivors get a
+    `ModiffError` naming the missing ranks before they launch a collective that could not
+    complete.  Nothing runs on the device here, so no kernel or collective is in flight when a
+    rank is found missing.  The reference has no counterpart (single process,
+    qdiff/layer_recon.py:102-105)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    store = dist.distributed_c10d._get_default_store()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    store.set(f"modiff/{tag}/{rank}", b"1")
+    missing = []
+    deadline = datetime.timedelta(seconds=float(timeout_s))
+    for r in range(world):
+        if r == rank:
+            continue
+        try:
+            store.wait([f"modiff/{tag}/{r}"], deadline)
+        except Exception:       # the store raises its own timeout type
+            missing.append(r)
+    if missing:
+        raise ModiffError(f"rank(s) {missing} did not reach '{tag}' within {timeout_s:.0f} s: "
+                          "not gathering (their shards are lost; restart the pass)")
+
+
+def gather_samples_checked(local, tag, timeout_s=30.0, group=None):
+    """`gather_samples` behind `await_peers`: raises instead of blocking when a rank is gone."""
+    await_peers(tag, timeout_s, group)
+    return gather_samples(local, group)

@@ -258,6 +258,20 @@ class QKVAttentionLegacy(nn.Module):
             assert self.qkv_matmul.scale == scale
         else:
             self.qkv_matmul.scale = scale
+        qm = self.qkv_matmul
+        if getattr(self, "int8_attention", False) and getattr(qm, "use_act_quant", False) and \
+                hasattr(qm, "act_quantizer_q"):
+            # heads stay where they are in the fused tensor: [N][H][q | k | v][ch][T]
+            bits = ops.int8_attention_bits(qm.act_quantizer_q, "attention")
+            qkv = qkv.contiguous()
+            h = self.n_heads
+            base = qkv.reshape(-1)
+            out = torch.empty((bs, h * ch, length), dtype=torch.float32, device=qkv.device)
+            st = (h * 3 * ch * length, 3 * ch * length, length, 1)
+            ops.attention_i8(base, base[ch * length:], base[2 * ch * length:], scale * scale, bs, h,
+                             ch, length, length, st, st, out, (h * ch * length, ch * length, length, 1),
+                             bits)
+            return out
         q, k, v = qkv.reshape(bs * self.n_heads, ch * 3, length).split(ch, dim=1)
         a = ops.attention(q, k, v, scale * scale)
         return a.reshape(bs, -1, length)
@@ -376,6 +390,16 @@ def cross_attention_forward(blk, x, context=None, mask=None):
             else blk.to_v.forward_shared(blk.to_k, context)
     b, n, inner = q.shape
     d = inner // h
+    if getattr(blk, "int8_attention", False) and getattr(blk, "use_act_quant", False) and \
+            hasattr(blk, "act_quantizer_q"):
+        # token-major in and out: 'b n (h d)' is read and written in place, no transposes
+        bits = ops.int8_attention_bits(blk.act_quantizer_q, "attention")
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        nk = k.shape[1]
+        out = torch.empty((b, n, inner), dtype=torch.float32, device=q.device)
+        ops.attention_i8(q, k, v, blk.scale, b, h, d, n, nk, (n * inner, d, 1, inner),
+                         (nk * inner, d, 1, inner), out, (n * inner, d, 1, inner), bits)
+        return blk.to_out[0](out)
     # 'b n (h d) -> (b h) d n': one transpose per tensor gives the channel-major heads
     qt = ops.transpose_last2(q).reshape(b * h, d, n)
     kt = ops.transpose_last2(k).reshape(b * h, d, k.shape[1])

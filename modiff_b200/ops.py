@@ -392,3 +392,58 @@ def attention(q, k, v, scale):
                            1.0, crow)
     _lib.call('modiff_gemm_bf16', C.byref(d2), C.byref(gv), _lib.stream_ptr())
     return out
+
+
+_ATTN_SCRATCH = {}
+
+
+def attention_i8(q, k, v, scale, batch, heads, c, tq, tk, strides_q, strides_kv, out, strides_out,
+                 n_bits=8):
+    """Integer attention (opt-in; see csrc/attention_i8.cu and oracle/attention_i8.py): q, k, v
+    through per-tensor symmetric dynamic quantisers of `n_bits`, both products as int8
+    tensor-core MMAs, fp32 softmax with unsigned 8-bit weights.
+
+    q, k, v are fp32 CUDA tensors addressed as x[b*s0 + h*s1 + c*s2 + t*s3] from their data
+    pointers with the element strides `strides_q` (q) and `strides_kv` (k and v); `out` likewise
+    with `strides_out`.  Channels or tokens must be the contiguous dimension."""
+    _req(q, k, v, out)
+    l = _lib.lib()
+    dev = q.device
+    bh = batch * heads
+    sizes = [l.modiff_attn_codes_bytes(bh, c, tq, tk, i) for i in range(3)]
+    qc, kc, vc = (torch.empty(n, dtype=torch.int8, device=dev) for n in sizes)
+    scales = torch.empty(4, dtype=torch.float32, device=dev)
+    scratch = _ATTN_SCRATCH.get(dev)
+    if scratch is None:
+        scratch = _ATTN_SCRATCH[dev] = torch.zeros(16, dtype=torch.uint8, device=dev)
+    sq = (C.c_int64 * 4)(*[int(x) for x in strides_q])
+    skv = (C.c_int64 * 4)(*[int(x) for x in strides_kv])
+    so = (C.c_int64 * 4)(*[int(x) for x in strides_out])
+    n_in = batch * heads * c * (tq + 2 * tk)
+    _lib.call('modiff_attn_quantize', q.data_ptr(), k.data_ptr(), v.data_ptr(), batch, heads, c, tq,
+              tk, sq, skv, n_bits, qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scales.data_ptr(),
+              scratch.data_ptr(), _lib.stream_ptr(), nbytes=9 * n_in)
+    _lib.call('modiff_attention_i8', qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scales.data_ptr(),
+              out.data_ptr(), batch, heads, c, tq, tk, so, float(scale), _lib.stream_ptr(),
+              nbytes=sum(sizes) + 4 * batch * heads * c * tq)
+    return out
+
+
+def attention_i8_channel_major(q, k, v, scale, n_bits=8):
+    """`attention_i8` for contiguous [B, C, T] tensors, one head per batch entry (the layout of
+    `attention`)."""
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    b, c, t = q.shape
+    tk = k.shape[2]
+    out = torch.empty((b, c, t), dtype=torch.float32, device=q.device)
+    return attention_i8(q, k, v, scale, b, 1, c, t, tk, (c * t, 0, t, 1), (c * tk, 0, tk, 1), out,
+                        (c * t, 0, t, 1), n_bits)
+
+
+def int8_attention_bits(quantizer, what):
+    """Bit width of an attention quantiser for the integer kernel; it covers symmetric
+    per-tensor quantisers only."""
+    if not quantizer.sym or quantizer.channel_wise:
+        raise ModiffError(f"int8 attention needs symmetric per-tensor {what} quantisers "
+                          "(build the model with symmetric activation parameters, --a_sym)")
+    return int(quantizer.n_bits)

@@ -25,6 +25,10 @@ class QuantModel(nn.Module):
         self.specials = get_specials(act_quant_params['leaf_param'])
         self.quant_module_refactor(self.model, weight_quant_params, act_quant_params)
         self.quant_block_refactor(self.model, weight_quant_params, act_quant_params)
+        # int8_attention=True (default False): apply the q / k / v / softmax quantisers the
+        # blocks construct (qdiff/quant_block.py:120-121, 139-144, 223-235, 331-335) in an integer
+        # attention kernel; the reference itself leaves them unapplied, so off reproduces it
+        self.set_int8_attention(bool(kwargs.get("int8_attention", False)))
 
     def quant_module_refactor(self, module: nn.Module, weight_quant_params: dict = {},
                               act_quant_params: dict = {}):
@@ -90,6 +94,15 @@ class QuantModel(nn.Module):
         for m in self.model.modules():
             if isinstance(m, QuantModule):
                 m.set_modualtion(modulation)
+
+    def set_int8_attention(self, enabled: bool):
+        """Switch the integer attention kernel on or off for every attention block (no
+        counterpart in the reference, whose attention products stay in floating point)."""
+        self._config_changed()
+        self.int8_attention = bool(enabled)
+        for m in self.model.modules():
+            if type(m).__name__ in ("QuantAttnBlock", "QKVAttentionLegacy", "CrossAttention"):
+                m.int8_attention = bool(enabled)
 
     def forward(self, x, timesteps=None, context=None):
         return self.model(x, timesteps, context)

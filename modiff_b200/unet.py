@@ -232,8 +232,14 @@ def attn_forward(blk, x):
         k = blk.k(h_)
         v = blk.v(h_)
     b, c, h, w = q.shape
-    h_ = ops.attention(q.reshape(b, c, h * w), k.reshape(b, c, h * w), v.reshape(b, c, h * w),
-                       float(int(c) ** (-0.5)))
+    if getattr(blk, "int8_attention", False) and getattr(blk, "use_act_quant", False):
+        # the block's own (otherwise unused) q / k / v quantisers give the bit width
+        bits = ops.int8_attention_bits(blk.act_quantizer_q, "attention")
+        h_ = ops.attention_i8_channel_major(q.reshape(b, c, h * w), k.reshape(b, c, h * w),
+                                            v.reshape(b, c, h * w), float(int(c) ** (-0.5)), bits)
+    else:
+        h_ = ops.attention(q.reshape(b, c, h * w), k.reshape(b, c, h * w),
+                           v.reshape(b, c, h * w), float(int(c) ** (-0.5)))
     h_ = blk.proj_out(h_.reshape(b, c, h, w))
     return ops.add(x, h_)
 

@@ -164,6 +164,33 @@ def test_adaround_weight_codes_bit_exact(cuda, golden_cali):
 
 
 @pytest.mark.gpu
+def test_adaround_quantizer_forward_on_the_device(cuda):
+    """AdaRoundQuantizer.forward (the stand-alone fake quantisation with the hard rounding
+    decision) runs as a device kernel and equals the oracle's restatement of
+    qdiff/adaptive_rounding.py:49-61 bit for bit; the training-time modes raise."""
+    import modiff_b200 as m
+    g = torch.Generator().manual_seed(6)
+    w = torch.randn(24, 16, 3, 3, generator=g)
+    uaq = m.UniformAffineQuantizer(n_bits=4, symmetric=False, channel_wise=True, scale_method="max")
+    uaq(w.to(cuda))                                   # sets delta / zero_point per channel
+    ada = m.AdaRoundQuantizer(uaq, w.to(cuda))
+    # initial logits: round to nearest, i.e. the uniform quantiser's own result
+    _, q, delta, zp = weight_codes(w, 4)
+    assert torch.equal(ada.delta.cpu().reshape(-1), delta.reshape(-1))
+    assert torch.equal(ada(w.to(cuda)).cpu(), (q - zp) * delta)
+    # arbitrary logits, as a checkpoint would hold
+    alpha = torch.randn(w.shape, generator=g)
+    ada.alpha.data = alpha.to(cuda)
+    want, _, _, _ = adaround_codes(w, alpha, delta, zp, 4)
+    assert torch.equal(ada(w.to(cuda)).cpu(), want)
+    ada.soft_targets = True
+    with pytest.raises(m.ModiffError):
+        ada(w.to(cuda))
+    with pytest.raises(m.ModiffError):
+        m.AdaRoundQuantizer(uaq, w.to(cuda), round_mode="nearest")
+
+
+@pytest.mark.gpu
 def test_static_scale_set_by_first_quantised_call(cuda):
     """Without a checkpoint a non-dynamic quantiser keeps the scale of its first quantised call
     (qdiff/quant_layer.py:72-79): compare a layer with the oracle over four steps."""
@@ -190,6 +217,40 @@ def test_static_scale_set_by_first_quantised_call(cuda):
         assert torch.equal(mod.a_hat.cpu(), orc.a_hat)
     # the last input saturates the fixed scale: codes clamp instead of the scale growing
     assert int(orc.last["codes"][0].abs().max()) >= 127
+
+
+@pytest.mark.gpu
+def test_static_scale_survives_another_batch_size(cuda):
+    """A non-dynamic quantiser's scale belongs to the quantiser, not to an input shape
+    (qdiff/quant_layer.py:72-79): measured at batch 2, it is the scale that quantises a batch of
+    1 after reset_cache(), exactly as the oracle (and the reference) carry it over."""
+    import modiff_b200 as m
+    from oracle.quant_module import OracleQuantModule
+    lc = dict(cases.LAYER_CASES[0])
+    org = cases.layer_module(lc)
+    w_cpu, b_cpu = org.weight.detach().clone(), org.bias.detach().clone()
+    wq, aq = cases.quant_params(lc)
+    mod = m.QuantModule(org, wq, dict(aq, dynamic=False), modulate=True).to(cuda)
+    mod.set_quant_state(True, True)
+    orc = OracleQuantModule(w_cpu, b_cpu, lc["stride"], lc["pad"], lc["w_bits"], lc["a_bits"], True,
+                            modulate=True, a_dynamic=False)
+    xs = cases.layer_inputs(lc)
+    for x in xs[:3]:                       # batch 2: the first quantised call sets the scale
+        orc.forward(x)
+        mod(x.to(cuda))
+    delta = float(mod.act_quantizer.delta)
+    assert delta == float(orc.act_scale[0][0])
+    mod.reset_cache()
+    orc.reset_cache()
+    for s, x in enumerate(xs[:3]):         # batch 1, other values: the scale must not move
+        x1 = 0.5 * x[:1].contiguous()
+        want = orc.forward(x1)
+        got = mod(x1.to(cuda)).cpu()
+        assert float(mod.act_quantizer.delta) == delta == float(orc.act_scale[0][0])
+        np.testing.assert_allclose(got.numpy(), want.numpy(), rtol=0,
+                                   atol=1e-4 * float(want.abs().max()))
+        assert torch.equal(mod.a_hat.cpu(), orc.a_hat)
+    assert m.device_status() == 0
 
 
 @pytest.mark.gpu

@@ -60,3 +60,44 @@ def test_shard_bounds_cover_the_batch():
     assert D.rank_seed(1, 3) == 4
     assert D.env_world() == (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
                              int(os.environ.get("WORLD_SIZE", 1)))
+
+
+def _leaver(rank, world, port, out_dir):
+    """Rank 1 finishes the first pass and leaves (between passes, nothing in flight); rank 0
+    goes on to a second pass and must learn on the host that its peer is gone."""
+    sys.path.insert(0, ROOT)
+    import time
+    from modiff_b200 import distributed as D
+    from modiff_b200._lib import ModiffError
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    D.init(backend="gloo")
+    local = D.shard_noise((2, 3, 4, 4), base_seed=3, rank=rank, device="cpu")
+    first = D.gather_samples_checked(local, "pass0", timeout_s=20.0)
+    assert first.shape[0] == 2 * world
+    if rank == 1:
+        os._exit(0)                       # leaves without a word
+    t0 = time.time()
+    try:
+        D.gather_samples_checked(local, "pass1", timeout_s=2.0)
+        outcome = "gathered"
+    except ModiffError as e:
+        outcome = f"raised after {time.time() - t0:.1f}s: {e}"
+    with open(os.path.join(out_dir, "r0.txt"), "w") as fh:
+        fh.write(outcome)
+    os._exit(0)                           # no collective teardown with a dead peer
+
+
+def test_rank_leaving_between_passes_is_detected_on_the_host(tmp_path):
+    """Failure detection without touching a device: a rank that exits between two sampling
+    passes makes the survivor's next gather raise within its timeout instead of blocking."""
+    world = 2
+    port = _free_port()
+    ctx = mp.spawn(_leaver, args=(world, port, str(tmp_path)), nprocs=world, join=False)
+    ok = ctx.join(timeout=90)
+    while not ok:
+        ok = ctx.join(timeout=90)
+    text = open(os.path.join(tmp_path, "r0.txt")).read()
+    assert text.startswith("raised after"), text
+    assert "rank(s) [1]" in text and "pass1" in text
+    assert float(text.split()[2][:-2]) < 15.0

@@ -103,3 +103,51 @@ def test_sd_unet_all_50_guided_evaluations(cuda):
                               unconditional_conditioning=uncond.to(cuda))
     assert len(sampler.ddim_timesteps) == 50
     _report(c["name"], fx, final.cpu().numpy())
+
+
+@pytest.mark.parametrize("kind", ["pixel_w8a8_b8", "ldm_full", "sd_full"])
+def test_int8_attention_full_runs(cuda, kind, golden_unet):
+    """The same full loops with the integer attention kernel switched on (QuantModel kwarg
+    int8_attention=True).  The reference's attention is floating point, so this is NOT a parity
+    test of the reference path: it records what applying the q / k / v / softmax quantisers
+    costs in PSNR against the reference's samples and requires a sane result."""
+    import modiff_b200 as m
+    if kind == "pixel_w8a8_b8":
+        c = next(u for u in cases.UNET_CASES if u["name"] == "w8a8_b8_s100")
+        torch.manual_seed(0)
+        net = m.Model(m.make_config(split_shortcut=c["split"])).eval()
+        wq, aq = cases.quant_params(c)
+        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True, int8_attention=True).to(cuda).eval()
+        qnn.set_quant_state(True, True)
+        qnn.reset_cache()
+        betas = torch.from_numpy(m.get_beta_schedule()).float()
+        xs, _ = m.generalized_steps(cases.unet_noise(c).to(cuda), cases.unet_sequence(c), qnn, betas,
+                                    eta=0.0)
+        final, ref = xs[-1].cpu().numpy(), golden_unet[c["name"] + "/final"]
+    else:
+        sd = kind == "sd_full"
+        c = next(f for f in cases.FULL_CASES if f["name"] == ("sd_w8a8_b1_full" if sd else
+                                                                "ldm_w8a8_b2_full"))
+        fx = _fixture(c["name"])
+        torch.manual_seed(0)
+        net = m.UNetModel(**(cases.SD_CONFIG if sd else cases.LDM_CONFIG)).eval()
+        m.rerandomize_zero_tensors(net, seed=c["zero_seed"])
+        wq, aq = cases.quant_params(c)
+        qnn = m.QuantModel(net, wq, aq, sm_abit=8, modulate=True, int8_attention=True).to(cuda).eval()
+        qnn.set_quant_state(True, True)
+        qnn.set_grad_ckpt(False)
+        qnn.reset_cache()
+        sampler = m.DDIMSampler(qnn, **(cases.SD_SCHEDULE if sd else cases.LDM_SCHEDULE))
+        if sd:
+            x, cond, uncond = cases.sd_inputs(c)
+            final, _ = sampler.sample(c["ddim_steps"], c["batch"], tuple(x.shape[1:]), eta=0.0,
+                                      conditioning=cond.to(cuda), x_T=x.to(cuda),
+                                      unconditional_guidance_scale=c["guidance"],
+                                      unconditional_conditioning=uncond.to(cuda))
+        else:
+            final, _ = sampler.sample(c["ddim_steps"], c["batch"], (4, 32, 32), eta=0.0,
+                                      x_T=cases.ldm_noise(c).to(cuda))
+        final, ref = final.cpu().numpy(), fx["final"]
+    p = oracle.psnr(ref, final)
+    print(f"{kind} with int8 attention: final PSNR vs the reference (fp attention) {p:.1f} dB")
+    assert np.isfinite(final).all() and p >= 15.0, p

@@ -256,6 +256,7 @@ HALO_CASES = [
     (1, 320, 128, 64),      # 4-row tiles, last K chunk partly beyond cin
     (2, 192, 384, 16),      # three channel tiles
     (150, 128, 128, 16),    # more tiles than SMs: every CTA walks several tiles
+    (80, 512, 256, 16),     # four K chunks, 256 output channels per tile, several tiles per pair
 ]
 
 
@@ -263,8 +264,9 @@ HALO_CASES = [
 @pytest.mark.parametrize("accumulate", [True, False])
 @pytest.mark.parametrize("case", HALO_CASES, ids=lambda c: "b%d_c%d_o%d_hw%d" % c)
 def test_igemm_activation_reuse_kernel(cuda, case, accumulate, w_bits, monkeypatch):
-    """The 3x3 kernel that reuses one activation copy for three filter taps gives the same
-    bits as the one-copy-per-tap kernel and matches the exact integer convolution."""
+    """The 3x3 kernels that reuse one activation copy for three filter taps - the two-SM kernel
+    (cta_group::2, both tile heights) and the single-CTA one - give the same bits as the
+    one-copy-per-tap kernel and match the exact integer convolution."""
     b, cin, cout, hw = case
     L = _lib()
     g = _geom(b, cin, cout, hw, hw, k=3, stride=1, pad=(1, 1, 1, 1))
@@ -272,17 +274,22 @@ def test_igemm_activation_reuse_kernel(cuda, case, accumulate, w_bits, monkeypat
     x_codes = torch.randint(-8, 8, (b, cin, hw, hw), dtype=torch.int8)
     w = torch.randn(cout, cin, 3, 3) * 0.05
     w[1] = w[1].abs() + 0.01   # an all-positive channel: zero point outside the code range
-    outs = []
-    for halo in ("1", "0"):
+    outs = {}
+    for name, pair, halo, mh in (("pair, 128-pixel tiles", "1", "1", "1"),
+                                 ("pair, 256-pixel tiles", "1", "1", "2"),
+                                 ("single CTA", "0", "1", ""), ("per tap", "0", "0", "")):
+        monkeypatch.setenv("MODIFF_IGEMM_PAIR", pair)
         monkeypatch.setenv("MODIFF_IGEMM_HALO", halo)
+        monkeypatch.setenv("MODIFF_PAIR_MH", mh)
         out, _, o_prev, ws = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda,
                                         accumulate=accumulate, want_acc=False)
-        outs.append(out)
-    assert torch.equal(outs[0], outs[1])
+        outs[name] = out
+    for name, out in outs.items():
+        assert torch.equal(out, outs["per tap"]), name
     exp_acc, dws = _expected_acc(x_codes, w, g, w_bits)
     exp = o_prev.double() if accumulate else torch.zeros_like(o_prev).double()
     exp = exp + exp_acc[0].double() * (float(np.float32(0.01)) * dws[0].double().view(1, -1, 1, 1))
-    err = (outs[0].double() - exp).abs().max() / exp.abs().max()
+    err = (outs["per tap"].double() - exp).abs().max() / exp.abs().max()
     assert err < 1e-5, err
 
 
@@ -431,3 +438,36 @@ def test_i8_peak_is_plausible(cuda):
     tops = L.measure_i8_peak(mode=1, umma_n=256, iters=2048, repeats=3)
     print(f"kind::i8 ceiling, cta_group::1 N=256: {tops:.0f} TOPS")
     assert 1100 < tops < 5500, tops
+
+
+def test_bounded_wait_gives_up_and_the_library_recovers(cuda):
+    """Failure detection on the device, without a fault: a wait that nothing satisfies runs out
+    after its limit (1 ms here), the kernel RETURNS, the sticky status word reports it, a reset
+    clears it, and the next ordinary call is bit-exact (the context stays usable)."""
+    L = _lib()
+    assert L.device_status() == 0
+    gave_up = torch.zeros(1, dtype=torch.int32, device=cuda)
+    L.call('modiff_wait_probe', 1_000_000, gave_up.data_ptr(), L.stream_ptr())
+    torch.cuda.synchronize()
+    assert int(gave_up) == 1
+    assert L.device_status(reset=False) & 1, "the status word must record the timed-out wait"
+    assert L.device_status(reset=True) & 1
+    assert L.device_status() == 0, "reset must clear it"
+    # samplers turn the flag into an exception
+    from modiff_b200.sampler import raise_on_device_status
+    L.call('modiff_wait_probe', 1_000_000, None, L.stream_ptr())
+    with pytest.raises(L.ModiffError):
+        raise_on_device_status()
+    assert L.device_status() == 0
+    # and the library still computes correctly afterwards
+    torch.manual_seed(9)
+    x = torch.randn(2, 128, 8, 8)
+    a = x + 0.1 * torch.randn(2, 128, 8, 8)
+    g = _geom(2, 128, 64, 8, 8, k=3, pad=(1, 1, 1, 1))
+    a_dev = a.to(cuda)
+    codes, scale = run_modq(x.to(cuda), a_dev, g, 8)
+    y, q, d, _ = fake_quant(x - a, 8, True)
+    got, _ = _codes_to_nchw(codes, g, 128)
+    assert float(scale[0]) == float(d) and torch.equal(got.float(), q)
+    with pytest.raises(L.ModiffError):
+        L.call('modiff_wait_probe', 2_000_000_000, None, L.stream_ptr())   # limit above the cap

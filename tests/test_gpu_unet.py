@@ -110,3 +110,36 @@ def test_cuda_graph_replay_is_bit_identical(cuda):
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[0], outs[2])
     assert len(qnn.graphed()._graphs) == 1
+
+
+def test_cuda_graph_is_recaptured_after_another_shape(cuda):
+    """Shape A, then shape B (e.g. a ragged last batch), then A again: the layers replace their
+    caches and code planes at every change of shape, so the graph captured for A the first time
+    holds stale addresses and must be captured again, not replayed.  Samples with graphs on
+    equal the eager run bit for bit in all three passes."""
+    import modiff_b200 as m
+    from modiff_b200 import _lib
+    c = next(u for u in cases.UNET_CASES if u["name"] == "w4a4_split_b2_s10")
+    qnn = build(c, cuda)
+    betas = torch.from_numpy(m.get_beta_schedule()).float()
+    seq = cases.unet_sequence(c)[-6:]
+    g = torch.Generator().manual_seed(77)
+    xa = torch.randn(2, 3, 32, 32, generator=g).to(cuda)
+    xb = torch.randn(3, 3, 32, 32, generator=g).to(cuda)
+    runs = {}
+    for use_graph in (False, True):
+        outs = []
+        for x in (xa, xb, xa):
+            qnn.reset_cache()
+            xs, _ = m.generalized_steps(x, seq, qnn, betas, eta=0.0, cuda_graph=use_graph)
+            outs.append(xs[-1].clone())
+        runs[use_graph] = outs
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    for k in range(3):
+        assert torch.equal(runs[False][k], runs[True][k]), f"pass {k}"
+    assert torch.equal(runs[True][0], runs[True][2])
+    # a flag set on ONE layer also invalidates the captured graphs
+    before = _lib.GENERATION[0]
+    next(mod for mod in qnn.modules() if isinstance(mod, m.QuantModule)).set_quant_state(True, True)
+    assert _lib.GENERATION[0] > before
