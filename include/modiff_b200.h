@@ -535,6 +535,26 @@ int modiff_unpack_int4(const uint8_t* packed, int8_t* codes, int64_t n, int is_s
 int modiff_quantize_static(const float* x, const float* delta, int8_t* codes,
                            const modiff_conv_geom* g, int n_bits, void* stream);
 
+/* Packed 4-bit operands: W4 weight codes and A4 / A3 activation codes travel two per byte
+ * through HBM and L2 and are expanded to int8 in shared memory, because the tensor cores have
+ * no 4-bit integer MMA (the storage convention of qdiff/quant_layer_int4.py:341-366: element 2i
+ * in the low nibble of byte i; the arithmetic is that of modiff_igemm_conv,
+ * qdiff/quant_layer.py:345-365, and the results are bit-identical to it).
+ *   modiff_pack_weights_int4  rows of modiff_weight_pack's wcodes (int8 q - zero_point, no
+ *                             receptive-field-sum rows) -> unsigned nibbles q; `bad` (device
+ *                             int, zero on entry) is set when a code does not fit 4 bits
+ *   modiff_igemm_conv_packed4 codes4 = modiff_pack_int4 of the activation code planes
+ *                             (two's-complement nibbles), wcodes4 from above, w_zp fp32 [cout];
+ *                             3x3 stride-1 pad-1 layers, cin and cout multiples of 128, per-tensor
+ *                             scales, no split; residual / sum_out optional as in
+ *                             modiff_igemm_conv_add */
+int modiff_pack_weights_int4(const int8_t* wcodes, const float* w_zp, uint8_t* packed,
+                             int64_t rows, int64_t row_bytes, int* bad, void* stream);
+int modiff_igemm_conv_packed4(const uint8_t* codes4, const uint8_t* wcodes4, const float* w_zp,
+                              const float* x_scale, const float* w_scale, float* o_hat,
+                              int accumulate, const modiff_conv_geom* g, const float* residual,
+                              float* sum_out, void* stream);
+
 /* Stand-alone fake quantisation of a weight tensor with learned (AdaRound) hard rounding
  * (qdiff/adaptive_rounding.py:49-61, soft_targets False), what AdaRoundQuantizer.forward returns:
  *   out = (clamp(floor(w / delta) + (alpha >= 0) + zero_point, 0, 2^b - 1) - zero_point) * delta

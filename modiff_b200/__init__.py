@@ -13,6 +13,7 @@ from .ldm_unet import UNetModel, rerandomize_zero_tensors
 from .ldm_sampler import DDIMSampler, PLMSSampler
 from .sampler import (generalized_steps, compute_alpha, get_beta_schedule,
                       make_timestep_sequence)
+from .autoencoder import Decoder, FirstStageDecoder, KL_F8
 from .calibration import generate_calibration_data, select_calibration_points
 
 __all__ = [
@@ -23,5 +24,5 @@ __all__ = [
     "load_calibrated_state",
     "get_specials", "QuantModel", "Model", "UNetModel", "DDIMSampler", "PLMSSampler", "rerandomize_zero_tensors", "make_config", "generalized_steps", "compute_alpha",
     "get_beta_schedule", "make_timestep_sequence", "generate_calibration_data",
-    "select_calibration_points",
+    "select_calibration_points", "Decoder", "FirstStageDecoder", "KL_F8",
 ]

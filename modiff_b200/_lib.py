@@ -132,6 +132,8 @@ SIGNATURES = {
     "modiff_quantize_static": (C.c_int, [_P, _P, _P, _G, C.c_int, _P]),
     "modiff_i8_mma_probe": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, _P]),
     "modiff_wait_probe": (C.c_int, [C.c_int64, _P, _P]),
+    "modiff_pack_weights_int4": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int64, _P, _P]),
+    "modiff_igemm_conv_packed4": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, _G, _P, _P, _P]),
     "modiff_adaround_fake_quant": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int,
                                              C.c_int, _P]),
     "modiff_attn_codes_bytes": (C.c_int64, [C.c_int] * 5),
@@ -169,6 +171,7 @@ KERNELS_PER_CALL = {
     "modiff_ddim_step": 1, "modiff_cfg_combine": 1, "modiff_pack_int4": 1, "modiff_unpack_int4": 1,
     "modiff_quantize_static": 1, "modiff_i8_mma_probe": 1, "modiff_wait_probe": 1,
     "modiff_attn_quantize": 2, "modiff_attention_i8": 1, "modiff_adaround_fake_quant": 1,
+    "modiff_pack_weights_int4": 1, "modiff_igemm_conv_packed4": 1,
 }
 LAUNCHES = [0]        # kernels launched through `call` since import
 # Bumped whenever a layer allocates or replaces a device buffer that kernels address directly

@@ -602,8 +602,11 @@ extern "C" int modiff_attn_quantize(const float* q, const float* k, const float*
     p.tv[i].t = i == 0 ? tq : tk;
     // one dense block (either canonical order), 16-byte aligned, a multiple of four elements
     const long long t = p.tv[i].t, n = (long long)batch * heads * c * t;
-    const bool cm = st[3] == 1 && st[2] == t && st[1] == (long long)c * t && st[0] == (long long)heads * c * t;
-    const bool tm = st[2] == 1 && st[1] == c && st[3] == (long long)heads * c && st[0] == t * heads * c;
+    // (a stride that is multiplied by an index that is always 0 does not matter)
+    const bool h_ok_cm = heads == 1 || st[1] == (long long)c * t;
+    const bool b_ok = batch == 1 || st[0] == (long long)heads * c * t;
+    const bool cm = st[3] == 1 && st[2] == t && h_ok_cm && b_ok;
+    const bool tm = st[2] == 1 && (heads == 1 || st[1] == c) && st[3] == (long long)heads * c && b_ok;
     p.dense[i] = ((cm || tm) && n % 4 == 0 && ((uintptr_t)xs[i] & 15) == 0) ? n : 0;
   }
   p.batch = batch;

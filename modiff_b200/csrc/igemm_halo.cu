@@ -39,6 +39,11 @@ constexpr int kOHalfBytes = 64 * 128 * 4;        // 64 channels x 128 pixels fp3
 constexpr int kMaxBStages = 6;
 constexpr int kLoadWarp = 2 + kEpiWarps;
 constexpr int kThreads = 32 * (3 + kEpiWarps);
+// packed 4-bit operands: four more warps expand nibbles into the int8 operand tiles
+constexpr int kUnpackWarps = 4;
+constexpr int kFirstUnpackWarp = kLoadWarp + 1;
+constexpr int kThreadsPacked = kThreads + 32 * kUnpackWarps;
+constexpr int kPkSlots = 2;
 
 struct HaloParams {
   int w, h, batch, cout;
@@ -69,6 +74,12 @@ struct HaloParams {
   const int32_t* w_csum;
   const float* residual;   // optional [batch][cout][h*w]: sum_out = new output + residual
   float* sum_out;
+  // packed 4-bit operands (igemm_halo_kernel<true>): staging slots hold what TMA delivers, two
+  // codes per byte; the unpack warps write the int8 tiles the MMAs read
+  int pk_a_bytes;          // one packed activation copy: a_bytes / 2
+  int pk_a_slot_bytes;
+  int pk_b_bytes;          // one packed weight tile: b_tile_bytes / 2
+  const float* w_zp;       // weight zero point per output channel (packed weights hold q, not q - zp)
 };
 
 struct HaloTile {
@@ -83,7 +94,31 @@ __device__ inline HaloTile decode(int tile, const HaloParams& p) {
   return t;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// 16 int8 codes from 16 nibbles (8 bytes, element 2i in the low nibble of byte i, 2i+1 in the
+// high nibble: the order of qdiff/quant_layer_int4.py:341-346).  SIGNED: two's-complement
+// nibbles are sign-extended; else unsigned nibbles minus `sub4` (a byte replicated four times).
+template <bool SIGNED>
+__device__ inline uint4 unpack16(uint2 pk, uint32_t sub4) {
+  uint32_t o[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t w = h == 0 ? pk.x : pk.y;
+    uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+    if (SIGNED) {
+      lo |= (lo & 0x08080808u) * 0x1Eu;      // bit 3 set -> bits 4..7 set, no carry between bytes
+      hi |= (hi & 0x08080808u) * 0x1Eu;
+    } else {
+      lo = __vsub4(lo, sub4);
+      hi = __vsub4(hi, sub4);
+    }
+    o[2 * h] = __byte_perm(lo, hi, 0x5140);      // lo0 hi0 lo1 hi1
+    o[2 * h + 1] = __byte_perm(lo, hi, 0x7362);  // lo2 hi2 lo3 hi3
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(PACKED ? kThreadsPacked : kThreads, 1)
 igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_o, const HaloParams p) {
@@ -92,6 +127,9 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ __align__(8) uint64_t bar_b_full[kMaxBStages], bar_b_empty[kMaxBStages];
   __shared__ __align__(8) uint64_t bar_tmem_full[2], bar_tmem_empty[2];
   __shared__ __align__(8) uint64_t bar_o_full[kMaxOSlots], bar_o_empty[kMaxOSlots];
+  __shared__ __align__(8) uint64_t bar_pa_full[kPkSlots], bar_pa_empty[kPkSlots];
+  __shared__ __align__(8) uint64_t bar_pb_full[kPkSlots], bar_pb_empty[kPkSlots];
+  __shared__ uint32_t zp4_sh[128];
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ float ep_scale[256];
@@ -108,16 +146,28 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t b_tile = (uint32_t)p.b_tile_bytes;
   const uint32_t obuf = b_ring + (uint32_t)p.b_stages * b_tile;
   float* obuf_ptr = reinterpret_cast<float*>(smem_raw + (obuf - raw));
+  // staging of packed operands behind the cached-output ring
+  const uint32_t pk_a = obuf + (uint32_t)p.o_slots * kOHalfBytes;
+  const uint32_t pk_b = pk_a + kPkSlots * (uint32_t)p.pk_a_slot_bytes;
 
   if (threadIdx.x == 0) {
     abort_sh = 0;
+    // operand tiles are complete when the copy has landed, or, with packed operands, when the
+    // four unpack warps have written them
+    const uint32_t fillers = PACKED ? kUnpackWarps : 1;
     for (int s = 0; s < p.a_slots; ++s) {
-      mbar_init(smem_u32(&bar_a_full[s]), 1);
+      mbar_init(smem_u32(&bar_a_full[s]), fillers);
       mbar_init(smem_u32(&bar_a_empty[s]), 1);
     }
     for (int s = 0; s < p.b_stages; ++s) {
-      mbar_init(smem_u32(&bar_b_full[s]), 1);
+      mbar_init(smem_u32(&bar_b_full[s]), fillers);
       mbar_init(smem_u32(&bar_b_empty[s]), 1);
+    }
+    for (int s = 0; s < kPkSlots; ++s) {
+      mbar_init(smem_u32(&bar_pa_full[s]), 1);
+      mbar_init(smem_u32(&bar_pa_empty[s]), kUnpackWarps);
+      mbar_init(smem_u32(&bar_pb_full[s]), 1);
+      mbar_init(smem_u32(&bar_pb_empty[s]), kUnpackWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
@@ -142,7 +192,111 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = tmem_base_sh;
   const int buf_cols = p.mh * p.umma_n;
 
-  if (warp == 0) {
+  if (warp == 0 && PACKED) {
+    // ------------------------------------------------------------ packed operand TMA producer
+    // Same order of copies as below, two codes per byte, into the staging slots.
+    if (lane == 0) {
+      int as = 0, bs = 0;
+      uint32_t aphase = 0, bphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const HaloTile t = decode(tile, p);
+        for (int ch = 0; ch < p.chunks && ok; ++ch) {
+          for (int dx = 0; dx < 3 && ok; ++dx) {
+            ok = mbar_wait(smem_u32(&bar_pa_empty[as]), aphase ^ 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t afull = smem_u32(&bar_pa_full[as]);
+            mbar_arrive_expect_tx(afull, (uint32_t)p.pk_a_bytes);
+            tma_load_5d(pk_a + as * (uint32_t)p.pk_a_slot_bytes, &map_a, afull, ch * (kChunkK / 2), dx,
+                        t.th * p.rows, 0, t.n);
+            if (++as == kPkSlots) { as = 0; aphase ^= 1u; }
+            for (int dy = 0; dy < 3; ++dy) {
+              ok = mbar_wait(smem_u32(&bar_pb_empty[bs]), bphase ^ 1u, abort_flag);
+              if (!ok) break;
+              const uint32_t bfull = smem_u32(&bar_pb_full[bs]);
+              mbar_arrive_expect_tx(bfull, (uint32_t)p.pk_b_bytes);
+              tma_load_2d(pk_b + bs * (uint32_t)p.pk_b_bytes, &map_b, bfull,
+                          ((dy * 3 + dx) * p.kp + ch * kChunkK) / 2, t.nt * p.umma_n);
+              if (++bs == kPkSlots) { bs = 0; bphase ^= 1u; }
+            }
+          }
+        }
+      }
+    }
+  } else if (PACKED && warp >= kFirstUnpackWarp) {
+    // ------------------------------------------------------------ unpack warps (packed operands)
+    // nibbles -> int8 in the 128-byte-swizzled K-major layout a tensor copy would have written:
+    // row r, 16-byte chunk j of the tile lives at r * 128 + ((j ^ (r & 7)) << 4).  Activation
+    // codes are two's-complement nibbles; weight nibbles hold the unsigned code q and become
+    // q - zero_point[channel], the value the convolution multiplies.
+    const int ut = threadIdx.x - 32 * kFirstUnpackWarp;          // 0 .. 127
+    uint8_t* const a_ring_ptr = smem_raw;
+    uint8_t* const b_ring_ptr = smem_raw + (b_ring - raw);
+    const uint8_t* const pk_a_ptr = smem_raw + (pk_a - raw);
+    const uint8_t* const pk_b_ptr = smem_raw + (pk_b - raw);
+    const int a_items = (p.a_bytes / kChunkK) * 8;               // 16-byte output chunks per copy
+    const int b_items = p.umma_n * 8;
+    int as = 0, bs = 0, aslot = 0, bst = 0, last_nt = -1;
+    uint32_t pa_phase = 0, pb_phase = 0, aphase = 0, bphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const HaloTile t = decode(tile, p);
+      if (t.nt != last_nt) {
+        asm volatile("bar.sync 2, 128;" ::: "memory");           // the table's readers are done
+        const uint32_t z = (uint32_t)(int)p.w_zp[t.nt * p.umma_n + ut] & 0xffu;
+        zp4_sh[ut] = z * 0x01010101u;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        last_nt = t.nt;
+      }
+      for (int ch = 0; ch < p.chunks && ok; ++ch) {
+        for (int dx = 0; dx < 3 && ok; ++dx) {
+          ok = mbar_wait(smem_u32(&bar_pa_full[as]), pa_phase, abort_flag) &&
+               mbar_wait(smem_u32(&bar_a_empty[aslot]), aphase ^ 1u, abort_flag);
+          if (!ok) break;
+          {
+            const uint8_t* src = pk_a_ptr + (size_t)as * p.pk_a_slot_bytes;
+            uint8_t* dst = a_ring_ptr + (size_t)aslot * p.a_slot_bytes;
+            for (int i = ut; i < a_items; i += 32 * kUnpackWarps) {
+              const int r = i >> 3, j = i & 7;
+              const uint2 pk = *reinterpret_cast<const uint2*>(src + r * 64 + j * 8);
+              *reinterpret_cast<uint4*>(dst + r * 128 + ((j ^ (r & 7)) << 4)) = unpack16<true>(pk, 0u);
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&bar_a_full[aslot]));
+            mbar_arrive(smem_u32(&bar_pa_empty[as]));
+          }
+          if (++as == kPkSlots) { as = 0; pa_phase ^= 1u; }
+          if (++aslot == p.a_slots) { aslot = 0; aphase ^= 1u; }
+          for (int dy = 0; dy < 3; ++dy) {
+            ok = mbar_wait(smem_u32(&bar_pb_full[bs]), pb_phase, abort_flag) &&
+                 mbar_wait(smem_u32(&bar_b_empty[bst]), bphase ^ 1u, abort_flag);
+            if (!ok) break;
+            {
+              const uint8_t* src = pk_b_ptr + (size_t)bs * p.pk_b_bytes;
+              uint8_t* dst = b_ring_ptr + (size_t)bst * p.b_tile_bytes;
+              for (int i = ut; i < b_items; i += 32 * kUnpackWarps) {
+                const int r = i >> 3, j = i & 7;
+                const uint2 pk = *reinterpret_cast<const uint2*>(src + r * 64 + j * 8);
+                *reinterpret_cast<uint4*>(dst + r * 128 + ((j ^ (r & 7)) << 4)) =
+                    unpack16<false>(pk, zp4_sh[r]);
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(smem_u32(&bar_b_full[bst]));
+              mbar_arrive(smem_u32(&bar_pb_empty[bs]));
+            }
+            if (++bs == kPkSlots) { bs = 0; pb_phase ^= 1u; }
+            if (++bst == p.b_stages) { bst = 0; bphase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ operand TMA producer
     if (lane == 0) {
       int aslot = 0, bst = 0;
@@ -397,7 +551,10 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
                       const float* residual, float* sum_out, const float* x_zp,
-                      const int32_t* w_csum) {
+                      const int32_t* w_csum, const float* packed_w_zp) {
+  // packed_w_zp != NULL: `codes` and `wcodes` hold two 4-bit codes per byte (activations
+  // two's complement, weights the unsigned code q) and are expanded in shared memory
+  const bool packed = packed_w_zp != nullptr;
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   static int sm_count = 0;
@@ -421,7 +578,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   const int rows1 = 128 / g->w, rows2 = 256 / g->w;
   const int chunks = ceil_div(g->cin, kChunkK);
   const char* force_n = getenv("MODIFF_HALO_N");      // measurement aid: "128" keeps N = 128
-  const bool wide = !with_sum_rows && g->cout % 256 == 0 && !(force_n && force_n[0] == '1');
+  const bool wide = !with_sum_rows && !packed && g->cout % 256 == 0 &&
+                    !(force_n && force_n[0] == '1');
   p.umma_n = with_sum_rows ? 144 : (wide ? 256 : 128);
   p.n_real = wide ? 256 : 128;
   p.n_tiles = g->cout / p.n_real;
@@ -436,7 +594,8 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   };
   p.mh = 1;
   // two m-halves of 144 columns, double buffered, would need 576 of the 512 tensor-memory columns
-  if (!with_sum_rows && !wide && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1)) p.mh = 2;
+  if (!with_sum_rows && !wide && !packed && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1))
+    p.mh = 2;
   p.nbuf = 2;
   p.rows = p.mh * rows1;
   p.half_rows = rows1;
@@ -449,7 +608,12 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   // shared memory: at least two activation copies, two cached-output half tiles and four weight
   // stages; what is left goes first to a third cached-output tile (its load latency from HBM is
   // the longest in the kernel), then to a third activation copy, then to weight stages
-  const int budget = 222 * 1024;
+  p.pk_a_bytes = packed ? p.a_bytes / 2 : 0;
+  p.pk_a_slot_bytes = round_up(p.pk_a_bytes, 128);
+  p.pk_b_bytes = packed ? p.b_tile_bytes / 2 : 0;
+  p.w_zp = packed_w_zp;
+  const int staging = kPkSlots * (p.pk_a_slot_bytes + p.pk_b_bytes);
+  const int budget = 222 * 1024 - staging;
   p.a_slots = 2;
   p.o_slots = 2;
   auto left = [&]() { return budget - p.a_slots * p.a_slot_bytes - p.o_slots * kOHalfBytes; };
@@ -469,29 +633,33 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   p.residual = residual;
   p.sum_out = sum_out;
   p.o_out = o_hat;
-  const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes;
+  const size_t smem = (size_t)fixed + (size_t)p.b_stages * p.b_tile_bytes + (size_t)staging;
 
+  // packed operands: every byte extent along the channel / K dimension halves, and the staging
+  // slots are plain rows (the unpack warps apply the swizzle)
+  const int pk = packed ? 2 : 1;
+  const CUtensorMapSwizzle swz = packed ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap map_a, map_b, map_o;
   {
-    cuuint64_t dims[5] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp, (cuuint64_t)d.hp, 1u,
+    cuuint64_t dims[5] = {(cuuint64_t)d.cp / pk, (cuuint64_t)d.wp, (cuuint64_t)d.hp, 1u,
                           (cuuint64_t)g->batch};
-    cuuint64_t strides[4] = {(cuuint64_t)d.cp, (cuuint64_t)d.wp * d.cp,
-                             (cuuint64_t)d.hp * d.wp * d.cp, (cuuint64_t)d.hp * d.wp * d.cp};
-    cuuint32_t box[5] = {(cuuint32_t)kChunkK, (cuuint32_t)g->w, (cuuint32_t)(p.rows + 2), 1u, 1u};
+    cuuint64_t strides[4] = {(cuuint64_t)d.cp / pk, (cuuint64_t)d.wp * d.cp / pk,
+                             (cuuint64_t)d.hp * d.wp * d.cp / pk, (cuuint64_t)d.hp * d.wp * d.cp / pk};
+    cuuint32_t box[5] = {(cuuint32_t)kChunkK / pk, (cuuint32_t)g->w, (cuuint32_t)(p.rows + 2), 1u, 1u};
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void*)codes, dims, strides, box,
-                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(activation codes) failed: %d", (int)r);
   }
   {
-    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp, (cuuint64_t)p.n_tiles * p.umma_n};
-    cuuint64_t strides[1] = {(cuuint64_t)d.taps * d.kp};
-    cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)p.umma_n};
+    cuuint64_t dims[2] = {(cuuint64_t)d.taps * d.kp / pk, (cuuint64_t)p.n_tiles * p.umma_n};
+    cuuint64_t strides[1] = {(cuuint64_t)d.taps * d.kp / pk};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkK / pk, (cuuint32_t)p.umma_n};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)wcodes, dims, strides, box,
-                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(weight codes) failed: %d", (int)r);
@@ -509,10 +677,16 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
       return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output) failed: %d", (int)r);
   }
 
-  static SmemLimit smem_limit;
-  MODIFF_CUDA(raise_smem_limit(igemm_halo_kernel, smem, smem_limit));
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
-  igemm_halo_kernel<<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);
+  if (packed) {
+    static SmemLimit smem_limit_packed;
+    MODIFF_CUDA(raise_smem_limit(igemm_halo_kernel<true>, smem, smem_limit_packed));
+    igemm_halo_kernel<true><<<grid, kThreadsPacked, smem, s>>>(map_a, map_b, map_o, p);
+  } else {
+    static SmemLimit smem_limit;
+    MODIFF_CUDA(raise_smem_limit(igemm_halo_kernel<false>, smem, smem_limit));
+    igemm_halo_kernel<false><<<grid, kThreads, smem, s>>>(map_a, map_b, map_o, p);
+  }
   MODIFF_LAUNCH_CHECK("igemm_halo_kernel");
   return MODIFF_OK;
 }

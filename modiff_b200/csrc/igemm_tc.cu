@@ -629,7 +629,7 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                       const float* x_scale, const float* w_scale, const int32_t* w_corr,
                       float* o_hat, int accumulate, const modiff_conv_geom* g, cudaStream_t s,
                       const float* residual, float* sum_out, const float* x_zp,
-                      const int32_t* w_csum);
+                      const int32_t* w_csum, const float* packed_w_zp);
 
 // MODIFF_IGEMM_PAIR=1 sends 3x3 layers to the two-SM kernel (cta_group::2, igemm_pair.cu): same
 // results, measured slower than the single-CTA kernel at every layer of the covered models, so
@@ -709,7 +709,7 @@ static int igemm_conv_impl(const int8_t* codes, const int8_t* wcodes, int with_s
                              g, s, residual, sum_out, x_zp, w_csum);
   if (halo_enabled() && halo_supported(g, with_sum_rows, per_sample, bias, acc_out, o_hat))
     return launch_igemm_halo(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
-                             g, s, residual, sum_out, x_zp, w_csum);
+                             g, s, residual, sum_out, x_zp, w_csum, nullptr);
   int rc2 = launch_igemm_tc(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
                             bias, g, per_sample, acc_out, s, x_zp, w_csum);
   if (rc2 || !residual) return rc2;
@@ -751,6 +751,27 @@ extern "C" int modiff_igemm_conv_offset(const int8_t* codes, const int8_t* wcode
                    "residual and sum must be 16-byte aligned");
   return igemm_conv_impl(codes, wcodes, with_sum_rows, x_scale, w_scale, w_corr, o_hat, accumulate,
                          bias, g, 0, impl, nullptr, residual, sum_out, x_zp, w_csum, stream);
+}
+
+extern "C" int modiff_igemm_conv_packed4(const uint8_t* codes4, const uint8_t* wcodes4,
+                                         const float* w_zp, const float* x_scale,
+                                         const float* w_scale, float* o_hat, int accumulate,
+                                         const modiff_conv_geom* g, const float* residual,
+                                         float* sum_out, void* stream) {
+  int rc = validate_geom(g);
+  if (rc) return rc;
+  MODIFF_CHECK_ARG(codes4 && wcodes4 && w_zp && x_scale && w_scale && o_hat, "NULL pointer argument");
+  MODIFF_CHECK_ARG((((uintptr_t)codes4 | (uintptr_t)wcodes4) & 15) == 0,
+                   "code buffers must be 16-byte aligned");
+  MODIFF_CHECK_ARG((residual == nullptr) == (sum_out == nullptr), "residual and sum go together");
+  if (!halo_supported(g, 0, 0, nullptr, nullptr, o_hat) || g->cin % 128 != 0)
+    return set_error(MODIFF_ERR_UNSUPPORTED,
+                     "packed 4-bit operands cover 3x3 stride-1 pad-1 layers with cin and cout "
+                     "multiples of 128 and at least 128 pixels per image in rows of 16..64");
+  return launch_igemm_halo(reinterpret_cast<const int8_t*>(codes4),
+                           reinterpret_cast<const int8_t*>(wcodes4), 0, x_scale, w_scale, nullptr,
+                           o_hat, accumulate, g, (cudaStream_t)stream, residual, sum_out, nullptr,
+                           nullptr, w_zp);
 }
 
 extern "C" int modiff_device_status(int* status, int reset) {

@@ -198,3 +198,37 @@ extern "C" int modiff_adaround_fake_quant(const float* w, const float* alpha, co
   MODIFF_LAUNCH_CHECK("adaround_fake_quant_kernel");
   return MODIFF_OK;
 }
+
+// Packed 4-bit weights for modiff_igemm_conv_packed4: the packed-weight rows of
+// modiff_weight_pack (int8 q - zero_point) become unsigned nibbles q, two per byte, element 2i in
+// the low nibble of byte i (the nibble order of qdiff/quant_layer_int4.py:341-346).
+namespace modiff {
+namespace {
+__global__ void pack_weights_int4_kernel(const int8_t* __restrict__ wcodes,
+                                         const float* __restrict__ w_zp,
+                                         uint8_t* __restrict__ packed, long long n_pairs,
+                                         int row_pairs, int* __restrict__ bad) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / row_pairs;
+    const int zp = (int)w_zp[r];
+    const int a = (int)wcodes[2 * i] + zp, b = (int)wcodes[2 * i + 1] + zp;
+    if ((a | b) & ~15) atomicExch(bad, 1);           // a code outside 0..15: not a 4-bit layer
+    packed[i] = (uint8_t)((a & 15) | ((b & 15) << 4));
+  }
+}
+}  // namespace
+}  // namespace modiff
+
+extern "C" int modiff_pack_weights_int4(const int8_t* wcodes, const float* w_zp, uint8_t* packed,
+                                        int64_t rows, int64_t row_bytes, int* bad, void* stream) {
+  MODIFF_CHECK_ARG(wcodes && w_zp && packed && bad, "NULL pointer argument");
+  MODIFF_CHECK_ARG(rows > 0 && row_bytes > 0 && row_bytes % 2 == 0 && row_bytes < (1ll << 31),
+                   "bad shape");
+  const long long n = rows * row_bytes / 2;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  modiff::pack_weights_int4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+      wcodes, w_zp, packed, n, (int)(row_bytes / 2), bad);
+  MODIFF_LAUNCH_CHECK("pack_weights_int4_kernel");
+  return MODIFF_OK;
+}

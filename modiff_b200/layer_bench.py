@@ -41,12 +41,30 @@ def main():
     ap.add_argument("--pair", action="store_true",
                     help="a residual block's conv1 (3x3 on GroupNorm+SiLU of x) and 1x1 shortcut on "
                          "the same x, quantised in shared sweeps (modiff_modq_pair)")
+    ap.add_argument("--attention-i8", action="store_true",
+                    help="time the integer attention (quantise + kernel) on [batch, cin, hw*hw]")
     ap.add_argument("--attention", action="store_true",
                     help="time ops.attention on [batch, cin, hw*hw] tensors instead of a layer")
     args = ap.parse_args()
 
     dev = torch.device("cuda")
     torch.manual_seed(0)
+    if args.attention_i8:
+        from . import ops
+        t = args.hw * args.hw
+        q, k, v = (torch.randn(args.batch, args.cin, t, device=dev) for _ in range(3))
+        scale = float(args.cin) ** -0.5
+        for _ in range(args.warmup):
+            ops.attention_i8_channel_major(q, k, v, scale)
+        _lib.TIMER = _lib.KernelTimer()
+        for _ in range(args.iters):
+            ops.attention_i8_channel_major(q, k, v, scale)
+        summ = _lib.TIMER.summary()
+        _lib.TIMER = None
+        print(json.dumps({"geometry": vars(args), "device_status": _lib.device_status(),
+                          "us_per_call": {n: 1000.0 * v_["ms"] / v_["launches"]
+                                          for n, v_ in summ.items()}}))
+        return
     if args.attention:
         from . import ops
         t = args.hw * args.hw

@@ -653,8 +653,47 @@ class QuantModule(nn.Module):
                   nbytes=((8 if accumulate else 4) + (8 if residual is not None else 0)) * n_out
                   + g.batch * g.cin * g.h * g.w + g.cout * g.cin * g.kh * g.kw, tag=g.key())
 
+    # MODIFF_PACKED_INT4=1 (or QuantModule.packed_int4 = True): W4 weight codes and A4 / A3
+    # activation codes of the layers the activation-reuse kernel covers travel two per byte and
+    # are expanded in shared memory (modiff_igemm_conv_packed4).  Same bits as the byte-per-code
+    # path; the activation planes are repacked by a separate kernel, so this path demonstrates
+    # the operand format rather than a speed-up and is off by default.
+    packed_int4 = os.environ.get("MODIFF_PACKED_INT4", "0") == "1"
+
+    def _packed4_ok(self, g, bias, acc_out):
+        aq = self.act_quantizer
+        return (self.packed_int4 and self.weight_quantizer.n_bits <= 4 and aq.n_bits <= 4 and aq.sym
+                and not aq.channel_wise and bias is None and acc_out is None and g.split == 0
+                and g.kh == 3 and g.kw == 3 and g.stride == 1
+                and (g.pad_t, g.pad_l, g.pad_b, g.pad_r) == (1, 1, 1, 1)
+                and g.cin % 128 == 0 and g.cout % 128 == 0 and g.w in (16, 32, 64)
+                and g.h & (g.h - 1) == 0 and g.h * g.w >= 128 and g.h >= 128 // g.w)
+
+    def _igemm_packed4(self, buf, pack, o_hat, accumulate, g, residual=None, out=None):
+        from .ops import pack_int4
+        if pack.get('wcodes4') is None:
+            rows, row_bytes = g.cout, pack['wcodes'].numel() // g.cout
+            w4 = torch.empty(rows * row_bytes // 2, dtype=torch.uint8, device=o_hat.device)
+            bad = _zeros(1, torch.int32, o_hat.device)
+            _lib.call('modiff_pack_weights_int4', pack['wcodes'].data_ptr(), pack['w_zp'].data_ptr(),
+                      w4.data_ptr(), rows, row_bytes, bad.data_ptr(), _lib.stream_ptr())
+            if int(bad.item()):                       # one-time host read at pack time
+                raise ModiffError("weight codes do not fit 4 bits")
+            pack['wcodes4'] = w4
+            _lib.bump_generation()
+        codes4 = pack_int4(buf.codes)
+        _lib.call('modiff_igemm_conv_packed4', codes4.data_ptr(), pack['wcodes4'].data_ptr(),
+                  pack['w_zp'].data_ptr(), buf.x_scale.data_ptr(), pack['w_scale'].data_ptr(),
+                  o_hat.data_ptr(), int(accumulate), C.byref(g), _lib.ptr(residual), _lib.ptr(out),
+                  _lib.stream_ptr(),
+                  nbytes=(8 if accumulate else 4) * o_hat.numel() + (g.batch * g.cin * g.h * g.w
+                                                                     + g.cout * g.cin * 9) // 2,
+                  tag=g.key())
+
     def _igemm(self, buf, pack, o_hat, accumulate, bias, g, acc_out=None):
         aq = self.act_quantizer
+        if pack['with_sum'] == 0 and self._packed4_ok(g, bias, acc_out):
+            return self._igemm_packed4(buf, pack, o_hat, accumulate, g)
         if self._use_im2col(g, buf):
             return self._igemm_im2col(buf, pack, o_hat, accumulate, bias, g, acc_out)
         if self._offset_codes():

@@ -295,3 +295,16 @@ def perturb_first_call(fn, rel=SENS_REL, seed=SENS_SEED):
         state["n"] += 1
         return out
     return wrapped
+
+
+# ---------------------------------------------------------------- first-stage decoder (kl-f8)
+# ddconfig of configs/latent-diffusion/lsun_churches-ldm-kl-8.yaml:47-56; random init seed 0; the
+# decoder is fully convolutional, so a 16x16 latent (128x128 pixels) exercises every layer.
+DECODER_CONFIG = dict(double_z=True, z_channels=4, resolution=256, in_channels=3, out_ch=3, ch=128,
+                      ch_mult=(1, 2, 4, 4), num_res_blocks=2, attn_resolutions=[], dropout=0.0)
+DECODER_CASE = dict(name="kl_f8_decode", embed_dim=4, batch=2, latent=16, init_seed=0, z_seed=41)
+
+
+def decoder_latents(c):
+    g = torch.Generator().manual_seed(c["z_seed"])
+    return torch.randn(c["batch"], c["embed_dim"], c["latent"], c["latent"], generator=g)

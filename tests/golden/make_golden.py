@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE (MoDiff's qdiff +
 ddim packages, imported read-only from a checkout) on CPU.
 
-    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali|running|sens|full [--case NAME]]
+    python tests/golden/make_golden.py /path/to/reference [--only layers|unet|weights|quantizer|ldm|plms|sd|cali|running|sens|full|decoder [--case NAME]]
 
 Needs the reference checkout, so it runs where that exists; the fixtures it writes are
 committed and are all the tests read.  Inputs and weights are NOT stored: they are re-created
@@ -537,11 +537,30 @@ def gen_full():
               "min sens", float(db.min()), flush=True)
 
 
+def gen_decoder():
+    """First-stage decoder: the reference's own Decoder (ldm/modules/diffusionmodules/model.py)
+    behind a 1x1 post_quant_conv as AutoencoderKL.decode composes them
+    (ldm/models/autoencoder.py:299-333; that class itself needs pytorch_lightning)."""
+    from ldm.modules.diffusionmodules.model import Decoder as RefDecoder
+    c = cases.DECODER_CASE
+    torch.manual_seed(c["init_seed"])
+    dec = RefDecoder(**cases.DECODER_CONFIG).eval()
+    pqc = nn.Conv2d(c["embed_dim"], cases.DECODER_CONFIG["z_channels"], 1)
+    z = cases.decoder_latents(c)
+    with torch.no_grad():
+        y = dec(pqc(z))
+    out = {c["name"] + "/image": y.numpy().copy(),
+           c["name"] + "/param_sum": np.float64(sum(float(p.double().sum()) for p in
+                                                    list(dec.parameters()) + list(pqc.parameters())))}
+    np.savez_compressed(os.path.join(HERE, "decoder.npz"), **out)
+    print("decoder.npz", tuple(y.shape), float(y.std()))
+
+
 if __name__ == "__main__":
-    torch.set_num_threads(os.cpu_count())
+    torch.set_num_threads(int(os.environ.get("MODIFF_GOLDEN_THREADS", os.cpu_count())))
     todo = dict(quantizer=gen_quantizer, layers=gen_layers, weights=gen_weights, unet=gen_unet,
                 ldm=gen_ldm, plms=gen_plms, sd=gen_sd, cali=gen_cali, running=gen_running,
-                sens=gen_sens, full=gen_full)
+                sens=gen_sens, full=gen_full, decoder=gen_decoder)
     for name, fn in todo.items():
         if ONLY in (None, name):
             fn()

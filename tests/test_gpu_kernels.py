@@ -471,3 +471,83 @@ def test_bounded_wait_gives_up_and_the_library_recovers(cuda):
     assert float(scale[0]) == float(d) and torch.equal(got.float(), q)
     with pytest.raises(L.ModiffError):
         L.call('modiff_wait_probe', 2_000_000_000, None, L.stream_ptr())   # limit above the cap
+
+
+PACKED4_CASES = [
+    # batch, cin, cout, hw
+    (3, 256, 256, 16),      # two K chunks, two channel tiles
+    (5, 128, 128, 32),      # 4-row tiles
+    (150, 128, 128, 16),    # more tiles than SMs
+    (1, 384, 128, 64),      # 2-row tiles, three K chunks
+]
+
+
+@pytest.mark.parametrize("accumulate", [True, False])
+@pytest.mark.parametrize("case", PACKED4_CASES, ids=lambda c: "b%d_c%d_o%d_hw%d" % c)
+def test_packed_int4_operands_give_the_same_bits(cuda, case, accumulate):
+    """W4 weight codes and 4-bit activation codes stored two per byte (the nibble order of
+    qdiff/quant_layer_int4.py:341-346) and expanded to int8 in shared memory: the output equals
+    the byte-per-code kernel's bit for bit, and the packed buffers are half the size."""
+    b, cin, cout, hw = case
+    L = _lib()
+    l = L.lib()
+    g = _geom(b, cin, cout, hw, hw, k=3, stride=1, pad=(1, 1, 1, 1))
+    torch.manual_seed(14)
+    x_codes = torch.randint(-8, 8, (b, cin, hw, hw), dtype=torch.int8)
+    w = torch.randn(cout, cin, 3, 3) * 0.05
+    ref, _, o_prev, ws = _run_igemm(x_codes, w, g, 4, L.IMPL_TCGEN05, cuda, accumulate=accumulate,
+                                    want_acc=False)
+    wcodes, ws, wz, wc, wdq = _pack(w, g, 4, 0, cuda)
+    assert not bool(wc.any())
+    codes = torch.zeros(l.modiff_codes_bytes(C.byref(g)), dtype=torch.int8, device=cuda)
+    one = torch.ones(2, device=cuda)
+    xf = x_codes.to(torch.float32).to(cuda).contiguous()
+    L.check(l.modiff_quantize_static(xf.data_ptr(), one.data_ptr(), codes.data_ptr(), C.byref(g), 8,
+                                     L.stream_ptr()))
+    codes4 = torch.empty(codes.numel() // 2, dtype=torch.uint8, device=cuda)
+    L.check(l.modiff_pack_int4(codes.data_ptr(), codes4.data_ptr(), codes.numel(), L.stream_ptr()))
+    w4 = torch.empty(wcodes.numel() // 2, dtype=torch.uint8, device=cuda)
+    bad = torch.zeros(1, dtype=torch.int32, device=cuda)
+    L.check(l.modiff_pack_weights_int4(wcodes.data_ptr(), wz.data_ptr(), w4.data_ptr(), cout,
+                                       wcodes.numel() // cout, bad.data_ptr(), L.stream_ptr()))
+    assert int(bad) == 0
+    o_hat = o_prev.clone().to(cuda)
+    xs = torch.tensor([0.01, 0.02], dtype=torch.float32, device=cuda)
+    L.check(l.modiff_igemm_conv_packed4(codes4.data_ptr(), w4.data_ptr(), wz.data_ptr(),
+                                        xs.data_ptr(), ws.data_ptr(), o_hat.data_ptr(),
+                                        int(accumulate), C.byref(g), None, None, L.stream_ptr()))
+    torch.cuda.synchronize()
+    assert L.device_status() == 0, "a bounded wait ran out inside the kernel"
+    assert torch.equal(o_hat.cpu(), ref)
+    # the nibble convention: element 2i in the low nibble, 2i + 1 in the high nibble
+    c8, c4 = codes.cpu().view(-1)[:64].to(torch.int32), codes4.cpu().view(-1)[:32].to(torch.int32)
+    assert torch.equal(c4 & 15, c8[0::2] & 15) and torch.equal(c4 >> 4, c8[1::2] & 15)
+
+
+def test_packed_int4_layer_switch(cuda, monkeypatch):
+    """QuantModule.packed_int4 routes an eligible W4A4 layer through the packed kernel: same
+    outputs and caches as the default path over three modulated steps."""
+    import modiff_b200 as m
+    torch.manual_seed(3)
+    org = torch.nn.Conv2d(128, 128, 3, padding=1)
+    wq = {'n_bits': 4, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 4, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    outs = []
+    for packed in (False, True):
+        mod = m.QuantModule(org, wq, aq, modulate=True).to(cuda)
+        mod.set_quant_state(True, True)
+        mod.packed_int4 = packed
+        mod.alias_output = False
+        g = torch.Generator().manual_seed(4)
+        x0 = torch.randn(4, 128, 32, 32, generator=g)
+        ys = []
+        with torch.no_grad():
+            for step in range(3):
+                ys.append(mod((x0 + 0.05 * step * torch.randn(x0.shape, generator=g)).to(cuda)))
+        outs.append((ys, mod.a_hat.clone(), mod._wpack.get('wcodes4') is not None))
+    assert outs[1][2] and not outs[0][2]
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs[0][1], outs[1][1])
+    assert m.device_status() == 0
