@@ -192,9 +192,12 @@ class KernelTimer:
 
     def __init__(self):
         self.records = {}
+        self.ops = {}         # entry point -> tensor-core operations the callers declared
 
-    def add(self, name, start, end, nbytes, tag=None):
+    def add(self, name, start, end, nbytes, tag=None, nops=0):
         self.records.setdefault(name, []).append((start, end, nbytes))
+        if nops:
+            self.ops[name] = self.ops.get(name, 0) + nops
         if tag is not None:
             self.records.setdefault((name, tag), []).append((start, end, nbytes))
 
@@ -205,7 +208,8 @@ class KernelTimer:
             if not isinstance(name, str):
                 continue
             ms = sum(s.elapsed_time(e) for s, e, _ in recs)
-            out[name] = dict(launches=len(recs), ms=ms, bytes=sum(b for _, _, b in recs))
+            out[name] = dict(launches=len(recs), ms=ms, bytes=sum(b for _, _, b in recs),
+                             ops=self.ops.get(name, 0))
         return out
 
     def by_tag(self):
@@ -215,7 +219,7 @@ class KernelTimer:
                 for k, r in self.records.items() if not isinstance(k, str)}
 
 
-def call(name, *args, nbytes=0, tag=None):
+def call(name, *args, nbytes=0, tag=None, nops=0):
     """Invoke an entry point, raise on a non-zero status, account its launches."""
     fn = getattr(lib(), name)
     if TIMER is None:
@@ -226,7 +230,7 @@ def call(name, *args, nbytes=0, tag=None):
         start.record()
         rc = fn(*args)
         end.record()
-        TIMER.add(name, start, end, nbytes, tag)
+        TIMER.add(name, start, end, nbytes, tag, nops)
     if rc != 0:
         check(rc)
     LAUNCHES[0] += KERNELS_PER_CALL.get(name, 0)

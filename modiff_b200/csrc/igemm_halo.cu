@@ -596,6 +596,10 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
   // two m-halves of 144 columns, double buffered, would need 576 of the 512 tensor-memory columns
   if (!with_sum_rows && !wide && !packed && rows2 <= g->h && g->h % rows2 == 0 && cost(2) < cost(1))
     p.mh = 2;
+  if (const char* e = getenv("MODIFF_HALO_MH")) {      // measurement aid: force the tile height
+    if (e[0] == '1') p.mh = 1;
+    if (e[0] == '2' && !with_sum_rows && !wide && !packed && rows2 <= g->h && g->h % rows2 == 0) p.mh = 2;
+  }
   p.nbuf = 2;
   p.rows = p.mh * rows1;
   p.half_rows = rows1;

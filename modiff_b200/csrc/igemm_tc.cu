@@ -51,6 +51,8 @@ struct TcParams {
   int tmem_cols;                 // allocation (power of two)
   int a_bytes;                   // bytes one activation-tile copy delivers
   int o_bytes;                   // bytes one cached-output-tile copy delivers
+  int row_epi;                   // linear layers: the cached output is token-major [rows][cout];
+                                 // a ring slot holds two swizzled boxes of 128 rows x 32 channels
   int chunks[2];                 // 128-byte K chunks per tap of segment 0 / 1
   int cbeg[2];                   // first channel of segment 0 / 1
   int nseg;
@@ -188,7 +190,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = mbar_wait(smem_u32(&bar_o_empty[oslot]), ophase ^ 1u, abort_flag);
             if (!ok) break;
             const uint32_t ofull = smem_u32(&bar_o_full[oslot]);
-            if (p.accumulate) {
+            if (p.accumulate && p.row_epi) {
+              mbar_arrive_expect_tx(ofull, (uint32_t)kOHalfBytes);
+              for (int b2 = 0; b2 < 2; ++b2)
+                tma_load_2d(obuf + oslot * kOHalfBytes + b2 * (kOHalfBytes / 2), &map_o, ofull,
+                            t.nt * 128 + half * 64 + b2 * 32, t.tn * p.bn);
+            } else if (p.accumulate) {
               mbar_arrive_expect_tx(ofull, (uint32_t)p.o_bytes);
               tma_load_3d(obuf + oslot * kOHalfBytes, &map_o, ofull, t.th * p.bh * p.d.wo,
                           t.nt * 128 + half * 64, t.tn * p.bn);
@@ -258,8 +265,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int hh = 0; hh < 2; ++hh) {
           ok = mbar_wait(smem_u32(&bar_o_ready[oslot]), ophase, abort_flag);
           if (!ok) break;
-          tma_store_3d(&map_o, obuf + oslot * kOHalfBytes, t.th * p.bh * p.d.wo,
-                       t.nt * 128 + hh * 64, t.tn * p.bn);
+          if (p.row_epi) {
+            for (int b2 = 0; b2 < 2; ++b2)
+              tma_store_2d(&map_o, obuf + oslot * kOHalfBytes + b2 * (kOHalfBytes / 2),
+                           t.nt * 128 + hh * 64 + b2 * 32, t.tn * p.bn);
+          } else {
+            tma_store_3d(&map_o, obuf + oslot * kOHalfBytes, t.th * p.bh * p.d.wo,
+                         t.nt * 128 + hh * 64, t.tn * p.bn);
+          }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           mbar_arrive(smem_u32(&bar_o_empty[oslot]));
@@ -334,9 +347,23 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           float* orow = obuf_ptr + (size_t)oslot * (kOHalfBytes / 4) + (size_t)ni * 64 * tile_px +
                         (size_t)(sub * 32) * tile_px + pl;
           const int colbase = hh * 64 + sub * 32;
+          // token-major layers: this warp's box is 128 rows x 32 channels, a row = 128 bytes whose
+          // 16-byte chunks are XORed with row % 8 (the 128-byte swizzle of the tensor copy), so the
+          // eight lanes of a quarter-warp touch eight different bank groups
+          uint8_t* rbox = reinterpret_cast<uint8_t*>(obuf_ptr) + (size_t)oslot * kOHalfBytes +
+                          (size_t)sub * (kOHalfBytes / 2) + (size_t)row * 128;
           float v[32];
+          if (p.row_epi) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * tile_px] : 0.0f;
+            for (int j4 = 0; j4 < 8; ++j4) {
+              float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.accumulate) f = *reinterpret_cast<const float4*>(rbox + ((j4 ^ (row & 7)) << 4));
+              v[4 * j4] = f.x; v[4 * j4 + 1] = f.y; v[4 * j4 + 2] = f.z; v[4 * j4 + 3] = f.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = p.accumulate ? orow[j * tile_px] : 0.0f;
+          }
 #pragma unroll
           for (int seg = 0; seg < NSEG; ++seg) {
             int a[32];
@@ -350,8 +377,15 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               v[j] = fmaf((float)iv, ep_scale[seg][colbase + j], v[j]);
             }
           }
+          if (p.row_epi) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) orow[j * tile_px] = v[j];
+            for (int j4 = 0; j4 < 8; ++j4)
+              *reinterpret_cast<float4*>(rbox + ((j4 ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) orow[j * tile_px] = v[j];
+          }
           if (hh == 1) tc_fence_before();
           // make the tile visible to the bulk-copy engine, then tell the store warp
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -514,8 +548,14 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   // The bulk-copy epilogue needs full-width row tiles of at least 4 pixels per image, per-tensor
   // scales, no bias and no accumulator dump.
   const int tile_px = p.bh * p.bw;
-  const bool tma_epi = !per_sample && !bias && !acc_out && tile_px >= 4 && p.bw == d.wo &&
-                       (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0);
+  // Linear layers (one pixel per row, output [rows][cout]): the same ring, filled and drained by
+  // 2-D copies of 128 rows x 32 channels with the 128-byte swizzle.
+  const bool row_epi = !per_sample && !bias && !acc_out && d.ho * d.wo == 1 && g->cout % 4 == 0 &&
+                       g->batch >= 128 && (((uintptr_t)o_hat & 15) == 0);
+  p.row_epi = row_epi ? 1 : 0;
+  const bool tma_epi = row_epi ||
+                       (!per_sample && !bias && !acc_out && tile_px >= 4 && p.bw == d.wo &&
+                        (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0));
   const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
   const uint32_t stage_bytes = kATileBytes + b_tile;
   const uint32_t o_ring = tma_epi ? (uint32_t)kOSlots * kOHalfBytes : 0u;
@@ -559,7 +599,21 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
 
   CUtensorMap map_o = map_b;   // placeholder when the bulk-copy epilogue is off
   p.o_bytes = 0;
-  if (tma_epi) {
+  if (row_epi) {
+    // Cached output of a linear layer: [rows][cout] fp32; boxes of 128 rows x 32 channels.
+    // Channels and rows beyond the tensor are filled with zeros on the way in and dropped on
+    // the way out, so ragged channel counts and row counts need no special case.
+    cuuint64_t dims[2] = {(cuuint64_t)g->cout, (cuuint64_t)g->batch};
+    cuuint64_t strides[1] = {(cuuint64_t)g->cout * 4};
+    cuuint32_t box[2] = {32u, 128u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&map_o, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)o_hat, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(cached output rows) failed: %d", (int)r);
+    p.o_bytes = kOHalfBytes;
+  } else if (tma_epi) {
     // Cached output: [batch][cout][ho*wo] fp32, innermost first.
     const int bn_box = p.bn < g->batch ? p.bn : g->batch;
     const int c_box = g->cout < 128 ? g->cout : 128;

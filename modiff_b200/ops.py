@@ -373,8 +373,11 @@ def attention(q, k, v, scale):
         vp = torch.empty(b * 2 * cr * tkp, dtype=torch.int16, device=dev)
         _lib.call('modiff_split_bf16_rows', v.data_ptr(), vp.data_ptr(), b, c, tk, cr, tkp,
                   _lib.stream_ptr())
+        # three bf16 products (hi*hi, hi*lo, lo*hi) for each of the two matrix products
         _lib.call('modiff_attention_tc', qp.data_ptr(), kp.data_ptr(), vp.data_ptr(), out.data_ptr(),
-                  b, c, t, tk, cp, tkp, cr, float(scale), _lib.stream_ptr())
+                  b, c, t, tk, cp, tkp, cr, float(scale), _lib.stream_ptr(),
+                  nbytes=2 * (qp.numel() + kp.numel() + vp.numel()) + 4 * out.numel(),
+                  nops=3 * 2 * 2 * b * t * tk * c)
         return out
     s = torch.empty((b, tk, t), dtype=torch.float32, device=dev)
     d1 = _lib.GemmBf16Desc(qp.data_ptr(), kp.data_ptr(), None, None, s.data_ptr(), 2, 2, 1, cp,
@@ -425,7 +428,9 @@ def attention_i8(q, k, v, scale, batch, heads, c, tq, tk, strides_q, strides_kv,
               scratch.data_ptr(), _lib.stream_ptr(), nbytes=9 * n_in)
     _lib.call('modiff_attention_i8', qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scales.data_ptr(),
               out.data_ptr(), batch, heads, c, tq, tk, so, float(scale), _lib.stream_ptr(),
-              nbytes=sum(sizes) + 4 * batch * heads * c * tq)
+              nbytes=sum(sizes) + 4 * batch * heads * c * tq,
+              # q k^T twice (maximum pass, weight pass) and w v^T once
+              nops=2 * batch * heads * tq * tk * (2 * c + c))
     return out
 
 

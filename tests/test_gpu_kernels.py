@@ -551,3 +551,28 @@ def test_packed_int4_layer_switch(cuda, monkeypatch):
         assert torch.equal(a, b)
     assert torch.equal(outs[0][1], outs[1][1])
     assert m.device_status() == 0
+
+
+@pytest.mark.parametrize("rows,cin,cout,w_bits", [(300, 512, 320, 8), (4096, 320, 2560, 8),
+                                                  (128, 128, 200, 4), (1000, 640, 640, 4)])
+@pytest.mark.parametrize("accumulate", [True, False])
+def test_linear_layers_bulk_copy_epilogue(cuda, rows, cin, cout, w_bits, accumulate):
+    """Token-major outputs [rows][cout] of linear layers with at least 128 rows travel through the
+    cached-output ring as swizzled 128 x 32 boxes: equal to the exact integer product (1e-5) and to
+    the CUDA-core kernel, ragged row and channel counts included."""
+    L = _lib()
+    g = _geom(rows, cin, cout, 1, 1, k=1)
+    torch.manual_seed(15)
+    x_codes = torch.randint(-127, 128, (rows, cin, 1, 1), dtype=torch.int8)
+    w = torch.randn(cout, cin, 1, 1) * 0.05
+    w[1] = w[1].abs() + 0.01
+    out_tc, _, o_prev, _ = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda,
+                                      accumulate=accumulate, want_acc=False)
+    out_simt, _, _, _ = _run_igemm(x_codes, w, g, w_bits, L.IMPL_SIMT, cuda, accumulate=accumulate,
+                                   want_acc=False)
+    exp_acc, dws = _expected_acc(x_codes, w, g, w_bits)
+    exp = o_prev.double() if accumulate else torch.zeros_like(o_prev).double()
+    exp = exp + exp_acc[0].double() * (float(np.float32(0.01)) * dws[0].double().view(1, -1, 1, 1))
+    err = (out_tc.double() - exp).abs().max() / exp.abs().max()
+    assert err < 1e-5, err
+    assert (out_tc - out_simt).abs().max() <= 1e-6 * exp.abs().max()
