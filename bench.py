@@ -44,10 +44,10 @@ CONFIGS = {
     "pixel_w4a3": dict(kind="pixel", w_bits=4, a_bits=3, split=True, batch=256, evals=100, seed=2,
                        workload="pixel UNet 3x32x32 W4A3 modulated, split shortcut, 100 DDIM quad "
                                 "steps, batch 256/GPU"),
-    "ldm_w8a8": dict(kind="ldm", w_bits=8, a_bits=8, batch=32, evals=500, seed=11,
+    "ldm_w8a8": dict(kind="ldm", w_bits=8, a_bits=8, batch=32, evals=500, seed=11, int8_attention=True,
                      workload="latent UNet 4x32x32 (LSUN-churches kl-8 shapes) W8A8 modulated, "
                               "DDIM -c 400 (500 evaluations), batch 32/GPU, decoder excluded"),
-    "sd_w8a8": dict(kind="sd", w_bits=8, a_bits=8, batch=8, evals=50, seed=21,
+    "sd_w8a8": dict(kind="sd", w_bits=8, a_bits=8, batch=8, evals=50, seed=21, int8_attention=True,
                     workload="SD-v1 UNet 4x64x64, context 77x768, W8A8 modulated, guidance 7.5 "
                              "(2x effective batch), 50 DDIM evaluations, batch 8/GPU"),
 }
@@ -245,8 +245,12 @@ def main():
                     help="asymmetric activation quantisers (the latent drivers' default without "
                          "--a_sym); the headline lines use symmetric ones")
     ap.add_argument("--int8-attention", action="store_true",
-                    help="integer attention kernel (q / k / v / softmax quantisers applied; the "
-                         "reference leaves them unapplied, so the headline lines keep it off)")
+                    help="integer attention kernel (q / k / v / softmax quantisers applied).  The "
+                         "latent and SD configurations are quoted WITH it and switch it on by "
+                         "default; the pixel configurations are quoted without")
+    ap.add_argument("--fp-attention", action="store_true",
+                    help="floating-point attention as the reference's code runs it (its attention "
+                         "quantisers are built but never applied), also for ldm_w8a8 / sd_w8a8")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-full", action="store_true",
                     help="time the CPU baseline on ALL steps of a batch-8 pass instead of the "
@@ -257,6 +261,8 @@ def main():
                          "headline configuration")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
+    args.int8_attention = ((args.int8_attention or cfg.get("int8_attention", False))
+                           and not args.fp_attention)
     if args.impl == "reference":
         return run_reference(args, cfg)
 
@@ -328,6 +334,8 @@ def main():
         workload += ", asymmetric activation codes"
     if args.int8_attention:
         workload += ", INT8 attention (q / k / v / softmax quantisers applied)"
+    elif cfg.get("int8_attention"):
+        workload += ", floating-point attention (reference behaviour)"
 
     out_host = torch.empty((world * batch,) + tuple(shape[1:])).pin_memory()
     dev_in = [t.to(dev) for t in host_in]

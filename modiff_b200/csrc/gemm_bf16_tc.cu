@@ -570,6 +570,9 @@ extern "C" int modiff_split_bf16(const float* x, uint16_t* planes, const modiff_
   MODIFF_CHECK_ARG(((uintptr_t)planes & 15) == 0, "planes must be 16-byte aligned");
   Derived d = derive(*g);
   const int hw = g->h * g->w;
+  if (hw == 1 && d.nplanes * d.hp * d.wp == 1)
+    // token-major linear layer: the planes are [token][2][cp], i.e. one padded row per token
+    return modiff_split_bf16_rows(x, planes, g->batch, 1, g->cin, 1, bf16_cp(g->cin), stream);
   const int pb = ceil_div(hw, kSplitTileP), cb = ceil_div(g->cin, kSplitTileC);
   const int64_t total = (int64_t)pb * cb * g->batch;
   MODIFF_CHECK_ARG(total < (1ll << 31), "activation tensor too large");

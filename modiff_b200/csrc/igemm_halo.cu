@@ -430,9 +430,11 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
       if (t.nt != last_nt) {
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ep_tid < p.n_real) {
-          ep_scale[ep_tid] = __fmul_rn(p.x_scale[0], p.w_scale[t.nt * p.n_real + ep_tid]);
-          ep_corr[ep_tid] = p.w_corr ? p.w_corr[t.nt * p.n_real + ep_tid] : 0;
-          ep_off[ep_tid] = p.x_zp ? -((int)p.x_zp[0] - 128) * p.w_csum[t.nt * p.n_real + ep_tid] : 0;
+          const int co = t.nt * p.n_real + ep_tid;
+          const bool cv = co < p.cout;          // the last channel tile may be partly empty
+          ep_scale[ep_tid] = cv ? __fmul_rn(p.x_scale[0], p.w_scale[co]) : 0.0f;
+          ep_corr[ep_tid] = (cv && p.w_corr) ? p.w_corr[co] : 0;
+          ep_off[ep_tid] = (cv && p.x_zp) ? -((int)p.x_zp[0] - 128) * p.w_csum[co] : 0;
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         last_nt = t.nt;
@@ -456,10 +458,13 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
                                  (size_t)(t.th * p.rows + m * p.half_rows) * p.w + row;
           // residual of the block (x + h, qdiff/quant_block.py:313): issued before the wait below
           // so that the loads are in flight while the cached-output tile arrives
+          // channels of this warp's 32 that exist (all of them except in a ragged last tile)
+          const int cvalid = min(32, p.cout - (t.nt * p.n_real + colbase));
           float res[32];
           if (p.residual) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) res[j] = __ldg(p.residual + out_off + (size_t)j * (p.h * p.w));
+            for (int j = 0; j < 32; ++j)
+              res[j] = j < cvalid ? __ldg(p.residual + out_off + (size_t)j * (p.h * p.w)) : 0.0f;
           }
           ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
@@ -492,11 +497,12 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
+          for (int j = 0; j < 32; ++j)
+            if (j < cvalid) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
           if (p.residual) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+              if (j < cvalid) p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
           }
           if (++oslot == p.o_slots) { oslot = 0; ophase ^= 1u; }
         }
@@ -540,7 +546,9 @@ bool halo_supported(const modiff_conv_geom* g, int with_sum_rows, int per_sample
   if (g->kh != 3 || g->kw != 3 || g->stride != 1) return false;
   if (g->pad_t != 1 || g->pad_b != 1 || g->pad_l != 1 || g->pad_r != 1) return false;
   if (per_sample || bias || acc_out || g->split != 0) return false;
-  if (g->cout % 128 != 0 || g->cin < 128 || g->cin % 16 != 0) return false;
+  // channel counts that are not a multiple of 128 (192, 320, ...) leave the last channel tile
+  // partly empty: the cached-output copies clip at the tensor's edge, the stores are masked
+  if (g->cout < 128 || g->cout % 32 != 0 || g->cin < 128 || g->cin % 16 != 0) return false;
   if (!is_pow2(g->w) || !is_pow2(g->h) || g->w < 16 || g->w > 64) return false;
   if (g->h * g->w < 128 || (128 / g->w) > g->h) return false;
   if (((uintptr_t)o_hat & 15) != 0) return false;
@@ -582,7 +590,7 @@ int launch_igemm_halo(const int8_t* codes, const int8_t* wcodes, int with_sum_ro
                     !(force_n && force_n[0] == '1');
   p.umma_n = with_sum_rows ? 144 : (wide ? 256 : 128);
   p.n_real = wide ? 256 : 128;
-  p.n_tiles = g->cout / p.n_real;
+  p.n_tiles = ceil_div(g->cout, p.n_real);
   p.b_tile_bytes = p.umma_n * kChunkK;
   // 256-pixel tiles halve the weight traffic but can leave the last wave emptier: compare
   // shared-memory fill bytes per 128 output pixels divided by the wave efficiency

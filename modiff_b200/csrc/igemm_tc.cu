@@ -818,7 +818,7 @@ extern "C" int modiff_igemm_conv_packed4(const uint8_t* codes4, const uint8_t* w
   MODIFF_CHECK_ARG((((uintptr_t)codes4 | (uintptr_t)wcodes4) & 15) == 0,
                    "code buffers must be 16-byte aligned");
   MODIFF_CHECK_ARG((residual == nullptr) == (sum_out == nullptr), "residual and sum go together");
-  if (!halo_supported(g, 0, 0, nullptr, nullptr, o_hat) || g->cin % 128 != 0)
+  if (!halo_supported(g, 0, 0, nullptr, nullptr, o_hat) || g->cin % 128 != 0 || g->cout % 128 != 0)
     return set_error(MODIFF_ERR_UNSUPPORTED,
                      "packed 4-bit operands cover 3x3 stride-1 pad-1 layers with cin and cout "
                      "multiples of 128 and at least 128 pixels per image in rows of 16..64");

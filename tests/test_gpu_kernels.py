@@ -257,6 +257,8 @@ HALO_CASES = [
     (2, 192, 384, 16),      # three channel tiles
     (150, 128, 128, 16),    # more tiles than SMs: every CTA walks several tiles
     (80, 512, 256, 16),     # four K chunks, 256 output channels per tile, several tiles per pair
+    (6, 192, 192, 32),      # latent-UNet width: K chunk and last channel tile half empty
+    (4, 320, 320, 16),      # SD width: 2.5 channel tiles
 ]
 
 
