@@ -241,6 +241,39 @@ __device__ inline float exp2_approx(float x) {
   return r;
 }
 
+// Softmax weights of 32 scores of one query row: u8 codes rne(255 * exp2((S - m) * c2)), (S - m) <= 0
+// exactly, one fp32 product, hardware exp2.  The codes go to the row's 128-byte line of the weight
+// tile (16-byte chunks XORed with row % 8, the tile's swizzle); their sum is added to l_part.
+// MAGIC: (float)(S - m) without the conversion unit (the caller guarantees |S - m| < 2^22).
+// MASK: only the first `nvalid` scores are keys, the others get weight 0.
+template <bool MAGIC, bool MASK>
+__device__ inline void weights32(const int (&a)[32], int m_row, float c2, int nvalid, uint8_t* prow,
+                                 int chunk0, int row, int& l_part) {
+  const int bias_i = 0x4B400000 - m_row;       // bits of 12582912.0f = 1.5 * 2^23
+#pragma unroll
+  for (int g8 = 0; g8 < 2; ++g8) {
+    uint32_t wds[4];
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+      uint32_t u[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int idx = g8 * 16 + wd * 4 + e;
+        const float x = MAGIC ? __fadd_rn(__int_as_float(a[idx] + bias_i), -12582912.0f)
+                              : (float)(a[idx] - m_row);
+        const float pr = exp2_approx(__fmul_rn(x, c2));
+        // adding 1.5 * 2^23 rounds half to even and leaves the code in the low mantissa byte
+        u[e] = __float_as_uint(__fadd_rn(__fmul_rn(pr, 255.0f), 12582912.0f));
+        if (MASK && idx >= nvalid) u[e] = 0u;
+      }
+      wds[wd] = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+      l_part = (int)__dp4a(wds[wd], 0x01010101u, (unsigned)l_part);   // sum of four u8 codes
+    }
+    const int chunk = (chunk0 + g8) ^ (row & 7);
+    *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnI8Params p) {
@@ -425,6 +458,9 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint8_t* p_ptr = smem_raw + 2 * kTile;
     const float dq = p.scales[0], dk = p.scales[1], dv = p.scales[2];
     const float c2 = __fmul_rn(__fmul_rn(dq, dk), __fmul_rn(p.scale, 1.4426950408889634f));
+    // |S - m| <= 2 * 128 * 128 * channels: below 2^22 the integer-to-float conversion is an integer
+    // add into the mantissa of 1.5 * 2^23 and one exact subtraction (no conversion-unit cycles)
+    const bool magic_ok = p.c * 32768 < (1 << 22);
     const int ch_half = ((p.d_rows / 2 + 31) / 32) * 32;       // channel columns of warp half 0
     uint32_t s_count = 0, p_count = 0, ophase = 0;
     bool ok = true;
@@ -444,9 +480,14 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tc_ld32(t_lane + b * 128u + (uint32_t)(half * 64 + c0), a);
           tc_wait_ld();
           const int key0 = j * 128 + half * 64 + c0;
+          if (key0 + 32 <= p.tk) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (key0 + e < p.tk) mx = max(mx, a[e]);
+            for (int e = 0; e < 32; ++e) mx = max(mx, a[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (key0 + e < p.tk) mx = max(mx, a[e]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -474,25 +515,14 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tc_ld32(t_lane + b * 128u + (uint32_t)(half * 64 + c0), a);
           tc_wait_ld();
           const int key0 = j * 128 + half * 64 + c0;
-#pragma unroll
-          for (int g8 = 0; g8 < 2; ++g8) {
-            uint32_t wds[4];
-#pragma unroll
-            for (int wd = 0; wd < 4; ++wd) {
-              uint32_t bits[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int idx = g8 * 16 + wd * 4 + e;
-                // (S - m) <= 0 exactly; one fp32 product, hardware exp2, round half to even
-                const float pr = exp2_approx(__fmul_rn((float)(a[idx] - m_row), c2));
-                const float u = __fadd_rn(__fmul_rn(pr, 255.0f), 12582912.0f);
-                bits[e] = (key0 + idx < p.tk) ? (__float_as_uint(u) & 0xffu) : 0u;
-              }
-              wds[wd] = bits[0] | (bits[1] << 8) | (bits[2] << 16) | (bits[3] << 24);
-              l_part = (int)__dp4a(wds[wd], 0x01010101u, (unsigned)l_part);   // sum of four u8 codes
-            }
-            const int chunk = (half * 4 + (c0 >> 4) + g8) ^ (row & 7);
-            *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+          const int chunk0 = half * 4 + (c0 >> 4);
+          const bool ragged = key0 + 32 > p.tk;      // only the last key block can be
+          if (magic_ok) {
+            if (ragged) weights32<true, true>(a, m_row, c2, p.tk - key0, prow, chunk0, row, l_part);
+            else weights32<true, false>(a, m_row, c2, 32, prow, chunk0, row, l_part);
+          } else {
+            if (ragged) weights32<false, true>(a, m_row, c2, p.tk - key0, prow, chunk0, row, l_part);
+            else weights32<false, false>(a, m_row, c2, 32, prow, chunk0, row, l_part);
           }
         }
         tc_fence_before();

@@ -28,15 +28,6 @@ struct ProbeParams {
   int m_rows;           // rows per CTA (128)
 };
 
-__device__ inline uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ inline void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 
 // rows x 128 bytes from global memory into the 128-byte-swizzled tile at `dst`
 __device__ inline void fill_swizzled(uint8_t* dst, const int8_t* src, int rows) {

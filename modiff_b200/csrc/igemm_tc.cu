@@ -59,6 +59,7 @@ struct TcParams {
   int with_sum;
   int accumulate;
   int per_sample;
+  int ksplit;                    // CTAs of a cluster sharing one tile's K range (1 = off)
   const float* x_scale;
   const float* w_scale;
   const int32_t* w_corr;
@@ -87,7 +88,14 @@ __device__ inline TileCoord decode_tile(int tile, const TcParams& p) {
 // epilogue, shared -> global after it), so the epilogue threads touch only tensor memory and
 // shared memory.  Used for full-size layers with per-tensor scales and no bias; the generic
 // variant reads and writes o_hat directly and covers everything else.
-template <int NSEG, bool WITH_SUM, bool TMA_EPI>
+//
+// KSPLIT (layers with fewer tiles than SMs, e.g. 768 channels at 2x2 or 4x4): a cluster of
+// `p.ksplit` CTAs shares ONE tile.  Each CTA accumulates a contiguous part of the K range
+// (taps x channel chunks) in its own tensor memory, leaves the int32 partial sums in its shared
+// memory, and after a cluster barrier each CTA adds up, across the cluster's shared memories,
+// the 128 / ksplit output channels it owns and applies the epilogue to them.  Integer addition
+// is associative, so the accumulators equal the unsplit kernel's bit for bit.
+template <int NSEG, bool WITH_SUM, bool TMA_EPI, bool KSPLIT = false>
 __global__ void __launch_bounds__(kThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_o, const TcParams p) {
@@ -149,6 +157,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_sh;
 
+  // KSPLIT: one tile per cluster, this CTA's share of its K iterations; else a persistent walk
+  const int krank = KSPLIT ? (int)cluster_ctarank() : 0;
+  const int tile_first = KSPLIT ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x;
+  const int tile_step = KSPLIT ? p.total_tiles : (int)gridDim.x;
+  const int it_all = p.d.taps * p.chunks[0];
+  const int it_lo = KSPLIT ? (krank * it_all) / p.ksplit : 0;
+  const int it_hi = KSPLIT ? ((krank + 1) * it_all) / p.ksplit : it_all;
+
   const int k_iters_seg0 = p.d.taps * p.chunks[0];
   const int k_iters_seg1 = (p.nseg == 2) ? p.d.taps * p.chunks[1] : 0;
   const int howo = p.d.ho * p.d.wo;
@@ -161,7 +177,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t ophase = 0;
       int oslot = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step) {
         const TileCoord t = decode_tile(tile, p);
         for (int seg = 0; seg < p.nseg && ok; ++seg) {
           for (int tap = 0; tap < p.d.taps && ok; ++tap) {
@@ -169,6 +185,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int plane = (r % p.g.stride) * p.g.stride + (sx % p.g.stride);
             const int dh = r / p.g.stride, dw = sx / p.g.stride;
             for (int ch = 0; ch < p.chunks[seg]; ++ch) {
+              if (KSPLIT) {
+                const int itn = tap * p.chunks[0] + ch;
+                if (itn < it_lo || itn >= it_hi) continue;    // another CTA of the cluster's
+              }
               ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
               if (!ok) break;
               const uint32_t full = smem_u32(&bar_full[stage]);
@@ -218,13 +238,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int buf = 0;
       uint32_t bphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      for (int tile = tile_first; tile < p.total_tiles; tile += tile_step) {
         ok = mbar_wait(smem_u32(&bar_tmem_empty[buf]), bphase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
         for (int seg = 0; seg < p.nseg; ++seg) {
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.buf_cols + seg * p.umma_n);
-          const int iters = seg == 0 ? k_iters_seg0 : k_iters_seg1;
+          const int iters = KSPLIT ? it_hi - it_lo : (seg == 0 ? k_iters_seg0 : k_iters_seg1);
           for (int it = 0; it < iters; ++it) {
             ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
             if (!ok) break;
@@ -260,7 +280,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int oslot = 0;
       uint32_t ophase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step) {
         const TileCoord t = decode_tile(tile, p);
         for (int hh = 0; hh < 2; ++hh) {
           ok = mbar_wait(smem_u32(&bar_o_ready[oslot]), ophase, abort_flag);
@@ -301,7 +321,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int oslot = 0;
     int last_nt = -1;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+    for (int tile = tile_first; tile < p.total_tiles; tile += tile_step) {
       const TileCoord t = decode_tile(tile, p);
       // per-tile channel parameters (only when the channel tile changes)
       if (t.nt != last_nt) {
@@ -397,6 +417,22 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (++oslot == kOSlots) { oslot = 0; ophase ^= 1u; }
         }
         if (!ok) break;
+      } else if (KSPLIT) {
+        // partial sums of this CTA's K range -> its own shared memory as [column][row] (the tile
+        // ring is idle: every product that read it has completed); column 128 = the sum row
+        int32_t* part = reinterpret_cast<int32_t*>(smem_raw);
+#pragma unroll 1
+        for (int c2 = 0; c2 < 2; ++c2) {
+          int a[32];
+          tc_ld32(t_row + col0 + c2 * 32, a);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[(col0 + c2 * 32 + j) * 128 + row] = a[j];
+        }
+        if (WITH_SUM && half == 0) part[128 * 128 + row] = rsum[0];
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
       } else {
         const int n = t.tn * p.bn + ni;
         const int hw = (t.th * p.bh + hi) * p.d.wo + (t.tw * p.bw + wi);
@@ -464,6 +500,52 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   }
 
+  if (KSPLIT) {
+    __syncwarp();
+    cluster_sync_all();          // every CTA's partial sums are in its shared memory
+    if (warp >= 2 && warp < 2 + kEpiWarps && tile_first < p.total_tiles && !abort_sh) {
+      const TileCoord t = decode_tile(tile_first, p);
+      const int ep_tid = threadIdx.x - 64;
+      const int row = ep_tid & 127;
+      const int cols_cta = 128 / p.ksplit;             // output channels this CTA finishes
+      const int cpt = cols_cta / 2;                    // ... and each of its threads
+      const int cbase = krank * cols_cta + (ep_tid >> 7) * cpt;
+      const int tile_px = p.bh * p.bw;
+      const int ni = row / tile_px, pl = row % tile_px;
+      const int n = t.tn * p.bn + ni;
+      const int hw = (t.th * p.bh + pl / p.bw) * p.d.wo + (t.tw * p.bw + pl % p.bw);
+      const bool valid = n < p.g.batch;
+      const size_t m = (size_t)n * howo + hw;
+      const float xs = p.per_sample ? (valid ? p.x_scale[n] : 0.0f) : p.x_scale[0];
+      const bool offset_codes = p.x_zp != nullptr;
+      uint32_t peer[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) peer[r] = map_to_cta(raw, (uint32_t)(r < p.ksplit ? r : 0));
+      int rs = 0;
+      if (WITH_SUM) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < p.ksplit) rs += ld_cluster_s32(peer[r] + (uint32_t)(128 * 128 + row) * 4u);
+      }
+      for (int j = 0; j < cpt; ++j) {
+        const int cl = cbase + j;
+        const int co = t.nt * 128 + cl;
+        int iv = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < p.ksplit) iv += ld_cluster_s32(peer[r] + (uint32_t)(cl * 128 + row) * 4u);
+        if (WITH_SUM) iv += ep_corr[0][cl] * rs;
+        if (offset_codes) iv += ep_off[0][cl];
+        if (valid && co < p.g.cout) {
+          float* o = p.o_hat + ((size_t)n * p.g.cout + co) * howo + hw;
+          const float old = p.accumulate ? *o : 0.0f;
+          *o = fmaf((float)iv, __fmul_rn(xs, ep_scale[0][cl]), old) + ep_bias[cl];
+          if (p.acc_out) p.acc_out[m * p.g.cout + co] = iv;
+        }
+      }
+    }
+  }
+
   // ---------------------------------------------------------------- teardown
   __syncwarp();
   if (abort_sh) {
@@ -472,6 +554,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if (KSPLIT) cluster_sync_all();   // peers may still be reading this CTA's partial sums
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -545,16 +628,37 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   p.o_hat = o_hat;
   p.acc_out = acc_out;
 
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    MODIFF_CUDA(cudaGetDevice(&dev));
+    MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  // Few tiles and a long K range: clusters of 2 / 4 / 8 CTAs share each tile's K iterations, as
+  // long as the grid still fits the SMs at once and every CTA keeps at least three iterations.
+  p.ksplit = 1;
+  {
+    const char* e = getenv("MODIFF_TC_KSPLIT");     // 1 switches the split off (tests compare)
+    const int allow = e ? atoi(e) : 8;
+    const int iters = d.taps * p.chunks[0];
+    if (p.nseg == 1)
+      while (p.ksplit * 2 <= allow && p.ksplit < 8 && p.total_tiles * p.ksplit * 2 <= sm_count &&
+             iters >= 3 * p.ksplit * 2)
+        p.ksplit *= 2;
+  }
+
   // The bulk-copy epilogue needs full-width row tiles of at least 4 pixels per image, per-tensor
   // scales, no bias and no accumulator dump.
   const int tile_px = p.bh * p.bw;
   // Linear layers (one pixel per row, output [rows][cout]): the same ring, filled and drained by
   // 2-D copies of 128 rows x 32 channels with the 128-byte swizzle.
-  const bool row_epi = !per_sample && !bias && !acc_out && d.ho * d.wo == 1 && g->cout % 4 == 0 &&
+  const bool row_epi = p.ksplit == 1 && !per_sample && !bias && !acc_out && d.ho * d.wo == 1 &&
+                       g->cout % 4 == 0 &&
                        g->batch >= 128 && (((uintptr_t)o_hat & 15) == 0);
   p.row_epi = row_epi ? 1 : 0;
   const bool tma_epi = row_epi ||
-                       (!per_sample && !bias && !acc_out && tile_px >= 4 && p.bw == d.wo &&
+                       (p.ksplit == 1 && !per_sample && !bias && !acc_out && tile_px >= 4 &&
+                        p.bw == d.wo &&
                         (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0));
   const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
   const uint32_t stage_bytes = kATileBytes + b_tile;
@@ -634,11 +738,32 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   }
   const bool use_tma_epi = tma_epi && p.o_bytes > 0;
 
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    MODIFF_CUDA(cudaGetDevice(&dev));
-    MODIFF_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  if (p.ksplit > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.total_tiles * p.ksplit));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (p.with_sum) {
+      static SmemLimit smem_limit;
+      MODIFF_CUDA(raise_smem_limit(igemm_tc_kernel<1, true, false, true>, smem, smem_limit));
+      MODIFF_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<1, true, false, true>, map_a, map_b,
+                                     map_o, p));
+    } else {
+      static SmemLimit smem_limit;
+      MODIFF_CUDA(raise_smem_limit(igemm_tc_kernel<1, false, false, true>, smem, smem_limit));
+      MODIFF_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<1, false, false, true>, map_a, map_b,
+                                     map_o, p));
+    }
+    MODIFF_LAUNCH_CHECK("igemm_tc_kernel (K split across a cluster)");
+    return MODIFF_OK;
   }
   const int grid = p.total_tiles < sm_count ? p.total_tiles : sm_count;
   const int variant = (p.nseg == 2 ? 4 : 0) | (p.with_sum ? 2 : 0) | (use_tma_epi ? 1 : 0);

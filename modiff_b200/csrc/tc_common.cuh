@@ -66,6 +66,59 @@ __device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* ab
   return mbar_wait_limit(bar, parity, abort_flag, 2000000000ull);
 }
 
+// ---------------------------------------------------------------- thread-block clusters
+__device__ inline uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ inline void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory object in CTA `rank` of the cluster
+__device__ inline uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ inline void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ inline bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait on a barrier that threads of the OTHER CTA arrive on (cluster-scope acquire)
+__device__ inline bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > 2000000000ull) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&g_device_status, 1);
+  return false;
+}
+
+__device__ inline int ld_cluster_s32(uint32_t cluster_addr) {
+  int v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 __device__ inline void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                    int c1, int c2, int c3, int c4) {
   asm volatile(

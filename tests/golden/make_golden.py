@@ -530,8 +530,9 @@ def gen_full():
         keep = sorted({n // 10, n // 4, n // 2, 3 * n // 4})
         final, kept, db, fin = _sens(_runner(c), keep)
         out = {"final": final.numpy().copy(), "sens_db": db, "final_sens_db": np.float32(fin)}
-        for i, x in kept.items():
-            out[f"x_after{i}"] = x
+        if c.get("batch", 1) < 64:          # batch-256 cases keep the final tensor only (3 MB)
+            for i, x in kept.items():
+                out[f"x_after{i}"] = x
         np.savez_compressed(os.path.join(HERE, f"full_{c['name']}.npz"), **out)
         print(c["name"], f"{time.time() - t0:.1f}s", float(final.std()), "final sens", round(fin, 1),
               "min sens", float(db.min()), flush=True)

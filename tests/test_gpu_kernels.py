@@ -295,6 +295,44 @@ def test_igemm_activation_reuse_kernel(cuda, case, accumulate, w_bits, monkeypat
     assert err < 1e-5, err
 
 
+KSPLIT_CASES = [
+    # batch, cin, cout, hw, k, w_bits: few output tiles and a long K range
+    (32, 768, 768, 2, 3, 8),      # latent UNet's deepest level: 6 tiles, clusters of 8
+    (32, 768, 768, 4, 3, 8),      # 24 tiles, clusters of 4
+    (32, 384, 384, 8, 3, 4),      # 48 tiles, clusters of 2, no sum rows
+    (7, 768, 200, 2, 1, 8),       # 1x1, ragged rows and channels, clusters of 2
+    (3, 1280, 320, 1, 1, 8),      # linear layer with three rows
+]
+
+
+@pytest.mark.parametrize("accumulate", [True, False])
+@pytest.mark.parametrize("case", KSPLIT_CASES, ids=lambda c: "b%d_c%d_o%d_hw%d_k%d_w%d" % c)
+def test_igemm_k_range_split_across_a_cluster(cuda, case, accumulate, monkeypatch):
+    """Layers with fewer tiles than SMs: clusters of CTAs share each tile's K range and add their
+    int32 partial sums through distributed shared memory.  Outputs and accumulators equal the
+    unsplit kernel's bit for bit, and the accumulators equal the exact integer convolution."""
+    b, cin, cout, hw, k, w_bits = case
+    L = _lib()
+    pad = (1, 1, 1, 1) if k == 3 else (0, 0, 0, 0)
+    g = _geom(b, cin, cout, hw, hw, k=k, stride=1, pad=pad)
+    torch.manual_seed(14)
+    x_codes = torch.randint(-127, 128, (b, cin, hw, hw), dtype=torch.int8)
+    w = torch.randn(cout, cin, k, k) * 0.05
+    w[1] = w[1].abs() + 0.01
+    bias = torch.randn(cout).to(cuda) if not accumulate else None
+    res = {}
+    for name, allow in (("split", "8"), ("unsplit", "1")):
+        monkeypatch.setenv("MODIFF_TC_KSPLIT", allow)
+        monkeypatch.setenv("MODIFF_IGEMM_HALO", "0")
+        monkeypatch.setenv("MODIFF_IGEMM_PAIR", "0")
+        res[name] = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda, accumulate=accumulate,
+                               bias=bias)
+    assert torch.equal(res["split"][1], res["unsplit"][1])
+    assert torch.equal(res["split"][0], res["unsplit"][0])
+    exp_acc, _ = _expected_acc(x_codes, w, g, w_bits)
+    assert torch.equal(res["split"][1][0].permute(0, 3, 1, 2).to(torch.int64), exp_acc[0])
+
+
 def test_conv_fp32_matches_torch(cuda):
     """First-step path: fp32 activations x dequantised weights + bias, tolerance 1e-4 relative
     to the output range (north-star bound for per-layer outputs is 1e-3)."""
