@@ -210,8 +210,11 @@ constexpr int kRowBytes = 128;
 constexpr int kTile = 128 * kRowBytes;           // 16 KB: 128 rows x 128 bytes
 constexpr int kStageBytes = 256 * kRowBytes;     // 32 KB: a key tile (16 KB) or a v tile (<= 32 KB)
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;               // softmax warps: kParts per tensor-memory lane quarter
+constexpr int kParts = kEpiWarps / 4;       // each takes 128 / kParts keys of a block
+constexpr int kPartCols = 128 / kParts;     // 32
 constexpr int kThreads = 64 + 32 * kEpiWarps;
+static_assert(kPartCols == 32, "a softmax warp handles one 32-column tensor-memory load per key block");
 
 struct AttnI8Params {
   int bh, heads, c, t, tk;
@@ -284,8 +287,8 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __shared__ __align__(8) uint64_t bar_o_full, bar_o_empty;
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
-  __shared__ int red_max[2][128];
-  __shared__ int red_sum[2][128];
+  __shared__ int red_max[kParts][128];
+  __shared__ int red_sum[kParts][128];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -448,11 +451,12 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (warps 2..9)
-    // Two warps share a tensor-memory lane quarter; a lane is one query row, each warp of the
-    // pair takes 64 of the 128 keys of a block and half of the output channels.
+    // ------------------------------------------------------------ softmax + epilogue (warps 2..)
+    // kParts warps share a tensor-memory lane quarter; a lane is one query row, each warp of the
+    // group takes 32 of the 128 keys of a block and every kParts-th 32-channel slice of the
+    // output.  Four warps per scheduler hide the tensor-memory loads and the exp2 latency.
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     uint8_t* p_ptr = smem_raw + 2 * kTile;
@@ -461,7 +465,6 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // |S - m| <= 2 * 128 * 128 * channels: below 2^22 the integer-to-float conversion is an integer
     // add into the mantissa of 1.5 * 2^23 and one exact subtraction (no conversion-unit cycles)
     const bool magic_ok = p.c * 32768 < (1 << 22);
-    const int ch_half = ((p.d_rows / 2 + 31) / 32) * 32;       // channel columns of warp half 0
     uint32_t s_count = 0, p_count = 0, ophase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
@@ -474,12 +477,11 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = mbar_wait(smem_u32(&bar_s_full[b]), par, abort_flag);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        {
           int a[32];
-          tc_ld32(t_lane + b * 128u + (uint32_t)(half * 64 + c0), a);
+          tc_ld32(t_lane + b * 128u + (uint32_t)(part * kPartCols), a);
           tc_wait_ld();
-          const int key0 = j * 128 + half * 64 + c0;
+          const int key0 = j * 128 + part * kPartCols;
           if (key0 + 32 <= p.tk) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx = max(mx, a[e]);
@@ -495,9 +497,11 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++s_count;
       }
       if (!ok) break;
-      red_max[half][row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const int m_row = max(red_max[0][row], red_max[1][row]);
+      red_max[part][row] = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+      int m_row = red_max[0][row];
+#pragma unroll
+      for (int i = 1; i < kParts; ++i) m_row = max(m_row, red_max[i][row]);
       // ---- pass B: weights, integer row sum
       int l_part = 0;
       for (int j = 0; j < p.nkb && ok; ++j) {
@@ -509,13 +513,12 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!ok) break;
         tc_fence_after();
         uint8_t* prow = p_ptr + (size_t)pb * kTile + (size_t)row * kRowBytes;
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        {
           int a[32];
-          tc_ld32(t_lane + b * 128u + (uint32_t)(half * 64 + c0), a);
+          tc_ld32(t_lane + b * 128u + (uint32_t)(part * kPartCols), a);
           tc_wait_ld();
-          const int key0 = j * 128 + half * 64 + c0;
-          const int chunk0 = half * 4 + (c0 >> 4);
+          const int key0 = j * 128 + part * kPartCols;
+          const int chunk0 = part * (kPartCols / 16);
           const bool ragged = key0 + 32 > p.tk;      // only the last key block can be
           if (magic_ok) {
             if (ragged) weights32<true, true>(a, m_row, c2, p.tk - key0, prow, chunk0, row, l_part);
@@ -536,19 +539,19 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++p_count;
       }
       if (!ok) break;
-      red_sum[half][row] = l_part;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const int l_row = red_sum[0][row] + red_sum[1][row];
+      red_sum[part][row] = l_part;
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+      int l_row = red_sum[0][row];
+#pragma unroll
+      for (int i = 1; i < kParts; ++i) l_row += red_sum[i][row];
       const float inv = __fdiv_rn(dv, (float)l_row);
       // ---- output
       ok = mbar_wait(smem_u32(&bar_o_full), ophase, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const int cbeg = half == 0 ? 0 : ch_half;
-      const int cend = half == 0 ? min(ch_half, p.d_rows) : p.d_rows;
       const int bimg = img / p.heads, head = img % p.heads;
       float* obase = p.out + (long long)bimg * p.ob + (long long)head * p.oh + (long long)q * p.ot;
-      for (int c0 = cbeg; c0 < cend; c0 += 32) {
+      for (int c0 = part * 32; c0 < p.d_rows; c0 += 32 * kParts) {
         int a[32];
         tc_ld32(t_lane + 256u + (uint32_t)c0, a);
         tc_wait_ld();

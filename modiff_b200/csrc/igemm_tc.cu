@@ -60,6 +60,7 @@ struct TcParams {
   int accumulate;
   int per_sample;
   int ksplit;                    // CTAs of a cluster sharing one tile's K range (1 = off)
+  int fused_round;               // K split: round as the bulk-copy epilogue does (one fma)
   const float* x_scale;
   const float* w_scale;
   const int32_t* w_corr;
@@ -527,20 +528,43 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int r = 0; r < 8; ++r)
           if (r < p.ksplit) rs += ld_cluster_s32(peer[r] + (uint32_t)(128 * 128 + row) * 4u);
       }
-      for (int j = 0; j < cpt; ++j) {
-        const int cl = cbase + j;
-        const int co = t.nt * 128 + cl;
-        int iv = 0;
+      // eight channels at a time: all loads of a group (cached output, every CTA's partial
+      // sums) are issued before the first use
+      for (int j0 = 0; j0 < cpt; j0 += 8) {
+        float old[8];
+        int iv[8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < p.ksplit) iv += ld_cluster_s32(peer[r] + (uint32_t)(cl * 128 + row) * 4u);
-        if (WITH_SUM) iv += ep_corr[0][cl] * rs;
-        if (offset_codes) iv += ep_off[0][cl];
-        if (valid && co < p.g.cout) {
-          float* o = p.o_hat + ((size_t)n * p.g.cout + co) * howo + hw;
-          const float old = p.accumulate ? *o : 0.0f;
-          *o = fmaf((float)iv, __fmul_rn(xs, ep_scale[0][cl]), old) + ep_bias[cl];
-          if (p.acc_out) p.acc_out[m * p.g.cout + co] = iv;
+        for (int jj = 0; jj < 8; ++jj) {
+          const int co = t.nt * 128 + cbase + j0 + jj;
+          old[jj] = (p.accumulate && valid && co < p.g.cout)
+                        ? p.o_hat[((size_t)n * p.g.cout + co) * howo + hw] : 0.0f;
+          iv[jj] = 0;
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < p.ksplit) {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              iv[jj] += ld_cluster_s32(peer[r] + (uint32_t)((cbase + j0 + jj) * 128 + row) * 4u);
+          }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int cl = cbase + j0 + jj;
+          const int co = t.nt * 128 + cl;
+          int a = iv[jj];
+          if (WITH_SUM) a += ep_corr[0][cl] * rs;
+          if (offset_codes) a += ep_off[0][cl];
+          if (valid && co < p.g.cout) {
+            const float sc = __fmul_rn(xs, ep_scale[0][cl]);
+            // the rounding of the unsplit kernel's epilogue that this layer would have taken:
+            // one fused multiply-add (bulk-copy epilogue) or product, sum, bias (generic)
+            const float v = p.fused_round ? fmaf((float)a, sc, old[jj])
+                                          : __fadd_rn(__fadd_rn(__fmul_rn((float)a, sc), old[jj]),
+                                                      ep_bias[cl]);
+            p.o_hat[((size_t)n * p.g.cout + co) * howo + hw] = v;
+            if (p.acc_out) p.acc_out[m * p.g.cout + co] = a;
+          }
         }
       }
     }
@@ -643,8 +667,10 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
     const int iters = d.taps * p.chunks[0];
     if (p.nseg == 1)
       while (p.ksplit * 2 <= allow && p.ksplit < 8 && p.total_tiles * p.ksplit * 2 <= sm_count &&
-             iters >= 3 * p.ksplit * 2)
+             iters >= 6 * p.ksplit * 2)
         p.ksplit *= 2;
+    // the cluster's barriers and the exchange of partial sums cost about what 20 K iterations do
+    if (iters * (p.ksplit - 1) < 20 * p.ksplit) p.ksplit = 1;
   }
 
   // The bulk-copy epilogue needs full-width row tiles of at least 4 pixels per image, per-tensor
@@ -652,14 +678,16 @@ int launch_igemm_tc(const int8_t* codes, const int8_t* wcodes, int with_sum_rows
   const int tile_px = p.bh * p.bw;
   // Linear layers (one pixel per row, output [rows][cout]): the same ring, filled and drained by
   // 2-D copies of 128 rows x 32 channels with the 128-byte swizzle.
-  const bool row_epi = p.ksplit == 1 && !per_sample && !bias && !acc_out && d.ho * d.wo == 1 &&
-                       g->cout % 4 == 0 &&
-                       g->batch >= 128 && (((uintptr_t)o_hat & 15) == 0);
+  const bool row_epi_u = !per_sample && !bias && !acc_out && d.ho * d.wo == 1 && g->cout % 4 == 0 &&
+                         g->batch >= 128 && (((uintptr_t)o_hat & 15) == 0);
+  const bool tma_epi_u = row_epi_u ||
+                         (!per_sample && !bias && !acc_out && tile_px >= 4 && p.bw == d.wo &&
+                          (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0));
+  // what the layer would take without the K split decides how the split epilogue rounds
+  p.fused_round = (row_epi_u || (tma_epi_u && g->cout >= 128)) ? 1 : 0;
+  const bool row_epi = row_epi_u && p.ksplit == 1;
+  const bool tma_epi = tma_epi_u && p.ksplit == 1;
   p.row_epi = row_epi ? 1 : 0;
-  const bool tma_epi = row_epi ||
-                       (p.ksplit == 1 && !per_sample && !bias && !acc_out && tile_px >= 4 &&
-                        p.bw == d.wo &&
-                        (d.ho * d.wo) % 4 == 0 && (((uintptr_t)o_hat & 15) == 0));
   const uint32_t b_tile = ((uint32_t)p.umma_n * kChunkK + 1023u) & ~1023u;
   const uint32_t stage_bytes = kATileBytes + b_tile;
   const uint32_t o_ring = tma_epi ? (uint32_t)kOSlots * kOHalfBytes : 0u;

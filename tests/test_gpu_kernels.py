@@ -299,9 +299,9 @@ KSPLIT_CASES = [
     # batch, cin, cout, hw, k, w_bits: few output tiles and a long K range
     (32, 768, 768, 2, 3, 8),      # latent UNet's deepest level: 6 tiles, clusters of 8
     (32, 768, 768, 4, 3, 8),      # 24 tiles, clusters of 4
-    (32, 384, 384, 8, 3, 4),      # 48 tiles, clusters of 2, no sum rows
-    (7, 768, 200, 2, 1, 8),       # 1x1, ragged rows and channels, clusters of 2
-    (3, 1280, 320, 1, 1, 8),      # linear layer with three rows
+    (8, 512, 384, 4, 3, 4),       # 3 tiles, clusters of 4 (36 K iterations), no sum rows
+    (7, 768, 200, 2, 3, 8),       # ragged rows and channels
+    (3, 4096, 320, 1, 1, 8),      # linear layer with three rows, 32 K iterations, clusters of 4
 ]
 
 
@@ -320,17 +320,19 @@ def test_igemm_k_range_split_across_a_cluster(cuda, case, accumulate, monkeypatc
     w = torch.randn(cout, cin, k, k) * 0.05
     w[1] = w[1].abs() + 0.01
     bias = torch.randn(cout).to(cuda) if not accumulate else None
-    res = {}
-    for name, allow in (("split", "8"), ("unsplit", "1")):
-        monkeypatch.setenv("MODIFF_TC_KSPLIT", allow)
-        monkeypatch.setenv("MODIFF_IGEMM_HALO", "0")
-        monkeypatch.setenv("MODIFF_IGEMM_PAIR", "0")
-        res[name] = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda, accumulate=accumulate,
-                               bias=bias)
-    assert torch.equal(res["split"][1], res["unsplit"][1])
-    assert torch.equal(res["split"][0], res["unsplit"][0])
-    exp_acc, _ = _expected_acc(x_codes, w, g, w_bits)
-    assert torch.equal(res["split"][1][0].permute(0, 3, 1, 2).to(torch.int64), exp_acc[0])
+    for want_acc in (True, False):      # False: the unsplit kernel takes its bulk-copy epilogue
+        res = {}
+        for name, allow in (("split", "8"), ("unsplit", "1")):
+            monkeypatch.setenv("MODIFF_TC_KSPLIT", allow)
+            monkeypatch.setenv("MODIFF_IGEMM_HALO", "0")
+            monkeypatch.setenv("MODIFF_IGEMM_PAIR", "0")
+            res[name] = _run_igemm(x_codes, w, g, w_bits, L.IMPL_TCGEN05, cuda,
+                                   accumulate=accumulate, bias=bias, want_acc=want_acc)
+        assert torch.equal(res["split"][0], res["unsplit"][0]), want_acc
+        if want_acc:
+            assert torch.equal(res["split"][1], res["unsplit"][1])
+            exp_acc, _ = _expected_acc(x_codes, w, g, w_bits)
+            assert torch.equal(res["split"][1][0].permute(0, 3, 1, 2).to(torch.int64), exp_acc[0])
 
 
 def test_conv_fp32_matches_torch(cuda):
