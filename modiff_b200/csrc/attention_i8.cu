@@ -213,7 +213,8 @@ constexpr int kStages = 4;
 constexpr int kEpiWarps = 16;               // softmax warps: kParts per tensor-memory lane quarter
 constexpr int kParts = kEpiWarps / 4;       // each takes 128 / kParts keys of a block
 constexpr int kPartCols = 128 / kParts;     // 32
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kCtlWarps = 4;                // copy producer, score MMAs, weighted-sum MMAs, (idle)
+constexpr int kThreads = 32 * (kCtlWarps + kEpiWarps);
 static_assert(kPartCols == 32, "a softmax warp handles one 32-column tensor-memory load per key block");
 
 struct AttnI8Params {
@@ -374,16 +375,22 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    // All lanes walk the loop (descriptors and addresses stay warp-uniform values); one
-    // elected lane issues the MMAs and commits.
+    // ------------------------------------------------------------ MMA issuer 1: scores
+    // The two MMA roles sit on different schedulers: each is one serial instruction stream that
+    // shares its scheduler with four busy softmax warps, and together they set the pace.  Both
+    // walk the SAME ring sequence (pass A: k(0..n-1); pass B: k(0), then k(j), v(j-1), then
+    // v(n-1)); each consumes its own entries and steps over the other's.  All lanes walk the
+    // loop; one elected lane issues the MMAs and commits.
     {
       const uint32_t idesc_s = make_idesc_i8(128, 128);
-      const uint32_t idesc_o = make_idesc_u8s8(128, p.d_rows);
       int stage = 0;
-      uint32_t phase = 0, qphase = 0, ophase = 0;
-      uint32_t s_count = 0, p_count = 0;
+      uint32_t phase = 0, qphase = 0;
+      uint32_t s_count = 0;
       bool ok = true;
+      auto skip = [&](int n) {
+        for (int i = 0; i < n; ++i)
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      };
       // scores of key block: S[s_count & 1] = q k^T
       auto scores = [&]() {
         const uint32_t b = s_count & 1u, par = (s_count >> 1) & 1u;
@@ -409,6 +416,33 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         ++s_count;
       };
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        ok = mbar_wait(smem_u32(&bar_q_full), qphase, abort_flag);
+        if (!ok) break;
+        qphase ^= 1u;
+        for (int j = 0; j < p.nkb; ++j) scores();                       // pass A
+        for (int j = 0; j < p.nkb; ++j) {                               // pass B
+          scores();
+          if (j > 0) skip(1);                                           // v(j-1)
+        }
+        skip(1);                                                        // v(n-1)
+        if (!ok) break;
+        if (elect_one()) tc_commit(smem_u32(&bar_q_empty));             // every product read q
+        __syncwarp();
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ MMA issuer 2: weighted sums
+    {
+      const uint32_t idesc_o = make_idesc_u8s8(128, p.d_rows);
+      int stage = 0;
+      uint32_t phase = 0, ophase = 0;
+      uint32_t p_count = 0;
+      bool ok = true;
+      auto skip = [&](int n) {
+        for (int i = 0; i < n; ++i)
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      };
       // O += w v^T for the weight tile p_count & 1
       auto weighted = [&](bool first) {
         const uint32_t b = p_count & 1u, par = (p_count >> 1) & 1u;
@@ -432,31 +466,27 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++p_count;
       };
       for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-        ok = mbar_wait(smem_u32(&bar_q_full), qphase, abort_flag);
-        if (!ok) break;
-        qphase ^= 1u;
-        for (int j = 0; j < p.nkb; ++j) scores();                       // pass A
+        skip(p.nkb * p.cch);                                            // pass A: k(0..n-1)
         for (int j = 0; j < p.nkb; ++j) {                               // pass B
-          scores();
+          skip(p.cch);                                                  // k(j)
           if (j > 0) weighted(j == 1);
         }
         weighted(p.nkb == 1);
         if (!ok) break;
-        if (elect_one()) {
-          tc_commit(smem_u32(&bar_o_full));
-          tc_commit(smem_u32(&bar_q_empty));
-        }
+        if (elect_one()) tc_commit(smem_u32(&bar_o_full));
         __syncwarp();
         ophase ^= 1u;
       }
     }
+  } else if (warp == 3) {
+    // idle: keeps the softmax warps' indices aligned with their tensor-memory lane quarters
   } else {
     // ------------------------------------------------------------ softmax + epilogue (warps 2..)
     // kParts warps share a tensor-memory lane quarter; a lane is one query row, each warp of the
     // group takes 32 of the 128 keys of a block and every kParts-th 32-channel slice of the
     // output.  Four warps per scheduler hide the tensor-memory loads and the exp2 latency.
     const int quarter = warp & 3;
-    const int part = (warp - 2) >> 2;
+    const int part = (warp - kCtlWarps) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     uint8_t* p_ptr = smem_raw + 2 * kTile;
