@@ -332,7 +332,7 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // Ring order = the order in which the MMA thread consumes: pass A k(0..n-1); pass B k(0),
+    // Ring order = the order in which the MMA warps consume: pass A k(0..n-1); pass B k(0),
     // then k(j), v(j-1) for j = 1..n-1, then v(n-1).
     if (lane == 0) {
       int stage = 0;
@@ -481,7 +481,7 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   } else if (warp == 3) {
     // idle: keeps the softmax warps' indices aligned with their tensor-memory lane quarters
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (warps 2..)
+    // ------------------------------------------------------------ softmax + epilogue (warps 4..19)
     // kParts warps share a tensor-memory lane quarter; a lane is one query row, each warp of the
     // group takes 32 of the 128 keys of a block and every kParts-th 32-channel slice of the
     // output.  Four warps per scheduler hide the tensor-memory loads and the exp2 latency.

@@ -462,9 +462,14 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           const int cvalid = min(32, p.cout - (t.nt * p.n_real + colbase));
           float res[32];
           if (p.residual) {
+            if (cvalid >= 32) {          // warp-uniform: full tiles keep unpredicated accesses
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              res[j] = j < cvalid ? __ldg(p.residual + out_off + (size_t)j * (p.h * p.w)) : 0.0f;
+              for (int j = 0; j < 32; ++j) res[j] = __ldg(p.residual + out_off + (size_t)j * (p.h * p.w));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                res[j] = j < cvalid ? __ldg(p.residual + out_off + (size_t)j * (p.h * p.w)) : 0.0f;
+            }
           }
           ok = mbar_wait(smem_u32(&bar_o_full[oslot]), ophase, abort_flag);
           if (!ok) break;
@@ -496,13 +501,23 @@ igemm_halo_kernel(const __grid_constant__ CUtensorMap map_a,
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaf((float)a[j], ep_scale[colbase + j], v[j]);
+          if (cvalid >= 32) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < cvalid) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
-          if (p.residual) {
+            for (int j = 0; j < 32; ++j) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
+            if (p.residual) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+            }
+          } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (j < cvalid) p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+              if (j < cvalid) p.o_out[out_off + (size_t)j * (p.h * p.w)] = v[j];
+            if (p.residual) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < cvalid) p.sum_out[out_off + (size_t)j * (p.h * p.w)] = __fadd_rn(res[j], v[j]);
+            }
           }
           if (++oslot == p.o_slots) { oslot = 0; ophase ^= 1u; }
         }
