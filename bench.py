@@ -216,7 +216,7 @@ def int8_summary(timer, hbm_peak, i8_peak):
         return None
     ops = sum(c["ops"] for c in classes.values())
     ms = sum(c["ms"] for c in classes.values())
-    top = sorted(classes.items(), key=lambda kv: -kv[1]["ms"])[:6]
+    top = sorted(classes.items(), key=lambda kv: -kv[1]["ms"])[:10]
     tops = ops / (ms / 1000.0) / 1e12
     return {
         "int8_tops": tops, "int8_gemm_ms": ms, "int8_tera_ops": ops / 1e12,
