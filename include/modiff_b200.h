@@ -572,7 +572,7 @@ int modiff_adaround_fake_quant(const float* w, const float* alpha, const float* 
  * tensor, delta = absmax / (2^(n_bits-1) - 1), floor 1e-8) in the layouts the MMAs read.
  *   q, k, v       fp32, addressed as x[b*s0 + h*s1 + c*s2 + t*s3] with the four element strides
  *                 of strides_q (q) / strides_kv (k and v); channels or tokens contiguous
- *   q_codes       int8 [batch*heads][tq][dp], dp = 128 (c <= 128) or 256, zero padded
+ *   q_codes       int8 [batch*heads][tq][dp], dp = c padded to 32, 64, 128 or 256, zero padded
  *   k_codes       int8 [batch*heads][tk][dp]
  *   v_codes       int8 [batch*heads][round_up(c,16)][round_up(tk,128)], zero padded
  *                 (sizes: modiff_attn_codes_bytes(batch*heads, c, tq, tk, which = 0 / 1 / 2))

@@ -11,7 +11,8 @@
 //
 //   modiff_attn_quantize   absmax of q, k, v (one launch), then codes in the layouts the MMAs
 //                          read: q / k token-major [head][token][dp] (dp = channels padded to
-//                          128 or 256 bytes), v channel-major [head][d_rows][keys padded to 128]
+//                          32, 64, 128 or 256 bytes), v channel-major [head][d_rows][keys padded
+//                          to 128]
 //   modiff_attention_i8    per 128-query tile and head, keys in blocks of 128:
 //        pass A  S = q_int k_int^T (M = 128, N = 128) into tensor memory, double buffered;
 //                the softmax warps keep the exact integer row maximum m;
@@ -30,6 +31,10 @@
 
 namespace modiff {
 namespace {
+
+// Bytes of a q / k code row: the head's channels padded to 32, 64, 128 or 256.  Rows of up to 128
+// bytes are one tile row in shared memory (32-, 64- or 128-byte swizzle); 256 bytes are two chunks.
+inline int attn_row_bytes(int c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : 256; }
 
 // ---------------------------------------------------------------------------------- quantise
 struct TensorView {
@@ -219,7 +224,9 @@ static_assert(kPartCols == 32, "a softmax warp handles one 32-column tensor-memo
 
 struct AttnI8Params {
   int bh, heads, c, t, tk;
-  int cch;                  // 128-byte chunks of a q / k row: dp / 128
+  int cch;                  // chunks of a q / k row: 1, or 2 for 256-byte rows
+  int rb;                   // bytes of a chunk row in shared memory: 32, 64 or 128
+  int ksteps;               // rb / 32: MMAs (K = 32 bytes) per chunk
   int d_rows;               // rows of a v tile (multiple of 16, <= 256)
   int nkb;                  // key blocks of 128
   int q_tiles, total_tiles;
@@ -237,6 +244,17 @@ __device__ inline uint32_t make_idesc_u8s8(int m, int n) {
   d |= 1u << 10;                // B format: signed 8 bit
   d |= (uint32_t)(n >> 3) << 17;
   d |= (uint32_t)(m >> 4) << 24;
+  return d;
+}
+// Shared-memory descriptor of a K-major tile whose rows are `rb` bytes (32, 64 or 128) stored with
+// the swizzle of that width: groups of eight rows are 8 * rb bytes apart.
+__device__ inline uint64_t make_smem_desc_rows(uint32_t saddr, int rb) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);            // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused: one atom wide)
+  d |= (uint64_t)((8 * rb) >> 4) << 32;                // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                              // descriptor version of sm_100
+  d |= (uint64_t)(rb == 128 ? 2 : rb == 64 ? 4 : 6) << 61;   // swizzle: 128 / 64 / 32 bytes
   return d;
 }
 __device__ inline float exp2_approx(float x) {
@@ -343,7 +361,7 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_flag);
           if (!ok) break;
           const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_arrive_expect_tx(full, (uint32_t)kTile);
+          mbar_arrive_expect_tx(full, (uint32_t)(128 * p.rb));
           // key rows beyond tk are filled with zeros by the copy and masked in the softmax
           tma_load_3d(ring + stage * kStageBytes, &map_k, full, ch * kRowBytes, j * 128, img);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -362,7 +380,7 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = mbar_wait(smem_u32(&bar_q_empty), qphase ^ 1u, abort_flag);
         if (!ok) break;
         const uint32_t qfull = smem_u32(&bar_q_full);
-        mbar_arrive_expect_tx(qfull, (uint32_t)(p.cch * kTile));
+        mbar_arrive_expect_tx(qfull, (uint32_t)(p.cch * 128 * p.rb));
         for (int ch = 0; ch < p.cch; ++ch)
           tma_load_3d(q_smem + ch * kTile, &map_q, qfull, ch * kRowBytes, qt * 128, img);
         qphase ^= 1u;
@@ -401,11 +419,10 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag);
           if (!ok) return;
           tc_fence_after();
-          const uint64_t adesc = make_smem_desc(q_smem + ch * kTile);
-          const uint64_t bdesc = make_smem_desc(ring + stage * kStageBytes);
+          const uint64_t adesc = make_smem_desc_rows(q_smem + ch * kTile, p.rb);
+          const uint64_t bdesc = make_smem_desc_rows(ring + stage * kStageBytes, p.rb);
           if (elect_one()) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int k = 0; k < p.ksteps; ++k)
               tc_mma_i8(tmem_base + b * 128u, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
                         idesc_s, (ch > 0 || k > 0) ? 1u : 0u);
             tc_commit(smem_u32(&bar_empty[stage]));
@@ -631,7 +648,7 @@ int read_device_status_attention_i8(int* status, int reset) {
 using namespace modiff;
 
 extern "C" int64_t modiff_attn_codes_bytes(int heads_total, int c, int tq, int tk, int which) {
-  const int dp = c <= 128 ? 128 : 256;
+  const int dp = attn_row_bytes(c);
   const int d_rows = round_up(c, 16);
   const int tkp = round_up(tk, 128);
   if (which == 0) return (int64_t)heads_total * tq * dp;
@@ -681,7 +698,7 @@ extern "C" int modiff_attn_quantize(const float* q, const float* k, const float*
   p.codes[0] = q_codes;
   p.codes[1] = k_codes;
   p.codes[2] = v_codes;
-  p.dp = c <= 128 ? 128 : 256;
+  p.dp = attn_row_bytes(c);
   p.d_rows = round_up(c, 16);
   p.tkp = round_up(tk, 128);
   cudaStream_t s = (cudaStream_t)stream;
@@ -690,7 +707,7 @@ extern "C" int modiff_attn_quantize(const float* q, const float* k, const float*
   attn_absmax_kernel<<<dim3(blocks, 3), 256, 0, s>>>(p);
   MODIFF_LAUNCH_CHECK("attn_absmax_kernel");
   const int tmax = tq > p.tkp ? tq : p.tkp;
-  const dim3 grid(ceil_div(tmax, 64), p.dp / 64, batch * heads * 3);
+  const dim3 grid(ceil_div(tmax, 64), ceil_div(p.dp, 64), batch * heads * 3);
   attn_encode_kernel<<<grid, 256, 0, s>>>(p);
   MODIFF_LAUNCH_CHECK("attn_encode_kernel");
   return MODIFF_OK;
@@ -708,7 +725,7 @@ extern "C" int modiff_attention_i8(const int8_t* q_codes, const int8_t* k_codes,
                    "code buffers must be 16-byte aligned");
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return set_error(MODIFF_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
-  const int dp = c <= 128 ? 128 : 256;
+  const int dp = attn_row_bytes(c);
   const int d_rows = round_up(c, 16);
   const int tkp = round_up(tk, 128);
   const int bh = batch * heads;
@@ -719,7 +736,9 @@ extern "C" int modiff_attention_i8(const int8_t* q_codes, const int8_t* k_codes,
   p.c = c;
   p.t = tq;
   p.tk = tk;
-  p.cch = dp / 128;
+  p.cch = dp > 128 ? 2 : 1;
+  p.rb = dp < 128 ? dp : 128;
+  p.ksteps = p.rb / 32;
   p.d_rows = d_rows;
   p.nkb = tkp / 128;
   p.q_tiles = ceil_div(tq, 128);
@@ -733,18 +752,23 @@ extern "C" int modiff_attention_i8(const int8_t* q_codes, const int8_t* k_codes,
   p.ot = strides_out[3];
 
   CUtensorMap map_q, map_k, map_v;
-  auto make = [&](CUtensorMap* m, const void* base, int inner, int rows, int box_rows) -> CUresult {
+  // a box is `box_rows` rows of `row_bytes` (32, 64 or 128), stored with the swizzle of that width
+  auto make = [&](CUtensorMap* m, const void* base, int inner, int rows, int box_rows,
+                  int row_bytes) -> CUresult {
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)bh};
     cuuint64_t strides[2] = {(cuuint64_t)inner, (cuuint64_t)inner * rows};
-    cuuint32_t box[3] = {128u, (cuuint32_t)box_rows, 1u};
+    cuuint32_t box[3] = {(cuuint32_t)row_bytes, (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                    : CU_TENSOR_MAP_SWIZZLE_32B;
     return encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
-  CUresult r = make(&map_q, q_codes, dp, tq, 128);                 // [head][query][dp]
-  if (r == CUDA_SUCCESS) r = make(&map_k, k_codes, dp, tk, 128);   // [head][key][dp]
-  if (r == CUDA_SUCCESS) r = make(&map_v, v_codes, tkp, d_rows, d_rows);   // [head][channel][key]
+  CUresult r = make(&map_q, q_codes, dp, tq, 128, p.rb);                 // [head][query][dp]
+  if (r == CUDA_SUCCESS) r = make(&map_k, k_codes, dp, tk, 128, p.rb);   // [head][key][dp]
+  if (r == CUDA_SUCCESS) r = make(&map_v, v_codes, tkp, d_rows, d_rows, 128);   // [head][channel][key]
   if (r != CUDA_SUCCESS)
     return set_error(MODIFF_ERR_CUDA, "cuTensorMapEncodeTiled(attention codes) failed: %d", (int)r);
 

@@ -72,7 +72,8 @@ def _run_gpu(q, k, v, scale, batch, heads, c, tq, tk, sq, skv, out_shape, so, bi
 
 
 def _check(out, codes, scales, want, aux, bh, c, tq, tk):
-    dp = 128 if c <= 128 else 256
+    dp = codes[0].numel() // (bh * tq)          # q / k rows: channels padded to 32, 64, 128 or 256
+    assert dp in (32, 64, 128, 256) and dp >= c and (dp == 32 or dp // 2 < c)
     d_rows, tkp = -(-c // 16) * 16, -(-tk // 128) * 128
     assert [float(s) for s in scales[:3]] == [float(aux["dq"]), float(aux["dk"]), float(aux["dv"])]
     qc = codes[0].view(bh, tq, dp)
