@@ -51,6 +51,12 @@ def test_size_helpers():
     g2 = _lib.ConvGeom(2, 3, 128, 32, 32, 3, 3, 2, 0, 0, 1, 1, 0)   # stride 2, pad right/bottom
     assert _lib.out_hw(g2) == (16, 16)
     assert lib.modiff_codes_bytes(C.byref(g2)) == 2 * 4 * 17 * 17 * 16
+    # integer attention: q / k rows are the head's channels padded to 32, 64, 128 or 256 bytes,
+    # v rows are channels (multiple of 16) by keys padded to 128
+    for c, dp in ((24, 32), (32, 32), (40, 64), (64, 64), (96, 128), (160, 256), (256, 256)):
+        assert lib.modiff_attn_codes_bytes(16, c, 300, 77, 0) == 16 * 300 * dp
+        assert lib.modiff_attn_codes_bytes(16, c, 300, 77, 1) == 16 * 77 * dp
+        assert lib.modiff_attn_codes_bytes(16, c, 300, 77, 2) == 16 * (-(-c // 16) * 16) * 128
 
 
 def test_invalid_geometry_is_reported_not_crashed():
