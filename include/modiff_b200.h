@@ -154,6 +154,18 @@ int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, f
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     void* stream);
 
+/* modiff_modq for a linear layer whose input is nn.LayerNorm(x) over the last dimension (the
+ * transformer blocks' norm1 / norm2 / norm3 in front of to_q and the feed-forward projection,
+ * ldm/modules/attention.py:229-241, qdiff/quant_block.py:249-256) over qdiff/quant_layer.py:325-336:
+ * both passes normalise the row on the fly with the arithmetic of modiff_layernorm (same bits), so
+ * the normalised tensor is never written.  Symmetric per-tensor dynamic codes, one scale.
+ *   x        fp32 [rows][c], c a multiple of 16;  gamma, beta fp32 [c]
+ *   a_hat    fp32 [rows][c] in/out;  codes int8 [rows][c];  x_scale fp32 [1] out
+ *   scratch  as for modiff_modq (zero-filled once by the caller, left zeroed) */
+int modiff_modq_ln(const float* x, const float* gamma, const float* beta, float eps, int64_t rows,
+                   int c, float* a_hat, int8_t* codes, float* x_scale, int n_bits, void* scratch,
+                   void* stream);
+
 /* Two quantisers of ONE tensor in two sweeps instead of four: layer A reads
  * nonlinearity(norm(x)) (modiff_modq_gn), layer B reads x itself (modiff_modq_src) - a residual
  * block's first convolution and its shortcut convolution (qdiff/quant_block.py:279-283 and

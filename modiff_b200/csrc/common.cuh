@@ -176,6 +176,51 @@ inline int groupnorm_lg_hw4(int hw) {
   return lg;
 }
 
+// LayerNorm of one row by one warp, the row held in registers: lane l owns the 16-byte chunks
+// l, l + 32, ... (NV of them, c4 = c / 4 chunks in the row); sums run chunk by chunk, element by
+// element, then a butterfly reduction.  Every kernel that normalises rows goes through these
+// functions with the same NV, so they agree to the bit.
+constexpr int kLnMaxChannels = 1280;
+inline int ln_chunks_per_lane(int c) { return c <= 384 ? 3 : (c <= 640 ? 5 : 10); }
+
+template <int NV>
+__device__ inline void ln_row_load(const float* __restrict__ row, int c4, int lane, float4 (&v)[NV]) {
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int idx = lane + 32 * k;
+    v[k] = idx < c4 ? __ldg(reinterpret_cast<const float4*>(row) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+template <int NV>
+__device__ inline void ln_row_stats(const float4 (&v)[NV], int c4, int lane, float eps, float& mean,
+                                    float& rstd) {
+  const float n = (float)(4 * c4);
+  float s = 0.0f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (lane + 32 * k < c4) { s += v[k].x; s += v[k].y; s += v[k].z; s += v[k].w; }
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  mean = s / n;
+  float q = 0.0f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (lane + 32 * k < c4) {
+      float d = v[k].x - mean; q += d * d;
+      d = v[k].y - mean; q += d * d;
+      d = v[k].z - mean; q += d * d;
+      d = v[k].w - mean; q += d * d;
+    }
+  for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+  rstd = 1.0f / sqrtf(q / n + eps);
+}
+__device__ inline float ln_value(float x, float mean, float rstd, float gamma, float beta) {
+  return fmaf((x - mean) * rstd, gamma, beta);
+}
+__device__ inline float4 ln_value4(float4 x, float mean, float rstd, float4 g, float4 b) {
+  return make_float4(ln_value(x.x, mean, rstd, g.x, b.x), ln_value(x.y, mean, rstd, g.y, b.y),
+                     ln_value(x.z, mean, rstd, g.z, b.z), ln_value(x.w, mean, rstd, g.w, b.w));
+}
+
 // Symmetric activation code range of an n-bit quantiser
 // (n_levels = 2^(b-1) - 1; clamp(-n_levels - 1, n_levels)).
 __host__ __device__ inline int sym_levels(int n_bits) { return (1 << (n_bits - 1)) - 1; }

@@ -152,10 +152,36 @@ attention_small_kernel(const float* __restrict__ q, const float* __restrict__ k,
   }
 }
 
-// LayerNorm over the last dimension: one warp per row (ldm/modules/attention.py:229-231).
+// LayerNorm over the last dimension: one warp per row (ldm/modules/attention.py:229-231).  Rows of
+// up to 1280 channels (a multiple of 4, 16-byte aligned) are held in registers (layernorm_kernel);
+// anything else takes the scalar kernel.
+template <int NV>
 __global__ void __launch_bounds__(256)
 layernorm_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ gamma,
                  const float* __restrict__ beta, int64_t rows, int c, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int c4 = c >> 2;
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+    float4 v[NV];
+    ln_row_load<NV>(x + row * c, c4, lane, v);
+    float mean, rstd;
+    ln_row_stats<NV>(v, c4, lane, eps, mean, rstd);
+    float4* yr = reinterpret_cast<float4*>(y + row * c);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int idx = lane + 32 * k;
+      if (idx < c4)
+        yr[idx] = ln_value4(v[k], mean, rstd, __ldg(reinterpret_cast<const float4*>(gamma) + idx),
+                            __ldg(reinterpret_cast<const float4*>(beta) + idx));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+layernorm_scalar_kernel(const float* __restrict__ x, float* __restrict__ y,
+                        const float* __restrict__ gamma, const float* __restrict__ beta, int64_t rows,
+                        int c, float eps) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -169,7 +195,7 @@ layernorm_kernel(const float* __restrict__ x, float* __restrict__ y, const float
   for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
   const float rstd = 1.0f / sqrtf(q / (float)c + eps);
   float* yr = y + row * c;
-  for (int i = lane; i < c; i += 32) yr[i] = fmaf((xr[i] - mean) * rstd, gamma[i], beta[i]);
+  for (int i = lane; i < c; i += 32) yr[i] = ln_value(xr[i], mean, rstd, gamma[i], beta[i]);
 }
 
 // GEGLU: y[r][j] = x[r][j] * gelu(x[r][n + j]), exact (erf) gelu (ldm/modules/attention.py:37-44).
@@ -384,7 +410,19 @@ int modiff_layernorm(const float* x, float* y, const float* gamma, const float* 
   MODIFF_CHECK_ARG(x && y && gamma && beta && rows > 0 && c > 0, "bad argument");
   const int64_t blocks = ceil_div64(rows, 8);
   MODIFF_CHECK_ARG(blocks < (1ll << 31), "too many rows");
-  layernorm_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, y, gamma, beta, rows, c, eps);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = c % 4 == 0 && c <= kLnMaxChannels &&
+                   ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)gamma | (uintptr_t)beta) & 15) == 0);
+  if (vec) {
+    const unsigned grid = (unsigned)(blocks < 148 * 8 ? blocks : 148 * 8);
+    switch (ln_chunks_per_lane(c)) {
+      case 3: layernorm_kernel<3><<<grid, 256, 0, s>>>(x, y, gamma, beta, rows, c, eps); break;
+      case 5: layernorm_kernel<5><<<grid, 256, 0, s>>>(x, y, gamma, beta, rows, c, eps); break;
+      default: layernorm_kernel<10><<<grid, 256, 0, s>>>(x, y, gamma, beta, rows, c, eps); break;
+    }
+  } else {
+    layernorm_scalar_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, y, gamma, beta, rows, c, eps);
+  }
   MODIFF_LAUNCH_CHECK("layernorm_kernel");
   return MODIFF_OK;
 }

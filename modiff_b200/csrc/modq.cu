@@ -758,6 +758,107 @@ modq_flat_encode_kernel(const float4* __restrict__ x, float4* __restrict__ a_hat
 }
 
 
+// Linear layers whose input is LayerNorm(x) over the last dimension (the transformer blocks'
+// norm1 / norm2 / norm3 in front of to_q and the feed-forward projection,
+// ldm/modules/attention.py:229-241): the normalised tensor is never written.  A warp owns a row,
+// holds it in registers, takes its statistics exactly as layernorm_kernel<NV> does (same
+// functions, same bits) and evaluates the residual against the cached input, in both passes.
+// Symmetric per-tensor codes, one scale.
+template <int NV>
+__global__ void __launch_bounds__(kThreads)
+modq_ln_absmax_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, float eps, const float* __restrict__ a_hat,
+                      int64_t rows, int c, int n_levels, ModqScratch* __restrict__ scratch,
+                      float* __restrict__ x_scale) {
+  __shared__ float s0[kThreads / 32];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  constexpr int kWarps = kThreads / 32;
+  const int c4 = c >> 2;
+  float m = 0.0f;
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + wib; row < rows; row += (int64_t)gridDim.x * kWarps) {
+    float4 v[NV], av[NV];
+    ln_row_load<NV>(x + row * c, c4, lane, v);
+    ln_row_load<NV>(a_hat + row * c, c4, lane, av);
+    float mean, rstd;
+    ln_row_stats<NV>(v, c4, lane, eps, mean, rstd);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int idx = lane + 32 * k;
+      if (idx < c4) {
+        const float4 y = ln_value4(v[k], mean, rstd, __ldg(reinterpret_cast<const float4*>(gamma) + idx),
+                                   __ldg(reinterpret_cast<const float4*>(beta) + idx));
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(__fsub_rn(y.x, av[k].x)), fabsf(__fsub_rn(y.y, av[k].y))),
+                           fmaxf(fabsf(__fsub_rn(y.z, av[k].z)), fabsf(__fsub_rn(y.w, av[k].w)))));
+      }
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s0[wib] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kWarps; ++i) m = fmaxf(m, s0[i]);
+    if (m > 0.0f) atomicMax(&scratch->absmax_bits[0], __float_as_uint(m));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int bits = atomicExch(&scratch->absmax_bits[0], 0u);
+    double delta = (double)__uint_as_float(bits) / (double)n_levels;   // as modq_flat_absmax_kernel
+    if (delta < 1e-8) delta = 1e-8;
+    x_scale[0] = (float)delta;
+    scratch->counter = 0u;
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kThreads)
+modq_ln_encode_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, float eps, float* __restrict__ a_hat,
+                      uint32_t* __restrict__ codes, const float* __restrict__ x_scale, int64_t rows,
+                      int c, int n_levels) {
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  constexpr int kWarps = kThreads / 32;
+  const int c4 = c >> 2;
+  const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+  const float delta = x_scale[0];
+  const float inv = __frcp_rn(delta);
+  for (int64_t row = (int64_t)blockIdx.x * kWarps + wib; row < rows; row += (int64_t)gridDim.x * kWarps) {
+    float4 v[NV], av[NV];
+    ln_row_load<NV>(x + row * c, c4, lane, v);
+    float4* ar = reinterpret_cast<float4*>(a_hat + row * c);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {     // plain loads: this kernel writes the cache below
+      const int idx = lane + 32 * k;
+      av[k] = idx < c4 ? ar[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float mean, rstd;
+    ln_row_stats<NV>(v, c4, lane, eps, mean, rstd);
+    uint32_t* cr = codes + row * c4;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int idx = lane + 32 * k;
+      if (idx < c4) {
+        const float4 y = ln_value4(v[k], mean, rstd, __ldg(reinterpret_cast<const float4*>(gamma) + idx),
+                                   __ldg(reinterpret_cast<const float4*>(beta) + idx));
+        const float ys[4] = {y.x, y.y, y.z, y.w}, as[4] = {av[k].x, av[k].y, av[k].z, av[k].w};
+        float nv[4];
+        uint32_t qb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float qf = quantise_clamp(__fsub_rn(ys[j], as[j]), delta, inv, lo, hi, qb[j]);
+          nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
+        }
+        ar[idx] = make_float4(nv[0], nv[1], nv[2], nv[3]);
+        cr[idx] = pack_low_bytes(qb[0], qb[1], qb[2], qb[3]);
+      }
+    }
+  }
+}
+
 // GroupNorm statistics and the residual maximum in ONE sweep over the source.
 //
 // A block takes one (image, group) slab at a time and keeps it in registers (NV float4 per
@@ -1485,6 +1586,36 @@ extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                      (cudaStream_t)stream);
+}
+
+extern "C" int modiff_modq_ln(const float* x, const float* gamma, const float* beta, float eps,
+                              int64_t rows, int c, float* a_hat, int8_t* codes, float* x_scale,
+                              int n_bits, void* scratch, void* stream) {
+  MODIFF_CHECK_ARG(x && gamma && beta && a_hat && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(rows > 0 && c > 0 && c % 16 == 0 && c <= kLnMaxChannels,
+                   "rows %lld x channels %d: channels must be a positive multiple of 16, at most %d",
+                   (long long)rows, c, kLnMaxChannels);
+  MODIFF_CHECK_ARG(((((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)beta | (uintptr_t)a_hat |
+                      (uintptr_t)codes) & 15) == 0), "buffers must be 16-byte aligned");
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n_levels = sym_levels(n_bits);
+  int64_t blocks = ceil_div64(rows, kThreads / 32);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+#define MODIFF_LN_LAUNCH(NV)                                                                      \
+  modq_ln_absmax_kernel<NV><<<(int)blocks, kThreads, 0, s>>>(x, gamma, beta, eps, a_hat, rows, c,   \
+                                                            n_levels, (ModqScratch*)scratch, x_scale); \
+  MODIFF_LAUNCH_CHECK("modq_ln_absmax_kernel");                                                    \
+  modq_ln_encode_kernel<NV><<<(int)blocks, kThreads, 0, s>>>(x, gamma, beta, eps, a_hat,            \
+                                                            (uint32_t*)codes, x_scale, rows, c, n_levels)
+  switch (ln_chunks_per_lane(c)) {
+    case 3: { MODIFF_LN_LAUNCH(3); break; }
+    case 5: { MODIFF_LN_LAUNCH(5); break; }
+    default: { MODIFF_LN_LAUNCH(10); break; }
+  }
+#undef MODIFF_LN_LAUNCH
+  MODIFF_LAUNCH_CHECK("modq_ln_encode_kernel");
+  return MODIFF_OK;
 }
 
 extern "C" int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes,

@@ -430,9 +430,12 @@ class BasicTransformerBlock(nn.Module):
 
 def transformer_block_forward(blk, x, context=None):
     """qdiff/quant_block.py:249-256."""
-    x = ops.add(cross_attention_forward(blk.attn1, ops.layernorm(x, blk.norm1)), x)
-    x = ops.add(cross_attention_forward(blk.attn2, ops.layernorm(x, blk.norm2), context), x)
-    x = ops.add(blk.ff(ops.layernorm(x, blk.norm3)), x)
+    # quantised consumers normalise the rows inside their quantiser passes (no LayerNorm output)
+    a1, a2 = blk.attn1, blk.attn2
+    x = ops.add(cross_attention_forward(
+        a1, ops.layernorm_source(x, blk.norm1, a1.to_q, a1.to_k, a1.to_v)), x)
+    x = ops.add(cross_attention_forward(a2, ops.layernorm_source(x, blk.norm2, a2.to_q), context), x)
+    x = ops.add(blk.ff(ops.layernorm_source(x, blk.norm3, blk.ff.net[0].proj)), x)
     return x
 
 

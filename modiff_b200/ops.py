@@ -54,6 +54,8 @@ class ActSource:
     normalised tensor is never written); everything else calls `materialize()`.
     """
 
+    layernorm = None          # set by LayerNormSource
+
     def __init__(self, x0, x1=None, chan_bias=None, norm=None, silu=False, film=None):
         _req(x0, x1, chan_bias, film)
         self.film = None if film is None else film.contiguous()   # [B, 2C] scale | shift
@@ -162,6 +164,56 @@ def layernorm(x, norm):
     _lib.call('modiff_layernorm', x.data_ptr(), y.data_ptr(), norm.weight.data_ptr(),
               norm.bias.data_ptr(), x.numel() // c, c, float(norm.eps), _lib.stream_ptr())
     return y
+
+
+class LayerNormSource(ActSource):
+    """A linear layer's input that is nn.LayerNorm(x) over the last dimension and has not been
+    written: a modulated `QuantModule` normalises the rows inside its quantiser passes
+    (`modiff_modq_ln`); every other consumer calls `materialize()`."""
+
+    def __init__(self, x, norm):
+        _req(x)
+        self.x0 = x.contiguous()
+        self.x1 = self.chan_bias = self.film = self.norm = None
+        self.silu = False
+        self.layernorm = norm
+        if self.x0.shape[-1] != norm.normalized_shape[-1] or len(norm.normalized_shape) != 1:
+            raise ModiffError(f"LayerNorm{tuple(norm.normalized_shape)} on a tensor of shape "
+                              f"{tuple(self.x0.shape)}")
+        self.shape = self.x0.shape
+        self.device = self.x0.device
+        self.dtype = self.x0.dtype
+        self.is_cuda = True
+        self._stats = self._tensor = self._struct = None
+
+    @property
+    def trivial(self):
+        return False
+
+    def pending_norm(self):
+        return False
+
+    def materialize(self):
+        if self._tensor is None:
+            self._tensor = layernorm(self.x0, self.layernorm)
+        return self._tensor
+
+    def affine(self):
+        raise ModiffError("a LayerNorm source has no per-channel table; materialize() it")
+
+    struct = raw_struct = affine
+
+
+def layernorm_source(x, norm, *consumers):
+    """LayerNorm(x) for layers that can read it lazily (every consumer a quantised layer of this
+    package), else the normalised tensor."""
+    from .quant_layer import QuantModule
+    if LayerNormSource.enabled and consumers and all(isinstance(c, QuantModule) for c in consumers):
+        return LayerNormSource(x, norm)
+    return layernorm(x, norm)
+
+
+LayerNormSource.enabled = os.environ.get("MODIFF_FUSE_LAYERNORM", "1") != "0"
 
 
 def geglu(x):

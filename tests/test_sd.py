@@ -142,3 +142,41 @@ def test_sd_layer_shapes_teacher_forced(cuda, kind, shape, cout):
                 assert float(ours.act_quantizer.delta) == float(orc.last['x_scale'][0])
                 assert torch.equal(ours.a_hat.cpu(), orc.a_hat)
     assert m.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,c,cout,bits", [(2 * 4096, 320, 320, 8), (300, 640, 5120, 8),
+                                             (77, 1280, 1280, 6)])
+def test_layernorm_inside_the_quantiser_equals_the_separate_kernel(cuda, rows, c, cout, bits):
+    """A transformer block's LayerNorm in front of a quantised linear layer is evaluated inside
+    the quantiser's two passes (modiff_modq_ln): cached input, codes' effect (the output) and
+    scale equal, bit for bit, what the stand-alone LayerNorm kernel followed by the plain
+    quantiser gives, over several steps."""
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(c, cout, bias=False)
+    norm = torch.nn.LayerNorm(c)
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+        norm.bias.normal_(0, 0.3)
+    norm = norm.to(cuda)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    mods = []
+    for _ in range(2):
+        q = m.QuantModule(lin, wq, aq, modulate=True).to(cuda)
+        q.set_quant_state(True, True)
+        mods.append(q)
+    x = torch.randn(2, rows // 2 if rows % 2 == 0 else rows, c, device=cuda) if rows % 2 == 0 \
+        else torch.randn(1, rows, c, device=cuda)
+    for step in range(4):
+        x = x + 0.05 * torch.randn_like(x)
+        fused = mods[0](ops.LayerNormSource(x, norm))
+        plain = mods[1](ops.layernorm(x, norm))
+        assert torch.equal(fused, plain), step
+        assert torch.equal(mods[0].a_hat, mods[1].a_hat), step
+    bufs = [next(iter(q._geom_buffers.values())) for q in mods]
+    assert torch.equal(bufs[0].x_scale, bufs[1].x_scale)
+    assert torch.equal(bufs[0].codes, bufs[1].codes)
