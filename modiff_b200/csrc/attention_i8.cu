@@ -75,6 +75,27 @@ __global__ void __launch_bounds__(256) attn_absmax_kernel(const QuantParams p) {
       const float4 v = __ldg(x4 + i);
       mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
     }
+  } else if (inner % 4 == 0 && ((tv.sb | tv.sh | (cmajor ? tv.sc : tv.st)) & 3) == 0 &&
+             (reinterpret_cast<uintptr_t>(tv.x) & 15) == 0) {
+    // rows of the contiguous dimension, 16 bytes per load; short rows share a block
+    const int inner4 = inner >> 2;
+    const int rpb = inner4 >= 256 ? 1 : 256 / inner4;
+    const int sub = inner4 >= 256 ? 0 : (int)threadIdx.x / inner4;
+    const int col0 = inner4 >= 256 ? (int)threadIdx.x : (int)threadIdx.x % inner4;
+    const int step = inner4 >= 256 ? 256 : inner4;
+    if (sub < rpb) {
+      for (long long r = (long long)blockIdx.x * rpb + sub; r < rows; r += (long long)gridDim.x * rpb) {
+        const int o = (int)(r % outer);
+        const int bh = (int)(r / outer);
+        const int b = bh / p.heads, h = bh % p.heads;
+        const float4* base =
+            reinterpret_cast<const float4*>(cmajor ? elem(tv, b, h, o, 0) : elem(tv, b, h, 0, o));
+        for (int i = col0; i < inner4; i += step) {
+          const float4 v = __ldg(base + i);
+          mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+      }
+    }
   } else {
     // rows of the contiguous dimension; short rows share a block (256 / inner rows at a time)
     const int rpb = inner >= 256 ? 1 : 256 / inner;
@@ -702,8 +723,11 @@ extern "C" int modiff_attn_quantize(const float* q, const float* k, const float*
   p.d_rows = round_up(c, 16);
   p.tkp = round_up(tk, 128);
   cudaStream_t s = (cudaStream_t)stream;
-  const long long rows = (long long)batch * heads * (c > tq ? c : tq);
-  const int blocks = (int)(rows < 1184 ? rows : 1184);
+  // about 4096 elements per block of the largest tensor: small levels get small grids (fewer
+  // same-address atomics and no waves of idle blocks), large ones every SM eight times
+  const long long elems = (long long)batch * heads * c * (tq > tk ? tq : tk);
+  const long long want = (elems + 4095) / 4096;
+  const int blocks = (int)(want < 1 ? 1 : (want < 1184 ? want : 1184));
   attn_absmax_kernel<<<dim3(blocks, 3), 256, 0, s>>>(p);
   MODIFF_LAUNCH_CHECK("attn_absmax_kernel");
   const int tmax = tq > p.tkp ? tq : p.tkp;
