@@ -457,11 +457,16 @@ class SpatialTransformer(nn.Module):
     def forward(self, x, context=None):
         b, c, h, w = x.shape
         src = ops.ActSource(x, norm=self.norm, silu=False)
-        t = self.proj_in(src if _is_quant(self.proj_in) else src.materialize())
-        inner = t.shape[1]
-        t = ops.transpose_last2(t.reshape(b, inner, h * w))          # b (h w) c
+        if _is_quant(self.proj_in):
+            t = self.proj_in.forward_tokens_out(src)                 # b (h w) c, no rearrange
+        else:
+            t = self.proj_in(src.materialize())
+            t = ops.transpose_last2(t.reshape(b, t.shape[1], h * w))
+        inner = t.shape[2]
         for block in self.transformer_blocks:
             t = block(t, context)
+        if _is_quant(self.proj_out):
+            return ops.add(self.proj_out.forward_tokens_in(t, h, w), x)
         t = ops.transpose_last2(t).reshape(b, inner, h, w)
         return ops.add(self.proj_out(t), x)
 

@@ -942,6 +942,86 @@ class QuantModule(nn.Module):
             self._igemm(buf, pack, out, False, bias, g)
         return self.activation_function(out)
 
+    # ------------------------------------------------------------------ 1x1 convolutions around tokens
+    # SpatialTransformer.proj_in / proj_out (ldm/modules/attention.py:270-285) sit between NCHW
+    # feature maps and token-major [B, H*W, C] tensors.  A 1x1 convolution without padding is the
+    # same GEMM in either layout (its code planes [B][H][W][C] ARE token-major rows), so the layer
+    # can quantise in one layout and multiply in the other, and both `rearrange`s disappear: the
+    # private caches (a_hat of a token-major input, o_hat of a token-major output) simply live in
+    # the layout of the tensor they mirror.
+    relayout_fusion = os.environ.get("MODIFF_FUSE_RELAYOUT", "1") != "0"
+
+    def _relayout_ok(self):
+        aq = self.act_quantizer
+        k = self.fwd_kwargs
+        return (self.relayout_fusion and self.fwd_func is F.conv2d
+                and tuple(self.weight.shape[2:]) == (1, 1) and tuple(k['stride']) == (1, 1)
+                and not isinstance(k['padding'], str) and tuple(k['padding']) == (0, 0)
+                and tuple(self.implicit_pad) == (0, 0, 0, 0) and self.weight.shape[1] % 16 == 0
+                and self.modulate and self.use_act_quant and not self.disable_act_quant
+                and self.use_weight_quant and self.split == 0 and aq.dynamic and aq.sym
+                and not aq.channel_wise and not aq.running_stat)
+
+    def forward_tokens_out(self, input):
+        """1x1 convolution of an NCHW tensor (or `ops.ActSource`) returned token-major,
+        [B, H*W, Cout]: `rearrange(proj_in(x), 'b c h w -> b (h w) c')`."""
+        from .ops import ActSource, transpose_last2
+        b, c, h, w = input.shape
+        cout = self.weight.shape[0]
+        if not self._relayout_ok():
+            return transpose_last2(self.forward(input).reshape(b, cout, h * w))
+        if self.a_hat is None:
+            # first evaluation: the public path, then the cached output moves to token-major
+            y = self.forward(input)
+            self._o_tok = self._reuse(getattr(self, '_o_tok', None), (b, h * w, cout), y.device)
+            _lib.call('modiff_transpose', y.data_ptr(), self._o_tok.data_ptr(), b, cout, h * w,
+                      _lib.stream_ptr())
+            self.o_hat = self._o_tok
+            return self.o_hat if self.alias_output else self.o_hat.clone()
+        src = input if isinstance(input, ActSource) and not input.trivial else None
+        x = None
+        if src is None:
+            x = (input.x0 if isinstance(input, ActSource) else input).contiguous()
+        if tuple(self.a_hat.shape) != tuple(input.shape) or tuple(self.o_hat.shape) != (b, h * w, cout):
+            raise ModiffError(f"input shape {tuple(input.shape)} differs from the cached "
+                              f"{tuple(self.a_hat.shape)}; call reset_cache() first")
+        gc = self._geom(input, 0)
+        gl = ConvGeom(b * h * w, c, cout, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0)
+        pack = self._pack_weights(gc)
+        buf = self._get_buffers(gc, self.a_hat.device)
+        self._modq(x, self.a_hat, buf, gc, src)          # codes [B][H][W][C] = token-major rows
+        self._igemm(buf, pack, self.o_hat, True, None, gl)
+        return self.o_hat if self.alias_output else self.o_hat.clone()
+
+    def forward_tokens_in(self, tokens, h, w):
+        """1x1 convolution of a token-major tensor [B, H*W, Cin] returned as NCHW:
+        `proj_out(rearrange(x, 'b (h w) c -> b c h w'))`."""
+        from .ops import transpose_last2
+        _lib.require_cuda(tokens, "QuantModule input")
+        tokens = tokens.contiguous()
+        b, n, c = tokens.shape
+        cout = self.weight.shape[0]
+        if n != h * w:
+            raise ModiffError(f"{n} tokens do not make a {h} x {w} map")
+        if not self._relayout_ok():
+            return self.forward(transpose_last2(tokens).reshape(b, c, h, w))
+        if self.a_hat is None:
+            y = self.forward(transpose_last2(tokens).reshape(b, c, h, w))
+            self._a_tok = self._reuse(getattr(self, '_a_tok', None), tokens.shape, tokens.device)
+            self._a_tok.copy_(tokens)
+            self.a_hat = self._a_tok                   # the cached input mirrors the token layout
+            return y
+        if tuple(self.a_hat.shape) != tuple(tokens.shape) or tuple(self.o_hat.shape) != (b, cout, h, w):
+            raise ModiffError(f"input shape {tuple(tokens.shape)} differs from the cached "
+                              f"{tuple(self.a_hat.shape)}; call reset_cache() first")
+        gc = ConvGeom(b, c, cout, h, w, 1, 1, 1, 0, 0, 0, 0, 0)
+        gl = ConvGeom(b * n, c, cout, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0)
+        pack = self._pack_weights(gc)
+        buf = self._get_buffers(gc, tokens.device)
+        self._modq(tokens, self.a_hat, buf, gl, None)    # flat rows = the convolution's code planes
+        self._igemm(buf, pack, self.o_hat, True, None, gc)
+        return self.o_hat if self.alias_output else self.o_hat.clone()
+
     # ------------------------------------------------------------------ two layers, one tensor
     pair_quantisers = os.environ.get("MODIFF_PAIR_QUANTISERS", "1") != "0"
 

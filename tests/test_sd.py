@@ -180,3 +180,44 @@ def test_layernorm_inside_the_quantiser_equals_the_separate_kernel(cuda, rows, c
     bufs = [next(iter(q._geom_buffers.values())) for q in mods]
     assert torch.equal(bufs[0].x_scale, bufs[1].x_scale)
     assert torch.equal(bufs[0].codes, bufs[1].codes)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("b,cin,cout,hw", [(2, 320, 320, 32), (3, 640, 1280, 8)])
+def test_pointwise_convolutions_around_tokens_need_no_rearrange(cuda, b, cin, cout, hw):
+    """SpatialTransformer.proj_in / proj_out: the layer quantises in one layout and multiplies in
+    the other (its caches follow the token-major tensor), and gives the bits of
+    rearrange + convolution / convolution + rearrange, step after step."""
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(5)
+    conv = torch.nn.Conv2d(cin, cout, 1)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': 8, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+
+    def pair():
+        mods = []
+        for fused in (True, False):
+            q = m.QuantModule(conv, wq, aq, modulate=True).to(cuda)
+            q.set_quant_state(True, True)
+            q.relayout_fusion = fused
+            mods.append(q)
+        return mods
+
+    out_f, out_p = pair()          # NCHW in, tokens out
+    in_f, in_p = pair()            # tokens in, NCHW out
+    x = torch.randn(b, cin, hw, hw, device=cuda)
+    for step in range(4):
+        x = x + 0.05 * torch.randn_like(x)
+        tok_f, tok_p = out_f.forward_tokens_out(x), out_p.forward_tokens_out(x)
+        assert tuple(tok_f.shape) == (b, hw * hw, cout)
+        assert torch.equal(tok_f, tok_p), step
+        assert torch.equal(tok_f, ops.transpose_last2(out_p.o_hat.reshape(b, cout, hw * hw))), step
+        t = ops.transpose_last2(x.reshape(b, cin, hw * hw))
+        y_f, y_p = in_f.forward_tokens_in(t, hw, hw), in_p.forward_tokens_in(t, hw, hw)
+        assert tuple(y_f.shape) == (b, cout, hw, hw)
+        assert torch.equal(y_f, y_p), step
+        if step:
+            assert tuple(in_f.a_hat.shape) == (b, hw * hw, cin)          # cache in the token layout
+            assert torch.equal(ops.transpose_last2(in_f.a_hat).reshape(b, cin, hw, hw), in_p.a_hat)
