@@ -154,6 +154,15 @@ int modiff_modq_src(const modiff_act_source* src, float* a_hat, int8_t* codes, f
                     const modiff_conv_geom* g, int n_bits, int per_sample, void* scratch,
                     void* stream);
 
+/* modiff_modq for a linear layer whose input is GEGLU(h) = h[:, :n] * gelu(h[:, n:]) with the exact
+ * (erf) gelu (the feed-forward's second linear layer, ldm/modules/attention.py:37-64) over
+ * qdiff/quant_layer.py:325-336: both passes evaluate the gate on the fly with the arithmetic of
+ * modiff_geglu (same bits), so the gated tensor is never written.  Symmetric per-tensor dynamic codes.
+ *   h        fp32 [rows][2n], n a multiple of 16
+ *   a_hat    fp32 [rows][n] in/out;  codes int8 [rows][n];  x_scale fp32 [1] out;  scratch as modiff_modq */
+int modiff_modq_geglu(const float* h, int64_t rows, int n, float* a_hat, int8_t* codes, float* x_scale,
+                      int n_bits, void* scratch, void* stream);
+
 /* modiff_modq for a linear layer whose input is nn.LayerNorm(x) over the last dimension (the
  * transformer blocks' norm1 / norm2 / norm3 in front of to_q and the feed-forward projection,
  * ldm/modules/attention.py:229-241, qdiff/quant_block.py:249-256) over qdiff/quant_layer.py:325-336:

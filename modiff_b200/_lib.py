@@ -79,6 +79,7 @@ SIGNATURES = {
     "modiff_modq": (C.c_int, [_P, _P, _P, _P, _G, C.c_int, C.c_int, _P, _P]),
     "modiff_modq_fixed": (C.c_int, [C.POINTER(ActSourceStruct), _P, _P, _P, _P, _G, C.c_int, C.c_int,
                                     _P]),
+    "modiff_modq_geglu": (C.c_int, [_P, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P, _P]),
     "modiff_modq_ln": (C.c_int, [_P, _P, _P, C.c_float, C.c_int64, C.c_int, _P, _P, _P, C.c_int, _P, _P]),
     "modiff_modq_src": (C.c_int, [C.POINTER(ActSourceStruct), _P, _P, _P, _G, C.c_int, C.c_int, _P,
                                   _P]),
@@ -165,7 +166,7 @@ def lib():
 
 # kernels one successful call of an entry point launches (for launch accounting)
 KERNELS_PER_CALL = {
-    "modiff_weight_pack": 2, "modiff_weight_pack_rounded": 2, "modiff_modq_fixed": 1, "modiff_codes_fill_halo": 1, "modiff_asym_bias": 1, "modiff_igemm_conv_offset": 1, "modiff_modq": 2, "modiff_modq_ln": 2, "modiff_modq_src": 2, "modiff_modq_gn": 2, "modiff_modq_asym": 2, "modiff_modq_running": 3, "modiff_modq_up2": 2, "modiff_modq_gn_asym": 2, "modiff_modq_pair": 2, "modiff_modq_static": 2, "modiff_linear_group": 1, "modiff_attention_tc": 1, "modiff_igemm_conv": 1, "modiff_igemm_conv_add": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
+    "modiff_weight_pack": 2, "modiff_weight_pack_rounded": 2, "modiff_modq_fixed": 1, "modiff_codes_fill_halo": 1, "modiff_asym_bias": 1, "modiff_igemm_conv_offset": 1, "modiff_modq": 2, "modiff_modq_ln": 2, "modiff_modq_geglu": 2, "modiff_modq_src": 2, "modiff_modq_gn": 2, "modiff_modq_asym": 2, "modiff_modq_running": 3, "modiff_modq_up2": 2, "modiff_modq_gn_asym": 2, "modiff_modq_pair": 2, "modiff_modq_static": 2, "modiff_linear_group": 1, "modiff_attention_tc": 1, "modiff_igemm_conv": 1, "modiff_igemm_conv_add": 1, "modiff_conv_fp32": 1, "modiff_im2col_codes": 1, "modiff_split_bf16": 1, "modiff_split_bf16_rows": 1,
     "modiff_weights_bf16": 1, "modiff_weights_bf16_rounded": 1, "modiff_gemm_bf16": 1, "modiff_softmax_split": 1, "modiff_attention_small": 1,
     "modiff_fake_quant": 2, "modiff_groupnorm_silu": 1, "modiff_silu": 1, "modiff_layernorm": 1, "modiff_geglu": 1, "modiff_transpose": 1, "modiff_add": 1,
     "modiff_upsample2x": 1, "modiff_avgpool2x": 1, "modiff_concat_c": 1, "modiff_timestep_embedding": 1,

@@ -221,6 +221,12 @@ __device__ inline float4 ln_value4(float4 x, float mean, float rstd, float4 g, f
                      ln_value(x.z, mean, rstd, g.z, b.z), ln_value(x.w, mean, rstd, g.w, b.w));
 }
 
+// GEGLU with the exact (erf) gelu: a * gelu(g) (ldm/modules/attention.py:37-44).  One function for
+// every kernel that evaluates it, so they agree to the bit.
+__device__ inline float geglu_value(float a, float g) {
+  return a * (0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)));
+}
+
 // Symmetric activation code range of an n-bit quantiser
 // (n_levels = 2^(b-1) - 1; clamp(-n_levels - 1, n_levels)).
 __host__ __device__ inline int sym_levels(int n_bits) { return (1 << (n_bits - 1)) - 1; }

@@ -207,7 +207,7 @@ __global__ void geglu_kernel(const float* __restrict__ x, float* __restrict__ y,
     const int64_t r = i / n;
     const int j = (int)(i % n);
     const float a = x[r * 2 * n + j], g = x[r * 2 * n + n + j];
-    y[i] = a * (0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)));
+    y[i] = geglu_value(a, g);
   }
 }
 

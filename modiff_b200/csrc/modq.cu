@@ -859,6 +859,78 @@ modq_ln_encode_kernel(const float* __restrict__ x, const float* __restrict__ gam
   }
 }
 
+// Linear layers whose input is GEGLU(h) = h[:, :n] * gelu(h[:, n:]) (the feed-forward's second
+// linear layer, ldm/modules/attention.py:37-64): both passes evaluate the gate on the fly from the
+// projection's output [rows][2n] with geglu_kernel's own function (same bits); the gated tensor is
+// never written.  Symmetric per-tensor codes, one scale; n a multiple of 4.
+__device__ inline float4 geglu_load4(const float* __restrict__ h, int64_t i, int n4) {
+  const int64_t r = i / n4;
+  const int j = (int)(i - r * n4);
+  const float4* row = reinterpret_cast<const float4*>(h) + r * 2 * n4;
+  const float4 a = __ldg(row + j), g = __ldg(row + n4 + j);
+  return make_float4(geglu_value(a.x, g.x), geglu_value(a.y, g.y), geglu_value(a.z, g.z),
+                     geglu_value(a.w, g.w));
+}
+
+__global__ void __launch_bounds__(kThreads)
+modq_geglu_absmax_kernel(const float* __restrict__ h, const float4* __restrict__ a_hat, int64_t total4,
+                         int n4, int n_levels, ModqScratch* __restrict__ scratch,
+                         float* __restrict__ x_scale) {
+  __shared__ float s0[kThreads / 32];
+  __shared__ bool is_last;
+  float m = 0.0f;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+    const float4 y = geglu_load4(h, i, n4);
+    const float4 av = __ldg(a_hat + i);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(__fsub_rn(y.x, av.x)), fabsf(__fsub_rn(y.y, av.y))),
+                       fmaxf(fabsf(__fsub_rn(y.z, av.z)), fabsf(__fsub_rn(y.w, av.w)))));
+  }
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) s0[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, s0[i]);
+    if (m > 0.0f) atomicMax(&scratch->absmax_bits[0], __float_as_uint(m));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&scratch->counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int bits = atomicExch(&scratch->absmax_bits[0], 0u);
+    double delta = (double)__uint_as_float(bits) / (double)n_levels;   // as modq_flat_absmax_kernel
+    if (delta < 1e-8) delta = 1e-8;
+    x_scale[0] = (float)delta;
+    scratch->counter = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+modq_geglu_encode_kernel(const float* __restrict__ h, float4* __restrict__ a_hat,
+                         uint32_t* __restrict__ codes, const float* __restrict__ x_scale,
+                         int64_t total4, int n4, int n_levels) {
+  const float lo = (float)(-n_levels - 1), hi = (float)n_levels;
+  const float delta = x_scale[0];
+  const float inv = __frcp_rn(delta);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+    const float4 y = geglu_load4(h, i, n4);
+    const float4 av = a_hat[i];
+    const float ys[4] = {y.x, y.y, y.z, y.w}, as[4] = {av.x, av.y, av.z, av.w};
+    float nv[4];
+    uint32_t qb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float qf = quantise_clamp(__fsub_rn(ys[j], as[j]), delta, inv, lo, hi, qb[j]);
+      nv[j] = __fadd_rn(as[j], __fmul_rn(qf, delta));
+    }
+    a_hat[i] = make_float4(nv[0], nv[1], nv[2], nv[3]);
+    codes[i] = pack_low_bytes(qb[0], qb[1], qb[2], qb[3]);
+  }
+}
+
 // GroupNorm statistics and the residual maximum in ONE sweep over the source.
 //
 // A block takes one (image, group) slab at a time and keeps it in registers (NV float4 per
@@ -1586,6 +1658,28 @@ extern "C" int modiff_modq(const float* x, float* a_hat, int8_t* codes, float* x
   MODIFF_CHECK_ARG(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
   return launch_modq(x, a_hat, codes, x_scale, g, n_bits, per_sample, scratch, true,
                      (cudaStream_t)stream);
+}
+
+extern "C" int modiff_modq_geglu(const float* h, int64_t rows, int n, float* a_hat, int8_t* codes,
+                                 float* x_scale, int n_bits, void* scratch, void* stream) {
+  MODIFF_CHECK_ARG(h && a_hat && codes && x_scale && scratch, "NULL pointer argument");
+  MODIFF_CHECK_ARG(rows > 0 && n > 0 && n % 16 == 0, "rows %lld x channels %d: channels must be a "
+                   "positive multiple of 16", (long long)rows, n);
+  MODIFF_CHECK_ARG(n_bits >= 2 && n_bits <= 8, "activation n_bits %d outside [2, 8]", n_bits);
+  MODIFF_CHECK_ARG(((((uintptr_t)h | (uintptr_t)a_hat | (uintptr_t)codes) & 15) == 0),
+                   "buffers must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n_levels = sym_levels(n_bits);
+  const int64_t total4 = rows * (n / 4);
+  int64_t blocks = ceil_div64(total4, kThreads);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  modq_geglu_absmax_kernel<<<(int)blocks, kThreads, 0, s>>>(h, (const float4*)a_hat, total4, n / 4,
+                                                           n_levels, (ModqScratch*)scratch, x_scale);
+  MODIFF_LAUNCH_CHECK("modq_geglu_absmax_kernel");
+  modq_geglu_encode_kernel<<<(int)blocks, kThreads, 0, s>>>(h, (float4*)a_hat, (uint32_t*)codes, x_scale,
+                                                           total4, n / 4, n_levels);
+  MODIFF_LAUNCH_CHECK("modq_geglu_encode_kernel");
+  return MODIFF_OK;
 }
 
 extern "C" int modiff_modq_ln(const float* x, const float* gamma, const float* beta, float eps,

@@ -338,7 +338,8 @@ class FeedForward(nn.Module):
                                  nn.Linear(inner_dim, dim_out))
 
     def forward(self, x):
-        return self.net[2](self.net[0](x))
+        # a quantised second layer evaluates the gate inside its quantiser passes
+        return self.net[2](ops.geglu_source(self.net[0].proj(x), self.net[2]))
 
 
 class CrossQKMatMul(nn.Module):

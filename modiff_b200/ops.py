@@ -55,6 +55,7 @@ class ActSource:
     """
 
     layernorm = None          # set by LayerNormSource
+    geglu = False             # set by GegluSource
 
     def __init__(self, x0, x1=None, chan_bias=None, norm=None, silu=False, film=None):
         _req(x0, x1, chan_bias, film)
@@ -202,6 +203,54 @@ class LayerNormSource(ActSource):
         raise ModiffError("a LayerNorm source has no per-channel table; materialize() it")
 
     struct = raw_struct = affine
+
+
+class GegluSource(ActSource):
+    """A linear layer's input that is GEGLU(h) = h[..., :n] * gelu(h[..., n:]) and has not been
+    written: a modulated `QuantModule` evaluates the gate inside its quantiser passes
+    (`modiff_modq_geglu`); every other consumer calls `materialize()`."""
+
+    def __init__(self, h):
+        _req(h)
+        self.x0 = h.contiguous()
+        self.x1 = self.chan_bias = self.film = self.norm = None
+        self.silu = False
+        self.geglu = True
+        if self.x0.shape[-1] % 2:
+            raise ModiffError(f"GEGLU needs an even last dimension, got {tuple(self.x0.shape)}")
+        self.shape = torch.Size(tuple(self.x0.shape[:-1]) + (self.x0.shape[-1] // 2,))
+        self.device = self.x0.device
+        self.dtype = self.x0.dtype
+        self.is_cuda = True
+        self._stats = self._tensor = self._struct = None
+
+    @property
+    def trivial(self):
+        return False
+
+    def pending_norm(self):
+        return False
+
+    def materialize(self):
+        if self._tensor is None:
+            self._tensor = geglu(self.x0)
+        return self._tensor
+
+    def affine(self):
+        raise ModiffError("a GEGLU source has no per-channel table; materialize() it")
+
+    struct = raw_struct = affine
+
+
+def geglu_source(h, consumer):
+    """GEGLU(h) for a quantised consumer that can read it lazily, else the gated tensor."""
+    from .quant_layer import QuantModule
+    if GegluSource.enabled and isinstance(consumer, QuantModule):
+        return GegluSource(h)
+    return geglu(h)
+
+
+GegluSource.enabled = os.environ.get("MODIFF_FUSE_GEGLU", "1") != "0"
 
 
 def layernorm_source(x, norm, *consumers):

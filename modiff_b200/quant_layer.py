@@ -499,6 +499,17 @@ class QuantModule(nn.Module):
                           tag=g.key())
                 return
             x, src = src.materialize(), None
+        if src is not None and src.geglu:
+            # GEGLU in front of the feed-forward's second linear layer: gated inside both passes
+            if (aq.dynamic and aq.sym and not aq.channel_wise and not aq.running_stat
+                    and a_hat is not None and g.split == 0 and g.h * g.w == 1 and g.kh * g.kw == 1
+                    and g.cin % 16 == 0):
+                _lib.call('modiff_modq_geglu', src.x0.data_ptr(), g.batch, g.cin, a_hat.data_ptr(),
+                          buf.codes.data_ptr(), buf.x_scale.data_ptr(), aq.n_bits,
+                          buf.scratch.data_ptr(), _lib.stream_ptr(), nbytes=13 * src.numel(),
+                          tag=g.key())
+                return
+            x, src = src.materialize(), None
         first_static = (not aq.dynamic) and not buf.scale_set
         if aq.running_stat or (first_static and aq.leaf_param and not aq.channel_wise):
             # moving-average ranges (act_momentum_update, quant_layer.py:113-132), and the first

@@ -221,3 +221,35 @@ def test_pointwise_convolutions_around_tokens_need_no_rearrange(cuda, b, cin, co
         if step:
             assert tuple(in_f.a_hat.shape) == (b, hw * hw, cin)          # cache in the token layout
             assert torch.equal(ops.transpose_last2(in_f.a_hat).reshape(b, cin, hw, hw), in_p.a_hat)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,n,cout,bits", [(2 * 1024, 1280, 320, 8), (154, 2560, 640, 8),
+                                             (77, 5120, 1280, 6)])
+def test_geglu_inside_the_quantiser_equals_the_separate_kernel(cuda, rows, n, cout, bits):
+    """The feed-forward's gate in front of its quantised second linear layer is evaluated inside
+    the quantiser's two passes (modiff_modq_geglu): same cached input, codes, scale and output,
+    bit for bit, as the stand-alone GEGLU kernel followed by the plain quantiser."""
+    import modiff_b200 as m
+    from modiff_b200 import ops
+    torch.manual_seed(4)
+    lin = torch.nn.Linear(n, cout)
+    wq = {'n_bits': 8, 'channel_wise': True, 'scale_method': 'max'}
+    aq = {'n_bits': bits, 'symmetric': True, 'channel_wise': False, 'scale_method': 'max',
+          'leaf_param': True, 'dynamic': True}
+    mods = []
+    for _ in range(2):
+        q = m.QuantModule(lin, wq, aq, modulate=True).to(cuda)
+        q.set_quant_state(True, True)
+        mods.append(q)
+    h = torch.randn(1, rows, 2 * n, device=cuda)
+    for step in range(4):
+        h = h + 0.05 * torch.randn_like(h)
+        fused = mods[0](ops.GegluSource(h))
+        plain = mods[1](ops.geglu(h))
+        assert tuple(fused.shape) == (1, rows, cout)
+        assert torch.equal(fused, plain), step
+        assert torch.equal(mods[0].a_hat, mods[1].a_hat), step
+    bufs = [next(iter(q._geom_buffers.values())) for q in mods]
+    assert torch.equal(bufs[0].x_scale, bufs[1].x_scale)
+    assert torch.equal(bufs[0].codes, bufs[1].codes)
