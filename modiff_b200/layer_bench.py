@@ -32,6 +32,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=int, default=_lib.IMPL_AUTO)
     ap.add_argument("--linear", action="store_true")
+    ap.add_argument("--layernorm", action="store_true",
+                    help="with --linear: the input is LayerNorm(x), evaluated inside the quantiser")
+    ap.add_argument("--geglu", action="store_true",
+                    help="with --linear: the input is GEGLU(h), h of 2*cin features, evaluated "
+                         "inside the quantiser")
     ap.add_argument("--static", action="store_true",
                     help="non-dynamic activation quantiser: the scale of the first quantised call "
                          "stays and later calls are the one-pass modiff_modq_fixed")
@@ -120,7 +125,7 @@ def main():
         return
     if args.linear:
         org = nn.Linear(args.cin, args.cout)
-        shape = (args.batch, args.cin)
+        shape = (args.batch, 2 * args.cin if args.geglu else args.cin)
     else:
         pad = args.k // 2 if args.stride == 1 else 0
         org = nn.Conv2d(args.cin, args.cout, args.k, stride=args.stride, padding=pad)
@@ -138,8 +143,15 @@ def main():
     drift = [0.05 * torch.randn(shape, device=dev) for _ in range(2)]
     kw = dict(split=args.split) if args.split else {}
     norm = nn.GroupNorm(32, args.cin, eps=1e-6).to(dev) if args.fused else None
+    lnorm = nn.LayerNorm(args.cin).to(dev) if args.layernorm else None
 
     def feed(t):
+        if lnorm is not None:
+            from .ops import LayerNormSource
+            return LayerNormSource(t, lnorm)
+        if args.geglu:
+            from .ops import GegluSource
+            return GegluSource(t)
         if norm is None:
             return t
         from .ops import ActSource
@@ -157,6 +169,7 @@ def main():
     status = _lib.device_status()
     out = {"geometry": vars(args), "device_status": status}
     for name in ("modiff_modq", "modiff_modq_src", "modiff_modq_gn", "modiff_modq_fixed",
+                 "modiff_modq_ln", "modiff_modq_geglu", "modiff_layernorm", "modiff_geglu",
                  "modiff_modq_asym", "modiff_codes_fill_halo", "modiff_groupnorm_silu",
                  "modiff_igemm_conv", "modiff_igemm_conv_offset"):
         if name not in summ:
